@@ -1,0 +1,80 @@
+// Device-side codecs for the storage formats the engine reads as-is: e2m1 (fp4) pairs,
+// e4m3 (fp8), e8m0 block exponents, bf16.  Host-side twins live in rt/codec.h.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace dgpp {
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+__device__ __forceinline__ float bf16_to_f32(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ bf16 f32_to_bf16(float v) { return __float2bfloat16_rn(v); }
+
+// e4m3 byte -> float (exact).
+__device__ __forceinline__ float e4m3_to_f32(uint8_t v) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(v, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+// two e4m3 bytes (low byte first) -> half2 (exact).
+__device__ __forceinline__ __half2 e4m3x2_to_h2(uint16_t v) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(v, __NV_E4M3);
+  return *reinterpret_cast<__half2*>(&h);
+}
+// float -> e4m3 byte, round-to-nearest-even, saturating to +-448.
+__device__ __forceinline__ uint8_t f32_to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+// e8m0 exponent byte -> float 2^(e-127); 255 is NaN by the MX spec.
+__device__ __forceinline__ float e8m0_to_f32(uint8_t e) {
+  if (e == 255) return __int_as_float(0x7fc00000);
+  if (e == 0) return __int_as_float(0x00400000);  // 2^-127 (subnormal)
+  return __int_as_float(static_cast<int>(e) << 23);
+}
+
+// One byte holding two e2m1 codes (low nibble = even element) -> half2 {even, odd}, exact.
+__device__ __forceinline__ __half2 e2m1x2_to_h2(uint8_t b) {
+  uint32_t out;
+  uint16_t in = b;
+  asm("{\n\t.reg .b8 lo, hi;\n\t"
+      "mov.b16 {lo, hi}, %1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, lo;\n\t}\n"
+      : "=r"(out)
+      : "h"(in));
+  return *reinterpret_cast<__half2*>(&out);
+}
+// Software decode of one e2m1 code (sign, 2-bit exponent, 1-bit mantissa).
+__host__ __device__ __forceinline__ float e2m1_to_f32(uint32_t c) {
+  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  float m = mag[c & 7];
+  return (c & 8) ? -m : m;
+}
+// Round a float (already divided by its block scale) to the nearest e2m1 code, ties to even code.
+__host__ __device__ __forceinline__ uint32_t f32_to_e2m1(float v) {
+  uint32_t s = v < 0.f ? 8u : 0u;
+  float a = v < 0.f ? -v : v;
+  uint32_t c;
+  if (a <= 0.25f) c = 0;            // 0 | 0.5 midpoint 0.25 -> even code 0
+  else if (a < 0.75f) c = 1;        // 0.5 | 1.0 midpoint 0.75 -> even code 2
+  else if (a <= 1.25f) c = 2;       // 1.0 | 1.5 midpoint 1.25 -> even code 2
+  else if (a < 1.75f) c = 3;        // 1.5 | 2.0 midpoint 1.75 -> even code 4
+  else if (a <= 2.5f) c = 4;        // 2 | 3 midpoint 2.5 -> even code 4
+  else if (a < 3.5f) c = 5;         // 3 | 4 midpoint 3.5 -> even code 6
+  else if (a <= 5.f) c = 6;         // 4 | 6 midpoint 5 -> even code 6
+  else c = 7;
+  return s | c;
+}
+
+union Pack16 {
+  uint4 u;
+  bf16 h[8];
+  bf162 h2[4];
+  uint8_t b[16];
+  uint16_t s[8];
+  uint32_t w[4];
+};
+
+}  // namespace dgpp

@@ -1,0 +1,498 @@
+// Linear layer on the 5th-generation tensor cores:   C[T, N] = alpha * X[T, K] . W[N, K]^T
+//
+// The weight tile is always the UMMA "A" operand (128 weight rows = 128 TMEM lanes) and the
+// activation rows are the "B" operand (BN = 16..256 tokens = TMEM columns), so the same kernel
+// serves decode (a handful of rows, pure weight streaming) and prefill (thousands of rows).
+// Accumulators are fp32 in TMEM; inputs to tcgen05.mma are 16-bit floats.
+//
+// Weight sources (WMODE):
+//   0  bf16 [N, K]                      TMA (128B swizzle) straight into the MMA stage
+//   1  NVFP4: e2m1 pairs [N, K/2] + e4m3 scale per 16 [N, K/16]
+//        TMA brings the packed bytes and their scales as stored; eight converter warps expand
+//        them into a 16-bit K-major swizzled stage (exact: e2m1 * e4m3 fits 16-bit floats), the
+//        fp32 tensor scale is `alpha` in the epilogue.  No dequantised copy ever reaches HBM.
+//   2  FP8 e4m3 [N, K] with one fp32 scale per 128x128 block [N/128, K/128]
+//        converter warps write bf16(e4m3 * scale).
+//   3  MXFP4: e2m1 pairs + e8m0 scale per 32 [N, K/32]   (scales read with plain loads)
+//
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..9 = converters (quantised modes), warps 2..5 = epilogue (TMEM -> registers -> global).
+// Split-K: grid.z CTAs write fp32 partials to a workspace; the last CTA to arrive on a tile's
+// counter folds them in ascending split order (deterministic) and resets the counter.
+//
+// Every wait is bounded; on expiry the kernel records a status code, unwinds and frees TMEM.
+// (reference counterparts: src/kernels/moe_w4a4.cu:476 dense_w4a4_tma_kernel, src/kernels/fp4w_gemm.cu:71,
+//  src/kernels/fp8w_gemm.cu:84, src/kernels/gemm_cublaslt.cpp -- all mma.sync / library there.)
+#include <cuda.h>
+#include <dlfcn.h>
+#include <string.h>
+
+#include "common/common.h"
+#include "common/dtypes.cuh"
+#include "common/ptx.cuh"
+
+namespace dgpp {
+
+constexpr int kBM = 128;          // weight rows per CTA (UMMA M)
+constexpr int kBK = 64;           // K elements per MMA stage (one 128-byte swizzle row of 16-bit values)
+constexpr int kGemmThreads = 320;
+constexpr int kConvWarps = 8;
+
+struct GemmParams {
+  float alpha;
+  bf16* out;               // [T, ldc] bf16 (may be null when out32 is set)
+  float* out32;            // [T, ldc] fp32 (optional)
+  const bf16* resid;       // optional residual added in the epilogue: out = bf16(resid + bf16(alpha*acc))
+  float* ws;               // split-K partials [splits, T, N] fp32
+  uint32_t* counters;      // split-K tile counters [n_tiles * m_tiles], zero at rest
+  const float* blk_scale;  // WMODE 2: [ceil(N/128), K/128] fp32
+  const uint8_t* sf_plain; // WMODE 3: e8m0 scales [N, K/32]
+  DeviceStatus* status;
+  int T, N, K, ldc;
+  int kb_per_split;        // k64 blocks per split
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStageB = BN * 128;                 // bytes
+  static constexpr int kStageA = kBM * 128;                // 16 KB
+  static constexpr int kStageRaw = kBM * 128;              // 16 KB packed fp4 (256 K per row) / fp8 (128 K per row)
+  static constexpr int kStageSf = kBM * 16;                // 2 KB
+};
+
+__device__ __forceinline__ void report(DeviceStatus* st, int code, int detail) {
+  if (atomicCAS(&st->code, 0, code) == 0) st->detail = detail;
+  atomicAdd(&st->count, 1);
+}
+
+// Bounded mbarrier wait with a wall-clock limit (~2 s); false on expiry.
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    for (int i = 0; i < 2048; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > 2000000000ull) return false;
+  }
+}
+
+// WMODE: 0 bf16, 1 nvfp4, 2 fp8 block, 3 mxfp4.  AF16: converted operand is f16 (1) or bf16 (0).
+template <int BN, int WMODE, int AF16, int SB, int SA, int SR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or packed raw weights (uint8)
+               const __grid_constant__ CUtensorMap tmB,   // activations bf16 [T, K]
+               const __grid_constant__ CUtensorMap tmSf,  // NVFP4 scales (uint8) [N, K/16]
+               GemmParams p) {
+  using L = GemmSmem<BN>;
+  constexpr bool kQuant = WMODE != 0;
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  // carve shared memory (all tile bases 1024-byte aligned)
+  unsigned char* sp = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned char* sB = sp;                   sp += SB * L::kStageB;
+  sp = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sp) + 1023) & ~uintptr_t(1023));
+  unsigned char* sA = sp;                   sp += (kQuant ? SA : SB) * L::kStageA;
+  unsigned char* sRaw = sp;                 sp += kQuant ? SR * L::kStageRaw : 0;
+  unsigned char* sSf = sp;                  sp += (WMODE == 1) ? SR * L::kStageSf : 0;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sp);
+  uint64_t* b_full = bars;                  // [SB]
+  uint64_t* b_empty = b_full + SB;          // [SB]
+  uint64_t* a_full = b_empty + SB;          // [SA]
+  uint64_t* a_empty = a_full + SA;          // [SA]
+  uint64_t* raw_full = a_empty + SA;        // [SR]
+  uint64_t* raw_empty = raw_full + SR;      // [SR]
+  uint64_t* acc_full = raw_empty + SR;      // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kBM;
+  const int m0 = blockIdx.y * BN;
+  const int split = blockIdx.z, splits = gridDim.z;
+  const int num_kb_total = p.K / kBK;
+  const int kb_begin = split * p.kb_per_split;
+  const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
+  const int nkb = max(0, kb_end - kb_begin);
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+    for (int i = 0; i < SA; ++i) { mbar_init(&a_full[i], kConvWarps); mbar_init(&a_empty[i], 1); }
+    for (int i = 0; i < SR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kConvWarps); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (WMODE == 1) tma_prefetch_desc(&tmSf);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      for (int i = 0; i < nkb; ++i) {
+        const int kb = kb_begin + i;
+        if (kQuant) {
+          // raw weight stage: WMODE 1/3 cover 256 K (4 k64 blocks), WMODE 2 covers 128 K (2 k64 blocks)
+          constexpr int kSubs = (WMODE == 2) ? 2 : 4;
+          if (i % kSubs == 0) {
+            const int r = i / kSubs, sr = r % SR;
+            if (!wait_bar(&raw_empty[sr], ((r / SR) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 1); *abort_flag = 1; break; }
+            const uint32_t bytes = L::kStageRaw + (WMODE == 1 ? L::kStageSf : 0);
+            mbar_expect_tx(&raw_full[sr], bytes);
+            // packed bytes: x in bytes. fp4: kb*32 bytes; fp8: kb*64 bytes
+            const int xb = (WMODE == 2) ? kb * 64 : kb * 32;
+            tma_load_2d(sRaw + sr * L::kStageRaw, &tmA, xb, n0, &raw_full[sr]);
+            if (WMODE == 1) tma_load_2d(sSf + sr * L::kStageSf, &tmSf, kb * 4, n0, &raw_full[sr]);
+          }
+        }
+        const int sb = i % SB;
+        if (!wait_bar(&b_empty[sb], ((i / SB) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 2); *abort_flag = 1; break; }
+        mbar_expect_tx(&b_full[sb], L::kStageB + (kQuant ? 0 : L::kStageA));
+        tma_load_2d(sB + sb * L::kStageB, &tmB, kb * kBK, m0, &b_full[sb]);
+        if (!kQuant) tma_load_2d(sA + sb * L::kStageA, &tmA, kb * kBK, n0, &b_full[sb]);
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, (kQuant && AF16) ? 0u : 1u, 1u);
+      for (int i = 0; i < nkb; ++i) {
+        const int sb = i % SB;
+        if (!wait_bar(&b_full[sb], (i / SB) & 1)) { report(p.status, kTimeoutTmaFull, 3); *abort_flag = 1; break; }
+        uint32_t a_addr;
+        if (kQuant) {
+          const int sa = i % SA;
+          if (!wait_bar(&a_full[sa], (i / SA) & 1)) { report(p.status, kTimeoutConvert, 4); *abort_flag = 1; break; }
+          a_addr = smem_u32(sA + sa * L::kStageA);
+        } else {
+          a_addr = smem_u32(sA + sb * L::kStageA);
+        }
+        tc_fence_after();
+        const uint32_t b_addr = smem_u32(sB + sb * L::kStageB);
+#pragma unroll
+        for (int kk = 0; kk < kBK / 16; ++kk) {
+          umma_f16(tmem_base, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32), idesc,
+                   (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&b_empty[sb]);
+        if (kQuant) umma_commit(&a_empty[i % SA]);
+        if (*abort_flag) break;
+      }
+      umma_commit(acc_full);
+    }
+  } else if (kQuant) {
+    // ------------------------------------------------------------------ converters (warps 2..9)
+    const int ct = threadIdx.x - 64;       // 0..255
+    const int row = ct >> 1, half = ct & 1;
+    constexpr int kSubs = (WMODE == 2) ? 2 : 4;
+    for (int i = 0; i < nkb; ++i) {
+      const int r = i / kSubs, sub = i % kSubs, sr = r % SR, sa = i % SA;
+      bool ok = true;
+      if (sub == 0) ok = wait_bar(&raw_full[sr], (r / SR) & 1);
+      if (ok) ok = wait_bar(&a_empty[sa], ((i / SA) & 1) ^ 1);
+      if (!ok) { report(p.status, kTimeoutTmaFull, 5); *abort_flag = 1; break; }
+      const unsigned char* raw = sRaw + sr * L::kStageRaw + row * 128;
+      unsigned char* dst = sA + sa * L::kStageA + row * 128;
+      const int kb = kb_begin + i;
+      if (WMODE == 1 || WMODE == 3) {
+        // 32 weights = 16 packed bytes at logical 16-byte chunk (sub*2 + half) of the swizzled 128-byte row
+        const int cl = sub * 2 + half;
+        Pack16 w;
+        w.u = *reinterpret_cast<const uint4*>(raw + ((cl ^ (row & 7)) << 4));
+        float s0f, s1f;
+        if (WMODE == 1) {
+          const unsigned char* sf = sSf + sr * L::kStageSf + row * 16 + sub * 4 + half * 2;
+          s0f = e4m3_to_f32(sf[0]);
+          s1f = e4m3_to_f32(sf[1]);
+        } else {
+          const int nrow = min(n0 + row, p.N - 1);
+          const uint8_t e = p.sf_plain[static_cast<size_t>(nrow) * (p.K / 32) + kb * 2 + half];
+          s0f = s1f = e8m0_to_f32(e);
+        }
+        Pack16 o[4];
+        if (AF16) {
+          const __half2 s0 = __float2half2_rn(s0f), s1 = __float2half2_rn(s1f);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            __half2 h = __hmul2(e2m1x2_to_h2(w.b[j]), j < 8 ? s0 : s1);
+            o[j >> 2].w[j & 3] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else {
+          // f16 bits >> 3 read as bf16 equal value * 2^-112; fold 2^112 into the (exact) bf16 scale
+          const bf162 s0 = __float2bfloat162_rn(s0f * 5.192296858534828e33f);
+          const bf162 s1 = __float2bfloat162_rn(s1f * 5.192296858534828e33f);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            __half2 h = e2m1x2_to_h2(w.b[j]);
+            const uint32_t hb = *reinterpret_cast<uint32_t*>(&h);
+            uint32_t bb = ((hb & 0x7FFF7FFFu) >> 3) | (hb & 0x80008000u);
+            bf162 v = __hmul2(*reinterpret_cast<bf162*>(&bb), j < 8 ? s0 : s1);
+            o[j >> 2].w[j & 3] = *reinterpret_cast<uint32_t*>(&v);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4*>(dst + (((half * 4 + c) ^ (row & 7)) << 4)) = o[c].u;
+      } else {
+        // FP8: 128-byte raw row holds 128 K; this k64 block is bytes [sub*64, sub*64+64); thread takes 32 of them
+        const float sc = p.blk_scale[static_cast<size_t>(blockIdx.x) * (p.K / 128) + (kb >> 1)];
+        Pack16 o[4];
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          const int cl = sub * 4 + half * 2 + c2;
+          Pack16 w;
+          w.u = *reinterpret_cast<const uint4*>(raw + ((cl ^ (row & 7)) << 4));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float2 f = __half22float2(e4m3x2_to_h2(w.s[j]));
+            bf162 v = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+            o[c2 * 2 + (j >> 2)].w[j & 3] = *reinterpret_cast<uint32_t*>(&v);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4*>(dst + (((half * 4 + c) ^ (row & 7)) << 4)) = o[c].u;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&a_full[sa]);
+        if (sub == kSubs - 1 || i == nkb - 1) mbar_arrive(&raw_empty[sr]);
+      }
+      if (*abort_flag) break;
+    }
+  }
+
+  // ------------------------------------------------------------------ epilogue (warps 2..5)
+  if (warp >= 2 && warp < 6) {
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const bool ok = nkb > 0 ? wait_bar(acc_full, 0) : true;
+    if (!ok) { report(p.status, kTimeoutAccum, 6); *abort_flag = 1; }
+    tc_fence_after();
+    const int n = n0 + q * 32 + lane;
+    const int cols = min(BN, p.T - m0);
+    if (ok && !*abort_flag) {
+      float* wsp = splits > 1 ? p.ws + (static_cast<size_t>(split) * p.T + m0) * p.N : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (c0 >= cols) break;
+        uint32_t r[16];
+        if (nkb > 0) {
+          tmem_ld_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0;
+        }
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c0 + j;
+            if (m < cols) {
+              const float v = __uint_as_float(r[j]);
+              if (splits > 1) {
+                wsp[static_cast<size_t>(m) * p.N + n] = v;
+              } else {
+                const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
+                float y = v * p.alpha;
+                if (p.out32) p.out32[o] = y;
+                if (p.out) {
+                  if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
+                  p.out[o] = f32_to_bf16(y);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+    if (splits > 1) {
+      // publish partials, elect the last CTA of this tile, fold in ascending split order
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const uint32_t prev = atomicAdd(&p.counters[blockIdx.y * gridDim.x + blockIdx.x], 1u);
+        *last_flag = (prev == static_cast<uint32_t>(splits - 1)) ? 1 : 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag) {
+        __threadfence();
+        if (n < p.N) {
+          for (int m = 0; m < cols; ++m) {
+            float acc = 0.f;
+            for (int s = 0; s < splits; ++s)
+              acc += __ldcg(p.ws + (static_cast<size_t>(s) * p.T + m0 + m) * p.N + n);
+            const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
+            float y = acc * p.alpha;
+            if (p.out32) p.out32[o] = y;
+            if (p.out) {
+              if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
+              p.out[o] = f32_to_bf16(y);
+            }
+          }
+        }
+        if (warp == 2 && lane == 0) p.counters[blockIdx.y * gridDim.x + blockIdx.x] = 0;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && p)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `esize`-byte elements with row pitch `pitch` bytes.
+int make_tmap_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int esize, uint64_t cols, uint64_t rows,
+                 uint64_t pitch, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  DGPP_REQUIRE(fn != nullptr, "cuTensorMapEncodeTiled is unavailable (no CUDA driver?)");
+  DGPP_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base %p is not 16-byte aligned", base);
+  DGPP_REQUIRE(pitch % 16 == 0, "TMA row pitch %llu is not a multiple of 16", (unsigned long long)pitch);
+  DGPP_REQUIRE((static_cast<uint64_t>(box_cols) * esize) % 16 == 0, "TMA box inner extent is not a multiple of 16 bytes");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DGPP_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+template <int BN, int WMODE, int AF16>
+struct GemmCfg {
+  static constexpr bool kQuant = WMODE != 0;
+  // ring depths: deep raw prefetch for small BN (weight streaming), wide B ring for large BN
+  static constexpr int kBf16Depth = (200 * 1024) / (BN * 128 + kBM * 128);
+  static constexpr int SB = !kQuant ? (kBf16Depth > 8 ? 8 : kBf16Depth)
+                                    : (BN <= 32 ? 12 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4)));
+  static constexpr int SA = kQuant ? (BN <= 128 ? 4 : 3) : 1;
+  static constexpr int SR = kQuant ? (BN <= 64 ? 4 : 2) : 1;
+  static constexpr size_t smem() {
+    size_t s = 1024;  // alignment slack
+    s += static_cast<size_t>(SB) * BN * 128 + 1024;
+    s += static_cast<size_t>(kQuant ? SA : SB) * kBM * 128;
+    if (kQuant) s += static_cast<size_t>(SR) * kBM * 128;
+    if (WMODE == 1) s += static_cast<size_t>(SR) * kBM * 16;
+    s += (2 * SB + 2 * SA + 2 * SR + 1) * 8 + 64;
+    return s;
+  }
+};
+
+template <int BN, int WMODE, int AF16>
+static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tSf, const GemmParams& p,
+                       int splits, cudaStream_t st) {
+  using C = GemmCfg<BN, WMODE, AF16>;
+  auto kern = gemm_tc_kernel<BN, WMODE, AF16, C::SB, C::SA, C::SR>;
+  static bool attr = false;
+  constexpr size_t smem = C::smem();
+  static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
+  if (!attr) {
+    DGPP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    attr = true;
+  }
+  dim3 grid(dgpp_ceil_div(p.N, kBM), dgpp_ceil_div(p.T, BN), splits);
+  kern<<<grid, kGemmThreads, smem, st>>>(tA, tB, tSf, p);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace dgpp
+
+using namespace dgpp;
+
+// Scratch sizes for split-K: ws = splits * T * N floats; counters = ceil(N/128) * ceil(T/BN) uint32 (zeroed once).
+//
+// wmode: 0 bf16, 1 nvfp4, 2 fp8-block, 3 mxfp4.   a_f16: converted weights as f16 (1) or bf16 (0).
+// bn: token tile (16, 32, 64, 128, 256).  splits >= 1; K/64 blocks are divided evenly (4-block aligned for fp4).
+DGPP_API int dgpp_gemm_tc(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
+                          const void* w_scale, float alpha, void* out, void* out32, const void* resid, int ldc,
+                          int T, int N, int K, int splits, void* ws, void* counters, cudaStream_t st) {
+  DGPP_REQUIRE(T >= 1 && N >= 1, "gemm_tc: empty problem");
+  DGPP_REQUIRE(K % 64 == 0, "gemm_tc: K %d must be a multiple of 64", K);
+  if (wmode == 1 || wmode == 3) DGPP_REQUIRE(K % 256 == 0, "gemm_tc: fp4 weights need K %% 256 == 0 (K=%d)", K);
+  if (wmode == 2) DGPP_REQUIRE(K % 128 == 0, "gemm_tc: fp8 block weights need K %% 128 == 0 (K=%d)", K);
+  DGPP_REQUIRE(splits >= 1, "gemm_tc: splits must be >= 1");
+  DGPP_REQUIRE(splits == 1 || (ws && counters), "gemm_tc: split-K needs workspace and counters");
+  DGPP_REQUIRE(out || out32, "gemm_tc: no output");
+  GemmParams p;
+  p.alpha = alpha;
+  p.out = static_cast<bf16*>(out);
+  p.out32 = static_cast<float*>(out32);
+  p.resid = static_cast<const bf16*>(resid);
+  p.ws = static_cast<float*>(ws);
+  p.counters = static_cast<uint32_t*>(counters);
+  p.blk_scale = wmode == 2 ? static_cast<const float*>(w_scale) : nullptr;
+  p.sf_plain = wmode == 3 ? static_cast<const uint8_t*>(w_scale) : nullptr;
+  p.status = device_status_ptr();
+  p.T = T; p.N = N; p.K = K; p.ldc = ldc;
+  const int num_kb = K / 64;
+  const int align = (wmode == 1 || wmode == 3) ? 4 : (wmode == 2 ? 2 : 1);
+  int per = dgpp_ceil_div(num_kb, splits);
+  per = dgpp_ceil_div(per, align) * align;
+  p.kb_per_split = per;
+  splits = dgpp_ceil_div(num_kb, per);
+
+  CUtensorMap tA, tB, tSf;
+  memset(&tSf, 0, sizeof(tSf));
+  if (make_tmap_2d(&tB, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, T, x_stride * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -1;
+  if (wmode == 0) {
+    if (make_tmap_2d(&tA, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, static_cast<uint64_t>(K) * 2, 64, kBM,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return -1;
+  } else if (wmode == 2) {
+    if (make_tmap_2d(&tA, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, 128, kBM, CU_TENSOR_MAP_SWIZZLE_128B))
+      return -1;
+  } else {
+    if (make_tmap_2d(&tA, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, K / 2, 128, kBM, CU_TENSOR_MAP_SWIZZLE_128B))
+      return -1;
+    if (wmode == 1 &&
+        make_tmap_2d(&tSf, w_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 16, N, K / 16, 16, kBM,
+                     CU_TENSOR_MAP_SWIZZLE_NONE))
+      return -1;
+  }
+#define DGPP_GEMM_BN(BNV)                                                                        \
+  if (bn == BNV) {                                                                               \
+    if (wmode == 0) return launch_gemm<BNV, 0, 0>(tA, tB, tSf, p, splits, st);                    \
+    if (wmode == 1 && a_f16) return launch_gemm<BNV, 1, 1>(tA, tB, tSf, p, splits, st);           \
+    if (wmode == 1) return launch_gemm<BNV, 1, 0>(tA, tB, tSf, p, splits, st);                    \
+    if (wmode == 2) return launch_gemm<BNV, 2, 0>(tA, tB, tSf, p, splits, st);                    \
+    if (wmode == 3 && a_f16) return launch_gemm<BNV, 3, 1>(tA, tB, tSf, p, splits, st);           \
+    if (wmode == 3) return launch_gemm<BNV, 3, 0>(tA, tB, tSf, p, splits, st);                    \
+  }
+  DGPP_GEMM_BN(16) DGPP_GEMM_BN(32) DGPP_GEMM_BN(64) DGPP_GEMM_BN(128) DGPP_GEMM_BN(256)
+#undef DGPP_GEMM_BN
+  dgpp_set_error("gemm_tc: unsupported bn %d / wmode %d", bn, wmode);
+  return -1;
+}

@@ -1,0 +1,195 @@
+"""Python entry points of the sm_100a kernels (thin: pointer marshalling and shape checks only)."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..quant.formats import QuantLinear
+from . import _lib
+from ._lib import call, ptr, stream_ptr
+
+_FMT_GEMV = {"nvfp4": 0, "mxfp4": 1, "bf16": 2}
+_FMT_GEMM = {"bf16": 0, "nvfp4": 1, "fp8": 2, "mxfp4": 3}
+
+# Converted-weight element type for the fp4 tensor-core path: 1 = f16 (one multiply per pair),
+# 0 = bf16 (bit re-biasing + multiply).  Both are exact; f16 needs kind::f16 to accept an f16 A
+# operand together with a bf16 B operand.
+A_F16_DEFAULT = 1
+
+
+def _chk(t: torch.Tensor, dtype, name: str):
+    if t.dtype != dtype:
+        raise TypeError(f"{name}: expected {dtype}, got {t.dtype}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name}: CUDA tensor required")
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(ids, torch.int32, "ids")
+    _chk(table, torch.bfloat16, "table")
+    rows, (vocab, hidden) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=table.device)
+    call("dgpp_embed_gather", ptr(ids), ptr(table), ptr(out), rows, hidden, vocab, stream_ptr())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, delta: Optional[torch.Tensor] = None,
+            resid_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+            one_plus_w: bool = False):
+    """out = rmsnorm(x [+ delta]).  With `delta` the sum is written to `resid_out` (default: x, in place)."""
+    _chk(x, torch.bfloat16, "x")
+    rows, hidden = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    if delta is not None and resid_out is None:
+        resid_out = x
+    call("dgpp_rmsnorm", ptr(x), ptr(delta), ptr(w), ptr(resid_out), ptr(out), rows, hidden, float(eps),
+         int(one_plus_w), stream_ptr())
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, limit: float = 0.0) -> torch.Tensor:
+    _chk(gate_up, torch.bfloat16, "gate_up")
+    rows, two_i = gate_up.shape
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty(rows, inter, dtype=torch.bfloat16, device=gate_up.device)
+    call("dgpp_swiglu", ptr(gate_up), ptr(out), rows, inter, float(limit), stream_ptr())
+    return out
+
+
+def argmax(logits: torch.Tensor, id_base: int = 0, out_id: Optional[torch.Tensor] = None,
+           out_val: Optional[torch.Tensor] = None):
+    rows, vocab = logits.shape
+    dt = {torch.bfloat16: 0, torch.float32: 1}[logits.dtype]
+    if out_id is None:
+        out_id = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if out_val is None:
+        out_val = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    call("dgpp_argmax", ptr(logits), dt, logits.stride(0), rows, vocab, id_base, ptr(out_id), ptr(out_val),
+         stream_ptr())
+    return out_id, out_val
+
+
+def gemv(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
+         out32: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """CUDA-core weight-streaming GEMV, rows <= 4."""
+    _chk(x, torch.bfloat16, "x")
+    rows, k = x.shape
+    assert k == w.k and w.fmt in _FMT_GEMV
+    if out is None and out32 is None:
+        out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=x.device)
+    ys = (out if out is not None else out32).stride(0)
+    call("dgpp_gemv_quant", _FMT_GEMV[w.fmt], ptr(x), ptr(w.payload), ptr(w.scale), float(w.alpha), ptr(out),
+         ptr(out32), rows, w.n, k, x.stride(0), ys, stream_ptr())
+    return out if out is not None else out32
+
+
+class GemmWorkspace:
+    """Split-K scratch for ``gemm_tc``: fp32 partials and per-tile arrival counters (zero at rest)."""
+
+    def __init__(self, device, max_partial_floats: int = 1 << 24, max_tiles: int = 1 << 16):
+        self.partials = torch.empty(max_partial_floats, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(max_tiles, dtype=torch.int32, device=device)
+
+
+_WS: dict = {}
+
+
+def default_workspace(device) -> GemmWorkspace:
+    key = str(device)
+    if key not in _WS:
+        _WS[key] = GemmWorkspace(device)
+    return _WS[key]
+
+
+def pick_bn(rows: int) -> int:
+    for bn in (16, 32, 64, 128):
+        if rows <= bn:
+            return bn
+    return 256
+
+
+def pick_splits(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:
+    """Split K until the grid covers the SMs (weight-streaming regime only)."""
+    tiles = math.ceil(n / 128) * math.ceil(rows / bn)
+    if tiles >= sms or rows > 128:
+        return 1
+    kb = k // 64
+    want = max(1, sms // tiles)
+    return max(1, min(want, kb // 8))
+
+
+def gemm_tc(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
+            out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+            bn: Optional[int] = None, splits: Optional[int] = None, a_f16: Optional[int] = None,
+            ws: Optional[GemmWorkspace] = None) -> torch.Tensor:
+    """tcgen05 linear: out[T, N] = alpha * x[T, K] @ dequant(w)[N, K]^T (+ resid)."""
+    _chk(x, torch.bfloat16, "x")
+    rows, k = x.shape
+    assert k == w.k, (k, w.k)
+    assert w.fmt in _FMT_GEMM, w.fmt
+    if out is None and out32 is None:
+        out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=x.device)
+    ldc = (out if out is not None else out32).stride(0)
+    if bn is None:
+        bn = pick_bn(rows)
+    if splits is None:
+        splits = pick_splits(rows, w.n, k, bn)
+    if a_f16 is None:
+        a_f16 = A_F16_DEFAULT if w.fmt == "nvfp4" else 0
+    wsp = cnt = None
+    if splits > 1:
+        ws = ws or default_workspace(x.device)
+        need = splits * rows * w.n
+        tiles = math.ceil(w.n / 128) * math.ceil(rows / bn)
+        if need > ws.partials.numel() or tiles > ws.counters.numel():
+            splits = 1
+        else:
+            wsp, cnt = ws.partials, ws.counters
+    call("dgpp_gemm_tc", _FMT_GEMM[w.fmt], int(a_f16), bn, ptr(x), x.stride(0), ptr(w.payload), ptr(w.scale),
+         float(w.alpha), ptr(out), ptr(out32), ptr(resid), ldc, rows, w.n, k, splits, ptr(wsp), ptr(cnt),
+         stream_ptr())
+    return out if out is not None else out32
+
+
+def linear(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
+           resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dispatch a linear layer to the tensor-core kernel (all row counts)."""
+    return gemm_tc(x, w, out=out, resid=resid)
+
+
+def rope_kv_write(qkv, positions, row_req, block_table, inv_freq, cache, hq: int, hkv: int, d: int,
+                  rot_dim: Optional[int] = None, mscale: float = 1.0, q_norm_w=None, k_norm_w=None,
+                  eps: float = 1e-6, norm_one_plus_w: bool = False) -> None:
+    """In-place RoPE on q/k of `qkv` and append of k/v into `cache` (a ``PagedKV`` layer view)."""
+    _chk(qkv, torch.bfloat16, "qkv")
+    rows = qkv.shape[0]
+    call("dgpp_rope_kv_write", ptr(qkv), ptr(positions), ptr(row_req), ptr(block_table), ptr(inv_freq),
+         ptr(q_norm_w), ptr(k_norm_w), ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale), rows,
+         hq, hkv, d, rot_dim or d, cache.page, block_table.shape[1], float(mscale), float(eps), int(cache.fp8),
+         int(norm_one_plus_w), stream_ptr())
+
+
+def attn_decode(q, q_stride: int, cache, block_table, row_req, positions, hq: int, hkv: int, d: int,
+                scale: float, splits: int = 1, scratch=None, out=None, window: int = 0):
+    rows = positions.numel()
+    if out is None:
+        out = torch.empty(rows, hq * d, dtype=torch.bfloat16, device=positions.device)
+    ml = acc = None
+    if splits > 1:
+        if scratch is None:
+            scratch = (torch.empty(rows * hq * splits * 2, dtype=torch.float32, device=out.device),
+                       torch.empty(rows * hq * splits * d, dtype=torch.float32, device=out.device))
+        ml, acc = scratch
+    call("dgpp_attn_decode", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale),
+         ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq, hkv, d, cache.page,
+         block_table.shape[1], splits, int(cache.fp8), float(scale), window, stream_ptr())
+    return out
+
+
+def check_status() -> None:
+    _lib.check_status()

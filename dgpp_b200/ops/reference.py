@@ -1,0 +1,124 @@
+"""Plain PyTorch fp32 restatements of every CUDA op: the oracle for kernel tests and the execution
+path on hosts without a GPU (CPU plumbing runs, gloo multi-rank tests)."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..quant.formats import QuantLinear
+
+BF = torch.bfloat16
+
+
+def _r(x: torch.Tensor) -> torch.Tensor:
+    """Round fp32 to bf16 and come back (marks a bf16 rounding point)."""
+    return x.to(BF).float()
+
+
+def embed_gather(ids, table):
+    return table[ids.long().clamp(0, table.shape[0] - 1)]
+
+
+def rmsnorm(x, w, eps=1e-6, delta=None, one_plus_w=False):
+    """Returns (out, new_residual).  out = bf16(w * bf16(x * rstd))."""
+    xf = x.float()
+    if delta is not None:
+        xf = _r(xf + delta.float())
+    rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    g = w.float() + (1.0 if one_plus_w else 0.0)
+    return (_r(xf * rstd) * g).to(BF), xf.to(BF)
+
+
+def swiglu(gate_up, limit: float = 0.0):
+    inter = gate_up.shape[-1] // 2
+    g, u = gate_up[..., :inter].float(), gate_up[..., inter:].float()
+    if limit > 0:
+        g = g.clamp(max=limit)
+        u = u.clamp(-limit, limit)
+    return (_r(g * torch.sigmoid(g)) * u).to(BF)
+
+
+def argmax(logits, id_base=0):
+    v, i = logits.float().max(-1)
+    # torch.max returns the first maximal index on CPU and CUDA for 1-D reductions; make it explicit
+    eq = logits.float() == v.unsqueeze(-1)
+    first = torch.argmax(eq.to(torch.int8), dim=-1)
+    return (first + id_base).to(torch.int32), v
+
+
+def linear(x, w: QuantLinear, resid=None, out_fp32=False):
+    """out = alpha * x @ dequant(w)^T in fp32, one bf16 rounding (+ residual add with a second one)."""
+    y = x.float() @ w.dequant().t().to(x.device)
+    if out_fp32:
+        return y
+    y = y.to(BF)
+    if resid is not None:
+        y = (resid.float() + y.float()).to(BF)
+    return y
+
+
+def rope_inv_freq(rot_dim: int, theta: float, device=None, yarn_factor: float = 1.0,
+                  original_max_pos: int = 0, beta_fast: float = 32.0, beta_slow: float = 1.0):
+    """fp32 inverse frequencies [rot_dim/2]; with yarn_factor > 1 returns the YaRN-blended table and the
+    attention scale (mscale) that multiplies cos/sin."""
+    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float32, device=device) / rot_dim))
+    if yarn_factor <= 1.0:
+        return inv, 1.0
+
+    def corr_dim(rot):
+        return (rot_dim * math.log(original_max_pos / (rot * 2 * math.pi))) / (2 * math.log(theta))
+
+    low = max(math.floor(corr_dim(beta_fast)), 0)
+    high = min(math.ceil(corr_dim(beta_slow)), rot_dim // 2 - 1)
+    ramp = ((torch.arange(rot_dim // 2, dtype=torch.float32, device=device) - low) / max(high - low, 1e-3)).clamp(0, 1)
+    mask = 1.0 - ramp
+    inv_yarn = inv / yarn_factor * (1 - mask) + inv * mask
+    mscale = 0.1 * math.log(yarn_factor) + 1.0
+    return inv_yarn, mscale
+
+
+def apply_rope(x, positions, inv_freq, rot_dim, mscale=1.0):
+    """x: [rows, heads, d] fp32; rotate-half pairing on the first rot_dim dims, one bf16 rounding."""
+    ang = positions.float().unsqueeze(-1) * inv_freq.unsqueeze(0)      # [rows, rot/2]
+    cs, sn = (torch.cos(ang) * mscale).unsqueeze(1), (torch.sin(ang) * mscale).unsqueeze(1)
+    h = rot_dim // 2
+    x0, x1 = x[..., :h], x[..., h:rot_dim]
+    out = x.clone()
+    out[..., :h] = x0 * cs - x1 * sn
+    out[..., h:rot_dim] = x1 * cs + x0 * sn
+    return _r(out)
+
+
+def head_norm(x, w, eps, one_plus_w=False):
+    rstd = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    g = w.float() + (1.0 if one_plus_w else 0.0)
+    return _r(_r(x * rstd) * g)
+
+
+def quant_kv_fp8(x):
+    """x: [..., d] fp32 -> (e4m3 codes uint8, fp32 scale [...]) with scale = amax / 448."""
+    amax = x.abs().amax(-1)
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    q = (x * (1.0 / scale).unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8), scale
+
+
+def attention(q, k, v, scale, causal_offset: Optional[int] = None, window: int = 0):
+    """q: [Tq, hq, d], k/v: [Tk, hkv, d] fp32.  causal_offset = position of q row 0 (None: no mask)."""
+    tq, hq, d = q.shape
+    tk, hkv, _ = k.shape
+    g = hq // hkv
+    kk = k.repeat_interleave(g, 1)
+    vv = v.repeat_interleave(g, 1)
+    s = torch.einsum("qhd,khd->hqk", q, kk) * scale
+    if causal_offset is not None:
+        qpos = torch.arange(tq, device=q.device).unsqueeze(-1) + causal_offset
+        kpos = torch.arange(tk, device=q.device).unsqueeze(0)
+        mask = kpos > qpos
+        if window > 0:
+            mask = mask | (kpos <= qpos - window)
+        s = s.masked_fill(mask.unsqueeze(0), float("-inf"))
+    p = torch.softmax(s, -1)
+    return torch.einsum("hqk,khd->qhd", p, vv)

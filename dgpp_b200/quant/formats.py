@@ -1,0 +1,209 @@
+"""Checkpoint weight formats, as PyTorch reference codecs.
+
+Every quantised weight keeps the byte layout of the safetensors checkpoints the engine reads
+(reference: src/models/quant_matrix.hpp:2-209 describes the same layouts):
+
+==========  ==============================  =============================================
+format      payload                         scales
+==========  ==============================  =============================================
+``nvfp4``   e2m1, 2 codes/byte [N, K/2]     e4m3 per 16 along K [N, K/16] + fp32 per tensor
+            (low nibble = even k)
+``mxfp4``   e2m1 packed [N, K/2]            e8m0 per 32 along K [N, K/32]
+``fp8``     e4m3 bytes [N, K]               fp32 per 128x128 block [ceil(N/128), K/128]
+``mxfp8``   e4m3 bytes [N, K]               e8m0 per 32 along K [N, K/32]
+``int4``    offset-binary, 2 codes/byte     bf16 per 64 along K [N, K/64]
+``int8``    offset-binary bytes [N, K]      bf16 per 64 along K [N, K/64]
+``bf16``    bf16 [N, K]                     --
+==========  ==============================  =============================================
+
+The quantisers here are used to build random-init models of a given format and as the oracle the
+CUDA kernels are tested against; ``QuantLinear.dequant()`` never runs on a serving path.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+_E2M1_BOUNDS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+# a tie on an odd boundary index rounds up (to the even code), on an even index it rounds down
+_E2M1_TIE_UP = (False, True, False, True, False, True, False)
+
+
+def e2m1_encode(x: torch.Tensor) -> torch.Tensor:
+    """Round fp32 values (already divided by their scale) to e2m1 codes 0..15, ties to the even code."""
+    a = x.abs().float()
+    code = torch.zeros_like(a, dtype=torch.uint8)
+    for i, b in enumerate(_E2M1_BOUNDS):
+        code += ((a >= b) if _E2M1_TIE_UP[i] else (a > b)).to(torch.uint8)
+    sign = (x < 0).to(torch.uint8) << 3
+    return code | sign
+
+
+def e2m1_decode(code: torch.Tensor) -> torch.Tensor:
+    lut = torch.tensor(E2M1_VALUES, dtype=torch.float32, device=code.device)
+    mag = lut[(code & 7).long()]
+    return torch.where((code & 8) != 0, -mag, mag)
+
+
+def pack_nibbles(codes: torch.Tensor) -> torch.Tensor:
+    """[..., K] codes -> [..., K/2] bytes, low nibble = even index."""
+    lo = codes[..., 0::2]
+    hi = codes[..., 1::2]
+    return (lo | (hi << 4)).to(torch.uint8)
+
+
+def unpack_nibbles(packed: torch.Tensor) -> torch.Tensor:
+    lo = packed & 0xF
+    hi = packed >> 4
+    return torch.stack((lo, hi), dim=-1).flatten(-2)
+
+
+def e8m0_decode(e: torch.Tensor) -> torch.Tensor:
+    return torch.exp2(e.float() - 127.0)
+
+
+@dataclass
+class QuantLinear:
+    """One quantised [N, K] matrix in checkpoint layout."""
+
+    fmt: str
+    n: int
+    k: int
+    payload: torch.Tensor                 # uint8 / bf16, see module docstring
+    scale: Optional[torch.Tensor] = None  # block scales (uint8 codes, fp32 or bf16 depending on fmt)
+    alpha: float = 1.0                    # per-tensor fp32 multiplier (nvfp4 global scale)
+
+    def to(self, device) -> "QuantLinear":
+        return QuantLinear(self.fmt, self.n, self.k, self.payload.to(device),
+                           None if self.scale is None else self.scale.to(device), self.alpha)
+
+    @property
+    def nbytes(self) -> int:
+        b = self.payload.numel() * self.payload.element_size()
+        if self.scale is not None:
+            b += self.scale.numel() * self.scale.element_size()
+        return b
+
+    def dequant(self) -> torch.Tensor:
+        """fp32 [N, K] values of the stored weights (oracle only)."""
+        f, n, k = self.fmt, self.n, self.k
+        if f == "bf16":
+            return self.payload.float()
+        if f == "nvfp4":
+            v = e2m1_decode(unpack_nibbles(self.payload)).view(n, k // 16, 16)
+            s = self.scale.view(torch.float8_e4m3fn).float().view(n, k // 16, 1)
+            return (v * s).view(n, k) * self.alpha
+        if f == "mxfp4":
+            v = e2m1_decode(unpack_nibbles(self.payload)).view(n, k // 32, 32)
+            return (v * e8m0_decode(self.scale).view(n, k // 32, 1)).view(n, k)
+        if f == "fp8":
+            v = self.payload.view(torch.float8_e4m3fn).float()
+            s = self.scale.repeat_interleave(128, 0)[:n].repeat_interleave(128, 1)[:, :k]
+            return v * s
+        if f == "mxfp8":
+            v = self.payload.view(torch.float8_e4m3fn).float().view(n, k // 32, 32)
+            return (v * e8m0_decode(self.scale).view(n, k // 32, 1)).view(n, k)
+        if f in ("int4", "int8"):
+            bits = 4 if f == "int4" else 8
+            codes = unpack_nibbles(self.payload) if bits == 4 else self.payload
+            v = (codes.float() - float(1 << (bits - 1))).view(n, k // 64, 64)
+            return (v * self.scale.float().view(n, k // 64, 1)).view(n, k)
+        raise ValueError(f"unknown format {f}")
+
+    def dequant_bf16_exact(self) -> torch.Tensor:
+        """What the tensor-core path multiplies with: per-element values before the fp32 tensor scale,
+        rounded the way the converter warps round (exact for fp4, bf16(e4m3*scale) for fp8)."""
+        if self.fmt == "nvfp4":
+            return (self.dequant() / self.alpha).to(torch.bfloat16)
+        return self.dequant().to(torch.bfloat16)
+
+
+def quantize(w: torch.Tensor, fmt: str) -> QuantLinear:
+    """Quantise an fp32/bf16 [N, K] matrix into `fmt` (see module docstring)."""
+    n, k = w.shape
+    wf = w.float()
+    if fmt == "bf16":
+        return QuantLinear("bf16", n, k, w.to(torch.bfloat16).contiguous())
+    if fmt == "nvfp4":
+        assert k % 16 == 0
+        amax = wf.abs().max().clamp_min(1e-12)
+        gs = (amax / (6.0 * 448.0)).item()
+        blk = wf.view(n, k // 16, 16)
+        sb = (blk.abs().amax(-1) / 6.0 / gs).clamp(max=448.0)
+        sb8 = sb.to(torch.float8_e4m3fn)
+        sbf = sb8.float().clamp_min(2.0 ** -9).unsqueeze(-1)
+        codes = e2m1_encode(blk / (sbf * gs))
+        return QuantLinear("nvfp4", n, k, pack_nibbles(codes.view(n, k)).contiguous(),
+                           sb8.view(torch.uint8).contiguous(), gs)
+    if fmt == "mxfp4":
+        assert k % 32 == 0
+        blk = wf.view(n, k // 32, 32)
+        amax = blk.abs().amax(-1).clamp_min(2.0 ** -126)
+        e = (torch.floor(torch.log2(amax)) - 2.0).clamp(-127, 127)
+        codes = e2m1_encode(blk / torch.exp2(e).unsqueeze(-1))
+        return QuantLinear("mxfp4", n, k, pack_nibbles(codes.view(n, k)).contiguous(),
+                           (e + 127).to(torch.uint8).contiguous())
+    if fmt == "fp8":
+        assert k % 128 == 0
+        nb = (n + 127) // 128
+        pad = nb * 128 - n
+        wp = torch.nn.functional.pad(wf, (0, 0, 0, pad)) if pad else wf
+        blk = wp.view(nb, 128, k // 128, 128)
+        s = (blk.abs().amax((1, 3)) / 448.0).clamp_min(1e-12)
+        q = (blk / s.view(nb, 1, k // 128, 1)).clamp(-448, 448).to(torch.float8_e4m3fn)
+        q = q.view(nb * 128, k)[:n]
+        return QuantLinear("fp8", n, k, q.view(torch.uint8).contiguous(), s.float().contiguous())
+    if fmt == "mxfp8":
+        assert k % 32 == 0
+        blk = wf.view(n, k // 32, 32)
+        amax = blk.abs().amax(-1).clamp_min(2.0 ** -126)
+        e = (torch.floor(torch.log2(amax)) - 8.0).clamp(-127, 127)
+        q = (blk / torch.exp2(e).unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn)
+        return QuantLinear("mxfp8", n, k, q.view(n, k).view(torch.uint8).contiguous(),
+                           (e + 127).to(torch.uint8).contiguous())
+    if fmt in ("int4", "int8"):
+        assert k % 64 == 0
+        bits = 4 if fmt == "int4" else 8
+        qmax = float((1 << (bits - 1)) - 1)
+        blk = wf.view(n, k // 64, 64)
+        s = (blk.abs().amax(-1) / qmax).clamp_min(1e-12).to(torch.bfloat16)
+        q = torch.round(blk / s.float().unsqueeze(-1)).clamp(-qmax - 1, qmax) + float(1 << (bits - 1))
+        codes = q.to(torch.uint8).view(n, k)
+        payload = pack_nibbles(codes) if bits == 4 else codes
+        return QuantLinear(fmt, n, k, payload.contiguous(), s.contiguous())
+    raise ValueError(f"unknown format {fmt}")
+
+
+def random_quant_linear(n: int, k: int, fmt: str, device, std: float = 0.02,
+                        generator: Optional[torch.Generator] = None, chunk_rows: int = 8192) -> QuantLinear:
+    """N(0, std) weights quantised to `fmt`, generated in row chunks so a 27B-class model can be
+    initialised on one device without an fp32 copy of a whole matrix.  nvfp4 uses the analytic
+    global scale of the distribution (std * 5.5 sigma) so chunks share one tensor scale."""
+    if fmt == "nvfp4":
+        gs = (5.5 * std) / (6.0 * 448.0)
+        payloads, scales = [], []
+        for r0 in range(0, n, chunk_rows):
+            r = min(chunk_rows, n - r0)
+            w = torch.randn(r, k, device=device, dtype=torch.float32, generator=generator) * std
+            blk = w.view(r, k // 16, 16)
+            sb8 = (blk.abs().amax(-1) / 6.0 / gs).clamp(max=448.0).to(torch.float8_e4m3fn)
+            sbf = sb8.float().clamp_min(2.0 ** -9).unsqueeze(-1)
+            codes = e2m1_encode(blk / (sbf * gs))
+            payloads.append(pack_nibbles(codes.view(r, k)))
+            scales.append(sb8.view(torch.uint8))
+        return QuantLinear("nvfp4", n, k, torch.cat(payloads).contiguous(), torch.cat(scales).contiguous(), gs)
+    if fmt == "fp8":
+        chunk_rows = max(128, chunk_rows // 128 * 128)
+    parts = []
+    for r0 in range(0, n, chunk_rows):
+        r = min(chunk_rows, n - r0)
+        w = torch.randn(r, k, device=device, dtype=torch.float32, generator=generator) * std
+        parts.append(quantize(w, fmt))
+    if len(parts) == 1:
+        return parts[0]
+    return QuantLinear(fmt, n, k, torch.cat([p.payload for p in parts]).contiguous(),
+                       None if parts[0].scale is None else torch.cat([p.scale for p in parts]).contiguous(),
+                       parts[0].alpha)
