@@ -79,8 +79,9 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity) {
   }
 }
 
-// WMODE: 0 bf16, 1 nvfp4, 2 fp8 block, 3 mxfp4.  AF16: converted operand is f16 (1) or bf16 (0).
-template <int BN, int WMODE, int AF16, int SB, int SA, int SR>
+// WMODE: 0 bf16, 1 nvfp4, 2 fp8 block, 3 mxfp4.  Converted operands are bf16 (kind::f16 requires A and B
+// to have the same 16-bit type; mixing an f16 A with a bf16 B is an illegal instruction on sm_100a).
+template <int BN, int WMODE, int SB, int SA, int SR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or packed raw weights (uint8)
                const __grid_constant__ CUtensorMap tmB,   // activations bf16 [T, K]
@@ -170,7 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, (kQuant && AF16) ? 0u : 1u, 1u);
+      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, 1u, 1u);
       for (int i = 0; i < nkb; ++i) {
         const int sb = i % SB;
         if (!wait_bar(&b_full[sb], (i / SB) & 1)) { report(p.status, kTimeoutTmaFull, 3); *abort_flag = 1; break; }
@@ -225,14 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
           s0f = s1f = e8m0_to_f32(e);
         }
         Pack16 o[4];
-        if (AF16) {
-          const __half2 s0 = __float2half2_rn(s0f), s1 = __float2half2_rn(s1f);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            __half2 h = __hmul2(e2m1x2_to_h2(w.b[j]), j < 8 ? s0 : s1);
-            o[j >> 2].w[j & 3] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        } else {
+        {
           // f16 bits >> 3 read as bf16 equal value * 2^-112; fold 2^112 into the (exact) bf16 scale
           const bf162 s0 = __float2bfloat162_rn(s0f * 5.192296858534828e33f);
           const bf162 s1 = __float2bfloat162_rn(s1f * 5.192296858534828e33f);
@@ -389,7 +383,7 @@ int make_tmap_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int e
   return 0;
 }
 
-template <int BN, int WMODE, int AF16>
+template <int BN, int WMODE>
 struct GemmCfg {
   static constexpr bool kQuant = WMODE != 0;
   // ring depths: deep raw prefetch for small BN (weight streaming), wide B ring for large BN
@@ -409,11 +403,11 @@ struct GemmCfg {
   }
 };
 
-template <int BN, int WMODE, int AF16>
+template <int BN, int WMODE>
 static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tSf, const GemmParams& p,
                        int splits, cudaStream_t st) {
-  using C = GemmCfg<BN, WMODE, AF16>;
-  auto kern = gemm_tc_kernel<BN, WMODE, AF16, C::SB, C::SA, C::SR>;
+  using C = GemmCfg<BN, WMODE>;
+  auto kern = gemm_tc_kernel<BN, WMODE, C::SB, C::SA, C::SR>;
   static bool attr = false;
   constexpr size_t smem = C::smem();
   static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
@@ -433,7 +427,7 @@ using namespace dgpp;
 
 // Scratch sizes for split-K: ws = splits * T * N floats; counters = ceil(N/128) * ceil(T/BN) uint32 (zeroed once).
 //
-// wmode: 0 bf16, 1 nvfp4, 2 fp8-block, 3 mxfp4.   a_f16: converted weights as f16 (1) or bf16 (0).
+// wmode: 0 bf16, 1 nvfp4, 2 fp8-block, 3 mxfp4.   a_f16 is ignored (kept for ABI stability).
 // bn: token tile (16, 32, 64, 128, 256).  splits >= 1; K/64 blocks are divided evenly (4-block aligned for fp4).
 DGPP_API int dgpp_gemm_tc(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
                           const void* w_scale, float alpha, void* out, void* out32, const void* resid, int ldc,
@@ -482,14 +476,12 @@ DGPP_API int dgpp_gemm_tc(int wmode, int a_f16, int bn, const void* x, int64_t x
                      CU_TENSOR_MAP_SWIZZLE_NONE))
       return -1;
   }
-#define DGPP_GEMM_BN(BNV)                                                                        \
-  if (bn == BNV) {                                                                               \
-    if (wmode == 0) return launch_gemm<BNV, 0, 0>(tA, tB, tSf, p, splits, st);                    \
-    if (wmode == 1 && a_f16) return launch_gemm<BNV, 1, 1>(tA, tB, tSf, p, splits, st);           \
-    if (wmode == 1) return launch_gemm<BNV, 1, 0>(tA, tB, tSf, p, splits, st);                    \
-    if (wmode == 2) return launch_gemm<BNV, 2, 0>(tA, tB, tSf, p, splits, st);                    \
-    if (wmode == 3 && a_f16) return launch_gemm<BNV, 3, 1>(tA, tB, tSf, p, splits, st);           \
-    if (wmode == 3) return launch_gemm<BNV, 3, 0>(tA, tB, tSf, p, splits, st);                    \
+#define DGPP_GEMM_BN(BNV)                                                       \
+  if (bn == BNV) {                                                              \
+    if (wmode == 0) return launch_gemm<BNV, 0>(tA, tB, tSf, p, splits, st);      \
+    if (wmode == 1) return launch_gemm<BNV, 1>(tA, tB, tSf, p, splits, st);      \
+    if (wmode == 2) return launch_gemm<BNV, 2>(tA, tB, tSf, p, splits, st);      \
+    if (wmode == 3) return launch_gemm<BNV, 3>(tA, tB, tSf, p, splits, st);      \
   }
   DGPP_GEMM_BN(16) DGPP_GEMM_BN(32) DGPP_GEMM_BN(64) DGPP_GEMM_BN(128) DGPP_GEMM_BN(256)
 #undef DGPP_GEMM_BN

@@ -1,0 +1,454 @@
+// Continuous-batching scheduler with a deterministic tick.
+//
+// One tick does, in this order:
+//   1. cancel sweep            -- requests flagged by the service are retired ("cancelled")
+//   2. reservation growth      -- (grow-on-demand policy) decoders about to cross a block boundary get a
+//                                 block; when the pool is dry the youngest request is shed back to the queue
+//   3. admission               -- FIFO by arrival while a slot and blocks are free; prefix-cache lookup
+//                                 shares cached blocks, LRU entries are evicted to make room
+//   4. prefill                 -- chunked and resumable, at most `prefill_budget` prompt tokens per tick
+//                                 (idle / busy budgets); the last chunk yields the first token
+//   5. one decode pass         -- all requests in decode state step together
+//   6. retirement              -- eos / length / stop-token / cancelled / error; finished prompts are
+//                                 published to the prefix cache
+// Every decision is a pure function of the submitted request stream and the engine's answers, so two
+// ranks fed the same stream make the same decisions; an FNV-1a digest of the op stream is kept for
+// cross-rank checks.
+// (behavioural spec: src/sched/scheduler.cpp:1500-1958 tick/quantum, admission 683, retire 1292;
+//  src/sched/scheduler.hpp:57-560 engine contract, 637-680 admission policies, 1197-1257 observer.)
+#pragma once
+#include <algorithm>
+#include <cstdint>
+#include <deque>
+#include <functional>
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "rt/prefix_cache.h"
+
+namespace dgpp {
+
+// What the scheduler needs from an execution engine.  Slots are 0 .. max_concurrent()-1.
+class SchedulerEngine {
+ public:
+  virtual ~SchedulerEngine() = default;
+  virtual int max_concurrent() const = 0;
+  virtual int block_tokens() const = 0;            // tokens per KV block
+  virtual int64_t total_blocks() const = 0;
+  virtual int64_t free_blocks() const = 0;
+  virtual int64_t max_context() const = 0;         // longest sequence a slot can hold
+  // Make slot own blocks covering `tokens` positions (after any attached prefix).  false = pool exhausted.
+  virtual bool reserve(int slot, int64_t tokens) = 0;
+  // Share cached blocks as the first blocks of an empty slot.
+  virtual void attach_prefix(int slot, const std::vector<int32_t>& blocks) = 0;
+  // Run prompt tokens [pos, pos+count) of the slot.  Returns the first generated token when `last`, else -1.
+  virtual int32_t prefill(int slot, const int32_t* tokens, int64_t pos, int64_t count, bool last) = 0;
+  // One decode pass; result[i] holds the new tokens of slots[i] (one, or several with speculative decoding).
+  virtual std::vector<std::vector<int32_t>> step_batch(const std::vector<int>& slots) = 0;
+  virtual int max_tokens_per_step() const { return 1; }
+  // Physical blocks of a slot, in position order (for publishing to the prefix cache).
+  virtual std::vector<int32_t> slot_blocks(int slot) const = 0;
+  virtual void retain_block(int32_t block) = 0;
+  virtual void release_block(int32_t block) = 0;
+  virtual int block_refcount(int32_t block) const = 0;
+  // Drop the slot's blocks and state.
+  virtual void close(int slot) = 0;
+};
+
+enum class RetireReason { Eos, Length, Stop, Cancelled, Error, Shed };
+
+inline const char* retire_name(RetireReason r) {
+  switch (r) {
+    case RetireReason::Eos: return "stop";
+    case RetireReason::Length: return "length";
+    case RetireReason::Stop: return "stop";
+    case RetireReason::Cancelled: return "cancelled";
+    case RetireReason::Error: return "error";
+    case RetireReason::Shed: return "shed";
+  }
+  return "?";
+}
+
+struct SchedRequest {
+  std::string id;
+  std::vector<int32_t> prompt;
+  int64_t max_tokens = 16;
+  std::vector<int32_t> eos_ids;
+  std::vector<int32_t> stop_ids;     // single-token stops handled here; stop strings live above
+  bool ignore_eos = false;
+  bool prefix_cache = true;
+  std::string cache_key;             // non-empty: pin published blocks
+};
+
+class SchedulerObserver {
+ public:
+  virtual ~SchedulerObserver() = default;
+  virtual void on_admit(const std::string& id, int slot, int64_t cached_tokens) { (void)id; (void)slot; (void)cached_tokens; }
+  virtual void on_token(const std::string& id, int32_t token, int64_t index) { (void)id; (void)token; (void)index; }
+  virtual void on_retire(const std::string& id, RetireReason why, int64_t generated) { (void)id; (void)why; (void)generated; }
+};
+
+enum class AdmissionPolicy { FullReserve, GrowOnDemand };
+
+struct SchedulerConfig {
+  AdmissionPolicy policy = AdmissionPolicy::FullReserve;
+  int64_t prefill_budget_idle = 4096;   // prompt tokens per tick when nobody is decoding
+  int64_t prefill_budget_busy = 1024;   // ... when decoders are waiting for their pass
+  int64_t prefill_chunk = 2048;         // largest single engine call
+  bool prefix_cache = true;
+  int64_t prefix_min_tokens = 16;
+  int64_t prefix_max_entries = 1 << 20;
+  int64_t grow_margin_tokens = 1;       // grow-on-demand keeps this many positions reserved ahead
+};
+
+struct SchedMeters {
+  int64_t ticks = 0, admitted = 0, retired = 0, shed = 0, decode_passes = 0, decode_tokens = 0;
+  int64_t prefill_tokens = 0, prefill_calls = 0, prefix_hit_tokens = 0, cancelled = 0;
+  int64_t queue_peak = 0, active_peak = 0;
+};
+
+class Scheduler {
+ public:
+  Scheduler(SchedulerEngine* engine, SchedulerConfig cfg, SchedulerObserver* obs = nullptr)
+      : eng_(engine), cfg_(cfg), obs_(obs),
+        cache_(engine->block_tokens(), cfg.prefix_max_entries),
+        slots_(static_cast<size_t>(engine->max_concurrent())) {}
+
+  ~Scheduler() {
+    cache_.clear([this](int32_t b) { eng_->release_block(b); });
+  }
+
+  void submit(SchedRequest req) {
+    fold("submit", req.id, static_cast<int64_t>(req.prompt.size()));
+    Pending p;
+    p.req = std::move(req);
+    p.arrival = next_arrival_++;
+    queue_.push_back(std::move(p));
+    meters_.queue_peak = std::max<int64_t>(meters_.queue_peak, static_cast<int64_t>(queue_.size()));
+  }
+
+  void cancel(const std::string& id) { cancels_.push_back(id); }
+
+  bool idle() const { return queue_.empty() && active_count() == 0; }
+  int active_count() const {
+    int n = 0;
+    for (const auto& s : slots_) n += s.live ? 1 : 0;
+    return n;
+  }
+  int64_t queued() const { return static_cast<int64_t>(queue_.size()); }
+  const SchedMeters& meters() const { return meters_; }
+  const PrefixStats& prefix_stats() const { return cache_.stats(); }
+  uint64_t op_digest() const { return digest_; }
+  uint64_t prefix_digest() const { return cache_.digest(); }
+  int64_t now() const { return meters_.ticks; }
+
+  // Returns the number of tokens produced in this tick.
+  int64_t tick() {
+    ++meters_.ticks;
+    int64_t produced = 0;
+    sweep_cancels();
+    if (cfg_.policy == AdmissionPolicy::GrowOnDemand) grow_reservations();
+    admit();
+    produced += advance_prefills();
+    produced += decode_pass();
+    meters_.active_peak = std::max<int64_t>(meters_.active_peak, active_count());
+    return produced;
+  }
+
+  // Convenience: tick until everything submitted has retired (bounded by max_ticks).
+  int64_t run(int64_t max_ticks = 1 << 30) {
+    int64_t total = 0;
+    for (int64_t t = 0; t < max_ticks && !idle(); ++t) total += tick();
+    return total;
+  }
+
+ private:
+  struct Pending {
+    SchedRequest req;
+    int64_t arrival = 0;
+    std::vector<int32_t> generated;  // non-empty when a shed request comes back
+  };
+  enum class Phase { Prefill, Decode };
+  struct Slot {
+    bool live = false;
+    Phase phase = Phase::Prefill;
+    SchedRequest req;
+    int64_t arrival = 0;
+    std::vector<int32_t> tokens;     // prompt followed by generated tokens
+    int64_t prompt_len = 0;          // length of the sequence to prefill (prompt + regenerated tail after a shed)
+    int64_t prefilled = 0;           // positions whose KV is in the cache
+    int64_t generated = 0;
+    int64_t reserved = 0;            // positions covered by reserved blocks
+    int64_t cached = 0;              // positions attached from the prefix cache
+    int64_t already_emitted = 0;     // tokens a shed request had emitted before (not re-reported)
+  };
+
+  void fold(const char* op, const std::string& id, int64_t v) {
+    digest_ = fnv1a_bytes(digest_, op, strlen_(op));
+    digest_ = fnv1a_bytes(digest_, id.data(), id.size());
+    digest_ = fnv1a_bytes(digest_, &v, sizeof(v));
+  }
+  static size_t strlen_(const char* s) { size_t n = 0; while (s[n]) ++n; return n; }
+
+  int64_t blocks_for(int64_t tokens) const {
+    const int64_t b = eng_->block_tokens();
+    return (tokens + b - 1) / b;
+  }
+
+  void sweep_cancels() {
+    for (const std::string& id : cancels_) {
+      bool found = false;
+      for (size_t s = 0; s < slots_.size(); ++s) {
+        if (slots_[s].live && slots_[s].req.id == id) {
+          retire(static_cast<int>(s), RetireReason::Cancelled);
+          found = true;
+          break;
+        }
+      }
+      if (!found) {
+        for (auto it = queue_.begin(); it != queue_.end(); ++it) {
+          if (it->req.id == id) {
+            fold("cancel_queued", id, 0);
+            if (obs_) obs_->on_retire(id, RetireReason::Cancelled, static_cast<int64_t>(it->generated.size()));
+            ++meters_.cancelled;
+            queue_.erase(it);
+            break;
+          }
+        }
+      }
+    }
+    cancels_.clear();
+  }
+
+  // Youngest live request goes back to the head of the queue, keeping what it generated so far.
+  bool shed_youngest(int except_slot) {
+    int victim = -1;
+    for (size_t s = 0; s < slots_.size(); ++s) {
+      if (!slots_[s].live || static_cast<int>(s) == except_slot) continue;
+      if (victim < 0 || slots_[s].arrival > slots_[victim].arrival) victim = static_cast<int>(s);
+    }
+    if (victim < 0) return false;
+    Slot& v = slots_[victim];
+    Pending p;
+    p.req = v.req;
+    p.arrival = v.arrival;
+    p.generated.assign(v.tokens.begin() + static_cast<int64_t>(v.req.prompt.size()), v.tokens.end());
+    fold("shed", v.req.id, v.generated);
+    ++meters_.shed;
+    eng_->close(victim);
+    v = Slot();
+    // keep FIFO order by arrival
+    auto pos = queue_.begin();
+    while (pos != queue_.end() && pos->arrival < p.arrival) ++pos;
+    queue_.insert(pos, std::move(p));
+    return true;
+  }
+
+  bool ensure_reserved(int s, int64_t tokens) {
+    Slot& sl = slots_[s];
+    if (tokens <= sl.reserved) return true;
+    for (;;) {
+      if (eng_->reserve(s, tokens)) {
+        sl.reserved = blocks_for(tokens) * eng_->block_tokens();
+        return true;
+      }
+      const int64_t need = blocks_for(tokens) - blocks_for(sl.reserved);
+      const int64_t freed = cache_.evict_to_free(
+          need, [this](int32_t b) { return eng_->block_refcount(b); }, [this](int32_t b) { eng_->release_block(b); });
+      if (freed > 0) continue;
+      return false;
+    }
+  }
+
+  void grow_reservations() {
+    // oldest first, so the youngest is the one that finds the pool dry
+    std::vector<int> order;
+    for (size_t s = 0; s < slots_.size(); ++s)
+      if (slots_[s].live && slots_[s].phase == Phase::Decode) order.push_back(static_cast<int>(s));
+    std::sort(order.begin(), order.end(), [this](int a, int b) { return slots_[a].arrival < slots_[b].arrival; });
+    for (int s : order) {
+      if (!slots_[s].live) continue;
+      const int64_t want = static_cast<int64_t>(slots_[s].tokens.size()) + cfg_.grow_margin_tokens +
+                           eng_->max_tokens_per_step() - 1;
+      while (slots_[s].live && !ensure_reserved(s, want)) {
+        if (!shed_youngest(s)) {
+          retire(s, RetireReason::Error);
+          break;
+        }
+      }
+    }
+  }
+
+  int free_slot() const {
+    for (size_t s = 0; s < slots_.size(); ++s)
+      if (!slots_[s].live) return static_cast<int>(s);
+    return -1;
+  }
+
+  void admit() {
+    while (!queue_.empty()) {
+      const int s = free_slot();
+      if (s < 0) return;
+      Pending& p = queue_.front();
+      const int64_t seq_len = static_cast<int64_t>(p.req.prompt.size() + p.generated.size());
+      const int64_t remaining = p.req.max_tokens - static_cast<int64_t>(p.generated.size());
+      const int64_t total = seq_len + std::max<int64_t>(remaining, 1);
+      if (seq_len == 0 || total > eng_->max_context()) {
+        fold("reject", p.req.id, total);
+        if (obs_) obs_->on_retire(p.req.id, RetireReason::Error, 0);
+        queue_.pop_front();
+        continue;
+      }
+      Slot sl;
+      sl.live = true;
+      sl.req = p.req;
+      sl.arrival = p.arrival;
+      sl.tokens = p.req.prompt;
+      sl.tokens.insert(sl.tokens.end(), p.generated.begin(), p.generated.end());
+      sl.prompt_len = seq_len;
+      sl.generated = static_cast<int64_t>(p.generated.size());
+      sl.already_emitted = sl.generated;
+      // prefix lookup (over the sequence to prefill)
+      PrefixHit hit;
+      if (cfg_.prefix_cache && sl.req.prefix_cache && seq_len >= cfg_.prefix_min_tokens)
+        hit = cache_.lookup(sl.tokens.data(), seq_len, meters_.ticks);
+      slots_[s] = std::move(sl);
+      Slot& cur = slots_[s];
+      if (hit.tokens > 0) {
+        eng_->attach_prefix(s, hit.blocks);
+        cur.cached = cur.prefilled = cur.reserved = hit.tokens;
+      }
+      const int64_t want = cfg_.policy == AdmissionPolicy::FullReserve
+                               ? total + eng_->max_tokens_per_step() - 1
+                               : seq_len + cfg_.grow_margin_tokens;
+      if (!ensure_reserved(s, want)) {
+        // not enough blocks even after evicting the prefix cache: wait for a retirement
+        eng_->close(s);
+        slots_[s] = Slot();
+        if (active_count() == 0) {
+          // nothing will ever free blocks: the request cannot run
+          fold("reject", queue_.front().req.id, want);
+          if (obs_) obs_->on_retire(queue_.front().req.id, RetireReason::Error, 0);
+          queue_.pop_front();
+          continue;
+        }
+        return;
+      }
+      fold("admit", cur.req.id, (static_cast<int64_t>(s) << 40) | hit.tokens);
+      ++meters_.admitted;
+      meters_.prefix_hit_tokens += hit.tokens;
+      if (obs_) obs_->on_admit(cur.req.id, s, hit.tokens);
+      queue_.pop_front();
+    }
+  }
+
+  int64_t advance_prefills() {
+    bool decoders = false;
+    for (const auto& s : slots_) decoders |= s.live && s.phase == Phase::Decode;
+    int64_t budget = decoders ? cfg_.prefill_budget_busy : cfg_.prefill_budget_idle;
+    int64_t produced = 0;
+    // oldest reader first
+    std::vector<int> order;
+    for (size_t s = 0; s < slots_.size(); ++s)
+      if (slots_[s].live && slots_[s].phase == Phase::Prefill) order.push_back(static_cast<int>(s));
+    std::sort(order.begin(), order.end(), [this](int a, int b) { return slots_[a].arrival < slots_[b].arrival; });
+    for (int s : order) {
+      while (budget > 0 && slots_[s].live && slots_[s].phase == Phase::Prefill) {
+        Slot& sl = slots_[s];
+        const int64_t left = sl.prompt_len - sl.prefilled;
+        const int64_t n = std::min<int64_t>({left, budget, cfg_.prefill_chunk});
+        const bool last = n == left;
+        const int32_t tok = eng_->prefill(s, sl.tokens.data() + sl.prefilled, sl.prefilled, n, last);
+        fold("prefill", sl.req.id, (sl.prefilled << 20) | n);
+        ++meters_.prefill_calls;
+        meters_.prefill_tokens += n;
+        sl.prefilled += n;
+        budget -= n;
+        if (last) {
+          sl.phase = Phase::Decode;
+          publish(s, sl.prompt_len);
+          produced += accept_token(s, tok) ? 1 : 0;
+        }
+      }
+      if (budget <= 0) break;
+    }
+    return produced;
+  }
+
+  int64_t decode_pass() {
+    std::vector<int> batch;
+    for (size_t s = 0; s < slots_.size(); ++s)
+      if (slots_[s].live && slots_[s].phase == Phase::Decode && slots_[s].decode_ready()) batch.push_back(static_cast<int>(s));
+    if (batch.empty()) return 0;
+    ++meters_.decode_passes;
+    const auto out = eng_->step_batch(batch);
+    int64_t produced = 0;
+    for (size_t i = 0; i < batch.size(); ++i) {
+      const int s = batch[i];
+      slots_[s].prefilled = static_cast<int64_t>(slots_[s].tokens.size());
+      for (int32_t t : out[i]) {
+        if (!slots_[s].live) break;
+        produced += accept_token(s, t) ? 1 : 0;
+      }
+    }
+    meters_.decode_tokens += produced;
+    return produced;
+  }
+
+  // Appends a token; returns true when it was delivered (not a swallowed eos/stop).
+  bool accept_token(int s, int32_t tok) {
+    Slot& sl = slots_[s];
+    const bool is_eos = !sl.req.ignore_eos &&
+                        std::find(sl.req.eos_ids.begin(), sl.req.eos_ids.end(), tok) != sl.req.eos_ids.end();
+    const bool is_stop = std::find(sl.req.stop_ids.begin(), sl.req.stop_ids.end(), tok) != sl.req.stop_ids.end();
+    if (is_eos || is_stop) {
+      fold("eos", sl.req.id, tok);
+      retire(s, is_eos ? RetireReason::Eos : RetireReason::Stop);
+      return false;
+    }
+    sl.tokens.push_back(tok);
+    ++sl.generated;
+    fold("token", sl.req.id, tok);
+    if (obs_ && sl.generated > sl.already_emitted) obs_->on_token(sl.req.id, tok, sl.generated - 1);
+    if (sl.generated >= sl.req.max_tokens) retire(s, RetireReason::Length);
+    return true;
+  }
+
+  void publish(int s, int64_t tokens) {
+    Slot& sl = slots_[s];
+    if (!cfg_.prefix_cache || !sl.req.prefix_cache || tokens < cfg_.prefix_min_tokens) return;
+    const auto blocks = eng_->slot_blocks(s);
+    cache_.insert(
+        sl.tokens.data(), tokens, blocks, meters_.ticks, !sl.req.cache_key.empty(),
+        [this](int32_t b) { eng_->retain_block(b); }, [this](int32_t b) { eng_->release_block(b); });
+  }
+
+  void retire(int s, RetireReason why) {
+    Slot& sl = slots_[s];
+    // positions whose KV is complete: everything but the last token (never fed back through the model)
+    if (why != RetireReason::Error && why != RetireReason::Cancelled && sl.phase == Phase::Decode)
+      publish(s, std::min<int64_t>(sl.prefilled, static_cast<int64_t>(sl.tokens.size())));
+    fold("retire", sl.req.id, static_cast<int64_t>(why));
+    ++meters_.retired;
+    if (why == RetireReason::Cancelled) ++meters_.cancelled;
+    if (obs_) obs_->on_retire(sl.req.id, why, sl.generated);
+    eng_->close(s);
+    sl = Slot();
+  }
+
+  SchedulerEngine* eng_;
+  SchedulerConfig cfg_;
+  SchedulerObserver* obs_;
+  PrefixCache cache_;
+  std::vector<Slot> slots_;
+  std::deque<Pending> queue_;
+  std::vector<std::string> cancels_;
+  SchedMeters meters_;
+  int64_t next_arrival_ = 0;
+  uint64_t digest_ = kFnvSeed;
+};
+
+}  // namespace dgpp

@@ -13,10 +13,8 @@ from ._lib import call, ptr, stream_ptr
 _FMT_GEMV = {"nvfp4": 0, "mxfp4": 1, "bf16": 2}
 _FMT_GEMM = {"bf16": 0, "nvfp4": 1, "fp8": 2, "mxfp4": 3}
 
-# Converted-weight element type for the fp4 tensor-core path: 1 = f16 (one multiply per pair),
-# 0 = bf16 (bit re-biasing + multiply).  Both are exact; f16 needs kind::f16 to accept an f16 A
-# operand together with a bf16 B operand.
-A_F16_DEFAULT = 1
+# The converted-weight operand is always bf16: tcgen05 kind::f16 takes A and B of one 16-bit type.
+A_F16_DEFAULT = 0
 
 
 def _chk(t: torch.Tensor, dtype, name: str):
