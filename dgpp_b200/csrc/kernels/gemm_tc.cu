@@ -67,22 +67,22 @@ __device__ __forceinline__ void report(DeviceStatus* st, int code, int detail) {
 
 // Bounded mbarrier wait with a wall-clock limit (~2 s); false on expiry.
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  // fast path: no timer reads while the barrier completes within a few thousand polls
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  // slow path: bound the wait by the SM cycle counter (about 2 s at 2 GHz)
+  const long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 2048; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > 2000000000ull) return false;
+    if (clock64() - t0 > 4000000000ll) return false;
   }
 }
 
 // WMODE: 0 bf16, 1 nvfp4, 2 fp8 block, 3 mxfp4.  Converted operands are bf16 (kind::f16 requires A and B
 // to have the same 16-bit type; mixing an f16 A with a bf16 B is an illegal instruction on sm_100a).
 template <int BN, int WMODE, int SB, int SA, int SR>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, (WMODE != 0 && BN <= 32) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or packed raw weights (uint8)
                const __grid_constant__ CUtensorMap tmB,   // activations bf16 [T, K]
                const __grid_constant__ CUtensorMap tmSf,  // NVFP4 scales (uint8) [N, K/16]
@@ -93,7 +93,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
   // carve shared memory (all tile bases 1024-byte aligned)
   unsigned char* sp = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* sB = sp;                   sp += SB * L::kStageB;
-  sp = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sp) + 1023) & ~uintptr_t(1023));
   unsigned char* sA = sp;                   sp += (kQuant ? SA : SB) * L::kStageA;
   unsigned char* sRaw = sp;                 sp += kQuant ? SR * L::kStageRaw : 0;
   unsigned char* sSf = sp;                  sp += (WMODE == 1) ? SR * L::kStageSf : 0;
@@ -388,13 +387,15 @@ struct GemmCfg {
   static constexpr bool kQuant = WMODE != 0;
   // ring depths: deep raw prefetch for small BN (weight streaming), wide B ring for large BN
   static constexpr int kBf16Depth = (200 * 1024) / (BN * 128 + kBM * 128);
+  // Quantised weights with a small token tile run two CTAs per SM (<= 113 KB each): the second CTA hides
+  // the converter <-> tensor-core handshakes of the first while both keep HBM requests in flight.
   static constexpr int SB = !kQuant ? (kBf16Depth > 8 ? 8 : kBf16Depth)
-                                    : (BN <= 32 ? 12 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4)));
-  static constexpr int SA = kQuant ? (BN <= 128 ? 4 : 3) : 1;
-  static constexpr int SR = kQuant ? (BN <= 64 ? 4 : 2) : 1;
+                                    : (BN <= 16 ? 8 : (BN <= 32 ? 6 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4))));
+  static constexpr int SA = kQuant ? (BN <= 32 ? 3 : (BN <= 128 ? 4 : 3)) : 1;
+  static constexpr int SR = kQuant ? (BN <= 32 ? 2 : (BN <= 64 ? 4 : 2)) : 1;
   static constexpr size_t smem() {
     size_t s = 1024;  // alignment slack
-    s += static_cast<size_t>(SB) * BN * 128 + 1024;
+    s += static_cast<size_t>(SB) * BN * 128;
     s += static_cast<size_t>(kQuant ? SA : SB) * kBM * 128;
     if (kQuant) s += static_cast<size_t>(SR) * kBM * 128;
     if (WMODE == 1) s += static_cast<size_t>(SR) * kBM * 16;

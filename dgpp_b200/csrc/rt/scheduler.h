@@ -381,7 +381,7 @@ class Scheduler {
   int64_t decode_pass() {
     std::vector<int> batch;
     for (size_t s = 0; s < slots_.size(); ++s)
-      if (slots_[s].live && slots_[s].phase == Phase::Decode && slots_[s].decode_ready()) batch.push_back(static_cast<int>(s));
+      if (slots_[s].live && slots_[s].phase == Phase::Decode) batch.push_back(static_cast<int>(s));
     if (batch.empty()) return 0;
     ++meters_.decode_passes;
     const auto out = eng_->step_batch(batch);
