@@ -154,6 +154,70 @@ def gemm_tc(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
     return out if out is not None else out32
 
 
+class QuantAct:
+    """Activations quantised to R residual NVFP4 terms: x ~= g[t] * sum_r dequant(q[r], sf[r])."""
+
+    def __init__(self, q, sf, g, rows, k, terms):
+        self.q, self.sf, self.g, self.rows, self.k, self.terms = q, sf, g, rows, k, terms
+
+    @property
+    def rows_pad(self) -> int:
+        return self.q.shape[1]
+
+    def dequant(self) -> torch.Tensor:
+        from ..quant.formats import e2m1_decode, unpack_nibbles
+        tot = torch.zeros(self.rows, self.k, dtype=torch.float32, device=self.q.device)
+        for r in range(self.terms):
+            v = e2m1_decode(unpack_nibbles(self.q[r, :self.rows])).view(self.rows, self.k // 16, 16)
+            s = self.sf[r, :self.rows].view(torch.float8_e4m3fn).float().unsqueeze(-1)
+            tot += (v * s).view(self.rows, self.k)
+        return tot * self.g[:self.rows].unsqueeze(-1)
+
+
+def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = None) -> QuantAct:
+    _chk(x, torch.bfloat16, "x")
+    rows, k = x.shape
+    if out is None:
+        rp = max(16, (rows + 15) // 16 * 16)
+        out = QuantAct(torch.zeros(terms, rp, k // 2, dtype=torch.uint8, device=x.device),
+                       torch.zeros(terms, rp, k // 16, dtype=torch.uint8, device=x.device),
+                       torch.ones(rp, dtype=torch.float32, device=x.device), rows, k, terms)
+    out.rows = rows
+    call("dgpp_act_quant_nvfp4", ptr(x), x.stride(0), ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k,
+         out.terms, stream_ptr())
+    return out
+
+
+def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
+             out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, bn: Optional[int] = None,
+             splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None) -> torch.Tensor:
+    """Block-scaled NVFP4 tensor-core linear on pre-quantised activations."""
+    assert w.fmt == "nvfp4" and xa.k == w.k
+    rows = xa.rows
+    dev = xa.q.device
+    if out is None and out32 is None:
+        out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=dev)
+    ldc = (out if out is not None else out32).stride(0)
+    if bn is None:
+        bn = pick_bn(rows)
+        if xa.terms > 1:
+            bn = min(bn, 64)
+    if splits is None:
+        tiles = math.ceil(w.n / 128) * math.ceil(rows / bn)
+        splits = 1 if tiles >= 148 else max(1, min(148 // tiles, (w.k // 256) // 2))
+    wsp = cnt = None
+    if splits > 1:
+        ws = ws or default_workspace(dev)
+        if splits * rows * w.n > ws.partials.numel():
+            splits = 1
+        else:
+            wsp, cnt = ws.partials, ws.counters
+    call("dgpp_gemm_fp4", bn, ptr(xa.q), ptr(xa.sf), ptr(xa.g), xa.terms, xa.rows_pad, ptr(w.payload), ptr(w.scale),
+         float(w.alpha), ptr(out), ptr(out32), ptr(resid), ldc, rows, w.n, w.k, splits, ptr(wsp), ptr(cnt),
+         stream_ptr())
+    return out if out is not None else out32
+
+
 def linear(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
            resid: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Dispatch a linear layer to the tensor-core kernel (all row counts)."""
@@ -191,3 +255,22 @@ def attn_decode(q, q_stride: int, cache, block_table, row_req, positions, hq: in
 
 def check_status() -> None:
     _lib.check_status()
+
+
+def attn_decode_tc(q, q_stride: int, cache, block_table, row_req, positions, hq: int, hkv: int, d: int,
+                   scale: float, splits: int = 1, scratch=None, out=None, window: int = 0):
+    """Tensor-core (tcgen05, FP8 operands) decode attention over an FP8 paged cache; head_dim 128."""
+    assert cache.fp8, "the tensor-core decode path reads e4m3 caches"
+    rows = positions.numel()
+    if out is None:
+        out = torch.empty(rows, hq * d, dtype=torch.bfloat16, device=positions.device)
+    ml = acc = None
+    if splits > 1:
+        if scratch is None:
+            scratch = (torch.empty(rows * hq * splits * 2, dtype=torch.float32, device=out.device),
+                       torch.empty(rows * hq * splits * d, dtype=torch.float32, device=out.device))
+        ml, acc = scratch
+    call("dgpp_attn_decode_tc", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale),
+         ptr(cache.v_scale), ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq,
+         hkv, d, cache.page, block_table.shape[1], cache.k.shape[0], splits, float(scale), window, stream_ptr())
+    return out
