@@ -1,0 +1,234 @@
+// Activation producer + NVFP4 residual-term quantiser, one thread-block CLUSTER per row.
+//
+// A decode batch has only a handful of rows, so one CTA per row leaves the GPU idle; here the K columns of a row
+// are split over the CTAs of a cluster (up to 8), and the two row-wide reductions (sum of squares for RMSNorm,
+// max |x| for the activation scale) go through distributed shared memory: every CTA publishes its partial in
+// its own shared memory, the cluster synchronises, and every CTA folds the partials in ascending CTA order
+// (so all CTAs compute bit-identical row statistics).
+//
+// Modes, output layout and arithmetic are those of fused_act_quant_kernel in gemm_fp4.cu:
+//   0 plain rows, 1 swiglu([gate | up]), 2 rmsnorm(resid + delta) * w
+//   q rows [token tile][term][token], scale factors in tcgen05.cp atom order per token tile.
+#include <cooperative_groups.h>
+
+#include "common/common.h"
+#include "common/dtypes.cuh"
+#include "common/ptx.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace dgpp {
+
+constexpr int kAqThreads = 128;
+constexpr int kAqAtom = 512;
+
+struct ClusterQuantArgs {
+  const bf16* in;
+  int64_t in_stride;
+  const bf16* delta;
+  const bf16* w;
+  bf16* resid_out;
+  bf16* x_out;
+  uint8_t* q;
+  uint8_t* sf;
+  float* g;
+  int T, T_pad, K, R, bn, cl;
+  float eps, limit;
+  int one_plus_w;
+};
+
+__device__ __forceinline__ float warp_red(float v, bool is_max) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float u = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, u) : v + u;
+  }
+  return v;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQuantArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* seg = reinterpret_cast<bf16*>(smem_raw);  // this CTA's K / cl columns
+  __shared__ float wred[kAqThreads / 32];
+  __shared__ float part[2];                       // [0] sum of squares, [1] max |x| of this CTA's segment
+  cg::cluster_group cluster = cg::this_cluster();
+  pdl_wait();
+  const int c = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int cl = a.cl, K = a.K, kseg = K / cl, k0 = c * kseg, nvec = kseg / 8;
+  auto cta_reduce = [&](float v, bool is_max) {
+    v = warp_red(v, is_max);
+    if (lane == 0) wred[wid] = v;
+    __syncthreads();
+    float r = wred[0];
+    for (int i = 1; i < kAqThreads / 32; ++i) r = is_max ? fmaxf(r, wred[i]) : r + wred[i];
+    __syncthreads();
+    return r;
+  };
+  auto cluster_fold = [&](int slot, bool is_max) {
+    float r = is_max ? 0.f : 0.f;
+    for (int i = 0; i < cl; ++i) {
+      const float* remote = cluster.map_shared_rank(part, i);
+      const float v = remote[slot];
+      r = is_max ? fmaxf(r, v) : r + v;
+    }
+    return r;
+  };
+  float amax = 0.f;
+  if (MODE == 2) {
+    const bf16* rr = a.in + static_cast<size_t>(t) * a.in_stride + k0;
+    float ss = 0.f;
+    for (int i = tid; i < nvec; i += kAqThreads) {
+      Pack16 x;
+      x.u = reinterpret_cast<const uint4*>(rr)[i];
+      if (a.delta) {
+        Pack16 d;
+        d.u = reinterpret_cast<const uint4*>(a.delta + static_cast<size_t>(t) * K + k0)[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x.h[j] = f32_to_bf16(bf16_to_f32(x.h[j]) + bf16_to_f32(d.h[j]));
+        reinterpret_cast<uint4*>(a.resid_out + static_cast<size_t>(t) * K + k0)[i] = x.u;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float f = bf16_to_f32(x.h[j]); ss += f * f; }
+      reinterpret_cast<uint4*>(seg)[i] = x.u;
+    }
+    ss = cta_reduce(ss, false);
+    if (tid == 0) part[0] = ss;
+    cluster.sync();
+    const float rstd = rsqrtf(cluster_fold(0, false) / static_cast<float>(K) + a.eps);
+    for (int i = tid; i < nvec; i += kAqThreads) {
+      Pack16 x, ww;
+      x.u = reinterpret_cast<const uint4*>(seg)[i];
+      ww.u = reinterpret_cast<const uint4*>(a.w + k0)[i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float nrm = bf16_to_f32(f32_to_bf16(bf16_to_f32(x.h[j]) * rstd));
+        float gw = bf16_to_f32(ww.h[j]);
+        if (a.one_plus_w) gw += 1.f;
+        x.h[j] = f32_to_bf16(nrm * gw);
+        amax = fmaxf(amax, fabsf(bf16_to_f32(x.h[j])));
+      }
+      reinterpret_cast<uint4*>(seg)[i] = x.u;
+      if (a.x_out) reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(t) * K + k0)[i] = x.u;
+    }
+  } else {
+    const bf16* rr = a.in + static_cast<size_t>(t) * a.in_stride + k0;
+    for (int i = tid; i < nvec; i += kAqThreads) {
+      Pack16 x;
+      x.u = reinterpret_cast<const uint4*>(rr)[i];
+      if (MODE == 1) {
+        Pack16 u;
+        u.u = reinterpret_cast<const uint4*>(rr + K)[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float gv = bf16_to_f32(x.h[j]), uv = bf16_to_f32(u.h[j]);
+          if (a.limit > 0.f) { gv = fminf(gv, a.limit); uv = fminf(fmaxf(uv, -a.limit), a.limit); }
+          const float sl = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-gv))));
+          x.h[j] = f32_to_bf16(sl * uv);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(bf16_to_f32(x.h[j])));
+      reinterpret_cast<uint4*>(seg)[i] = x.u;
+      if (a.x_out) reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(t) * K + k0)[i] = x.u;
+    }
+  }
+  amax = cta_reduce(amax, true);
+  if (tid == 0) part[1] = amax;
+  cluster.sync();
+  amax = cluster_fold(1, true);
+  const float gs = amax > 0.f ? amax / (6.f * 256.f) : 1.f;
+  if (c == 0 && tid == 0) a.g[t] = gs;
+  const float inv_g = 1.f / gs;
+  const int stages = K / 256;
+  const int atoms = a.R * a.bn > 128 ? 2 : 1;
+  const int tile = t / a.bn, m = t % a.bn;
+  for (int gl = tid; gl < kseg / 16; gl += kAqThreads) {
+    const int gi = k0 / 16 + gl;
+    Pack16 lo, hi;
+    lo.u = reinterpret_cast<const uint4*>(seg + gl * 16)[0];
+    hi.u = reinterpret_cast<const uint4*>(seg + gl * 16)[1];
+    float res[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      res[j] = bf16_to_f32(lo.h[j]) * inv_g;
+      res[8 + j] = bf16_to_f32(hi.h[j]) * inv_g;
+    }
+    const int st = gi >> 4, step = (gi >> 2) & 3, fi = gi & 3;
+    for (int r = 0; r < a.R; ++r) {
+      float bm = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) bm = fmaxf(bm, fabsf(res[j]));
+      const uint8_t sb = f32_to_e4m3(bm * (1.f / 6.f));
+      const float s = e4m3_to_f32(sb);
+      const float inv_s = s > 0.f ? 1.f / s : 0.f;
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const uint32_t cde = f32_to_e2m1(res[j] * inv_s);
+        res[j] -= e2m1_to_f32(cde) * s;
+        if (j < 8) w0 |= cde << (4 * j); else w1 |= cde << (4 * (j - 8));
+      }
+      const size_t ro = static_cast<size_t>(tile) * a.R * a.bn + static_cast<size_t>(r) * a.bn + m;
+      *reinterpret_cast<uint2*>(a.q + ro * (K / 2) + gi * 8) = make_uint2(w0, w1);
+      const int brow = r * a.bn + m, h = brow >> 7, mm = brow & 127;
+      const size_t atom_idx = ((static_cast<size_t>(tile) * stages + st) * 4 + step) * atoms + h;
+      a.sf[atom_idx * kAqAtom + (mm & 31) * 16 + (mm >> 5) * 4 + fi] = sb;
+    }
+  }
+  cluster.sync();  // keep every CTA's shared memory alive until all remote reads are done
+}
+
+template <int MODE>
+static int launch_cluster(const ClusterQuantArgs& a, cudaStream_t st) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(a.cl, a.T, 1);
+  cfg.blockDim = dim3(kAqThreads, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(a.K / a.cl) * 2;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = a.cl;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  DGPP_CUDA_OK(cudaLaunchKernelEx(&cfg, act_quant_cluster_kernel<MODE>, a));
+  return 0;
+}
+
+}  // namespace dgpp
+
+using namespace dgpp;
+
+// Same contract as dgpp_act_quant_nvfp4, row split over a cluster of `cl` CTAs (1, 2, 4 or 8; K / cl % 16 == 0).
+DGPP_API int dgpp_act_quant_nvfp4_cluster(int mode, const void* in, int64_t in_stride, const void* delta,
+                                          const void* w, void* resid_out, void* x_out, void* q, void* sf, void* g,
+                                          int T, int T_pad, int K, int R, int bn, int cl, float eps, float limit,
+                                          int one_plus_w, cudaStream_t st) {
+  DGPP_REQUIRE(K % 256 == 0, "act_quant: K %d must be a multiple of 256", K);
+  DGPP_REQUIRE(cl == 1 || cl == 2 || cl == 4 || cl == 8, "act_quant: cluster size %d not in {1,2,4,8}", cl);
+  DGPP_REQUIRE((K / cl) % 16 == 0 && K % cl == 0, "act_quant: K %d does not split over %d CTAs", K, cl);
+  DGPP_REQUIRE(R >= 1 && R <= 4 && R * bn <= 256, "act_quant: bad terms %d / tile %d", R, bn);
+  DGPP_REQUIRE(T_pad % bn == 0 && T_pad >= T, "act_quant: T_pad %d must be a multiple of bn %d and >= T", T_pad, bn);
+  DGPP_REQUIRE(static_cast<size_t>(K / cl) * 2 <= 48 * 1024, "act_quant: segment too large");
+  if (T == 0) return 0;
+  ClusterQuantArgs a;
+  a.in = static_cast<const bf16*>(in);
+  a.in_stride = in_stride;
+  a.delta = static_cast<const bf16*>(delta);
+  a.w = static_cast<const bf16*>(w);
+  a.resid_out = static_cast<bf16*>(resid_out);
+  a.x_out = static_cast<bf16*>(x_out);
+  a.q = static_cast<uint8_t*>(q);
+  a.sf = static_cast<uint8_t*>(sf);
+  a.g = static_cast<float*>(g);
+  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.cl = cl; a.eps = eps; a.limit = limit;
+  a.one_plus_w = one_plus_w;
+  if (mode == 0) return launch_cluster<0>(a, st);
+  if (mode == 1) return launch_cluster<1>(a, st);
+  if (mode == 2) return launch_cluster<2>(a, st);
+  dgpp_set_error("act_quant: unknown mode %d", mode);
+  return -1;
+}

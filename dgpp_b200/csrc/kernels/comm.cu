@@ -1,0 +1,290 @@
+// Tensor-parallel collectives over NVLink peer memory, issued from our own kernels (no NCCL on this path).
+//
+// Symmetric memory: every rank cudaMallocs one region of the same size and shares it through CUDA IPC;
+// each rank keeps a device table with the W peer base pointers (its own included).  Region layout:
+//     [ 2 parities ][ W source slots ][ slot_bytes ]   payload pushed by the source rank
+//     [ 2 parities ][ W source slots ][ kMaxCtas ]     uint32 flags (epoch numbers)
+//     pick table: [ 2 parities ][ W ][ kPickRows ] (value, id) pairs + [2][W] flags
+//
+// One-shot all-reduce (decode sizes): every CTA owns a slice of the vector.  It stores its bf16 slice into
+// slot `me` of every peer (plain 16-byte stores to peer pointers), fences at system scope, raises
+// flag[parity][me][cta] = epoch on every peer with st.release.sys, then waits (ld.acquire.sys, bounded) for the
+// W flags of its own slice and folds the W slices in ASCENDING RANK ORDER in fp32 with one bf16 rounding, so
+// every rank computes bit-identical results.  Two parities are enough: a rank can enter all-reduce k + 2 only
+// after every peer has pushed for k + 1, i.e. has finished reading k.
+// The epoch lives in device memory and is advanced by the kernel itself, so a captured CUDA graph replays
+// without any host-side arming.
+// (reference behaviour: src/net/bus_kernel.cu:361,625,890 -- fold order and graph-node all-reduce; there the
+//  transport is RoCE with host-pinned staging, here it is direct peer stores.)
+#include <string.h>
+
+#include "common/common.h"
+#include "common/dtypes.cuh"
+#include "common/ptx.cuh"
+
+namespace dgpp {
+
+constexpr int kCommMaxWorld = 8;
+constexpr int kCommMaxCtas = 64;
+constexpr int kPickRows = 256;
+
+struct CommState {
+  unsigned char* peers[kCommMaxWorld];  // base of every rank's symmetric region (peer-mapped pointers)
+  int world, rank;
+  size_t slot_bytes;
+  uint32_t* epoch;      // device counter of completed all-reduces (local memory)
+  uint32_t* done_ctas;  // CTAs finished in the current call (local)
+  uint32_t* pick_epoch;
+};
+
+__device__ __forceinline__ unsigned char* payload(const CommState& c, int owner, int parity, int src) {
+  return c.peers[owner] + (static_cast<size_t>(parity) * c.world + src) * c.slot_bytes;
+}
+__device__ __forceinline__ uint32_t* flag(const CommState& c, int owner, int parity, int src, int cta) {
+  unsigned char* base = c.peers[owner] + 2 * static_cast<size_t>(c.world) * c.slot_bytes;
+  return reinterpret_cast<uint32_t*>(base) + (static_cast<size_t>(parity) * c.world + src) * kCommMaxCtas + cta;
+}
+__device__ __forceinline__ unsigned char* pick_base(const CommState& c, int owner) {
+  return c.peers[owner] + 2 * static_cast<size_t>(c.world) * c.slot_bytes +
+         2 * static_cast<size_t>(c.world) * kCommMaxCtas * sizeof(uint32_t);
+}
+
+// Bounded spin on a flag written by a peer; false when it gave up (about 2 s).
+__device__ __forceinline__ bool wait_flag(const uint32_t* f, uint32_t want) {
+  for (int i = 0; i < 1 << 14; ++i)
+    if (ld_acquire_sys(f) == want) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 256; ++i) {
+      if (ld_acquire_sys(f) == want) return true;
+      __nanosleep(64);
+    }
+    if (clock64() - t0 > 4000000000ll) return false;
+  }
+}
+
+// data: [n] bf16 (n multiple of 8), reduced in place.  resid (optional): out = bf16(resid + bf16(sum)).
+__global__ void __launch_bounds__(256)
+ar_oneshot_kernel(CommState c, bf16* __restrict__ data, const bf16* __restrict__ resid, int64_t n,
+                  DeviceStatus* status) {
+  pdl_wait();
+  const uint32_t epoch = *c.epoch + 1;
+  const int parity = epoch & 1;
+  const int64_t nvec = n / 8;
+  const int64_t per = (nvec + gridDim.x - 1) / gridDim.x;
+  const int64_t v0 = blockIdx.x * per, v1 = min(nvec, v0 + per);
+  // 1. push my slice to every rank (my own slot included: the fold below reads all W slots uniformly)
+  for (int64_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    const uint4 x = reinterpret_cast<const uint4*>(data)[v];
+    for (int r = 0; r < c.world; ++r) {
+      const int dst = (c.rank + r) % c.world;  // stagger destinations across ranks
+      st_v4_global(payload(c, dst, parity, c.rank) + v * 16, x);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < c.world) st_release_sys(flag(c, threadIdx.x, parity, c.rank, blockIdx.x), epoch);
+  // 2. wait for every source's flag of this slice
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    if (!wait_flag(flag(c, c.rank, parity, threadIdx.x, blockIdx.x), epoch)) {
+      if (atomicCAS(&status->code, 0, kTimeoutPeerFlag) == 0) status->detail = threadIdx.x;
+      atomicAdd(&status->count, 1);
+      ok_s = 0;
+    }
+  }
+  __syncthreads();
+  // 3. fold in ascending rank order
+  if (ok_s) {
+    for (int64_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int r = 0; r < c.world; ++r) {
+        Pack16 p;
+        p.u = ld_v4_global_volatile(payload(c, c.rank, parity, r) + v * 16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += bf16_to_f32(p.h[j]);
+      }
+      Pack16 o;
+      if (resid) {
+        Pack16 rr;
+        rr.u = reinterpret_cast<const uint4*>(resid)[v];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.h[j] = f32_to_bf16(bf16_to_f32(rr.h[j]) + bf16_to_f32(f32_to_bf16(acc[j])));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.h[j] = f32_to_bf16(acc[j]);
+      }
+      reinterpret_cast<uint4*>(data)[v] = o.u;
+    }
+  }
+  // 4. the last CTA advances the epoch for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.done_ctas, 1u) == gridDim.x - 1) {
+      *c.done_ctas = 0;
+      *c.epoch = epoch;
+      __threadfence();
+    }
+  }
+}
+
+// Vocab-sharded greedy pick: every rank contributes (value, id) of its slice per row; all ranks end up with
+// the global winner (strictly greater value wins scanning ranks ascending => ties go to the lowest rank/id).
+__global__ void __launch_bounds__(256)
+pick_merge_kernel(CommState c, int32_t* __restrict__ ids, float* __restrict__ vals, int rows, DeviceStatus* status) {
+  pdl_wait();
+  const uint32_t epoch = *c.pick_epoch + 1;
+  const int parity = epoch & 1;
+  const int t = threadIdx.x;
+  struct Pair { float v; int32_t i; };
+  auto table = [&](int owner, int src) {
+    return reinterpret_cast<Pair*>(pick_base(c, owner)) + (static_cast<size_t>(parity) * c.world + src) * kPickRows;
+  };
+  auto pflag = [&](int owner, int src) {
+    return reinterpret_cast<uint32_t*>(pick_base(c, owner) + 2 * static_cast<size_t>(c.world) * kPickRows * sizeof(Pair)) +
+           parity * c.world + src;
+  };
+  if (t < rows) {
+    Pair p{vals[t], ids[t]};
+    for (int r = 0; r < c.world; ++r) table(r, c.rank)[t] = p;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (t < c.world) st_release_sys(pflag(t, c.rank), epoch);
+  __shared__ int ok_s;
+  if (t == 0) ok_s = 1;
+  __syncthreads();
+  if (t < c.world && !wait_flag(pflag(c.rank, t), epoch)) {
+    if (atomicCAS(&status->code, 0, kTimeoutPeerFlag) == 0) status->detail = 100 + t;
+    atomicAdd(&status->count, 1);
+    ok_s = 0;
+  }
+  __syncthreads();
+  if (ok_s && t < rows) {
+    float bv = -INFINITY;
+    int32_t bi = 0;
+    for (int r = 0; r < c.world; ++r) {
+      const volatile Pair* q = table(c.rank, r) + t;
+      const float v = q->v;
+      const int32_t i = q->i;
+      if (r == 0 || v > bv) { bv = v; bi = i; }
+    }
+    ids[t] = bi;
+    vals[t] = bv;
+  }
+  __syncthreads();
+  if (t == 0) *c.pick_epoch = epoch;
+}
+
+}  // namespace dgpp
+
+using namespace dgpp;
+
+struct DgppComm {
+  CommState st;
+  void* local;
+  void* opened[kCommMaxWorld];
+  size_t region_bytes;
+};
+
+static size_t region_size(int world, size_t slot_bytes) {
+  return 2 * static_cast<size_t>(world) * slot_bytes + 2 * static_cast<size_t>(world) * kCommMaxCtas * sizeof(uint32_t) +
+         2 * static_cast<size_t>(world) * kPickRows * 8 + 2 * static_cast<size_t>(world) * sizeof(uint32_t) + 256;
+}
+
+// Step 1: allocate the local symmetric region; returns the comm handle and writes the 64-byte IPC handle.
+DGPP_API void* dgpp_comm_create(int world, int rank, int64_t slot_bytes, void* ipc_handle_out) {
+  if (world < 1 || world > kCommMaxWorld || rank < 0 || rank >= world || slot_bytes % 16 != 0) {
+    dgpp_set_error("comm_create: bad arguments (world %d rank %d slot %lld)", world, rank, (long long)slot_bytes);
+    return nullptr;
+  }
+  DgppComm* c = new DgppComm();
+  memset(c, 0, sizeof(*c));
+  c->region_bytes = region_size(world, static_cast<size_t>(slot_bytes));
+  if (cudaMalloc(&c->local, c->region_bytes) != cudaSuccess || cudaMemset(c->local, 0, c->region_bytes) != cudaSuccess) {
+    dgpp_set_error("comm_create: cudaMalloc of %zu bytes failed", c->region_bytes);
+    delete c;
+    return nullptr;
+  }
+  uint32_t* counters = nullptr;
+  if (cudaMalloc(&counters, 64) != cudaSuccess || cudaMemset(counters, 0, 64) != cudaSuccess) {
+    dgpp_set_error("comm_create: counter allocation failed");
+    cudaFree(c->local);
+    delete c;
+    return nullptr;
+  }
+  c->st.world = world;
+  c->st.rank = rank;
+  c->st.slot_bytes = static_cast<size_t>(slot_bytes);
+  c->st.epoch = counters;
+  c->st.done_ctas = counters + 1;
+  c->st.pick_epoch = counters + 2;
+  c->st.peers[rank] = static_cast<unsigned char*>(c->local);
+  if (world > 1) {
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, c->local) != cudaSuccess) {
+      dgpp_set_error("comm_create: cudaIpcGetMemHandle failed: %s", cudaGetErrorString(cudaGetLastError()));
+      cudaFree(c->local);
+      cudaFree(counters);
+      delete c;
+      return nullptr;
+    }
+    memcpy(ipc_handle_out, &h, sizeof(h));
+  }
+  cudaDeviceSynchronize();
+  return c;
+}
+
+// Step 2: map the regions of all peers.  handles: world x 64 bytes, in rank order.
+DGPP_API int dgpp_comm_connect(void* comm, const void* handles) {
+  DgppComm* c = static_cast<DgppComm*>(comm);
+  for (int r = 0; r < c->st.world; ++r) {
+    if (r == c->st.rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const unsigned char*>(handles) + r * sizeof(h), sizeof(h));
+    void* p = nullptr;
+    DGPP_CUDA_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    c->opened[r] = p;
+    c->st.peers[r] = static_cast<unsigned char*>(p);
+  }
+  return 0;
+}
+
+DGPP_API int dgpp_comm_destroy(void* comm) {
+  DgppComm* c = static_cast<DgppComm*>(comm);
+  if (!c) return 0;
+  cudaDeviceSynchronize();
+  for (int r = 0; r < c->st.world; ++r)
+    if (c->opened[r]) cudaIpcCloseMemHandle(c->opened[r]);
+  cudaFree(c->st.epoch);
+  cudaFree(c->local);
+  delete c;
+  return 0;
+}
+
+// In-place sum of `n` bf16 values over all ranks (n * 2 <= slot_bytes, n % 8 == 0); optional fused residual.
+DGPP_API int dgpp_comm_all_reduce(void* comm, void* data, const void* resid, int64_t n, int ctas, cudaStream_t st) {
+  DgppComm* c = static_cast<DgppComm*>(comm);
+  DGPP_REQUIRE(n % 8 == 0, "all_reduce: n %lld must be a multiple of 8", (long long)n);
+  DGPP_REQUIRE(static_cast<size_t>(n) * 2 <= c->st.slot_bytes, "all_reduce: %lld values exceed the slot", (long long)n);
+  if (ctas < 1) ctas = 1;
+  if (ctas > kCommMaxCtas) ctas = kCommMaxCtas;
+  ar_oneshot_kernel<<<ctas, 256, 0, st>>>(c->st, static_cast<bf16*>(data), static_cast<const bf16*>(resid), n,
+                                         device_status_ptr());
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+DGPP_API int dgpp_comm_pick_merge(void* comm, void* ids, void* vals, int rows, cudaStream_t st) {
+  DgppComm* c = static_cast<DgppComm*>(comm);
+  DGPP_REQUIRE(rows >= 1 && rows <= kPickRows, "pick_merge: rows %d outside 1..%d", rows, kPickRows);
+  pick_merge_kernel<<<1, 256, 0, st>>>(c->st, static_cast<int32_t*>(ids), static_cast<float*>(vals), rows,
+                                      device_status_ptr());
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}

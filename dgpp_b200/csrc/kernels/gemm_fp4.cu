@@ -4,20 +4,24 @@
 //     C[T, N] = alpha_w * g[t] * sum_r  Wq[N, K] . Xq_r[T, K]^T
 //
 // The packed e2m1 weight bytes go from HBM through TMA into shared memory and straight into the
-// tensor core: no thread ever touches a weight.  Activations arrive already quantised by
-// `act_quant_nvfp4_kernel` as R "residual terms": x ~= g[t] * (x_1 + x_2 + ... + x_R), each term an
+// tensor core: no thread ever touches a weight or a scale.  Activations arrive already quantised by
+// `fused_act_quant_kernel` as R "residual terms": x ~= g[t] * (x_1 + x_2 + ... + x_R), each term an
 // NVFP4 tensor of what the previous terms left over.  All R terms accumulate into the same fp32
 // TMEM accumulator, so R = 1 is plain W4A4 and R = 3 carries about 8 mantissa bits of the bf16
 // activation (every term removes ~2.6 bits of the remaining error) at no extra weight traffic.
 //
 // Layout: weight tile = UMMA A (128 rows), token tile = UMMA B (BN = 16..256 rows).  One pipeline
 // stage covers 256 K: 128 bytes of packed fp4 per row (one 128-byte swizzle row = four K=64 MMAs).
-// Scale factors are read from their checkpoint layout [rows, K/16] by four helper warps that write
-// them as the 512-byte "32 lanes x 16 bytes" atoms tcgen05.cp expects (row m, factor i of a K=64 step
-// -> byte (m % 32) * 16 + (m / 32) * 4 + i); the MMA thread copies the atoms into TMEM.
 //
-// Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2..5 scale
-// staging then epilogue.  Split-K as in gemm_tc.cu (deterministic ascending fold by the last CTA).
+// Scale factors travel in the layout tcgen05.cp consumes, so a stage's factors are one contiguous bulk
+// copy: for a tile of 128 rows and a K=64 step the 512-byte "atom" holds factor i of row m at byte
+// (m % 32) * 16 + (m / 32) * 4 + i.  Weight scales are permuted into [n_tile][stage][4 steps][atom] once at
+// bind time (an index permutation of the checkpoint bytes); the activation quantiser writes its scales in
+// [term][token_tile][stage][4 steps][atoms of the tile] directly.
+//
+// Warp roles (192 threads): warp 0 TMA / bulk-copy producer, warp 1 MMA issuer + TMEM owner (copies the
+// atoms into TMEM with tcgen05.cp, then issues the MMAs), warps 2..5 epilogue.  Split-K as in gemm_tc.cu
+// (deterministic ascending fold by the last CTA of a tile).
 // (reference counterpart: src/kernels/moe_w4a4.cu:87,139,476 -- block-scaled mma.sync m16n8k64 there.)
 #include <cuda.h>
 #include <string.h>
@@ -38,8 +42,8 @@ constexpr int kF4Atom = 512;              // bytes of one scale-factor atom (128
 struct Fp4Params {
   float alpha;                 // weight tensor scale
   const float* g;              // per-token activation scale [T]
-  const uint8_t* sfa;          // weight scales [N, K/16] (e4m3 bytes, checkpoint layout)
-  const uint8_t* sfb;          // activation scales [R, T_pad, K/16]
+  const uint8_t* sfa;          // weight scales, tiled [n_tiles][stages][4][512]
+  const uint8_t* sfb;          // activation scales, tiled [R][token_tiles][stages][4 * atoms][512]
   bf16* out;
   float* out32;
   const bf16* resid;
@@ -50,12 +54,16 @@ struct Fp4Params {
   int stages_per_split;
 };
 
-template <int BN, int RMAX, int S>
-__global__ void __launch_bounds__(kF4Threads, 1)
+// BN = MMA N = (token tile) x (residual terms): with R > 1 the terms of one token tile are stacked along N
+// (rows r * bn_tok + m of the B operand) so a K=64 step is ONE tcgen05.mma whatever R is; the epilogue adds the
+// R column groups.  Stacking needs the whole batch in one token tile (decode); R = 1 tiles freely.
+template <int BN, int S>
+__global__ void __launch_bounds__(kF4Threads, BN <= 96 ? 2 : 1)
 gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as bytes [N, K/2]
                 const __grid_constant__ CUtensorMap tmB,   // packed activations as bytes [R*T_pad, K/2]
                 Fp4Params p) {
-  constexpr int kStageB = BN * 128;                  // one term
+  constexpr int kStageB = BN * 128;
+  constexpr int RMAX = 1;
   constexpr int kAtomsB = BN > 128 ? 2 : 1;          // 128-row atoms per K=64 step
   constexpr int kSfaBytes = 4 * kF4Atom;             // 4 K-steps
   constexpr int kSfbBytes = 4 * kAtomsB * kF4Atom;   // per term
@@ -67,21 +75,21 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   unsigned char* sSfb = sp;  sp += S * RMAX * kSfbBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(sp);
   uint64_t* empty = full + S;
-  uint64_t* sf_ready = empty + S;
-  uint64_t* acc_full = sf_ready + S;
+  uint64_t* acc_full = empty + S;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kF4BM;
-  const int m0 = blockIdx.y * BN;
+  const int bn_tok = BN / p.R;             // tokens per tile
+  const int m0 = blockIdx.y * bn_tok;
   const int split = blockIdx.z, splits = gridDim.z;
   const int total_stages = p.K / kF4StageK;
   const int st_begin = split * p.stages_per_split;
   const int st_end = min(total_stages, st_begin + p.stages_per_split);
   const int nst = max(0, st_end - st_begin);
-  const int R = p.R;
+  const int R = 1;  // terms are stacked inside the single B tile
   // TMEM columns: accumulator, then double-buffered scale factors (4 columns per K=64 step and 128 rows)
   constexpr uint32_t kColD = BN < 32 ? 32 : BN;
   constexpr uint32_t kColSfa = 16;
@@ -93,7 +101,6 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
     for (int i = 0; i < S; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
-      mbar_init(&sf_ready[i], 4);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -115,16 +122,23 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   pdl_wait();
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ producer: weights, activations, scales
     if (elect_one()) {
+      const int token_tiles = p.T_pad / bn_tok;
+      const uint8_t* sfa_tile = p.sfa + static_cast<size_t>(blockIdx.x) * total_stages * kSfaBytes;
       for (int i = 0; i < nst; ++i) {
         const int s = i % S;
+        const int st = st_begin + i;
         if (!wait_bar(&empty[s], ((i / S) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 11); *abort_flag = 1; break; }
-        mbar_expect_tx(&full[s], kF4StageA + R * kStageB);
-        const int xb = (st_begin + i) * 128;  // byte column of this stage
+        mbar_expect_tx(&full[s], kF4StageA + kSfaBytes + R * (kStageB + kSfbBytes));
+        const int xb = st * 128;  // byte column of this stage
         tma_load_2d(sA + s * kF4StageA, &tmA, xb, n0, &full[s]);
-        for (int r = 0; r < R; ++r)
-          tma_load_2d(sB + (s * RMAX + r) * kStageB, &tmB, xb, r * p.T_pad + m0, &full[s]);
+        bulk_load_1d(sSfa + s * kSfaBytes, sfa_tile + static_cast<size_t>(st) * kSfaBytes, kSfaBytes, &full[s]);
+        for (int r = 0; r < R; ++r) {
+          tma_load_2d(sB + (s * RMAX + r) * kStageB, &tmB, xb, blockIdx.y * BN, &full[s]);
+          const uint8_t* sfb = p.sfb + ((static_cast<size_t>(r) * token_tiles + blockIdx.y) * total_stages + st) * kSfbBytes;
+          bulk_load_1d(sSfb + (s * RMAX + r) * kSfbBytes, sfb, kSfbBytes, &full[s]);
+        }
         if (*abort_flag) break;
       }
     }
@@ -134,9 +148,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
       constexpr uint32_t idesc = umma_idesc_fp4bs(kF4BM, BN, 0u);
       for (int i = 0; i < nst; ++i) {
         const int s = i % S;
-        const uint32_t par = (i / S) & 1;
-        if (!wait_bar(&full[s], par)) { report(p.status, kTimeoutTmaFull, 12); *abort_flag = 1; break; }
-        if (!wait_bar(&sf_ready[s], par)) { report(p.status, kTimeoutConvert, 13); *abort_flag = 1; break; }
+        if (!wait_bar(&full[s], (i / S) & 1)) { report(p.status, kTimeoutTmaFull, 12); *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t buf = i & 1;
         const uint32_t t_sfa = tmem_sfa + buf * kColSfa;
@@ -165,88 +177,40 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
       umma_commit(acc_full);
     }
   } else {
-    // ------------------------------------------------------------------ scale-factor staging (warps 2..5)
-    const int t = threadIdx.x - 64;  // 0..127 = row inside a 128-row atom
-    const int sf_pitch = p.K / 16;
-    const int arow = min(n0 + t, p.N - 1);
-    const uint8_t* a_src = p.sfa + static_cast<size_t>(arow) * sf_pitch + static_cast<size_t>(st_begin) * 16;
-    const uint32_t atom_off = (t & 31) * 16 + (t >> 5) * 4;
-    uint4 a_next = nst > 0 ? *reinterpret_cast<const uint4*>(a_src) : make_uint4(0, 0, 0, 0);
-    for (int i = 0; i < nst; ++i) {
-      const int s = i % S;
-      const uint4 a_cur = a_next;
-      if (i + 1 < nst) a_next = *reinterpret_cast<const uint4*>(a_src + static_cast<size_t>(i + 1) * 16);
-      // activation scales of this stage (small: BN rows per term), loaded before the wait
-      uint4 b_cur[RMAX * kAtomsB];
-#pragma unroll
-      for (int r = 0; r < RMAX; ++r) {
-#pragma unroll
-        for (int h = 0; h < kAtomsB; ++h) {
-          const int row = m0 + h * 128 + t;
-          b_cur[r * kAtomsB + h] = make_uint4(0, 0, 0, 0);
-          if (r < R && h * 128 + t < BN && row < p.T)
-            b_cur[r * kAtomsB + h] = *reinterpret_cast<const uint4*>(
-                p.sfb + (static_cast<size_t>(r) * p.T_pad + row) * sf_pitch + static_cast<size_t>(st_begin + i) * 16);
-        }
-      }
-      if (!wait_bar(&empty[s], ((i / S) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 14); *abort_flag = 1; break; }
-      unsigned char* da = sSfa + s * kSfaBytes + atom_off;
-      *reinterpret_cast<uint32_t*>(da + 0 * kF4Atom) = a_cur.x;
-      *reinterpret_cast<uint32_t*>(da + 1 * kF4Atom) = a_cur.y;
-      *reinterpret_cast<uint32_t*>(da + 2 * kF4Atom) = a_cur.z;
-      *reinterpret_cast<uint32_t*>(da + 3 * kF4Atom) = a_cur.w;
-#pragma unroll
-      for (int r = 0; r < RMAX; ++r) {
-        if (r < R) {
-#pragma unroll
-          for (int h = 0; h < kAtomsB; ++h) {
-            // K-step j of atom-group h lives at atom index j * kAtomsB + h
-            unsigned char* db = sSfb + (s * RMAX + r) * kSfbBytes + atom_off;
-            const uint4 v = b_cur[r * kAtomsB + h];
-            *reinterpret_cast<uint32_t*>(db + (0 * kAtomsB + h) * kF4Atom) = v.x;
-            *reinterpret_cast<uint32_t*>(db + (1 * kAtomsB + h) * kF4Atom) = v.y;
-            *reinterpret_cast<uint32_t*>(db + (2 * kAtomsB + h) * kF4Atom) = v.z;
-            *reinterpret_cast<uint32_t*>(db + (3 * kAtomsB + h) * kF4Atom) = v.w;
-          }
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sf_ready[s]);
-      if (*abort_flag) break;
-    }
-
-    // ------------------------------------------------------------------ epilogue (same warps)
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;
     const bool ok = nst > 0 ? wait_bar(acc_full, 0) : true;
     if (!ok) { report(p.status, kTimeoutAccum, 15); *abort_flag = 1; }
     tc_fence_after();
     const int n = n0 + q * 32 + lane;
-    const int cols = min(BN, p.T - m0);
+    const int cols = min(bn_tok, p.T - m0);
     if (ok && !*abort_flag) {
       float* wsp = splits > 1 ? p.ws + (static_cast<size_t>(split) * p.T + m0) * p.N : nullptr;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+      for (int c0 = 0; c0 < bn_tok; c0 += 16) {
         if (c0 >= cols) break;
-        uint32_t r[16];
-        if (nst > 0) {
-          tmem_ld_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
-          tmem_ld_wait();
-        } else {
+        float v[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) r[j] = 0;
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        if (nst > 0) {
+          for (int r = 0; r < p.R; ++r) {  // add the residual-term column groups
+            uint32_t rr[16];
+            tmem_ld_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + r * bn_tok + c0, rr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(rr[j]);
+          }
         }
         if (n < p.N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = c0 + j;
             if (m < cols) {
-              const float v = __uint_as_float(r[j]);
               if (splits > 1) {
-                wsp[static_cast<size_t>(m) * p.N + n] = v;
+                wsp[static_cast<size_t>(m) * p.N + n] = v[j];
               } else {
                 const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
-                float y = v * p.alpha * p.g[m0 + m];
+                float y = v[j] * p.alpha * p.g[m0 + m];
                 if (p.out32) p.out32[o] = y;
                 if (p.out) {
                   if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
@@ -292,78 +256,169 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
 }
 
 // --------------------------------------------------------------------------------------------------
-// Activation quantiser: bf16 rows -> R residual NVFP4 terms.
-//   g[t]      = max|x[t, :]| / (6 * 256)      (fp32; the e4m3 block scales then stay <= 256)
-//   term r    : block scale s = e4m3(amax_16(res) / (6 g)), codes = e2m1(res / (s g)), res -= codes * s * g
-// q: [R, T_pad, K/2] bytes (low nibble = even k), sf: [R, T_pad, K/16] e4m3 bytes.  One warp per row.
-// Optional fused input transforms: `gate_up` != null quantises swiglu(gate_up) instead of x.
-__global__ void __launch_bounds__(256)
-act_quant_nvfp4_kernel(const bf16* __restrict__ x, int64_t x_stride, uint8_t* __restrict__ q,
-                       uint8_t* __restrict__ sf, float* __restrict__ g, int T, int T_pad, int K, int R) {
+// Activation producer + quantiser: one CTA per row computes the row's bf16 activation (optionally with the
+// operator that precedes the linear layer fused in), then splits it into R residual NVFP4 terms:
+//   g[t]   = max|x[t, :]| / (6 * 256)            (fp32; the e4m3 block scales then stay <= 256)
+//   term r : block scale s = e4m3(amax_16(res) / 6), codes = e2m1(res / s), res -= codes * s   (res in units of g)
+// MODE 0: x = in                                    (plain rows)
+// MODE 1: x = swiglu(in = [gate | up])               bf16( bf16(silu(gate)) * up )
+// MODE 2: x = rmsnorm(resid + delta) * w             resid_out = bf16(resid + delta); x = bf16(w * bf16(r * rstd))
+// q  rows are ordered [token tile][term][token in tile]; sf : [T_pad / bn][K / 256][4 steps][atoms][512] e4m3 bytes in
+//      tcgen05.cp atom order, where the B-operand row of (term r, token m) is r * bn + m and atoms = (R * bn > 128 ? 2 : 1)
+// The bf16 activation itself is also written when `x_out` is given (the prefill path and tests read it).
+struct QuantArgs {
+  const bf16* in;        // MODE 0: [T, K]; MODE 1: [T, 2K]; MODE 2: residual [T, K]
+  int64_t in_stride;
+  const bf16* delta;     // MODE 2 (optional)
+  const bf16* w;         // MODE 2 norm weight
+  bf16* resid_out;       // MODE 2
+  bf16* x_out;           // optional bf16 copy of the activation
+  uint8_t* q;
+  uint8_t* sf;
+  float* g;
+  int T, T_pad, K, R, bn;
+  float eps, limit;
+  int one_plus_w;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(256) fused_act_quant_kernel(QuantArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* row_s = reinterpret_cast<bf16*>(smem_raw);  // [K]
+  __shared__ float red[8];
   pdl_wait();
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= T) return;
-  const bf16* row = x + static_cast<size_t>(warp) * x_stride;
-  const int groups = K / 16;
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int K = a.K, nvec = K / 8;
+  auto block_reduce = [&](float v, bool is_max) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float u = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, u) : v + u;
+    }
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int i = 1; i < 8; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+    __syncthreads();
+    return r;
+  };
   float amax = 0.f;
-  for (int gi = lane; gi < groups; gi += 32) {
-    Pack16 a, b;
-    a.u = reinterpret_cast<const uint4*>(row + gi * 16)[0];
-    b.u = reinterpret_cast<const uint4*>(row + gi * 16)[1];
+  if (MODE == 2) {
+    const bf16* rr = a.in + static_cast<size_t>(t) * a.in_stride;
+    float ss = 0.f;
+    for (int i = tid; i < nvec; i += 256) {
+      Pack16 x;
+      x.u = reinterpret_cast<const uint4*>(rr)[i];
+      if (a.delta) {
+        Pack16 d;
+        d.u = reinterpret_cast<const uint4*>(a.delta + static_cast<size_t>(t) * K)[i];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fmaxf(fabsf(bf16_to_f32(a.h[j])), fabsf(bf16_to_f32(b.h[j]))));
+        for (int j = 0; j < 8; ++j) x.h[j] = f32_to_bf16(bf16_to_f32(x.h[j]) + bf16_to_f32(d.h[j]));
+        reinterpret_cast<uint4*>(a.resid_out + static_cast<size_t>(t) * K)[i] = x.u;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float f = bf16_to_f32(x.h[j]); ss += f * f; }
+      reinterpret_cast<uint4*>(row_s)[i] = x.u;
+    }
+    const float rstd = rsqrtf(block_reduce(ss, false) / static_cast<float>(K) + a.eps);
+    for (int i = tid; i < nvec; i += 256) {
+      Pack16 x, ww;
+      x.u = reinterpret_cast<const uint4*>(row_s)[i];
+      ww.u = reinterpret_cast<const uint4*>(a.w)[i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float nrm = bf16_to_f32(f32_to_bf16(bf16_to_f32(x.h[j]) * rstd));
+        float gw = bf16_to_f32(ww.h[j]);
+        if (a.one_plus_w) gw += 1.f;
+        x.h[j] = f32_to_bf16(nrm * gw);
+        amax = fmaxf(amax, fabsf(bf16_to_f32(x.h[j])));
+      }
+      reinterpret_cast<uint4*>(row_s)[i] = x.u;
+      if (a.x_out) reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(t) * K)[i] = x.u;
+    }
+  } else {
+    const bf16* rr = a.in + static_cast<size_t>(t) * a.in_stride;
+    for (int i = tid; i < nvec; i += 256) {
+      Pack16 x;
+      x.u = reinterpret_cast<const uint4*>(rr)[i];
+      if (MODE == 1) {
+        Pack16 u;
+        u.u = reinterpret_cast<const uint4*>(rr + K)[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float gv = bf16_to_f32(x.h[j]), uv = bf16_to_f32(u.h[j]);
+          if (a.limit > 0.f) { gv = fminf(gv, a.limit); uv = fminf(fmaxf(uv, -a.limit), a.limit); }
+          const float sl = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-gv))));
+          x.h[j] = f32_to_bf16(sl * uv);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(bf16_to_f32(x.h[j])));
+      reinterpret_cast<uint4*>(row_s)[i] = x.u;
+      if (a.x_out) reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(t) * K)[i] = x.u;
+    }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  __syncthreads();
+  amax = block_reduce(amax, true);
   const float gs = amax > 0.f ? amax / (6.f * 256.f) : 1.f;
-  if (lane == 0) g[warp] = gs;
+  if (tid == 0) a.g[t] = gs;
   const float inv_g = 1.f / gs;
-  for (int gi = lane; gi < groups; gi += 32) {
-    Pack16 a, b;
-    a.u = reinterpret_cast<const uint4*>(row + gi * 16)[0];
-    b.u = reinterpret_cast<const uint4*>(row + gi * 16)[1];
+  const int groups = K / 16, stages = K / 256;
+  // B-operand rows of a token tile: term r of token m sits at row r * bn + m (terms stacked along the MMA N axis)
+  const int atoms = a.R * a.bn > 128 ? 2 : 1;
+  const int tile = t / a.bn, m = t % a.bn;
+  const size_t tiles = static_cast<size_t>(a.T_pad / a.bn);
+  for (int gi = tid; gi < groups; gi += 256) {
+    Pack16 lo, hi;
+    lo.u = reinterpret_cast<const uint4*>(row_s + gi * 16)[0];
+    hi.u = reinterpret_cast<const uint4*>(row_s + gi * 16)[1];
     float res[16];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      res[j] = bf16_to_f32(a.h[j]) * inv_g;
-      res[8 + j] = bf16_to_f32(b.h[j]) * inv_g;
+      res[j] = bf16_to_f32(lo.h[j]) * inv_g;
+      res[8 + j] = bf16_to_f32(hi.h[j]) * inv_g;
     }
-    for (int r = 0; r < R; ++r) {
+    const int st = gi >> 4, step = (gi >> 2) & 3, fi = gi & 3;
+    for (int r = 0; r < a.R; ++r) {
       float bm = 0.f;
 #pragma unroll
       for (int j = 0; j < 16; ++j) bm = fmaxf(bm, fabsf(res[j]));
       const uint8_t sb = f32_to_e4m3(bm * (1.f / 6.f));
       const float s = e4m3_to_f32(sb);
       const float inv_s = s > 0.f ? 1.f / s : 0.f;
-      uint32_t lo = 0, hi = 0;
+      uint32_t w0 = 0, w1 = 0;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const uint32_t c = f32_to_e2m1(res[j] * inv_s);
         res[j] -= e2m1_to_f32(c) * s;
-        if (j < 8) lo |= c << (4 * j); else hi |= c << (4 * (j - 8));
+        if (j < 8) w0 |= c << (4 * j); else w1 |= c << (4 * (j - 8));
       }
-      const size_t ro = static_cast<size_t>(r) * T_pad + warp;
-      *reinterpret_cast<uint2*>(q + ro * (K / 2) + gi * 8) = make_uint2(lo, hi);
-      sf[ro * groups + gi] = sb;
+      const size_t ro = static_cast<size_t>(tile) * a.R * a.bn + static_cast<size_t>(r) * a.bn + m;
+      *reinterpret_cast<uint2*>(a.q + ro * (K / 2) + gi * 8) = make_uint2(w0, w1);
+      const int brow = r * a.bn + m, h = brow >> 7, mm = brow & 127;
+      const size_t atom_idx = ((static_cast<size_t>(tile) * stages + st) * 4 + step) * atoms + h;
+      a.sf[atom_idx * kF4Atom + (mm & 31) * 16 + (mm >> 5) * 4 + fi] = sb;
     }
   }
 }
 
-template <int BN, int RMAX>
+template <int BN>
 struct Fp4Cfg {
   static constexpr int kAtomsB = BN > 128 ? 2 : 1;
   static constexpr size_t stage_bytes() {
-    return kF4StageA + static_cast<size_t>(RMAX) * BN * 128 + 4 * kF4Atom + static_cast<size_t>(RMAX) * 4 * kAtomsB * kF4Atom;
+    return kF4StageA + static_cast<size_t>(BN) * 128 + 4 * kF4Atom + static_cast<size_t>(4) * kAtomsB * kF4Atom;
   }
-  static constexpr int S = (200 * 1024) / stage_bytes() > 6 ? 6 : (200 * 1024) / stage_bytes();
-  static constexpr size_t smem() { return 1024 + S * stage_bytes() + (3 * S + 1) * 8 + 64; }
+  // small token tiles (decode): two CTAs per SM, each <= ~110 KB; large tiles: one CTA with a deep ring
+  static constexpr size_t kBudget = BN <= 96 ? 108 * 1024 : 200 * 1024;
+  static constexpr int S = kBudget / stage_bytes() > 6 ? 6 : static_cast<int>(kBudget / stage_bytes());
+  static constexpr size_t smem() { return 1024 + S * stage_bytes() + (2 * S + 1) * 8 + 64; }
 };
 
-template <int BN, int RMAX>
+template <int BN>
 static int launch_fp4(const CUtensorMap& tA, const CUtensorMap& tB, const Fp4Params& p, int splits, cudaStream_t st) {
-  using C = Fp4Cfg<BN, RMAX>;
+  using C = Fp4Cfg<BN>;
   static_assert(C::S >= 2, "not enough shared memory for two stages");
-  auto kern = gemm_fp4_kernel<BN, RMAX, C::S>;
+  auto kern = gemm_fp4_kernel<BN, C::S>;
   static bool attr = false;
   constexpr size_t smem = C::smem();
   static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
@@ -371,7 +426,8 @@ static int launch_fp4(const CUtensorMap& tA, const CUtensorMap& tB, const Fp4Par
     DGPP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     attr = true;
   }
-  dim3 grid(dgpp_ceil_div(p.N, kF4BM), dgpp_ceil_div(p.T, BN), splits);
+  const int bn_tok = BN / p.R;
+  dim3 grid(dgpp_ceil_div(p.N, kF4BM), dgpp_ceil_div(p.T, bn_tok), splits);
   kern<<<grid, kF4Threads, smem, st>>>(tA, tB, p);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
@@ -381,33 +437,59 @@ static int launch_fp4(const CUtensorMap& tA, const CUtensorMap& tB, const Fp4Par
 
 using namespace dgpp;
 
-// Quantise T rows of bf16 activations into R residual NVFP4 terms (see act_quant_nvfp4_kernel).
-DGPP_API int dgpp_act_quant_nvfp4(const void* x, int64_t x_stride, void* q, void* sf, void* g, int T, int T_pad,
-                                  int K, int R, cudaStream_t st) {
-  DGPP_REQUIRE(K % 16 == 0, "act_quant: K %d must be a multiple of 16", K);
+// Fused activation producer + NVFP4 quantiser (see fused_act_quant_kernel).  mode: 0 plain, 1 swiglu, 2 add+rmsnorm.
+// sf must be zero-initialised once (rows that are never written keep scale 0); its size is
+// R * (T_pad / bn) * (K / 256) * 4 * atoms * 512 bytes with atoms = (bn > 128 ? 2 : 1).
+DGPP_API int dgpp_act_quant_nvfp4(int mode, const void* in, int64_t in_stride, const void* delta, const void* w,
+                                  void* resid_out, void* x_out, void* q, void* sf, void* g, int T, int T_pad, int K,
+                                  int R, int bn, float eps, float limit, int one_plus_w, cudaStream_t st) {
+  DGPP_REQUIRE(K % 256 == 0, "act_quant: K %d must be a multiple of 256", K);
   DGPP_REQUIRE(R >= 1 && R <= 4, "act_quant: R %d outside 1..4", R);
+  DGPP_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "act_quant: bad token tile %d", bn);
+  DGPP_REQUIRE(T_pad % bn == 0 && T_pad >= T, "act_quant: T_pad %d must be a multiple of bn %d and >= T", T_pad, bn);
+  DGPP_REQUIRE(static_cast<size_t>(K) * 2 <= 96 * 1024, "act_quant: K %d too large", K);
   if (T == 0) return 0;
-  act_quant_nvfp4_kernel<<<dgpp_ceil_div(T * 32, 256), 256, 0, st>>>(
-      static_cast<const bf16*>(x), x_stride, static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf),
-      static_cast<float*>(g), T, T_pad, K, R);
+  QuantArgs a;
+  a.in = static_cast<const bf16*>(in);
+  a.in_stride = in_stride;
+  a.delta = static_cast<const bf16*>(delta);
+  a.w = static_cast<const bf16*>(w);
+  a.resid_out = static_cast<bf16*>(resid_out);
+  a.x_out = static_cast<bf16*>(x_out);
+  a.q = static_cast<uint8_t*>(q);
+  a.sf = static_cast<uint8_t*>(sf);
+  a.g = static_cast<float*>(g);
+  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.eps = eps; a.limit = limit; a.one_plus_w = one_plus_w;
+  const size_t smem = static_cast<size_t>(K) * 2;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(fused_act_quant_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    cudaFuncSetAttribute(fused_act_quant_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    cudaFuncSetAttribute(fused_act_quant_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    attr = true;
+  }
+  if (mode == 0) fused_act_quant_kernel<0><<<T, 256, smem, st>>>(a);
+  else if (mode == 1) fused_act_quant_kernel<1><<<T, 256, smem, st>>>(a);
+  else if (mode == 2) fused_act_quant_kernel<2><<<T, 256, smem, st>>>(a);
+  else { dgpp_set_error("act_quant: unknown mode %d", mode); return -1; }
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
-// out[T, N] = alpha * g[t] * sum_r Wq . Xq_r^T.   xq: [R, T_pad, K/2], xsf: [R, T_pad, K/16], g: [T].
+// out[T, N] = alpha * g[t] * sum_r Wq . Xq_r^T.   xq: [R, T_pad, K/2]; xsf / wsf_tiled: tiled scale factors; g: [T].
 DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* g, int R, int T_pad, const void* wq,
-                           const void* wsf, float alpha, void* out, void* out32, const void* resid, int ldc, int T,
-                           int N, int K, int splits, void* ws, void* counters, cudaStream_t st) {
+                           const void* wsf_tiled, float alpha, void* out, void* out32, const void* resid, int ldc,
+                           int T, int N, int K, int splits, void* ws, void* counters, cudaStream_t st) {
   DGPP_REQUIRE(K % 256 == 0, "gemm_fp4: K %d must be a multiple of 256", K);
   DGPP_REQUIRE(R >= 1 && R <= 4, "gemm_fp4: R %d outside 1..4", R);
   DGPP_REQUIRE(splits >= 1, "gemm_fp4: splits must be >= 1");
   DGPP_REQUIRE(splits == 1 || (ws && counters), "gemm_fp4: split-K needs workspace and counters");
   DGPP_REQUIRE(out || out32, "gemm_fp4: no output");
-  DGPP_REQUIRE(T_pad >= T, "gemm_fp4: T_pad < T");
+  DGPP_REQUIRE(T_pad >= T && T_pad % bn == 0, "gemm_fp4: T_pad %d must cover T and be a multiple of bn %d", T_pad, bn);
   Fp4Params p;
   p.alpha = alpha;
   p.g = static_cast<const float*>(g);
-  p.sfa = static_cast<const uint8_t*>(wsf);
+  p.sfa = static_cast<const uint8_t*>(wsf_tiled);
   p.sfb = static_cast<const uint8_t*>(xsf);
   p.out = static_cast<bf16*>(out);
   p.out32 = static_cast<float*>(out32);
@@ -423,20 +505,20 @@ DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* 
   CUtensorMap tA, tB;
   if (make_tmap_2d(&tA, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, K / 2, 128, kF4BM, CU_TENSOR_MAP_SWIZZLE_128B))
     return -1;
+  const int bnn = bn * R;  // MMA N: the R terms of a token tile are stacked
   if (make_tmap_2d(&tB, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, static_cast<uint64_t>(R) * T_pad, K / 2, 128,
-                   bn, CU_TENSOR_MAP_SWIZZLE_128B))
+                   bnn, CU_TENSOR_MAP_SWIZZLE_128B))
     return -1;
-  if (R > 1) {
-    DGPP_REQUIRE(bn <= 64, "gemm_fp4: residual terms need bn <= 64 (bn=%d)", bn);
-    if (bn == 16) return launch_fp4<16, 4>(tA, tB, p, splits, st);
-    if (bn == 32) return launch_fp4<32, 4>(tA, tB, p, splits, st);
-    if (bn == 64) return launch_fp4<64, 4>(tA, tB, p, splits, st);
-  } else {
-    if (bn == 16) return launch_fp4<16, 1>(tA, tB, p, splits, st);
-    if (bn == 32) return launch_fp4<32, 1>(tA, tB, p, splits, st);
-    if (bn == 64) return launch_fp4<64, 1>(tA, tB, p, splits, st);
-    if (bn == 128) return launch_fp4<128, 1>(tA, tB, p, splits, st);
-    if (bn == 256) return launch_fp4<256, 1>(tA, tB, p, splits, st);
+  DGPP_REQUIRE(bnn <= 256 && bnn % 16 == 0, "gemm_fp4: token tile %d x %d terms does not fit one MMA", bn, R);
+  switch (bnn) {
+    case 16: return launch_fp4<16>(tA, tB, p, splits, st);
+    case 32: return launch_fp4<32>(tA, tB, p, splits, st);
+    case 48: return launch_fp4<48>(tA, tB, p, splits, st);
+    case 64: return launch_fp4<64>(tA, tB, p, splits, st);
+    case 96: return launch_fp4<96>(tA, tB, p, splits, st);
+    case 128: return launch_fp4<128>(tA, tB, p, splits, st);
+    case 192: return launch_fp4<192>(tA, tB, p, splits, st);
+    case 256: return launch_fp4<256>(tA, tB, p, splits, st);
   }
   dgpp_set_error("gemm_fp4: unsupported bn %d", bn);
   return -1;

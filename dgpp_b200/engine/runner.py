@@ -22,8 +22,15 @@ BF = torch.bfloat16
 
 
 class DenseRunner:
-    def __init__(self, model: DenseModel, kv: PagedKV, max_rows: int, reducer=None, decode_splits: int = 8):
+    def __init__(self, model: DenseModel, kv: PagedKV, max_rows: int, reducer=None, decode_splits: int = 8,
+                 decode_fp4: bool = True, act_terms: int = 3, attn_tc: bool = True):
         self.m, self.kv, self.max_rows, self.reducer = model, kv, max_rows, reducer
+        # decode rows (<= 64) run the linears on the block-scaled FP4 tensor-core path with the activations
+        # expanded into `act_terms` residual NVFP4 terms; attention reads the FP8 cache through tcgen05
+        self.decode_fp4 = decode_fp4 and model.cfg.weight_fmt == "nvfp4"
+        self.act_terms = act_terms
+        self.attn_tc = attn_tc and model.cfg.kv_fp8 and model.cfg.head_dim == 128 and \
+            (model.cfg.q_heads // model.cfg.kv_heads) in (1, 2, 4, 5, 8)
         c = model.cfg
         dev = model.embed.device
         d = c.head_dim
@@ -45,6 +52,40 @@ class DenseRunner:
         self.att_ml = torch.empty(R * self.hq * decode_splits * 2, dtype=torch.float32, device=dev)
         self.att_acc = torch.empty(min(R, 256) * self.hq * decode_splits * d, dtype=torch.float32, device=dev)
         self.ws = ops.default_workspace(dev)
+        self.qa = {}
+        self.fp4_rows = min(64, max_rows)
+        if self.decode_fp4:
+            bn = min(64, ops.pick_bn(self.fp4_rows))
+            for k in {H, self.hq * d, I}:
+                self.qa[k] = ops.QuantAct(bn, k, act_terms, bn, dev)
+
+    def linear(self, x, w, out, fp4: bool):
+        if fp4 and w.fmt == "nvfp4" and w.k % 256 == 0:
+            xa = ops.act_quant_nvfp4(x, self.act_terms, out=self.qa[w.k])
+            return ops.gemm_fp4(xa, w, out=out)
+        return ops.linear(x, w, out=out)
+
+    def _layer_fp4(self, L, cache, x, delta, have_delta, qkv, attn, gu, positions, row_req, rows, splits):
+        """One decoder layer on the block-scaled FP4 path: every linear consumes NVFP4 residual terms written by
+        the kernel that produces its input (add + RMSNorm, attention output, SwiGLU)."""
+        m, c = self.m, self.m.cfg
+        H = c.hidden
+        xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta if have_delta else None,
+                                 norm_w=L.in_norm, eps=c.eps)
+        ops.gemm_fp4(xa, L.qkv, out=qkv)
+        ops.rope_kv_write(qkv, positions, row_req, self.kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
+                          rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm, eps=c.eps)
+        self.attention(qkv, cache, row_req, positions, rows, splits, attn)
+        xa = ops.act_quant_nvfp4(attn, out=self.qa[self.hq * self.d], mode="plain")
+        ops.gemm_fp4(xa, L.o, out=delta)
+        if self.reducer is not None:
+            self.reducer.all_reduce(delta)
+        xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta, norm_w=L.post_norm, eps=c.eps)
+        ops.gemm_fp4(xa, L.gate_up, out=gu)
+        xa = ops.act_quant_nvfp4(gu, out=self.qa[gu.shape[1] // 2], mode="swiglu")
+        ops.gemm_fp4(xa, L.down, out=delta)
+        if self.reducer is not None:
+            self.reducer.all_reduce(delta)
 
     # ------------------------------------------------------------------
     def forward(self, rows: int, tokens, positions, row_req, logits_rows: Optional[slice] = None,
@@ -58,21 +99,27 @@ class DenseRunner:
         ops.embed_gather(tokens, m.embed, out=x)
         have_delta = False
         splits = self.decode_splits if (decode and rows <= 256) else 1
+        fp4 = self.decode_fp4 and decode and rows <= self.fp4_rows and all(
+            w.k % 256 == 0 for w in (m.layers[0].qkv, m.layers[0].o, m.layers[0].down))
         for li, L in enumerate(m.layers):
+            if fp4:
+                self._layer_fp4(L, kv.layers[li], x, delta, have_delta, qkv, attn, gu, positions, row_req, rows, splits)
+                have_delta = True
+                continue
             ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have_delta else None, out=xn)
-            ops.linear(xn, L.qkv, out=qkv)
+            self.linear(xn, L.qkv, qkv, fp4)
             cache = kv.layers[li]
             ops.rope_kv_write(qkv, positions, row_req, kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
                               rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm,
                               eps=c.eps)
             self.attention(qkv, cache, row_req, positions, rows, splits, attn)
-            ops.linear(attn, L.o, out=delta)
+            self.linear(attn, L.o, delta, fp4)
             if self.reducer is not None:
                 self.reducer.all_reduce(delta)
             ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
-            ops.linear(xn, L.gate_up, out=gu)
+            self.linear(xn, L.gate_up, gu, fp4)
             ops.swiglu(gu, out=act)
-            ops.linear(act, L.down, out=delta)
+            self.linear(act, L.down, delta, fp4)
             if self.reducer is not None:
                 self.reducer.all_reduce(delta)
             have_delta = True
@@ -93,7 +140,11 @@ class DenseRunner:
 
     def attention(self, qkv, cache, row_req, positions, rows, splits, out):
         """Attention of `rows` query rows against the paged cache (their own K/V already appended)."""
-        if splits > 1:
+        if self.attn_tc:
+            ops.attn_decode_tc(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, self.hq, self.hkv,
+                               self.d, self.scale, splits=splits,
+                               scratch=(self.att_ml, self.att_acc) if splits > 1 else None, out=out)
+        elif splits > 1:
             ops.attn_decode(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, self.hq, self.hkv,
                             self.d, self.scale, splits=splits, scratch=(self.att_ml, self.att_acc), out=out)
         else:

@@ -155,56 +155,69 @@ def gemm_tc(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
 
 
 class QuantAct:
-    """Activations quantised to R residual NVFP4 terms: x ~= g[t] * sum_r dequant(q[r], sf[r])."""
+    """Activations quantised to R residual NVFP4 terms: x ~= g[t] * sum_r dequant(term r).
+    Rows of `q` are ordered [token tile][term][token in tile] (the B operand of one MMA is a token tile with its
+    terms stacked); `sf` holds the e4m3 block scales in tcgen05.cp atom order per token tile; g: [rows_pad].
+    With more than one term the whole batch must fit one token tile (decode)."""
 
-    def __init__(self, q, sf, g, rows, k, terms):
-        self.q, self.sf, self.g, self.rows, self.k, self.terms = q, sf, g, rows, k, terms
-
-    @property
-    def rows_pad(self) -> int:
-        return self.q.shape[1]
+    def __init__(self, rows_pad: int, k: int, terms: int, bn: int, device):
+        assert rows_pad % bn == 0 and terms * bn <= 256
+        assert terms == 1 or rows_pad == bn, "residual terms are stacked inside a single token tile"
+        atoms = 2 if terms * bn > 128 else 1
+        self.q = torch.zeros(rows_pad * terms, k // 2, dtype=torch.uint8, device=device)
+        self.sf = torch.zeros((rows_pad // bn) * (k // 256) * 4 * atoms * 512, dtype=torch.uint8, device=device)
+        self.g = torch.ones(rows_pad, dtype=torch.float32, device=device)
+        self.rows, self.k, self.terms, self.bn, self.rows_pad = 0, k, terms, bn, rows_pad
 
     def dequant(self) -> torch.Tensor:
-        from ..quant.formats import e2m1_decode, unpack_nibbles
-        tot = torch.zeros(self.rows, self.k, dtype=torch.float32, device=self.q.device)
-        for r in range(self.terms):
-            v = e2m1_decode(unpack_nibbles(self.q[r, :self.rows])).view(self.rows, self.k // 16, 16)
-            s = self.sf[r, :self.rows].view(torch.float8_e4m3fn).float().unsqueeze(-1)
-            tot += (v * s).view(self.rows, self.k)
-        return tot * self.g[:self.rows].unsqueeze(-1)
+        from ..quant.formats import e2m1_decode, unpack_nibbles, untile_scales
+        tiles, R, bn, k = self.rows_pad // self.bn, self.terms, self.bn, self.k
+        v = e2m1_decode(unpack_nibbles(self.q)).view(tiles, R, bn, k // 16, 16)
+        sf = untile_scales(self.sf, tiles * R * bn, k // 16, R * bn).view(tiles, R, bn, k // 16)
+        x = (v * sf.view(torch.float8_e4m3fn).float().unsqueeze(-1)).sum(1).reshape(tiles * bn, k)
+        return x[:self.rows] * self.g[:self.rows].unsqueeze(-1)
 
 
-def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = None) -> QuantAct:
+def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = None, bn: Optional[int] = None,
+                    mode: str = "plain", delta=None, norm_w=None, resid_out=None, x_out=None, eps: float = 1e-6,
+                    limit: float = 0.0, one_plus_w: bool = False) -> QuantAct:
+    """Quantise rows to residual NVFP4 terms, optionally fused with the producing operator:
+    mode "plain": x [T, K];  "swiglu": x = [gate | up] [T, 2K];  "rmsnorm": x = residual [T, K] (+ delta), norm_w."""
     _chk(x, torch.bfloat16, "x")
-    rows, k = x.shape
+    rows = x.shape[0]
+    k = x.shape[1] // 2 if mode == "swiglu" else x.shape[1]
     if out is None:
-        rp = max(16, (rows + 15) // 16 * 16)
-        out = QuantAct(torch.zeros(terms, rp, k // 2, dtype=torch.uint8, device=x.device),
-                       torch.zeros(terms, rp, k // 16, dtype=torch.uint8, device=x.device),
-                       torch.ones(rp, dtype=torch.float32, device=x.device), rows, k, terms)
+        bn = bn or min(pick_bn(rows), 64 if terms > 1 else 256)
+        out = QuantAct((rows + bn - 1) // bn * bn, k, terms, bn, x.device)
     out.rows = rows
-    call("dgpp_act_quant_nvfp4", ptr(x), x.stride(0), ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k,
-         out.terms, stream_ptr())
+    assert rows <= out.rows_pad and out.k == k
+    m = {"plain": 0, "swiglu": 1, "rmsnorm": 2}[mode]
+    if m == 2 and delta is not None and resid_out is None:
+        resid_out = x
+    cl = next((c for c in (8, 4, 2, 1) if k % c == 0 and (k // c) % 16 == 0 and (k // c) * 2 <= 48 * 1024), 0)
+    if cl:
+        call("dgpp_act_quant_nvfp4_cluster", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out),
+             ptr(x_out), ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, cl,
+             float(eps), float(limit), int(one_plus_w), stream_ptr())
+    else:
+        call("dgpp_act_quant_nvfp4", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out), ptr(x_out),
+             ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, float(eps),
+             float(limit), int(one_plus_w), stream_ptr())
     return out
 
 
 def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
-             out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, bn: Optional[int] = None,
+             out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
              splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None) -> torch.Tensor:
-    """Block-scaled NVFP4 tensor-core linear on pre-quantised activations."""
+    """Block-scaled NVFP4 tensor-core linear on pre-quantised activations (token tile = xa.bn)."""
     assert w.fmt == "nvfp4" and xa.k == w.k
-    rows = xa.rows
+    rows, bn = xa.rows, xa.bn
     dev = xa.q.device
     if out is None and out32 is None:
         out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=dev)
     ldc = (out if out is not None else out32).stride(0)
-    if bn is None:
-        bn = pick_bn(rows)
-        if xa.terms > 1:
-            bn = min(bn, 64)
     if splits is None:
-        tiles = math.ceil(w.n / 128) * math.ceil(rows / bn)
-        splits = 1 if tiles >= 148 else max(1, min(148 // tiles, (w.k // 256) // 2))
+        splits = pick_splits_fp4(rows, w.n, w.k, bn)
     wsp = cnt = None
     if splits > 1:
         ws = ws or default_workspace(dev)
@@ -212,10 +225,19 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
             splits = 1
         else:
             wsp, cnt = ws.partials, ws.counters
-    call("dgpp_gemm_fp4", bn, ptr(xa.q), ptr(xa.sf), ptr(xa.g), xa.terms, xa.rows_pad, ptr(w.payload), ptr(w.scale),
-         float(w.alpha), ptr(out), ptr(out32), ptr(resid), ldc, rows, w.n, w.k, splits, ptr(wsp), ptr(cnt),
-         stream_ptr())
+    call("dgpp_gemm_fp4", bn, ptr(xa.q), ptr(xa.sf), ptr(xa.g), xa.terms, xa.rows_pad, ptr(w.payload),
+         ptr(w.tiled_scales()), float(w.alpha), ptr(out), ptr(out32), ptr(resid), ldc, rows, w.n, w.k, splits,
+         ptr(wsp), ptr(cnt), stream_ptr())
     return out if out is not None else out32
+
+
+def pick_splits_fp4(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:
+    """Split K so that a weight-streaming launch covers the SMs (two CTAs fit per SM for decode tiles)."""
+    tiles = math.ceil(n / 128) * math.ceil(rows / bn)
+    if tiles >= sms:
+        return 1
+    stages = k // 256
+    return max(1, min(round(1.5 * sms / tiles), stages // 2))
 
 
 def linear(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,

@@ -75,10 +75,19 @@ class QuantLinear:
     payload: torch.Tensor                 # uint8 / bf16, see module docstring
     scale: Optional[torch.Tensor] = None  # block scales (uint8 codes, fp32 or bf16 depending on fmt)
     alpha: float = 1.0                    # per-tensor fp32 multiplier (nvfp4 global scale)
+    scale_tiled: Optional[torch.Tensor] = None  # nvfp4: the same scale bytes in tcgen05.cp atom order (see tile_scales)
 
     def to(self, device) -> "QuantLinear":
         return QuantLinear(self.fmt, self.n, self.k, self.payload.to(device),
-                           None if self.scale is None else self.scale.to(device), self.alpha)
+                           None if self.scale is None else self.scale.to(device), self.alpha,
+                           None if self.scale_tiled is None else self.scale_tiled.to(device))
+
+    def tiled_scales(self) -> torch.Tensor:
+        """Scale bytes permuted for the block-scaled tensor-core kernel (built once, cached)."""
+        if self.scale_tiled is None:
+            assert self.fmt == "nvfp4"
+            self.scale_tiled = tile_scales(self.scale.view(self.n, self.k // 16))
+        return self.scale_tiled
 
     @property
     def nbytes(self) -> int:
@@ -119,6 +128,30 @@ class QuantLinear:
         if self.fmt == "nvfp4":
             return (self.dequant() / self.alpha).to(torch.bfloat16)
         return self.dequant().to(torch.bfloat16)
+
+
+def tile_scales(sf: torch.Tensor) -> torch.Tensor:
+    """[rows, K/16] e4m3 bytes -> flat bytes ordered [row_tile][stage][step][m % 32][m / 32][factor], i.e. one
+    512-byte atom per (128-row tile, K=64 step) with factor i of row m at byte (m % 32) * 16 + (m / 32) * 4 + i,
+    four atoms (one 256-K pipeline stage) contiguous.  Rows are padded to a multiple of 128 with zeros."""
+    rows, groups = sf.shape
+    assert groups % 16 == 0, "K must be a multiple of 256"
+    tiles = (rows + 127) // 128
+    pad = tiles * 128 - rows
+    if pad:
+        sf = torch.cat([sf, torch.zeros(pad, groups, dtype=sf.dtype, device=sf.device)])
+    v = sf.view(tiles, 4, 32, groups // 16, 4, 4)          # [tile][m/32][m%32][stage][step][factor]
+    return v.permute(0, 3, 4, 2, 1, 5).contiguous().view(-1)
+
+
+def untile_scales(flat: torch.Tensor, rows: int, groups: int, row_tile: int = 128) -> torch.Tensor:
+    """Inverse of the atom order for token tiles of `row_tile` rows (activation scales): returns [rows, K/16]."""
+    atoms = 2 if row_tile > 128 else 1
+    tiles = flat.numel() // ((groups // 16) * 4 * atoms * 512)
+    v = flat.view(tiles, groups // 16, 4, atoms, 32, 4, 4)  # [tile][stage][step][atom][m%32][m/32][factor]
+    v = v.permute(0, 3, 5, 4, 1, 2, 6).contiguous()         # [tile][atom][m/32][m%32][stage][step][factor]
+    full = v.view(tiles, atoms * 128, groups)
+    return full[:, :row_tile].reshape(tiles * row_tile, groups)[:rows]
 
 
 def quantize(w: torch.Tensor, fmt: str) -> QuantLinear:
