@@ -68,6 +68,30 @@ __host__ __device__ __forceinline__ uint32_t f32_to_e2m1(float v) {
   return s | c;
 }
 
+// Eight floats -> eight e2m1 codes in one word (element 0 in the lowest nibble), round-to-nearest-even on the
+// e2m1 grid, saturating at +-6: the hardware conversion (two values per instruction).
+__device__ __forceinline__ uint32_t f32x8_to_e2m1x8(const float* v) {
+  uint32_t out;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}\n"
+      : "=r"(out)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return out;
+}
+// Subtract the decoded codes (times s) from the eight values they were produced from.
+__device__ __forceinline__ void e2m1x8_residual(uint32_t codes, float s, float* v) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 d = __half22float2(e2m1x2_to_h2(static_cast<uint8_t>((codes >> (8 * i)) & 0xffu)));
+    v[2 * i] -= d.x * s;
+    v[2 * i + 1] -= d.y * s;
+  }
+}
+
 union Pack16 {
   uint4 u;
   bf16 h[8];

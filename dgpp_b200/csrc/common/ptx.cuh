@@ -256,7 +256,13 @@ __device__ __forceinline__ uint4 ld_v4_global_volatile(const void* p) {
 }
 
 // Programmatic dependent launch: let the next kernel's prologue start / wait for the previous grid.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// pdl_wait(): block until the preceding grid has completed and its memory is visible, THEN allow the next grid
+// in the stream / graph to start launching.  Triggering only after the wait keeps the overlap to one kernel deep:
+// a grid's prologue can run under its immediate predecessor only, never under an older, still running grid.
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }

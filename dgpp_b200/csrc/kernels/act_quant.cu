@@ -162,13 +162,12 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
       const uint8_t sb = f32_to_e4m3(bm * (1.f / 6.f));
       const float s = e4m3_to_f32(sb);
       const float inv_s = s > 0.f ? 1.f / s : 0.f;
-      uint32_t w0 = 0, w1 = 0;
+      float sc[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const uint32_t cde = f32_to_e2m1(res[j] * inv_s);
-        res[j] -= e2m1_to_f32(cde) * s;
-        if (j < 8) w0 |= cde << (4 * j); else w1 |= cde << (4 * (j - 8));
-      }
+      for (int j = 0; j < 16; ++j) sc[j] = res[j] * inv_s;
+      const uint32_t w0 = f32x8_to_e2m1x8(sc), w1 = f32x8_to_e2m1x8(sc + 8);
+      e2m1x8_residual(w0, s, res);
+      e2m1x8_residual(w1, s, res + 8);
       const size_t ro = static_cast<size_t>(tile) * a.R * a.bn + static_cast<size_t>(r) * a.bn + m;
       *reinterpret_cast<uint2*>(a.q + ro * (K / 2) + gi * 8) = make_uint2(w0, w1);
       const int brow = r * a.bn + m, h = brow >> 7, mm = brow & 127;

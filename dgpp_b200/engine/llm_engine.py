@@ -22,13 +22,15 @@ import torch
 from ..models.dense import DenseModel
 from ..ops import _lib
 from ..ops._lib import call, ptr, stream_ptr
+from .graph import NativeGraph
 from .kv_cache import PagedKV
 from .runner import DenseRunner
 
 
 class LLMEngine:
     def __init__(self, model: DenseModel, max_batch: int = 8, max_seq_len: int = 4096, prefill_chunk: int = 2048,
-                 kv_blocks: Optional[int] = None, reducer=None, use_graphs: bool = True, ring_steps: int = 1024):
+                 kv_blocks: Optional[int] = None, reducer=None, use_graphs: bool = True, ring_steps: int = 1024,
+                 decode_pdl: bool = True, act_terms: int = 3):
         c = model.cfg
         self.model, self.max_batch, self.max_seq_len = model, max_batch, max_seq_len
         self.prefill_chunk = prefill_chunk
@@ -40,8 +42,10 @@ class LLMEngine:
         self.kv = PagedKV(c.layers, model.hkv_local, c.head_dim, kv_blocks, max_batch, max_blocks_per_req, page,
                           c.kv_fp8, self.dev)
         rows = max(prefill_chunk, max_batch)
-        splits = max(1, min(16, 148 // max(1, model.hkv_local * max_batch)))
-        self.runner = DenseRunner(model, self.kv, rows, reducer=reducer, decode_splits=splits)
+        splits = max(1, min(16, round(296 / max(1, model.hkv_local * max_batch))))
+        self.decode_pdl = decode_pdl
+        self.runner = DenseRunner(model, self.kv, rows, reducer=reducer, decode_splits=splits, decode_rows=max_batch,
+                                  act_terms=act_terms)
         self.use_graphs = use_graphs
         self.ring_steps = ring_steps
         i32 = dict(dtype=torch.int32, device=self.dev)
@@ -109,9 +113,7 @@ class LLMEngine:
             torch.cuda.synchronize()
             self.d_tokens.copy_(saved[0]); self.d_positions.copy_(saved[1])
             self.d_step.copy_(saved[2]); self.d_ring.copy_(saved[3])
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._decode_body(b)
+            g = NativeGraph(lambda: self._decode_body(b), pdl=self.decode_pdl)
             self.graphs[b] = g
         return g
 

@@ -23,7 +23,8 @@ BF = torch.bfloat16
 
 class DenseRunner:
     def __init__(self, model: DenseModel, kv: PagedKV, max_rows: int, reducer=None, decode_splits: int = 8,
-                 decode_fp4: bool = True, act_terms: int = 3, attn_tc: bool = True):
+                 decode_fp4: bool = True, act_terms: int = 3, attn_tc: bool = True,
+                 decode_rows: Optional[int] = None):
         self.m, self.kv, self.max_rows, self.reducer = model, kv, max_rows, reducer
         # decode rows (<= 64) run the linears on the block-scaled FP4 tensor-core path with the activations
         # expanded into `act_terms` residual NVFP4 terms; attention reads the FP8 cache through tcgen05
@@ -53,7 +54,7 @@ class DenseRunner:
         self.att_acc = torch.empty(min(R, 256) * self.hq * decode_splits * d, dtype=torch.float32, device=dev)
         self.ws = ops.default_workspace(dev)
         self.qa = {}
-        self.fp4_rows = min(64, max_rows)
+        self.fp4_rows = min(64, decode_rows or max_rows)
         if self.decode_fp4:
             bn = min(64, ops.pick_bn(self.fp4_rows))
             for k in {H, self.hq * d, I}:

@@ -232,12 +232,12 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
 
 
 def pick_splits_fp4(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:
-    """Split K so that a weight-streaming launch covers the SMs (two CTAs fit per SM for decode tiles)."""
+    """Split K only for long-K, few-tile problems (the deterministic fold costs a few microseconds)."""
     tiles = math.ceil(n / 128) * math.ceil(rows / bn)
-    if tiles >= sms:
-        return 1
     stages = k // 256
-    return max(1, min(round(1.5 * sms / tiles), stages // 2))
+    if tiles >= sms // 2 + 1 or stages <= 24:
+        return 1 if (rows > 1 or tiles >= sms // 2 + 1) else max(1, min(3, stages // 4))
+    return max(1, min(math.ceil(sms / tiles), stages // 8))
 
 
 def linear(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
