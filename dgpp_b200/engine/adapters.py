@@ -1,0 +1,231 @@
+"""Scheduler-facing engines: implementations of the native ``SchedulerEngine`` contract.
+
+* ``ReferenceEngine`` -- runs ``DenseModel.forward_reference`` (pure PyTorch, any device, optional gloo / NCCL
+  tensor parallelism) over a block-paged KV store, so the scheduler, the prefix cache (block sharing by
+  reference count) and multi-rank agreement can be exercised without a GPU.
+* ``KernelEngine``    -- the sm_100a path: ``LLMEngine`` prefill chunks and CUDA-graph decode steps.
+
+Both keep KV in blocks of ``block_tokens`` positions handed out by the native ``PagedBlockTable``; attaching a
+cached prefix only bumps reference counts.
+(contract: csrc/rt/scheduler.h ``SchedulerEngine``; reference counterpart src/engine/eager_engine.hpp:49-999,
+ src/engine/graph_engine.hpp:233.)
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..models.dense import DenseModel
+from ..runtime import rt
+
+
+class ReferenceEngine(rt.SchedulerEngine):
+    def __init__(self, model: DenseModel, slots: int = 4, num_blocks: int = 256, block_tokens: int = 16,
+                 max_context: int = 1024, all_reduce=None):
+        super().__init__()
+        self.m, self.slots_n, self.bt, self.maxctx = model, slots, block_tokens, max_context
+        self.table = rt.PagedBlockTable(num_blocks)
+        c = model.cfg
+        dev = model.embed.device
+        shape = (c.layers, num_blocks, block_tokens, model.hkv_local, c.head_dim)
+        self.k = torch.zeros(shape, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(shape, dtype=torch.float32, device=dev)
+        self.blocks: List[List[int]] = [[] for _ in range(slots)]
+        self.filled = [0] * slots
+        self.pending: List[Optional[int]] = [None] * slots
+        self.all_reduce = all_reduce
+
+    # ---- geometry
+    def max_concurrent(self):
+        return self.slots_n
+
+    def block_tokens(self):
+        return self.bt
+
+    def total_blocks(self):
+        return self.table.num_blocks()
+
+    def free_blocks(self):
+        return self.table.free_count()
+
+    def max_context(self):
+        return self.maxctx
+
+    # ---- blocks
+    def reserve(self, slot, tokens):
+        need = (tokens + self.bt - 1) // self.bt
+        if need - len(self.blocks[slot]) > self.table.free_count():
+            return False
+        while len(self.blocks[slot]) < need:
+            self.blocks[slot].append(self.table.alloc())
+        return True
+
+    def attach_prefix(self, slot, blocks):
+        assert not self.blocks[slot]
+        for b in blocks:
+            self.table.retain(b)
+            self.blocks[slot].append(b)
+        self.filled[slot] = len(blocks) * self.bt
+
+    def slot_blocks(self, slot):
+        return list(self.blocks[slot])
+
+    def retain_block(self, b):
+        self.table.retain(b)
+
+    def release_block(self, b):
+        self.table.release(b)
+
+    def block_refcount(self, b):
+        return self.table.refcount(b)
+
+    def close(self, slot):
+        for b in self.blocks[slot]:
+            self.table.release(b)
+        self.blocks[slot] = []
+        self.filled[slot] = 0
+        self.pending[slot] = None
+
+    # ---- compute
+    def _run(self, slot: int, tokens: List[int]) -> int:
+        c = self.m.cfg
+        n0 = self.filled[slot]
+        idx = torch.tensor(self.blocks[slot], dtype=torch.long, device=self.k.device)
+        kv = []
+        for li in range(c.layers):
+            if n0:
+                k = self.k[li, idx].reshape(-1, self.m.hkv_local, c.head_dim)[:n0]
+                v = self.v[li, idx].reshape(-1, self.m.hkv_local, c.head_dim)[:n0]
+                kv.append((k, v))
+            else:
+                kv.append(None)
+        logits, kv = self.m.forward_reference(torch.tensor(tokens, device=self.k.device), start_pos=n0, kv=kv,
+                                              all_reduce=self.all_reduce)
+        n1 = n0 + len(tokens)
+        pos = torch.arange(n0, n1, device=self.k.device)
+        blk = idx[pos // self.bt]
+        off = pos % self.bt
+        for li in range(c.layers):
+            self.k[li, blk, off] = kv[li][0][n0:n1]
+            self.v[li, blk, off] = kv[li][1][n0:n1]
+        self.filled[slot] = n1
+        row = logits[-1].float()
+        if self.all_reduce is not None and self.m.tp_size > 1:
+            return self._sharded_pick(row)
+        return int(torch.argmax(row))  # first maximal index = lowest id
+
+    def _sharded_pick(self, row: torch.Tensor) -> int:
+        import torch.distributed as dist
+
+        v, i = torch.max(row, 0)
+        vl = self.m.cfg.vocab // self.m.tp_size
+        mine = torch.tensor([float(v), float(int(i) + self.m.tp_rank * vl)], dtype=torch.float64)
+        allv = [torch.zeros_like(mine) for _ in range(self.m.tp_size)]
+        dist.all_gather(allv, mine)
+        best = 0
+        for r in range(1, self.m.tp_size):
+            if allv[r][0] > allv[best][0]:
+                best = r
+        return int(allv[best][1])
+
+    def prefill(self, slot, tokens, pos, last):
+        assert pos == self.filled[slot], (pos, self.filled[slot])
+        tok = self._run(slot, list(tokens))
+        if last:
+            self.pending[slot] = tok
+            return tok
+        return -1
+
+    def step_batch(self, slots):
+        out = []
+        for s in slots:
+            tok = self._run(s, [self.pending[s]])
+            self.pending[s] = tok
+            out.append([tok])
+        return out
+
+
+class KernelEngine(rt.SchedulerEngine):
+    """The CUDA engine behind the scheduler: chunked prefill and graph-replayed decode for arbitrary slot sets."""
+
+    def __init__(self, engine):
+        super().__init__()
+        self.e = engine
+        self.kv = engine.kv
+        self.pending = [None] * engine.max_batch
+        self.filled = [0] * engine.max_batch
+        b = engine.max_batch
+        self.h_tok = torch.zeros(b, dtype=torch.int32).pin_memory()
+        self.h_pos = torch.zeros(b, dtype=torch.int32).pin_memory()
+        self.h_req = torch.zeros(b, dtype=torch.int32).pin_memory()
+        self.h_out = torch.zeros(b, dtype=torch.int32).pin_memory()
+
+    def max_concurrent(self):
+        return self.e.max_batch
+
+    def block_tokens(self):
+        return self.kv.page
+
+    def total_blocks(self):
+        return self.kv.num_blocks
+
+    def free_blocks(self):
+        return self.kv.free_blocks()
+
+    def max_context(self):
+        return self.e.max_seq_len
+
+    def reserve(self, slot, tokens):
+        return self.kv.reserve(slot, tokens)
+
+    def attach_prefix(self, slot, blocks):
+        self.kv.attach(slot, list(blocks))
+        self.filled[slot] = len(blocks) * self.kv.page
+
+    def slot_blocks(self, slot):
+        return list(self.kv.req_blocks[slot])
+
+    def retain_block(self, b):
+        self.kv.alloc.retain(b)
+
+    def release_block(self, b):
+        self.kv.alloc.release(b)
+
+    def block_refcount(self, b):
+        return self.kv.alloc.refcount(b)
+
+    def close(self, slot):
+        self.kv.release(slot)
+        self.filled[slot] = 0
+        self.pending[slot] = None
+
+    def prefill(self, slot, tokens, pos, last):
+        first = self.e.prefill(slot, list(tokens), start_pos=pos)
+        self.filled[slot] = pos + len(tokens)
+        if last:
+            tok = int(first.item())
+            self.pending[slot] = tok
+            return tok
+        return -1
+
+    def step_batch(self, slots):
+        b = len(slots)
+        e = self.e
+        for i, s in enumerate(slots):
+            self.h_tok[i] = self.pending[s]
+            self.h_pos[i] = self.filled[s]
+            self.h_req[i] = s
+        e.d_tokens[:b].copy_(self.h_tok[:b], non_blocking=True)
+        e.d_positions[:b].copy_(self.h_pos[:b], non_blocking=True)
+        e.d_row_req[:b].copy_(self.h_req[:b], non_blocking=True)
+        e.decode_step(b)
+        self.h_out[:b].copy_(e.d_tokens[:b], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        out = []
+        for i, s in enumerate(slots):
+            tok = int(self.h_out[i])
+            self.filled[s] += 1
+            self.pending[s] = tok
+            out.append([tok])
+        return out

@@ -49,6 +49,14 @@ class DenseConfig:
         return DenseConfig(**kw)
 
     @staticmethod
+    def plumbing_fp32(**kw) -> "DenseConfig":
+        """The CPU-plumbing model: 2 layers, hidden 256, 4 q / 2 kv heads of 64, SwiGLU 688, RoPE 1e4, fp32."""
+        base = dict(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=64, ffn=688, vocab=4096, rope_theta=1e4,
+                    weight_fmt="fp32", head_fmt="fp32", kv_fp8=False, page=16, name="plumbing-fp32")
+        base.update(kw)
+        return DenseConfig(**base)
+
+    @staticmethod
     def tiny(**kw) -> "DenseConfig":
         base = dict(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=64, ffn=768, vocab=4096,
                     rope_theta=1e4, weight_fmt="nvfp4", name="dense-tiny")
@@ -110,9 +118,10 @@ class DenseModel:
 
         hq_l, hkv_l, ffn_l = cfg.q_heads // W, cfg.kv_heads // W, cfg.ffn // W
         r = tp_rank
-        embed = (torch.randn(cfg.vocab, H, device=device, dtype=torch.float32, generator=g) * std).to(BF)
+        adt = torch.float32 if cfg.weight_fmt == "fp32" else BF
+        embed = (torch.randn(cfg.vocab, H, device=device, dtype=torch.float32, generator=g) * std).to(adt)
         layers = []
-        ones = lambda n: torch.ones(n, device=device, dtype=BF)
+        ones = lambda n: torch.ones(n, device=device, dtype=adt)
         for _ in range(cfg.layers):
             nq, nkv = cfg.q_heads * d, cfg.kv_heads * d
             qkv = make(nq + 2 * nkv, H, cfg.weight_fmt,
@@ -190,7 +199,7 @@ class DenseModel:
                 k = torch.cat([kv[li][0], k])
                 v = torch.cat([kv[li][1], v])
             kv[li] = (k, v)
-            a = ref.attention(q, k, v, scale, causal_offset=start_pos).reshape(T, hq * d).to(BF)
+            a = ref.act(ref.attention(q, k, v, scale, causal_offset=start_pos).reshape(T, hq * d))
             o = ref.linear(a, L.o)
             if all_reduce is not None:
                 o = all_reduce(o)

@@ -11,10 +11,32 @@ from ..quant.formats import QuantLinear
 
 BF = torch.bfloat16
 
+# Activation dtype of the reference path.  bf16 reproduces the rounding points of the kernels; float32 turns every
+# rounding point into the identity (used by the fp32 CPU-plumbing model).
+_ACT = {"dtype": torch.bfloat16}
+
+
+class activation_dtype:
+    """Context manager: run the reference ops with another activation dtype (torch.float32 or torch.bfloat16)."""
+
+    def __init__(self, dtype):
+        self.dtype, self.prev = dtype, None
+
+    def __enter__(self):
+        self.prev = _ACT["dtype"]
+        _ACT["dtype"] = self.dtype
+
+    def __exit__(self, *a):
+        _ACT["dtype"] = self.prev
+
+
+def act(x: torch.Tensor) -> torch.Tensor:
+    return x.to(_ACT["dtype"])
+
 
 def _r(x: torch.Tensor) -> torch.Tensor:
-    """Round fp32 to bf16 and come back (marks a bf16 rounding point)."""
-    return x.to(BF).float()
+    """Round fp32 to the activation dtype and come back (marks a rounding point)."""
+    return x.to(_ACT["dtype"]).float()
 
 
 def embed_gather(ids, table):
@@ -28,7 +50,7 @@ def rmsnorm(x, w, eps=1e-6, delta=None, one_plus_w=False):
         xf = _r(xf + delta.float())
     rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     g = w.float() + (1.0 if one_plus_w else 0.0)
-    return (_r(xf * rstd) * g).to(BF), xf.to(BF)
+    return act(_r(xf * rstd) * g), act(xf)
 
 
 def swiglu(gate_up, limit: float = 0.0):
@@ -37,7 +59,7 @@ def swiglu(gate_up, limit: float = 0.0):
     if limit > 0:
         g = g.clamp(max=limit)
         u = u.clamp(-limit, limit)
-    return (_r(g * torch.sigmoid(g)) * u).to(BF)
+    return act(_r(g * torch.sigmoid(g)) * u)
 
 
 def argmax(logits, id_base=0):
@@ -53,9 +75,9 @@ def linear(x, w: QuantLinear, resid=None, out_fp32=False):
     y = x.float() @ w.dequant().t().to(x.device)
     if out_fp32:
         return y
-    y = y.to(BF)
+    y = act(y)
     if resid is not None:
-        y = (resid.float() + y.float()).to(BF)
+        y = act(resid.float() + y.float())
     return y
 
 

@@ -99,7 +99,7 @@ class QuantLinear:
     def dequant(self) -> torch.Tensor:
         """fp32 [N, K] values of the stored weights (oracle only)."""
         f, n, k = self.fmt, self.n, self.k
-        if f == "bf16":
+        if f in ("bf16", "fp32"):
             return self.payload.float()
         if f == "nvfp4":
             v = e2m1_decode(unpack_nibbles(self.payload)).view(n, k // 16, 16)
@@ -160,6 +160,8 @@ def quantize(w: torch.Tensor, fmt: str) -> QuantLinear:
     wf = w.float()
     if fmt == "bf16":
         return QuantLinear("bf16", n, k, w.to(torch.bfloat16).contiguous())
+    if fmt == "fp32":
+        return QuantLinear("fp32", n, k, wf.contiguous())
     if fmt == "nvfp4":
         assert k % 16 == 0
         amax = wf.abs().max().clamp_min(1e-12)
