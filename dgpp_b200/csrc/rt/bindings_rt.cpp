@@ -133,6 +133,9 @@ void bind_more(py::module_& m) {
            py::arg("blocks"), py::arg("max_context"), py::arg("vocab"), py::arg("tokens_per_step") = 1)
       .def("free_blocks", &FakeEngine::free_blocks)
       .def("total_blocks", &FakeEngine::total_blocks)
+      .def("max_context", &FakeEngine::max_context)
+      .def("max_concurrent", &FakeEngine::max_concurrent)
+      .def("block_tokens", &FakeEngine::block_tokens)
       .def_readonly("prefill_calls", &FakeEngine::prefill_calls)
       .def_readonly("prefill_tokens", &FakeEngine::prefill_tokens)
       .def_readonly("decode_passes", &FakeEngine::decode_passes)

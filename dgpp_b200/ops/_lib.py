@@ -33,6 +33,7 @@ _SIGNATURES = {
     "dgpp_rope_kv_write": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
     "dgpp_attn_decode": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_decode_tc": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "dgpp_attn_prefill_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_decode_advance": [P, P, P, P, P, I, I, P],
     "dgpp_act_quant_nvfp4": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
     "dgpp_act_quant_nvfp4_cluster": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],

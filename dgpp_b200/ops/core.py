@@ -296,3 +296,17 @@ def attn_decode_tc(q, q_stride: int, cache, block_table, row_req, positions, hq:
          ptr(cache.v_scale), ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq,
          hkv, d, cache.page, block_table.shape[1], cache.k.shape[0], splits, float(scale), window, stream_ptr())
     return out
+
+
+def attn_prefill_tc(q, q_stride: int, cache, block_table_row, pos0: int, hq: int, hkv: int, d: int, scale: float,
+                    out=None, window: int = 0, rows: Optional[int] = None):
+    """Causal tensor-core flash attention of a prefill chunk (rows at positions pos0.. of one request) against the
+    FP8 paged cache that already holds those positions.  head_dim 128."""
+    assert cache.fp8
+    T = rows if rows is not None else q.shape[0]
+    if out is None:
+        out = torch.empty(T, hq * d, dtype=torch.bfloat16, device=q.device)
+    call("dgpp_attn_prefill_tc", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale),
+         ptr(block_table_row), ptr(out), T, pos0, hq, hkv, d, cache.page, block_table_row.numel(), cache.k.shape[0],
+         float(scale), window, stream_ptr())
+    return out

@@ -1,0 +1,316 @@
+"""OpenAI-compatible server: native HTTP/SSE front end + native scheduler around a scheduler engine.
+
+    python -m dgpp_b200.serve.app --model tiny --port 8000          (random-init model, byte-level tokenizer)
+
+Threads: the C++ epoll thread owns the sockets; ONE service thread (this module) drains parsed requests,
+renders + tokenises them, submits them to the scheduler, runs one scheduler tick per loop turn and turns token
+events into SSE chunks / final JSON.  Routes: POST /v1/chat/completions, POST /v1/completions, GET /v1/models,
+GET /v1/models/{id}, GET /health, GET /metrics, GET /v1/metrics, GET /metrics/prometheus.
+(behavioural spec: apps/dgpp_serve.cpp:1483-1744 serve_openai, src/serve/generation_service.cpp:4300-4439
+ engine_pass, docs/openai-compatibility.md:17-135 of the reference.)
+"""
+from __future__ import annotations
+
+import json
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+from ..runtime import rt
+
+DEFAULT_TEMPLATE = ("{% for m in messages %}<|im_start|>{{ m.role }}\n{{ m.content }}<|im_end|>\n{% endfor %}"
+                    "{% if add_generation_prompt %}<|im_start|>assistant\n{% endif %}")
+
+
+@dataclass
+class _Live:
+    rid: str
+    conn: int
+    req: dict
+    index: int
+    group: str
+    prompt_tokens: int
+    created: int
+    decoder: object
+    scanner: object
+    text: bytearray = field(default_factory=bytearray)
+    tokens: int = 0
+    cached: int = 0
+    first_chunk: bool = True
+    finish: str = ""
+    t_submit: float = 0.0
+    t_first: float = 0.0
+
+
+class Metrics:
+    def __init__(self):
+        self.c: Dict[str, float] = {"requests_total": 0, "requests_failed": 0, "prompt_tokens_total": 0,
+                                    "completion_tokens_total": 0, "cached_tokens_total": 0, "cancelled_total": 0}
+        self.ttft: List[float] = []
+        self.buckets = [0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1, 2.5, 5, 10]
+
+    def prometheus(self, sched_meters: dict, prefix: str = "dgpp_b200") -> str:
+        out = []
+        for k, v in self.c.items():
+            out += [f"# TYPE {prefix}_{k} counter", f"{prefix}_{k} {v:g}"]
+        for k, v in sched_meters.items():
+            out += [f"# TYPE {prefix}_sched_{k} gauge", f"{prefix}_sched_{k} {v:g}"]
+        out.append(f"# TYPE {prefix}_time_to_first_token_seconds histogram")
+        for b in self.buckets:
+            out.append(f'{prefix}_time_to_first_token_seconds_bucket{{le="{b}"}} {sum(1 for t in self.ttft if t <= b)}')
+        out.append(f'{prefix}_time_to_first_token_seconds_bucket{{le="+Inf"}} {len(self.ttft)}')
+        out.append(f"{prefix}_time_to_first_token_seconds_sum {sum(self.ttft):g}")
+        out.append(f"{prefix}_time_to_first_token_seconds_count {len(self.ttft)}")
+        return "\n".join(out) + "\n"
+
+
+class Server:
+    def __init__(self, engine, tokenizer, template_src: str = DEFAULT_TEMPLATE, model_name: str = "dgpp-b200",
+                 host: str = "127.0.0.1", port: int = 0, eos_ids: Optional[List[int]] = None,
+                 default_max_tokens: int = 256, sched_config=None):
+        self.engine, self.tok = engine, tokenizer
+        self.template = rt.ChatTemplate(template_src)
+        self.model_name = model_name
+        self.eos_ids = eos_ids or []
+        self.default_max_tokens = default_max_tokens
+        self.sched = rt.Scheduler(engine, sched_config or rt.SchedulerConfig())
+        self.http = rt.HttpServer(host, port)
+        self.live: Dict[str, _Live] = {}
+        self.groups: Dict[str, dict] = {}
+        self.metrics = Metrics()
+        self.started = int(time.time())
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+        self.failed: Optional[str] = None
+
+    # ------------------------------------------------------------------ lifecycle
+    def start(self) -> int:
+        self.http.start()
+        self._thread = threading.Thread(target=self._loop, name="dgpp-service", daemon=True)
+        self._thread.start()
+        return self.http.port()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=30)
+        self.http.stop()
+
+    def port(self) -> int:
+        return self.http.port()
+
+    # ------------------------------------------------------------------ loop
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            busy = not self.sched.idle()
+            for req in self.http.poll(0 if busy else 50):
+                try:
+                    self._route(req)
+                except rt.ApiError as e:
+                    self.metrics.c["requests_failed"] += 1
+                    self.http.respond(req["conn"], e.args[0], "application/json", e.args[1].encode())
+                except Exception as e:  # never let one request kill the loop
+                    self.metrics.c["requests_failed"] += 1
+                    body = rt.error_json(500, f"internal error: {e}", type="server_error")
+                    self.http.respond(req["conn"], 500, "application/json", body.encode())
+            for conn in self.http.poll_disconnects():
+                for lv in list(self.live.values()):
+                    if lv.conn == conn:
+                        self.sched.cancel(lv.rid)
+            if not self.sched.idle():
+                try:
+                    self.sched.tick()
+                except Exception as e:
+                    self._fail_engine(str(e))
+                    return
+                self._drain_events()
+
+    def _fail_engine(self, why: str) -> None:
+        """Engine failure: every open request gets an error, the server stops accepting work."""
+        self.failed = why
+        err = rt.error_json(500, f"engine failure: {why}", type="engine_failure")
+        for lv in list(self.live.values()):
+            g = self.groups.get(lv.group)
+            if g and g["stream"]:
+                self.http.stream_send(lv.conn, f"data: {err}\n\n".encode())
+                self.http.stream_end(lv.conn)
+            else:
+                self.http.respond(lv.conn, 500, "application/json", err.encode())
+        self.live.clear()
+        self.groups.clear()
+
+    # ------------------------------------------------------------------ routing
+    def _route(self, req: dict) -> None:
+        path, method, conn = req["path"].rstrip("/") or "/", req["method"], req["conn"]
+        if self.failed:
+            self.http.respond(conn, 503, "application/json",
+                              rt.error_json(503, "engine failed: " + self.failed, type="engine_failure").encode())
+            return
+        if method == "GET" and path == "/health":
+            self.http.respond(conn, 200, "application/json", b'{"status":"ok"}')
+        elif method == "GET" and path == "/v1/models":
+            self.http.respond(conn, 200, "application/json", rt.models_json([self.model_name], self.started).encode())
+        elif method == "GET" and path.startswith("/v1/models/"):
+            if path[len("/v1/models/"):] == self.model_name:
+                body = json.dumps({"id": self.model_name, "object": "model", "created": self.started, "owned_by": "dgpp_b200"})
+                self.http.respond(conn, 200, "application/json", body.encode())
+            else:
+                self.http.respond(conn, 404, "application/json", rt.error_json(404, "model not found", param="model").encode())
+        elif method == "GET" and path in ("/metrics", "/v1/metrics"):
+            body = json.dumps({"counters": self.metrics.c, "scheduler": self.sched.meters(), "live": len(self.live)})
+            self.http.respond(conn, 200, "application/json", body.encode())
+        elif method == "GET" and path == "/metrics/prometheus":
+            self.http.respond(conn, 200, "text/plain; version=0.0.4", self.metrics.prometheus(self.sched.meters()).encode())
+        elif method == "POST" and path in ("/v1/chat/completions", "/v1/completions"):
+            self._submit(conn, req["body"].decode("utf-8", "replace"), chat=path.endswith("chat/completions"))
+        elif path in ("/v1/chat/completions", "/v1/completions", "/health", "/v1/models"):
+            self.http.respond(conn, 405, "application/json", rt.error_json(405, "method not allowed").encode())
+        else:
+            self.http.respond(conn, 404, "application/json", rt.error_json(404, f"unknown route {path}").encode())
+
+    def _submit(self, conn: int, body: str, chat: bool) -> None:
+        r = rt.parse_chat_request(body) if chat else rt.parse_completion_request(body)
+        if chat:
+            ctx = {"messages": json.loads(r["messages_json"]), "add_generation_prompt": True}
+            tools = json.loads(r["tools_json"])
+            if tools:
+                ctx["tools"] = tools
+            kw = json.loads(r["chat_template_kwargs_json"])
+            if kw:
+                ctx.update(kw)
+            ids = self.tok.encode(self.template.render_json(json.dumps(ctx)))
+        elif r["prompt_ids"]:
+            ids = list(r["prompt_ids"])
+        else:
+            ids = self.tok.encode(r["prompt_text"])
+        if not ids:
+            raise rt.ApiError(400, rt.error_json(400, "the prompt is empty", param="messages" if chat else "prompt"))
+        max_tokens = r["max_tokens"] if r["max_tokens"] > 0 else self.default_max_tokens
+        if len(ids) + max_tokens > self.engine.max_context():
+            raise rt.ApiError(400, rt.error_json(
+                400, f"prompt ({len(ids)} tokens) plus max_tokens ({max_tokens}) exceeds the context window "
+                     f"({self.engine.max_context()})", param="max_tokens", code="context_length_exceeded"))
+        group = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
+        created = int(time.time())
+        self.groups[group] = {"conn": conn, "chat": chat, "stream": r["stream"], "n": r["n"], "done": 0, "req": r,
+                              "choices": [None] * r["n"], "created": created, "prompt_tokens": len(ids)}
+        self.metrics.c["requests_total"] += 1
+        self.metrics.c["prompt_tokens_total"] += len(ids)
+        if r["stream"]:
+            self.http.stream_begin(conn)
+        for i in range(r["n"]):
+            rid = f"{group}-{i}"
+            self.live[rid] = _Live(rid, conn, r, i, group, len(ids), created, rt.StreamDecoder(self.tok, True),
+                                   rt.StopScanner(list(r["stop"])), t_submit=time.time())
+            self.sched.submit(rid, ids, max_tokens, eos_ids=[] if r["ignore_eos"] else self.eos_ids,
+                              ignore_eos=r["ignore_eos"], prefix_cache=r["prefix_cache"], cache_key=r["prompt_cache_key"])
+
+    # ------------------------------------------------------------------ events -> responses
+    def _drain_events(self) -> None:
+        for kind, rid, a, b in self.sched.events():
+            lv = self.live.get(rid)
+            if lv is None:
+                continue
+            g = self.groups[lv.group]
+            if kind == "admit":
+                lv.cached = b
+                self.metrics.c["cached_tokens_total"] += b
+            elif kind == "token":
+                if lv.finish:
+                    continue
+                if lv.tokens == 0:
+                    lv.t_first = time.time()
+                    self.metrics.ttft.append(lv.t_first - lv.t_submit)
+                lv.tokens += 1
+                self.metrics.c["completion_tokens_total"] += 1
+                piece = lv.scanner.feed(lv.decoder.push(a))
+                self._emit(lv, g, piece)
+                if lv.scanner.stopped():
+                    lv.finish = "stop"
+                    self.sched.cancel(rid)
+            elif kind.startswith("retire"):
+                why = kind.split(":", 1)[1]
+                if not lv.finish:
+                    tail = lv.scanner.feed(lv.decoder.flush())
+                    tail += lv.scanner.flush()
+                    self._emit(lv, g, tail)
+                    lv.finish = {"length": "length", "stop": "stop", "cancelled": "stop", "error": "error"}.get(why, why)
+                    if why == "cancelled":
+                        self.metrics.c["cancelled_total"] += 1
+                self._finish(lv, g)
+
+    def _emit(self, lv: _Live, g: dict, piece: bytes) -> None:
+        if not piece and not (g["stream"] and lv.first_chunk and g["chat"]):
+            return
+        lv.text += piece
+        if g["stream"]:
+            ev = rt.chunk_event(g["chat"], lv.group, self.model_name, lv.created, lv.index,
+                                piece.decode("utf-8", "replace"), role_delta=lv.first_chunk and g["chat"])
+            lv.first_chunk = False
+            self.http.stream_send(lv.conn, ev.encode())
+
+    def _finish(self, lv: _Live, g: dict) -> None:
+        if g["stream"]:
+            ev = rt.chunk_event(g["chat"], lv.group, self.model_name, lv.created, lv.index, "", finish_reason=lv.finish)
+            self.http.stream_send(lv.conn, ev.encode())
+        g["choices"][lv.index] = (lv.index, lv.text.decode("utf-8", "replace"), lv.finish)
+        g["done"] += 1
+        g.setdefault("completion_tokens", 0)
+        g["completion_tokens"] += lv.tokens
+        g["cached"] = max(g.get("cached", 0), lv.cached)
+        del self.live[lv.rid]
+        if g["done"] == g["n"]:
+            if g["stream"]:
+                if g["req"]["include_usage"]:
+                    self.http.stream_send(lv.conn, rt.usage_event(g["chat"], lv.group, self.model_name, g["created"],
+                                                                  g["prompt_tokens"], g["completion_tokens"],
+                                                                  g["cached"]).encode())
+                self.http.stream_send(lv.conn, rt.done_event().encode())
+                self.http.stream_end(lv.conn)
+            else:
+                body = rt.completion_json(g["chat"], lv.group, self.model_name, g["created"], g["choices"],
+                                          g["prompt_tokens"], g["completion_tokens"], g["cached"])
+                self.http.respond(lv.conn, 200, "application/json", body.encode())
+            del self.groups[lv.group]
+
+
+def main(argv=None) -> int:
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--model", default="tiny", choices=["tiny", "fake"])
+    ap.add_argument("--slots", type=int, default=8)
+    args = ap.parse_args(argv)
+    tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)], rt.SplitPattern.Qwen2)
+    if args.model == "fake":
+        eng = rt.FakeEngine(slots=args.slots, block_tokens=16, blocks=4096, max_context=8192, vocab=256)
+    else:
+        import torch
+
+        from ..engine.adapters import KernelEngine, ReferenceEngine
+        from ..engine.llm_engine import LLMEngine
+        from ..models.dense import DenseConfig, DenseModel
+
+        if torch.cuda.is_available():
+            cfg = DenseConfig.tiny(vocab=4096)
+            model = DenseModel.random_init(cfg, device="cuda", seed=0, std=0.05)
+            eng = KernelEngine(LLMEngine(model, max_batch=args.slots, max_seq_len=4096, prefill_chunk=512))
+        else:
+            cfg = DenseConfig.tiny(vocab=4096, weight_fmt="bf16")
+            eng = ReferenceEngine(DenseModel.random_init(cfg, device="cpu", seed=0, std=0.05), slots=args.slots)
+    srv = Server(eng, tok, model_name=f"dgpp-b200-{args.model}", host=args.host, port=args.port, eos_ids=[257])
+    print(f"listening on http://{args.host}:{srv.start()}", flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        srv.stop()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
