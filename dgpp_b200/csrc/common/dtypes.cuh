@@ -92,6 +92,24 @@ __device__ __forceinline__ void e2m1x8_residual(uint32_t codes, float s, float* 
   }
 }
 
+// Two floats -> two e4m3 terms each (value + residual), packed: a = {e4m3(x0), e4m3(x1)} (x0 in the low byte),
+// b = e4m3 of what a left.  The residual is formed in f16x2: x rounded to f16 (11 bits) minus a 4-bit value is
+// exact, so the pair keeps ~2^-8 relative error.  Five conversions / subtractions per PAIR of elements.
+__device__ __forceinline__ void f32x2_to_e4m3x2_two_term(float x0, float x1, uint16_t& a, uint16_t& b) {
+  uint32_t xh, ah, rh;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(a) : "f"(x0), "f"(x1));
+  asm("cvt.rn.f16x2.f32 %0, %2, %1;" : "=r"(xh) : "f"(x0), "f"(x1));
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(ah) : "h"(a));
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(rh) : "r"(xh), "r"(ah));
+  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(b) : "r"(rh));
+}
+// 2^x, one MUFU; flushes denormals, ex2(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 union Pack16 {
   uint4 u;
   bf16 h[8];

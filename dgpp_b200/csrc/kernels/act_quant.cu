@@ -10,10 +10,12 @@
 //   0 plain rows, 1 swiglu([gate | up]), 2 rmsnorm(resid + delta) * w
 //   q rows [token tile][term][token], scale factors in tcgen05.cp atom order per token tile.
 #include <cooperative_groups.h>
+#include <string.h>
 
 #include "common/common.h"
 #include "common/dtypes.cuh"
 #include "common/ptx.cuh"
+#include "kernels/comm.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -33,8 +35,15 @@ struct ClusterQuantArgs {
   uint8_t* sf;
   float* g;
   int T, T_pad, K, R, bn, cl;
+  DeviceStatus* status;
   float eps, limit;
   int one_plus_w;
+  // MODE 2 with fold = 1: `delta` is not read from memory but folded from the W partial tiles that the
+  // tensor-parallel GEMMs pushed into this rank's symmetric region (ascending rank order, fp32, one bf16
+  // rounding: the bits an all-reduce would have produced).  The kernel waits for the tile flags it needs and its
+  // last CTA advances the collective epoch.
+  int fold;
+  CommState comm;
 };
 
 __device__ __forceinline__ float warp_red(float v, bool is_max) {
@@ -75,13 +84,42 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
     return r;
   };
   float amax = 0.f;
+  uint32_t fold_epoch = 0;
+  int fold_parity = 0;
+  if (MODE == 2 && a.fold) {
+    fold_epoch = *a.comm.epoch + 1;
+    fold_parity = fold_epoch & 1;
+    const int tile0 = k0 / 128, ntile = (k0 + kseg - 1) / 128 - tile0 + 1;
+    for (int i = tid; i < ntile * a.comm.world; i += kAqThreads) {
+      const int src = i / ntile, tl = tile0 + i % ntile;
+      if (!wait_flag(flag(a.comm, a.comm.rank, fold_parity, src, tl), fold_epoch)) {
+        if (atomicCAS(&a.status->code, 0, kTimeoutPeerFlag) == 0) a.status->detail = src;
+        atomicAdd(&a.status->count, 1);
+      }
+    }
+    __syncthreads();
+  }
   if (MODE == 2) {
     const bf16* rr = a.in + static_cast<size_t>(t) * a.in_stride + k0;
     float ss = 0.f;
     for (int i = tid; i < nvec; i += kAqThreads) {
       Pack16 x;
       x.u = reinterpret_cast<const uint4*>(rr)[i];
-      if (a.delta) {
+      if (a.fold) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < a.comm.world; ++r) {
+          Pack16 d;
+          d.u = ld_v4_global_volatile(payload(a.comm, a.comm.rank, fold_parity, r) +
+                                      (static_cast<size_t>(t) * K + k0) * 2 + static_cast<size_t>(i) * 16);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += bf16_to_f32(d.h[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x.h[j] = f32_to_bf16(bf16_to_f32(x.h[j]) + bf16_to_f32(f32_to_bf16(acc[j])));
+        reinterpret_cast<uint4*>(a.resid_out + static_cast<size_t>(t) * K + k0)[i] = x.u;
+      } else if (a.delta) {
         Pack16 d;
         d.u = reinterpret_cast<const uint4*>(a.delta + static_cast<size_t>(t) * K + k0)[i];
 #pragma unroll
@@ -176,6 +214,14 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
     }
   }
   cluster.sync();  // keep every CTA's shared memory alive until all remote reads are done
+  if (MODE == 2 && a.fold && tid == 0) {
+    __threadfence();
+    if (atomicAdd(a.comm.done_ctas, 1u) == gridDim.x * gridDim.y - 1) {
+      *a.comm.done_ctas = 0;
+      *a.comm.epoch = fold_epoch;
+      __threadfence();
+    }
+  }
 }
 
 template <int MODE>
@@ -205,7 +251,7 @@ using namespace dgpp;
 DGPP_API int dgpp_act_quant_nvfp4_cluster(int mode, const void* in, int64_t in_stride, const void* delta,
                                           const void* w, void* resid_out, void* x_out, void* q, void* sf, void* g,
                                           int T, int T_pad, int K, int R, int bn, int cl, float eps, float limit,
-                                          int one_plus_w, cudaStream_t st) {
+                                          int one_plus_w, void* comm_fold, cudaStream_t st) {
   DGPP_REQUIRE(K % 256 == 0, "act_quant: K %d must be a multiple of 256", K);
   DGPP_REQUIRE(cl == 1 || cl == 2 || cl == 4 || cl == 8, "act_quant: cluster size %d not in {1,2,4,8}", cl);
   DGPP_REQUIRE((K / cl) % 16 == 0 && K % cl == 0, "act_quant: K %d does not split over %d CTAs", K, cl);
@@ -225,6 +271,18 @@ DGPP_API int dgpp_act_quant_nvfp4_cluster(int mode, const void* in, int64_t in_s
   a.g = static_cast<float*>(g);
   a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.cl = cl; a.eps = eps; a.limit = limit;
   a.one_plus_w = one_plus_w;
+  a.status = device_status_ptr();
+  a.fold = 0;
+  memset(&a.comm, 0, sizeof(a.comm));
+  if (comm_fold) {
+    const DgppComm* c = static_cast<const DgppComm*>(comm_fold);
+    DGPP_REQUIRE(mode == 2, "act_quant: the all-reduce fold exists for the add + RMSNorm mode only");
+    DGPP_REQUIRE(resid_out != nullptr, "act_quant fold: resid_out required");
+    DGPP_REQUIRE(K % 128 == 0 && K / 128 <= kCommMaxCtas && static_cast<size_t>(T) * K * 2 <= c->st.slot_bytes,
+                 "act_quant fold: %d x %d does not fit the symmetric slot / flag table", T, K);
+    a.fold = 1;
+    a.comm = c->st;
+  }
   if (mode == 0) return launch_cluster<0>(a, st);
   if (mode == 1) return launch_cluster<1>(a, st);
   if (mode == 2) return launch_cluster<2>(a, st);

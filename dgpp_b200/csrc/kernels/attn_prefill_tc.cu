@@ -45,6 +45,73 @@ __device__ __forceinline__ uint32_t sw128_off(uint32_t row, uint32_t byte_in_row
   return row * 128u + ((((byte_in_row >> 4) ^ (row & 7u)) << 4) | (byte_in_row & 15u));
 }
 
+// Row maximum of raw score * k_scale over one 128-token tile (thread = query row, scores read from TMEM).
+template <bool kMask>
+__device__ __forceinline__ float tile_row_max(uint32_t taddr, const float* ks, int t0, int my_pos, int my_first) {
+  float mt = -INFINITY;
+#pragma unroll 2
+  for (int c0 = 0; c0 < kApTile; c0 += 16) {
+    uint32_t raw[16];
+    tmem_ld_x16(taddr + c0, raw);
+    tmem_ld_wait();
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(ks + c0 + q4 * 4);
+      const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float sv = __uint_as_float(raw[q4 * 4 + j]) * kk[j];
+        if (kMask) {
+          const int t = t0 + c0 + q4 * 4 + j;
+          mt = fmaxf(mt, (t <= my_pos && t >= my_first) ? sv : -INFINITY);
+        } else {
+          mt = fmaxf(mt, sv);
+        }
+      }
+    }
+  }
+  return mt;
+}
+
+// Probabilities of one tile: p = 2^(raw * k_scale * sm - m); P = p * v_scale * c_tile as two e4m3 terms written
+// to row r of the swizzled A operand (term 2 one tile further).  Returns the row sum of p.
+template <bool kMask>
+__device__ __forceinline__ float tile_probs(uint32_t taddr, const float* ks, const float* vs, unsigned char* sP, int r,
+                                            float sm, float neg_m, float c_tile, int t0, int my_pos, int my_first) {
+  float lsum = 0.f;
+#pragma unroll 2
+  for (int c0 = 0; c0 < kApTile; c0 += 16) {
+    uint32_t raw[16];
+    tmem_ld_x16(taddr + c0, raw);
+    tmem_ld_wait();
+    Pack16 a, bq;
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(ks + c0 + q4 * 4);
+      const float4 v4 = *reinterpret_cast<const float4*>(vs + c0 + q4 * 4);
+      const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+      const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+      float pw[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float e = fmaf(__uint_as_float(raw[q4 * 4 + j]) * kk[j], sm, neg_m);
+        if (kMask) {
+          const int t = t0 + c0 + q4 * 4 + j;
+          e = (t <= my_pos && t >= my_first) ? e : -INFINITY;
+        }
+        const float pv = fast_exp2(e);
+        lsum += pv;
+        pw[j] = pv * (vv[j] * c_tile);
+      }
+      f32x2_to_e4m3x2_two_term(pw[0], pw[1], a.s[q4 * 2], bq.s[q4 * 2]);
+      f32x2_to_e4m3x2_two_term(pw[2], pw[3], a.s[q4 * 2 + 1], bq.s[q4 * 2 + 1]);
+    }
+    *reinterpret_cast<uint4*>(sP + sw128_off(r, c0)) = a.u;
+    *reinterpret_cast<uint4*>(sP + kApTile * 128 + sw128_off(r, c0)) = bq.u;
+  }
+  return lsum;
+}
+
 __global__ void __launch_bounds__(kApThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        AttnPrefillParams p) {
@@ -95,7 +162,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   // ---- quantise this CTA's query rows into two e4m3 terms (thread = row)
   float q_scale = 1.f;
   if (warp >= 2) {
-    const int r = threadIdx.x - 64;
+    const int r = (warp & 3) * 32 + lane;   // the TMEM lane quadrant this warp may read: warp % 4
     float v[D];
     float amax = 0.f;
     if (r < rows) {
@@ -117,11 +184,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     for (int c = 0; c < D / 16; ++c) {
       Pack16 a, b;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float x = v[c * 16 + j] * inv;
-        a.b[j] = f32_to_e4m3(x);
-        b.b[j] = f32_to_e4m3(x - e4m3_to_f32(a.b[j]));
-      }
+      for (int j = 0; j < 8; ++j)
+        f32x2_to_e4m3x2_two_term(v[c * 16 + 2 * j] * inv, v[c * 16 + 2 * j + 1] * inv, a.s[j], b.s[j]);
       *reinterpret_cast<uint4*>(sQ + sw128_off(r, c * 16)) = a.u;
       *reinterpret_cast<uint4*>(sQ + kTileBytes + sw128_off(r, c * 16)) = b.u;
     }
@@ -238,21 +302,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       const float c_tile = vmax > 0.f ? 256.f / vmax : 0.f;
       // pass 1: row maximum of the scaled, masked scores (the scores are re-read from TMEM in pass 2 instead of
       // being kept in 128 registers next to the 128 output accumulators)
-      float mt = -INFINITY;
-#pragma unroll 2
-      for (int c0 = 0; c0 < kApTile; c0 += 16) {
-        uint32_t raw[16];
-        tmem_ld_x16(tmem_s + b * 128 + lane_addr + c0, raw);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int t = t0 + c0 + j;
-          const bool valid = t <= my_pos && t >= my_first;
-          mt = fmaxf(mt, valid ? __uint_as_float(raw[j]) * sm * ks[c0 + j] : -INFINITY);
-        }
-      }
-      const float mn = fmaxf(m_run, mt);
-      const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - mn);
+      const bool full = (t0 + kApTile - 1 <= my_pos) && (t0 >= my_first);
+      const float mt = full ? tile_row_max<false>(tmem_s + b * 128 + lane_addr, ks, t0, my_pos, my_first)
+                            : tile_row_max<true>(tmem_s + b * 128 + lane_addr, ks, t0, my_pos, my_first);
+      const float mn = fmaxf(m_run, mt * sm);   // sm > 0: scaling commutes with the maximum
+      const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - mn);
       m_run = mn;
       float lsum = 0.f;
       // the previous tile's PV product must be folded in before P is overwritten
@@ -275,25 +329,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 #pragma unroll
       for (int j = 0; j < D; ++j) o[j] *= corr;
       // pass 2: probabilities -> two e4m3 terms of P (row r of the A operand)
-#pragma unroll 2
-      for (int c0 = 0; c0 < kApTile; c0 += 16) {
-        uint32_t raw[16];
-        tmem_ld_x16(tmem_s + b * 128 + lane_addr + c0, raw);
-        tmem_ld_wait();
-        Pack16 a, bq;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int t = t0 + c0 + j;
-          const bool valid = t <= my_pos && t >= my_first && mn > -INFINITY;
-          const float pv = valid ? exp2f(__uint_as_float(raw[j]) * sm * ks[c0 + j] - mn) : 0.f;
-          lsum += pv;
-          const float pw = pv * vs[c0 + j] * c_tile;
-          a.b[j] = f32_to_e4m3(pw);
-          bq.b[j] = f32_to_e4m3(pw - e4m3_to_f32(a.b[j]));
-        }
-        *reinterpret_cast<uint4*>(sP + sw128_off(r, c0)) = a.u;
-        *reinterpret_cast<uint4*>(sP + kTileBytes + sw128_off(r, c0)) = bq.u;
-      }
+      const float neg_m = (mn == -INFINITY) ? 0.f : -mn;
+      lsum = full ? tile_probs<false>(tmem_s + b * 128 + lane_addr, ks, vs, sP, r, sm, neg_m, c_tile, t0, my_pos, my_first)
+                  : tile_probs<true>(tmem_s + b * 128 + lane_addr, ks, vs, sP, r, sm, neg_m, c_tile, t0, my_pos, my_first);
       l_run = l_run * corr + lsum;
       inv_c_prev = c_tile > 0.f ? 1.f / c_tile : 0.f;
       fence_proxy_async_smem();

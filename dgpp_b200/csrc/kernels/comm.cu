@@ -21,47 +21,9 @@
 #include "common/common.h"
 #include "common/dtypes.cuh"
 #include "common/ptx.cuh"
+#include "kernels/comm.cuh"
 
 namespace dgpp {
-
-constexpr int kCommMaxWorld = 8;
-constexpr int kCommMaxCtas = 64;
-constexpr int kPickRows = 256;
-
-struct CommState {
-  unsigned char* peers[kCommMaxWorld];  // base of every rank's symmetric region (peer-mapped pointers)
-  int world, rank;
-  size_t slot_bytes;
-  uint32_t* epoch;      // device counter of completed all-reduces (local memory)
-  uint32_t* done_ctas;  // CTAs finished in the current call (local)
-  uint32_t* pick_epoch;
-};
-
-__device__ __forceinline__ unsigned char* payload(const CommState& c, int owner, int parity, int src) {
-  return c.peers[owner] + (static_cast<size_t>(parity) * c.world + src) * c.slot_bytes;
-}
-__device__ __forceinline__ uint32_t* flag(const CommState& c, int owner, int parity, int src, int cta) {
-  unsigned char* base = c.peers[owner] + 2 * static_cast<size_t>(c.world) * c.slot_bytes;
-  return reinterpret_cast<uint32_t*>(base) + (static_cast<size_t>(parity) * c.world + src) * kCommMaxCtas + cta;
-}
-__device__ __forceinline__ unsigned char* pick_base(const CommState& c, int owner) {
-  return c.peers[owner] + 2 * static_cast<size_t>(c.world) * c.slot_bytes +
-         2 * static_cast<size_t>(c.world) * kCommMaxCtas * sizeof(uint32_t);
-}
-
-// Bounded spin on a flag written by a peer; false when it gave up (about 2 s).
-__device__ __forceinline__ bool wait_flag(const uint32_t* f, uint32_t want) {
-  for (int i = 0; i < 1 << 14; ++i)
-    if (ld_acquire_sys(f) == want) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    for (int i = 0; i < 256; ++i) {
-      if (ld_acquire_sys(f) == want) return true;
-      __nanosleep(64);
-    }
-    if (clock64() - t0 > 4000000000ll) return false;
-  }
-}
 
 // data: [n] bf16 (n multiple of 8), reduced in place.  resid (optional): out = bf16(resid + bf16(sum)).
 __global__ void __launch_bounds__(256)
@@ -185,12 +147,6 @@ pick_merge_kernel(CommState c, int32_t* __restrict__ ids, float* __restrict__ va
 
 using namespace dgpp;
 
-struct DgppComm {
-  CommState st;
-  void* local;
-  void* opened[kCommMaxWorld];
-  size_t region_bytes;
-};
 
 static size_t region_size(int world, size_t slot_bytes) {
   return 2 * static_cast<size_t>(world) * slot_bytes + 2 * static_cast<size_t>(world) * kCommMaxCtas * sizeof(uint32_t) +

@@ -29,6 +29,7 @@
 #include "common/common.h"
 #include "common/dtypes.cuh"
 #include "common/ptx.cuh"
+#include "kernels/comm.cuh"
 #include "kernels/gemm_common.cuh"
 
 namespace dgpp {
@@ -52,7 +53,27 @@ struct Fp4Params {
   DeviceStatus* status;
   int T, T_pad, N, K, ldc, R;
   int stages_per_split;
+  // Fused all-reduce push (tensor-parallel o_proj / down_proj at decode sizes): instead of writing `out`, the CTA
+  // that finishes an output tile stores it as bf16 into slot `rank` of EVERY rank's symmetric region and raises
+  // flag[parity][rank][n tile] = epoch there.  The consumer (fold + add + RMSNorm + quantise) waits on the flags.
+  int push;
+  CommState comm;
 };
+
+// One bf16 of the finished output tile -> slot `rank` of every rank (destinations staggered by rank).
+__device__ __forceinline__ void push_value(const Fp4Params& p, int parity, size_t idx, bf16 v) {
+  for (int r = 0; r < p.comm.world; ++r) {
+    const int dst = (p.comm.rank + r) % p.comm.world;
+    reinterpret_cast<bf16*>(payload(p.comm, dst, parity, p.comm.rank))[idx] = v;
+  }
+}
+// Called by the 128 epilogue threads of the CTA that wrote the tile: make the stores visible at system scope, then
+// raise this tile's flag on every rank.
+__device__ __forceinline__ void push_flags(const Fp4Params& p, int parity, uint32_t epoch, int warp, int lane) {
+  __threadfence_system();
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (warp == 2 && lane < p.comm.world) st_release_sys(flag(p.comm, lane, parity, p.comm.rank, blockIdx.x), epoch);
+}
 
 // BN = MMA N = (token tile) x (residual terms): with R > 1 the terms of one token tile are stacked along N
 // (rows r * bn_tok + m of the B operand) so a K=64 step is ONE tcgen05.mma whatever R is; the epilogue adds the
@@ -184,6 +205,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
     tc_fence_after();
     const int n = n0 + q * 32 + lane;
     const int cols = min(bn_tok, p.T - m0);
+    const uint32_t push_epoch = p.push ? *p.comm.epoch + 1 : 0u;
+    const int push_parity = push_epoch & 1;
     if (ok && !*abort_flag) {
       float* wsp = splits > 1 ? p.ws + (static_cast<size_t>(split) * p.T + m0) * p.N : nullptr;
 #pragma unroll 1
@@ -211,6 +234,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
               } else {
                 const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
                 float y = v[j] * p.alpha * p.g[m0 + m];
+                if (p.push) {
+                  push_value(p, push_parity, static_cast<size_t>(m0 + m) * p.N + n, f32_to_bf16(y));
+                  continue;
+                }
                 if (p.out32) p.out32[o] = y;
                 if (p.out) {
                   if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
@@ -222,6 +249,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
         }
       }
     }
+    if (p.push && splits == 1) push_flags(p, push_parity, push_epoch, warp, lane);
     if (splits > 1) {
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -239,6 +267,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
               acc += __ldcg(p.ws + (static_cast<size_t>(s2) * p.T + m0 + m) * p.N + n);
             const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
             float y = acc * p.alpha * p.g[m0 + m];
+            if (p.push) {
+              push_value(p, push_parity, static_cast<size_t>(m0 + m) * p.N + n, f32_to_bf16(y));
+              continue;
+            }
             if (p.out32) p.out32[o] = y;
             if (p.out) {
               if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
@@ -247,6 +279,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
           }
         }
         if (warp == 2 && lane == 0) p.counters[blockIdx.y * gridDim.x + blockIdx.x] = 0;
+        if (p.push) push_flags(p, push_parity, push_epoch, warp, lane);
       }
     }
   }
@@ -478,12 +511,13 @@ DGPP_API int dgpp_act_quant_nvfp4(int mode, const void* in, int64_t in_stride, c
 // out[T, N] = alpha * g[t] * sum_r Wq . Xq_r^T.   xq: [R, T_pad, K/2]; xsf / wsf_tiled: tiled scale factors; g: [T].
 DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* g, int R, int T_pad, const void* wq,
                            const void* wsf_tiled, float alpha, void* out, void* out32, const void* resid, int ldc,
-                           int T, int N, int K, int splits, void* ws, void* counters, cudaStream_t st) {
+                           int T, int N, int K, int splits, void* ws, void* counters, void* comm_push,
+                           cudaStream_t st) {
   DGPP_REQUIRE(K % 256 == 0, "gemm_fp4: K %d must be a multiple of 256", K);
   DGPP_REQUIRE(R >= 1 && R <= 4, "gemm_fp4: R %d outside 1..4", R);
   DGPP_REQUIRE(splits >= 1, "gemm_fp4: splits must be >= 1");
   DGPP_REQUIRE(splits == 1 || (ws && counters), "gemm_fp4: split-K needs workspace and counters");
-  DGPP_REQUIRE(out || out32, "gemm_fp4: no output");
+  DGPP_REQUIRE(out || out32 || comm_push, "gemm_fp4: no output");
   DGPP_REQUIRE(T_pad >= T && T_pad % bn == 0, "gemm_fp4: T_pad %d must cover T and be a multiple of bn %d", T_pad, bn);
   Fp4Params p;
   p.alpha = alpha;
@@ -497,6 +531,17 @@ DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* 
   p.counters = static_cast<uint32_t*>(counters);
   p.status = device_status_ptr();
   p.T = T; p.T_pad = T_pad; p.N = N; p.K = K; p.ldc = ldc; p.R = R;
+  p.push = 0;
+  memset(&p.comm, 0, sizeof(p.comm));
+  if (comm_push) {
+    const DgppComm* c = static_cast<const DgppComm*>(comm_push);
+    DGPP_REQUIRE(T <= bn, "gemm_fp4 push: %d rows do not fit one token tile of %d", T, bn);
+    DGPP_REQUIRE(N % 128 == 0 && N / 128 <= kCommMaxCtas, "gemm_fp4 push: N %d needs N %% 128 == 0 and <= %d tiles", N,
+                 kCommMaxCtas);
+    DGPP_REQUIRE(static_cast<size_t>(T) * N * 2 <= c->st.slot_bytes, "gemm_fp4 push: %d x %d exceeds the slot", T, N);
+    p.push = 1;
+    p.comm = c->st;
+  }
   const int stages = K / 256;
   const int per = dgpp_ceil_div(stages, splits);
   p.stages_per_split = per;

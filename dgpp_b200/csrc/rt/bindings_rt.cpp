@@ -11,6 +11,7 @@ namespace py = pybind11;
 using namespace dgpp;
 
 void bind_text(py::module_& m);     // tokenizer, chat template (bindings_text.cpp)
+void bind_load(py::module_& m);     // safetensors, hub cache, architecture detect, shard specs (bindings_load.cpp)
 void bind_serve(py::module_& m);    // sampler oracle, grammars, http server (bindings_serve.cpp)
 
 namespace {
@@ -174,4 +175,5 @@ void bind_more(py::module_& m) {
 
   bind_text(m);
   bind_serve(m);
+  bind_load(m);
 }

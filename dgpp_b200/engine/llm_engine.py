@@ -30,7 +30,7 @@ from .runner import DenseRunner
 class LLMEngine:
     def __init__(self, model: DenseModel, max_batch: int = 8, max_seq_len: int = 4096, prefill_chunk: int = 2048,
                  kv_blocks: Optional[int] = None, reducer=None, use_graphs: bool = True, ring_steps: int = 1024,
-                 decode_pdl: bool = True, act_terms: int = 3):
+                 decode_pdl: bool = True, act_terms: int = 3, fuse_ar: bool = True):
         c = model.cfg
         self.model, self.max_batch, self.max_seq_len = model, max_batch, max_seq_len
         self.prefill_chunk = prefill_chunk
@@ -45,7 +45,7 @@ class LLMEngine:
         splits = max(1, min(16, round(296 / max(1, model.hkv_local * max_batch))))
         self.decode_pdl = decode_pdl
         self.runner = DenseRunner(model, self.kv, rows, reducer=reducer, decode_splits=splits, decode_rows=max_batch,
-                                  act_terms=act_terms)
+                                  act_terms=act_terms, fuse_ar=fuse_ar)
         self.use_graphs = use_graphs
         self.ring_steps = ring_steps
         i32 = dict(dtype=torch.int32, device=self.dev)
@@ -88,7 +88,8 @@ class LLMEngine:
             torch.arange(start_pos + done, start_pos + done + t, dtype=torch.int32, device=self.dev,
                          out=self.p_positions[:t])
             self.p_row_req[:t].fill_(slot)
-            r.forward(t, self.p_tokens[:t], self.p_positions[:t], self.p_row_req[:t], decode=False)
+            r.forward(t, self.p_tokens[:t], self.p_positions[:t], self.p_row_req[:t], decode=False,
+                      chunk=(slot, start_pos + done))
             done += t
         self.lengths[slot] = start_pos + n
         return r.pick_id[:1]

@@ -24,12 +24,16 @@ BF = torch.bfloat16
 class DenseRunner:
     def __init__(self, model: DenseModel, kv: PagedKV, max_rows: int, reducer=None, decode_splits: int = 8,
                  decode_fp4: bool = True, act_terms: int = 3, attn_tc: bool = True,
-                 decode_rows: Optional[int] = None):
+                 decode_rows: Optional[int] = None, fuse_ar: bool = True):
         self.m, self.kv, self.max_rows, self.reducer = model, kv, max_rows, reducer
         # decode rows (<= 64) run the linears on the block-scaled FP4 tensor-core path with the activations
         # expanded into `act_terms` residual NVFP4 terms; attention reads the FP8 cache through tcgen05
         self.decode_fp4 = decode_fp4 and model.cfg.weight_fmt == "nvfp4"
         self.act_terms = act_terms
+        self.chunk = None
+        # fused GEMM -> all-reduce (peer-memory push in the GEMM epilogue, fold in the next norm kernel)
+        self.fuse_ar = fuse_ar and reducer is not None and getattr(reducer, "comm", None) is not None and \
+            model.cfg.hidden % 128 == 0 and model.cfg.hidden // 128 <= 64
         self.attn_tc = attn_tc and model.cfg.kv_fp8 and model.cfg.head_dim == 128 and \
             (model.cfg.q_heads // model.cfg.kv_heads) in (1, 2, 4, 5, 8)
         c = model.cfg
@@ -66,45 +70,65 @@ class DenseRunner:
             return ops.gemm_fp4(xa, w, out=out)
         return ops.linear(x, w, out=out)
 
-    def _layer_fp4(self, L, cache, x, delta, have_delta, qkv, attn, gu, positions, row_req, rows, splits):
+    def _layer_fp4(self, L, cache, x, delta, have_delta, qkv, attn, gu, positions, row_req, rows, splits,
+                   pending_fold=False, last=False):
         """One decoder layer on the block-scaled FP4 path: every linear consumes NVFP4 residual terms written by
         the kernel that produces its input (add + RMSNorm, attention output, SwiGLU)."""
         m, c = self.m, self.m.cfg
         H = c.hidden
-        xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta if have_delta else None,
-                                 norm_w=L.in_norm, eps=c.eps)
+        if pending_fold:
+            xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", norm_w=L.in_norm, eps=c.eps,
+                                     fold_comm=self.reducer.comm)
+        else:
+            xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta if have_delta else None,
+                                     norm_w=L.in_norm, eps=c.eps)
         ops.gemm_fp4(xa, L.qkv, out=qkv)
         ops.rope_kv_write(qkv, positions, row_req, self.kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
                           rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm, eps=c.eps)
         self.attention(qkv, cache, row_req, positions, rows, splits, attn)
         xa = ops.act_quant_nvfp4(attn, out=self.qa[self.hq * self.d], mode="plain")
-        ops.gemm_fp4(xa, L.o, out=delta)
-        if self.reducer is not None:
-            self.reducer.all_reduce(delta)
-        xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta, norm_w=L.post_norm, eps=c.eps)
+        # tensor parallel, peer memory: the GEMM epilogue pushes its tiles to every rank and the next
+        # add + RMSNorm + quantise kernel folds them (no separate all-reduce launch)
+        fuse = getattr(self.reducer, "comm", None) if self.fuse_ar else None
+        if fuse:
+            ops.gemm_fp4(xa, L.o, push_comm=fuse)
+            xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", norm_w=L.post_norm, eps=c.eps, fold_comm=fuse)
+        else:
+            ops.gemm_fp4(xa, L.o, out=delta)
+            if self.reducer is not None:
+                self.reducer.all_reduce(delta)
+            xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta, norm_w=L.post_norm, eps=c.eps)
         ops.gemm_fp4(xa, L.gate_up, out=gu)
         xa = ops.act_quant_nvfp4(gu, out=self.qa[gu.shape[1] // 2], mode="swiglu")
+        if fuse and not last:
+            ops.gemm_fp4(xa, L.down, push_comm=fuse)
+            return True            # the next layer's first kernel folds the pushed tiles
         ops.gemm_fp4(xa, L.down, out=delta)
         if self.reducer is not None:
             self.reducer.all_reduce(delta)
+        return False
 
     # ------------------------------------------------------------------
     def forward(self, rows: int, tokens, positions, row_req, logits_rows: Optional[slice] = None,
-                decode: bool = False, pick: bool = True):
+                decode: bool = False, pick: bool = True, chunk: Optional[tuple] = None):
         """Run `rows` rows through the model.  tokens/positions/row_req: int32 device tensors [rows].
         Logits (fp32, this rank's vocab slice) are produced for `logits_rows` (default: all rows when
         decode, else only the last row) and the greedy pick of those rows lands in self.pick_id."""
         m, c, kv = self.m, self.m.cfg, self.kv
+        # chunk = (slot, first position): all rows are consecutive positions of ONE request -> flash-attention prefill
+        self.chunk = None if decode else chunk
         x, xn, delta = self.x[:rows], self.xn[:rows], self.delta[:rows]
         qkv, attn, gu, act = self.qkv[:rows], self.attn[:rows], self.gu[:rows], self.act[:rows]
         ops.embed_gather(tokens, m.embed, out=x)
         have_delta = False
+        pending = False
         splits = self.decode_splits if (decode and rows <= 256) else 1
         fp4 = self.decode_fp4 and decode and rows <= self.fp4_rows and all(
             w.k % 256 == 0 for w in (m.layers[0].qkv, m.layers[0].o, m.layers[0].down))
         for li, L in enumerate(m.layers):
             if fp4:
-                self._layer_fp4(L, kv.layers[li], x, delta, have_delta, qkv, attn, gu, positions, row_req, rows, splits)
+                pending = self._layer_fp4(L, kv.layers[li], x, delta, have_delta, qkv, attn, gu, positions, row_req,
+                                          rows, splits, pending_fold=pending, last=li == len(m.layers) - 1)
                 have_delta = True
                 continue
             ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have_delta else None, out=xn)
@@ -141,7 +165,11 @@ class DenseRunner:
 
     def attention(self, qkv, cache, row_req, positions, rows, splits, out):
         """Attention of `rows` query rows against the paged cache (their own K/V already appended)."""
-        if self.attn_tc:
+        if self.chunk is not None and self.attn_tc and self.d == 128 and cache.fp8:
+            slot, pos0 = self.chunk
+            ops.attn_prefill_tc(qkv, qkv.stride(0), cache, self.kv.block_table[slot], pos0, self.hq, self.hkv, self.d,
+                                self.scale, out=out, rows=rows)
+        elif self.attn_tc:
             ops.attn_decode_tc(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, self.hq, self.hkv,
                                self.d, self.scale, splits=splits,
                                scratch=(self.att_ml, self.att_acc) if splits > 1 else None, out=out)

@@ -180,9 +180,11 @@ class QuantAct:
 
 def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = None, bn: Optional[int] = None,
                     mode: str = "plain", delta=None, norm_w=None, resid_out=None, x_out=None, eps: float = 1e-6,
-                    limit: float = 0.0, one_plus_w: bool = False) -> QuantAct:
+                    limit: float = 0.0, one_plus_w: bool = False, fold_comm=None) -> QuantAct:
     """Quantise rows to residual NVFP4 terms, optionally fused with the producing operator:
-    mode "plain": x [T, K];  "swiglu": x = [gate | up] [T, 2K];  "rmsnorm": x = residual [T, K] (+ delta), norm_w."""
+    mode "plain": x [T, K];  "swiglu": x = [gate | up] [T, 2K];  "rmsnorm": x = residual [T, K] (+ delta), norm_w.
+    fold_comm (rmsnorm mode): native peer-communicator handle; the delta is then the fixed-order fold of the tiles
+    the tensor-parallel GEMMs pushed into this rank's symmetric region (see gemm_fp4 push_comm)."""
     _chk(x, torch.bfloat16, "x")
     rows = x.shape[0]
     k = x.shape[1] // 2 if mode == "swiglu" else x.shape[1]
@@ -192,14 +194,15 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
     out.rows = rows
     assert rows <= out.rows_pad and out.k == k
     m = {"plain": 0, "swiglu": 1, "rmsnorm": 2}[mode]
-    if m == 2 and delta is not None and resid_out is None:
+    if m == 2 and (delta is not None or fold_comm) and resid_out is None:
         resid_out = x
     cl = next((c for c in (8, 4, 2, 1) if k % c == 0 and (k // c) % 16 == 0 and (k // c) * 2 <= 48 * 1024), 0)
     if cl:
         call("dgpp_act_quant_nvfp4_cluster", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out),
              ptr(x_out), ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, cl,
-             float(eps), float(limit), int(one_plus_w), stream_ptr())
+             float(eps), float(limit), int(one_plus_w), fold_comm, stream_ptr())
     else:
+        assert not fold_comm, "the all-reduce fold needs the cluster quantiser"
         call("dgpp_act_quant_nvfp4", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out), ptr(x_out),
              ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, float(eps),
              float(limit), int(one_plus_w), stream_ptr())
@@ -208,14 +211,16 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
 
 def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
              out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
-             splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None) -> torch.Tensor:
-    """Block-scaled NVFP4 tensor-core linear on pre-quantised activations (token tile = xa.bn)."""
+             splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, push_comm=None) -> torch.Tensor:
+    """Block-scaled NVFP4 tensor-core linear on pre-quantised activations (token tile = xa.bn).
+    push_comm: native peer-communicator handle; the finished bf16 tiles are then stored into every rank's
+    symmetric region (with per-tile flags) instead of `out` -- the first half of a fused all-reduce."""
     assert w.fmt == "nvfp4" and xa.k == w.k
     rows, bn = xa.rows, xa.bn
     dev = xa.q.device
-    if out is None and out32 is None:
+    if out is None and out32 is None and not push_comm:
         out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=dev)
-    ldc = (out if out is not None else out32).stride(0)
+    ldc = w.n if push_comm and out is None and out32 is None else (out if out is not None else out32).stride(0)
     if splits is None:
         splits = pick_splits_fp4(rows, w.n, w.k, bn)
     wsp = cnt = None
@@ -227,7 +232,7 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
             wsp, cnt = ws.partials, ws.counters
     call("dgpp_gemm_fp4", bn, ptr(xa.q), ptr(xa.sf), ptr(xa.g), xa.terms, xa.rows_pad, ptr(w.payload),
          ptr(w.tiled_scales()), float(w.alpha), ptr(out), ptr(out32), ptr(resid), ldc, rows, w.n, w.k, splits,
-         ptr(wsp), ptr(cnt), stream_ptr())
+         ptr(wsp), ptr(cnt), push_comm, stream_ptr())
     return out if out is not None else out32
 
 
