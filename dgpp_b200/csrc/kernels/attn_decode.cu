@@ -279,3 +279,55 @@ DGPP_API int dgpp_attn_decode(const void* q, int64_t q_stride, const void* k_cac
   dgpp_set_error("attn_decode: unsupported head_dim %d / group %d", d, g);
   return -1;
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// Fixed-scratch variant: see attn_decode_static.h for the contract (no allocation, 4 MiB device array).
+#include "kernels/attn_decode_static.h"
+
+namespace dgpp {
+
+constexpr size_t kAttnStaticScratchFloats = DGPP_ATTN_STATIC_SCRATCH_FLOATS;
+static __device__ __align__(256) float g_attn_static_scratch[kAttnStaticScratchFloats];
+
+// Address of the array on the current device; resolved once per device (first call: before any stream capture).
+static float* attn_static_scratch_ptr() {
+  static float* cache[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    dgpp_set_error("attn_decode_static: cudaGetDevice failed or device %d out of range: %s", dev, cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (!cache[dev]) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_attn_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      dgpp_set_error("attn_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cache[dev] = ptr;
+  }
+  return cache[dev];
+}
+
+}  // namespace dgpp
+
+int dgpp_attn_decode_static(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                            const void* k_scale, const void* v_scale, const void* block_table, const void* row_req,
+                            const void* positions, void* out, int rows, int hq, int hkv, int d, int page,
+                            int max_blocks, int splits, int kv_fp8, float scale, int window, cudaStream_t st) {
+  DGPP_REQUIRE(rows >= 0 && hq > 0 && d > 0 && splits >= 1, "attn_decode_static: bad sizes rows %d hq %d d %d splits %d",
+               rows, hq, d, splits);
+  const size_t parts = static_cast<size_t>(rows) * hq * splits;
+  const size_t ml_floats = (parts * 2 + 63) & ~static_cast<size_t>(63);      // keeps the second region 256-byte aligned
+  const size_t need = splits > 1 ? ml_floats + parts * d : 0;
+  DGPP_REQUIRE(need <= kAttnStaticScratchFloats,
+               "attn_decode_static: rows %d x heads %d x splits %d x head_dim %d needs %zu scratch floats, the fixed "
+               "array holds %zu; use fewer splits or rows, or dgpp_attn_decode with caller-owned scratch",
+               rows, hq, splits, d, need, static_cast<size_t>(kAttnStaticScratchFloats));
+  float* ptr = attn_static_scratch_ptr();
+  if (ptr == nullptr) return -1;
+  return dgpp_attn_decode(q, q_stride, k_cache, v_cache, k_scale, v_scale, block_table, row_req, positions,
+                          splits > 1 ? ptr : nullptr, splits > 1 ? ptr + ml_floats : nullptr, out, rows, hq, hkv, d,
+                          page, max_blocks, splits, kv_fp8, scale, window, st);
+}
