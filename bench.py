@@ -84,6 +84,8 @@ def main():
     ap.add_argument("--reducer", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--prefill-lens", default="", help="comma list of cold-prefill lengths to time as extras")
     ap.add_argument("--also-c1", action="store_true", help="also time C=1 decode as an extra")
+    ap.add_argument("--no-fuse-ar", action="store_true",
+                    help="tensor parallel: separate all-reduce kernels instead of the GEMM-epilogue push + fold")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -123,7 +125,8 @@ def main():
     C, L, K, W = args.concurrency, args.prompt_len, args.steps, args.warmup
     prefill_lens = [int(x) for x in args.prefill_lens.split(",") if x]
     max_len = max([L + K + W + 8] + [p + 8 for p in prefill_lens])
-    eng = LLMEngine(model, max_batch=C, max_seq_len=max_len, prefill_chunk=2048, reducer=reducer)
+    eng = LLMEngine(model, max_batch=C, max_seq_len=max_len, prefill_chunk=2048, reducer=reducer,
+                    fuse_ar=not args.no_fuse_ar)
 
     g = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab, (L,), generator=g).tolist() for _ in range(C)]

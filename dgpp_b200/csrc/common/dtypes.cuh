@@ -16,13 +16,12 @@ __device__ __forceinline__ bf16 f32_to_bf16(float v) { return __float2bfloat16_r
 
 // e4m3 byte -> float (exact).
 __device__ __forceinline__ float e4m3_to_f32(uint8_t v) {
-  __half_raw h = __nv_cvt_fp8_to_halfraw(v, __NV_E4M3);
-  return __half2float(*reinterpret_cast<__half*>(&h));
+  const __half h(__nv_cvt_fp8_to_halfraw(v, __NV_E4M3));   // converting constructor: no pointer punning
+  return __half2float(h);
 }
 // two e4m3 bytes (low byte first) -> half2 (exact).
 __device__ __forceinline__ __half2 e4m3x2_to_h2(uint16_t v) {
-  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(v, __NV_E4M3);
-  return *reinterpret_cast<__half2*>(&h);
+  return __half2(__nv_cvt_fp8x2_to_halfraw2(v, __NV_E4M3));
 }
 // float -> e4m3 byte, round-to-nearest-even, saturating to +-448.
 __device__ __forceinline__ uint8_t f32_to_e4m3(float v) {
@@ -44,7 +43,10 @@ __device__ __forceinline__ __half2 e2m1x2_to_h2(uint8_t b) {
       "cvt.rn.f16x2.e2m1x2 %0, lo;\n\t}\n"
       : "=r"(out)
       : "h"(in));
-  return *reinterpret_cast<__half2*>(&out);
+  __half2_raw r;
+  r.x = static_cast<unsigned short>(out & 0xffffu);
+  r.y = static_cast<unsigned short>(out >> 16);
+  return __half2(r);
 }
 // Software decode of one e2m1 code (sign, 2-bit exponent, 1-bit mantissa).
 __host__ __device__ __forceinline__ float e2m1_to_f32(uint32_t c) {
@@ -93,15 +95,12 @@ __device__ __forceinline__ void e2m1x8_residual(uint32_t codes, float s, float* 
 }
 
 // Two floats -> two e4m3 terms each (value + residual), packed: a = {e4m3(x0), e4m3(x1)} (x0 in the low byte),
-// b = e4m3 of what a left.  The residual is formed in f16x2: x rounded to f16 (11 bits) minus a 4-bit value is
-// exact, so the pair keeps ~2^-8 relative error.  Five conversions / subtractions per PAIR of elements.
+// b = e4m3 of what a left (residual formed in fp32), so the pair keeps ~2^-8 relative error.
 __device__ __forceinline__ void f32x2_to_e4m3x2_two_term(float x0, float x1, uint16_t& a, uint16_t& b) {
-  uint32_t xh, ah, rh;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(a) : "f"(x0), "f"(x1));
-  asm("cvt.rn.f16x2.f32 %0, %2, %1;" : "=r"(xh) : "f"(x0), "f"(x1));
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(ah) : "h"(a));
-  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(rh) : "r"(xh), "r"(ah));
-  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(b) : "r"(rh));
+  const __nv_fp8x2_storage_t a2 = __nv_cvt_float2_to_fp8x2(make_float2(x0, x1), __NV_SATFINITE, __NV_E4M3);
+  const float2 af = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(a2, __NV_E4M3)));
+  a = a2;
+  b = __nv_cvt_float2_to_fp8x2(make_float2(x0 - af.x, x1 - af.y), __NV_SATFINITE, __NV_E4M3);
 }
 // 2^x, one MUFU; flushes denormals, ex2(-inf) = 0.
 __device__ __forceinline__ float fast_exp2(float x) {

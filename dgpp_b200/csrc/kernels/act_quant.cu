@@ -44,6 +44,10 @@ struct ClusterQuantArgs {
   // last CTA advances the collective epoch.
   int fold;
   CommState comm;
+  // Grouped rows (mixture-of-experts): row t belongs to slot t / bn; rows of inactive slots (group_list[slot] < 0)
+  // and rows t % bn >= group_rows are skipped.
+  const int32_t* group_list;
+  int group_rows;
 };
 
 __device__ __forceinline__ float warp_red(float v, bool is_max) {
@@ -64,6 +68,7 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
   cg::cluster_group cluster = cg::this_cluster();
   pdl_wait();
   const int c = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  if (a.group_list && (a.group_list[t / a.bn] < 0 || t % a.bn >= a.group_rows)) return;   // whole cluster leaves together
   const int cl = a.cl, K = a.K, kseg = K / cl, k0 = c * kseg, nvec = kseg / 8;
   auto cta_reduce = [&](float v, bool is_max) {
     v = warp_red(v, is_max);
@@ -251,7 +256,8 @@ using namespace dgpp;
 DGPP_API int dgpp_act_quant_nvfp4_cluster(int mode, const void* in, int64_t in_stride, const void* delta,
                                           const void* w, void* resid_out, void* x_out, void* q, void* sf, void* g,
                                           int T, int T_pad, int K, int R, int bn, int cl, float eps, float limit,
-                                          int one_plus_w, void* comm_fold, cudaStream_t st) {
+                                          int one_plus_w, void* comm_fold, const void* group_list, int group_rows,
+                                          cudaStream_t st) {
   DGPP_REQUIRE(K % 256 == 0, "act_quant: K %d must be a multiple of 256", K);
   DGPP_REQUIRE(cl == 1 || cl == 2 || cl == 4 || cl == 8, "act_quant: cluster size %d not in {1,2,4,8}", cl);
   DGPP_REQUIRE((K / cl) % 16 == 0 && K % cl == 0, "act_quant: K %d does not split over %d CTAs", K, cl);
@@ -272,6 +278,8 @@ DGPP_API int dgpp_act_quant_nvfp4_cluster(int mode, const void* in, int64_t in_s
   a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.cl = cl; a.eps = eps; a.limit = limit;
   a.one_plus_w = one_plus_w;
   a.status = device_status_ptr();
+  a.group_list = static_cast<const int32_t*>(group_list);
+  a.group_rows = group_rows;
   a.fold = 0;
   memset(&a.comm, 0, sizeof(a.comm));
   if (comm_fold) {

@@ -184,8 +184,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     for (int c = 0; c < D / 16; ++c) {
       Pack16 a, b;
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        f32x2_to_e4m3x2_two_term(v[c * 16 + 2 * j] * inv, v[c * 16 + 2 * j + 1] * inv, a.s[j], b.s[j]);
+      for (int j = 0; j < 16; ++j) {   // signed values: the residual is formed in fp32 (once per CTA, not per tile)
+        const float x = v[c * 16 + j] * inv;
+        a.b[j] = f32_to_e4m3(x);
+        b.b[j] = f32_to_e4m3(x - e4m3_to_f32(a.b[j]));
+      }
       *reinterpret_cast<uint4*>(sQ + sw128_off(r, c * 16)) = a.u;
       *reinterpret_cast<uint4*>(sQ + kTileBytes + sw128_off(r, c * 16)) = b.u;
     }
@@ -302,7 +305,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       const float c_tile = vmax > 0.f ? 256.f / vmax : 0.f;
       // pass 1: row maximum of the scaled, masked scores (the scores are re-read from TMEM in pass 2 instead of
       // being kept in 128 registers next to the 128 output accumulators)
-      const bool full = (t0 + kApTile - 1 <= my_pos) && (t0 >= my_first);
+      // warp-uniform choice: tcgen05.ld is .sync.aligned, every lane of the warp must take the same path
+      const bool full = __all_sync(0xffffffffu, (t0 + kApTile - 1 <= my_pos) && (t0 >= my_first)) != 0;
       const float mt = full ? tile_row_max<false>(tmem_s + b * 128 + lane_addr, ks, t0, my_pos, my_first)
                             : tile_row_max<true>(tmem_s + b * 128 + lane_addr, ks, t0, my_pos, my_first);
       const float mn = fmaxf(m_run, mt * sm);   // sm > 0: scaling commutes with the maximum
@@ -311,7 +315,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       float lsum = 0.f;
       // the previous tile's PV product must be folded in before P is overwritten
       if (i > 0) {
-        if (wait_bar(o_full, (i - 1) & 1)) {
+        if (__all_sync(0xffffffffu, wait_bar(o_full, (i - 1) & 1))) {
           tc_fence_after();
 #pragma unroll
           for (int c0 = 0; c0 < D; c0 += 16) {
@@ -340,7 +344,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       if (lane == 0) mbar_arrive(p_full);
     }
     if (ok && !*abort_flag && ntiles > 0) {
-      if (wait_bar(o_full, (ntiles - 1) & 1)) {
+      if (__all_sync(0xffffffffu, wait_bar(o_full, (ntiles - 1) & 1))) {
         tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 16) {

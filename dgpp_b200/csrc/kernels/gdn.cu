@@ -1,0 +1,236 @@
+// Gated DeltaNet linear attention: causal depthwise convolution, gated delta-rule recurrence, gated RMSNorm.
+//
+// Per head the state S is [dk, dv] fp32.  For token t with decay a_t = exp(g_t), write strength b_t, unit-norm
+// q_t, k_t (q also scaled by dk^-1/2) and value v_t:
+//     S   <- a_t * S
+//     u   =  b_t * (v_t - S^T k_t)          (what the memory does not already return for k_t)
+//     S   <- S + k_t u^T
+//     o_t =  S^T q_t
+// Every column S[:, j] evolves on its own, so a (request, head) is split over dv / 32 CTAs; a thread keeps
+// 16 rows of one column in registers for the whole token loop, 8 threads share a column (shuffle reductions in a
+// fixed order).  The same kernel serves decode (one token per request) and chunked prefill (a run of tokens of one
+// request, state carried in and out), so prefill and decode agree bit for bit.
+//     g_t = -exp(A_log[h]) * softplus(alpha_t + dt_bias[h]),  b_t = sigmoid(beta_t)
+// (reference counterparts: src/kernels/gdn_chunk.cu chunked scan, src/kernels/kda.cu recurrent step.)
+#include <math.h>
+
+#include "common/common.h"
+#include "common/dtypes.cuh"
+#include "common/ptx.cuh"
+
+namespace dgpp {
+
+constexpr int kGdnCols = 32;      // state columns per CTA
+constexpr int kGdnParts = 8;      // threads per column
+constexpr int kGdnThreads = kGdnCols * kGdnParts;
+
+struct GdnArgs {
+  const bf16* q;          // [T, hk * dk]   (after conv + SiLU)
+  const bf16* k;          // [T, hk * dk]
+  const bf16* v;          // [T, hv * dv]
+  int64_t q_stride, k_stride, v_stride;
+  const bf16* alpha;      // [T, hv] raw decay input
+  const bf16* beta;       // [T, hv] raw write-strength input
+  int64_t ab_stride;
+  const float* A_log;     // [hv]
+  const float* dt_bias;   // [hv]
+  float* state;           // [slots, hv, dk, dv] fp32
+  const int32_t* row_slot;   // [T] state slot of each row (decode) or null: all rows belong to `slot`
+  int slot;
+  bf16* out;              // [T, hv * dv]
+  int T, hk, hv, dk, dv;
+  int sequential;         // 1: rows are consecutive tokens of ONE request (prefill); 0: one token per request
+};
+
+template <int DK>
+__global__ void __launch_bounds__(kGdnThreads) gdn_recurrent_kernel(GdnArgs a) {
+  constexpr int PER = DK / kGdnParts;          // state rows per thread
+  __shared__ float qs[DK], ks[DK];
+  __shared__ float red[2][kGdnThreads / 32];
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const int col = tid / kGdnParts, part = tid % kGdnParts;
+  const int h = blockIdx.y, j = blockIdx.x * kGdnCols + col;
+  const int hk_idx = h / (a.hv / a.hk);        // value heads share key heads in groups
+  const float A = -expf(a.A_log[h]);
+  const float dtb = a.dt_bias[h];
+  const int first = a.sequential ? 0 : blockIdx.z;
+  const int last = a.sequential ? a.T : blockIdx.z + 1;
+  const int slot0 = a.row_slot ? a.row_slot[first] : a.slot;
+  float* sp = a.state + ((static_cast<size_t>(slot0) * a.hv + h) * DK) * a.dv + j;
+  float s[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) s[i] = sp[static_cast<size_t>(part * PER + i) * a.dv];
+  for (int t = first; t < last; ++t) {
+    // ---- unit-norm q, k of this token's key head (all threads cooperate, fixed reduction order)
+    float qv = 0.f, kv = 0.f;
+    if (tid < DK) {
+      qv = bf16_to_f32(a.q[static_cast<size_t>(t) * a.q_stride + hk_idx * DK + tid]);
+      kv = bf16_to_f32(a.k[static_cast<size_t>(t) * a.k_stride + hk_idx * DK + tid]);
+    }
+    float q2 = qv * qv, k2 = kv * kv;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      q2 += __shfl_xor_sync(0xffffffffu, q2, o);
+      k2 += __shfl_xor_sync(0xffffffffu, k2, o);
+    }
+    __syncthreads();     // previous token's readers of qs / ks / red are done
+    if ((tid & 31) == 0) { red[0][tid >> 5] = q2; red[1][tid >> 5] = k2; }
+    __syncthreads();
+    float qn = 0.f, kn = 0.f;
+#pragma unroll
+    for (int w = 0; w < DK / 32; ++w) { qn += red[0][w]; kn += red[1][w]; }
+    if (tid < DK) {
+      qs[tid] = qv * rsqrtf(qn + 1e-6f) * rsqrtf(static_cast<float>(DK));
+      ks[tid] = kv * rsqrtf(kn + 1e-6f);
+    }
+    __syncthreads();
+    const float al = bf16_to_f32(a.alpha[static_cast<size_t>(t) * a.ab_stride + h]) + dtb;
+    const float softplus = al > 20.f ? al : log1pf(expf(al));
+    const float decay = expf(A * softplus);
+    const float bt = 1.f / (1.f + expf(-bf16_to_f32(a.beta[static_cast<size_t>(t) * a.ab_stride + h])));
+    const float vt = bf16_to_f32(a.v[static_cast<size_t>(t) * a.v_stride + h * a.dv + j]);
+    // ---- S <- a S ; m = S^T k (this column)
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      s[i] *= decay;
+      m = fmaf(s[i], ks[part * PER + i], m);
+    }
+#pragma unroll
+    for (int o = kGdnParts / 2; o > 0; o >>= 1) m += __shfl_xor_sync(0xffffffffu, m, o);
+    const float u = bt * (vt - m);
+    float ov = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      s[i] = fmaf(ks[part * PER + i], u, s[i]);
+      ov = fmaf(s[i], qs[part * PER + i], ov);
+    }
+#pragma unroll
+    for (int o = kGdnParts / 2; o > 0; o >>= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
+    if (part == 0) a.out[static_cast<size_t>(t) * a.hv * a.dv + h * a.dv + j] = f32_to_bf16(ov);
+  }
+#pragma unroll
+  for (int i = 0; i < PER; ++i) sp[static_cast<size_t>(part * PER + i) * a.dv] = s[i];
+}
+
+// Causal depthwise convolution (kernel width W <= 4) + SiLU over channels, with the last W - 1 inputs of every
+// channel carried per state slot.  x: [T, C] bf16 rows; sequential = 1: consecutive tokens of one request.
+struct ConvArgs {
+  const bf16* x;
+  int64_t x_stride;
+  const bf16* w;        // [C, W]
+  const bf16* bias;     // [C] or null
+  float* state;         // [slots, W - 1, C] fp32 (oldest first)
+  const int32_t* row_slot;
+  int slot;
+  bf16* out;            // [T, C]
+  int T, C, W, sequential;
+};
+
+__global__ void __launch_bounds__(256) gdn_conv_kernel(ConvArgs a) {
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.C) return;
+  float wv[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i = 0; i < a.W; ++i) wv[i] = bf16_to_f32(a.w[c * a.W + i]);
+  const float b = a.bias ? bf16_to_f32(a.bias[c]) : 0.f;
+  const int first = a.sequential ? 0 : blockIdx.y, last = a.sequential ? a.T : blockIdx.y + 1;
+  const int slot = a.row_slot ? a.row_slot[first] : a.slot;
+  float* st = a.state + static_cast<size_t>(slot) * (a.W - 1) * a.C + c;
+  float hist[3] = {0.f, 0.f, 0.f};             // hist[W - 2] is the newest
+  for (int i = 0; i < a.W - 1; ++i) hist[i] = st[static_cast<size_t>(i) * a.C];
+  for (int t = first; t < last; ++t) {
+    const float xv = bf16_to_f32(a.x[static_cast<size_t>(t) * a.x_stride + c]);
+    float acc = b;
+    for (int i = 0; i < a.W - 1; ++i) acc = fmaf(wv[i], hist[i], acc);
+    acc = fmaf(wv[a.W - 1], xv, acc);
+    a.out[static_cast<size_t>(t) * a.C + c] = f32_to_bf16(acc / (1.f + expf(-acc)));
+    for (int i = 0; i + 1 < a.W - 1; ++i) hist[i] = hist[i + 1];
+    if (a.W > 1) hist[a.W - 2] = xv;
+  }
+  for (int i = 0; i < a.W - 1; ++i) st[static_cast<size_t>(i) * a.C] = hist[i];
+}
+
+// out[t, h, :] = rmsnorm(o[t, h, :]) * w * silu(z[t, h, :]); one warp per (row, head).
+__global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const bf16* __restrict__ o, const bf16* __restrict__ z,
+                                                            int64_t z_stride, const bf16* __restrict__ w,
+                                                            bf16* __restrict__ out, int rows, int heads, int d, float eps) {
+  pdl_wait();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows * heads) return;
+  const int t = warp / heads, h = warp % heads;
+  const bf16* op = o + (static_cast<size_t>(t) * heads + h) * d;
+  const bf16* zp = z + static_cast<size_t>(t) * z_stride + h * d;
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) { const float f = bf16_to_f32(op[i]); ss += f * f; }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  const float rstd = rsqrtf(ss / static_cast<float>(d) + eps);
+  for (int i = lane; i < d; i += 32) {
+    const float n = bf16_to_f32(f32_to_bf16(bf16_to_f32(op[i]) * rstd)) * bf16_to_f32(w[i]);
+    const float zv = bf16_to_f32(zp[i]);
+    out[(static_cast<size_t>(t) * heads + h) * d + i] = f32_to_bf16(n * (zv / (1.f + expf(-zv))));
+  }
+}
+
+}  // namespace dgpp
+
+using namespace dgpp;
+
+DGPP_API int dgpp_gdn_recurrent(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                int64_t v_stride, const void* alpha, const void* beta, int64_t ab_stride,
+                                const void* A_log, const void* dt_bias, void* state, const void* row_slot, int slot,
+                                void* out, int T, int hk, int hv, int dk, int dv, int sequential, cudaStream_t st) {
+  DGPP_REQUIRE(dk == 64 || dk == 128 || dk == 256, "gdn: key dim %d unsupported", dk);
+  DGPP_REQUIRE(dv % kGdnCols == 0 && hk > 0 && hv % hk == 0, "gdn: bad head geometry hk %d hv %d dv %d", hk, hv, dv);
+  DGPP_REQUIRE(sequential || row_slot, "gdn: batched single-token rows need row_slot");
+  if (T == 0) return 0;
+  GdnArgs a;
+  a.q = static_cast<const bf16*>(q); a.k = static_cast<const bf16*>(k); a.v = static_cast<const bf16*>(v);
+  a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
+  a.alpha = static_cast<const bf16*>(alpha); a.beta = static_cast<const bf16*>(beta); a.ab_stride = ab_stride;
+  a.A_log = static_cast<const float*>(A_log); a.dt_bias = static_cast<const float*>(dt_bias);
+  a.state = static_cast<float*>(state);
+  a.row_slot = static_cast<const int32_t*>(row_slot);
+  a.slot = slot;
+  a.out = static_cast<bf16*>(out);
+  a.T = T; a.hk = hk; a.hv = hv; a.dk = dk; a.dv = dv; a.sequential = sequential;
+  dim3 grid(dv / kGdnCols, hv, sequential ? 1 : T);
+  if (dk == 64) gdn_recurrent_kernel<64><<<grid, kGdnThreads, 0, st>>>(a);
+  else if (dk == 128) gdn_recurrent_kernel<128><<<grid, kGdnThreads, 0, st>>>(a);
+  else gdn_recurrent_kernel<256><<<grid, kGdnThreads, 0, st>>>(a);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+DGPP_API int dgpp_gdn_conv(const void* x, int64_t x_stride, const void* w, const void* bias, void* state,
+                           const void* row_slot, int slot, void* out, int T, int C, int W, int sequential,
+                           cudaStream_t st) {
+  DGPP_REQUIRE(W >= 1 && W <= 4, "gdn_conv: kernel width %d outside 1..4", W);
+  DGPP_REQUIRE(sequential || row_slot, "gdn_conv: batched single-token rows need row_slot");
+  if (T == 0) return 0;
+  ConvArgs a;
+  a.x = static_cast<const bf16*>(x); a.x_stride = x_stride;
+  a.w = static_cast<const bf16*>(w); a.bias = static_cast<const bf16*>(bias);
+  a.state = static_cast<float*>(state);
+  a.row_slot = static_cast<const int32_t*>(row_slot);
+  a.slot = slot;
+  a.out = static_cast<bf16*>(out);
+  a.T = T; a.C = C; a.W = W; a.sequential = sequential;
+  dim3 grid(dgpp_ceil_div(C, 256), sequential ? 1 : T);
+  gdn_conv_kernel<<<grid, 256, 0, st>>>(a);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+DGPP_API int dgpp_gated_rmsnorm(const void* o, const void* z, int64_t z_stride, const void* w, void* out, int rows,
+                                int heads, int d, float eps, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int warps = rows * heads;
+  gated_rmsnorm_kernel<<<dgpp_ceil_div(warps * 32, 256), 256, 0, st>>>(
+      static_cast<const bf16*>(o), static_cast<const bf16*>(z), z_stride, static_cast<const bf16*>(w),
+      static_cast<bf16*>(out), rows, heads, d, eps);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}

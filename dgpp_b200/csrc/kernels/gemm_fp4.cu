@@ -58,6 +58,15 @@ struct Fp4Params {
   // flag[parity][rank][n tile] = epoch there.  The consumer (fold + add + RMSNorm + quantise) waits on the flags.
   int push;
   CommState comm;
+  // Grouped mode (mixture-of-experts): the weight matrix is the experts' matrices stacked along N
+  // ([experts * N, K]); blockIdx.x = slot * group_tiles + n tile, group_list[slot] = expert id of the slot or -1
+  // (inactive slot: the CTA does nothing).  Outputs of slot s start at out + s * group_out_stride (elements);
+  // with group_b the activations / their scales / g are per slot as well (down projection), otherwise every
+  // slot multiplies the same token tile (gate / up projection).
+  const int32_t* group_list;
+  const float* group_alpha;    // per-expert tensor scale, replaces alpha
+  int group_tiles, group_b, grid_x;
+  int64_t group_out_stride;
 };
 
 // One bf16 of the finished output tile -> slot `rank` of every rank (destinations staggered by rank).
@@ -102,14 +111,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kF4BM;
   const int bn_tok = BN / p.R;             // tokens per tile
   const int m0 = blockIdx.y * bn_tok;
   const int split = blockIdx.z, splits = gridDim.z;
   const int total_stages = p.K / kF4StageK;
   const int st_begin = split * p.stages_per_split;
   const int st_end = min(total_stages, st_begin + p.stages_per_split);
-  const int nst = max(0, st_end - st_begin);
   const int R = 1;  // terms are stacked inside the single B tile
   // TMEM columns: accumulator, then double-buffered scale factors (4 columns per K=64 step and 128 rows)
   constexpr uint32_t kColD = BN < 32 ? 32 : BN;
@@ -141,12 +148,28 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   const uint32_t tmem_sfa = tmem_base + kColD;
   const uint32_t tmem_sfb = tmem_sfa + 2 * kColSfa;
   pdl_wait();
+  // tile of the (stacked) weight matrix, output / activation group
+  int tile_x = blockIdx.x, grp = 0;
+  bool active = true;
+  float alpha = p.alpha;
+  if (p.group_list) {
+    grp = blockIdx.x / p.group_tiles;
+    const int e = p.group_list[grp];
+    active = e >= 0;
+    tile_x = (active ? e : 0) * p.group_tiles + blockIdx.x % p.group_tiles;
+    if (active && p.group_alpha) alpha = p.group_alpha[e];
+  }
+  const int n0 = tile_x * kF4BM;
+  const int nst = active ? max(0, st_end - st_begin) : 0;
+  const int b_row0 = (p.group_b ? grp * p.R * p.T_pad : 0) + blockIdx.y * BN;
+  const size_t sfb_grp = p.group_b ? static_cast<size_t>(grp) * (p.T_pad / bn_tok) * total_stages * kSfbBytes : 0;
+  const float* gvec = p.g + (p.group_b ? grp * p.T_pad : 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer: weights, activations, scales
     if (elect_one()) {
       const int token_tiles = p.T_pad / bn_tok;
-      const uint8_t* sfa_tile = p.sfa + static_cast<size_t>(blockIdx.x) * total_stages * kSfaBytes;
+      const uint8_t* sfa_tile = p.sfa + static_cast<size_t>(tile_x) * total_stages * kSfaBytes;
       for (int i = 0; i < nst; ++i) {
         const int s = i % S;
         const int st = st_begin + i;
@@ -156,8 +179,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
         tma_load_2d(sA + s * kF4StageA, &tmA, xb, n0, &full[s]);
         bulk_load_1d(sSfa + s * kSfaBytes, sfa_tile + static_cast<size_t>(st) * kSfaBytes, kSfaBytes, &full[s]);
         for (int r = 0; r < R; ++r) {
-          tma_load_2d(sB + (s * RMAX + r) * kStageB, &tmB, xb, blockIdx.y * BN, &full[s]);
-          const uint8_t* sfb = p.sfb + ((static_cast<size_t>(r) * token_tiles + blockIdx.y) * total_stages + st) * kSfbBytes;
+          tma_load_2d(sB + (s * RMAX + r) * kStageB, &tmB, xb, b_row0, &full[s]);
+          const uint8_t* sfb = p.sfb + sfb_grp + ((static_cast<size_t>(r) * token_tiles + blockIdx.y) * total_stages + st) * kSfbBytes;
           bulk_load_1d(sSfb + (s * RMAX + r) * kSfbBytes, sfb, kSfbBytes, &full[s]);
         }
         if (*abort_flag) break;
@@ -203,12 +226,15 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
     const bool ok = nst > 0 ? wait_bar(acc_full, 0) : true;
     if (!ok) { report(p.status, kTimeoutAccum, 15); *abort_flag = 1; }
     tc_fence_after();
-    const int n = n0 + q * 32 + lane;
+    // n: output column (within the expert in grouped mode); n_ws: column in the split-K workspace
+    const int n = (p.group_list ? (blockIdx.x % p.group_tiles) * kF4BM : n0) + q * 32 + lane;
+    const int n_ws = blockIdx.x * kF4BM + q * 32 + lane, N_ws = p.group_list ? gridDim.x * kF4BM : p.N;
+    const size_t out_grp = p.group_list ? static_cast<size_t>(grp) * p.group_out_stride : 0;
     const int cols = min(bn_tok, p.T - m0);
     const uint32_t push_epoch = p.push ? *p.comm.epoch + 1 : 0u;
     const int push_parity = push_epoch & 1;
-    if (ok && !*abort_flag) {
-      float* wsp = splits > 1 ? p.ws + (static_cast<size_t>(split) * p.T + m0) * p.N : nullptr;
+    if (ok && !*abort_flag && active) {
+      float* wsp = splits > 1 ? p.ws + (static_cast<size_t>(split) * p.T + m0) * N_ws : nullptr;
 #pragma unroll 1
       for (int c0 = 0; c0 < bn_tok; c0 += 16) {
         if (c0 >= cols) break;
@@ -230,10 +256,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
             const int m = c0 + j;
             if (m < cols) {
               if (splits > 1) {
-                wsp[static_cast<size_t>(m) * p.N + n] = v[j];
+                wsp[static_cast<size_t>(m) * N_ws + n_ws] = v[j];
               } else {
-                const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
-                float y = v[j] * p.alpha * p.g[m0 + m];
+                const size_t o = out_grp + static_cast<size_t>(m0 + m) * p.ldc + n;
+                float y = v[j] * alpha * gvec[m0 + m];
                 if (p.push) {
                   push_value(p, push_parity, static_cast<size_t>(m0 + m) * p.N + n, f32_to_bf16(y));
                   continue;
@@ -250,7 +276,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
       }
     }
     if (p.push && splits == 1) push_flags(p, push_parity, push_epoch, warp, lane);
-    if (splits > 1) {
+    if (splits > 1 && active) {
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (warp == 2 && lane == 0) {
@@ -264,9 +290,9 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
           for (int m = 0; m < cols; ++m) {
             float acc = 0.f;
             for (int s2 = 0; s2 < splits; ++s2)
-              acc += __ldcg(p.ws + (static_cast<size_t>(s2) * p.T + m0 + m) * p.N + n);
-            const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
-            float y = acc * p.alpha * p.g[m0 + m];
+              acc += __ldcg(p.ws + (static_cast<size_t>(s2) * p.T + m0 + m) * N_ws + n_ws);
+            const size_t o = out_grp + static_cast<size_t>(m0 + m) * p.ldc + n;
+            float y = acc * alpha * gvec[m0 + m];
             if (p.push) {
               push_value(p, push_parity, static_cast<size_t>(m0 + m) * p.N + n, f32_to_bf16(y));
               continue;
@@ -459,7 +485,7 @@ static int launch_fp4(const CUtensorMap& tA, const CUtensorMap& tB, const Fp4Par
     attr = true;
   }
   const int bn_tok = BN / p.R;
-  dim3 grid(dgpp_ceil_div(p.N, kF4BM), dgpp_ceil_div(p.T, bn_tok), splits);
+  dim3 grid(p.grid_x > 0 ? p.grid_x : dgpp_ceil_div(p.N, kF4BM), dgpp_ceil_div(p.T, bn_tok), splits);
   kern<<<grid, kF4Threads, smem, st>>>(tA, tB, p);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
@@ -532,6 +558,7 @@ DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* 
   p.status = device_status_ptr();
   p.T = T; p.T_pad = T_pad; p.N = N; p.K = K; p.ldc = ldc; p.R = R;
   p.push = 0;
+  p.group_list = nullptr; p.group_alpha = nullptr; p.group_tiles = 0; p.group_b = 0; p.grid_x = 0; p.group_out_stride = 0;
   memset(&p.comm, 0, sizeof(p.comm));
   if (comm_push) {
     const DgppComm* c = static_cast<const DgppComm*>(comm_push);
@@ -565,5 +592,66 @@ DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* 
     case 256: return launch_fp4<256>(tA, tB, p, splits, st);
   }
   dgpp_set_error("gemm_fp4: unsupported bn %d", bn);
+  return -1;
+}
+
+// Grouped (mixture-of-experts) form: wq / wsf_tiled hold `experts` matrices of [N, K] stacked along N; slot s of
+// group_list (device, int32, `slots` entries, -1 = unused) names the expert whose matrix multiplies
+//   group_b = 0: the one shared token tile xq (gate / up projection of every active expert)
+//   group_b = 1: the slot's own token tile, xq rows [s * R * T_pad, (s + 1) * R * T_pad) (down projection)
+// and writes out + s * group_out_stride + t * ldc + n.  T <= bn (one token tile per group); T_pad = bn.
+DGPP_API int dgpp_gemm_fp4_grouped(int bn, const void* xq, const void* xsf, const void* g, int R, const void* wq,
+                                   const void* wsf_tiled, const void* group_alpha, void* out, int ldc,
+                                   int64_t group_out_stride, int T, int N, int K, int experts, int slots,
+                                   const void* group_list, int group_b, int splits, void* ws, void* counters,
+                                   cudaStream_t st) {
+  DGPP_REQUIRE(K % 256 == 0 && N % 128 == 0, "gemm_fp4_grouped: K %d %% 256 and N %d %% 128 must be 0", K, N);
+  DGPP_REQUIRE(R >= 1 && R <= 4 && T >= 1 && T <= bn, "gemm_fp4_grouped: %d rows / %d terms do not fit one token tile of %d", T, R, bn);
+  DGPP_REQUIRE(experts >= 1 && slots >= 1 && group_list && out, "gemm_fp4_grouped: bad group arguments");
+  DGPP_REQUIRE(splits >= 1 && (splits == 1 || (ws && counters)), "gemm_fp4_grouped: split-K needs workspace and counters");
+  const int bnn = bn * R;
+  DGPP_REQUIRE(bnn <= 256 && bnn % 16 == 0, "gemm_fp4_grouped: token tile %d x %d terms does not fit one MMA", bn, R);
+  Fp4Params p;
+  p.alpha = 1.f;
+  p.g = static_cast<const float*>(g);
+  p.sfa = static_cast<const uint8_t*>(wsf_tiled);
+  p.sfb = static_cast<const uint8_t*>(xsf);
+  p.out = static_cast<bf16*>(out);
+  p.out32 = nullptr;
+  p.resid = nullptr;
+  p.ws = static_cast<float*>(ws);
+  p.counters = static_cast<uint32_t*>(counters);
+  p.status = device_status_ptr();
+  p.T = T; p.T_pad = bn; p.N = N; p.K = K; p.ldc = ldc; p.R = R;
+  p.push = 0;
+  memset(&p.comm, 0, sizeof(p.comm));
+  p.group_list = static_cast<const int32_t*>(group_list);
+  p.group_alpha = static_cast<const float*>(group_alpha);
+  p.group_tiles = N / 128;
+  p.group_b = group_b;
+  p.grid_x = slots * p.group_tiles;
+  p.group_out_stride = group_out_stride;
+  const int stages = K / 256;
+  const int per = dgpp_ceil_div(stages, splits);
+  p.stages_per_split = per;
+  splits = dgpp_ceil_div(stages, per);
+  CUtensorMap tA, tB;
+  if (make_tmap_2d(&tA, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, static_cast<uint64_t>(experts) * N, K / 2, 128,
+                   kF4BM, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -1;
+  const uint64_t b_rows = static_cast<uint64_t>(R) * bn * (group_b ? slots : 1);
+  if (make_tmap_2d(&tB, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, b_rows, K / 2, 128, bnn, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -1;
+  switch (bnn) {
+    case 16: return launch_fp4<16>(tA, tB, p, splits, st);
+    case 32: return launch_fp4<32>(tA, tB, p, splits, st);
+    case 48: return launch_fp4<48>(tA, tB, p, splits, st);
+    case 64: return launch_fp4<64>(tA, tB, p, splits, st);
+    case 96: return launch_fp4<96>(tA, tB, p, splits, st);
+    case 128: return launch_fp4<128>(tA, tB, p, splits, st);
+    case 192: return launch_fp4<192>(tA, tB, p, splits, st);
+    case 256: return launch_fp4<256>(tA, tB, p, splits, st);
+  }
+  dgpp_set_error("gemm_fp4_grouped: unsupported bn %d", bn);
   return -1;
 }

@@ -12,6 +12,7 @@ using namespace dgpp;
 
 void bind_text(py::module_& m);     // tokenizer, chat template (bindings_text.cpp)
 void bind_load(py::module_& m);     // safetensors, hub cache, architecture detect, shard specs (bindings_load.cpp)
+void bind_grammar(py::module_& m);  // JSON / schema constrained decoding (bindings_grammar.cpp)
 void bind_serve(py::module_& m);    // sampler oracle, grammars, http server (bindings_serve.cpp)
 
 namespace {
@@ -46,6 +47,7 @@ class PyEngine : public SchedulerEngine {
   void retain_block(int32_t b) override { PYBIND11_OVERRIDE_PURE(void, SchedulerEngine, retain_block, b); }
   void release_block(int32_t b) override { PYBIND11_OVERRIDE_PURE(void, SchedulerEngine, release_block, b); }
   int block_refcount(int32_t b) const override { PYBIND11_OVERRIDE_PURE(int, SchedulerEngine, block_refcount, b); }
+  void open(int slot, const std::string& id) override { PYBIND11_OVERRIDE(void, SchedulerEngine, open, slot, id); }
   void close(int slot) override { PYBIND11_OVERRIDE_PURE(void, SchedulerEngine, close, slot); }
 };
 
@@ -176,4 +178,5 @@ void bind_more(py::module_& m) {
   bind_text(m);
   bind_serve(m);
   bind_load(m);
+  bind_grammar(m);
 }

@@ -82,7 +82,8 @@ void bind_serve(py::module_& m) {
   m.def("sample_reference",
         [](const std::vector<float>& logits, float temperature, int top_k, float top_p, float min_p, float rep, float pres,
            float freq, uint64_t seed, int top_logprobs, const std::map<int32_t, float>& bias,
-           const std::map<int32_t, int>& counts, uint64_t position, py::object allowed) {
+           const std::map<int32_t, int>& counts, uint64_t position, py::object allowed, int candidates,
+           bool return_width) -> py::object {
           sample::Params p;
           p.temperature = temperature; p.top_k = top_k; p.top_p = top_p; p.min_p = min_p;
           p.repetition_penalty = rep; p.presence_penalty = pres; p.frequency_penalty = freq;
@@ -90,14 +91,16 @@ void bind_serve(py::module_& m) {
           std::vector<uint8_t> mask;
           const std::vector<uint8_t>* mp = nullptr;
           if (!allowed.is_none()) { mask = allowed.cast<std::vector<uint8_t>>(); mp = &mask; }
-          const sample::Result r = sample::sample(logits, p, counts, position, mp);
+          const sample::Result r = sample::sample(logits, p, counts, position, mp, candidates);
+          if (return_width) return py::make_tuple(r.token, r.logprob, r.top, r.candidates_used);
           return py::make_tuple(r.token, r.logprob, r.top);
         },
         py::arg("logits"), py::arg("temperature") = 0.f, py::arg("top_k") = 0, py::arg("top_p") = 1.f,
         py::arg("min_p") = 0.f, py::arg("repetition_penalty") = 1.f, py::arg("presence_penalty") = 0.f,
         py::arg("frequency_penalty") = 0.f, py::arg("seed") = 0, py::arg("top_logprobs") = 0,
         py::arg("logit_bias") = std::map<int32_t, float>{}, py::arg("counts") = std::map<int32_t, int>{},
-        py::arg("position") = 0, py::arg("allowed") = py::none());
+        py::arg("position") = 0, py::arg("allowed") = py::none(), py::arg("candidates") = 128,
+        py::arg("return_width") = false);
 
   // ---------------- OpenAI layer
   static py::exception<ApiErrorPy> api_error(m, "ApiError");

@@ -6,10 +6,11 @@
 //      seen tokens), presence (subtract once), frequency (subtract count times)
 //   2. logit_bias, then the grammar mask (disallowed ids -> -inf)
 //   3. temperature == 0 (or top_p == 0): greedy, ties to the lowest token id
-//   4. logits / temperature; candidates ordered by (value descending, id ascending); top_k keeps the first k
-//   5. softmax over the candidates with det::exp, summed in candidate order
-//   6. min_p keeps p >= min_p * p_max; top_p keeps the shortest prefix whose mass reaches top_p * total
-//   7. draw u = uniform01(seed, position) and walk the renormalised prefix
+//   4. z = logits / temperature; row-wide (max, sum exp) over fixed 256-wide chunks folded pairwise
+//   5. candidates = a prefix of the canonical order (value descending, id ascending), 128 wide at first
+//   6. top_k / min_p / top_p / draw on that prefix (common/sampler_core.h); when the prefix cannot resolve the
+//      draw it is widened: 1,024 -> 8,192 -> 65,536 -> the whole vocabulary
+//   7. u = uniform01(seed, position)
 // Log-probabilities describe the filtered, renormalised distribution when temperature > 0 and the raw
 // distribution when temperature == 0.
 // Sharded vocabularies: each rank reports its top candidates and a slice log-sum-exp computed over fixed
@@ -25,6 +26,7 @@
 #include <vector>
 
 #include "common/det_math.h"
+#include "common/sampler_core.h"
 
 namespace dgpp {
 namespace sample {
@@ -46,6 +48,7 @@ struct Result {
   int32_t token = -1;
   float logprob = 0.f;
   std::vector<std::pair<int32_t, float>> top;  // (token, logprob), best first
+  int candidates_used = 0;                     // width of the candidate prefix that resolved the draw
 };
 
 constexpr int kLseChunk = 256;
@@ -118,7 +121,7 @@ inline int32_t argmax_lowest(const std::vector<float>& l) {
 }
 
 inline Result sample(const std::vector<float>& logits, const Params& p, const std::map<int32_t, int>& counts,
-                     uint64_t position, const std::vector<uint8_t>* allowed = nullptr) {
+                     uint64_t position, const std::vector<uint8_t>* allowed = nullptr, int candidates = 128) {
   std::vector<float> l = logits;
   apply_penalties(l, p, counts, allowed);
   Result r;
@@ -144,61 +147,48 @@ inline Result sample(const std::vector<float>& logits, const Params& p, const st
     return r;
   }
   const float inv_t = 1.f / p.temperature;
-  std::vector<std::pair<float, int32_t>> cand;
-  cand.reserve(l.size());
-  for (int32_t i = 0; i < static_cast<int32_t>(l.size()); ++i)
-    if (l[i] > -std::numeric_limits<float>::infinity()) cand.emplace_back(l[i] * inv_t, i);
+  std::vector<float> z(l.size());
+  int64_t n_total = 0;
+  for (size_t i = 0; i < l.size(); ++i) {
+    z[i] = l[i] > -std::numeric_limits<float>::infinity() ? l[i] * inv_t : l[i];
+    if (l[i] > -std::numeric_limits<float>::infinity()) ++n_total;
+  }
+  if (n_total == 0) { r.token = 0; return r; }
+  const auto ms = slice_max_sum(z.data(), static_cast<int64_t>(z.size()));
+  std::vector<std::pair<float, int32_t>> all;
+  all.reserve(static_cast<size_t>(n_total));
+  for (int32_t i = 0; i < static_cast<int32_t>(z.size()); ++i)
+    if (l[i] > -std::numeric_limits<float>::infinity()) all.emplace_back(z[i], i);
   auto order = [](const std::pair<float, int32_t>& a, const std::pair<float, int32_t>& b) {
     return a.first != b.first ? a.first > b.first : a.second < b.second;
   };
-  if (p.top_k > 0 && static_cast<size_t>(p.top_k) < cand.size()) {
-    std::partial_sort(cand.begin(), cand.begin() + p.top_k, cand.end(), order);
-    cand.resize(static_cast<size_t>(p.top_k));
-  } else {
-    std::sort(cand.begin(), cand.end(), order);
-  }
-  if (cand.empty()) { r.token = 0; return r; }
-  const float mx = cand[0].first;
-  std::vector<float> prob(cand.size());
-  float total = 0.f;
-  for (size_t i = 0; i < cand.size(); ++i) {
-    prob[i] = det::exp(cand[i].first - mx);
-    total = total + prob[i];
-  }
-  size_t keep = cand.size();
-  if (p.min_p > 0.f) {
-    const float thr = p.min_p * prob[0];
-    size_t k = 0;
-    while (k < keep && prob[k] >= thr) ++k;
-    keep = std::max<size_t>(k, 1);
-    total = 0.f;
-    for (size_t i = 0; i < keep; ++i) total = total + prob[i];
-  }
-  if (p.top_p < 1.f) {
-    const float want = p.top_p * total;
-    float cum = 0.f;
-    size_t k = 0;
-    while (k < keep) {
-      cum = cum + prob[k];
-      ++k;
-      if (cum >= want) break;
+  Filter f;
+  f.temperature = p.temperature; f.top_k = p.top_k; f.top_p = p.top_p; f.min_p = p.min_p;
+  const float u = det::uniform01(p.seed, position);
+  // candidate prefix, widened until the draw resolves (the device sampler stops at its first width and asks the
+  // host for the rest)
+  const int64_t widths[5] = {candidates, 1024, 8192, 65536, n_total};
+  size_t sorted = 0;
+  for (int64_t w : widths) {
+    const size_t c = static_cast<size_t>(std::min<int64_t>(std::max<int64_t>(w, 1), n_total));
+    if (c <= sorted && c < static_cast<size_t>(n_total)) continue;
+    if (c > sorted) {
+      std::partial_sort(all.begin(), all.begin() + c, all.end(), order);
+      sorted = c;
     }
-    keep = std::max<size_t>(k, 1);
-    total = 0.f;
-    for (size_t i = 0; i < keep; ++i) total = total + prob[i];
+    std::vector<float> pc(c);
+    for (size_t i = 0; i < c; ++i) pc[i] = det::exp(all[i].first - ms.first);
+    const Decision d = decide(pc.data(), static_cast<int>(c), n_total, ms.second, f, u);
+    if (!d.resolved) continue;
+    const float lse = ms.first + det::log(d.total);
+    r.token = all[d.pick].second;
+    r.logprob = all[d.pick].first - lse;
+    r.candidates_used = static_cast<int>(c);
+    all.resize(std::min<size_t>(c, static_cast<size_t>(d.keep)));
+    fill_top(all, lse);
+    return r;
   }
-  const float u = det::uniform01(p.seed, position) * total;
-  float cum = 0.f;
-  size_t pick = keep - 1;
-  for (size_t i = 0; i < keep; ++i) {
-    cum = cum + prob[i];
-    if (u < cum) { pick = i; break; }
-  }
-  const float lse = mx + det::log(total);
-  r.token = cand[pick].second;
-  r.logprob = cand[pick].first - lse;
-  cand.resize(keep);
-  fill_top(cand, lse);
+  r.token = all[0].second;  // unreachable: the full width always resolves
   return r;
 }
 

@@ -55,6 +55,9 @@ class SchedulerEngine {
   virtual void release_block(int32_t block) = 0;
   virtual int block_refcount(int32_t block) const = 0;
   // Drop the slot's blocks and state.
+  // Called once when request `id` is admitted into `slot`, before its first prefill chunk: the engine binds the
+  // request's sampling parameters, grammar and token-count row to the slot.
+  virtual void open(int slot, const std::string& id) { (void)slot; (void)id; }
   virtual void close(int slot) = 0;
 };
 
@@ -340,6 +343,7 @@ class Scheduler {
       fold("admit", cur.req.id, (static_cast<int64_t>(s) << 40) | hit.tokens);
       ++meters_.admitted;
       meters_.prefix_hit_tokens += hit.tokens;
+      eng_->open(s, cur.req.id);
       if (obs_) obs_->on_admit(cur.req.id, s, hit.tokens);
       queue_.pop_front();
     }

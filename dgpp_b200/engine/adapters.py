@@ -160,6 +160,10 @@ class KernelEngine(rt.SchedulerEngine):
         self.h_pos = torch.zeros(b, dtype=torch.int32).pin_memory()
         self.h_req = torch.zeros(b, dtype=torch.int32).pin_memory()
         self.h_out = torch.zeros(b, dtype=torch.int32).pin_memory()
+        self.by_id = {}
+        self.slot_cfg = [None] * b
+        self.last_logprobs = [None] * b
+        self.sampler = None
 
     def max_concurrent(self):
         return self.e.max_batch
@@ -199,12 +203,69 @@ class KernelEngine(rt.SchedulerEngine):
         self.kv.release(slot)
         self.filled[slot] = 0
         self.pending[slot] = None
+        self.slot_cfg[slot] = None
+
+    # ------------------------------------------------------------------ sampling / constraints
+    def configure(self, request_id: str, params=None, grammar=None, prompt_ids=None) -> None:
+        """Registers sampling parameters (``SamplingParams``), a token grammar (``rt.JsonGrammar``) and the prompt ids
+        (for the penalties' token counts) of a request before it is submitted to the scheduler."""
+        self.by_id[request_id] = (params, grammar, prompt_ids)
+
+    def open(self, slot, request_id):
+        cfg = self.by_id.pop(request_id, None)
+        self.slot_cfg[slot] = None
+        self.last_logprobs[slot] = None
+        if cfg is None or (cfg[0] is None and cfg[1] is None):
+            return
+        params, grammar, prompt_ids = cfg
+        if self.e.model.tp_size > 1:
+            raise RuntimeError("sampled / constrained decoding needs the full vocabulary on one rank (tp_size 1)")
+        from ..sampling.device import DeviceSampler, SamplingParams
+        if self.sampler is None:
+            self.sampler = DeviceSampler(self.e.model.cfg.vocab, self.e.max_batch, self.e.max_batch, self.e.dev)
+        self.sampler.reset_slot(slot)
+        params = params or SamplingParams()
+        if prompt_ids and (params.repetition_penalty != 1.0 or params.presence_penalty or params.frequency_penalty):
+            self.sampler.count(slot, prompt_ids)
+        self.slot_cfg[slot] = (params, grammar)
+
+    def _sample_rows(self, logits, slots):
+        """Device sampler over the rows of `slots` (rows of plain greedy slots keep the engine's own pick)."""
+        import numpy as np
+        from ..sampling.device import SamplingParams
+        rows = len(slots)
+        params, masks = [], None
+        for s in slots:
+            cfg = self.slot_cfg[s]
+            params.append(cfg[0] if cfg else SamplingParams())
+        if any(self.slot_cfg[s] and self.slot_cfg[s][1] is not None for s in slots):
+            words = (self.e.model.cfg.vocab + 31) // 32
+            m = np.full((rows, words), 0xFFFFFFFF, dtype=np.uint32)
+            for r, s in enumerate(slots):
+                cfg = self.slot_cfg[s]
+                if cfg and cfg[1] is not None:
+                    gm = cfg[1].mask()
+                    m[r, :] = 0
+                    m[r, :min(words, gm.shape[0])] = gm[:words]
+            masks = torch.from_numpy(m.view(np.int32)).to(self.e.dev)
+        picked = self.sampler.sample(logits, params, [s if self.slot_cfg[s] else -1 for s in slots],
+                                     [self.filled[s] for s in slots], masks=masks)
+        for r, s in enumerate(slots):
+            cfg = self.slot_cfg[s]
+            if cfg:
+                self.last_logprobs[s] = (picked[r].logprob, picked[r].top)
+                if cfg[1] is not None:
+                    cfg[1].accept(picked[r].token)
+        return [p.token for p in picked]
 
     def prefill(self, slot, tokens, pos, last):
         first = self.e.prefill(slot, list(tokens), start_pos=pos)
         self.filled[slot] = pos + len(tokens)
         if last:
-            tok = int(first.item())
+            if self.slot_cfg[slot]:
+                tok = self._sample_rows(self.e.runner.logits[:1], [slot])[0]
+            else:
+                tok = int(first.item())
             self.pending[slot] = tok
             return tok
         return -1
@@ -222,10 +283,14 @@ class KernelEngine(rt.SchedulerEngine):
         e.decode_step(b)
         self.h_out[:b].copy_(e.d_tokens[:b], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        for s in slots:
+            self.filled[s] += 1
+        toks = [int(self.h_out[i]) for i in range(b)]
+        if any(self.slot_cfg[s] for s in slots):
+            sampled = self._sample_rows(e.runner.logits[:b], slots)
+            toks = [sampled[i] if self.slot_cfg[s] else toks[i] for i, s in enumerate(slots)]
         out = []
         for i, s in enumerate(slots):
-            tok = int(self.h_out[i])
-            self.filled[s] += 1
-            self.pending[s] = tok
-            out.append([tok])
+            self.pending[s] = toks[i]
+            out.append([toks[i]])
         return out

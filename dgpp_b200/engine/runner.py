@@ -41,7 +41,7 @@ class DenseRunner:
         d = c.head_dim
         self.hq, self.hkv, self.d = model.hq_local, model.hkv_local, d
         self.qkv_cols = (self.hq + 2 * self.hkv) * d
-        H, I = c.hidden, c.ffn // model.tp_size
+        H, I = c.hidden, model.layers[0].down.k       # local intermediate width (padded to the GEMM's K granule)
         R = max_rows
         e = lambda *s: torch.empty(*s, dtype=BF, device=dev)
         self.x, self.xn, self.delta = e(R, H), e(R, H), e(R, H)

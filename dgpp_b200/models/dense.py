@@ -108,15 +108,24 @@ class DenseModel:
         def full(n, k):
             return torch.randn(n, k, device=device, dtype=torch.float32, generator=g) * std
 
-        def make(n, k, fmt, row_slices=None, col_slice=None):
+        def make(n, k, fmt, row_slices=None, col_slice=None, pad_rows=0, pad_cols=0):
             w = full(n, k)
             if W > 1 and row_slices is not None:
-                w = torch.cat([w[a:b] for a, b in row_slices])
+                parts = [w[a:b] for a, b in row_slices]
+                if pad_rows:   # zero rows after every slice (the padded intermediate channels stay exactly zero)
+                    parts = [torch.cat([q, q.new_zeros(pad_rows, k)]) for q in parts]
+                w = torch.cat(parts)
             if W > 1 and col_slice is not None:
-                w = w[:, col_slice[0]:col_slice[1]].contiguous()
+                w = w[:, col_slice[0]:col_slice[1]]
+                if pad_cols:
+                    w = torch.cat([w, w.new_zeros(n, pad_cols)], dim=1)
+                w = w.contiguous()
             return quantize_like_random(w, fmt, std)
 
         hq_l, hkv_l, ffn_l = cfg.q_heads // W, cfg.kv_heads // W, cfg.ffn // W
+        # a rank's slice of the intermediate dimension is padded with zero channels up to the K granule of the
+        # block-scaled tensor-core GEMM (256), e.g. 17408 / 8 = 2176 -> 2304
+        ffn_pad = (-ffn_l) % 256 if (W > 1 and cfg.weight_fmt == "nvfp4") else 0
         r = tp_rank
         adt = torch.float32 if cfg.weight_fmt == "fp32" else BF
         embed = (torch.randn(cfg.vocab, H, device=device, dtype=torch.float32, generator=g) * std).to(adt)
@@ -129,9 +138,9 @@ class DenseModel:
                                    (nq + r * hkv_l * d, nq + (r + 1) * hkv_l * d),
                                    (nq + nkv + r * hkv_l * d, nq + nkv + (r + 1) * hkv_l * d)])
             o = make(H, nq, cfg.weight_fmt, col_slice=(r * hq_l * d, (r + 1) * hq_l * d))
-            gu = make(2 * cfg.ffn, H, cfg.weight_fmt,
+            gu = make(2 * cfg.ffn, H, cfg.weight_fmt, pad_rows=ffn_pad,
                       row_slices=[(r * ffn_l, (r + 1) * ffn_l), (cfg.ffn + r * ffn_l, cfg.ffn + (r + 1) * ffn_l)])
-            dn = make(H, cfg.ffn, cfg.weight_fmt, col_slice=(r * ffn_l, (r + 1) * ffn_l))
+            dn = make(H, cfg.ffn, cfg.weight_fmt, col_slice=(r * ffn_l, (r + 1) * ffn_l), pad_cols=ffn_pad)
             layers.append(DenseLayer(ones(H), ones(H), qkv, o, gu, dn,
                                      ones(d) if cfg.qk_norm else None, ones(d) if cfg.qk_norm else None))
         vl = cfg.vocab // W

@@ -1,0 +1,201 @@
+"""Mixture-of-experts feed-forward block: sigmoid (or softmax) router with selection bias and group-limited top-k,
+routed SwiGLU experts with NVFP4 weights stacked into one matrix, optional shared experts, ordered accumulation.
+
+* ``moe_reference``  PyTorch oracle of the numerics contract (fp32 router, weights from uncorrected scores, ids
+  ascending = accumulation order, bf16 rounding points of the expert MLP).
+* ``MoEBlock.forward`` the sm_100a path for decode-sized batches (rows <= token tile): router kernel, active-expert
+  list, ONE grouped block-scaled GEMM launch for every active expert's gate/up, fused SwiGLU + quantiser over the
+  slots, ONE grouped GEMM for the down projections, ordered combine.  Every token is a column of every active
+  expert's MMA (the MMA N minimum is 16 anyway); the combine picks each token's experts.  Larger batches fall back
+  to per-expert GEMMs over gathered rows.
+(numerics: src/kernels/glm_moe.cu:86-331,1447 and DESIGN.md:1293-1413 of the reference.)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..ops import core as ops
+from ..ops import reference as ref
+from ..quant.formats import QuantLinear, tile_scales
+from .dense import quantize_like_random
+
+BF = torch.bfloat16
+
+
+@dataclass
+class MoEConfig:
+    hidden: int = 2048
+    experts: int = 64
+    top_k: int = 8
+    moe_ffn: int = 1024
+    shared_ffn: int = 0            # 0: no shared expert
+    n_group: int = 1
+    topk_group: int = 1
+    router: str = "sigmoid"        # or "softmax"
+    norm_topk_prob: bool = True
+    routed_scaling: float = 1.0
+    swiglu_limit: float = 0.0
+
+
+@dataclass
+class MoEWeights:
+    cfg: MoEConfig
+    gate: torch.Tensor                     # [E, H] bf16
+    bias: Optional[torch.Tensor]           # [E] fp32 selection correction
+    experts_gu: List[QuantLinear]          # per expert [2I, H]
+    experts_down: List[QuantLinear]        # per expert [H, I]
+    shared_gu: Optional[QuantLinear] = None
+    shared_down: Optional[QuantLinear] = None
+    # stacked device views for the grouped GEMM (built by `stack`)
+    gu_q: Optional[torch.Tensor] = None
+    gu_sf: Optional[torch.Tensor] = None
+    gu_alpha: Optional[torch.Tensor] = None
+    down_q: Optional[torch.Tensor] = None
+    down_sf: Optional[torch.Tensor] = None
+    down_alpha: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def random_init(cfg: MoEConfig, device, seed: int = 0, std: float = 0.02, fmt: str = "nvfp4") -> "MoEWeights":
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+        rnd = lambda n, k: torch.randn(n, k, device=device, dtype=torch.float32, generator=g) * std
+        gate = (rnd(cfg.experts, cfg.hidden) * 4).to(BF)
+        bias = torch.randn(cfg.experts, device=device, generator=g) * 0.05
+        gu = [quantize_like_random(rnd(2 * cfg.moe_ffn, cfg.hidden), fmt, std) for _ in range(cfg.experts)]
+        dn = [quantize_like_random(rnd(cfg.hidden, cfg.moe_ffn), fmt, std) for _ in range(cfg.experts)]
+        sgu = sdn = None
+        if cfg.shared_ffn:
+            sgu = quantize_like_random(rnd(2 * cfg.shared_ffn, cfg.hidden), fmt, std)
+            sdn = quantize_like_random(rnd(cfg.hidden, cfg.shared_ffn), fmt, std)
+        w = MoEWeights(cfg, gate, bias, gu, dn, sgu, sdn)
+        if fmt == "nvfp4" and torch.device(device).type == "cuda":
+            w.stack()
+        return w
+
+    def stack(self) -> None:
+        """Concatenate the experts' payloads / tiled scales along N: one tensor map serves every expert."""
+        def cat(ws: List[QuantLinear]):
+            q = torch.cat([w.payload for w in ws]).contiguous()
+            sf = torch.cat([tile_scales(w.scale.view(w.n, w.k // 16)).reshape(-1) for w in ws]).contiguous()
+            al = torch.tensor([w.alpha for w in ws], dtype=torch.float32, device=q.device)
+            return q, sf, al
+        self.gu_q, self.gu_sf, self.gu_alpha = cat(self.experts_gu)
+        self.down_q, self.down_sf, self.down_alpha = cat(self.experts_down)
+
+
+def route_reference(x: torch.Tensor, w: MoEWeights):
+    """fp32 router of the contract.  Returns (ids [T, k] ascending, weights [T, k] fp32, logits [T, E])."""
+    c = w.cfg
+    logits = x.float() @ w.gate.float().t()
+    scores = torch.softmax(logits, -1) if c.router == "softmax" else torch.sigmoid(logits)
+    sel = scores + (w.bias.float() if w.bias is not None else 0.0)
+    if c.n_group > 1:
+        T = x.shape[0]
+        per = c.experts // c.n_group
+        gs = sel.view(T, c.n_group, per)
+        top2 = gs.topk(min(2, per), dim=-1).values.sum(-1)                # [T, n_group]
+        keep = torch.zeros_like(top2, dtype=torch.bool)
+        order = torch.argsort(-top2, dim=-1, stable=True)[:, :c.topk_group]   # ties -> lower group id
+        keep.scatter_(1, order, True)
+        sel = torch.where(keep.unsqueeze(-1).expand(T, c.n_group, per).reshape(T, c.experts), sel,
+                          torch.full_like(sel, float("-inf")))
+    order = torch.argsort(-sel, dim=-1, stable=True)[:, :c.top_k]         # ties -> lower expert id
+    ids = torch.sort(order, dim=-1).values
+    wts = scores.gather(1, ids)
+    if c.norm_topk_prob:
+        wts = wts / (wts.sum(-1, keepdim=True) + 1e-20)
+    return ids.to(torch.int32), wts * c.routed_scaling, logits
+
+
+def moe_reference(x: torch.Tensor, w: MoEWeights, ids=None, wts=None) -> torch.Tensor:
+    """x [T, H] (normed hidden, bf16).  Expert MLP: bf16(bf16(silu(g)) * u) -> down; fp32 ordered accumulation of
+    w_e * y_e over ascending expert ids, shared expert added last, one bf16 rounding."""
+    c = w.cfg
+    if ids is None:
+        ids, wts, _ = route_reference(x, w)
+    T = x.shape[0]
+    acc = torch.zeros(T, c.hidden, dtype=torch.float32, device=x.device)
+    for e in sorted(set(ids.flatten().tolist())):
+        rows = (ids == e).any(-1).nonzero().flatten()
+        xe = x[rows]
+        h = ref.linear(xe, w.experts_gu[e])
+        y = ref.linear(ref.swiglu(h, c.swiglu_limit), w.experts_down[e])
+        we = (wts * (ids == e)).sum(-1)[rows]
+        acc[rows] += we.unsqueeze(-1) * y.float()
+    if w.shared_gu is not None:
+        acc += ref.linear(ref.swiglu(ref.linear(x, w.shared_gu), c.swiglu_limit), w.shared_down).float()
+    return ref.act(acc)
+
+
+class MoEBlock:
+    """Device buffers + launch sequence of one MoE block for up to `max_rows` decode rows."""
+
+    def __init__(self, w: MoEWeights, max_rows: int, device, act_terms: int = 3):
+        c = w.cfg
+        assert w.gu_q is not None, "call MoEWeights.stack() on the device first"
+        self.w, self.c, self.dev, self.terms = w, c, device, act_terms
+        self.bn = 16 if max_rows <= 16 else (32 if max_rows <= 32 else 64)
+        assert max_rows <= self.bn and act_terms * self.bn <= 256
+        self.max_rows = max_rows
+        self.slots = min(c.experts, max_rows * c.top_k)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.ids = torch.zeros(max_rows, c.top_k, **i32)
+        self.wts = torch.zeros(max_rows, c.top_k, dtype=torch.float32, device=device)
+        self.group_list = torch.full((self.slots,), -1, **i32)
+        self.slot_of = torch.full((c.experts,), -1, **i32)
+        self.n_active = torch.zeros(1, **i32)
+        self.h = torch.zeros(self.slots, self.bn, 2 * c.moe_ffn, dtype=BF, device=device)
+        self.y = torch.zeros(self.slots, self.bn, c.hidden, dtype=BF, device=device)
+        self.qa_in = ops.QuantAct(self.bn, c.hidden, act_terms, self.bn, device)
+        self.qa_mid = ops.QuantAct(self.slots * self.bn, c.moe_ffn, act_terms, self.bn, device)
+        self.shared = None
+        if w.shared_gu is not None:
+            self.shared = torch.zeros(max_rows, c.hidden, dtype=BF, device=device)
+            self.sh_gu = torch.zeros(max_rows, 2 * c.shared_ffn, dtype=BF, device=device)
+            self.qa_sh = ops.QuantAct(self.bn, c.shared_ffn, act_terms, self.bn, device)
+
+    def forward(self, xn: torch.Tensor, out: torch.Tensor, xa: Optional[ops.QuantAct] = None) -> torch.Tensor:
+        """xn: [rows, H] bf16 normed hidden; xa: its NVFP4 terms when the caller's norm kernel already produced
+        them.  out: [rows, H] bf16."""
+        c, w = self.c, self.w
+        rows = xn.shape[0]
+        assert rows <= self.max_rows
+        if xa is None:
+            xa = ops.act_quant_nvfp4(xn, self.terms, out=self.qa_in)
+        ops.moe_route(xn, w.gate, w.bias, c.top_k, c.n_group, c.topk_group, c.router == "softmax", c.norm_topk_prob,
+                      c.routed_scaling, ids=self.ids[:rows], weights=self.wts[:rows])
+        ops.moe_active(self.ids[:rows], rows, c.experts, self.slots, self.group_list, self.slot_of, self.n_active)
+        ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, self.h, rows, 2 * c.moe_ffn, c.hidden, c.experts,
+                             self.group_list, group_b=False)
+        xm = ops.act_quant_nvfp4(self.h.view(self.slots * self.bn, 2 * c.moe_ffn), self.terms, out=self.qa_mid,
+                                 mode="swiglu", limit=c.swiglu_limit, group_list=self.group_list, group_rows=rows)
+        ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, self.y, rows, c.hidden, c.moe_ffn, c.experts,
+                             self.group_list, group_b=True)
+        sh = None
+        if self.shared is not None:
+            ops.gemm_fp4(xa, w.shared_gu, out=self.sh_gu[:rows])
+            xs = ops.act_quant_nvfp4(self.sh_gu[:rows], self.terms, out=self.qa_sh, mode="swiglu", limit=c.swiglu_limit)
+            ops.gemm_fp4(xs, w.shared_down, out=self.shared[:rows])
+            sh = self.shared
+        return ops.moe_combine(self.y, sh, self.ids[:rows], self.wts[:rows], self.slot_of, out, rows)
+
+    def forward_gathered(self, xn: torch.Tensor) -> torch.Tensor:
+        """Prefill-sized batches: route on the device, then one GEMM pair per active expert over its gathered rows
+        (W4A16 converter GEMM, exact bf16 activations), ordered accumulation in fp32."""
+        c, w = self.c, self.w
+        ids, wts = ops.moe_route(xn, w.gate, w.bias, c.top_k, c.n_group, c.topk_group, c.router == "softmax",
+                                 c.norm_topk_prob, c.routed_scaling)
+        acc = torch.zeros(xn.shape[0], c.hidden, dtype=torch.float32, device=xn.device)
+        for e in torch.unique(ids).tolist():
+            hit = ids == e
+            rows = hit.any(-1).nonzero().flatten()
+            xe = xn.index_select(0, rows).contiguous()
+            h = ops.linear(xe, w.experts_gu[e])
+            y = ops.linear(ops.swiglu(h, limit=c.swiglu_limit), w.experts_down[e])
+            acc.index_add_(0, rows, (wts * hit).sum(-1)[rows].unsqueeze(-1) * y.float())
+        if w.shared_gu is not None:
+            acc += ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu), limit=c.swiglu_limit), w.shared_down).float()
+        return acc.to(BF)

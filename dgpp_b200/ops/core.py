@@ -162,7 +162,6 @@ class QuantAct:
 
     def __init__(self, rows_pad: int, k: int, terms: int, bn: int, device):
         assert rows_pad % bn == 0 and terms * bn <= 256
-        assert terms == 1 or rows_pad == bn, "residual terms are stacked inside a single token tile"
         atoms = 2 if terms * bn > 128 else 1
         self.q = torch.zeros(rows_pad * terms, k // 2, dtype=torch.uint8, device=device)
         self.sf = torch.zeros((rows_pad // bn) * (k // 256) * 4 * atoms * 512, dtype=torch.uint8, device=device)
@@ -180,7 +179,8 @@ class QuantAct:
 
 def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = None, bn: Optional[int] = None,
                     mode: str = "plain", delta=None, norm_w=None, resid_out=None, x_out=None, eps: float = 1e-6,
-                    limit: float = 0.0, one_plus_w: bool = False, fold_comm=None) -> QuantAct:
+                    limit: float = 0.0, one_plus_w: bool = False, fold_comm=None, group_list=None,
+                    group_rows: int = 0) -> QuantAct:
     """Quantise rows to residual NVFP4 terms, optionally fused with the producing operator:
     mode "plain": x [T, K];  "swiglu": x = [gate | up] [T, 2K];  "rmsnorm": x = residual [T, K] (+ delta), norm_w.
     fold_comm (rmsnorm mode): native peer-communicator handle; the delta is then the fixed-order fold of the tiles
@@ -200,9 +200,9 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
     if cl:
         call("dgpp_act_quant_nvfp4_cluster", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out),
              ptr(x_out), ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, cl,
-             float(eps), float(limit), int(one_plus_w), fold_comm, stream_ptr())
+             float(eps), float(limit), int(one_plus_w), fold_comm, ptr(group_list), group_rows, stream_ptr())
     else:
-        assert not fold_comm, "the all-reduce fold needs the cluster quantiser"
+        assert not fold_comm and group_list is None, "the all-reduce fold needs the cluster quantiser"
         call("dgpp_act_quant_nvfp4", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out), ptr(x_out),
              ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, float(eps),
              float(limit), int(one_plus_w), stream_ptr())
@@ -314,4 +314,141 @@ def attn_prefill_tc(q, q_stride: int, cache, block_table_row, pos0: int, hq: int
     call("dgpp_attn_prefill_tc", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale),
          ptr(block_table_row), ptr(out), T, pos0, hq, hkv, d, cache.page, block_table_row.numel(), cache.k.shape[0],
          float(scale), window, stream_ptr())
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- mixture of experts
+from ._lib import F, I, L, P  # noqa: E402  (ctypes aliases for the signatures below)
+
+_lib.declare("dgpp_moe_route", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
+_lib.declare("dgpp_moe_active", [P, I, I, I, I, P, P, P, P])
+_lib.declare("dgpp_moe_combine", [P, P, P, P, P, P, I, I, I, I, P])
+_lib.declare("dgpp_gemm_fp4_grouped", [I, P, P, P, I, P, P, P, P, I, L, I, I, I, I, I, P, I, I, P, P, P])
+
+
+def moe_route(x, gate, bias, k: int, n_group: int = 1, topk_group: int = 1, softmax: bool = False,
+              norm_topk: bool = True, scaling: float = 1.0, ids=None, weights=None, logits_out=None):
+    """Router: x [T, H] bf16, gate [E, H] bf16, bias [E] fp32 or None -> (ids [T, k] int32 ascending, weights [T, k])."""
+    T, H = x.shape
+    E = gate.shape[0]
+    if ids is None:
+        ids = torch.empty(T, k, dtype=torch.int32, device=x.device)
+        weights = torch.empty(T, k, dtype=torch.float32, device=x.device)
+    call("dgpp_moe_route", ptr(x), x.stride(0), ptr(gate), ptr(bias), ptr(ids), ptr(weights), ptr(logits_out), T, H, E, k,
+         n_group, topk_group, int(softmax), int(norm_topk), float(scaling), stream_ptr())
+    return ids, weights
+
+
+def moe_active(ids, rows: int, experts: int, slots: int, group_list=None, slot_of=None, n_active=None):
+    dev = ids.device
+    if group_list is None:
+        group_list = torch.empty(slots, dtype=torch.int32, device=dev)
+        slot_of = torch.empty(experts, dtype=torch.int32, device=dev)
+        n_active = torch.empty(1, dtype=torch.int32, device=dev)
+    call("dgpp_moe_active", ptr(ids), rows, ids.shape[1], experts, slots, ptr(group_list), ptr(slot_of), ptr(n_active),
+         stream_ptr())
+    return group_list, slot_of, n_active
+
+
+def moe_combine(y, shared, ids, weights, slot_of, out, rows: int):
+    """y [slots, rows_per_slot, H]; out[t] = sum_j w[t, j] * y[slot_of[ids[t, j]], t] (+ shared[t])."""
+    call("dgpp_moe_combine", ptr(y), ptr(shared), ptr(ids), ptr(weights), ptr(slot_of), ptr(out), rows, y.shape[2],
+         ids.shape[1], y.shape[1], stream_ptr())
+    return out
+
+
+def gemm_fp4_grouped(xa: "QuantAct", wq, wsf_tiled, alphas, out, rows: int, n: int, k: int, experts: int, group_list,
+                     group_b: bool, splits: int = 1, ws: Optional["GemmWorkspace"] = None):
+    """Grouped block-scaled NVFP4 GEMM over stacked expert matrices (see dgpp_gemm_fp4_grouped).
+    out: [slots, bn, n] bf16 (row stride n)."""
+    slots = group_list.numel()
+    wsp = cnt = None
+    if splits > 1:
+        ws = ws or default_workspace(xa.q.device)
+        if splits * rows * slots * n > ws.partials.numel() or slots * (n // 128) > ws.counters.numel():
+            splits = 1
+        else:
+            wsp, cnt = ws.partials, ws.counters
+    call("dgpp_gemm_fp4_grouped", xa.bn, ptr(xa.q), ptr(xa.sf), ptr(xa.g), xa.terms, ptr(wq), ptr(wsf_tiled), ptr(alphas),
+         ptr(out), out.stride(1), out.stride(0), rows, n, k, experts, slots, ptr(group_list), int(group_b), splits,
+         ptr(wsp), ptr(cnt), stream_ptr())
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- gated delta net
+_lib.declare("dgpp_gdn_recurrent", [P, L, P, L, P, L, P, P, L, P, P, P, P, I, P, I, I, I, I, I, I, P])
+_lib.declare("dgpp_gdn_conv", [P, L, P, P, P, P, I, P, I, I, I, I, P])
+_lib.declare("dgpp_gated_rmsnorm", [P, P, L, P, P, I, I, I, F, P])
+
+
+def gdn_conv(x, w, bias, state, out, row_slot=None, slot: int = 0, sequential: bool = True):
+    """Causal depthwise conv (width w.shape[1]) + SiLU.  x: [T, C] bf16 rows (may be a strided column view);
+    state: [slots, W - 1, C] fp32, updated in place."""
+    T, C = x.shape
+    call("dgpp_gdn_conv", ptr(x), x.stride(0), ptr(w), ptr(bias), ptr(state), ptr(row_slot), slot, ptr(out), T, C,
+         w.shape[1], int(sequential), stream_ptr())
+    return out
+
+
+def gdn_recurrent(q, k, v, alpha, beta, A_log, dt_bias, state, out, hk: int, hv: int, dk: int, dv: int, row_slot=None,
+                  slot: int = 0, sequential: bool = True):
+    """Gated delta-rule recurrence.  q/k: [T, hk*dk], v: [T, hv*dv] (column views allowed), alpha/beta: [T, hv]
+    views with a common row stride; state [slots, hv, dk, dv] fp32 updated in place; out [T, hv*dv] bf16."""
+    T = q.shape[0]
+    assert alpha.stride(0) == beta.stride(0)
+    call("dgpp_gdn_recurrent", ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0), ptr(alpha), ptr(beta),
+         alpha.stride(0), ptr(A_log), ptr(dt_bias), ptr(state), ptr(row_slot), slot, ptr(out), T, hk, hv, dk, dv,
+         int(sequential), stream_ptr())
+    return out
+
+
+def gated_rmsnorm(o, z, w, out, heads: int, d: int, eps: float = 1e-6):
+    """out = rmsnorm(o per head) * w * silu(z); o/out: [rows, heads*d] contiguous, z: [rows, heads*d] view."""
+    call("dgpp_gated_rmsnorm", ptr(o), ptr(z), z.stride(0), ptr(w), ptr(out), o.shape[0], heads, d, float(eps), stream_ptr())
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- latent attention
+_lib.declare("dgpp_mla_decode", [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P])
+_lib.declare("dgpp_dsa_index", [P, P, P, P, P, P, P, I, I, I, I, I, I, P])
+_lib.declare("dgpp_topk_select", [P, L, P, P, I, I, P])
+
+
+def mla_decode(q, cache, block_table, row_req, positions, scale: float, dc: int, dr: int, sel=None, splits: int = 1,
+               out=None):
+    """Absorbed multi-head latent attention.  q: [rows, heads, dc + dr] bf16; cache: [blocks, page, dc + dr] bf16;
+    sel: optional [rows, n_sel] int32 selected token positions (ascending, -1 padded) for sparse attention.
+    Returns the latent outputs [rows, heads, dc] bf16."""
+    rows, heads, _ = q.shape
+    dev = q.device
+    if out is None:
+        out = torch.empty(rows, heads, dc, dtype=torch.bfloat16, device=dev)
+    ml = acc = None
+    if splits > 1:
+        ml = torch.empty(rows * heads * splits * 2, dtype=torch.float32, device=dev)
+        acc = torch.empty(rows * heads * splits * dc, dtype=torch.float32, device=dev)
+    call("dgpp_mla_decode", ptr(q), ptr(cache), ptr(block_table), ptr(row_req), ptr(positions), ptr(sel),
+         0 if sel is None else sel.shape[1], ptr(ml), ptr(acc), ptr(out), rows, heads, dc, dr, cache.shape[1],
+         block_table.shape[1], splits, float(scale), stream_ptr())
+    return out
+
+
+def dsa_index(q_idx, w_idx, k_idx, block_table, row_req, positions, max_ctx: int, scores=None):
+    """Lightning-indexer scores [rows, max_ctx] fp32 (-inf beyond each row's position).
+    q_idx: [rows, hi, di] bf16, w_idx: [rows, hi] fp32, k_idx: paged [blocks, page, di] bf16."""
+    rows, hi, di = q_idx.shape
+    if scores is None:
+        scores = torch.empty(rows, max_ctx, dtype=torch.float32, device=q_idx.device)
+    call("dgpp_dsa_index", ptr(q_idx), ptr(w_idx), ptr(k_idx), ptr(block_table), ptr(row_req), ptr(positions),
+         ptr(scores), rows, hi, di, k_idx.shape[1], block_table.shape[1], scores.shape[1], stream_ptr())
+    return scores
+
+
+def topk_select(scores, positions, k: int, out=None):
+    """Exact top-k token positions per row among positions 0..positions[row] (ties to the lower position),
+    ascending, -1 padded."""
+    rows = scores.shape[0]
+    if out is None:
+        out = torch.empty(rows, k, dtype=torch.int32, device=scores.device)
+    call("dgpp_topk_select", ptr(scores), scores.stride(0), ptr(positions), ptr(out), rows, k, stream_ptr())
     return out

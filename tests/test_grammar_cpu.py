@@ -1,0 +1,83 @@
+"""JSON / JSON-schema constrained decoding: byte machine acceptance and token masks."""
+import json
+
+import numpy as np
+import pytest
+
+from dgpp_b200.runtime import rt
+
+
+def chk(schema, text):
+    return rt.json_machine_check(json.dumps(schema) if schema is not None else "", text.encode())
+
+
+def test_json_object_mode_accepts_exactly_objects():
+    assert chk(None, '{"a": 1, "b": [true, null, {"c": "x\\n\\u00e9"}], "d": -1.5e+3}') == (True, True)
+    assert chk(None, '{"a": 1') == (True, False)
+    assert chk(None, '[1]')[0] is False                      # top level must be an object
+    assert chk(None, '{"a": 01}')[0] is False                # leading zero
+    assert chk(None, '{"a": 1,}')[0] is False                # trailing comma
+    assert chk(None, '{"a": 1, "a": 2}')[0] is False         # duplicate key
+    assert chk(None, '{"a": "\x01"}')[0] is False            # raw control character
+    assert chk(None, '{      "a": 1}')[0] is False           # more than 4 blanks in a row
+    assert chk(None, '{"a": tru')[0] is True and chk(None, '{"a": trx')[0] is False
+
+
+SCHEMA = {"type": "object", "additionalProperties": False, "required": ["name", "age"],
+          "properties": {"name": {"type": "string"}, "age": {"type": "integer"},
+                         "tags": {"type": "array", "items": {"enum": ["a", "b", 3]}, "minItems": 1, "maxItems": 2},
+                         "mode": {"const": "fast"}, "score": {"type": ["number", "null"]}}}
+
+
+def test_schema_subset():
+    assert chk(SCHEMA, '{"name": "x", "age": 3}') == (True, True)
+    assert chk(SCHEMA, '{"age": 3, "name": "x", "tags": ["a", 3], "mode": "fast", "score": null}') == (True, True)
+    assert chk(SCHEMA, '{"name": "x"}')[0] is False                       # required age missing at '}'
+    assert chk(SCHEMA, '{"name": "x", "age": 3.5}')[0] is False           # integer
+    assert chk(SCHEMA, '{"name": "x", "age": 3, "other": 1}')[0] is False  # additionalProperties false
+    assert chk(SCHEMA, '{"name": "x", "age": 3, "tags": []}')[0] is False  # minItems
+    assert chk(SCHEMA, '{"name": "x", "age": 3, "tags": ["a", "b", "a"]}')[0] is False   # maxItems
+    assert chk(SCHEMA, '{"name": "x", "age": 3, "tags": ["c"]}')[0] is False  # enum
+    assert chk(SCHEMA, '{"name": "x", "age": 3, "mode": "slow"}')[0] is False
+    assert chk(SCHEMA, '{"name": "x", "age": 3, "score": 1e5}') == (True, True)
+    assert chk(SCHEMA, '{"na') == (True, False) and chk(SCHEMA, '{"nb')[0] is False   # key prefixes are checked
+    with pytest.raises(RuntimeError, match="anyOf"):
+        chk({"anyOf": [{"type": "string"}]}, "1")
+    with pytest.raises(RuntimeError, match="never be written"):
+        chk({"type": "object", "required": ["x"], "additionalProperties": False, "properties": {}}, "{}")
+
+
+def test_token_masks_drive_a_valid_generation():
+    # a toy vocabulary: single bytes plus a few multi-byte tokens and two specials
+    vocab = [bytes([i]) for i in range(256)] + [b'{"', b'": ', b'", "', b'"}', b"true", b"null", b"name", b"age", b""]
+    eos = len(vocab) - 1
+    g = rt.JsonGrammar(json.dumps(SCHEMA), vocab, [eos])
+    assert g.words() == (len(vocab) + 31) // 32
+
+    def allowed():
+        m = g.mask()
+        return {i for i in range(len(vocab)) if (int(m[i >> 5]) >> (i & 31)) & 1}
+
+    a0 = allowed()
+    assert vocab.index(b'{"') in a0 and ord("{") in a0 and ord("[") not in a0 and eos not in a0
+    # greedy walk: always take the allowed token that makes the text match a target document
+    target = b'{"name": "bo", "age": 41}'
+    text = b""
+    steps = 0
+    while text != target:
+        al = allowed()
+        cand = [i for i in al if i != eos and vocab[i] and target.startswith(text + vocab[i])]
+        assert cand, (text, sorted(al)[:10])
+        tok = max(cand, key=lambda i: len(vocab[i]))
+        assert g.accept(tok)
+        text += vocab[tok]
+        steps += 1
+    assert g.complete() and eos in allowed()
+    assert steps < len(target)                       # multi-byte tokens were usable
+    assert g.accept(eos)
+    # a token that breaks the schema is refused
+    g2 = rt.JsonGrammar(json.dumps(SCHEMA), vocab, [eos])
+    assert not g2.accept(ord("["))
+    # masks are cached per state: same object state -> identical mask
+    g3 = rt.JsonGrammar("", vocab, [eos])
+    assert np.array_equal(g3.mask(), g3.mask())
