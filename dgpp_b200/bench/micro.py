@@ -1,0 +1,248 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+    python -m dgpp_b200.bench.micro gemm_fp4 --rows 8 --n 34816 --k 5120 [--terms 3] [--splits 0]
+    python -m dgpp_b200.bench.micro gemm_tc --rows 2048 --n 5120 --k 5120 [--fmt nvfp4]
+    python -m dgpp_b200.bench.micro attn_decode --rows 8 --ctx 2048 [--hq 40 --hkv 8 --splits 4]
+    python -m dgpp_b200.bench.micro attn_prefill --ctx 8192 [--hq 40 --hkv 8]
+    python -m dgpp_b200.bench.micro act_quant --rows 8 --k 5120 [--mode rmsnorm]
+    python -m dgpp_b200.bench.micro gdn --rows 8192 [--hv 32]
+    python -m dgpp_b200.bench.micro moe --rows 8 [--experts 128 --top-k 8]
+
+Timing: the launches are captured in a CUDA graph, replayed `--reps` times between CUDA events after a warm-up replay.
+Weight-streaming kernels rotate over enough weight copies to exceed the 126 MB L2, so every launch reads its
+weights from HBM.  Fractions are "of measured": the copy bandwidth / cuBLAS bf16 throughput in MEASURED_PEAKS.json
+at the repository root (fallback 6650 GB/s, 1590 TFLOP/s when the file is absent).  `--once` runs a few plain
+launches without graph or timing (the form used under a profiler).  Prints one JSON line.
+(reference counterparts: benchmarks/micro/*.)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+from pathlib import Path
+
+import torch
+
+BF = torch.bfloat16
+L2_BYTES = 126 << 20
+
+
+def peaks() -> dict:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return {"hbm_gbs": j["hbm_gbs"], "tflops": j["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
+
+
+def graph_time(fns, reps: int) -> float:
+    """Mean milliseconds per launch of the callables in `fns` (captured once, replayed)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for f in fns:
+            f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps / len(fns)
+
+
+def run(fns, args) -> float:
+    if args.once:
+        for f in fns[:3]:
+            f()
+        torch.cuda.synchronize()
+        return float("nan")
+    return graph_time(fns, args.reps)
+
+
+def report(args, name: str, ms: float, bytes_: float = 0.0, flops: float = 0.0, **extra) -> None:
+    pk = peaks()
+    out = {"kernel": name, "us": round(ms * 1e3, 2), "peaks": pk["source"], **extra}
+    if bytes_:
+        gbs = bytes_ / ms / 1e6
+        out.update(gb_s=round(gbs, 1), frac_hbm=round(gbs / pk["hbm_gbs"], 3))
+    if flops:
+        tf = flops / ms / 1e9
+        out.update(tflops=round(tf, 1), frac_tensor=round(tf / pk["tflops"], 3))
+    print(json.dumps(out), flush=True)
+
+
+def bench_gemm_fp4(args, dev):
+    from ..ops import core as ops
+    from ..quant.formats import random_quant_linear
+
+    n, k, rows = args.n, args.k, args.rows
+    w_bytes = n * k // 2 + n * k // 16
+    copies = max(2, min(16, math.ceil(2 * L2_BYTES / w_bytes))) if rows <= 64 else 2
+    ws = [random_quant_linear(n, k, "nvfp4", dev) for _ in range(copies)]
+    x = torch.randn(rows, k, device=dev).to(BF)
+    terms = args.terms if rows <= 64 else 1
+    xa = ops.act_quant_nvfp4(x, terms)
+    out = torch.empty(rows, n, device=dev, dtype=BF)
+    splits = args.splits or None
+    fns = [(lambda w=w: ops.gemm_fp4(xa, w, out=out, splits=splits)) for w in ws]
+    ms = run(fns, args)
+    ops.check_status()
+    report(args, "gemm_fp4", ms, bytes_=w_bytes + rows * k * terms // 2 + rows * n * 2, flops=2.0 * rows * n * k,
+           rows=rows, n=n, k=k, terms=terms, weight_copies=copies)
+
+
+def bench_gemm_tc(args, dev):
+    from ..ops import core as ops
+    from ..quant.formats import random_quant_linear
+
+    n, k, rows = args.n, args.k, args.rows
+    ws = [random_quant_linear(n, k, args.fmt, dev) for _ in range(2)]
+    x = torch.randn(rows, k, device=dev).to(BF)
+    out = torch.empty(rows, n, device=dev, dtype=BF)
+    fns = [(lambda w=w: ops.gemm_tc(x, w, out=out)) for w in ws]
+    ms = run(fns, args)
+    ops.check_status()
+    report(args, "gemm_tc", ms, bytes_=ws[0].nbytes + rows * k * 2 + rows * n * 2, flops=2.0 * rows * n * k, rows=rows, n=n, k=k,
+           fmt=args.fmt)
+
+
+def _cache(dev, hq, hkv, ctx, page=64, slots=1):
+    from ..engine.kv_cache import PagedKV
+    from ..ops import core as ops, reference as ref
+
+    d = 128
+    per = ctx // page + 2
+    kv = PagedKV(1, hkv, d, slots * per + 2, slots, per, page, True, dev)
+    inv_freq, _ = ref.rope_inv_freq(d, 1e4, dev)
+    for s in range(slots):
+        assert kv.reserve(s, ctx)
+        qkv = torch.randn(ctx, (hq + 2 * hkv) * d, device=dev).to(BF)
+        pos = torch.arange(ctx, device=dev, dtype=torch.int32)
+        req = torch.full((ctx,), s, device=dev, dtype=torch.int32)
+        ops.rope_kv_write(qkv, pos, req, kv.block_table, inv_freq, kv.layers[0], hq, hkv, d)
+    return kv, qkv
+
+
+def bench_attn_decode(args, dev):
+    from ..ops import core as ops
+
+    hq, hkv, ctx, rows = args.hq, args.hkv, args.ctx, args.rows
+    kv, _ = _cache(dev, hq, hkv, ctx, slots=rows)
+    q = torch.randn(rows, (hq + 2 * hkv) * 128, device=dev).to(BF)
+    pos = torch.full((rows,), ctx - 1, device=dev, dtype=torch.int32)
+    req = torch.arange(rows, device=dev, dtype=torch.int32)
+    out = torch.empty(rows, hq * 128, device=dev, dtype=BF)
+    sp = args.splits or 4
+    scratch = (torch.empty(rows * hq * sp * 2, device=dev), torch.empty(rows * hq * sp * 128, device=dev))
+    fn = lambda: ops.attn_decode_tc(q, q.stride(0), kv.layers[0], kv.block_table, req, pos, hq, hkv, 128, 0.088, splits=sp,
+                                    scratch=scratch, out=out)
+    ms = run([fn] * 4, args)
+    ops.check_status()
+    report(args, "attn_decode_tc", ms, bytes_=2.0 * rows * ctx * hkv * 128, flops=4.0 * rows * hq * ctx * 128, rows=rows, ctx=ctx,
+           hq=hq, hkv=hkv, splits=sp)
+
+
+def bench_attn_prefill(args, dev):
+    from ..ops import core as ops
+
+    hq, hkv, ctx = args.hq, args.hkv, args.ctx
+    kv, qkv = _cache(dev, hq, hkv, ctx)
+    out = torch.empty(ctx, hq * 128, device=dev, dtype=BF)
+    fn = lambda: ops.attn_prefill_tc(qkv, qkv.stride(0), kv.layers[0], kv.block_table[0], 0, hq, hkv, 128, 0.088, out=out)
+    ms = run([fn] * 2, args)
+    ops.check_status()
+    report(args, "attn_prefill_tc", ms, flops=4.0 * ctx * ctx / 2 * 128 * hq, bytes_=2.0 * ctx * hkv * 128 + 4.0 * ctx * hq * 128,
+           ctx=ctx, hq=hq, hkv=hkv, note="causal, bf16-equivalent FLOPs (two-term fp8 operands issue 4x the MMAs)")
+
+
+def bench_act_quant(args, dev):
+    from ..ops import core as ops
+
+    rows, k = args.rows, args.k
+    x = torch.randn(rows, k, device=dev).to(BF)
+    d = torch.randn(rows, k, device=dev).to(BF)
+    w = torch.ones(k, device=dev, dtype=BF)
+    xa = ops.act_quant_nvfp4(x, args.terms)
+    if args.mode == "rmsnorm":
+        fn = lambda: ops.act_quant_nvfp4(x, out=xa, mode="rmsnorm", delta=d, norm_w=w)
+    elif args.mode == "swiglu":
+        gu = torch.randn(rows, 2 * k, device=dev).to(BF)
+        fn = lambda: ops.act_quant_nvfp4(gu, out=xa, mode="swiglu")
+    else:
+        fn = lambda: ops.act_quant_nvfp4(x, out=xa)
+    ms = run([fn] * 8, args)
+    report(args, "act_quant_" + args.mode, ms, bytes_=rows * k * 2 * (3 if args.mode == "rmsnorm" else 1) + rows * k * args.terms * 0.5625,
+           rows=rows, k=k, terms=args.terms)
+
+
+def bench_gdn(args, dev):
+    from ..models.gdn import GdnConfig, GdnLayer, GdnState, GdnWeights
+
+    cfg = GdnConfig(hidden=2048, k_heads=args.hv // 2, v_heads=args.hv, dk=128, dv=128)
+    w = GdnWeights.random_init(cfg, dev, seed=1)
+    layer, st = GdnLayer(w, args.rows, dev), GdnState(cfg, 1, dev)
+    x = torch.randn(args.rows, cfg.hidden, device=dev).to(BF)
+    out = torch.empty_like(x)
+    fn = lambda: layer.forward(x, st, out, slot=0)
+    ms = run([fn], args)
+    report(args, "gdn_layer_prefill", ms * 1.0, rows=args.rows, v_heads=args.hv,
+           note="in_proj + conv + recurrence + gated norm + out_proj of one layer; sequential recurrence")
+
+
+def bench_moe(args, dev):
+    from ..models.moe import MoEBlock, MoEConfig, MoEWeights
+
+    cfg = MoEConfig(hidden=args.k, experts=args.experts, top_k=args.top_k, moe_ffn=args.moe_ffn, shared_ffn=args.moe_ffn)
+    w = MoEWeights.random_init(cfg, dev, seed=1)
+    blk = MoEBlock(w, max_rows=16, device=dev)
+    x = torch.randn(args.rows, cfg.hidden, device=dev).to(BF)
+    out = torch.empty_like(x)
+    fn = lambda: blk.forward(x, out)
+    ms = run([fn] * 2, args)
+    active = int(blk.n_active)
+    per_expert = 3 * cfg.hidden * cfg.moe_ffn * 0.5625
+    report(args, "moe_block_decode", ms, bytes_=(active + 1) * per_expert, rows=args.rows, experts=args.experts, top_k=args.top_k,
+           active_experts=active)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm_fp4", "gemm_tc", "attn_decode", "attn_prefill", "act_quant", "gdn", "moe"])
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--n", type=int, default=5120)
+    ap.add_argument("--k", type=int, default=5120)
+    ap.add_argument("--terms", type=int, default=3)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--fmt", default="nvfp4")
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--hq", type=int, default=40)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--hv", type=int, default=32)
+    ap.add_argument("--mode", default="rmsnorm", choices=["plain", "rmsnorm", "swiglu"])
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--top-k", type=int, default=8)
+    ap.add_argument("--moe-ffn", type=int, default=1536)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--once", action="store_true", help="a few plain launches, no graph, no timing (for profilers)")
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    {"gemm_fp4": bench_gemm_fp4, "gemm_tc": bench_gemm_tc, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill,
+     "act_quant": bench_act_quant, "gdn": bench_gdn, "moe": bench_moe}[args.kernel](args, dev)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

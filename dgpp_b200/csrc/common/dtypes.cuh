@@ -94,13 +94,32 @@ __device__ __forceinline__ void e2m1x8_residual(uint32_t codes, float s, float* 
   }
 }
 
+// Value of x after round-to-nearest-even onto the e4m3 grid (3 mantissa bits), computed with integer arithmetic on
+// the fp32 bits: no fp8 decode instruction is involved.  Saturates at +-448.  Below 2^-6 (the e4m3 subnormal range)
+// the result keeps 3 mantissa bits instead of the fixed 2^-9 step; callers use it for residuals, where that
+// difference is far below the second term's own rounding.
+__device__ __forceinline__ float e4m3_round_f32(float x) {
+  const uint32_t u = __float_as_uint(x);
+  const uint32_t r = (u + 0x0007FFFFu + ((u >> 20) & 1u)) & 0xFFF00000u;
+  return fminf(fmaxf(__uint_as_float(r), -448.f), 448.f);
+}
+// Exact value of the e4m3 code that a saturating round-to-nearest-even conversion of x produces, subnormal range
+// (|x| < 2^-6, step 2^-9) included; checked against a reference conversion over 10^7 values.  Used where a value
+// is encoded and its decoded value is needed right away (block scales, residual terms).
+__device__ __forceinline__ float e4m3_value_f32(float x) {
+  const uint32_t u = __float_as_uint(x);
+  const float normal = __uint_as_float((u + 0x0007FFFFu + ((u >> 20) & 1u)) & 0xFFF00000u);
+  const float sub = rintf(x * 512.f) * (1.f / 512.f);
+  const float y = fabsf(x) >= 0.015625f ? normal : sub;
+  return fminf(fmaxf(y, -448.f), 448.f);
+}
 // Two floats -> two e4m3 terms each (value + residual), packed: a = {e4m3(x0), e4m3(x1)} (x0 in the low byte),
-// b = e4m3 of what a left (residual formed in fp32), so the pair keeps ~2^-8 relative error.
+// b = e4m3 of what a left, so the pair keeps ~2^-8 relative error.  The value of the first term is recomputed
+// arithmetically (e4m3_round_f32) rather than decoded from `a`: chaining the packed e4m3x2 -> f16x2 conversion to
+// the packing conversion returned wrong values for every other pair on B200 in this kernel family.
 __device__ __forceinline__ void f32x2_to_e4m3x2_two_term(float x0, float x1, uint16_t& a, uint16_t& b) {
-  const __nv_fp8x2_storage_t a2 = __nv_cvt_float2_to_fp8x2(make_float2(x0, x1), __NV_SATFINITE, __NV_E4M3);
-  const float2 af = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(a2, __NV_E4M3)));
-  a = a2;
-  b = __nv_cvt_float2_to_fp8x2(make_float2(x0 - af.x, x1 - af.y), __NV_SATFINITE, __NV_E4M3);
+  a = __nv_cvt_float2_to_fp8x2(make_float2(x0, x1), __NV_SATFINITE, __NV_E4M3);
+  b = __nv_cvt_float2_to_fp8x2(make_float2(x0 - e4m3_round_f32(x0), x1 - e4m3_round_f32(x1)), __NV_SATFINITE, __NV_E4M3);
 }
 // 2^x, one MUFU; flushes denormals, ex2(-inf) = 0.
 __device__ __forceinline__ float fast_exp2(float x) {

@@ -131,7 +131,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         q_scale[h < G ? h : 0] = sc;
         const float v = bf16_to_f32(p.q[static_cast<size_t>(row) * p.q_stride + (kvh * G + h) * D + d]) / sc;
         b1 = f32_to_e4m3(v);
-        b2 = f32_to_e4m3((v - e4m3_to_f32(b1)) * 16.f);
+        b2 = f32_to_e4m3((v - e4m3_value_f32(v)) * 16.f);   // residual against the VALUE of b1 (no fp8 decode of b1)
       }
       sQ[sw128_byte(h, d)] = b1;
       sQ[sw128_byte(8 + h, d)] = b2;
@@ -293,7 +293,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         m_run[h] = mn;
         const float pw = pv * vs * c_tile;
         pb1[h] = f32_to_e4m3(pw);
-        pb2[h] = f32_to_e4m3((pw - e4m3_to_f32(pb1[h])) * 16.f);
+        pb2[h] = f32_to_e4m3((pw - e4m3_value_f32(pw)) * 16.f);
       }
       unsigned char* pbuf = sP + b * kAdCols * 128;
 #pragma unroll

@@ -184,11 +184,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     for (int c = 0; c < D / 16; ++c) {
       Pack16 a, b;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {   // signed values: the residual is formed in fp32 (once per CTA, not per tile)
-        const float x = v[c * 16 + j] * inv;
-        a.b[j] = f32_to_e4m3(x);
-        b.b[j] = f32_to_e4m3(x - e4m3_to_f32(a.b[j]));
-      }
+      for (int j = 0; j < 8; ++j)
+        f32x2_to_e4m3x2_two_term(v[c * 16 + 2 * j] * inv, v[c * 16 + 2 * j + 1] * inv, a.s[j], b.s[j]);
       *reinterpret_cast<uint4*>(sQ + sw128_off(r, c * 16)) = a.u;
       *reinterpret_cast<uint4*>(sQ + kTileBytes + sw128_off(r, c * 16)) = b.u;
     }

@@ -443,7 +443,7 @@ __global__ void __launch_bounds__(256) fused_act_quant_kernel(QuantArgs a) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) bm = fmaxf(bm, fabsf(res[j]));
       const uint8_t sb = f32_to_e4m3(bm * (1.f / 6.f));
-      const float s = e4m3_to_f32(sb);
+      const float s = e4m3_value_f32(bm * (1.f / 6.f));   // value of the code sb, without an fp8 decode of it
       const float inv_s = s > 0.f ? 1.f / s : 0.f;
       float sc[16];
 #pragma unroll

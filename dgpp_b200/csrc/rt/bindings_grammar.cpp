@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 
 #include "rt/json_grammar.h"
+#include "rt/speculative.h"
 
 namespace py = pybind11;
 using namespace dgpp;
@@ -42,4 +43,27 @@ void bind_grammar(py::module_& m) {
         std::memcpy(out.mutable_data(), mk.data(), mk.size() * sizeof(uint32_t));
         return out;
       });
+
+  // ---- speculative decoding control
+  py::class_<spec::LookupDraft>(m, "LookupDraft")
+      .def(py::init<int, int>(), py::arg("min_ngram") = 2, py::arg("max_ngram") = 4)
+      .def("reset", &spec::LookupDraft::reset)
+      .def("append", &spec::LookupDraft::append)
+      .def("push", &spec::LookupDraft::push)
+      .def("propose", &spec::LookupDraft::propose)
+      .def("size", &spec::LookupDraft::size);
+  py::class_<spec::VerifySchedule>(m, "VerifySchedule")
+      .def(py::init<int, int, int>(), py::arg("min_draft") = 0, py::arg("max_draft") = 7, py::arg("start") = 3)
+      .def("draft_len", &spec::VerifySchedule::draft_len)
+      .def("acceptance", &spec::VerifySchedule::acceptance)
+      .def("observe", &spec::VerifySchedule::observe)
+      .def("steps", &spec::VerifySchedule::steps)
+      .def("proposed_total", &spec::VerifySchedule::proposed_total)
+      .def("accepted_total", &spec::VerifySchedule::accepted_total);
+  m.def("spec_judge", [](int64_t base, const std::vector<int32_t>& draft, const std::vector<int32_t>& target,
+                         const std::vector<int32_t>& stop_ids, int64_t budget) {
+    const spec::Verdict v = spec::judge(base, draft, target, stop_ids, budget);
+    return py::make_tuple(v.accepted, v.emitted, v.keep_length);
+  }, py::arg("base"), py::arg("draft"), py::arg("target"), py::arg("stop_ids") = std::vector<int32_t>{},
+     py::arg("budget") = int64_t(-1));
 }

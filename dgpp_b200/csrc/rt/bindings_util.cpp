@@ -1,0 +1,88 @@
+// pybind11 surface of the small runtime services (logger, trace, crc32c, watchdogs, deployment config, memory plan).
+#include <pybind11/functional.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "rt/core_util.h"
+
+namespace py = pybind11;
+using namespace dgpp;
+
+namespace {
+
+// A Python callable that may be released from a thread that does not hold the GIL.
+std::shared_ptr<py::object> keep(py::object fn) {
+  return std::shared_ptr<py::object>(new py::object(std::move(fn)), [](py::object* p) {
+    py::gil_scoped_acquire g;
+    delete p;
+  });
+}
+// The watchdogs join their thread in the destructor; that thread may be waiting for the GIL inside a callback.
+template <class T>
+struct NoGilDelete {
+  void operator()(T* p) const {
+    py::gil_scoped_release r;
+    delete p;
+  }
+};
+
+}  // namespace
+
+void bind_util(py::module_& m) {
+  m.def("log", [](const std::string& level, const std::string& component, const std::string& msg) {
+    Logger::get().log(Logger::parse(level, LogLevel::Info), component, msg);
+  });
+  m.def("set_log_level", [](const std::string& level) { Logger::get().set_level(Logger::parse(level, LogLevel::Info)); });
+  m.def("log_level", [] { return static_cast<int>(Logger::get().level()); });
+  m.def("set_log_sink", [](py::object fn) {
+    if (fn.is_none()) { Logger::get().set_sink(nullptr); return; }
+    auto h = keep(fn);
+    Logger::get().set_sink([h](const std::string& line) { py::gil_scoped_acquire g; (*h)(line); });
+  });
+  m.def("trace_open", [](const std::string& path) { Trace::get().open(path); });
+  m.def("trace_close", [] { Trace::get().close(); });
+  m.def("trace_enabled", [] { return Trace::get().enabled(); });
+  m.def("trace_emit", [](const std::string& name, int64_t ts, int64_t dur, const std::string& args) {
+    Trace::get().emit(name, ts, dur, args);
+  }, py::arg("name"), py::arg("ts_us"), py::arg("dur_us"), py::arg("args_json") = "{}");
+  m.def("trace_now_us", &Trace::now_us);
+  m.def("crc32c", [](const py::bytes& b, uint32_t crc) {
+    const std::string s = b;
+    return crc32c(s.data(), s.size(), crc);
+  }, py::arg("data"), py::arg("crc") = 0u);
+
+  py::class_<EngineWatchdog, std::unique_ptr<EngineWatchdog, NoGilDelete<EngineWatchdog>>>(m, "EngineWatchdog")
+      .def(py::init([](int deadline_ms, py::object on_stall, int poll_ms) {
+        std::function<void(int64_t)> cb;
+        if (!on_stall.is_none()) {
+          auto h = keep(on_stall);
+          cb = [h](int64_t ms) { py::gil_scoped_acquire g; (*h)(ms); };
+        }
+        return new EngineWatchdog(std::chrono::milliseconds(deadline_ms), cb, std::chrono::milliseconds(poll_ms));
+      }), py::arg("deadline_ms") = 120000, py::arg("on_stall") = py::none(), py::arg("poll_ms") = 50)
+      .def("progress", &EngineWatchdog::progress)
+      .def("set_busy", &EngineWatchdog::set_busy)
+      .def("fired", &EngineWatchdog::fired);
+  py::class_<ShutdownWatchdog, std::unique_ptr<ShutdownWatchdog, NoGilDelete<ShutdownWatchdog>>>(m, "ShutdownWatchdog")
+      .def(py::init([](int limit_ms, py::object on_timeout) {
+        std::function<void()> cb;
+        if (!on_timeout.is_none()) {
+          auto h = keep(on_timeout);
+          cb = [h] { py::gil_scoped_acquire g; (*h)(); };
+        }
+        return new ShutdownWatchdog(std::chrono::milliseconds(limit_ms), cb);
+      }), py::arg("limit_ms") = 30000, py::arg("on_timeout") = py::none())
+      .def("disarm", &ShutdownWatchdog::disarm)
+      .def("timed_out", &ShutdownWatchdog::timed_out);
+
+  m.def("parse_cluster_config", [](const std::string& text) {
+    const ClusterConfig c = ClusterConfig::parse(text);
+    return py::make_tuple(c.to_json().dump(), c.digest());
+  });
+  m.def("plan_kv", [](int64_t free_bytes, int64_t headroom, int64_t workspace, int layers, int kv_heads, int head_dim,
+                      int block_tokens, bool fp8, int64_t max_blocks) {
+    const MemoryPlan p = plan_kv(free_bytes, headroom, workspace, layers, kv_heads, head_dim, block_tokens, fp8, max_blocks);
+    return py::make_tuple(p.kv_blocks, p.kv_bytes, p.tokens);
+  }, py::arg("free_bytes"), py::arg("headroom_bytes"), py::arg("workspace_bytes"), py::arg("layers"), py::arg("kv_heads"),
+     py::arg("head_dim"), py::arg("block_tokens"), py::arg("fp8") = true, py::arg("max_blocks") = int64_t(-1));
+}

@@ -1,0 +1,318 @@
+// Small runtime services: levelled logger, scoped JSONL trace spans, CRC-32C, progress / shutdown watchdogs,
+// deployment-config parser with digest, KV memory plan.
+// (same roles as src/common/log.hpp, src/core/trace.hpp, src/common/crc32c.hpp, src/serve/engine_watchdog.hpp,
+//  shutdown_watchdog.hpp, cluster_config.cpp, src/engine/memory_plan.hpp of the reference.)
+#pragma once
+#include <atomic>
+#include <chrono>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <map>
+#include <mutex>
+#include <set>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "rt/json.h"
+
+namespace dgpp {
+
+// ------------------------------------------------------------------------------------------- logging
+enum class LogLevel { Trace = 0, Debug, Info, Warn, Error, Off };
+
+class Logger {
+ public:
+  static Logger& get() {
+    static Logger l;
+    return l;
+  }
+  static LogLevel parse(const std::string& s, LogLevel dflt) {
+    static const std::map<std::string, LogLevel> m = {{"trace", LogLevel::Trace}, {"debug", LogLevel::Debug},
+                                                      {"info", LogLevel::Info},   {"warn", LogLevel::Warn},
+                                                      {"error", LogLevel::Error}, {"off", LogLevel::Off}};
+    std::string k;
+    for (char c : s) k.push_back(static_cast<char>(tolower(c)));
+    auto it = m.find(k);
+    return it == m.end() ? dflt : it->second;
+  }
+  void set_level(LogLevel l) { level_.store(static_cast<int>(l)); }
+  LogLevel level() const { return static_cast<LogLevel>(level_.load()); }
+  void set_sink(std::function<void(const std::string&)> sink) {
+    std::lock_guard<std::mutex> g(mu_);
+    sink_ = std::move(sink);
+  }
+  void log(LogLevel l, const std::string& component, const std::string& msg) {
+    if (static_cast<int>(l) < level_.load()) return;
+    static const char* names[] = {"TRACE", "DEBUG", "INFO", "WARN", "ERROR"};
+    const auto now = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::system_clock::now().time_since_epoch()).count();
+    char head[96];
+    snprintf(head, sizeof(head), "%lld.%03lld %-5s [%s] ", static_cast<long long>(now / 1000), static_cast<long long>(now % 1000),
+             names[static_cast<int>(l)], component.c_str());
+    const std::string line = std::string(head) + msg;
+    std::lock_guard<std::mutex> g(mu_);
+    if (sink_) sink_(line);
+    else fprintf(stderr, "%s\n", line.c_str());
+  }
+
+ private:
+  Logger() {
+    const char* e = getenv("DGPP_LOG_LEVEL");
+    level_.store(static_cast<int>(e ? parse(e, LogLevel::Info) : LogLevel::Info));
+  }
+  std::atomic<int> level_;
+  std::mutex mu_;
+  std::function<void(const std::string&)> sink_;
+};
+
+// ------------------------------------------------------------------------------------------- trace spans
+// One JSON object per line: {"name":..., "ts_us":..., "dur_us":..., "tid":..., "args":{...}}.  Off unless a path is set
+// (DGPP_TRACE=<file> at start-up or Trace::open).
+class Trace {
+ public:
+  static Trace& get() {
+    static Trace t;
+    return t;
+  }
+  bool enabled() const { return f_ != nullptr; }
+  void open(const std::string& path) {
+    std::lock_guard<std::mutex> g(mu_);
+    if (f_) fclose(f_);
+    f_ = path.empty() ? nullptr : fopen(path.c_str(), "w");
+  }
+  void close() { open(""); }
+  static int64_t now_us() {
+    return std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+  }
+  void emit(const std::string& name, int64_t ts_us, int64_t dur_us, const std::string& args_json = "{}") {
+    if (!f_) return;
+    json::Value v = json::Value::object();
+    v.set("name", name);
+    v.set("ts_us", ts_us);
+    v.set("dur_us", dur_us);
+    v.set("tid", static_cast<int64_t>(std::hash<std::thread::id>()(std::this_thread::get_id()) & 0xffff));
+    std::string line = v.dump();
+    line.insert(line.size() - 1, ",\"args\":" + args_json);
+    std::lock_guard<std::mutex> g(mu_);
+    if (f_) { fprintf(f_, "%s\n", line.c_str()); fflush(f_); }
+  }
+
+ private:
+  Trace() {
+    const char* e = getenv("DGPP_TRACE");
+    if (e && *e) f_ = fopen(e, "w");
+  }
+  std::mutex mu_;
+  FILE* f_ = nullptr;
+};
+
+class TraceSpan {
+ public:
+  explicit TraceSpan(std::string name, std::string args_json = "{}")
+      : name_(std::move(name)), args_(std::move(args_json)), t0_(Trace::get().enabled() ? Trace::now_us() : 0) {}
+  ~TraceSpan() {
+    if (Trace::get().enabled()) Trace::get().emit(name_, t0_, Trace::now_us() - t0_, args_);
+  }
+
+ private:
+  std::string name_, args_;
+  int64_t t0_;
+};
+
+// ------------------------------------------------------------------------------------------- CRC-32C (Castagnoli)
+inline uint32_t crc32c(const void* data, size_t n, uint32_t crc = 0) {
+  static uint32_t table[256];
+  static bool init = false;
+  if (!init) {
+    for (uint32_t i = 0; i < 256; ++i) {
+      uint32_t c = i;
+      for (int k = 0; k < 8; ++k) c = (c & 1) ? (c >> 1) ^ 0x82F63B78u : c >> 1;
+      table[i] = c;
+    }
+    init = true;
+  }
+  crc = ~crc;
+  const unsigned char* p = static_cast<const unsigned char*>(data);
+  for (size_t i = 0; i < n; ++i) crc = table[(crc ^ p[i]) & 0xff] ^ (crc >> 8);
+  return ~crc;
+}
+
+// ------------------------------------------------------------------------------------------- watchdogs
+// The engine loop calls progress() whenever it completes a pass; a monitor thread fires `on_stall` once when no
+// progress was seen for `deadline` while work was pending.  Atomics only on the hot side.
+class EngineWatchdog {
+ public:
+  EngineWatchdog(std::chrono::milliseconds deadline, std::function<void(int64_t stalled_ms)> on_stall,
+                 std::chrono::milliseconds poll = std::chrono::milliseconds(50))
+      : deadline_(deadline), poll_(poll), on_stall_(std::move(on_stall)) {
+    last_.store(now_ms());
+    th_ = std::thread([this] { loop(); });
+  }
+  ~EngineWatchdog() {
+    stop_.store(true);
+    if (th_.joinable()) th_.join();
+  }
+  void progress() { last_.store(now_ms()); }
+  void set_busy(bool busy) {
+    if (busy && !busy_.load()) last_.store(now_ms());
+    busy_.store(busy);
+  }
+  bool fired() const { return fired_.load(); }
+
+ private:
+  static int64_t now_ms() {
+    return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+  }
+  void loop() {
+    while (!stop_.load()) {
+      std::this_thread::sleep_for(poll_);
+      if (!busy_.load() || fired_.load()) continue;
+      const int64_t idle = now_ms() - last_.load();
+      if (idle > deadline_.count()) {
+        fired_.store(true);
+        if (on_stall_) on_stall_(idle);
+      }
+    }
+  }
+  std::chrono::milliseconds deadline_, poll_;
+  std::function<void(int64_t)> on_stall_;
+  std::atomic<int64_t> last_{0};
+  std::atomic<bool> busy_{false}, fired_{false}, stop_{false};
+  std::thread th_;
+};
+
+// Armed at shutdown: if the process has not finished within `limit`, `on_timeout` runs (the server's emergency
+// exit).  disarm() on a clean finish.
+class ShutdownWatchdog {
+ public:
+  ShutdownWatchdog(std::chrono::milliseconds limit, std::function<void()> on_timeout)
+      : th_([this, limit, on_timeout] {
+          const auto end = std::chrono::steady_clock::now() + limit;
+          while (!done_.load() && std::chrono::steady_clock::now() < end) std::this_thread::sleep_for(std::chrono::milliseconds(10));
+          if (!done_.load()) { timed_out_.store(true); if (on_timeout) on_timeout(); }
+        }) {}
+  ~ShutdownWatchdog() {
+    done_.store(true);
+    if (th_.joinable()) th_.join();
+  }
+  void disarm() { done_.store(true); }
+  bool timed_out() const { return timed_out_.load(); }
+
+ private:
+  std::atomic<bool> done_{false}, timed_out_{false};
+  std::thread th_;
+};
+
+// ------------------------------------------------------------------------------------------- deployment config
+// Flat JSON deployment description.  Unknown keys are errors (a typo must not silently fall back to a default);
+// digest() is the CRC-32C of the canonical (sorted-key) dump, compared across ranks before serving.
+struct ClusterConfig {
+  std::string model;
+  std::string host = "127.0.0.1";
+  int port = 8000;
+  int tensor_parallel = 1;
+  int expert_parallel = 1;
+  int max_concurrency = 8;
+  int64_t max_context = 32768;
+  int prefill_chunk = 2048;
+  std::string kv_dtype = "fp8";
+  int64_t kv_headroom_mib = 4096;
+  bool prefix_cache = true;
+  int64_t prefix_min_tokens = 16;
+  std::string scheduler_policy = "grow";
+  int mtp_depth = 0;
+  int sampling_candidates = 128;
+  bool fuse_all_reduce = true;
+  std::string log_level = "info";
+
+  static ClusterConfig parse(const std::string& text) {
+    const json::Value v = json::parse(text, /*reject_duplicates=*/true);
+    if (!v.is_object()) throw std::runtime_error("config: the top level must be an object");
+    static const std::set<std::string> known = {
+        "model", "host", "port", "tensor_parallel", "expert_parallel", "max_concurrency", "max_context", "prefill_chunk",
+        "kv_dtype", "kv_headroom_mib", "prefix_cache", "prefix_min_tokens", "scheduler_policy", "mtp_depth",
+        "sampling_candidates", "fuse_all_reduce", "log_level"};
+    for (const auto& kv : v.members())
+      if (!known.count(kv.first)) throw std::runtime_error("config: unknown key '" + kv.first + "'");
+    ClusterConfig c;
+    c.model = v.get_string("model");
+    if (c.model.empty()) throw std::runtime_error("config: 'model' is required");
+    c.host = v.get_string("host", c.host);
+    c.port = static_cast<int>(v.get_int("port", c.port));
+    c.tensor_parallel = static_cast<int>(v.get_int("tensor_parallel", 1));
+    c.expert_parallel = static_cast<int>(v.get_int("expert_parallel", 1));
+    c.max_concurrency = static_cast<int>(v.get_int("max_concurrency", c.max_concurrency));
+    c.max_context = v.get_int("max_context", c.max_context);
+    c.prefill_chunk = static_cast<int>(v.get_int("prefill_chunk", c.prefill_chunk));
+    c.kv_dtype = v.get_string("kv_dtype", c.kv_dtype);
+    c.kv_headroom_mib = v.get_int("kv_headroom_mib", c.kv_headroom_mib);
+    c.prefix_cache = v.get_bool("prefix_cache", true);
+    c.prefix_min_tokens = v.get_int("prefix_min_tokens", c.prefix_min_tokens);
+    c.scheduler_policy = v.get_string("scheduler_policy", c.scheduler_policy);
+    c.mtp_depth = static_cast<int>(v.get_int("mtp_depth", 0));
+    c.sampling_candidates = static_cast<int>(v.get_int("sampling_candidates", 128));
+    c.fuse_all_reduce = v.get_bool("fuse_all_reduce", true);
+    c.log_level = v.get_string("log_level", c.log_level);
+    auto need = [](bool ok, const std::string& what) { if (!ok) throw std::runtime_error("config: " + what); };
+    need(c.port > 0 && c.port < 65536, "port out of range");
+    need(c.tensor_parallel == 1 || c.tensor_parallel == 2 || c.tensor_parallel == 4 || c.tensor_parallel == 8,
+         "tensor_parallel must be 1, 2, 4 or 8");
+    need(c.expert_parallel >= 1 && c.expert_parallel <= 8, "expert_parallel must be 1..8");
+    need(c.max_concurrency >= 1 && c.max_concurrency <= 64, "max_concurrency must be 1..64");
+    need(c.max_context >= 16, "max_context too small");
+    need(c.prefill_chunk >= 16 && c.prefill_chunk % 16 == 0, "prefill_chunk must be a positive multiple of 16");
+    need(c.kv_dtype == "fp8" || c.kv_dtype == "bf16", "kv_dtype must be fp8 or bf16");
+    need(c.scheduler_policy == "grow" || c.scheduler_policy == "reserve", "scheduler_policy must be grow or reserve");
+    need(c.mtp_depth >= 0 && c.mtp_depth <= 5, "mtp_depth must be 0..5");
+    need(c.sampling_candidates >= 1 && c.sampling_candidates <= 256, "sampling_candidates must be 1..256");
+    return c;
+  }
+  json::Value to_json() const {
+    json::Value v = json::Value::object();
+    v.set("expert_parallel", expert_parallel); v.set("fuse_all_reduce", fuse_all_reduce); v.set("host", host);
+    v.set("kv_dtype", kv_dtype); v.set("kv_headroom_mib", kv_headroom_mib); v.set("log_level", log_level);
+    v.set("max_concurrency", max_concurrency); v.set("max_context", max_context); v.set("model", model);
+    v.set("mtp_depth", mtp_depth); v.set("port", port); v.set("prefill_chunk", prefill_chunk);
+    v.set("prefix_cache", prefix_cache); v.set("prefix_min_tokens", prefix_min_tokens);
+    v.set("sampling_candidates", sampling_candidates); v.set("scheduler_policy", scheduler_policy);
+    v.set("tensor_parallel", tensor_parallel);
+    return v;
+  }
+  // Same on every rank iff the engine-relevant settings agree (host / port / log level are per process).
+  uint32_t digest() const {
+    json::Value v = to_json();
+    json::Value f = json::Value::object();
+    for (const auto& kv : v.members())
+      if (kv.first != "host" && kv.first != "port" && kv.first != "log_level") f.set(kv.first, kv.second);
+    const std::string s = f.dump();
+    return crc32c(s.data(), s.size());
+  }
+};
+
+// ------------------------------------------------------------------------------------------- memory plan
+// How many KV blocks fit: free device memory minus head-room minus the activation workspace, divided by the bytes of
+// one block across all layers.
+struct MemoryPlan {
+  int64_t kv_blocks = 0;
+  int64_t kv_bytes = 0;
+  int64_t tokens = 0;
+};
+inline MemoryPlan plan_kv(int64_t free_bytes, int64_t headroom_bytes, int64_t workspace_bytes, int layers, int kv_heads,
+                          int head_dim, int block_tokens, bool fp8, int64_t max_blocks = -1) {
+  const int64_t elem = fp8 ? 1 : 2;
+  const int64_t per_block = static_cast<int64_t>(layers) * 2 * kv_heads * block_tokens * (head_dim * elem + (fp8 ? 4 : 0));
+  const int64_t avail = free_bytes - headroom_bytes - workspace_bytes;
+  MemoryPlan p;
+  if (avail <= 0 || per_block <= 0) return p;
+  p.kv_blocks = avail / per_block;
+  if (max_blocks >= 0 && p.kv_blocks > max_blocks) p.kv_blocks = max_blocks;
+  p.kv_bytes = p.kv_blocks * per_block;
+  p.tokens = p.kv_blocks * block_tokens;
+  return p;
+}
+
+}  // namespace dgpp

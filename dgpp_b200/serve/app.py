@@ -84,6 +84,7 @@ class Server:
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self.failed: Optional[str] = None
+        self._tok_bytes = None
 
     # ------------------------------------------------------------------ lifecycle
     def start(self) -> int:
@@ -200,12 +201,53 @@ class Server:
         self.metrics.c["prompt_tokens_total"] += len(ids)
         if r["stream"]:
             self.http.stream_begin(conn)
+        params, schema = self._sampling_of(r)
         for i in range(r["n"]):
             rid = f"{group}-{i}"
+            if (params is not None or schema is not None) and hasattr(self.engine, "configure"):
+                if params is not None and r["n"] > 1 and r["seed"] is not None:
+                    params = type(params)(**{**params.__dict__, "seed": int(r["seed"]) + i})
+                grammar = None
+                if schema is not None:
+                    grammar = rt.JsonGrammar(schema, self._token_table(), self.eos_ids)
+                self.engine.configure(rid, params, grammar, ids)
             self.live[rid] = _Live(rid, conn, r, i, group, len(ids), created, rt.StreamDecoder(self.tok, True),
                                    rt.StopScanner(list(r["stop"])), t_submit=time.time())
             self.sched.submit(rid, ids, max_tokens, eos_ids=[] if r["ignore_eos"] else self.eos_ids,
                               ignore_eos=r["ignore_eos"], prefix_cache=r["prefix_cache"], cache_key=r["prompt_cache_key"])
+
+    def _token_table(self):
+        """Raw bytes of every vocabulary entry (specials empty): the grammar's view of the tokenizer."""
+        if self._tok_bytes is None:
+            n = self.tok.vocab_size()
+            self._tok_bytes = [b"" if self.tok.is_special(i) else self.tok.token_bytes(i) for i in range(n)]
+        return self._tok_bytes
+
+    def _sampling_of(self, r: dict):
+        """(SamplingParams or None, schema text or None) of a parsed request; None / None = plain greedy."""
+        from ..sampling.device import SamplingParams
+
+        fmt = json.loads(r["response_format_json"])
+        schema = None
+        if isinstance(fmt, dict) and fmt.get("type") == "json_object":
+            schema = ""
+        elif isinstance(fmt, dict) and fmt.get("type") == "json_schema":
+            js = fmt.get("json_schema") or {}
+            schema = json.dumps(js.get("schema", js))
+            try:
+                rt.json_machine_check(schema, b"")
+            except RuntimeError as e:
+                raise rt.ApiError(400, rt.error_json(400, str(e), param="response_format"))
+        plain = (r["temperature"] <= 0 and r["repetition_penalty"] == 1.0 and not r["presence_penalty"]
+                 and not r["frequency_penalty"] and not r["logit_bias"] and not r["logprobs"])
+        if plain:
+            return None, schema
+        seed = r["seed"] if r["seed"] is not None else int(uuid.uuid4().int & 0x7FFFFFFF)
+        return SamplingParams(temperature=r["temperature"], top_k=r["top_k"], top_p=r["top_p"], min_p=r["min_p"],
+                              repetition_penalty=r["repetition_penalty"], presence_penalty=r["presence_penalty"],
+                              frequency_penalty=r["frequency_penalty"], seed=int(seed),
+                              top_logprobs=r["top_logprobs"] if r["logprobs"] else 0,
+                              logit_bias={int(k): float(v) for k, v in r["logit_bias"].items()}), schema
 
     # ------------------------------------------------------------------ events -> responses
     def _drain_events(self) -> None:
