@@ -23,6 +23,7 @@ namespace dgpp {
 constexpr int kGdnCols = 32;      // state columns per CTA
 constexpr int kGdnParts = 8;      // threads per column
 constexpr int kGdnThreads = kGdnCols * kGdnParts;
+constexpr int kGdnChunk = 16;     // tokens staged in shared memory at a time
 
 struct GdnArgs {
   const bf16* q;          // [T, hk * dk]   (after conv + SiLU)
@@ -38,84 +39,119 @@ struct GdnArgs {
   const int32_t* row_slot;   // [T] state slot of each row (decode) or null: all rows belong to `slot`
   int slot;
   bf16* out;              // [T, hv * dv]
+  float* prep;            // scratch: qn [T, hk, dk] | kn [T, hk, dk] | decay [T, hv] | beta [T, hv]
   int T, hk, hv, dk, dv;
   int sequential;         // 1: rows are consecutive tokens of ONE request (prefill); 0: one token per request
 };
 
+// Token-parallel part: unit-norm q (scaled by dk^-1/2) and k per key head, decay and write strength per value head.
+// grid (T, hk + 1): blocks y < hk normalise one key head (dk threads), block y == hk does the per-head scalars.
+template <int DK>
+__global__ void __launch_bounds__(DK) gdn_prep_kernel(GdnArgs a) {
+  __shared__ float red[2][DK / 32];
+  pdl_wait();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  float* qn = a.prep;
+  float* kn = qn + static_cast<size_t>(a.T) * a.hk * DK;
+  float* dec = kn + static_cast<size_t>(a.T) * a.hk * DK;
+  float* bet = dec + static_cast<size_t>(a.T) * a.hv;
+  if (blockIdx.y == static_cast<unsigned>(a.hk)) {
+    for (int h = tid; h < a.hv; h += DK) {
+      const float al = bf16_to_f32(a.alpha[static_cast<size_t>(t) * a.ab_stride + h]) + a.dt_bias[h];
+      const float softplus = al > 20.f ? al : log1pf(expf(al));
+      dec[static_cast<size_t>(t) * a.hv + h] = expf(-expf(a.A_log[h]) * softplus);
+      bet[static_cast<size_t>(t) * a.hv + h] = 1.f / (1.f + expf(-bf16_to_f32(a.beta[static_cast<size_t>(t) * a.ab_stride + h])));
+    }
+    return;
+  }
+  const int h = blockIdx.y;
+  const float qv = bf16_to_f32(a.q[static_cast<size_t>(t) * a.q_stride + h * DK + tid]);
+  const float kv = bf16_to_f32(a.k[static_cast<size_t>(t) * a.k_stride + h * DK + tid]);
+  float q2 = qv * qv, k2 = kv * kv;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    q2 += __shfl_xor_sync(0xffffffffu, q2, o);
+    k2 += __shfl_xor_sync(0xffffffffu, k2, o);
+  }
+  if ((tid & 31) == 0) { red[0][tid >> 5] = q2; red[1][tid >> 5] = k2; }
+  __syncthreads();
+  float qs = 0.f, ks = 0.f;
+#pragma unroll
+  for (int w = 0; w < DK / 32; ++w) { qs += red[0][w]; ks += red[1][w]; }
+  const size_t o = (static_cast<size_t>(t) * a.hk + h) * DK + tid;
+  qn[o] = qv * rsqrtf(qs + 1e-6f) * rsqrtf(static_cast<float>(DK));
+  kn[o] = kv * rsqrtf(ks + 1e-6f);
+}
+
+// Sequential part.  Thread (column j, part p) keeps state rows p, p + 8, p + 16, ... of column j in registers; the
+// normalised keys / queries of kGdnChunk tokens are staged in shared memory (one block-wide sync pair per chunk).
 template <int DK>
 __global__ void __launch_bounds__(kGdnThreads) gdn_recurrent_kernel(GdnArgs a) {
   constexpr int PER = DK / kGdnParts;          // state rows per thread
-  __shared__ float qs[DK], ks[DK];
-  __shared__ float red[2][kGdnThreads / 32];
+  __shared__ float ks[kGdnChunk][DK], qs[kGdnChunk][DK];
+  __shared__ float vs[kGdnChunk][kGdnCols], ds[kGdnChunk], bs[kGdnChunk];
   pdl_wait();
   const int tid = threadIdx.x;
   const int col = tid / kGdnParts, part = tid % kGdnParts;
   const int h = blockIdx.y, j = blockIdx.x * kGdnCols + col;
   const int hk_idx = h / (a.hv / a.hk);        // value heads share key heads in groups
-  const float A = -expf(a.A_log[h]);
-  const float dtb = a.dt_bias[h];
   const int first = a.sequential ? 0 : blockIdx.z;
   const int last = a.sequential ? a.T : blockIdx.z + 1;
   const int slot0 = a.row_slot ? a.row_slot[first] : a.slot;
+  const float* qn = a.prep;
+  const float* kn = qn + static_cast<size_t>(a.T) * a.hk * DK;
+  const float* dec = kn + static_cast<size_t>(a.T) * a.hk * DK;
+  const float* bet = dec + static_cast<size_t>(a.T) * a.hv;
   float* sp = a.state + ((static_cast<size_t>(slot0) * a.hv + h) * DK) * a.dv + j;
   float s[PER];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) s[i] = sp[static_cast<size_t>(part * PER + i) * a.dv];
-  for (int t = first; t < last; ++t) {
-    // ---- unit-norm q, k of this token's key head (all threads cooperate, fixed reduction order)
-    float qv = 0.f, kv = 0.f;
-    if (tid < DK) {
-      qv = bf16_to_f32(a.q[static_cast<size_t>(t) * a.q_stride + hk_idx * DK + tid]);
-      kv = bf16_to_f32(a.k[static_cast<size_t>(t) * a.k_stride + hk_idx * DK + tid]);
+  for (int i = 0; i < PER; ++i) s[i] = sp[static_cast<size_t>(part + kGdnParts * i) * a.dv];
+  for (int t0 = first; t0 < last; t0 += kGdnChunk) {
+    const int n = min(kGdnChunk, last - t0);
+    __syncthreads();                            // the previous chunk's readers are done
+    for (int i = tid; i < n * DK; i += kGdnThreads) {
+      const int tt = i / DK, d = i % DK;
+      const size_t o = (static_cast<size_t>(t0 + tt) * a.hk + hk_idx) * DK + d;
+      ks[tt][d] = kn[o];
+      qs[tt][d] = qn[o];
     }
-    float q2 = qv * qv, k2 = kv * kv;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      q2 += __shfl_xor_sync(0xffffffffu, q2, o);
-      k2 += __shfl_xor_sync(0xffffffffu, k2, o);
+    for (int i = tid; i < n * kGdnCols; i += kGdnThreads) {
+      const int tt = i / kGdnCols, c = i % kGdnCols;
+      vs[tt][c] = bf16_to_f32(a.v[static_cast<size_t>(t0 + tt) * a.v_stride + h * a.dv + blockIdx.x * kGdnCols + c]);
     }
-    __syncthreads();     // previous token's readers of qs / ks / red are done
-    if ((tid & 31) == 0) { red[0][tid >> 5] = q2; red[1][tid >> 5] = k2; }
-    __syncthreads();
-    float qn = 0.f, kn = 0.f;
-#pragma unroll
-    for (int w = 0; w < DK / 32; ++w) { qn += red[0][w]; kn += red[1][w]; }
-    if (tid < DK) {
-      qs[tid] = qv * rsqrtf(qn + 1e-6f) * rsqrtf(static_cast<float>(DK));
-      ks[tid] = kv * rsqrtf(kn + 1e-6f);
+    if (tid < n) {
+      ds[tid] = dec[static_cast<size_t>(t0 + tid) * a.hv + h];
+      bs[tid] = bet[static_cast<size_t>(t0 + tid) * a.hv + h];
     }
     __syncthreads();
-    const float al = bf16_to_f32(a.alpha[static_cast<size_t>(t) * a.ab_stride + h]) + dtb;
-    const float softplus = al > 20.f ? al : log1pf(expf(al));
-    const float decay = expf(A * softplus);
-    const float bt = 1.f / (1.f + expf(-bf16_to_f32(a.beta[static_cast<size_t>(t) * a.ab_stride + h])));
-    const float vt = bf16_to_f32(a.v[static_cast<size_t>(t) * a.v_stride + h * a.dv + j]);
-    // ---- S <- a S ; m = S^T k (this column)
-    float m = 0.f;
+    for (int tt = 0; tt < n; ++tt) {
+      const float decay = ds[tt];
+      float m = 0.f;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      s[i] *= decay;
-      m = fmaf(s[i], ks[part * PER + i], m);
+      for (int i = 0; i < PER; ++i) {
+        s[i] *= decay;
+        m = fmaf(s[i], ks[tt][part + kGdnParts * i], m);
+      }
+#pragma unroll
+      for (int o = kGdnParts / 2; o > 0; o >>= 1) m += __shfl_xor_sync(0xffffffffu, m, o);
+      const float u = bs[tt] * (vs[tt][col] - m);
+      float ov = 0.f;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        s[i] = fmaf(ks[tt][part + kGdnParts * i], u, s[i]);
+        ov = fmaf(s[i], qs[tt][part + kGdnParts * i], ov);
+      }
+#pragma unroll
+      for (int o = kGdnParts / 2; o > 0; o >>= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
+      if (part == 0) a.out[static_cast<size_t>(t0 + tt) * a.hv * a.dv + h * a.dv + j] = f32_to_bf16(ov);
     }
-#pragma unroll
-    for (int o = kGdnParts / 2; o > 0; o >>= 1) m += __shfl_xor_sync(0xffffffffu, m, o);
-    const float u = bt * (vt - m);
-    float ov = 0.f;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      s[i] = fmaf(ks[part * PER + i], u, s[i]);
-      ov = fmaf(s[i], qs[part * PER + i], ov);
-    }
-#pragma unroll
-    for (int o = kGdnParts / 2; o > 0; o >>= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
-    if (part == 0) a.out[static_cast<size_t>(t) * a.hv * a.dv + h * a.dv + j] = f32_to_bf16(ov);
   }
 #pragma unroll
-  for (int i = 0; i < PER; ++i) sp[static_cast<size_t>(part * PER + i) * a.dv] = s[i];
+  for (int i = 0; i < PER; ++i) sp[static_cast<size_t>(part + kGdnParts * i) * a.dv] = s[i];
 }
 
 // Causal depthwise convolution (kernel width W <= 4) + SiLU over channels, with the last W - 1 inputs of every
-// channel carried per state slot.  x: [T, C] bf16 rows; sequential = 1: consecutive tokens of one request.
+// channel carried per state slot (two passes: outputs in parallel over tokens, then the tail update).  x: [T, C] bf16 rows; sequential = 1: consecutive tokens of one request.
 struct ConvArgs {
   const bf16* x;
   int64_t x_stride;
@@ -128,28 +164,43 @@ struct ConvArgs {
   int T, C, W, sequential;
 };
 
+// Output pass, parallel over tokens and channels: out[t, c] = silu(b + sum_i w[i] * X(t - (W - 1) + i)), where X(u)
+// is row u of the chunk for u >= 0 and the carried tail (state) for u < 0.  grid (C / 256, rows).
 __global__ void __launch_bounds__(256) gdn_conv_kernel(ConvArgs a) {
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= a.C) return;
-  float wv[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int i = 0; i < a.W; ++i) wv[i] = bf16_to_f32(a.w[c * a.W + i]);
-  const float b = a.bias ? bf16_to_f32(a.bias[c]) : 0.f;
-  const int first = a.sequential ? 0 : blockIdx.y, last = a.sequential ? a.T : blockIdx.y + 1;
-  const int slot = a.row_slot ? a.row_slot[first] : a.slot;
-  float* st = a.state + static_cast<size_t>(slot) * (a.W - 1) * a.C + c;
-  float hist[3] = {0.f, 0.f, 0.f};             // hist[W - 2] is the newest
-  for (int i = 0; i < a.W - 1; ++i) hist[i] = st[static_cast<size_t>(i) * a.C];
-  for (int t = first; t < last; ++t) {
-    const float xv = bf16_to_f32(a.x[static_cast<size_t>(t) * a.x_stride + c]);
-    float acc = b;
-    for (int i = 0; i < a.W - 1; ++i) acc = fmaf(wv[i], hist[i], acc);
-    acc = fmaf(wv[a.W - 1], xv, acc);
-    a.out[static_cast<size_t>(t) * a.C + c] = f32_to_bf16(acc / (1.f + expf(-acc)));
-    for (int i = 0; i + 1 < a.W - 1; ++i) hist[i] = hist[i + 1];
-    if (a.W > 1) hist[a.W - 2] = xv;
+  const int t = blockIdx.y;
+  const int slot = a.row_slot ? a.row_slot[t] : a.slot;
+  const float* st = a.state + static_cast<size_t>(slot) * (a.W - 1) * a.C + c;
+  float acc = a.bias ? bf16_to_f32(a.bias[c]) : 0.f;
+  for (int i = 0; i < a.W; ++i) {
+    const int u = (a.sequential ? t : 0) - (a.W - 1) + i;       // batched single tokens: only the row itself is new
+    float xv;
+    if (u >= 0) xv = bf16_to_f32(a.x[static_cast<size_t>(a.sequential ? u : t) * a.x_stride + c]);
+    else xv = st[static_cast<size_t>(a.W - 1 + u) * a.C];
+    acc = fmaf(bf16_to_f32(a.w[c * a.W + i]), xv, acc);
   }
-  for (int i = 0; i < a.W - 1; ++i) st[static_cast<size_t>(i) * a.C] = hist[i];
+  a.out[static_cast<size_t>(t) * a.C + c] = f32_to_bf16(acc / (1.f + expf(-acc)));
+}
+
+// State pass (after the output pass): the tail becomes the last W - 1 inputs.  One thread per (channel, request):
+// it reads everything it needs before it writes, so the in-place shift is safe.  grid (C / 256, sequential ? 1 : rows).
+__global__ void __launch_bounds__(256) gdn_conv_state_kernel(ConvArgs a) {
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.C) return;
+  const int r = blockIdx.y;                                     // row (batched mode) or 0
+  const int n = a.sequential ? a.T : 1;                         // new inputs of this request
+  const int slot = a.row_slot ? a.row_slot[r] : a.slot;
+  float* st = a.state + static_cast<size_t>(slot) * (a.W - 1) * a.C + c;
+  float nv[3] = {0.f, 0.f, 0.f};
+  for (int i = 0; i < a.W - 1; ++i) {
+    const int u = n - (a.W - 1) + i;                            // input index that lands in tail position i
+    nv[i] = u >= 0 ? bf16_to_f32(a.x[static_cast<size_t>(a.sequential ? u : r) * a.x_stride + c])
+                   : st[static_cast<size_t>(a.W - 1 + u) * a.C];
+  }
+  for (int i = 0; i < a.W - 1; ++i) st[static_cast<size_t>(i) * a.C] = nv[i];
 }
 
 // out[t, h, :] = rmsnorm(o[t, h, :]) * w * silu(z[t, h, :]); one warp per (row, head).
@@ -181,10 +232,12 @@ using namespace dgpp;
 DGPP_API int dgpp_gdn_recurrent(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
                                 int64_t v_stride, const void* alpha, const void* beta, int64_t ab_stride,
                                 const void* A_log, const void* dt_bias, void* state, const void* row_slot, int slot,
-                                void* out, int T, int hk, int hv, int dk, int dv, int sequential, cudaStream_t st) {
+                                void* out, void* prep, int T, int hk, int hv, int dk, int dv, int sequential,
+                                cudaStream_t st) {
   DGPP_REQUIRE(dk == 64 || dk == 128 || dk == 256, "gdn: key dim %d unsupported", dk);
   DGPP_REQUIRE(dv % kGdnCols == 0 && hk > 0 && hv % hk == 0, "gdn: bad head geometry hk %d hv %d dv %d", hk, hv, dv);
   DGPP_REQUIRE(sequential || row_slot, "gdn: batched single-token rows need row_slot");
+  DGPP_REQUIRE(prep != nullptr, "gdn: scratch of T * (2 * hk * dk + 2 * hv) floats required");
   if (T == 0) return 0;
   GdnArgs a;
   a.q = static_cast<const bf16*>(q); a.k = static_cast<const bf16*>(k); a.v = static_cast<const bf16*>(v);
@@ -195,7 +248,13 @@ DGPP_API int dgpp_gdn_recurrent(const void* q, int64_t q_stride, const void* k, 
   a.row_slot = static_cast<const int32_t*>(row_slot);
   a.slot = slot;
   a.out = static_cast<bf16*>(out);
+  a.prep = static_cast<float*>(prep);
   a.T = T; a.hk = hk; a.hv = hv; a.dk = dk; a.dv = dv; a.sequential = sequential;
+  dim3 pgrid(T, hk + 1);
+  if (dk == 64) gdn_prep_kernel<64><<<pgrid, 64, 0, st>>>(a);
+  else if (dk == 128) gdn_prep_kernel<128><<<pgrid, 128, 0, st>>>(a);
+  else gdn_prep_kernel<256><<<pgrid, 256, 0, st>>>(a);
+  DGPP_CUDA_OK(cudaGetLastError());
   dim3 grid(dv / kGdnCols, hv, sequential ? 1 : T);
   if (dk == 64) gdn_recurrent_kernel<64><<<grid, kGdnThreads, 0, st>>>(a);
   else if (dk == 128) gdn_recurrent_kernel<128><<<grid, kGdnThreads, 0, st>>>(a);
@@ -218,9 +277,12 @@ DGPP_API int dgpp_gdn_conv(const void* x, int64_t x_stride, const void* w, const
   a.slot = slot;
   a.out = static_cast<bf16*>(out);
   a.T = T; a.C = C; a.W = W; a.sequential = sequential;
-  dim3 grid(dgpp_ceil_div(C, 256), sequential ? 1 : T);
-  gdn_conv_kernel<<<grid, 256, 0, st>>>(a);
+  gdn_conv_kernel<<<dim3(dgpp_ceil_div(C, 256), T), 256, 0, st>>>(a);
   DGPP_CUDA_OK(cudaGetLastError());
+  if (W > 1) {
+    gdn_conv_state_kernel<<<dim3(dgpp_ceil_div(C, 256), sequential ? 1 : T), 256, 0, st>>>(a);
+    DGPP_CUDA_OK(cudaGetLastError());
+  }
   return 0;
 }
 

@@ -5,6 +5,7 @@
 
 #include "rt/json_grammar.h"
 #include "rt/speculative.h"
+#include "rt/tool_parser.h"
 
 namespace py = pybind11;
 using namespace dgpp;
@@ -66,4 +67,25 @@ void bind_grammar(py::module_& m) {
     return py::make_tuple(v.accepted, v.emitted, v.keep_length);
   }, py::arg("base"), py::arg("draft"), py::arg("target"), py::arg("stop_ids") = std::vector<int32_t>{},
      py::arg("budget") = int64_t(-1));
+
+  // ---- streaming tool-call parser
+  py::enum_<tools::Format>(m, "ToolFormat").value("JsonTags", tools::Format::JsonTags).value("ArgTags", tools::Format::ArgTags);
+  py::class_<tools::ToolParser>(m, "ToolParser")
+      .def(py::init<tools::Format, std::string>(), py::arg("format"), py::arg("id_prefix") = "call_")
+      .def("calls", &tools::ToolParser::calls)
+      // events: ("content", text) or ("tool_call", index, id, name, arguments_json)
+      .def("feed", [](tools::ToolParser& p, const py::bytes& piece) {
+        py::list out;
+        for (const auto& e : p.feed(std::string(piece))) {
+          if (e.is_call) out.append(py::make_tuple("tool_call", e.index, e.id, e.name, e.arguments));
+          else out.append(py::make_tuple("content", py::bytes(e.text)));
+        }
+        return out;
+      })
+      .def("finish", [](tools::ToolParser& p) {
+        py::list out;
+        for (const auto& e : p.finish()) out.append(py::make_tuple("content", py::bytes(e.text)));
+        return out;
+      });
+  m.def("render_tools_block", [](const std::string& tools_json) { return tools::render_tools_block(json::parse(tools_json)); });
 }

@@ -20,7 +20,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..models.dense import DenseConfig, DenseLayer, DenseModel
+from ..models.dense import DenseConfig, DenseLayer, DenseModel, padded_q_heads
 from ..quant.formats import QuantLinear
 from ..runtime import rt
 
@@ -133,6 +133,29 @@ def _read_linear(ck: OpenCheckpoint, prefix: str, fmt: str, rows: Optional[Tuple
     raise ValueError(f"unsupported weight format {fmt}")
 
 
+def _pad(w: QuantLinear, rows: int = 0, cols: int = 0) -> QuantLinear:
+    """Appends zero rows / zero K columns in storage format (zero codes, zero block scales): padding channels that
+    keep a tensor-parallel shard on the GEMM's K granule contribute exact zeros."""
+    if not rows and not cols:
+        return w
+    assert w.fmt in ("nvfp4", "bf16", "fp32"), "padding is only needed for (and defined on) nvfp4 / unquantised shards"
+    pay, sc = w.payload, w.scale
+    if w.fmt == "nvfp4":
+        sc = sc.view(w.n, w.k // 16)
+        if cols:
+            pay = torch.cat([pay, pay.new_zeros(w.n, cols // 2)], 1)
+            sc = torch.cat([sc, sc.new_zeros(w.n, cols // 16)], 1)
+        if rows:
+            pay = torch.cat([pay, pay.new_zeros(rows, pay.shape[1])])
+            sc = torch.cat([sc, sc.new_zeros(rows, sc.shape[1])])
+        return QuantLinear(w.fmt, w.n + rows, w.k + cols, pay.contiguous(), sc.contiguous(), w.alpha)
+    if cols:
+        pay = torch.cat([pay, pay.new_zeros(w.n, cols)], 1)
+    if rows:
+        pay = torch.cat([pay, pay.new_zeros(rows, pay.shape[1])])
+    return QuantLinear(w.fmt, w.n + rows, w.k + cols, pay.contiguous())
+
+
 def _cat(parts: List[QuantLinear]) -> QuantLinear:
     """Stack projections along N (q|k|v, gate|up).  NVFP4 tensors keep their own global scale, so differing
     globals are folded into the e4m3 block scales only when they are equal; otherwise the caller keeps them apart."""
@@ -158,6 +181,9 @@ def load_dense(spec: str, device="cuda", tp_rank: int = 0, tp_size: int = 1, wei
         return ck.tensor(name).to(adt).to(dev)
 
     fmt = cfg.weight_fmt
+    # the same padding DenseModel.random_init applies to tensor-parallel NVFP4 shards
+    q_pad = (padded_q_heads(cfg, W) - hq_l) * d
+    ffn_pad = (-ffn_l) % 256 if (W > 1 and fmt == "nvfp4") else 0
     layers = []
     for i in range(cfg.layers):
         p = f"model.layers.{i}."
@@ -171,7 +197,8 @@ def load_dense(spec: str, device="cuda", tp_rank: int = 0, tp_size: int = 1, wei
         qn = vec(p + "self_attn.q_norm.weight") if cfg.qk_norm and ck.has(p + "self_attn.q_norm.weight") else None
         kn = vec(p + "self_attn.k_norm.weight") if cfg.qk_norm and ck.has(p + "self_attn.k_norm.weight") else None
         layers.append(DenseLayer(vec(p + "input_layernorm.weight"), vec(p + "post_attention_layernorm.weight"),
-                                 _cat([q, k, v]), o, _cat([g, u]), dn, qn, kn))
+                                 _cat([_pad(q, rows=q_pad), k, v]), _pad(o, cols=q_pad),
+                                 _cat([_pad(g, rows=ffn_pad), _pad(u, rows=ffn_pad)]), _pad(dn, cols=ffn_pad), qn, kn))
     embed = vec("model.embed_tokens.weight")
     head_name = "lm_head" if ck.has("lm_head.weight") else "model.embed_tokens"
     head = _read_linear(ck, head_name, cfg.head_fmt, (r * vl, (r + 1) * vl), None, dev)

@@ -108,12 +108,14 @@ class DenseModel:
         def full(n, k):
             return torch.randn(n, k, device=device, dtype=torch.float32, generator=g) * std
 
-        def make(n, k, fmt, row_slices=None, col_slice=None, pad_rows=0, pad_cols=0):
+        def make(n, k, fmt, row_slices=None, col_slice=None, pad_rows=0, pad_cols=0, pad_first=0):
             w = full(n, k)
             if W > 1 and row_slices is not None:
                 parts = [w[a:b] for a, b in row_slices]
                 if pad_rows:   # zero rows after every slice (the padded intermediate channels stay exactly zero)
                     parts = [torch.cat([q, q.new_zeros(pad_rows, k)]) for q in parts]
+                if pad_first:  # zero rows after the first slice only (padding query heads)
+                    parts[0] = torch.cat([parts[0], parts[0].new_zeros(pad_first, k)])
                 w = torch.cat(parts)
             if W > 1 and col_slice is not None:
                 w = w[:, col_slice[0]:col_slice[1]]
@@ -126,6 +128,7 @@ class DenseModel:
         # a rank's slice of the intermediate dimension is padded with zero channels up to the K granule of the
         # block-scaled tensor-core GEMM (256), e.g. 17408 / 8 = 2176 -> 2304
         ffn_pad = (-ffn_l) % 256 if (W > 1 and cfg.weight_fmt == "nvfp4") else 0
+        q_pad = (padded_q_heads(cfg, W) - hq_l) * d
         r = tp_rank
         adt = torch.float32 if cfg.weight_fmt == "fp32" else BF
         embed = (torch.randn(cfg.vocab, H, device=device, dtype=torch.float32, generator=g) * std).to(adt)
@@ -133,11 +136,11 @@ class DenseModel:
         ones = lambda n: torch.ones(n, device=device, dtype=adt)
         for _ in range(cfg.layers):
             nq, nkv = cfg.q_heads * d, cfg.kv_heads * d
-            qkv = make(nq + 2 * nkv, H, cfg.weight_fmt,
+            qkv = make(nq + 2 * nkv, H, cfg.weight_fmt, pad_first=q_pad,
                        row_slices=[(r * hq_l * d, (r + 1) * hq_l * d),
                                    (nq + r * hkv_l * d, nq + (r + 1) * hkv_l * d),
                                    (nq + nkv + r * hkv_l * d, nq + nkv + (r + 1) * hkv_l * d)])
-            o = make(H, nq, cfg.weight_fmt, col_slice=(r * hq_l * d, (r + 1) * hq_l * d))
+            o = make(H, nq, cfg.weight_fmt, col_slice=(r * hq_l * d, (r + 1) * hq_l * d), pad_cols=q_pad)
             gu = make(2 * cfg.ffn, H, cfg.weight_fmt, pad_rows=ffn_pad,
                       row_slices=[(r * ffn_l, (r + 1) * ffn_l), (cfg.ffn + r * ffn_l, cfg.ffn + (r + 1) * ffn_l)])
             dn = make(H, cfg.ffn, cfg.weight_fmt, col_slice=(r * ffn_l, (r + 1) * ffn_l), pad_cols=ffn_pad)
@@ -157,7 +160,8 @@ class DenseModel:
 
     @property
     def hq_local(self) -> int:
-        return self.cfg.q_heads // self.tp_size
+        """Query heads computed on this rank, padding heads included (see `padded_q_heads`)."""
+        return padded_q_heads(self.cfg, self.tp_size)
 
     @property
     def hkv_local(self) -> int:
@@ -222,6 +226,20 @@ class DenseModel:
             return xn, kv
         logits = ref.linear(xn, self.head, out_fp32=True)
         return logits, kv
+
+
+def padded_q_heads(cfg: "DenseConfig", tp_size: int) -> int:
+    """Local query heads.  With NVFP4 weights under tensor parallelism the o_proj K dimension (heads * head_dim)
+    must be a multiple of the block-scaled GEMM's K granule (256) and the q-per-kv group one the tensor-core
+    attention supports; otherwise zero heads are appended (zero q rows in qkv, zero columns in o_proj: they add
+    exact zeros).  40 heads / 8 ranks = 5 heads of 128 (K = 640) becomes 8 heads (K = 1024)."""
+    hq, hkv = cfg.q_heads // tp_size, max(cfg.kv_heads // tp_size, 1)
+    if tp_size == 1 or cfg.weight_fmt != "nvfp4" or (hq * cfg.head_dim) % 256 == 0:
+        return hq
+    for cand in range(hq + 1, 8 * hkv + 1):
+        if (cand * cfg.head_dim) % 256 == 0 and cand % hkv == 0 and cand // hkv in (1, 2, 4, 5, 8):
+            return cand
+    return hq
 
 
 def quantize_like_random(w: torch.Tensor, fmt: str, std: float) -> QuantLinear:

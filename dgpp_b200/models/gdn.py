@@ -134,6 +134,7 @@ class GdnLayer:
         e = lambda *s: torch.empty(*s, dtype=BF, device=device)
         self.proj, self.conv = e(max_rows, c.proj_cols), e(max_rows, c.conv_channels)
         self.o, self.gated = e(max_rows, c.v_heads * c.dv), e(max_rows, c.v_heads * c.dv)
+        self.prep = torch.empty(max_rows * (2 * c.k_heads * c.dk + 2 * c.v_heads), dtype=torch.float32, device=device)
 
     def forward(self, x: torch.Tensor, state: GdnState, out: torch.Tensor, slot: int = 0,
                 row_slot: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -146,6 +147,6 @@ class GdnLayer:
         mixed, z, al, be, nq, nv = _split(c, proj)
         conv = ops.gdn_conv(mixed, w.conv_w, w.conv_b, state.conv, self.conv[:rows], row_slot, slot, seq)
         ops.gdn_recurrent(conv[:, :nq], conv[:, nq:2 * nq], conv[:, 2 * nq:], al, be, w.A_log, w.dt_bias, state.ssm,
-                          self.o[:rows], c.k_heads, c.v_heads, c.dk, c.dv, row_slot, slot, seq)
+                          self.o[:rows], c.k_heads, c.v_heads, c.dk, c.dv, row_slot, slot, seq, prep=self.prep)
         ops.gated_rmsnorm(self.o[:rows], z, w.norm_w, self.gated[:rows], c.v_heads, c.dv, c.eps)
         return ops.linear(self.gated[:rows], w.out_proj, out=out)

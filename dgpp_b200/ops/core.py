@@ -376,7 +376,7 @@ def gemm_fp4_grouped(xa: "QuantAct", wq, wsf_tiled, alphas, out, rows: int, n: i
 
 
 # ---------------------------------------------------------------------------------------------- gated delta net
-_lib.declare("dgpp_gdn_recurrent", [P, L, P, L, P, L, P, P, L, P, P, P, P, I, P, I, I, I, I, I, I, P])
+_lib.declare("dgpp_gdn_recurrent", [P, L, P, L, P, L, P, P, L, P, P, P, P, I, P, P, I, I, I, I, I, I, P])
 _lib.declare("dgpp_gdn_conv", [P, L, P, P, P, P, I, P, I, I, I, I, P])
 _lib.declare("dgpp_gated_rmsnorm", [P, P, L, P, P, I, I, I, F, P])
 
@@ -391,14 +391,17 @@ def gdn_conv(x, w, bias, state, out, row_slot=None, slot: int = 0, sequential: b
 
 
 def gdn_recurrent(q, k, v, alpha, beta, A_log, dt_bias, state, out, hk: int, hv: int, dk: int, dv: int, row_slot=None,
-                  slot: int = 0, sequential: bool = True):
+                  slot: int = 0, sequential: bool = True, prep=None):
     """Gated delta-rule recurrence.  q/k: [T, hk*dk], v: [T, hv*dv] (column views allowed), alpha/beta: [T, hv]
     views with a common row stride; state [slots, hv, dk, dv] fp32 updated in place; out [T, hv*dv] bf16."""
     T = q.shape[0]
     assert alpha.stride(0) == beta.stride(0)
+    need = T * (2 * hk * dk + 2 * hv)
+    if prep is None or prep.numel() < need:
+        prep = torch.empty(need, dtype=torch.float32, device=q.device)
     call("dgpp_gdn_recurrent", ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0), ptr(alpha), ptr(beta),
-         alpha.stride(0), ptr(A_log), ptr(dt_bias), ptr(state), ptr(row_slot), slot, ptr(out), T, hk, hv, dk, dv,
-         int(sequential), stream_ptr())
+         alpha.stride(0), ptr(A_log), ptr(dt_bias), ptr(state), ptr(row_slot), slot, ptr(out), ptr(prep), T, hk, hv, dk,
+         dv, int(sequential), stream_ptr())
     return out
 
 

@@ -40,6 +40,8 @@ class _Live:
     cached: int = 0
     first_chunk: bool = True
     finish: str = ""
+    tool_parser: object = None
+    tool_calls: list = field(default_factory=list)
     t_submit: float = 0.0
     t_first: float = 0.0
 
@@ -69,12 +71,13 @@ class Metrics:
 class Server:
     def __init__(self, engine, tokenizer, template_src: str = DEFAULT_TEMPLATE, model_name: str = "dgpp-b200",
                  host: str = "127.0.0.1", port: int = 0, eos_ids: Optional[List[int]] = None,
-                 default_max_tokens: int = 256, sched_config=None):
+                 default_max_tokens: int = 256, sched_config=None, tool_format=None):
         self.engine, self.tok = engine, tokenizer
         self.template = rt.ChatTemplate(template_src)
         self.model_name = model_name
         self.eos_ids = eos_ids or []
         self.default_max_tokens = default_max_tokens
+        self.tool_format = tool_format or rt.ToolFormat.JsonTags
         self.sched = rt.Scheduler(engine, sched_config or rt.SchedulerConfig())
         self.http = rt.HttpServer(host, port)
         self.live: Dict[str, _Live] = {}
@@ -213,6 +216,8 @@ class Server:
                 self.engine.configure(rid, params, grammar, ids)
             self.live[rid] = _Live(rid, conn, r, i, group, len(ids), created, rt.StreamDecoder(self.tok, True),
                                    rt.StopScanner(list(r["stop"])), t_submit=time.time())
+            if chat and r["tools_json"] not in ("null", "[]") and json.loads(r["tool_choice_json"]) != "none":
+                self.live[rid].tool_parser = rt.ToolParser(self.tool_format, f"call_{uuid.uuid4().hex[:12]}_")
             self.sched.submit(rid, ids, max_tokens, eos_ids=[] if r["ignore_eos"] else self.eos_ids,
                               ignore_eos=r["ignore_eos"], prefix_cache=r["prefix_cache"], cache_key=r["prompt_cache_key"])
 
@@ -277,13 +282,36 @@ class Server:
                 if not lv.finish:
                     tail = lv.scanner.feed(lv.decoder.flush())
                     tail += lv.scanner.flush()
-                    self._emit(lv, g, tail)
+                    self._emit(lv, g, tail, final=True)
                     lv.finish = {"length": "length", "stop": "stop", "cancelled": "stop", "error": "error"}.get(why, why)
                     if why == "cancelled":
                         self.metrics.c["cancelled_total"] += 1
                 self._finish(lv, g)
 
-    def _emit(self, lv: _Live, g: dict, piece: bytes) -> None:
+    def _emit(self, lv: _Live, g: dict, piece: bytes, final: bool = False) -> None:
+        """Routes generated text: plain content is streamed / collected; with tools enabled the text first goes
+        through the streaming tool-call parser, whose calls become `tool_calls` deltas."""
+        if lv.tool_parser is None:
+            self._emit_content(lv, g, piece)
+            return
+        events = lv.tool_parser.feed(piece) if piece else []
+        if final:
+            events = list(events) + list(lv.tool_parser.finish())
+        for ev in events:
+            if ev[0] == "content":
+                self._emit_content(lv, g, ev[1])
+            else:
+                _, index, call_id, name, arguments = ev
+                call = {"id": call_id, "type": "function", "function": {"name": name, "arguments": arguments}}
+                lv.tool_calls.append(call)
+                if g["stream"]:
+                    delta = json.dumps([{"index": index, **call}])
+                    evt = rt.chunk_event(g["chat"], lv.group, self.model_name, lv.created, lv.index, "",
+                                         role_delta=lv.first_chunk and g["chat"], tool_calls_json=delta)
+                    lv.first_chunk = False
+                    self.http.stream_send(lv.conn, evt.encode())
+
+    def _emit_content(self, lv: _Live, g: dict, piece: bytes) -> None:
         if not piece and not (g["stream"] and lv.first_chunk and g["chat"]):
             return
         lv.text += piece
@@ -294,10 +322,13 @@ class Server:
             self.http.stream_send(lv.conn, ev.encode())
 
     def _finish(self, lv: _Live, g: dict) -> None:
+        if lv.tool_calls and lv.finish == "stop":
+            lv.finish = "tool_calls"
         if g["stream"]:
             ev = rt.chunk_event(g["chat"], lv.group, self.model_name, lv.created, lv.index, "", finish_reason=lv.finish)
             self.http.stream_send(lv.conn, ev.encode())
-        g["choices"][lv.index] = (lv.index, lv.text.decode("utf-8", "replace"), lv.finish)
+        g["choices"][lv.index] = (lv.index, lv.text.decode("utf-8", "replace"), lv.finish,
+                                  json.dumps(lv.tool_calls) if lv.tool_calls else "")
         g["done"] += 1
         g.setdefault("completion_tokens", 0)
         g["completion_tokens"] += lv.tokens

@@ -26,8 +26,8 @@ def test_hybrid_runner_matches_reference(dev, moe):
     g = torch.Generator().manual_seed(1)
     a = torch.randint(0, cfg.vocab, (50,), generator=g).tolist()
     b = torch.randint(0, cfg.vocab, (23,), generator=g).tolist()
-    la = r.prefill(1, a[:40], chunk=16)              # three chunks
-    lb = r.prefill(2, b[:20], chunk=64)
+    la = r.prefill(1, a[:40], chunk=16).clone()      # three chunks (the runner returns a view of its logits buffer)
+    lb = r.prefill(2, b[:20], chunk=64).clone()
     want_a = m.forward_reference(torch.tensor(a, device=dev))
     want_b = m.forward_reference(torch.tensor(b, device=dev))
     torch.cuda.synchronize()

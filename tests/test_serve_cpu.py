@@ -121,3 +121,68 @@ def test_metrics(server):
     st, data = _req(port, "GET", "/metrics/prometheus")
     text = data.decode()
     assert "dgpp_b200_requests_total 1" in text and "time_to_first_token_seconds_count 1" in text
+
+
+def test_tool_calls_are_parsed_from_generated_text():
+    """An engine that 'generates' a fixed text with a tool call: the server must return it as tool_calls."""
+    tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)], rt.SplitPattern.Qwen2)
+    script = b'Checking.\n<tool_call>\n{"name": "get_weather", "arguments": {"city": "Oslo"}}\n</tool_call>'
+    script_ids = list(script) + [257]
+
+    class Engine(rt.SchedulerEngine):
+        def __init__(self):
+            super().__init__()
+            self.pos = {}
+            self.blocks = {}
+        def max_concurrent(self): return 2
+        def block_tokens(self): return 16
+        def total_blocks(self): return 512
+        def free_blocks(self): return 512 - sum(len(b) for b in self.blocks.values())
+        def max_context(self): return 4096
+        def reserve(self, slot, tokens):
+            need = (tokens + 15) // 16
+            cur = self.blocks.setdefault(slot, [])
+            while len(cur) < need:
+                cur.append(len(cur) + slot * 256)
+            return True
+        def attach_prefix(self, slot, blocks): self.blocks[slot] = list(blocks)
+        def prefill(self, slot, tokens, pos, last):
+            self.pos[slot] = 0
+            return script_ids[0] if last else -1
+        def step_batch(self, slots):
+            out = []
+            for s in slots:
+                self.pos[s] += 1
+                out.append([script_ids[min(self.pos[s], len(script_ids) - 1)]])
+            return out
+        def slot_blocks(self, slot): return list(self.blocks.get(slot, []))
+        def retain_block(self, b): pass
+        def release_block(self, b): pass
+        def block_refcount(self, b): return 1
+        def close(self, slot): self.blocks.pop(slot, None)
+
+    srv = Server(Engine(), tok, model_name="scripted", eos_ids=[257])
+    port = srv.start()
+    try:
+        req = {"model": "scripted", "messages": [{"role": "user", "content": "weather?"}], "max_tokens": 200,
+               "tools": [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object"}}}]}
+        st, data = _req(port, "POST", "/v1/chat/completions", json.dumps(req))
+        j = json.loads(data)
+        ch = j["choices"][0]
+        assert st == 200 and ch["finish_reason"] == "tool_calls"
+        assert ch["message"]["content"] == "Checking.\n"
+        call = ch["message"]["tool_calls"][0]
+        assert call["function"]["name"] == "get_weather" and json.loads(call["function"]["arguments"]) == {"city": "Oslo"}
+        # streaming: the call arrives as one tool_calls delta, then finish_reason tool_calls
+        st, data = _req(port, "POST", "/v1/chat/completions", json.dumps({**req, "stream": True}))
+        events = [json.loads(e[6:]) for e in data.decode().split("\n\n") if e.startswith("data: {")]
+        deltas = [c["choices"][0]["delta"] for c in events if c["choices"]]
+        calls = [d["tool_calls"][0] for d in deltas if d.get("tool_calls")]
+        assert len(calls) == 1 and calls[0]["function"]["name"] == "get_weather" and calls[0]["index"] == 0
+        assert "".join(d.get("content") or "" for d in deltas) == "Checking.\n"
+        assert [c["choices"][0]["finish_reason"] for c in events if c["choices"]][-1] == "tool_calls"
+        # without tools in the request the same text is plain content
+        st, data = _req(port, "POST", "/v1/chat/completions", json.dumps({k: v for k, v in req.items() if k != "tools"}))
+        assert "<tool_call>" in json.loads(data)["choices"][0]["message"]["content"]
+    finally:
+        srv.stop()
