@@ -16,6 +16,7 @@
 #include "common/common.h"
 #include "common/dtypes.cuh"
 #include "common/ptx.cuh"
+#include "kernels/comm.cuh"
 
 namespace dgpp {
 
@@ -150,7 +151,8 @@ __global__ void __launch_bounds__(kRouterThreads) moe_router_kernel(RouterArgs a
 
 // ids: [T, k].  list: [slots] ascending active experts then -1; slot_of: [E]; n_active: [1].
 __global__ void __launch_bounds__(512) moe_active_kernel(const int32_t* ids, int T, int k, int E, int slots,
-                                                         int32_t* list, int32_t* slot_of, int32_t* n_active) {
+                                                         int32_t* list, int32_t* slot_of, int32_t* n_active, int e_begin,
+                                                         int e_end) {
   __shared__ int flag[kMoeMaxExperts];
   pdl_wait();
   const int tid = threadIdx.x;
@@ -164,7 +166,8 @@ __global__ void __launch_bounds__(512) moe_active_kernel(const int32_t* ids, int
   if (tid == 0) {
     int n = 0;
     for (int e = 0; e < E; ++e) {
-      if (flag[e] && n < slots) { list[n] = e; slot_of[e] = n; ++n; } else { slot_of[e] = -1; }
+      // expert parallelism: only experts [e_begin, e_end) live here; the list holds LOCAL indices (e - e_begin)
+      if (flag[e] && e >= e_begin && e < e_end && n < slots) { list[n] = e - e_begin; slot_of[e] = n; ++n; } else { slot_of[e] = -1; }
     }
     *n_active = n;
     for (int s = n; s < slots; ++s) list[s] = -1;
@@ -205,6 +208,54 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
   *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + v * 8) = o.u;
 }
 
+// Expert-parallel combine fused with the all-reduce push: every rank holds a slice of the experts and computes, for
+// ALL tokens, the weighted sum over ITS experts; instead of writing that partial locally, the CTA owning a 128-column
+// tile stores it into slot `rank` of every rank's symmetric region and raises the tile flag there (the protocol of
+// the tensor-parallel GEMM push).  The consumer is the fold + add + RMSNorm + quantise kernel of the next layer, so
+// the combine, the cross-rank sum and the next norm need no separate collective launch.
+// Experts that live on other ranks have slot_of[e] < 0 here and are skipped; `shared` is added by the rank that owns it.
+// grid (H / 128), 128 threads; rows <= 16.
+__global__ void __launch_bounds__(128) moe_combine_push_kernel(const bf16* __restrict__ y, const bf16* __restrict__ shared,
+                                                               const int32_t* __restrict__ ids, const float* __restrict__ w,
+                                                               const int32_t* __restrict__ slot_of, CommState comm, int T,
+                                                               int H, int k, int rows_per_slot) {
+  pdl_wait();
+  const uint32_t epoch = *comm.epoch + 1;
+  const int parity = epoch & 1;
+  const int col0 = blockIdx.x * 128;
+  for (int idx = threadIdx.x; idx < T * 16; idx += blockDim.x) {
+    const int t = idx / 16, c = col0 + (idx % 16) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int i = 0; i < k; ++i) {
+      const int s = slot_of[ids[t * k + i]];
+      if (s < 0) continue;
+      const float wi = w[t * k + i];
+      Pack16 p;
+      p.u = *reinterpret_cast<const uint4*>(y + (static_cast<size_t>(s) * rows_per_slot + t) * H + c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(wi, bf16_to_f32(p.h[j]), acc[j]);
+    }
+    if (shared) {
+      Pack16 p;
+      p.u = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * H + c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += bf16_to_f32(p.h[j]);
+    }
+    Pack16 o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o.h[j] = f32_to_bf16(acc[j]);
+    for (int r = 0; r < comm.world; ++r) {
+      const int dst = (comm.rank + r) % comm.world;
+      st_v4_global(payload(comm, dst, parity, comm.rank) + (static_cast<size_t>(t) * H + c) * 2, o.u);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < comm.world) st_release_sys(flag(comm, threadIdx.x, parity, comm.rank, blockIdx.x), epoch);
+}
+
 }  // namespace dgpp
 
 using namespace dgpp;
@@ -232,10 +283,11 @@ DGPP_API int dgpp_moe_route(const void* x, int64_t x_stride, const void* gate, c
 }
 
 DGPP_API int dgpp_moe_active(const void* ids, int T, int k, int E, int slots, void* list, void* slot_of, void* n_active,
-                             cudaStream_t st) {
+                             int e_begin, int e_end, cudaStream_t st) {
   DGPP_REQUIRE(E >= 1 && E <= kMoeMaxExperts && slots >= 1, "moe_active: bad sizes");
   moe_active_kernel<<<1, 512, 0, st>>>(static_cast<const int32_t*>(ids), T, k, E, slots, static_cast<int32_t*>(list),
-                                       static_cast<int32_t*>(slot_of), static_cast<int32_t*>(n_active));
+                                       static_cast<int32_t*>(slot_of), static_cast<int32_t*>(n_active), e_begin,
+                                       e_end > 0 ? e_end : E);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -249,6 +301,21 @@ DGPP_API int dgpp_moe_combine(const void* y, const void* shared, const void* ids
                                            static_cast<const int32_t*>(ids), static_cast<const float*>(w),
                                            static_cast<const int32_t*>(slot_of), static_cast<bf16*>(out), T, H, k,
                                            rows_per_slot);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Expert-parallel form of dgpp_moe_combine: pushes this rank's partial to every rank (see moe_combine_push_kernel).
+DGPP_API int dgpp_moe_combine_push(const void* y, const void* shared, const void* ids, const void* w, const void* slot_of,
+                                   void* comm, int T, int H, int k, int rows_per_slot, cudaStream_t st) {
+  DGPP_REQUIRE(comm != nullptr, "moe_combine_push: communicator required");
+  const DgppComm* c = static_cast<const DgppComm*>(comm);
+  DGPP_REQUIRE(T >= 1 && T <= 16, "moe_combine_push: %d rows outside 1..16", T);
+  DGPP_REQUIRE(H % 128 == 0 && H / 128 <= kCommMaxCtas && static_cast<size_t>(T) * H * 2 <= c->st.slot_bytes,
+               "moe_combine_push: %d x %d does not fit the symmetric slot / flag table", T, H);
+  moe_combine_push_kernel<<<H / 128, 128, 0, st>>>(static_cast<const bf16*>(y), static_cast<const bf16*>(shared),
+                                                   static_cast<const int32_t*>(ids), static_cast<const float*>(w),
+                                                   static_cast<const int32_t*>(slot_of), c->st, T, H, k, rows_per_slot);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }

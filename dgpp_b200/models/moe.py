@@ -56,21 +56,36 @@ class MoEWeights:
     down_q: Optional[torch.Tensor] = None
     down_sf: Optional[torch.Tensor] = None
     down_alpha: Optional[torch.Tensor] = None
+    # expert parallelism: this rank holds experts [e_begin, e_end) (experts_gu / experts_down are that slice); the
+    # router weights are replicated; the shared expert lives on rank 0
+    e_begin: int = 0
+    e_end: int = 0
 
     @staticmethod
-    def random_init(cfg: MoEConfig, device, seed: int = 0, std: float = 0.02, fmt: str = "nvfp4") -> "MoEWeights":
+    def random_init(cfg: MoEConfig, device, seed: int = 0, std: float = 0.02, fmt: str = "nvfp4", ep_rank: int = 0,
+                    ep_size: int = 1) -> "MoEWeights":
+        """Every rank draws all experts from the same seed and keeps its contiguous block, so the union over ranks
+        is the model a single rank would build."""
+        from ..runtime import rt
+
         g = torch.Generator(device=device)
         g.manual_seed(seed)
         rnd = lambda n, k: torch.randn(n, k, device=device, dtype=torch.float32, generator=g) * std
         gate = (rnd(cfg.experts, cfg.hidden) * 4).to(BF)
         bias = torch.randn(cfg.experts, device=device, generator=g) * 0.05
-        gu = [quantize_like_random(rnd(2 * cfg.moe_ffn, cfg.hidden), fmt, std) for _ in range(cfg.experts)]
-        dn = [quantize_like_random(rnd(cfg.hidden, cfg.moe_ffn), fmt, std) for _ in range(cfg.experts)]
+        e0, e1 = rt.expert_slice(cfg.experts, ep_size, ep_rank)
+        gu, dn = [], []
+        for e in range(cfg.experts):
+            a, b = rnd(2 * cfg.moe_ffn, cfg.hidden), rnd(cfg.hidden, cfg.moe_ffn)
+            if e0 <= e < e1:
+                gu.append(quantize_like_random(a, fmt, std))
+                dn.append(quantize_like_random(b, fmt, std))
         sgu = sdn = None
         if cfg.shared_ffn:
-            sgu = quantize_like_random(rnd(2 * cfg.shared_ffn, cfg.hidden), fmt, std)
-            sdn = quantize_like_random(rnd(cfg.hidden, cfg.shared_ffn), fmt, std)
-        w = MoEWeights(cfg, gate, bias, gu, dn, sgu, sdn)
+            a, b = rnd(2 * cfg.shared_ffn, cfg.hidden), rnd(cfg.hidden, cfg.shared_ffn)
+            if ep_rank == 0:
+                sgu, sdn = quantize_like_random(a, fmt, std), quantize_like_random(b, fmt, std)
+        w = MoEWeights(cfg, gate, bias, gu, dn, sgu, sdn, e_begin=e0, e_end=e1)
         if fmt == "nvfp4" and torch.device(device).type == "cuda":
             w.stack()
         return w
@@ -118,11 +133,14 @@ def moe_reference(x: torch.Tensor, w: MoEWeights, ids=None, wts=None) -> torch.T
         ids, wts, _ = route_reference(x, w)
     T = x.shape[0]
     acc = torch.zeros(T, c.hidden, dtype=torch.float32, device=x.device)
+    e0, e1 = w.e_begin, (w.e_end or c.experts)
     for e in sorted(set(ids.flatten().tolist())):
+        if not (e0 <= e < e1):
+            continue                      # another rank's expert
         rows = (ids == e).any(-1).nonzero().flatten()
         xe = x[rows]
-        h = ref.linear(xe, w.experts_gu[e])
-        y = ref.linear(ref.swiglu(h, c.swiglu_limit), w.experts_down[e])
+        h = ref.linear(xe, w.experts_gu[e - e0])
+        y = ref.linear(ref.swiglu(h, c.swiglu_limit), w.experts_down[e - e0])
         we = (wts * (ids == e)).sum(-1)[rows]
         acc[rows] += we.unsqueeze(-1) * y.float()
     if w.shared_gu is not None:
@@ -140,7 +158,9 @@ class MoEBlock:
         self.bn = 16 if max_rows <= 16 else (32 if max_rows <= 32 else 64)
         assert max_rows <= self.bn and act_terms * self.bn <= 256
         self.max_rows = max_rows
-        self.slots = min(c.experts, max_rows * c.top_k)
+        self.e0, self.e1 = w.e_begin, (w.e_end or c.experts)
+        self.local_experts = self.e1 - self.e0
+        self.slots = min(self.local_experts, max_rows * c.top_k)
         i32 = dict(dtype=torch.int32, device=device)
         self.ids = torch.zeros(max_rows, c.top_k, **i32)
         self.wts = torch.zeros(max_rows, c.top_k, dtype=torch.float32, device=device)
@@ -157,9 +177,12 @@ class MoEBlock:
             self.sh_gu = torch.zeros(max_rows, 2 * c.shared_ffn, dtype=BF, device=device)
             self.qa_sh = ops.QuantAct(self.bn, c.shared_ffn, act_terms, self.bn, device)
 
-    def forward(self, xn: torch.Tensor, out: torch.Tensor, xa: Optional[ops.QuantAct] = None) -> torch.Tensor:
+    def forward(self, xn: torch.Tensor, out: Optional[torch.Tensor], xa: Optional[ops.QuantAct] = None,
+                push_comm=None) -> Optional[torch.Tensor]:
         """xn: [rows, H] bf16 normed hidden; xa: its NVFP4 terms when the caller's norm kernel already produced
-        them.  out: [rows, H] bf16."""
+        them.  out: [rows, H] bf16.  push_comm (expert parallelism): native peer communicator; this rank's partial
+        sum over ITS experts is then pushed to every rank instead of being written to `out` (the next layer's
+        fold + add + RMSNorm + quantise kernel sums the ranks)."""
         c, w = self.c, self.w
         rows = xn.shape[0]
         assert rows <= self.max_rows
@@ -167,12 +190,13 @@ class MoEBlock:
             xa = ops.act_quant_nvfp4(xn, self.terms, out=self.qa_in)
         ops.moe_route(xn, w.gate, w.bias, c.top_k, c.n_group, c.topk_group, c.router == "softmax", c.norm_topk_prob,
                       c.routed_scaling, ids=self.ids[:rows], weights=self.wts[:rows])
-        ops.moe_active(self.ids[:rows], rows, c.experts, self.slots, self.group_list, self.slot_of, self.n_active)
-        ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, self.h, rows, 2 * c.moe_ffn, c.hidden, c.experts,
+        ops.moe_active(self.ids[:rows], rows, c.experts, self.slots, self.group_list, self.slot_of, self.n_active,
+                       self.e0, self.e1)
+        ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, self.h, rows, 2 * c.moe_ffn, c.hidden, self.local_experts,
                              self.group_list, group_b=False)
         xm = ops.act_quant_nvfp4(self.h.view(self.slots * self.bn, 2 * c.moe_ffn), self.terms, out=self.qa_mid,
                                  mode="swiglu", limit=c.swiglu_limit, group_list=self.group_list, group_rows=rows)
-        ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, self.y, rows, c.hidden, c.moe_ffn, c.experts,
+        ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, self.y, rows, c.hidden, c.moe_ffn, self.local_experts,
                              self.group_list, group_b=True)
         sh = None
         if self.shared is not None:
@@ -180,6 +204,9 @@ class MoEBlock:
             xs = ops.act_quant_nvfp4(self.sh_gu[:rows], self.terms, out=self.qa_sh, mode="swiglu", limit=c.swiglu_limit)
             ops.gemm_fp4(xs, w.shared_down, out=self.shared[:rows])
             sh = self.shared
+        if push_comm:
+            ops.moe_combine_push(self.y, sh, self.ids[:rows], self.wts[:rows], self.slot_of, push_comm, rows)
+            return None
         return ops.moe_combine(self.y, sh, self.ids[:rows], self.wts[:rows], self.slot_of, out, rows)
 
     def forward_gathered(self, xn: torch.Tensor) -> torch.Tensor:
@@ -190,11 +217,13 @@ class MoEBlock:
                                  c.norm_topk_prob, c.routed_scaling)
         acc = torch.zeros(xn.shape[0], c.hidden, dtype=torch.float32, device=xn.device)
         for e in torch.unique(ids).tolist():
+            if not (self.e0 <= e < self.e1):
+                continue
             hit = ids == e
             rows = hit.any(-1).nonzero().flatten()
             xe = xn.index_select(0, rows).contiguous()
-            h = ops.linear(xe, w.experts_gu[e])
-            y = ops.linear(ops.swiglu(h, limit=c.swiglu_limit), w.experts_down[e])
+            h = ops.linear(xe, w.experts_gu[e - self.e0])
+            y = ops.linear(ops.swiglu(h, limit=c.swiglu_limit), w.experts_down[e - self.e0])
             acc.index_add_(0, rows, (wts * hit).sum(-1)[rows].unsqueeze(-1) * y.float())
         if w.shared_gu is not None:
             acc += ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu), limit=c.swiglu_limit), w.shared_down).float()

@@ -321,7 +321,8 @@ def attn_prefill_tc(q, q_stride: int, cache, block_table_row, pos0: int, hq: int
 from ._lib import F, I, L, P  # noqa: E402  (ctypes aliases for the signatures below)
 
 _lib.declare("dgpp_moe_route", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
-_lib.declare("dgpp_moe_active", [P, I, I, I, I, P, P, P, P])
+_lib.declare("dgpp_moe_active", [P, I, I, I, I, P, P, P, I, I, P])
+_lib.declare("dgpp_moe_combine_push", [P, P, P, P, P, P, I, I, I, I, P])
 _lib.declare("dgpp_moe_combine", [P, P, P, P, P, P, I, I, I, I, P])
 _lib.declare("dgpp_gemm_fp4_grouped", [I, P, P, P, I, P, P, P, P, I, L, I, I, I, I, I, P, I, I, P, P, P])
 
@@ -339,14 +340,16 @@ def moe_route(x, gate, bias, k: int, n_group: int = 1, topk_group: int = 1, soft
     return ids, weights
 
 
-def moe_active(ids, rows: int, experts: int, slots: int, group_list=None, slot_of=None, n_active=None):
+def moe_active(ids, rows: int, experts: int, slots: int, group_list=None, slot_of=None, n_active=None,
+               e_begin: int = 0, e_end: int = 0):
+    """Active-expert list.  With expert parallelism only experts [e_begin, e_end) are listed (as local indices)."""
     dev = ids.device
     if group_list is None:
         group_list = torch.empty(slots, dtype=torch.int32, device=dev)
         slot_of = torch.empty(experts, dtype=torch.int32, device=dev)
         n_active = torch.empty(1, dtype=torch.int32, device=dev)
     call("dgpp_moe_active", ptr(ids), rows, ids.shape[1], experts, slots, ptr(group_list), ptr(slot_of), ptr(n_active),
-         stream_ptr())
+         e_begin, e_end, stream_ptr())
     return group_list, slot_of, n_active
 
 
@@ -355,6 +358,13 @@ def moe_combine(y, shared, ids, weights, slot_of, out, rows: int):
     call("dgpp_moe_combine", ptr(y), ptr(shared), ptr(ids), ptr(weights), ptr(slot_of), ptr(out), rows, y.shape[2],
          ids.shape[1], y.shape[1], stream_ptr())
     return out
+
+
+def moe_combine_push(y, shared, ids, weights, slot_of, comm, rows: int):
+    """Expert-parallel combine: this rank's partial is pushed to every rank's symmetric region (consumed by the
+    fold in the next add + RMSNorm + quantise kernel)."""
+    call("dgpp_moe_combine_push", ptr(y), ptr(shared), ptr(ids), ptr(weights), ptr(slot_of), comm, rows, y.shape[2],
+         ids.shape[1], y.shape[1], stream_ptr())
 
 
 def gemm_fp4_grouped(xa: "QuantAct", wq, wsf_tiled, alphas, out, rows: int, n: int, k: int, experts: int, group_list,

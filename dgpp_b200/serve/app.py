@@ -42,6 +42,8 @@ class _Live:
     finish: str = ""
     tool_parser: object = None
     tool_calls: list = field(default_factory=list)
+    slot: int = -1
+    logprobs: list = field(default_factory=list)
     t_submit: float = 0.0
     t_first: float = 0.0
 
@@ -262,6 +264,7 @@ class Server:
                 continue
             g = self.groups[lv.group]
             if kind == "admit":
+                lv.slot = a
                 lv.cached = b
                 self.metrics.c["cached_tokens_total"] += b
             elif kind == "token":
@@ -272,6 +275,7 @@ class Server:
                     self.metrics.ttft.append(lv.t_first - lv.t_submit)
                 lv.tokens += 1
                 self.metrics.c["completion_tokens_total"] += 1
+                self._note_logprob(lv, g, a)
                 piece = lv.scanner.feed(lv.decoder.push(a))
                 self._emit(lv, g, piece)
                 if lv.scanner.stopped():
@@ -311,6 +315,17 @@ class Server:
                     lv.first_chunk = False
                     self.http.stream_send(lv.conn, evt.encode())
 
+    def _note_logprob(self, lv: _Live, g: dict, token: int) -> None:
+        """Collects (token text, logprob, alternatives) of the token just produced when the request asked for it."""
+        if not g["req"]["logprobs"] or lv.slot < 0:
+            return
+        last = getattr(self.engine, "last_logprobs", None)
+        rec = last[lv.slot] if last is not None and lv.slot < len(last) else None
+        if rec is None:
+            return
+        text = lambda i: self.tok.token_bytes(int(i)).decode("utf-8", "replace")
+        lv.logprobs.append((text(token), float(rec[0]), [(text(i), float(v)) for i, v in rec[1]]))
+
     def _emit_content(self, lv: _Live, g: dict, piece: bytes) -> None:
         if not piece and not (g["stream"] and lv.first_chunk and g["chat"]):
             return
@@ -328,7 +343,8 @@ class Server:
             ev = rt.chunk_event(g["chat"], lv.group, self.model_name, lv.created, lv.index, "", finish_reason=lv.finish)
             self.http.stream_send(lv.conn, ev.encode())
         g["choices"][lv.index] = (lv.index, lv.text.decode("utf-8", "replace"), lv.finish,
-                                  json.dumps(lv.tool_calls) if lv.tool_calls else "")
+                                  json.dumps(lv.tool_calls) if lv.tool_calls else "", list(lv.logprobs),
+                                  bool(g["req"]["logprobs"]) and bool(lv.logprobs))
         g["done"] += 1
         g.setdefault("completion_tokens", 0)
         g["completion_tokens"] += lv.tokens
