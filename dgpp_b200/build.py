@@ -98,6 +98,16 @@ def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool =
     return out
 
 
+def _shared_stdcxx() -> list[str]:
+    """Link against the system's shared libstdc++ by file name.  A toolchain wrapper that cannot find
+    ``libstdc++.so`` silently links the static archive instead; a second copy of libstdc++ in one process (PyTorch
+    loads the shared one) corrupts iostream locale state, so the shared library is named explicitly."""
+    for d in ("/usr/lib/x86_64-linux-gnu", "/lib/x86_64-linux-gnu", "/usr/lib64"):
+        if (Path(d) / "libstdc++.so.6").exists():
+            return ["-L" + d, "-l:libstdc++.so.6"]
+    return []
+
+
 def rt_module_path() -> Path:
     suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
     return LIB / ("_dgpp_rt" + suffix)
@@ -125,7 +135,7 @@ def build_rt(verbose: bool = False, force: bool = False) -> Path:
                 if verbose and log.strip():
                     print(log)
     if jobs or not out.exists():
-        _run([CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread"])
+        _run([CXX, "-shared", "-o", str(out), *map(str, objs), *_shared_stdcxx(), "-pthread"])
     return out
 
 

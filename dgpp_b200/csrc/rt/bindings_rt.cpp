@@ -14,6 +14,7 @@ void bind_text(py::module_& m);     // tokenizer, chat template (bindings_text.c
 void bind_load(py::module_& m);     // safetensors, hub cache, architecture detect, shard specs (bindings_load.cpp)
 void bind_grammar(py::module_& m);  // JSON / schema constrained decoding (bindings_grammar.cpp)
 void bind_util(py::module_& m);     // logger, trace, crc32c, watchdogs, config, memory plan (bindings_util.cpp)
+void bind_ctl(py::module_& m);      // prefill controller, journal, framed TCP, roster, disk tier (bindings_ctl.cpp)
 void bind_serve(py::module_& m);    // sampler oracle, grammars, http server (bindings_serve.cpp)
 
 namespace {
@@ -180,5 +181,6 @@ void bind_more(py::module_& m) {
   bind_serve(m);
   bind_load(m);
   bind_grammar(m);
+  bind_ctl(m);
   bind_util(m);
 }
