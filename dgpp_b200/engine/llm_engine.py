@@ -118,6 +118,12 @@ class LLMEngine:
             self.graphs[b] = g
         return g
 
+    def set_adapter(self, adapter) -> None:
+        """Install (or with None remove) a bound low-rank adapter.  Captured decode graphs are dropped: the
+        adapted and the plain step are different launch sequences."""
+        self.runner.lora = adapter
+        self.graphs.clear()
+
     def launches_per_step(self) -> int:
         """Kernel launches of this package inside one decode step (for reporting)."""
         c = self.model.cfg

@@ -31,6 +31,7 @@ class DenseRunner:
         self.decode_fp4 = decode_fp4 and model.cfg.weight_fmt == "nvfp4"
         self.act_terms = act_terms
         self.chunk = None
+        self._li = 0
         # fused GEMM -> all-reduce (peer-memory push in the GEMM epilogue, fold in the next norm kernel)
         self.fuse_ar = fuse_ar and reducer is not None and getattr(reducer, "comm", None) is not None and \
             model.cfg.hidden % 128 == 0 and model.cfg.hidden // 128 <= 64
@@ -57,6 +58,10 @@ class DenseRunner:
         self.att_ml = torch.empty(R * self.hq * decode_splits * 2, dtype=torch.float32, device=dev)
         self.att_acc = torch.empty(min(R, 256) * self.hq * decode_splits * d, dtype=torch.float32, device=dev)
         self.ws = ops.default_workspace(dev)
+        # runtime low-rank adapter (adapters.lora.LoraAdapter) applied after every adapted projection; the fused
+        # GEMM -> all-reduce push is bypassed while one is installed (the update is added to the partial output)
+        self.lora = None
+        self.lora_scratch = torch.empty(R * 256, dtype=torch.float32, device=dev)
         self.qa = {}
         self.fp4_rows = min(64, decode_rows or max_rows)
         if self.decode_fp4:
@@ -76,34 +81,47 @@ class DenseRunner:
         the kernel that produces its input (add + RMSNorm, attention output, SwiGLU)."""
         m, c = self.m, self.m.cfg
         H = c.hidden
+        lora, li = self.lora, self._li
+        xn = self.xn[:rows] if lora is not None else None       # bf16 input of the adapted projections
         if pending_fold:
             xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", norm_w=L.in_norm, eps=c.eps,
                                      fold_comm=self.reducer.comm)
         else:
             xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta if have_delta else None,
-                                     norm_w=L.in_norm, eps=c.eps)
+                                     norm_w=L.in_norm, eps=c.eps, x_out=xn)
         ops.gemm_fp4(xa, L.qkv, out=qkv)
+        if lora is not None:
+            lora.apply(li, "qkv", xn, qkv, self.lora_scratch)
         ops.rope_kv_write(qkv, positions, row_req, self.kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
                           rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm, eps=c.eps)
         self.attention(qkv, cache, row_req, positions, rows, splits, attn)
         xa = ops.act_quant_nvfp4(attn, out=self.qa[self.hq * self.d], mode="plain")
         # tensor parallel, peer memory: the GEMM epilogue pushes its tiles to every rank and the next
         # add + RMSNorm + quantise kernel folds them (no separate all-reduce launch)
-        fuse = getattr(self.reducer, "comm", None) if self.fuse_ar else None
+        fuse = getattr(self.reducer, "comm", None) if (self.fuse_ar and lora is None) else None
         if fuse:
             ops.gemm_fp4(xa, L.o, push_comm=fuse)
             xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", norm_w=L.post_norm, eps=c.eps, fold_comm=fuse)
         else:
             ops.gemm_fp4(xa, L.o, out=delta)
+            if lora is not None:
+                lora.apply(li, "o", attn, delta, self.lora_scratch)
             if self.reducer is not None:
                 self.reducer.all_reduce(delta)
-            xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta, norm_w=L.post_norm, eps=c.eps)
+            xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta, norm_w=L.post_norm, eps=c.eps,
+                                     x_out=xn)
         ops.gemm_fp4(xa, L.gate_up, out=gu)
-        xa = ops.act_quant_nvfp4(gu, out=self.qa[gu.shape[1] // 2], mode="swiglu")
+        act = None
+        if lora is not None:
+            lora.apply(li, "gate_up", xn, gu, self.lora_scratch)
+            act = self.act[:rows]
+        xa = ops.act_quant_nvfp4(gu, out=self.qa[gu.shape[1] // 2], mode="swiglu", x_out=act)
         if fuse and not last:
             ops.gemm_fp4(xa, L.down, push_comm=fuse)
             return True            # the next layer's first kernel folds the pushed tiles
         ops.gemm_fp4(xa, L.down, out=delta)
+        if lora is not None:
+            lora.apply(li, "down", act, delta, self.lora_scratch)
         if self.reducer is not None:
             self.reducer.all_reduce(delta)
         return False
@@ -125,7 +143,9 @@ class DenseRunner:
         splits = self.decode_splits if (decode and rows <= 256) else 1
         fp4 = self.decode_fp4 and decode and rows <= self.fp4_rows and all(
             w.k % 256 == 0 for w in (m.layers[0].qkv, m.layers[0].o, m.layers[0].down))
+        lora = self.lora
         for li, L in enumerate(m.layers):
+            self._li = li
             if fp4:
                 pending = self._layer_fp4(L, kv.layers[li], x, delta, have_delta, qkv, attn, gu, positions, row_req,
                                           rows, splits, pending_fold=pending, last=li == len(m.layers) - 1)
@@ -133,18 +153,26 @@ class DenseRunner:
                 continue
             ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have_delta else None, out=xn)
             self.linear(xn, L.qkv, qkv, fp4)
+            if lora is not None:
+                lora.apply(li, "qkv", xn, qkv, self.lora_scratch)
             cache = kv.layers[li]
             ops.rope_kv_write(qkv, positions, row_req, kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
                               rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm,
                               eps=c.eps)
             self.attention(qkv, cache, row_req, positions, rows, splits, attn)
             self.linear(attn, L.o, delta, fp4)
+            if lora is not None:
+                lora.apply(li, "o", attn, delta, self.lora_scratch)
             if self.reducer is not None:
                 self.reducer.all_reduce(delta)
             ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
             self.linear(xn, L.gate_up, gu, fp4)
+            if lora is not None:
+                lora.apply(li, "gate_up", xn, gu, self.lora_scratch)
             ops.swiglu(gu, out=act)
             self.linear(act, L.down, delta, fp4)
+            if lora is not None:
+                lora.apply(li, "down", act, delta, self.lora_scratch)
             if self.reducer is not None:
                 self.reducer.all_reduce(delta)
             have_delta = True

@@ -176,10 +176,20 @@ class DenseModel:
     # ------------------------------------------------------------------ PyTorch oracle
     @torch.no_grad()
     def forward_reference(self, tokens: torch.Tensor, start_pos: int = 0, kv: Optional[list] = None,
-                          all_reduce=None, return_hidden: bool = False):
+                          all_reduce=None, return_hidden: bool = False, lora=None):
         """Full-precision-accumulate reference of one request: tokens [T] at positions start_pos.. .
         `kv` is a list (per layer) of (k, v) fp32 tensors [Tk, hkv, d] that is extended in place; KV
-        values go through the same FP8 round trip as the paged cache when cfg.kv_fp8."""
+        values go through the same FP8 round trip as the paged cache when cfg.kv_fp8.  `lora`: a bound
+        ``adapters.lora.LoraAdapter`` whose updates are added to the bf16 outputs of the projections."""
+        from ..adapters.lora import lora_reference
+
+        def adapt(li, proj, xin, out):
+            if lora is not None:
+                for p in lora.pairs(li, proj):
+                    sl = slice(p.col0, p.col0 + p.b.shape[0])
+                    out[:, sl] = lora_reference(xin, p.a, p.b, out[:, sl], lora.scale)
+            return out
+
         c = self.cfg
         T = tokens.numel()
         dev = self.embed.device
@@ -192,7 +202,7 @@ class DenseModel:
         scale = 1.0 / math.sqrt(d)  # the YaRN attention factor is carried by cos/sin (mscale)
         for li, L in enumerate(self.layers):
             xn, x = ref.rmsnorm(x, L.in_norm, c.eps, delta)
-            qkv = ref.linear(xn, L.qkv).float()
+            qkv = adapt(li, "qkv", xn, ref.linear(xn, L.qkv)).float()
             q = qkv[:, :hq * d].view(T, hq, d)
             k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
             v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
@@ -213,12 +223,12 @@ class DenseModel:
                 v = torch.cat([kv[li][1], v])
             kv[li] = (k, v)
             a = ref.act(ref.attention(q, k, v, scale, causal_offset=start_pos).reshape(T, hq * d))
-            o = ref.linear(a, L.o)
+            o = adapt(li, "o", a, ref.linear(a, L.o))
             if all_reduce is not None:
                 o = all_reduce(o)
             xn, x = ref.rmsnorm(x, L.post_norm, c.eps, o)
-            act = ref.swiglu(ref.linear(xn, L.gate_up))
-            delta = ref.linear(act, L.down)
+            act = ref.swiglu(adapt(li, "gate_up", xn, ref.linear(xn, L.gate_up)))
+            delta = adapt(li, "down", act, ref.linear(act, L.down))
             if all_reduce is not None:
                 delta = all_reduce(delta)
         xn, x = ref.rmsnorm(x, self.final_norm, c.eps, delta)

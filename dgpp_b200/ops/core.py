@@ -465,3 +465,23 @@ def topk_select(scores, positions, k: int, out=None):
         out = torch.empty(rows, k, dtype=torch.int32, device=scores.device)
     call("dgpp_topk_select", ptr(scores), scores.stride(0), ptr(positions), ptr(out), rows, k, stream_ptr())
     return out
+
+
+# ---------------------------------------------------------------------------------------------- low-rank adapters
+_lib.declare("dgpp_lora_apply", [P, L, P, P, P, P, L, F, I, I, I, I, P])
+
+
+def lora_apply(x, a, b, out, scale: float, scratch=None):
+    """out += scale * (x @ a.T) @ b.T in place.  x [T, K] bf16, a [r, K] bf16, b [N, r] bf16, out [T, N] bf16;
+    the rank-r intermediate stays in fp32 (`scratch`: >= T * r floats)."""
+    _chk(x, torch.bfloat16, "x")
+    _chk(out, torch.bfloat16, "out")
+    rows, k = x.shape
+    r, n = a.shape[0], b.shape[0]
+    assert a.shape == (r, k) and b.shape == (n, r) and out.shape == (rows, n) and a.is_contiguous() and b.is_contiguous()
+    if scratch is None:
+        scratch = torch.empty(rows * r, dtype=torch.float32, device=x.device)
+    assert scratch.numel() >= rows * r
+    call("dgpp_lora_apply", ptr(x), x.stride(0), ptr(a), ptr(b), ptr(scratch), ptr(out), out.stride(0), float(scale),
+         rows, n, k, r, stream_ptr())
+    return out
