@@ -211,6 +211,16 @@ DGPP_API int dgpp_comm_connect(void* comm, const void* handles) {
   return 0;
 }
 
+// Single-GPU stand-in for the peers: every rank slot that has no mapping yet points at this rank's own region.
+// Pushes then land in the local region and the flags of the other source ranks are never raised, which is how the
+// bounded-wait / status path is exercised without a second process (a missing peer looks exactly like this).
+DGPP_API int dgpp_comm_loopback(void* comm) {
+  DgppComm* c = static_cast<DgppComm*>(comm);
+  for (int r = 0; r < c->st.world; ++r)
+    if (!c->st.peers[r]) c->st.peers[r] = static_cast<unsigned char*>(c->local);
+  return 0;
+}
+
 DGPP_API int dgpp_comm_destroy(void* comm) {
   DgppComm* c = static_cast<DgppComm*>(comm);
   if (!c) return 0;
