@@ -470,10 +470,6 @@ struct Fp4Cfg {
   static constexpr size_t kBudget = BN <= 96 ? 108 * 1024 : 200 * 1024;
   static constexpr int S = kBudget / stage_bytes() > 6 ? 6 : static_cast<int>(kBudget / stage_bytes());
   static constexpr size_t smem() { return 1024 + S * stage_bytes() + (2 * S + 1) * 8 + 64; }
-  // Launches with at most one CTA per SM (few output tiles: qkv / o projections at decode sizes) are bound by the
-  // bytes one SM keeps in flight, so they run a ring twice as deep in the shared memory a second CTA would have used.
-  static constexpr int SD = BN <= 96 ? (216 * 1024 / stage_bytes() > 8 ? 8 : static_cast<int>(216 * 1024 / stage_bytes())) : S;
-  static constexpr size_t smem_deep() { return 1024 + SD * stage_bytes() + (2 * SD + 1) * 8 + 64; }
 };
 
 template <int BN>
@@ -490,19 +486,6 @@ static int launch_fp4(const CUtensorMap& tA, const CUtensorMap& tB, const Fp4Par
   }
   const int bn_tok = BN / p.R;
   dim3 grid(p.grid_x > 0 ? p.grid_x : dgpp_ceil_div(p.N, kF4BM), dgpp_ceil_div(p.T, bn_tok), splits);
-  if (C::SD > C::S && static_cast<size_t>(grid.x) * grid.y * grid.z <= 148 && p.K / 256 > C::S) {
-    auto deep = gemm_fp4_kernel<BN, C::SD>;
-    static bool attr_deep = false;
-    constexpr size_t smem_deep = C::smem_deep();
-    static_assert(smem_deep <= 227 * 1024, "shared memory budget exceeded");
-    if (!attr_deep) {
-      DGPP_CUDA_OK(cudaFuncSetAttribute(deep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_deep)));
-      attr_deep = true;
-    }
-    deep<<<grid, kF4Threads, smem_deep, st>>>(tA, tB, p);
-    DGPP_CUDA_OK(cudaGetLastError());
-    return 0;
-  }
   kern<<<grid, kF4Threads, smem, st>>>(tA, tB, p);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;

@@ -5,6 +5,7 @@
 
 #include "rt/json_grammar.h"
 #include "rt/speculative.h"
+#include "rt/tool_grammar.h"
 #include "rt/tool_parser.h"
 
 namespace py = pybind11;
@@ -39,6 +40,42 @@ void bind_grammar(py::module_& m) {
       .def("accept", &TokenGrammar::accept)
       // allowed-token bitmask: uint32 words, bit i of word i / 32 = token i (the device sampler's mask layout)
       .def("mask", [](TokenGrammar& g) {
+        const std::vector<uint32_t>& mk = g.mask();
+        py::array_t<uint32_t> out(static_cast<py::ssize_t>(mk.size()));
+        std::memcpy(out.mutable_data(), mk.data(), mk.size() * sizeof(uint32_t));
+        return out;
+      });
+
+  // tools_json: the request's "tools" array ([{"type":"function","function":{"name":..,"parameters":{..}}}, ...])
+  py::class_<ToolTokenGrammar>(m, "ToolGrammar")
+      .def(py::init([](const std::string& tools_json, bool required, bool parallel, const std::vector<py::bytes>& token_bytes,
+                       std::vector<int32_t> eos, const std::string& only) {
+        auto specs = std::make_shared<std::vector<ToolSpec>>();
+        const json::Value tools = json::parse(tools_json);
+        for (const auto& t : tools.items()) {
+          const json::Value* fn = t.find("function");
+          const json::Value& f = fn ? *fn : t;
+          ToolSpec s;
+          s.name = f.at("name").as_string();
+          if (!only.empty() && s.name != only) continue;
+          const json::Value* p = f.find("parameters");
+          s.parameters = (p && p->is_object() && p->size() > 0) ? std::make_shared<const Schema>(Schema::compile(*p))
+                                                                : std::make_shared<const Schema>(Schema::any_object());
+          specs->push_back(std::move(s));
+        }
+        if (specs->empty()) throw std::invalid_argument("tool grammar: no (matching) tools");
+        auto toks = std::make_shared<std::vector<std::string>>();
+        toks->reserve(token_bytes.size());
+        for (const auto& b : token_bytes) toks->push_back(std::string(b));
+        return new ToolTokenGrammar(specs, required ? ToolChoice::Required : ToolChoice::Auto, parallel, toks, std::move(eos));
+      }), py::arg("tools_json"), py::arg("required"), py::arg("parallel"), py::arg("token_bytes"), py::arg("eos_ids"),
+          py::arg("only") = "")
+      .def("words", &ToolTokenGrammar::words)
+      .def("complete", &ToolTokenGrammar::complete)
+      .def("in_call", &ToolTokenGrammar::in_call)
+      .def("calls", &ToolTokenGrammar::calls)
+      .def("accept", &ToolTokenGrammar::accept)
+      .def("mask", [](ToolTokenGrammar& g) {
         const std::vector<uint32_t>& mk = g.mask();
         py::array_t<uint32_t> out(static_cast<py::ssize_t>(mk.size()));
         std::memcpy(out.mutable_data(), mk.data(), mk.size() * sizeof(uint32_t));

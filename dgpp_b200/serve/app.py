@@ -73,13 +73,14 @@ class Metrics:
 class Server:
     def __init__(self, engine, tokenizer, template_src: str = DEFAULT_TEMPLATE, model_name: str = "dgpp-b200",
                  host: str = "127.0.0.1", port: int = 0, eos_ids: Optional[List[int]] = None,
-                 default_max_tokens: int = 256, sched_config=None, tool_format=None):
+                 default_max_tokens: int = 256, sched_config=None, tool_format=None, constrain_tools: bool = False):
         self.engine, self.tok = engine, tokenizer
         self.template = rt.ChatTemplate(template_src)
         self.model_name = model_name
         self.eos_ids = eos_ids or []
         self.default_max_tokens = default_max_tokens
         self.tool_format = tool_format or rt.ToolFormat.JsonTags
+        self.constrain_tools = constrain_tools
         self.sched = rt.Scheduler(engine, sched_config or rt.SchedulerConfig())
         self.http = rt.HttpServer(host, port)
         self.live: Dict[str, _Live] = {}
@@ -209,11 +210,16 @@ class Server:
         params, schema = self._sampling_of(r)
         for i in range(r["n"]):
             rid = f"{group}-{i}"
-            if (params is not None or schema is not None) and hasattr(self.engine, "configure"):
+            tool_mode = self._tool_constraint(r) if chat else None
+            if (params is not None or schema is not None or tool_mode is not None) and hasattr(self.engine, "configure"):
                 if params is not None and r["n"] > 1 and r["seed"] is not None:
                     params = type(params)(**{**params.__dict__, "seed": int(r["seed"]) + i})
                 grammar = None
-                if schema is not None:
+                if tool_mode is not None:
+                    required, only = tool_mode
+                    grammar = rt.ToolGrammar(r["tools_json"], required, bool(r.get("parallel_tool_calls", True)),
+                                             self._token_table(), self.eos_ids, only)
+                elif schema is not None:
                     grammar = rt.JsonGrammar(schema, self._token_table(), self.eos_ids)
                 self.engine.configure(rid, params, grammar, ids)
             self.live[rid] = _Live(rid, conn, r, i, group, len(ids), created, rt.StreamDecoder(self.tok, True),
@@ -222,6 +228,25 @@ class Server:
                 self.live[rid].tool_parser = rt.ToolParser(self.tool_format, f"call_{uuid.uuid4().hex[:12]}_")
             self.sched.submit(rid, ids, max_tokens, eos_ids=[] if r["ignore_eos"] else self.eos_ids,
                               ignore_eos=r["ignore_eos"], prefix_cache=r["prefix_cache"], cache_key=r["prompt_cache_key"])
+
+    def _tool_constraint(self, r: dict):
+        """(required, only-this-function) when the request's tool calls are decoded under the tool grammar, else None.
+        tool_choice "required" or a named function forces a call; "auto" is constrained only when the server was
+        started with constrain_tools (the text stays free until the model opens a call)."""
+        if self.tool_format != rt.ToolFormat.JsonTags or r["tools_json"] in ("null", "[]"):
+            return None
+        choice = json.loads(r["tool_choice_json"])
+        if choice == "none":
+            return None
+        if choice == "required":
+            return True, ""
+        if isinstance(choice, dict):
+            name = (choice.get("function") or {}).get("name") or choice.get("name") or ""
+            names = [(t.get("function") or t).get("name") for t in json.loads(r["tools_json"])]
+            if name not in names:
+                raise rt.ApiError(400, rt.error_json(400, f"tool_choice names an unknown function {name!r}", param="tool_choice"))
+            return True, name
+        return (False, "") if self.constrain_tools else None
 
     def _token_table(self):
         """Raw bytes of every vocabulary entry (specials empty): the grammar's view of the tokenizer."""

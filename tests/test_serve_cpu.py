@@ -186,3 +186,14 @@ def test_tool_calls_are_parsed_from_generated_text():
         assert "<tool_call>" in json.loads(data)["choices"][0]["message"]["content"]
     finally:
         srv.stop()
+
+
+def test_tool_choice_naming_an_unknown_function_is_rejected(server):
+    _, port = server
+    req = {"model": "fake", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+           "tools": [{"type": "function", "function": {"name": "f", "parameters": {"type": "object"}}}],
+           "tool_choice": {"type": "function", "function": {"name": "g"}}}
+    st, data = _req(port, "POST", "/v1/chat/completions", json.dumps(req))
+    assert st == 400 and json.loads(data)["error"]["param"] == "tool_choice"
+    req["tool_choice"] = {"type": "function", "function": {"name": "f"}}
+    assert _req(port, "POST", "/v1/chat/completions", json.dumps(req))[0] == 200
