@@ -31,7 +31,20 @@ struct AttnDecodeParams {
   int rows, hq, hkv, page, max_blocks, splits, kv_fp8;
   float scale;            // softmax scale (1/sqrt(D) times any rope mscale^2)
   int window;             // > 0: attend only to the last `window` positions (sliding window); 0 = full
+  const float* sink;      // optional [hq]: one more softmax column per head with this logit and no value
 };
+
+// Normalisation with the optional sink column: out = acc / (l + exp(sink - m)), computed against max(m, sink).
+__device__ __forceinline__ float finish_softmax(float a, float l, float m, const float* sink, int h) {
+  if (sink != nullptr) {
+    const float sk = sink[h];
+    const float mx = fmaxf(m, sk);
+    const float c = m == -INFINITY ? 0.f : __expf(m - mx);
+    a *= c;
+    l = l * c + __expf(sk - mx);
+  }
+  return l > 0.f ? a / l : 0.f;
+}
 
 constexpr int kDecWarps = 4;
 
@@ -198,7 +211,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_kernel(AttnDecodeP
     }
     const int h = kvh * G + g;
     if (p.splits == 1) {
-      p.out[(static_cast<size_t>(row) * p.hq + h) * D + d] = f32_to_bf16(ll > 0.f ? a / ll : 0.f);
+      p.out[(static_cast<size_t>(row) * p.hq + h) * D + d] = f32_to_bf16(finish_softmax(a, ll, mm, p.sink, h));
     } else {
       const size_t pi = (static_cast<size_t>(row) * p.hq + h) * p.splits + split;
       p.part_acc[pi * D + d] = a;
@@ -212,7 +225,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_kernel(AttnDecodeP
 
 template <int D>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc,
-                                           bf16* __restrict__ out, int splits) {
+                                           bf16* __restrict__ out, int splits, const float* __restrict__ sink, int hq) {
   pdl_wait();
   const size_t rh = blockIdx.x;  // row * hq + h
   const int d = threadIdx.x;
@@ -225,7 +238,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_ml, co
     ll += part_ml[(rh * splits + s) * 2 + 1] * c;
     a += part_acc[(rh * splits + s) * D + d] * c;
   }
-  out[rh * D + d] = f32_to_bf16(ll > 0.f ? a / ll : 0.f);
+  out[rh * D + d] = f32_to_bf16(finish_softmax(a, ll, mm, sink, static_cast<int>(rh % hq)));
 }
 
 template <int D, int G>
@@ -234,7 +247,7 @@ static int launch_decode(const AttnDecodeParams& p, cudaStream_t st) {
   attn_decode_kernel<D, G><<<grid, kDecWarps * 32, 0, st>>>(p);
   DGPP_CUDA_OK(cudaGetLastError());
   if (p.splits > 1) {
-    attn_decode_combine_kernel<D><<<p.rows * p.hq, D, 0, st>>>(p.part_ml, p.part_acc, p.out, p.splits);
+    attn_decode_combine_kernel<D><<<p.rows * p.hq, D, 0, st>>>(p.part_ml, p.part_acc, p.out, p.splits, p.sink, p.hq);
     DGPP_CUDA_OK(cudaGetLastError());
   }
   return 0;
@@ -245,11 +258,11 @@ static int launch_decode(const AttnDecodeParams& p, cudaStream_t st) {
 using namespace dgpp;
 
 // Scratch needed for `splits` > 1: part_ml rows*hq*splits*2 floats, part_acc rows*hq*splits*d floats.
-DGPP_API int dgpp_attn_decode(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
-                              const void* k_scale, const void* v_scale, const void* block_table,
-                              const void* row_req, const void* positions, void* part_ml, void* part_acc, void* out,
-                              int rows, int hq, int hkv, int d, int page, int max_blocks, int splits, int kv_fp8,
-                              float scale, int window, cudaStream_t st) {
+static int attn_decode_impl(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                            const void* k_scale, const void* v_scale, const void* block_table,
+                            const void* row_req, const void* positions, void* part_ml, void* part_acc, void* out,
+                            int rows, int hq, int hkv, int d, int page, int max_blocks, int splits, int kv_fp8,
+                            float scale, int window, const void* sink, cudaStream_t st) {
   DGPP_REQUIRE(hkv > 0 && hq % hkv == 0, "attn_decode: hq %d not a multiple of hkv %d", hq, hkv);
   DGPP_REQUIRE(splits >= 1, "attn_decode: splits must be >= 1");
   DGPP_REQUIRE(splits == 1 || (part_ml && part_acc), "attn_decode: scratch required when splits > 1");
@@ -269,6 +282,7 @@ DGPP_API int dgpp_attn_decode(const void* q, int64_t q_stride, const void* k_cac
   p.out = static_cast<bf16*>(out);
   p.rows = rows; p.hq = hq; p.hkv = hkv; p.page = page; p.max_blocks = max_blocks; p.splits = splits;
   p.kv_fp8 = kv_fp8; p.scale = scale; p.window = window;
+  p.sink = static_cast<const float*>(sink);
   const int g = hq / hkv;
 #define DGPP_DEC_CASE(DD, GG) \
   if (d == DD && g == GG) return launch_decode<DD, GG>(p, st);
@@ -278,6 +292,26 @@ DGPP_API int dgpp_attn_decode(const void* q, int64_t q_stride, const void* k_cac
 #undef DGPP_DEC_CASE
   dgpp_set_error("attn_decode: unsupported head_dim %d / group %d", d, g);
   return -1;
+}
+
+DGPP_API int dgpp_attn_decode(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                              const void* k_scale, const void* v_scale, const void* block_table,
+                              const void* row_req, const void* positions, void* part_ml, void* part_acc, void* out,
+                              int rows, int hq, int hkv, int d, int page, int max_blocks, int splits, int kv_fp8,
+                              float scale, int window, cudaStream_t st) {
+  return attn_decode_impl(q, q_stride, k_cache, v_cache, k_scale, v_scale, block_table, row_req, positions, part_ml,
+                          part_acc, out, rows, hq, hkv, d, page, max_blocks, splits, kv_fp8, scale, window, nullptr, st);
+}
+
+// Sliding-window attention with per-head sink logits (sink: [hq] fp32, the logit of a value-less softmax column).
+// (reference counterpart: src/kernels/sink_attn_impl.cuh:394-398.)
+DGPP_API int dgpp_attn_decode_sink(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                                   const void* k_scale, const void* v_scale, const void* block_table,
+                                   const void* row_req, const void* positions, void* part_ml, void* part_acc, void* out,
+                                   int rows, int hq, int hkv, int d, int page, int max_blocks, int splits, int kv_fp8,
+                                   float scale, int window, const void* sink, cudaStream_t st) {
+  return attn_decode_impl(q, q_stride, k_cache, v_cache, k_scale, v_scale, block_table, row_req, positions, part_ml,
+                          part_acc, out, rows, hq, hkv, d, page, max_blocks, splits, kv_fp8, scale, window, sink, st);
 }
 
 // ------------------------------------------------------------------------------------------------------------

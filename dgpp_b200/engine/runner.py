@@ -94,7 +94,7 @@ class DenseRunner:
             lora.apply(li, "qkv", xn, qkv, self.lora_scratch)
         ops.rope_kv_write(qkv, positions, row_req, self.kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
                           rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm, eps=c.eps)
-        self.attention(qkv, cache, row_req, positions, rows, splits, attn)
+        self.attention(qkv, cache, row_req, positions, rows, splits, attn, L)
         xa = ops.act_quant_nvfp4(attn, out=self.qa[self.hq * self.d], mode="plain")
         # tensor parallel, peer memory: the GEMM epilogue pushes its tiles to every rank and the next
         # add + RMSNorm + quantise kernel folds them (no separate all-reduce launch)
@@ -159,7 +159,7 @@ class DenseRunner:
             ops.rope_kv_write(qkv, positions, row_req, kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
                               rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm,
                               eps=c.eps)
-            self.attention(qkv, cache, row_req, positions, rows, splits, attn)
+            self.attention(qkv, cache, row_req, positions, rows, splits, attn, L)
             self.linear(attn, L.o, delta, fp4)
             if lora is not None:
                 lora.apply(li, "o", attn, delta, self.lora_scratch)
@@ -191,19 +191,29 @@ class DenseRunner:
                 self.reducer.merge_picks(self.pick_id[:n], self.pick_val[:n])
         return logits
 
-    def attention(self, qkv, cache, row_req, positions, rows, splits, out):
-        """Attention of `rows` query rows against the paged cache (their own K/V already appended)."""
-        if self.chunk is not None and self.attn_tc and self.d == 128 and cache.fp8:
+    def attention(self, qkv, cache, row_req, positions, rows, splits, out, layer=None):
+        """Attention of `rows` query rows against the paged cache (their own K/V already appended).  `layer` carries
+        the sliding window and the sink logits of windowed-sink families; sink layers run on the CUDA-core kernel
+        (the sink column is folded into its final normalisation), the tensor-core kernels take the window."""
+        window = layer.window if layer is not None else 0
+        sink = layer.sink if layer is not None else None
+        if sink is not None:
+            sp = splits if rows <= 256 else 1
+            ops.attn_decode(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, self.hq, self.hkv,
+                            self.d, self.scale, splits=sp, scratch=(self.att_ml, self.att_acc) if sp > 1 else None,
+                            out=out, window=window, sink=sink)
+        elif self.chunk is not None and self.attn_tc and self.d == 128 and cache.fp8:
             slot, pos0 = self.chunk
             ops.attn_prefill_tc(qkv, qkv.stride(0), cache, self.kv.block_table[slot], pos0, self.hq, self.hkv, self.d,
-                                self.scale, out=out, rows=rows)
+                                self.scale, out=out, rows=rows, window=window)
         elif self.attn_tc:
             ops.attn_decode_tc(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, self.hq, self.hkv,
                                self.d, self.scale, splits=splits,
-                               scratch=(self.att_ml, self.att_acc) if splits > 1 else None, out=out)
+                               scratch=(self.att_ml, self.att_acc) if splits > 1 else None, out=out, window=window)
         elif splits > 1:
             ops.attn_decode(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, self.hq, self.hkv,
-                            self.d, self.scale, splits=splits, scratch=(self.att_ml, self.att_acc), out=out)
+                            self.d, self.scale, splits=splits, scratch=(self.att_ml, self.att_acc), out=out,
+                            window=window)
         else:
             ops.attn_decode(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, self.hq, self.hkv,
-                            self.d, self.scale, splits=1, out=out)
+                            self.d, self.scale, splits=1, out=out, window=window)

@@ -42,7 +42,18 @@ class DenseConfig:
     page: int = 64
     yarn_factor: float = 1.0
     yarn_original_max_pos: int = 0
+    # sliding-window + sink attention families: layers attend to the last `sliding_window` positions, except every
+    # `global_every`-th layer (1-based) which stays global; `attn_sinks` adds a learned per-head sink logit (a
+    # value-less softmax column) to every layer
+    sliding_window: int = 0
+    global_every: int = 0
+    attn_sinks: bool = False
     name: str = "dense-27b-nvfp4"
+
+    def layer_window(self, li: int) -> int:
+        if self.sliding_window <= 0 or (self.global_every > 0 and (li + 1) % self.global_every == 0):
+            return 0
+        return self.sliding_window
 
     @staticmethod
     def dense_27b(**kw) -> "DenseConfig":
@@ -79,6 +90,8 @@ class DenseLayer:
     down: QuantLinear         # [hidden, ffn / W]
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
+    sink: Optional[torch.Tensor] = None    # [local q heads] fp32 sink logits
+    window: int = 0                        # sliding window of this layer (0 = global)
 
 
 @dataclass
@@ -144,8 +157,14 @@ class DenseModel:
             gu = make(2 * cfg.ffn, H, cfg.weight_fmt, pad_rows=ffn_pad,
                       row_slices=[(r * ffn_l, (r + 1) * ffn_l), (cfg.ffn + r * ffn_l, cfg.ffn + (r + 1) * ffn_l)])
             dn = make(H, cfg.ffn, cfg.weight_fmt, col_slice=(r * ffn_l, (r + 1) * ffn_l), pad_cols=ffn_pad)
+            sink = None
+            if cfg.attn_sinks:
+                full_sink = torch.randn(cfg.q_heads, device=device, dtype=torch.float32, generator=g)
+                sink = torch.full((padded_q_heads(cfg, W),), -1e4, device=device, dtype=torch.float32)
+                sink[:hq_l] = full_sink[r * hq_l:(r + 1) * hq_l]
             layers.append(DenseLayer(ones(H), ones(H), qkv, o, gu, dn,
-                                     ones(d) if cfg.qk_norm else None, ones(d) if cfg.qk_norm else None))
+                                     ones(d) if cfg.qk_norm else None, ones(d) if cfg.qk_norm else None,
+                                     sink, cfg.layer_window(len(layers))))
         vl = cfg.vocab // W
         head = make(cfg.vocab, H, cfg.head_fmt, row_slices=[(r * vl, (r + 1) * vl)])
         m = DenseModel(cfg, embed, layers, ones(H), head, tp_rank, tp_size)
@@ -222,7 +241,8 @@ class DenseModel:
                 k = torch.cat([kv[li][0], k])
                 v = torch.cat([kv[li][1], v])
             kv[li] = (k, v)
-            a = ref.act(ref.attention(q, k, v, scale, causal_offset=start_pos).reshape(T, hq * d))
+            a = ref.act(ref.attention(q, k, v, scale, causal_offset=start_pos, window=L.window,
+                                      sink=L.sink).reshape(T, hq * d))
             o = adapt(li, "o", a, ref.linear(a, L.o))
             if all_reduce is not None:
                 o = all_reduce(o)

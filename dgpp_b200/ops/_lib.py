@@ -32,6 +32,7 @@ _SIGNATURES = {
     "dgpp_gemv_quant": [I, P, P, P, F, P, P, I, I, I, L, L, P],
     "dgpp_rope_kv_write": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
     "dgpp_attn_decode": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "dgpp_attn_decode_sink": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
     "dgpp_attn_decode_tc": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_prefill_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_decode_advance": [P, P, P, P, P, I, I, P],

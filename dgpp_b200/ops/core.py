@@ -264,7 +264,9 @@ def rope_kv_write(qkv, positions, row_req, block_table, inv_freq, cache, hq: int
 
 
 def attn_decode(q, q_stride: int, cache, block_table, row_req, positions, hq: int, hkv: int, d: int,
-                scale: float, splits: int = 1, scratch=None, out=None, window: int = 0):
+                scale: float, splits: int = 1, scratch=None, out=None, window: int = 0, sink=None):
+    """CUDA-core decode attention over the paged cache (bf16 or FP8).  window > 0: sliding window; sink: optional
+    [hq] fp32 logits of a value-less softmax column (sliding-window + sink attention families)."""
     rows = positions.numel()
     if out is None:
         out = torch.empty(rows, hq * d, dtype=torch.bfloat16, device=positions.device)
@@ -274,6 +276,14 @@ def attn_decode(q, q_stride: int, cache, block_table, row_req, positions, hq: in
             scratch = (torch.empty(rows * hq * splits * 2, dtype=torch.float32, device=out.device),
                        torch.empty(rows * hq * splits * d, dtype=torch.float32, device=out.device))
         ml, acc = scratch
+    if sink is not None:
+        _chk(sink, torch.float32, "sink")
+        assert sink.numel() == hq
+        call("dgpp_attn_decode_sink", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale),
+             ptr(cache.v_scale), ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq,
+             hkv, d, cache.page, block_table.shape[1], splits, int(cache.fp8), float(scale), window, ptr(sink),
+             stream_ptr())
+        return out
     call("dgpp_attn_decode", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale),
          ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq, hkv, d, cache.page,
          block_table.shape[1], splits, int(cache.fp8), float(scale), window, stream_ptr())

@@ -127,8 +127,9 @@ def quant_kv_fp8(x):
     return q.view(torch.uint8), scale
 
 
-def attention(q, k, v, scale, causal_offset: Optional[int] = None, window: int = 0):
-    """q: [Tq, hq, d], k/v: [Tk, hkv, d] fp32.  causal_offset = position of q row 0 (None: no mask)."""
+def attention(q, k, v, scale, causal_offset: Optional[int] = None, window: int = 0, sink=None):
+    """q: [Tq, hq, d], k/v: [Tk, hkv, d] fp32.  causal_offset = position of q row 0 (None: no mask).
+    sink: optional [hq] logits of a value-less extra softmax column (sliding-window + sink attention)."""
     tq, hq, d = q.shape
     tk, hkv, _ = k.shape
     g = hq // hkv
@@ -142,5 +143,9 @@ def attention(q, k, v, scale, causal_offset: Optional[int] = None, window: int =
         if window > 0:
             mask = mask | (kpos <= qpos - window)
         s = s.masked_fill(mask.unsqueeze(0), float("-inf"))
-    p = torch.softmax(s, -1)
+    if sink is not None:
+        s = torch.cat([s, sink.float().view(hq, 1, 1).expand(hq, tq, 1)], dim=-1)
+        p = torch.softmax(s, -1)[..., :-1]
+    else:
+        p = torch.softmax(s, -1)
     return torch.einsum("hqk,khd->qhd", p, vv)
