@@ -398,7 +398,10 @@ def main(argv=None) -> int:
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--model", default="tiny", choices=["tiny", "fake"])
     ap.add_argument("--slots", type=int, default=8)
+    ap.add_argument("--config", default="", help="deployment JSON (see dgpp_b200.cli resolve); overrides the flags above")
     args = ap.parse_args(argv)
+    if args.config:
+        return serve_deployment(args.config)
     tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)], rt.SplitPattern.Qwen2)
     if args.model == "fake":
         eng = rt.FakeEngine(slots=args.slots, block_tokens=16, blocks=4096, max_context=8192, vocab=256)
@@ -418,6 +421,66 @@ def main(argv=None) -> int:
             eng = ReferenceEngine(DenseModel.random_init(cfg, device="cpu", seed=0, std=0.05), slots=args.slots)
     srv = Server(eng, tok, model_name=f"dgpp-b200-{args.model}", host=args.host, port=args.port, eos_ids=[257])
     print(f"listening on http://{args.host}:{srv.start()}", flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        srv.stop()
+    return 0
+
+
+def serve_deployment(config_path: str) -> int:
+    """Serve the checkpoint a deployment JSON names: weights through the native loader (or this rank's resident
+    image), tokenizer.json and the chat template of the checkpoint directory, engine sized by the config.
+    `model` may also be "fake" / "tiny" (no checkpoint: the launcher's smoke deployments)."""
+    import os
+
+    text = open(config_path).read()
+    cfg_json, digest = rt.parse_cluster_config(text)
+    cfg = json.loads(cfg_json)
+    rt.set_log_level(cfg["log_level"])
+    rt.log("info", "serve", f"config: {cfg_json} digest={digest:016x}")
+    eos = [257]
+    template = DEFAULT_TEMPLATE
+    if cfg["model"] in ("fake", "tiny"):
+        return main(["--model", cfg["model"], "--host", cfg["host"], "--port", str(cfg["port"]),
+                     "--slots", str(cfg["max_concurrency"])])
+    import torch
+
+    from ..engine.adapters import KernelEngine
+    from ..engine.llm_engine import LLMEngine
+    from ..loaders import resident_image
+    from ..loaders.checkpoint import dense_config_from_hf, load_dense, open_checkpoint
+
+    if cfg["tensor_parallel"] != 1:
+        raise SystemExit("the HTTP front end drives one rank; tensor-parallel serving is started through bench.py / "
+                         "the engine API (sampling needs the full vocabulary on one rank)")
+    ck = open_checkpoint(cfg["model"])
+    dcfg = dense_config_from_hf(ck.config)
+    cache_dir = os.environ.get("DGPP_RESIDENT_CACHE_DIR", "")
+    build = lambda: load_dense(cfg["model"], device="cuda")
+    if cache_dir:
+        model, hit = resident_image.load_or_build(build, cache_dir, f"{ck.dir}", dcfg, device="cuda")
+        rt.log("info", "serve", f"weights from {'the resident image' if hit else 'the checkpoint (image written)'}")
+    else:
+        model = build()
+    tok = rt.Tokenizer.from_file(os.path.join(ck.dir, "tokenizer.json"))
+    tc_path = os.path.join(ck.dir, "tokenizer_config.json")
+    if os.path.exists(tc_path):
+        tc = json.load(open(tc_path))
+        template = tc.get("chat_template") or template
+        e = tc.get("eos_token")
+        e = e.get("content") if isinstance(e, dict) else e
+        if e and tok.token_to_id(e) >= 0:
+            eos = [tok.token_to_id(e)]
+    gen = ck.config.get("eos_token_id")
+    if gen is not None:
+        eos = sorted(set(eos + (list(gen) if isinstance(gen, list) else [gen])))
+    eng = KernelEngine(LLMEngine(model, max_batch=cfg["max_concurrency"], max_seq_len=cfg["max_context"],
+                                 prefill_chunk=cfg["prefill_chunk"]))
+    srv = Server(eng, tok, template_src=template, model_name=os.path.basename(os.path.normpath(ck.dir)),
+                 host=cfg["host"], port=cfg["port"], eos_ids=eos)
+    print(f"listening on http://{cfg['host']}:{srv.start()}", flush=True)
     try:
         while True:
             time.sleep(3600)
