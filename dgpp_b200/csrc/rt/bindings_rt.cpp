@@ -43,6 +43,9 @@ class PyEngine : public SchedulerEngine {
     PYBIND11_OVERRIDE_PURE(std::vector<std::vector<int32_t>>, SchedulerEngine, step_batch, slots);
   }
   int max_tokens_per_step() const override { PYBIND11_OVERRIDE(int, SchedulerEngine, max_tokens_per_step); }
+  int64_t usable_prefix(const std::vector<int32_t>& blocks) const override {
+    PYBIND11_OVERRIDE(int64_t, SchedulerEngine, usable_prefix, blocks);
+  }
   std::vector<int32_t> slot_blocks(int slot) const override {
     PYBIND11_OVERRIDE_PURE(std::vector<int32_t>, SchedulerEngine, slot_blocks, slot);
   }

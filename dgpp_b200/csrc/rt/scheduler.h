@@ -42,6 +42,10 @@ class SchedulerEngine {
   virtual int64_t max_context() const = 0;         // longest sequence a slot can hold
   // Make slot own blocks covering `tokens` positions (after any attached prefix).  false = pool exhausted.
   virtual bool reserve(int slot, int64_t tokens) = 0;
+  // How many of the matched cached blocks (a prefix of `blocks`) the engine can resume from.  Engines whose state is
+  // more than KV blocks (recurrent layers) keep state snapshots only at some block boundaries and answer with the
+  // longest prefix that ends on one; the default is all of them.
+  virtual int64_t usable_prefix(const std::vector<int32_t>& blocks) const { return static_cast<int64_t>(blocks.size()); }
   // Share cached blocks as the first blocks of an empty slot.
   virtual void attach_prefix(int slot, const std::vector<int32_t>& blocks) = 0;
   // Run prompt tokens [pos, pos+count) of the slot.  Returns the first generated token when `last`, else -1.
@@ -318,6 +322,13 @@ class Scheduler {
       PrefixHit hit;
       if (cfg_.prefix_cache && sl.req.prefix_cache && seq_len >= cfg_.prefix_min_tokens)
         hit = cache_.lookup(sl.tokens.data(), seq_len, meters_.ticks);
+      if (hit.tokens > 0) {
+        const int64_t keep = std::max<int64_t>(0, std::min<int64_t>(eng_->usable_prefix(hit.blocks), static_cast<int64_t>(hit.blocks.size())));
+        if (keep < static_cast<int64_t>(hit.blocks.size())) {
+          hit.blocks.resize(static_cast<size_t>(keep));
+          hit.tokens = keep * eng_->block_tokens();
+        }
+      }
       slots_[s] = std::move(sl);
       Slot& cur = slots_[s];
       if (hit.tokens > 0) {

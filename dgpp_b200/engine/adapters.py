@@ -294,3 +294,135 @@ class KernelEngine(rt.SchedulerEngine):
             self.pending[s] = toks[i]
             out.append([toks[i]])
         return out
+
+
+class HybridEngine(rt.SchedulerEngine):
+    """The hybrid (Gated DeltaNet + gated full attention + MoE) runner behind the scheduler.
+
+    A request's state is its paged KV blocks (attention layers) plus one convolution tail and one delta-rule memory
+    per GDN layer.  The prefix cache shares KV blocks by hash; the recurrent state cannot be rebuilt from blocks, so
+    the engine snapshots it whenever a prefill crosses a multiple of `snapshot_every` tokens and files the snapshot
+    under the physical block that ends there (with the block's generation, so a recycled block never matches).
+    `usable_prefix` tells the scheduler how much of a matched chain ends on a live snapshot; `attach_prefix` shares
+    the blocks and restores that snapshot.  (reference counterparts: src/engine/prefix_arena.hpp state snapshots at
+    cut positions, src/models/kda_snapshot.hpp, src/sched/prefix_cache.cpp.)"""
+
+    def __init__(self, runner, snapshot_every: int = 1024, max_snapshots: int = 64, prefill_chunk: int = 256):
+        super().__init__()
+        self.r = runner
+        self.kv = runner.kv
+        page = self.kv.page
+        self.snapshot_every = max(page, snapshot_every // page * page)
+        self.max_snapshots = max_snapshots
+        self.prefill_chunk = prefill_chunk
+        self.snaps = {}                 # block id -> (generation, [per GDN layer (conv, ssm)], stamp)
+        self.stamp = 0
+        self.pending = [None] * len(runner.lengths)
+        self.snapshots_taken = self.snapshots_restored = 0
+
+    # ---- geometry
+    def max_concurrent(self):
+        return len(self.r.lengths)
+
+    def block_tokens(self):
+        return self.kv.page
+
+    def total_blocks(self):
+        return self.kv.num_blocks
+
+    def free_blocks(self):
+        return self.kv.free_blocks()
+
+    def max_context(self):
+        return (self.kv.max_blocks - 1) * self.kv.page
+
+    def reserve(self, slot, tokens):
+        return self.kv.reserve(slot, tokens)
+
+    def slot_blocks(self, slot):
+        return list(self.kv.req_blocks[slot])
+
+    def retain_block(self, b):
+        self.kv.alloc.retain(b)
+
+    def release_block(self, b):
+        self.kv.alloc.release(b)
+
+    def block_refcount(self, b):
+        return self.kv.alloc.refcount(b)
+
+    # ---- snapshots
+    def _live(self, block):
+        s = self.snaps.get(block)
+        if s is None:
+            return None
+        if s[0] != self.kv.alloc.generation(block) or self.kv.alloc.refcount(block) <= 0:
+            del self.snaps[block]
+            return None
+        return s
+
+    def _snapshot(self, slot, tokens_done):
+        block = self.kv.req_blocks[slot][tokens_done // self.kv.page - 1]
+        if len(self.snaps) >= self.max_snapshots:
+            dead = [b for b in self.snaps if self._live(b) is None]
+            if len(self.snaps) >= self.max_snapshots:
+                oldest = min(self.snaps, key=lambda b: self.snaps[b][2])
+                del self.snaps[oldest]
+        self.stamp += 1
+        state = [st.snapshot(slot) for st in self.r.gdn_state.values()]
+        self.snaps[block] = (self.kv.alloc.generation(block), state, self.stamp)
+        self.snapshots_taken += 1
+
+    def usable_prefix(self, blocks):
+        for j in range(len(blocks), 0, -1):
+            if self._live(blocks[j - 1]) is not None:
+                return j
+        return 0
+
+    def attach_prefix(self, slot, blocks):
+        blocks = list(blocks)
+        snap = self._live(blocks[-1])
+        assert snap is not None, "attach_prefix without a state snapshot at the cut (usable_prefix decides the cut)"
+        self.kv.attach(slot, blocks)
+        for st, s in zip(self.r.gdn_state.values(), snap[1]):
+            st.restore(slot, s)
+        self.stamp += 1
+        self.snaps[blocks[-1]] = (snap[0], snap[1], self.stamp)
+        self.r.lengths[slot] = len(blocks) * self.kv.page
+        self.snapshots_restored += 1
+
+    # ---- execution
+    def prefill(self, slot, tokens, pos, last):
+        tokens = list(tokens)
+        if pos == 0 and self.r.lengths[slot] != 0:
+            self.close(slot)
+        assert self.r.lengths[slot] == pos, (self.r.lengths[slot], pos)
+        logits = None
+        o = 0
+        while o < len(tokens):
+            at = pos + o
+            to_cut = self.snapshot_every - at % self.snapshot_every
+            n = min(len(tokens) - o, to_cut)
+            logits = self.r.prefill(slot, tokens[o:o + n], chunk=self.prefill_chunk)
+            o += n
+            if (pos + o) % self.snapshot_every == 0:
+                self._snapshot(slot, pos + o)
+        if last:
+            tok = int(torch.argmax(logits[0]).item())
+            self.pending[slot] = tok
+            return tok
+        return -1
+
+    def step_batch(self, slots):
+        slots = list(slots)
+        logits = self.r.decode(slots, [self.pending[s] for s in slots])
+        toks = torch.argmax(logits[:len(slots)], dim=-1).tolist()
+        out = []
+        for s, t in zip(slots, toks):
+            self.pending[s] = int(t)
+            out.append([int(t)])
+        return out
+
+    def close(self, slot):
+        self.r.reset(slot)
+        self.pending[slot] = None

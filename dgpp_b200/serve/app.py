@@ -396,7 +396,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
-    ap.add_argument("--model", default="tiny", choices=["tiny", "fake"])
+    ap.add_argument("--model", default="tiny", choices=["tiny", "fake", "hybrid-tiny"])
     ap.add_argument("--slots", type=int, default=8)
     ap.add_argument("--config", default="", help="deployment JSON (see dgpp_b200.cli resolve); overrides the flags above")
     args = ap.parse_args(argv)
@@ -405,6 +405,18 @@ def main(argv=None) -> int:
     tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)], rt.SplitPattern.Qwen2)
     if args.model == "fake":
         eng = rt.FakeEngine(slots=args.slots, block_tokens=16, blocks=4096, max_context=8192, vocab=256)
+    elif args.model == "hybrid-tiny":
+        # Gated DeltaNet + gated attention + MoE family behind the same scheduler / HTTP surface (needs a GPU)
+        from ..engine.adapters import HybridEngine
+        from ..models.hybrid import HybridConfig, HybridModel, HybridRunner
+        from ..models.moe import MoEConfig
+
+        hc = HybridConfig(layers=4, hidden=512, full_every=4, q_heads=4, kv_heads=2, head_dim=128, gdn_k_heads=2,
+                          gdn_v_heads=4, gdn_dk=128, gdn_dv=128, ffn=1024, vocab=4096,
+                          moe=MoEConfig(experts=16, top_k=2, moe_ffn=512, shared_ffn=512))
+        hm = HybridModel.random_init(hc, "cuda", seed=0, std=0.05)
+        eng = HybridEngine(HybridRunner(hm, max_rows=256, slots=args.slots, max_seq_len=4096, device="cuda"),
+                           snapshot_every=512)
     else:
         import torch
 

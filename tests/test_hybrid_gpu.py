@@ -44,3 +44,45 @@ def test_hybrid_runner_matches_reference(dev, moe):
     assert r.lengths[1] == 43 and r.lengths[2] == 23
     r.reset(1)
     assert r.lengths[1] == 0
+
+
+def test_hybrid_engine_behind_the_scheduler_with_state_snapshots(dev):
+    """Requests sharing a long prefix: the second one attaches the cached KV blocks AND the recurrent-state snapshot
+    taken at the cut; its tokens equal those of a run without any prefix cache."""
+    from dgpp_b200.engine.adapters import HybridEngine
+    from dgpp_b200.models.hybrid import HybridConfig, HybridModel, HybridRunner
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.runtime import rt
+
+    cfg = HybridConfig(layers=4, hidden=512, full_every=4, q_heads=4, kv_heads=2, head_dim=128, gdn_k_heads=2,
+                       gdn_v_heads=4, gdn_dk=128, gdn_dv=128, ffn=1024, vocab=2048)
+    m = HybridModel.random_init(cfg, dev, seed=7, std=0.05)
+    g = torch.Generator().manual_seed(3)
+    shared = torch.randint(0, cfg.vocab, (300,), generator=g).tolist()
+    reqs = {"a": shared + torch.randint(0, cfg.vocab, (21,), generator=g).tolist(),
+            "b": shared + torch.randint(0, cfg.vocab, (35,), generator=g).tolist(),
+            "c": torch.randint(0, cfg.vocab, (90,), generator=g).tolist()}
+
+    def run(prefix: bool, order):
+        r = HybridRunner(m, max_rows=64, slots=2, max_seq_len=512, device=dev)
+        eng = HybridEngine(r, snapshot_every=128, prefill_chunk=64)
+        sc = rt.SchedulerConfig()
+        sc.prefix_cache = prefix
+        sc.prefix_min_tokens = 16
+        s = rt.Scheduler(eng, sc)
+        out = {}
+        for rid in order:                       # one after the other, so that "b" can hit what "a" published
+            s.submit(rid, reqs[rid], 6)
+            s.run(100000)
+            for kind, x, a, b in s.events():
+                if kind == "token":
+                    out.setdefault(x, []).append(a)
+        ops.check_status()
+        return out, s.meters(), eng
+
+    plain, m0, _ = run(False, ["a", "b", "c"])
+    cached, m1, eng = run(True, ["a", "b", "c"])
+    assert m0["prefix_hit_tokens"] == 0
+    # the chain matches 256 + tokens (4 blocks of 64), snapshots exist at 128 and 256 -> 256 tokens are reused
+    assert m1["prefix_hit_tokens"] == 256 and eng.snapshots_restored == 1 and eng.snapshots_taken >= 2
+    assert cached == plain and all(len(v) == 6 for v in cached.values())

@@ -245,3 +245,54 @@ def test_json_parser_strictness():
     for bad in ['{"a": }', '[1,]', '{"a" 1}', '"\\x"', '01', '[1] x']:
         with pytest.raises(Exception):
             rt.json_roundtrip(bad)
+
+
+def test_engine_can_shorten_a_prefix_hit():
+    """An engine that can only resume at some block boundaries (recurrent state snapshots) trims the matched chain."""
+    class Eng(rt.SchedulerEngine):
+        def __init__(self):
+            super().__init__()
+            self.t = rt.PagedBlockTable(64)
+            self.blocks = {}
+            self.attached = []
+            self.prefilled = []
+        def max_concurrent(self): return 2
+        def block_tokens(self): return 16
+        def total_blocks(self): return 64
+        def free_blocks(self): return self.t.free_count()
+        def max_context(self): return 512
+        def reserve(self, slot, tokens):
+            cur = self.blocks.setdefault(slot, [])
+            while len(cur) * 16 < tokens:
+                cur.append(self.t.alloc())
+            return True
+        def usable_prefix(self, blocks): return len(blocks) // 4 * 4      # snapshots every 4 blocks
+        def attach_prefix(self, slot, blocks):
+            self.attached.append(len(blocks))
+            for b in blocks:
+                self.t.retain(b)
+            self.blocks[slot] = list(blocks)
+        def prefill(self, slot, tokens, pos, last):
+            self.prefilled.append((pos, len(tokens)))
+            return 7 if last else -1
+        def step_batch(self, slots): return [[7] for _ in slots]
+        def slot_blocks(self, slot): return list(self.blocks.get(slot, []))
+        def retain_block(self, b): self.t.retain(b)
+        def release_block(self, b): self.t.release(b)
+        def block_refcount(self, b): return self.t.refcount(b)
+        def close(self, slot):
+            for b in self.blocks.pop(slot, []):
+                self.t.release(b)
+
+    eng = Eng()
+    cfg = rt.SchedulerConfig()
+    cfg.prefix_min_tokens = 16
+    s = rt.Scheduler(eng, cfg)
+    prompt = list(range(100, 100 + 16 * 7 + 5))          # 7 full blocks + 5 tokens
+    s.submit("a", prompt, 2)
+    s.run(10000)
+    s.submit("b", prompt, 2)
+    s.run(10000)
+    assert eng.attached == [4]                            # 7 blocks matched, the engine resumes at block 4
+    assert s.meters()["prefix_hit_tokens"] == 64
+    assert (64, len(prompt) - 64) in eng.prefilled or sum(n for p, n in eng.prefilled if p >= 64) >= len(prompt) - 64
