@@ -3,6 +3,7 @@
 #include <pybind11/stl.h>
 
 #include "rt/chat_template.h"
+#include "rt/ds_prompt.h"
 #include "rt/json.h"
 #include "rt/tokenizer.h"
 
@@ -68,6 +69,8 @@ void bind_text(py::module_& m) {
         return t.render(json::parse(context_json));
       });
 
+  // prompt renderer for checkpoints without a chat template (DeepSeek-V4 style layout); globals as JSON text
+  m.def("deepseek_prompt", [](const std::string& globals_json) { return DeepSeekPrompt::render(json::parse(globals_json)); });
   m.def("json_roundtrip", [](const std::string& s, bool reject_dup) { return json::parse(s, reject_dup).dump(); },
         py::arg("text"), py::arg("reject_duplicates") = false);
 }

@@ -12,6 +12,7 @@ cached prefix only bumps reference counts.
 """
 from __future__ import annotations
 
+import time
 from typing import List, Optional
 
 import torch
@@ -164,6 +165,8 @@ class KernelEngine(rt.SchedulerEngine):
         self.slot_cfg = [None] * b
         self.last_logprobs = [None] * b
         self.sampler = None
+        from ..utils.step_timing import StepTimer
+        self.timer = StepTimer()                 # DGPP_STEP_TIMING=1 turns the event slots on
 
     def max_concurrent(self):
         return self.e.max_batch
@@ -259,7 +262,8 @@ class KernelEngine(rt.SchedulerEngine):
         return [p.token for p in picked]
 
     def prefill(self, slot, tokens, pos, last):
-        first = self.e.prefill(slot, list(tokens), start_pos=pos)
+        with self.timer.phase("prefill"):
+            first = self.e.prefill(slot, list(tokens), start_pos=pos)
         self.filled[slot] = pos + len(tokens)
         if last:
             if self.slot_cfg[slot]:
@@ -280,9 +284,15 @@ class KernelEngine(rt.SchedulerEngine):
         e.d_tokens[:b].copy_(self.h_tok[:b], non_blocking=True)
         e.d_positions[:b].copy_(self.h_pos[:b], non_blocking=True)
         e.d_row_req[:b].copy_(self.h_req[:b], non_blocking=True)
-        e.decode_step(b)
+        with self.timer.phase("decode"):
+            e.decode_step(b)
         self.h_out[:b].copy_(e.d_tokens[:b], non_blocking=True)
+        t_sync = time.perf_counter() if self.timer.enabled else 0.0
         torch.cuda.current_stream().synchronize()
+        if self.timer.enabled:
+            self.timer.total_ms["sync"] += (time.perf_counter() - t_sync) * 1e3
+            self.timer.count["sync"] += 1
+            self.timer.collect()
         for s in slots:
             self.filled[s] += 1
         toks = [int(self.h_out[i]) for i in range(b)]
