@@ -106,7 +106,7 @@ void bind_grammar(py::module_& m) {
      py::arg("budget") = int64_t(-1));
 
   // ---- streaming tool-call parser
-  py::enum_<tools::Format>(m, "ToolFormat").value("JsonTags", tools::Format::JsonTags).value("ArgTags", tools::Format::ArgTags);
+  py::enum_<tools::Format>(m, "ToolFormat").value("JsonTags", tools::Format::JsonTags).value("ArgTags", tools::Format::ArgTags).value("Dsml", tools::Format::Dsml);
   py::class_<tools::ToolParser>(m, "ToolParser")
       .def(py::init<tools::Format, std::string>(), py::arg("format"), py::arg("id_prefix") = "call_")
       .def("calls", &tools::ToolParser::calls)

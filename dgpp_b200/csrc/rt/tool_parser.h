@@ -5,6 +5,9 @@
 //   JsonTags   <tool_call>{"name": "f", "arguments": {...}}</tool_call>            (Qwen / Hermes style)
 //   ArgTags    <tool_call>f\n<arg_key>k</arg_key>\n<arg_value>v</arg_value>...</tool_call>   (GLM markers; a value
 //              that parses as JSON is kept as JSON, anything else becomes a string)
+//   Dsml       <｜DSML｜tool_calls> <｜DSML｜invoke name="f"> <｜DSML｜parameter name="k" string="true|false">v</｜DSML｜parameter>
+//              ... </｜DSML｜invoke> </｜DSML｜tool_calls>   (every invoke is one call; string="false" values are JSON; the
+//              tool_calls wrapper tags are formatting and never reach the content)
 // Content outside the tags is released as soon as it cannot be the beginning of an opening tag.  A call is emitted
 // when its closing tag has arrived (name, arguments as one JSON text, running index, generated id).  A body that is
 // not a valid call, or text still open at finish(), is returned as content: nothing the model wrote is dropped.
@@ -20,7 +23,7 @@
 namespace dgpp {
 namespace tools {
 
-enum class Format { JsonTags, ArgTags };
+enum class Format { JsonTags, ArgTags, Dsml };
 
 struct Event {
   bool is_call = false;
@@ -31,7 +34,16 @@ struct Event {
 
 class ToolParser {
  public:
-  explicit ToolParser(Format f, std::string id_prefix = "call_") : fmt_(f), id_prefix_(std::move(id_prefix)) {}
+  explicit ToolParser(Format f, std::string id_prefix = "call_") : fmt_(f), id_prefix_(std::move(id_prefix)) {
+    if (f == Format::Dsml) {
+      open_ = "<\xef\xbd\x9c" "DSML\xef\xbd\x9c" "invoke";
+      close_ = "</\xef\xbd\x9c" "DSML\xef\xbd\x9c" "invoke>";
+      silent_ = {"<\xef\xbd\x9c" "DSML\xef\xbd\x9c" "tool_calls>", "</\xef\xbd\x9c" "DSML\xef\xbd\x9c" "tool_calls>"};
+    } else {
+      open_ = "<tool_call>";
+      close_ = "</tool_call>";
+    }
+  }
 
   std::vector<Event> feed(const std::string& piece) {
     buf_ += piece;
@@ -42,25 +54,48 @@ class ToolParser {
           if (buf_[0] == '\n') buf_.erase(0, 1);
           skip_newline_ = false;
         }
-        const size_t p = buf_.find(kOpen);
+        // earliest of: the opening tag of a call, a formatting-only tag of this format
+        size_t p = buf_.find(open_);
+        const std::string* silent = nullptr;
+        for (const auto& t : silent_) {
+          const size_t q = buf_.find(t);
+          if (q != std::string::npos && (p == std::string::npos || q < p)) { p = q; silent = &t; }
+        }
         if (p == std::string::npos) {
-          // keep the longest tail that is a proper prefix of the opening tag
+          // keep the longest tail that is a proper prefix of one of those tags
           size_t hold = 0;
-          const size_t lim = std::min(buf_.size(), sizeof(kOpen) - 2);
-          for (size_t k = lim; k > 0; --k)
-            if (buf_.compare(buf_.size() - k, k, kOpen, k) == 0) { hold = k; break; }
-          emit_content(out, buf_.substr(0, buf_.size() - hold));
-          buf_.erase(0, buf_.size() - hold);
+          auto consider = [&](const std::string& tag) {
+            const size_t lim = std::min(buf_.size(), tag.size() - 1);
+            for (size_t k = lim; k > hold; --k)
+              if (buf_.compare(buf_.size() - k, k, tag, 0, k) == 0) { hold = k; break; }
+          };
+          consider(open_);
+          for (const auto& t : silent_) consider(t);
+          size_t cut = buf_.size() - hold;
+          // newlines that may turn out to separate the text from a formatting-only tag wait for what follows them
+          if (!silent_.empty())
+            while (cut > 0 && buf_[cut - 1] == '\n') --cut;
+          emit_content(out, buf_.substr(0, cut));
+          buf_.erase(0, cut);
           return out;
         }
+        if (silent) {
+          std::string before = buf_.substr(0, p);
+          // the blank line that separates the answer text from the tool-call block is formatting too
+          while (!before.empty() && before.back() == '\n') before.pop_back();
+          emit_content(out, before);
+          buf_.erase(0, p + silent->size());
+          skip_newline_ = true;
+          continue;
+        }
         emit_content(out, buf_.substr(0, p));
-        buf_.erase(0, p + sizeof(kOpen) - 1);
+        buf_.erase(0, p + open_.size());
         inside_ = true;
       } else {
-        const size_t p = buf_.find(kClose);
+        const size_t p = buf_.find(close_);
         if (p == std::string::npos) return out;
         const std::string body = buf_.substr(0, p);
-        buf_.erase(0, p + sizeof(kClose) - 1);
+        buf_.erase(0, p + close_.size());
         inside_ = false;
         Event e;
         if (parse_body(body, e)) {
@@ -70,14 +105,14 @@ class ToolParser {
           out.push_back(std::move(e));
           skip_newline_ = true;   // one separator newline after a call is formatting, not content
         } else {
-          emit_content(out, std::string(kOpen) + body + kClose);
+          emit_content(out, open_ + body + close_);
         }
       }
     }
   }
   std::vector<Event> finish() {
     std::vector<Event> out;
-    if (inside_) emit_content(out, std::string(kOpen) + buf_);
+    if (inside_) emit_content(out, open_ + buf_);
     else emit_content(out, buf_);
     buf_.clear();
     inside_ = false;
@@ -86,9 +121,6 @@ class ToolParser {
   int calls() const { return calls_; }
 
  private:
-  static constexpr char kOpen[] = "<tool_call>";
-  static constexpr char kClose[] = "</tool_call>";
-
   static void emit_content(std::vector<Event>& out, const std::string& text) {
     if (text.empty()) return;
     if (!out.empty() && !out.back().is_call) { out.back().text += text; return; }
@@ -117,6 +149,41 @@ class ToolParser {
       } catch (const std::exception&) {
         return false;
       }
+    }
+    if (fmt_ == Format::Dsml) {
+      // body:  name="f">  then parameter elements
+      static const std::string kParam = "<\xef\xbd\x9c" "DSML\xef\xbd\x9c" "parameter";
+      static const std::string kParamEnd = "</\xef\xbd\x9c" "DSML\xef\xbd\x9c" "parameter>";
+      auto attr = [](const std::string& head, const std::string& key, std::string* val) {
+        const size_t a = head.find(key + "=\"");
+        if (a == std::string::npos) return false;
+        const size_t b = head.find('"', a + key.size() + 2);
+        if (b == std::string::npos) return false;
+        *val = head.substr(a + key.size() + 2, b - a - key.size() - 2);
+        return true;
+      };
+      const size_t gt = body.find('>');
+      if (gt == std::string::npos || !attr(body.substr(0, gt), "name", &e.name) || e.name.empty()) return false;
+      json::Value args = json::Value::object();
+      size_t p = body.find(kParam, gt);
+      while (p != std::string::npos) {
+        const size_t he = body.find('>', p);
+        const size_t pe = he == std::string::npos ? std::string::npos : body.find(kParamEnd, he);
+        if (pe == std::string::npos) return false;
+        const std::string head = body.substr(p, he - p);
+        std::string key, is_str = "true";
+        if (!attr(head, "name", &key)) return false;
+        attr(head, "string", &is_str);
+        const std::string raw = body.substr(he + 1, pe - he - 1);
+        if (is_str == "false") {
+          try { args.set(key, json::parse(trim(raw))); } catch (const std::exception&) { args.set(key, json::Value(raw)); }
+        } else {
+          args.set(key, json::Value(raw));
+        }
+        p = body.find(kParam, pe);
+      }
+      e.arguments = args.dump();
+      return true;
     }
     // ArgTags: first line = function name, then key / value tag pairs
     const std::string t = trim(body);
@@ -148,6 +215,8 @@ class ToolParser {
 
   Format fmt_;
   std::string id_prefix_;
+  std::string open_, close_;
+  std::vector<std::string> silent_;
   std::string buf_;
   bool inside_ = false, skip_newline_ = false;
   int calls_ = 0;

@@ -63,3 +63,17 @@ def test_arg_tags_format():
 def test_tools_block():
     s = rt.render_tools_block(json.dumps([{"type": "function", "function": {"name": "f"}}]))
     assert s.startswith("<tools>\n") and s.endswith("</tools>") and '"name":"f"' in s
+
+
+def test_dsml_calls_in_any_chunking():
+    text = ('I will look.\n\n<｜DSML｜tool_calls>\n<｜DSML｜invoke name="get_weather">\n'
+            '<｜DSML｜parameter name="city" string="true">Oslo</｜DSML｜parameter>\n'
+            '<｜DSML｜parameter name="days" string="false">3</｜DSML｜parameter>\n</｜DSML｜invoke>\n'
+            '<｜DSML｜invoke name="now">\n</｜DSML｜invoke>\n</｜DSML｜tool_calls>').encode()
+    rnd = random.Random(1)
+    for trial in range(40):
+        cuts = sorted(rnd.sample(range(1, len(text)), rnd.randint(0, 40)))
+        content, calls = run(rt.ToolFormat.Dsml, text, cuts)
+        assert content == b"I will look.", (cuts, content)
+        assert [(c[0], c[2], json.loads(c[3])) for c in calls] == [(0, "get_weather", {"city": "Oslo", "days": 3}),
+                                                                    (1, "now", {})], cuts
