@@ -143,14 +143,126 @@ pick_merge_kernel(CommState c, int32_t* __restrict__ ids, float* __restrict__ va
   if (t == 0) *c.pick_epoch = epoch;
 }
 
+// Second half of a fused GEMM -> reduce-scatter -> all-gather (prefill sizes).  The tensor-parallel GEMM's epilogue
+// has pushed every output tile [tile_rows tokens x 128 columns] as bf16 into slot `source rank` of the rank that OWNS
+// those tokens (token tiles are dealt to ranks in contiguous runs of `tiles_per_rank`) and bumped the owner's arrival
+// counter of (source, token tile).  Here CTA (token tile t, column chunk) of the owner waits until all W sources have
+// delivered all `n_tiles` tiles of t, folds the W partial tiles in ascending rank order (fp32, one bf16 rounding),
+// adds the residual stream, stores the new residual rows locally and into every peer's slot `owner` (those rows of a
+// source slot are unused by the reduce-scatter), and raises the peers' all-gather flag of (t, chunk).  CTAs of tiles
+// owned by other ranks wait for that flag and copy the rows into the local residual stream.  Blocks are numbered so
+// that a rank's own (folding) tiles are scheduled first: a fold never waits on a copy, so the ranks cannot block
+// each other.  Traffic per rank is 2 (W-1)/W of the tensor instead of (W-1) for the one-shot all-reduce.
+// x: [T, H] bf16 residual stream, updated in place on every rank to bf16(x + bf16(sum over ranks of the partials)).
+__global__ void __launch_bounds__(256)
+rs_ag_kernel(CommState c, bf16* __restrict__ x, int T, int H, int tile_rows, int tiles_per_rank, int n_tiles,
+             DeviceStatus* status) {
+  pdl_wait();
+  const uint32_t epoch = *c.epoch + 1;
+  const int parity = epoch & 1;
+  const int chunks = gridDim.y, chunk = blockIdx.y;
+  const int tiles = gridDim.x;
+  // own tiles first: block b of the grid's x dimension handles tile (first own tile + b) modulo the tile count
+  const int own0 = min(c.rank * tiles_per_rank, tiles);
+  const int t = (own0 + static_cast<int>(blockIdx.x)) % tiles;
+  const int owner = min(t / tiles_per_rank, c.world - 1);
+  const int r0 = t * tile_rows, rows = min(tile_rows, T - r0);
+  const int cols = H / chunks, c0 = chunk * cols, vec = cols / 8;      // host checks H % (8 * chunks) == 0
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (owner == c.rank) {
+    if (threadIdx.x < c.world) {
+      uint32_t* cnt = rs_counter(c, c.rank, parity, threadIdx.x, t);
+      bool got = false;
+      const long long t0 = clock64();
+      for (long long i = 0; !got; ++i) {
+        got = ld_acquire_sys(cnt) >= static_cast<uint32_t>(n_tiles);
+        if (!got) {
+          if (i > (1 << 14)) __nanosleep(64);
+          if ((i & 255) == 255 && clock64() - t0 > 4000000000ll) break;
+        }
+      }
+      if (!got) {
+        if (atomicCAS(&status->code, 0, kTimeoutPeerFlag) == 0) status->detail = 200 + threadIdx.x;
+        atomicAdd(&status->count, 1);
+        ok_s = 0;
+      }
+    }
+    __syncthreads();
+    if (ok_s) {
+      for (int i = threadIdx.x; i < rows * vec; i += blockDim.x) {
+        const int r = r0 + i / vec, v = i % vec;
+        const size_t off = (static_cast<size_t>(r) * H + c0) * 2 + static_cast<size_t>(v) * 16;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int s = 0; s < c.world; ++s) {
+          Pack16 pk;
+          pk.u = ld_v4_global_volatile(payload(c, c.rank, parity, s) + off);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += bf16_to_f32(pk.h[j]);
+        }
+        Pack16 xr;
+        xr.u = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(x) + off);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xr.h[j] = f32_to_bf16(bf16_to_f32(xr.h[j]) + bf16_to_f32(f32_to_bf16(acc[j])));
+        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(x) + off) = xr.u;
+        for (int d = 1; d < c.world; ++d) {
+          const int dst = (c.rank + d) % c.world;
+          st_v4_global(payload(c, dst, parity, c.rank) + off, xr.u);
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < c.world && threadIdx.x != c.rank && ok_s)
+      st_release_sys(ag_flag(c, threadIdx.x, parity, t, chunk), epoch);
+    // the last column chunk of this tile zeroes the arrival counters for the next use of this parity
+    if (threadIdx.x == 0) {
+      if (atomicAdd(rs_local_done(c, t), 1u) == static_cast<uint32_t>(chunks - 1)) {
+        *rs_local_done(c, t) = 0;
+        for (int s = 0; s < c.world; ++s) *rs_counter(c, c.rank, parity, s, t) = 0;
+        __threadfence_system();
+      }
+    }
+  } else {
+    if (threadIdx.x == 0 && !wait_flag(ag_flag(c, c.rank, parity, t, chunk), epoch)) {
+      if (atomicCAS(&status->code, 0, kTimeoutPeerFlag) == 0) status->detail = 300 + owner;
+      atomicAdd(&status->count, 1);
+      ok_s = 0;
+    }
+    __syncthreads();
+    if (ok_s) {
+      for (int i = threadIdx.x; i < rows * vec; i += blockDim.x) {
+        const int r = r0 + i / vec, v = i % vec;
+        const size_t off = (static_cast<size_t>(r) * H + c0) * 2 + static_cast<size_t>(v) * 16;
+        const uint4 val = ld_v4_global_volatile(payload(c, c.rank, parity, owner) + off);
+        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(x) + off) = val;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.done_ctas, 1u) == gridDim.x * gridDim.y - 1) {
+      *c.done_ctas = 0;
+      *c.epoch = epoch;
+      __threadfence();
+    }
+  }
+}
+
 }  // namespace dgpp
 
 using namespace dgpp;
 
 
 static size_t region_size(int world, size_t slot_bytes) {
+  const size_t rs_tables = (2 * static_cast<size_t>(world) * kCommMaxCtas + 2 * static_cast<size_t>(kCommMaxCtas) * kRsMaxChunks +
+                            kCommMaxCtas) * sizeof(uint32_t);
   return 2 * static_cast<size_t>(world) * slot_bytes + 2 * static_cast<size_t>(world) * kCommMaxCtas * sizeof(uint32_t) +
-         2 * static_cast<size_t>(world) * kPickRows * 8 + 2 * static_cast<size_t>(world) * sizeof(uint32_t) + 256;
+         2 * static_cast<size_t>(world) * kPickRows * 8 + 2 * static_cast<size_t>(world) * sizeof(uint32_t) + 512 + rs_tables;
 }
 
 // Step 1: allocate the local symmetric region; returns the comm handle and writes the 64-byte IPC handle.
@@ -242,6 +354,29 @@ DGPP_API int dgpp_comm_all_reduce(void* comm, void* data, const void* resid, int
   if (ctas > kCommMaxCtas) ctas = kCommMaxCtas;
   ar_oneshot_kernel<<<ctas, 256, 0, st>>>(c->st, static_cast<bf16*>(data), static_cast<const bf16*>(resid), n,
                                          device_status_ptr());
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Geometry of the reduce-scatter: token tiles of `tile_rows` rows are dealt to ranks in runs of tiles_per_rank.
+static int rs_tiles_per_rank(int T, int tile_rows, int world) {
+  const int tiles = dgpp_ceil_div(T, tile_rows);
+  return dgpp_ceil_div(tiles, world);
+}
+
+// x [T, H] += sum over ranks of the partial tiles the preceding dgpp_gemm_tc(..., comm_push) calls delivered.
+DGPP_API int dgpp_comm_rs_ag(void* comm, void* x, int T, int H, int tile_rows, cudaStream_t st) {
+  DgppComm* c = static_cast<DgppComm*>(comm);
+  const int tiles = dgpp_ceil_div(T, tile_rows);
+  DGPP_REQUIRE(T > 0 && tiles <= kCommMaxCtas, "rs_ag: %d rows in tiles of %d exceed %d token tiles", T, tile_rows, kCommMaxCtas);
+  DGPP_REQUIRE(H % 128 == 0, "rs_ag: hidden %d must be a multiple of 128", H);
+  DGPP_REQUIRE(static_cast<size_t>(T) * H * 2 <= c->st.slot_bytes, "rs_ag: %d x %d exceeds the slot", T, H);
+  int chunks = 1;
+  for (int cand : {16, 8, 5, 4, 2})
+    if (cand <= kRsMaxChunks && H % (cand * 8) == 0 && tiles * cand <= 592) { chunks = cand; break; }
+  rs_ag_kernel<<<dim3(tiles, chunks), 256, 0, st>>>(c->st, static_cast<bf16*>(x), T, H, tile_rows,
+                                                    rs_tiles_per_rank(T, tile_rows, c->st.world), H / 128,
+                                                    device_status_ptr());
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }

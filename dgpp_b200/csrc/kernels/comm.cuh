@@ -3,6 +3,10 @@
 //     [ 2 parities ][ W source slots ][ slot_bytes ]   payload pushed by the source rank
 //     [ 2 parities ][ W source slots ][ kCommMaxCtas ] uint32 flags (epoch numbers), one per pushed slice / tile
 //     pick table: [ 2 parities ][ W ][ kPickRows ] (value, id) pairs + [2][W] flags
+//     reduce-scatter tables: [ 2 parities ][ W source ranks ][ kCommMaxCtas token tiles ] uint32 arrival counters
+//                            (how many output tiles of that token tile the source has pushed; the owner zeroes them
+//                            after folding), [ 2 parities ][ kCommMaxCtas ][ kRsMaxChunks ] uint32 all-gather flags
+//                            (epoch numbers), [ kCommMaxCtas ] uint32 local fold counters
 // Peer memory is only touched with plain vector stores, volatile loads and system-scope flag accesses.
 #pragma once
 #include <stdint.h>
@@ -15,6 +19,7 @@ namespace dgpp {
 constexpr int kCommMaxWorld = 8;
 constexpr int kCommMaxCtas = 64;
 constexpr int kPickRows = 256;
+constexpr int kRsMaxChunks = 16;
 
 struct CommState {
   unsigned char* peers[kCommMaxWorld];  // base of every rank's symmetric region (peer-mapped pointers)
@@ -35,6 +40,25 @@ __device__ __forceinline__ uint32_t* flag(const CommState& c, int owner, int par
 __device__ __forceinline__ unsigned char* pick_base(const CommState& c, int owner) {
   return c.peers[owner] + 2 * static_cast<size_t>(c.world) * c.slot_bytes +
          2 * static_cast<size_t>(c.world) * kCommMaxCtas * sizeof(uint32_t);
+}
+
+__device__ __forceinline__ unsigned char* rs_base(const CommState& c, int owner) {
+  const size_t off = 2 * static_cast<size_t>(c.world) * kPickRows * 8 + 2 * static_cast<size_t>(c.world) * sizeof(uint32_t);
+  return pick_base(c, owner) + ((off + 255) & ~static_cast<size_t>(255));
+}
+// Arrival counter of (source rank, token tile) in `owner`'s region.
+__device__ __forceinline__ uint32_t* rs_counter(const CommState& c, int owner, int parity, int src, int tile) {
+  return reinterpret_cast<uint32_t*>(rs_base(c, owner)) + (static_cast<size_t>(parity) * c.world + src) * kCommMaxCtas + tile;
+}
+// All-gather flag of (token tile, column chunk) in `owner`'s region, written by the tile's owner rank.
+__device__ __forceinline__ uint32_t* ag_flag(const CommState& c, int owner, int parity, int tile, int chunk) {
+  uint32_t* base = reinterpret_cast<uint32_t*>(rs_base(c, owner)) + 2 * static_cast<size_t>(c.world) * kCommMaxCtas;
+  return base + (static_cast<size_t>(parity) * kCommMaxCtas + tile) * kRsMaxChunks + chunk;
+}
+__device__ __forceinline__ uint32_t* rs_local_done(const CommState& c, int tile) {
+  uint32_t* base = reinterpret_cast<uint32_t*>(rs_base(c, c.rank)) + 2 * static_cast<size_t>(c.world) * kCommMaxCtas +
+                   2 * static_cast<size_t>(kCommMaxCtas) * kRsMaxChunks;
+  return base + tile;
 }
 
 // Bounded spin on a flag written by a peer; false when it gave up (about 2 s).

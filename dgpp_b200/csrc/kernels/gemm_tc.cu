@@ -31,6 +31,7 @@
 #include "common/dtypes.cuh"
 #include "common/ptx.cuh"
 #include "kernels/gemm_common.cuh"
+#include "kernels/comm.cuh"
 
 namespace dgpp {
 
@@ -51,6 +52,11 @@ struct GemmParams {
   DeviceStatus* status;
   int T, N, K, ldc;
   int kb_per_split;        // k64 blocks per split
+  // Reduce-scatter push (tensor-parallel o_proj / down_proj at prefill sizes): the finished bf16 tile goes into slot
+  // `rank` of the rank that owns the tile's tokens (token tiles are dealt in runs of tiles_per_rank) and that
+  // owner's arrival counter of (this rank, token tile) is bumped; dgpp_comm_rs_ag folds and redistributes.
+  int push, tiles_per_rank;
+  CommState comm;
 };
 
 template <int BN>
@@ -261,6 +267,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
     tc_fence_after();
     const int n = n0 + q * 32 + lane;
     const int cols = min(BN, p.T - m0);
+    uint32_t push_epoch = 0;
+    int push_owner = 0;
+    bf16* push_dst = nullptr;
+    if (p.push) {
+      push_epoch = *p.comm.epoch + 1;
+      push_owner = min(static_cast<int>(blockIdx.y) / p.tiles_per_rank, p.comm.world - 1);
+      push_dst = reinterpret_cast<bf16*>(payload(p.comm, push_owner, push_epoch & 1, p.comm.rank));
+    }
     if (ok && !*abort_flag) {
       float* wsp = splits > 1 ? p.ws + (static_cast<size_t>(split) * p.T + m0) * p.N : nullptr;
 #pragma unroll 1
@@ -282,6 +296,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
               const float v = __uint_as_float(r[j]);
               if (splits > 1) {
                 wsp[static_cast<size_t>(m) * p.N + n] = v;
+              } else if (p.push) {
+                push_dst[static_cast<size_t>(m0 + m) * p.N + n] = f32_to_bf16(v * p.alpha);
               } else {
                 const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
                 float y = v * p.alpha;
@@ -295,6 +311,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
           }
         }
       }
+    }
+    if (p.push) {
+      // make the tile visible at system scope, then count it in at the owner (also after a failed wait: the owner's
+      // bounded wait reports the missing data through the status block of THIS rank, not by stalling there)
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0)
+        red_release_sys_add(rs_counter(p.comm, push_owner, push_epoch & 1, p.comm.rank, blockIdx.y), 1u);
     }
     if (splits > 1) {
       // publish partials, elect the last CTA of this tile, fold in ascending split order
@@ -379,17 +403,29 @@ using namespace dgpp;
 //
 // wmode: 0 bf16, 1 nvfp4, 2 fp8-block, 3 mxfp4.   a_f16 is ignored (kept for ABI stability).
 // bn: token tile (16, 32, 64, 128, 256).  splits >= 1; K/64 blocks are divided evenly (4-block aligned for fp4).
-DGPP_API int dgpp_gemm_tc(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
-                          const void* w_scale, float alpha, void* out, void* out32, const void* resid, int ldc,
-                          int T, int N, int K, int splits, void* ws, void* counters, cudaStream_t st) {
+static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
+                        const void* w_scale, float alpha, void* out, void* out32, const void* resid, int ldc,
+                        int T, int N, int K, int splits, void* ws, void* counters, void* comm_push, cudaStream_t st) {
   DGPP_REQUIRE(T >= 1 && N >= 1, "gemm_tc: empty problem");
   DGPP_REQUIRE(K % 64 == 0, "gemm_tc: K %d must be a multiple of 64", K);
   if (wmode == 1 || wmode == 3) DGPP_REQUIRE(K % 256 == 0, "gemm_tc: fp4 weights need K %% 256 == 0 (K=%d)", K);
   if (wmode == 2) DGPP_REQUIRE(K % 128 == 0, "gemm_tc: fp8 block weights need K %% 128 == 0 (K=%d)", K);
   DGPP_REQUIRE(splits >= 1, "gemm_tc: splits must be >= 1");
   DGPP_REQUIRE(splits == 1 || (ws && counters), "gemm_tc: split-K needs workspace and counters");
-  DGPP_REQUIRE(out || out32, "gemm_tc: no output");
+  DGPP_REQUIRE(out || out32 || comm_push, "gemm_tc: no output");
   GemmParams p;
+  p.push = 0;
+  p.tiles_per_rank = 1;
+  if (comm_push) {
+    const DgppComm* c = static_cast<const DgppComm*>(comm_push);
+    DGPP_REQUIRE(splits == 1, "gemm_tc push: split-K is not combined with the reduce-scatter push");
+    DGPP_REQUIRE(N % 128 == 0, "gemm_tc push: N %d must be a multiple of 128", N);
+    DGPP_REQUIRE(dgpp_ceil_div(T, bn) <= kCommMaxCtas, "gemm_tc push: %d rows in tiles of %d exceed %d token tiles", T, bn, kCommMaxCtas);
+    DGPP_REQUIRE(static_cast<size_t>(T) * N * 2 <= c->st.slot_bytes, "gemm_tc push: %d x %d exceeds the slot", T, N);
+    p.push = 1;
+    p.comm = c->st;
+    p.tiles_per_rank = dgpp_ceil_div(dgpp_ceil_div(T, bn), c->st.world);
+  }
   p.alpha = alpha;
   p.out = static_cast<bf16*>(out);
   p.out32 = static_cast<float*>(out32);
@@ -437,4 +473,18 @@ DGPP_API int dgpp_gemm_tc(int wmode, int a_f16, int bn, const void* x, int64_t x
 #undef DGPP_GEMM_BN
   dgpp_set_error("gemm_tc: unsupported bn %d / wmode %d", bn, wmode);
   return -1;
+}
+
+DGPP_API int dgpp_gemm_tc(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
+                          const void* w_scale, float alpha, void* out, void* out32, const void* resid, int ldc,
+                          int T, int N, int K, int splits, void* ws, void* counters, cudaStream_t st) {
+  return gemm_tc_impl(wmode, a_f16, bn, x, x_stride, w, w_scale, alpha, out, out32, resid, ldc, T, N, K, splits, ws,
+                      counters, nullptr, st);
+}
+
+// Same GEMM with the reduce-scatter push epilogue (see GemmParams::push); pair with dgpp_comm_rs_ag(comm, x, T, N, bn).
+DGPP_API int dgpp_gemm_tc_push(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
+                               const void* w_scale, float alpha, int T, int N, int K, void* comm_push, cudaStream_t st) {
+  return gemm_tc_impl(wmode, a_f16, bn, x, x_stride, w, w_scale, alpha, nullptr, nullptr, nullptr, N, T, N, K, 1, nullptr,
+                      nullptr, comm_push, st);
 }

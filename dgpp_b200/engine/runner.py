@@ -160,16 +160,28 @@ class DenseRunner:
                               rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm,
                               eps=c.eps)
             self.attention(qkv, cache, row_req, positions, rows, splits, attn, L)
-            self.linear(attn, L.o, delta, fp4)
-            if lora is not None:
-                lora.apply(li, "o", attn, delta, self.lora_scratch)
-            if self.reducer is not None:
-                self.reducer.all_reduce(delta)
-            ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
+            # tensor parallel at prefill sizes: GEMM epilogue -> reduce-scatter push, fold at the owner + all-gather
+            rs = (self.fuse_ar and lora is None and not fp4 and rows > 64 and
+                  getattr(self.reducer, "can_rs", lambda *a: False)(rows, c.hidden, ops.pick_bn(rows)))
+            if rs:
+                # (x already holds the residual stream: the input norm above folded the previous block's output in)
+                self.reducer.rs_ag(x, ops.gemm_tc_push(attn, L.o, self.reducer.comm))
+                ops.rmsnorm(x, L.post_norm, c.eps, out=xn)
+            else:
+                self.linear(attn, L.o, delta, fp4)
+                if lora is not None:
+                    lora.apply(li, "o", attn, delta, self.lora_scratch)
+                if self.reducer is not None:
+                    self.reducer.all_reduce(delta)
+                ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
             self.linear(xn, L.gate_up, gu, fp4)
             if lora is not None:
                 lora.apply(li, "gate_up", xn, gu, self.lora_scratch)
             ops.swiglu(gu, out=act)
+            if rs:
+                self.reducer.rs_ag(x, ops.gemm_tc_push(act, L.down, self.reducer.comm))
+                have_delta = False                     # the block's output is already in the residual stream
+                continue
             self.linear(act, L.down, delta, fp4)
             if lora is not None:
                 lora.apply(li, "down", act, delta, self.lora_scratch)

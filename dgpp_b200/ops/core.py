@@ -154,6 +154,19 @@ def gemm_tc(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
     return out if out is not None else out32
 
 
+def gemm_tc_push(x: torch.Tensor, w: QuantLinear, push_comm, bn: Optional[int] = None) -> int:
+    """The same linear with the reduce-scatter epilogue: every finished bf16 tile is stored into the symmetric
+    region of the rank that owns the tile's tokens (native peer communicator `push_comm`).  Returns the token tile
+    size, which the matching ``PeerReducer.rs_ag`` call needs."""
+    _chk(x, torch.bfloat16, "x")
+    rows, k = x.shape
+    assert k == w.k and w.fmt in _FMT_GEMM
+    bn = bn or pick_bn(rows)
+    call("dgpp_gemm_tc_push", _FMT_GEMM[w.fmt], 0, bn, ptr(x), x.stride(0), ptr(w.payload), ptr(w.scale), float(w.alpha),
+         rows, w.n, k, push_comm, stream_ptr())
+    return bn
+
+
 class QuantAct:
     """Activations quantised to R residual NVFP4 terms: x ~= g[t] * sum_r dequant(term r).
     Rows of `q` are ordered [token tile][term][token in tile] (the B operand of one MMA is a token tile with its

@@ -18,6 +18,7 @@ _lib.declare("dgpp_comm_connect", [P, P])
 _lib.declare("dgpp_comm_destroy", [P])
 _lib.declare("dgpp_comm_all_reduce", [P, P, P, L, I, P])
 _lib.declare("dgpp_comm_pick_merge", [P, P, P, I, P])
+_lib.declare("dgpp_comm_rs_ag", [P, P, I, I, I, P])
 
 
 class PeerReducer:
@@ -61,6 +62,16 @@ class PeerReducer:
         ctas = self.ctas if n <= 64 * 8192 else 64
         call("dgpp_comm_all_reduce", self.comm, ptr(t), ptr(resid), n, ctas, stream_ptr())
         return t
+
+    def rs_ag(self, x: torch.Tensor, tile_rows: int) -> torch.Tensor:
+        """Second half of the fused GEMM -> reduce-scatter -> all-gather: x [T, H] += the sum over ranks of the
+        partial tiles that ``ops.gemm_tc_push`` delivered (fixed-order fold at the owner, then broadcast)."""
+        assert x.is_contiguous() and x.dtype == torch.bfloat16
+        call("dgpp_comm_rs_ag", self.comm, ptr(x), x.shape[0], x.shape[1], tile_rows, stream_ptr())
+        return x
+
+    def can_rs(self, rows: int, hidden: int, tile_rows: int) -> bool:
+        return (rows * hidden <= self.max_values and hidden % 128 == 0 and (rows + tile_rows - 1) // tile_rows <= 64)
 
     def merge_picks(self, ids: torch.Tensor, vals: torch.Tensor) -> None:
         call("dgpp_comm_pick_merge", self.comm, ptr(ids), ptr(vals), ids.numel(), stream_ptr())
