@@ -82,6 +82,6 @@ def test_closed_runtime_calls_are_not_named():
 def test_no_cluster_multicast_loads():
     hits = []
     for path in _sources():
-        if ".multicast::cluster" in open(path).read():
+        if (".multi" + "cast::" + "cluster") in open(path).read():
             hits.append(os.path.basename(path))
     assert not hits, hits
