@@ -120,7 +120,7 @@ def bind_adapter(tensors: Dict[str, torch.Tensor], cfg: DenseConfig, rank: int, 
     """Slice unsharded adapter tensors for one tensor-parallel rank, mirroring the model's own slicing and padding."""
     W, r, d = tp_size, tp_rank, cfg.head_dim
     hq_l, hkv_l, ffn_l = cfg.q_heads // W, max(cfg.kv_heads // W, 1), cfg.ffn // W
-    ffn_pad = (-ffn_l) % 256 if (W > 1 and cfg.weight_fmt == "nvfp4") else 0
+    ffn_pad = (-ffn_l) % 256 if (W > 1 and cfg.weight_fmt in ("nvfp4", "mxfp4")) else 0
     q_pad = (padded_q_heads(cfg, W) - hq_l) * d
     nq_l, nkv_l, I_l = hq_l * d + q_pad, hkv_l * d, ffn_l + ffn_pad
     up = lambda t: t.to(BF).contiguous().to(device)

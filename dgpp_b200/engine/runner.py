@@ -28,7 +28,25 @@ class DenseRunner:
         self.m, self.kv, self.max_rows, self.reducer = model, kv, max_rows, reducer
         # decode rows (<= 64) run the linears on the block-scaled FP4 tensor-core path with the activations
         # expanded into `act_terms` residual NVFP4 terms; attention reads the FP8 cache through tcgen05
-        self.decode_fp4 = decode_fp4 and model.cfg.weight_fmt == "nvfp4"
+        self.decode_fp4 = decode_fp4 and model.cfg.weight_fmt in ("nvfp4", "mxfp4")
+        # MXFP4 checkpoints: the decode path sees the same bytes through exact block-scaled views (e2m1 codes shared,
+        # e8m0 scales re-expressed as e4m3 per 16 + tensor scale); a layer that cannot be re-expressed keeps the
+        # whole model on the converter GEMM
+        self.layers_fp4 = model.layers
+        if self.decode_fp4 and model.cfg.weight_fmt == "mxfp4":
+            import dataclasses
+            from ..quant.formats import mxfp4_as_nvfp4
+            views = []
+            for L in model.layers:
+                conv = {nm: mxfp4_as_nvfp4(getattr(L, nm)) for nm in ("qkv", "o", "gate_up", "down")}
+                if any(v is None for v in conv.values()):
+                    views = None
+                    break
+                views.append(dataclasses.replace(L, **conv))
+            if views is None:
+                self.decode_fp4 = False
+            else:
+                self.layers_fp4 = views
         self.act_terms = act_terms
         self.chunk = None
         self._li = 0
@@ -147,7 +165,7 @@ class DenseRunner:
         for li, L in enumerate(m.layers):
             self._li = li
             if fp4:
-                pending = self._layer_fp4(L, kv.layers[li], x, delta, have_delta, qkv, attn, gu, positions, row_req,
+                pending = self._layer_fp4(self.layers_fp4[li], kv.layers[li], x, delta, have_delta, qkv, attn, gu, positions, row_req,
                                           rows, splits, pending_fold=pending, last=li == len(m.layers) - 1)
                 have_delta = True
                 continue

@@ -138,13 +138,14 @@ def _pad(w: QuantLinear, rows: int = 0, cols: int = 0) -> QuantLinear:
     keep a tensor-parallel shard on the GEMM's K granule contribute exact zeros."""
     if not rows and not cols:
         return w
-    assert w.fmt in ("nvfp4", "bf16", "fp32"), "padding is only needed for (and defined on) nvfp4 / unquantised shards"
+    assert w.fmt in ("nvfp4", "mxfp4", "bf16", "fp32"), "padding is defined on fp4 / unquantised shards"
     pay, sc = w.payload, w.scale
-    if w.fmt == "nvfp4":
-        sc = sc.view(w.n, w.k // 16)
+    if w.fmt in ("nvfp4", "mxfp4"):
+        grp = 16 if w.fmt == "nvfp4" else 32
+        sc = sc.view(w.n, w.k // grp)
         if cols:
             pay = torch.cat([pay, pay.new_zeros(w.n, cols // 2)], 1)
-            sc = torch.cat([sc, sc.new_zeros(w.n, cols // 16)], 1)
+            sc = torch.cat([sc, sc.new_zeros(w.n, cols // grp)], 1)
         if rows:
             pay = torch.cat([pay, pay.new_zeros(rows, pay.shape[1])])
             sc = torch.cat([sc, sc.new_zeros(rows, sc.shape[1])])
@@ -183,7 +184,7 @@ def load_dense(spec: str, device="cuda", tp_rank: int = 0, tp_size: int = 1, wei
     fmt = cfg.weight_fmt
     # the same padding DenseModel.random_init applies to tensor-parallel NVFP4 shards
     q_pad = (padded_q_heads(cfg, W) - hq_l) * d
-    ffn_pad = (-ffn_l) % 256 if (W > 1 and fmt == "nvfp4") else 0
+    ffn_pad = (-ffn_l) % 256 if (W > 1 and fmt in ("nvfp4", "mxfp4")) else 0
     layers = []
     for i in range(cfg.layers):
         p = f"model.layers.{i}."

@@ -140,7 +140,7 @@ class DenseModel:
         hq_l, hkv_l, ffn_l = cfg.q_heads // W, cfg.kv_heads // W, cfg.ffn // W
         # a rank's slice of the intermediate dimension is padded with zero channels up to the K granule of the
         # block-scaled tensor-core GEMM (256), e.g. 17408 / 8 = 2176 -> 2304
-        ffn_pad = (-ffn_l) % 256 if (W > 1 and cfg.weight_fmt == "nvfp4") else 0
+        ffn_pad = (-ffn_l) % 256 if (W > 1 and cfg.weight_fmt in ("nvfp4", "mxfp4")) else 0
         q_pad = (padded_q_heads(cfg, W) - hq_l) * d
         r = tp_rank
         adt = torch.float32 if cfg.weight_fmt == "fp32" else BF
@@ -264,7 +264,7 @@ def padded_q_heads(cfg: "DenseConfig", tp_size: int) -> int:
     attention supports; otherwise zero heads are appended (zero q rows in qkv, zero columns in o_proj: they add
     exact zeros).  40 heads / 8 ranks = 5 heads of 128 (K = 640) becomes 8 heads (K = 1024)."""
     hq, hkv = cfg.q_heads // tp_size, max(cfg.kv_heads // tp_size, 1)
-    if tp_size == 1 or cfg.weight_fmt != "nvfp4" or (hq * cfg.head_dim) % 256 == 0:
+    if tp_size == 1 or cfg.weight_fmt not in ("nvfp4", "mxfp4") or (hq * cfg.head_dim) % 256 == 0:
         return hq
     for cand in range(hq + 1, 8 * hkv + 1):
         if (cand * cfg.head_dim) % 256 == 0 and cand % hkv == 0 and cand // hkv in (1, 2, 4, 5, 8):

@@ -50,6 +50,8 @@ class MoEWeights:
     shared_gu: Optional[QuantLinear] = None
     shared_down: Optional[QuantLinear] = None
     # stacked device views for the grouped GEMM (built by `stack`)
+    shared_gu_k: Optional[QuantLinear] = None
+    shared_down_k: Optional[QuantLinear] = None
     gu_q: Optional[torch.Tensor] = None
     gu_sf: Optional[torch.Tensor] = None
     gu_alpha: Optional[torch.Tensor] = None
@@ -86,19 +88,36 @@ class MoEWeights:
             if ep_rank == 0:
                 sgu, sdn = quantize_like_random(a, fmt, std), quantize_like_random(b, fmt, std)
         w = MoEWeights(cfg, gate, bias, gu, dn, sgu, sdn, e_begin=e0, e_end=e1)
-        if fmt == "nvfp4" and torch.device(device).type == "cuda":
+        if fmt in ("nvfp4", "mxfp4") and torch.device(device).type == "cuda":
             w.stack()
         return w
 
     def stack(self) -> None:
         """Concatenate the experts' payloads / tiled scales along N: one tensor map serves every expert."""
         def cat(ws: List[QuantLinear]):
+            if ws and ws[0].fmt == "mxfp4":
+                # MXFP4 experts stream through the same grouped block-scaled GEMM: the e2m1 bytes stay as stored, the
+                # power-of-two block scales are re-expressed exactly as e4m3 per 16 + an fp32 tensor scale
+                from ..quant.formats import mxfp4_as_nvfp4
+                conv = [mxfp4_as_nvfp4(w) for w in ws]
+                if any(c is None for c in conv):
+                    return None, None, None
+                ws = conv
             q = torch.cat([w.payload for w in ws]).contiguous()
             sf = torch.cat([tile_scales(w.scale.view(w.n, w.k // 16)).reshape(-1) for w in ws]).contiguous()
             al = torch.tensor([w.alpha for w in ws], dtype=torch.float32, device=q.device)
             return q, sf, al
         self.gu_q, self.gu_sf, self.gu_alpha = cat(self.experts_gu)
         self.down_q, self.down_sf, self.down_alpha = cat(self.experts_down)
+        if self.gu_q is None or self.down_q is None:
+            self.gu_q = self.down_q = None          # a scale range too wide to re-express: the oracle path serves it
+        # kernel views of the shared expert (the stored MXFP4 tensors stay the oracle's)
+        self.shared_gu_k, self.shared_down_k = self.shared_gu, self.shared_down
+        if self.shared_gu is not None and self.shared_gu.fmt == "mxfp4":
+            from ..quant.formats import mxfp4_as_nvfp4
+            self.shared_gu_k, self.shared_down_k = mxfp4_as_nvfp4(self.shared_gu), mxfp4_as_nvfp4(self.shared_down)
+            if self.shared_gu_k is None or self.shared_down_k is None:
+                self.gu_q = self.down_q = None
 
 
 def route_reference(x: torch.Tensor, w: MoEWeights):
@@ -200,9 +219,9 @@ class MoEBlock:
                              self.group_list, group_b=True)
         sh = None
         if self.shared is not None:
-            ops.gemm_fp4(xa, w.shared_gu, out=self.sh_gu[:rows])
+            ops.gemm_fp4(xa, w.shared_gu_k, out=self.sh_gu[:rows])
             xs = ops.act_quant_nvfp4(self.sh_gu[:rows], self.terms, out=self.qa_sh, mode="swiglu", limit=c.swiglu_limit)
-            ops.gemm_fp4(xs, w.shared_down, out=self.shared[:rows])
+            ops.gemm_fp4(xs, w.shared_down_k, out=self.shared[:rows])
             sh = self.shared
         if push_comm:
             ops.moe_combine_push(self.y, sh, self.ids[:rows], self.wts[:rows], self.slot_of, push_comm, rows)

@@ -130,6 +130,35 @@ class QuantLinear:
         return self.dequant().to(torch.bfloat16)
 
 
+def mxfp4_as_nvfp4(w: "QuantLinear") -> Optional["QuantLinear"]:
+    """Re-express an MXFP4 matrix (e2m1 codes, one e8m0 power-of-two scale per 32 elements) in the NVFP4 layout
+    (same e2m1 code bytes, one e4m3 scale per 16 elements, fp32 tensor scale) WITHOUT changing any value, so that
+    the block-scaled tensor-core GEMM (and its grouped expert mode) can stream MXFP4 checkpoints as stored.
+    A power of two 2^p is an exact e4m3 value for p in [-9, 8]; the tensor scale recentres the matrix's exponent
+    range into that window (largest scale -> 2^8).  Returns None when the range of one matrix is wider than the
+    window (18 octaves), in which case the converter GEMM keeps serving it."""
+    assert w.fmt == "mxfp4"
+    e = w.scale.view(w.n, w.k // 32).to(torch.int32)
+    if bool((e == 0).any()):
+        # scale 2^-127 cannot be kept; fine when those blocks are all zero (the usual meaning), otherwise refuse
+        by_block = w.payload.view(w.n, w.k // 32, 16)
+        if bool((by_block[e == 0] != 0).any()):
+            return None
+    used = e[e > 0] if bool((e > 0).any()) else e
+    hi = int(used.max())
+    lo = int(used.min())
+    if hi - lo > 17:
+        return None
+    shift = hi - 127 - 8                      # tensor scale 2^shift, block scales 2^(e - 127 - shift) in [2^-9, 2^8]
+    p = (e - 127 - shift).clamp(min=-9)       # e == 0 blocks (2^-127, all-zero in practice) land on the smallest value
+    val = torch.exp2(p.float())
+    code = val.to(torch.float8_e4m3fn).view(torch.uint8)
+    assert torch.equal(code.view(torch.float8_e4m3fn).float(), val), "a power of two in the window is exact in e4m3"
+    scale16 = code.repeat_interleave(2, dim=1).contiguous()
+    return QuantLinear("nvfp4", w.n, w.k, w.payload, scale16.view(-1) if w.scale.dim() == 1 else scale16,
+                       float(2.0 ** shift))
+
+
 def tile_scales(sf: torch.Tensor) -> torch.Tensor:
     """[rows, K/16] e4m3 bytes -> flat bytes ordered [row_tile][stage][step][m % 32][m / 32][factor], i.e. one
     512-byte atom per (128-row tile, K=64 step) with factor i of row m at byte (m % 32) * 16 + (m / 32) * 4 + i,

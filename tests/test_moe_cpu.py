@@ -39,3 +39,19 @@ def test_moe_reference_matches_dense_formula():
     a = (torch.nn.functional.silu(h[:48]).to(torch.bfloat16).float() * h[48:]).to(torch.bfloat16).float()
     acc += (a @ w.shared_down.dequant().t()).to(torch.bfloat16).float()
     assert torch.allclose(out[t].float(), acc.to(torch.bfloat16).float(), atol=2e-2)
+
+
+def test_mxfp4_is_reexpressed_exactly_in_the_block_scaled_layout():
+    import torch
+    from dgpp_b200.quant.formats import mxfp4_as_nvfp4, quantize
+    torch.manual_seed(0)
+    w = torch.randn(64, 256) * 0.02
+    w[3] *= 300.0
+    w[7, :64] = 0.0
+    q = quantize(w, "mxfp4")
+    r = mxfp4_as_nvfp4(q)
+    assert r is not None and r.fmt == "nvfp4" and r.scale.numel() == 64 * 256 // 16
+    assert torch.equal(r.dequant(), q.dequant())
+    assert r.payload.data_ptr() == q.payload.data_ptr()
+    w[9] *= 1e9                                   # more than 18 octaves between block scales: refused, not rounded
+    assert mxfp4_as_nvfp4(quantize(w, "mxfp4")) is None

@@ -65,3 +65,28 @@ def test_moe_block_matches_reference(dev, rows, shared):
     blk.forward(x2, out)
     want2 = moe_reference(x2, w, ids=blk.ids[:rows].long(), wts=blk.wts[:rows])
     assert (out.float() - want2.float()).abs().max().item() <= 2e-2 * want2.float().abs().max().item() + 2e-3
+
+
+def test_mxfp4_experts_stream_through_the_block_scaled_grouped_gemm(dev):
+    """MXFP4 expert weights (e8m0 scale per 32) are re-expressed exactly in the block-scaled layout and run on the
+    same grouped tensor-core GEMM; the oracle decodes the stored MXFP4 tensors."""
+    from dgpp_b200.models.moe import MoEBlock, MoEConfig, MoEWeights, moe_reference
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.quant.formats import mxfp4_as_nvfp4
+
+    torch.manual_seed(5)
+    cfg = MoEConfig(hidden=1024, experts=16, top_k=4, moe_ffn=512, shared_ffn=512, routed_scaling=1.0)
+    w = MoEWeights.random_init(cfg, dev, seed=6, std=0.05, fmt="mxfp4")
+    assert w.experts_gu[0].fmt == "mxfp4" and w.gu_q is not None
+    conv = mxfp4_as_nvfp4(w.experts_down[3])
+    assert torch.equal(conv.dequant(), w.experts_down[3].dequant())          # value for value
+    assert conv.payload.data_ptr() == w.experts_down[3].payload.data_ptr()   # the code bytes are not copied
+    blk = MoEBlock(w, max_rows=16, device=dev)
+    x = torch.randn(8, cfg.hidden, device=dev).to(BF)
+    out = torch.empty(8, cfg.hidden, dtype=BF, device=dev)
+    blk.forward(x, out)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = moe_reference(x, w, ids=blk.ids[:8].long(), wts=blk.wts[:8])
+    err = (out.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * want.float().abs().max().item() + 2e-3, err
