@@ -150,17 +150,35 @@ class ReferenceEngine(rt.SchedulerEngine):
 class KernelEngine(rt.SchedulerEngine):
     """The CUDA engine behind the scheduler: chunked prefill and graph-replayed decode for arbitrary slot sets."""
 
-    def __init__(self, engine):
+    def __init__(self, engine, spec_drafts: int = 0):
+        """spec_drafts > 0: greedy speculative decoding with context-lookup drafts.  Every decode pass carries, per
+        request, its pending token plus up to `spec_drafts` proposed continuations as extra rows of the same batch;
+        the rows' own greedy picks verify the drafts (longest matching prefix + one bonus token), so the output is
+        token for token what plain greedy decoding gives.  Rejected positions are simply overwritten later: the
+        dense family has no state besides the KV cache.  (reference counterparts: src/engine/speculative.hpp
+        GreedySpeculator / judge_verify, src/engine/lookup_draft.hpp, verify rows batched into the decode pass.)"""
         super().__init__()
         self.e = engine
         self.kv = engine.kv
+        self.spec_k = max(0, int(spec_drafts))
+        self.drafts = [rt.LookupDraft(2, 4) for _ in range(engine.max_batch)] if self.spec_k else None
+        self.schedule = [rt.VerifySchedule(0, self.spec_k, min(self.spec_k, 3)) for _ in range(engine.max_batch)] \
+            if self.spec_k else None
+        self.spec_graphs = {}
+        self.spec_proposed = self.spec_accepted = 0
         self.pending = [None] * engine.max_batch
         self.filled = [0] * engine.max_batch
         b = engine.max_batch
-        self.h_tok = torch.zeros(b, dtype=torch.int32).pin_memory()
-        self.h_pos = torch.zeros(b, dtype=torch.int32).pin_memory()
-        self.h_req = torch.zeros(b, dtype=torch.int32).pin_memory()
-        self.h_out = torch.zeros(b, dtype=torch.int32).pin_memory()
+        hb = max(b, engine.runner.max_logit_rows if self.spec_k else b)
+        self.h_tok = torch.zeros(hb, dtype=torch.int32).pin_memory()
+        self.h_pos = torch.zeros(hb, dtype=torch.int32).pin_memory()
+        self.h_req = torch.zeros(hb, dtype=torch.int32).pin_memory()
+        self.h_out = torch.zeros(hb, dtype=torch.int32).pin_memory()
+        if self.spec_k:
+            dev = engine.dev
+            self.s_tok = torch.zeros(hb, dtype=torch.int32, device=dev)
+            self.s_pos = torch.zeros(hb, dtype=torch.int32, device=dev)
+            self.s_req = torch.zeros(hb, dtype=torch.int32, device=dev)
         self.by_id = {}
         self.slot_cfg = [None] * b
         self.last_logprobs = [None] * b
@@ -170,6 +188,9 @@ class KernelEngine(rt.SchedulerEngine):
 
     def max_concurrent(self):
         return self.e.max_batch
+
+    def max_tokens_per_step(self):
+        return 1 + self.spec_k
 
     def block_tokens(self):
         return self.kv.page
@@ -265,16 +286,93 @@ class KernelEngine(rt.SchedulerEngine):
         with self.timer.phase("prefill"):
             first = self.e.prefill(slot, list(tokens), start_pos=pos)
         self.filled[slot] = pos + len(tokens)
+        if self.spec_k:
+            if pos == 0:
+                self.drafts[slot].reset()
+            self.drafts[slot].append(list(tokens))
         if last:
             if self.slot_cfg[slot]:
                 tok = self._sample_rows(self.e.runner.logits[:1], [slot])[0]
             else:
                 tok = int(first.item())
             self.pending[slot] = tok
+            if self.spec_k:
+                self.drafts[slot].push(tok)
             return tok
         return -1
 
+    def _spec_graph(self, rows: int):
+        """One captured forward per row count (rows = requests + draft rows of this pass)."""
+        g = self.spec_graphs.get(rows)
+        if g is None:
+            from .graph import NativeGraph
+            r = self.e.runner
+            body = lambda: r.forward(rows, self.s_tok[:rows], self.s_pos[:rows], self.s_req[:rows], decode=True)
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                body()                                   # warm up outside capture
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = NativeGraph(body, pdl=self.e.decode_pdl)
+            self.spec_graphs[rows] = g
+        return g
+
+    def _step_spec(self, slots):
+        """Decode pass with draft rows: returns, per slot, the verified tokens (1 .. 1 + drafts)."""
+        e, r = self.e, self.e.runner
+        cap = min(r.max_logit_rows, r.fp4_rows if r.decode_fp4 else r.max_rows)
+        plan, rows = [], 0
+        for i, s in enumerate(slots):
+            room = cap - rows - (len(slots) - i)             # every later slot still needs its own row
+            k = min(self.schedule[s].draft_len(), self.spec_k, max(room, 0),
+                    e.max_seq_len - self.filled[s] - 1, len(self.kv.req_blocks[s]) * self.kv.page - self.filled[s] - 1)
+            d = self.drafts[s].propose(k) if k > 0 and not self.slot_cfg[s] else []
+            toks = [self.pending[s]] + list(d)
+            for j, t in enumerate(toks):
+                self.h_tok[rows + j] = t
+                self.h_pos[rows + j] = self.filled[s] + j
+                self.h_req[rows + j] = s
+            plan.append((s, rows, d))
+            rows += len(toks)
+        self.s_tok[:rows].copy_(self.h_tok[:rows], non_blocking=True)
+        self.s_pos[:rows].copy_(self.h_pos[:rows], non_blocking=True)
+        self.s_req[:rows].copy_(self.h_req[:rows], non_blocking=True)
+        with self.timer.phase("decode"):
+            if e.use_graphs and e.dev.type == "cuda":
+                self._spec_graph(rows).replay()
+            else:
+                r.forward(rows, self.s_tok[:rows], self.s_pos[:rows], self.s_req[:rows], decode=True)
+        self.h_out[:rows].copy_(r.pick_id[:rows], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        out = []
+        for s, row0, d in plan:
+            if self.slot_cfg[s]:
+                tok = self._sample_rows(r.logits[row0:row0 + 1], [s])[0]
+                acc = [tok]
+            else:
+                acc = []
+                for j in range(len(d) + 1):
+                    t = int(self.h_out[row0 + j])
+                    acc.append(t)
+                    if j == len(d) or d[j] != t:
+                        break
+                self.spec_proposed += len(d)
+                self.spec_accepted += len(acc) - 1
+                if d:
+                    self.schedule[s].observe(len(d), len(acc) - 1)
+            # the pending token and the accepted drafts now have KV; the last pick is the new pending token.  The
+            # drafter's history always ends with the pending token (what follows it is what a draft predicts).
+            for t in acc:
+                self.drafts[s].push(t)
+            self.filled[s] += len(acc)
+            self.pending[s] = acc[-1]
+            out.append(acc)
+        return out
+
     def step_batch(self, slots):
+        if self.spec_k:
+            return self._step_spec(list(slots))
         b = len(slots)
         e = self.e
         for i, s in enumerate(slots):

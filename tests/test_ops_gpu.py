@@ -171,11 +171,12 @@ def test_rope_kv_and_decode_attention(dev, fp8, hq, hkv, d):
         assert (out.float() - want).abs().mean().item() < 5e-3
 
 
-def test_tiny_model_engine_matches_reference(dev):
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_tiny_model_engine_matches_reference(dev, fmt):
     from dgpp_b200.engine.llm_engine import LLMEngine
     from dgpp_b200.models.dense import DenseConfig, DenseModel
 
-    cfg = DenseConfig.tiny()
+    cfg = DenseConfig.tiny(weight_fmt=fmt)
     model = DenseModel.random_init(cfg, device=dev, seed=0, std=0.05)
     eng = LLMEngine(model, max_batch=2, max_seq_len=256, prefill_chunk=64)
     g = torch.Generator().manual_seed(5)
@@ -275,3 +276,40 @@ def test_windowed_sink_model_engine_matches_reference(dev, sinks):
     l1, _ = model.forward_reference(torch.tensor(prompts[0], device=dev))
     l2, _ = model2.forward_reference(torch.tensor(prompts[0], device=dev))
     assert (l1[-1] - l2[-1]).abs().max() > 1e-3
+
+
+def test_speculative_lookup_decode_equals_plain_greedy(dev):
+    """Greedy speculative decoding (context-lookup drafts verified as extra rows of the decode pass) emits exactly
+    the tokens of plain greedy decoding, and on a repetitive prompt most drafts are accepted."""
+    from dgpp_b200.engine.adapters import KernelEngine
+    from dgpp_b200.engine.llm_engine import LLMEngine
+    from dgpp_b200.models.dense import DenseConfig, DenseModel
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.runtime import rt
+
+    cfg = DenseConfig.tiny(hidden=512, q_heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2048, layers=2)
+    model = DenseModel.random_init(cfg, device=dev, seed=0, std=0.05)
+    g = torch.Generator().manual_seed(11)
+    motif = torch.randint(0, cfg.vocab, (12,), generator=g).tolist()
+    prompts = {"rep": motif * 8, "rnd": torch.randint(0, cfg.vocab, (70,), generator=g).tolist()}
+
+    def run(spec):
+        eng = KernelEngine(LLMEngine(model, max_batch=4, max_seq_len=512, prefill_chunk=64), spec_drafts=spec)
+        s = rt.Scheduler(eng, rt.SchedulerConfig())
+        for rid, p in prompts.items():
+            s.submit(rid, p, 40)
+        s.run(100000)
+        out = {}
+        for kind, rid, a, b in s.events():
+            if kind == "token":
+                out.setdefault(rid, []).append(a)
+        ops.check_status()
+        return out, s.meters(), eng
+
+    plain, m0, _ = run(0)
+    spec, m1, eng = run(3)
+    assert spec == plain and all(len(v) == 40 for v in spec.values())
+    assert eng.spec_proposed > 0
+    # fewer decode passes than tokens when drafts land (a random-init model repeats itself often enough after a
+    # repetitive prompt; the equality above is the contract, this only checks that the path is live)
+    assert m1["decode_passes"] <= m0["decode_passes"]
