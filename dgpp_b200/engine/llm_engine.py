@@ -124,12 +124,24 @@ class LLMEngine:
         self.runner.lora = adapter
         self.graphs.clear()
 
-    def launches_per_step(self) -> int:
-        """Kernel launches of this package inside one decode step (for reporting)."""
+    def launches_per_step(self, b: Optional[int] = None) -> int:
+        """Kernel launches of this package inside one decode step: the kernel-node count of the captured graph of
+        batch width `b` (any captured width when b is None); without a captured graph, the launch sequence counted
+        from the runner's layer walk."""
+        if self.graphs:
+            g = self.graphs.get(b) if b is not None else None
+            g = g or next(iter(self.graphs.values()))
+            return int(g.kernel_nodes)
         c = self.model.cfg
-        per_layer = 8 + (1 if self.runner.decode_splits > 1 else 0)
-        if self.runner.reducer is not None:
-            per_layer += 2 * self.runner.reducer.launches_per_all_reduce
+        r = self.runner
+        if r.decode_fp4:
+            per_layer = 10 + (1 if r.decode_splits > 1 else 0)          # 4 quantisers, 4 GEMMs, rope / append, attention
+            if r.reducer is not None and not r.fuse_ar:
+                per_layer += 2 * r.reducer.launches_per_all_reduce
+        else:
+            per_layer = 9 + (1 if r.decode_splits > 1 else 0)
+            if r.reducer is not None:
+                per_layer += 2 * r.reducer.launches_per_all_reduce
         return 1 + c.layers * per_layer + 4
 
     @torch.no_grad()

@@ -81,6 +81,7 @@ class Server:
         self.default_max_tokens = default_max_tokens
         self.tool_format = tool_format or rt.ToolFormat.JsonTags
         self.constrain_tools = constrain_tools
+        self.throughput_log_s = 10.0
         self.sched = rt.Scheduler(engine, sched_config or rt.SchedulerConfig())
         self.http = rt.HttpServer(host, port)
         self.live: Dict[str, _Live] = {}
@@ -109,8 +110,26 @@ class Server:
         return self.http.port()
 
     # ------------------------------------------------------------------ loop
+    def _throughput_line(self, now: float) -> None:
+        """One log line per interval while there was traffic: requests, prompt / completion tokens per second,
+        live and queued requests, prefix-hit tokens (the 10 s throughput log of the serving process)."""
+        c = self.metrics.c
+        dt = now - self._tp_t
+        dp, dc, dr = (c["prompt_tokens_total"] - self._tp_last[0], c["completion_tokens_total"] - self._tp_last[1],
+                      c["requests_total"] - self._tp_last[2])
+        if dp or dc or dr or self.live:
+            m = self.sched.meters()
+            rt.log("info", "serve", f"throughput: {dr} req, prompt {dp / dt:.1f} tok/s, completion {dc / dt:.1f} tok/s, "
+                                    f"live {len(self.live)}, queued {self.sched.queued()}, "
+                                    f"prefix hit tokens {m['prefix_hit_tokens']}")
+        self._tp_last = (c["prompt_tokens_total"], c["completion_tokens_total"], c["requests_total"])
+        self._tp_t = now
+
     def _loop(self) -> None:
+        self._tp_t, self._tp_last = time.time(), (0, 0, 0)
         while not self._stop.is_set():
+            if time.time() - self._tp_t >= self.throughput_log_s:
+                self._throughput_line(time.time())
             busy = not self.sched.idle()
             for req in self.http.poll(0 if busy else 50):
                 try:
