@@ -35,6 +35,7 @@ py::dict record_dict(const JournalRecord& r) {
   d["id"] = r.id;
   d["tokens"] = r.tokens;
   d["arg"] = r.arg;
+  d["extra"] = r.extra;
   d["digest"] = r.digest;
   d["line"] = r.to_line();
   return d;
@@ -58,10 +59,17 @@ void bind_ctl(py::module_& m) {
 
   py::class_<Journal>(m, "Journal")
       .def(py::init<>())
-      .def("append", [](Journal& j, const std::string& op, const std::string& id, const std::vector<int32_t>& tokens, int64_t arg) {
-        return record_dict(j.append(op, id, tokens, arg));
-      }, py::arg("op"), py::arg("id") = "", py::arg("tokens") = std::vector<int32_t>(), py::arg("arg") = 0)
-      .def("replay_line", [](Journal& j, const std::string& line) { j.replay(JournalRecord::from_line(line)); })
+      .def("append", [](Journal& j, const std::string& op, const std::string& id, const std::vector<int32_t>& tokens, int64_t arg,
+                        const std::string& extra) {
+        return record_dict(j.append(op, id, tokens, arg, extra));
+      }, py::arg("op"), py::arg("id") = "", py::arg("tokens") = std::vector<int32_t>(), py::arg("arg") = 0,
+         py::arg("extra") = "")
+      // replays one wire line (order and digest are checked) and returns the record
+      .def("replay_line", [](Journal& j, const std::string& line) {
+        const JournalRecord r = JournalRecord::from_line(line);
+        j.replay(r);
+        return record_dict(r);
+      })
       .def("since", [](const Journal& j, uint64_t seq) {
         std::vector<std::string> out;
         for (const auto& r : j.since(seq)) out.push_back(r.to_line());

@@ -81,7 +81,8 @@ struct JournalRecord {
   std::string op;        // "submit" | "cancel" | "tick"
   std::string id;
   std::vector<int32_t> tokens;   // submit: prompt ids
-  int64_t arg = 0;               // submit: max_tokens; tick: scheduler op digest after the tick (low 63 bits)
+  int64_t arg = 0;               // submit: max_tokens; tick: the leader's scheduler op digest before the tick (low 63 bits)
+  std::string extra;             // submit: the remaining request fields as JSON text (part of the digest)
   uint64_t digest = 0;           // running digest after this record
 
   // One line of newline-delimited JSON (the wire and file format); digests travel as decimal strings because
@@ -95,6 +96,7 @@ struct JournalRecord {
     for (int32_t v : tokens) t.push(static_cast<int64_t>(v));
     o.set("tokens", std::move(t));
     o.set("arg", arg);
+    if (!extra.empty()) o.set("extra", extra);
     o.set("digest", std::to_string(digest));
     return o.dump();
   }
@@ -107,6 +109,7 @@ struct JournalRecord {
     if (const json::Value* t = o.find("tokens"))
       for (const auto& v : t->items()) r.tokens.push_back(static_cast<int32_t>(v.as_int()));
     r.arg = o.get_int("arg");
+    r.extra = o.get_string("extra");
     r.digest = std::stoull(o.at("digest").as_string());
     return r;
   }
@@ -115,10 +118,11 @@ struct JournalRecord {
 class Journal {
  public:
   // Leader side.
-  const JournalRecord& append(const std::string& op, const std::string& id, const std::vector<int32_t>& tokens, int64_t arg) {
+  const JournalRecord& append(const std::string& op, const std::string& id, const std::vector<int32_t>& tokens, int64_t arg,
+                              const std::string& extra = std::string()) {
     JournalRecord r;
     r.seq = next_seq_++;
-    r.op = op; r.id = id; r.tokens = tokens; r.arg = arg;
+    r.op = op; r.id = id; r.tokens = tokens; r.arg = arg; r.extra = extra;
     r.digest = digest_ = fold(digest_, r);
     log_.push_back(r);
     if (log_.size() > keep_) log_.pop_front();
@@ -159,6 +163,7 @@ class Journal {
     h = mix(h, "\0", 1);
     h = mix(h, r.tokens.data(), r.tokens.size() * 4);
     h = mix(h, &r.arg, 8);
+    h = mix(h, r.extra.data(), r.extra.size());
     return h;
   }
   std::deque<JournalRecord> log_;

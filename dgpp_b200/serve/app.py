@@ -73,7 +73,8 @@ class Metrics:
 class Server:
     def __init__(self, engine, tokenizer, template_src: str = DEFAULT_TEMPLATE, model_name: str = "dgpp-b200",
                  host: str = "127.0.0.1", port: int = 0, eos_ids: Optional[List[int]] = None,
-                 default_max_tokens: int = 256, sched_config=None, tool_format=None, constrain_tools: bool = False):
+                 default_max_tokens: int = 256, sched_config=None, tool_format=None, constrain_tools: bool = False,
+                 world_leader=None):
         self.engine, self.tok = engine, tokenizer
         self.template = rt.ChatTemplate(template_src)
         self.model_name = model_name
@@ -82,6 +83,8 @@ class Server:
         self.tool_format = tool_format or rt.ToolFormat.JsonTags
         self.constrain_tools = constrain_tools
         self.throughput_log_s = 10.0
+        # multi-rank serving: every scheduler input goes through the journal to the follower ranks first
+        self.world = world_leader
         self.sched = rt.Scheduler(engine, sched_config or rt.SchedulerConfig())
         self.http = rt.HttpServer(host, port)
         self.live: Dict[str, _Live] = {}
@@ -105,6 +108,8 @@ class Server:
         if self._thread:
             self._thread.join(timeout=30)
         self.http.stop()
+        if self.world is not None:
+            self.world.shutdown()
 
     def port(self) -> int:
         return self.http.port()
@@ -144,10 +149,16 @@ class Server:
             for conn in self.http.poll_disconnects():
                 for lv in list(self.live.values()):
                     if lv.conn == conn:
-                        self.sched.cancel(lv.rid)
+                        if self.world is not None:
+                            self.world.cancel(self.sched, lv.rid)
+                        else:
+                            self.sched.cancel(lv.rid)
             if not self.sched.idle():
                 try:
-                    self.sched.tick()
+                    if self.world is not None:
+                        self.world.tick(self.sched)
+                    else:
+                        self.sched.tick()
                 except Exception as e:
                     self._fail_engine(str(e))
                     return
@@ -245,8 +256,12 @@ class Server:
                                    rt.StopScanner(list(r["stop"])), t_submit=time.time())
             if chat and r["tools_json"] not in ("null", "[]") and json.loads(r["tool_choice_json"]) != "none":
                 self.live[rid].tool_parser = rt.ToolParser(self.tool_format, f"call_{uuid.uuid4().hex[:12]}_")
-            self.sched.submit(rid, ids, max_tokens, eos_ids=[] if r["ignore_eos"] else self.eos_ids,
-                              ignore_eos=r["ignore_eos"], prefix_cache=r["prefix_cache"], cache_key=r["prompt_cache_key"])
+            kw = dict(eos_ids=[] if r["ignore_eos"] else self.eos_ids, ignore_eos=r["ignore_eos"],
+                      prefix_cache=r["prefix_cache"], cache_key=r["prompt_cache_key"])
+            if self.world is not None:
+                self.world.submit(self.sched, rid, ids, max_tokens, **kw)
+            else:
+                self.sched.submit(rid, ids, max_tokens, **kw)
 
     def _tool_constraint(self, r: dict):
         """(required, only-this-function) when the request's tool calls are decoded under the tool grammar, else None.
@@ -324,7 +339,10 @@ class Server:
                 self._emit(lv, g, piece)
                 if lv.scanner.stopped():
                     lv.finish = "stop"
-                    self.sched.cancel(rid)
+                    if self.world is not None:
+                        self.world.cancel(self.sched, rid)
+                    else:
+                        self.sched.cancel(rid)
             elif kind.startswith("retire"):
                 why = kind.split(":", 1)[1]
                 if not lv.finish:
