@@ -73,8 +73,48 @@ class WorldLeader:
         self.followers = []
 
 
+class RankMetrics:
+    """Per-rank Prometheus listener of a follower (`dgpp_rank_*` families): the leader's HTTP endpoint only knows
+    rank 0, so every other rank answers GET /metrics/prometheus (and /health) on its own port.
+    (reference counterpart: src/serve/rank_metrics.cpp.)"""
+
+    def __init__(self, rank: int, port: int = 0, host: str = "127.0.0.1"):
+        import threading
+        self.rank = rank
+        self.c = {"journal_records_total": 0, "ticks_total": 0, "tokens_total": 0, "submits_total": 0,
+                  "cancels_total": 0}
+        self.http = rt.HttpServer(host, port)
+        self.http.start()
+        self.port = self.http.port()
+        self._stop = threading.Event()
+        self._t = threading.Thread(target=self._loop, daemon=True)
+        self._t.start()
+
+    def text(self) -> str:
+        lines = [f'dgpp_rank_up{{rank="{self.rank}"}} 1']
+        for k, v in self.c.items():
+            lines.append(f"# TYPE dgpp_rank_{k} counter")
+            lines.append(f'dgpp_rank_{k}{{rank="{self.rank}"}} {v}')
+        return "\n".join(lines) + "\n"
+
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            for req in self.http.poll(50):
+                if req["method"] == "GET" and req["path"] in ("/metrics", "/metrics/prometheus"):
+                    self.http.respond(req["conn"], 200, "text/plain; version=0.0.4", self.text().encode())
+                elif req["method"] == "GET" and req["path"] == "/health":
+                    self.http.respond(req["conn"], 200, "application/json", b'{"status":"ok"}')
+                else:
+                    self.http.respond(req["conn"], 404, "application/json", b'{"error":"not found"}')
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._t.join(5)
+        self.http.stop()
+
+
 def run_follower(engine, host: str, port: int, sched_config=None, config_digest: int = 0, on_events=None,
-                 idle_timeout_ms: int = 1000, max_idle_s: float = 0.0) -> int:
+                 idle_timeout_ms: int = 1000, max_idle_s: float = 0.0, metrics: Optional[RankMetrics] = None) -> int:
     """Replay the leader's journal into a local scheduler + engine until a `shutdown` record (returns 0) or until
     the leader goes away (returns 3).  A digest mismatch raises.  `on_events(list)` receives the scheduler's events
     after every tick (followers normally drop them: rank 0 answers the clients)."""
@@ -103,6 +143,10 @@ def run_follower(engine, host: str, port: int, sched_config=None, config_digest:
         idle = 0.0
         rec = journal.replay_line(frame.decode())       # order + running digest are checked here
         op = rec["op"]
+        if metrics is not None:
+            metrics.c["journal_records_total"] += 1
+            if op in ("submit", "cancel", "tick"):
+                metrics.c[op + "s_total"] += 1
         if op == "submit":
             kw = json.loads(rec["extra"]) if rec["extra"] else {}
             sched.submit(rec["id"], list(rec["tokens"]), rec["arg"], **kw)
@@ -115,6 +159,8 @@ def run_follower(engine, host: str, port: int, sched_config=None, config_digest:
                                    f"record {rec['seq']}: this rank has diverged")
             sched.tick()
             ev = sched.events()
+            if metrics is not None:
+                metrics.c["tokens_total"] += sum(1 for e in ev if e[0] == "token")
             if on_events is not None:
                 on_events(ev)
         elif op == "shutdown":

@@ -118,3 +118,27 @@ def test_follower_ends_when_the_leader_vanishes():
         s.close()                        # no shutdown record: the connection just goes away
     t.join(10)
     assert out["rc"] == 3
+
+
+def test_follower_rank_metrics_listener():
+    from dgpp_b200.serve.world import RankMetrics
+    leader = WorldLeader(world=2)
+    m = RankMetrics(rank=1)
+    out = {}
+    t = threading.Thread(target=lambda: out.setdefault("rc", run_follower(_engine(), "127.0.0.1", leader.port, metrics=m)))
+    t.start()
+    leader.wait_for_followers()
+    sched = rt.Scheduler(_engine(), rt.SchedulerConfig())
+    leader.submit(sched, "r", [1, 2, 3, 4], 5)
+    while not sched.idle():
+        leader.tick(sched)
+    leader.shutdown()
+    t.join(10)
+    c = http.client.HTTPConnection("127.0.0.1", m.port, timeout=10)
+    c.request("GET", "/metrics/prometheus")
+    text = c.getresponse().read().decode()
+    c.close()
+    m.stop()
+    assert out["rc"] == 0
+    assert 'dgpp_rank_up{rank="1"} 1' in text and 'dgpp_rank_tokens_total{rank="1"} 5' in text
+    assert 'dgpp_rank_submits_total{rank="1"} 1' in text
