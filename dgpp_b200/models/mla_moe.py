@@ -1,0 +1,268 @@
+"""MLA + MoE decoder family (DeepSeek-V3 / GLM-DSA style): multi-head latent attention with a low-rank query path,
+optional lightning-indexer sparse attention, dense or mixture-of-experts FFN.
+
+Per layer (token x, RMSNorm pre-norms, residual stream in bf16):
+    c_q   = norm(W_qa x)                      [q_lora]
+    q     = W_qb c_q                          [heads, nope + rope]      (rope part rotated)
+    c_kv  = norm((W_kva x)[:dc]),  k_r = rope((W_kva x)[dc:])            cache row = [c_kv | k_r]  (dc + dr per token)
+    k_h   = [W_uk_h c_kv | k_r],  v_h = W_uv_h c_kv                      (never materialised by the kernel path)
+    a_h   = softmax(q_h . k_h / sqrt(nope + rope)) v_h ;  out = W_o [a_1 .. a_H]
+The kernel path runs the ABSORBED form: q_abs_h = W_uk_h^T q_nope_h (so the score is q_abs . c + q_r . k_r against the
+shared cache row) and a_h = W_uv_h (sum_t p_t c_t); the oracle below runs the plain form, so agreement checks the
+absorption as well as the kernels.  With the sparse index, every query row keeps the top-k cached positions by
+sum_i w_i relu(q_idx_i . k_idx_t) (k_idx cached per token) and attends only to them.
+(reference counterparts: src/models/glm_dsa/model.cpp, src/models/dsa_layer.cu, dsa_reference.cpp, the MoE layers of
+ src/models/glm/moe_layer.cpp; kernels src/kernels/dsa.cu.)
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..ops import core as ops
+from ..ops import reference as ref
+from ..quant.formats import QuantLinear, quantize
+from .moe import MoEBlock, MoEConfig, MoEWeights, moe_reference
+
+BF = torch.bfloat16
+
+
+@dataclass
+class MlaMoeConfig:
+    layers: int = 4
+    hidden: int = 1024
+    heads: int = 8
+    q_lora: int = 256
+    kv_lora: int = 128           # dc
+    nope: int = 64
+    rope: int = 32               # dr
+    v_dim: int = 64
+    ffn: int = 2048              # dense layers
+    dense_layers: int = 1        # the first layers use a dense FFN, the rest the MoE
+    vocab: int = 4096
+    eps: float = 1e-6
+    rope_theta: float = 1e4
+    page: int = 64
+    moe: Optional[MoEConfig] = None
+    # sparse index (0 heads = dense attention everywhere)
+    index_heads: int = 0
+    index_dim: int = 64
+    index_topk: int = 64
+
+
+@dataclass
+class MlaLayer:
+    in_norm: torch.Tensor
+    post_norm: torch.Tensor
+    q_a: QuantLinear             # [q_lora, H]
+    q_a_norm: torch.Tensor
+    q_b: QuantLinear             # [heads * (nope + rope), q_lora]
+    kv_a: QuantLinear            # [dc + dr, H]
+    kv_a_norm: torch.Tensor
+    w_uk: torch.Tensor           # [heads, nope, dc] bf16
+    w_uv: torch.Tensor           # [heads, v, dc] bf16
+    o: QuantLinear               # [H, heads * v]
+    gate_up: Optional[QuantLinear] = None
+    down: Optional[QuantLinear] = None
+    moe: Optional[MoEWeights] = None
+    idx_q: Optional[QuantLinear] = None   # [hi * di, H]
+    idx_k: Optional[QuantLinear] = None   # [di, H]
+    idx_w: Optional[QuantLinear] = None   # [hi, H]
+
+
+def _rope(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """x [..., T?, d] with leading token axis 0: rotate-half convention on the last axis.  fp32 in / out."""
+    ang = pos.float().unsqueeze(-1) * inv_freq                     # [T, d/2]
+    while ang.dim() < x.dim():
+        ang = ang.unsqueeze(1)
+    c, s = torch.cos(ang), torch.sin(ang)
+    h = x.shape[-1] // 2
+    a, b = x[..., :h], x[..., h:]
+    return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+
+class MlaMoeModel:
+    def __init__(self, cfg: MlaMoeConfig, embed, layers: List[MlaLayer], final_norm, head: QuantLinear, inv_freq):
+        self.cfg, self.embed, self.layers, self.final_norm, self.head, self.inv_freq = cfg, embed, layers, final_norm, head, inv_freq
+
+    @staticmethod
+    def random_init(cfg: MlaMoeConfig, device, seed: int = 0, std: float = 0.05, fmt: str = "bf16") -> "MlaMoeModel":
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+        rnd = lambda n, k: torch.randn(n, k, device=device, dtype=torch.float32, generator=g) * std
+        lin = lambda n, k: quantize(rnd(n, k), fmt if (k % 256 == 0 or fmt == "bf16") else "bf16")
+        ones = lambda n: torch.ones(n, device=device, dtype=BF)
+        H, c = cfg.hidden, cfg
+        layers = []
+        for i in range(cfg.layers):
+            L = MlaLayer(ones(H), ones(H), lin(c.q_lora, H), ones(c.q_lora), lin(c.heads * (c.nope + c.rope), c.q_lora),
+                         lin(c.kv_lora + c.rope, H), ones(c.kv_lora),
+                         (torch.randn(c.heads, c.nope, c.kv_lora, device=device, generator=g) * std * 2).to(BF),
+                         (torch.randn(c.heads, c.v_dim, c.kv_lora, device=device, generator=g) * std * 2).to(BF),
+                         lin(H, c.heads * c.v_dim))
+            if cfg.moe is not None and i >= cfg.dense_layers:
+                L.moe = MoEWeights.random_init(cfg.moe, device, seed=seed * 1000 + i, std=std)
+            else:
+                L.gate_up, L.down = lin(2 * c.ffn, H), lin(H, c.ffn)
+            if cfg.index_heads:
+                L.idx_q = quantize(rnd(c.index_heads * c.index_dim, H) * 4, "bf16")
+                L.idx_k = quantize(rnd(c.index_dim, H) * 4, "bf16")
+                L.idx_w = quantize(rnd(c.index_heads, H), "bf16")
+            layers.append(L)
+        embed = (torch.randn(cfg.vocab, H, device=device, generator=g) * std).to(BF)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.rope, 2, device=device).float() / cfg.rope))
+        return MlaMoeModel(cfg, embed, layers, ones(H), quantize(rnd(cfg.vocab, H), "bf16"), inv)
+
+    # ------------------------------------------------------------------ oracle (plain, non-absorbed attention)
+    def forward_reference(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Logits [T, V] of one request from position 0 (PyTorch, fp32 accumulation, bf16 rounding at the points the
+        kernel path rounds: projections, cache rows, attention output, FFN output)."""
+        c = self.cfg
+        T = tokens.numel()
+        dev = self.embed.device
+        pos = torch.arange(T, device=dev)
+        x = ref.embed_gather(tokens.to(dev), self.embed)
+        delta = None
+        scale = 1.0 / math.sqrt(c.nope + c.rope)
+        for L in self.layers:
+            xn, x = ref.rmsnorm(x, L.in_norm, c.eps, delta)
+            cq = ref.rmsnorm(ref.linear(xn, L.q_a), L.q_a_norm, c.eps)[0]
+            q = ref.linear(cq, L.q_b).float().view(T, c.heads, c.nope + c.rope)
+            q_n, q_r = q[..., :c.nope], ref._r(_rope(q[..., c.nope:], pos, self.inv_freq))
+            kv = ref.linear(xn, L.kv_a)
+            ckv = ref.rmsnorm(kv[:, :c.kv_lora].contiguous(), L.kv_a_norm, c.eps)[0].float()         # bf16 values
+            k_r = ref._r(_rope(kv[:, c.kv_lora:].float(), pos, self.inv_freq))                        # [T, dr]
+            k_n = torch.einsum("hnd,td->thn", L.w_uk.float(), ckv)                                    # [T, heads, nope]
+            v = torch.einsum("hvd,td->thv", L.w_uv.float(), ckv)                                      # [T, heads, v]
+            s = (torch.einsum("qhn,khn->hqk", q_n, k_n) + torch.einsum("qhr,kr->hqk", q_r, k_r)) * scale
+            mask = pos.unsqueeze(0) > pos.unsqueeze(1)                                                # [q, k]
+            if L.idx_q is not None:
+                qi = ref.linear(xn, L.idx_q).float().view(T, c.index_heads, c.index_dim)
+                ki = ref.linear(xn, L.idx_k).float()                                                  # [T, di]
+                wi = ref.linear(xn, L.idx_w).float()                                                  # [T, hi]
+                sc = (torch.relu(torch.einsum("qhd,kd->qhk", qi, ki)) * wi.unsqueeze(-1)).sum(1)      # [q, k]
+                sc = sc.masked_fill(mask, float("-inf"))
+                keep = torch.zeros_like(mask)
+                for t in range(T):
+                    n = t + 1
+                    if n <= c.index_topk:
+                        keep[t, :n] = True
+                    else:
+                        order = torch.argsort(-sc[t, :n], stable=True)[:c.index_topk]                 # ties -> lower position
+                        keep[t, order] = True
+                mask = mask | ~keep
+            p = torch.softmax(s.masked_fill(mask.unsqueeze(0), float("-inf")), -1)
+            a = ref._r(torch.einsum("hqk,khv->qhv", p, v)).reshape(T, c.heads * c.v_dim)
+            o = ref.linear(ref.act(a), L.o)
+            xn, x = ref.rmsnorm(x, L.post_norm, c.eps, o)
+            if L.moe is not None:
+                delta = moe_reference(xn, L.moe)
+            else:
+                delta = ref.linear(ref.swiglu(ref.linear(xn, L.gate_up)), L.down)
+        xn, x = ref.rmsnorm(x, self.final_norm, c.eps, delta)
+        return ref.linear(xn, self.head, out_fp32=True)
+
+
+class MlaMoeRunner:
+    """Kernel execution: latent cache + index-key cache in pages, absorbed MLA decode kernel (dense or sparse), MoE
+    block, tensor-core linears.  Rows may be a prefill chunk of one request or one decode token per request."""
+
+    def __init__(self, model: MlaMoeModel, max_rows: int, slots: int, max_seq_len: int, device):
+        c = model.cfg
+        self.m, self.c, self.dev, self.max_rows = model, c, device, max_rows
+        self.page = c.page
+        self.max_blocks = (max_seq_len + c.page - 1) // c.page + 1
+        nblocks = slots * self.max_blocks + 1
+        self.max_ctx = self.max_blocks * c.page
+        self.latent = [torch.zeros(nblocks, c.page, c.kv_lora + c.rope, dtype=BF, device=device) for _ in model.layers]
+        self.kidx = [torch.zeros(nblocks, c.page, c.index_dim, dtype=BF, device=device) if c.index_heads else None
+                     for _ in model.layers]
+        # static block table: slot s owns blocks [1 + s * max_blocks, 1 + (s + 1) * max_blocks)
+        self.block_table = (1 + torch.arange(slots * self.max_blocks, device=device, dtype=torch.int32)
+                            ).view(slots, self.max_blocks).contiguous()
+        self.lengths = [0] * slots
+        self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
+                    if L.moe is not None and L.moe.gu_q is not None}
+        self.scale = 1.0 / math.sqrt(c.nope + c.rope)
+        self.scores = torch.empty(max_rows, self.max_ctx, dtype=torch.float32, device=device) if c.index_heads else None
+
+    def reset(self, slot: int) -> None:
+        self.lengths[slot] = 0
+
+    def _append(self, cache: torch.Tensor, rows: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor) -> None:
+        blk = self.block_table[row_req.long(), (positions // self.page).long()].long()
+        cache[blk, (positions % self.page).long()] = rows
+
+    @torch.no_grad()
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor) -> torch.Tensor:
+        m, c = self.m, self.c
+        rows = tokens.shape[0]
+        x = torch.empty(rows, c.hidden, dtype=BF, device=self.dev)
+        xn, delta = torch.empty_like(x), torch.empty_like(x)
+        ops.embed_gather(tokens, m.embed, out=x)
+        have = False
+        for i, L in enumerate(m.layers):
+            ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have else None, out=xn)
+            cq = ops.rmsnorm(ops.linear(xn, L.q_a), L.q_a_norm, c.eps)
+            q = ops.linear(cq, L.q_b).view(rows, c.heads, c.nope + c.rope)
+            kv = ops.linear(xn, L.kv_a)
+            ckv = ops.rmsnorm(kv[:, :c.kv_lora].contiguous(), L.kv_a_norm, c.eps)
+            k_r = _rope(kv[:, c.kv_lora:].float(), positions, m.inv_freq).to(BF)
+            self._append(self.latent[i], torch.cat([ckv, k_r], -1), row_req, positions)
+            # absorbed query: [heads, nope] x [heads, nope, dc] -> [heads, dc], rotated rope part appended
+            q_abs = torch.einsum("thn,hnd->thd", q[..., :c.nope].float(), L.w_uk.float())
+            q_r = _rope(q[..., c.nope:].float(), positions, m.inv_freq).to(BF).float()
+            q_full = torch.cat([q_abs, q_r], -1).to(BF).contiguous()
+            sel = None
+            if L.idx_q is not None:
+                self._append(self.kidx[i], ops.linear(xn, L.idx_k), row_req, positions)
+                qi = ops.linear(xn, L.idx_q).view(rows, c.index_heads, c.index_dim)
+                wi = ops.linear(xn, L.idx_w).float().contiguous()
+                sc = ops.dsa_index(qi, wi, self.kidx[i], self.block_table, row_req, positions, self.max_ctx,
+                                   scores=self.scores[:rows])
+                sel = ops.topk_select(sc, positions, c.index_topk)
+            lat = ops.mla_decode(q_full, self.latent[i], self.block_table, row_req, positions, self.scale, c.kv_lora,
+                                 c.rope, sel=sel, splits=4 if rows <= 16 else 1)
+            a = torch.einsum("thd,hvd->thv", lat.float(), L.w_uv.float()).to(BF).reshape(rows, c.heads * c.v_dim)
+            ops.linear(a, L.o, out=delta)
+            ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
+            have = True
+            if L.moe is not None:
+                blk = self.moe.get(i)
+                if blk is not None and rows <= blk.max_rows:
+                    blk.forward(xn, delta)
+                elif blk is not None:
+                    delta.copy_(blk.forward_gathered(xn))
+                else:
+                    delta.copy_(moe_reference(xn, L.moe))
+            else:
+                ops.linear(ops.swiglu(ops.linear(xn, L.gate_up)), L.down, out=delta)
+        ops.rmsnorm(x, m.final_norm, c.eps, delta=delta, out=xn)
+        return ops.gemm_tc(xn, m.head, out32=torch.empty(rows, c.vocab, dtype=torch.float32, device=self.dev))
+
+    @torch.no_grad()
+    def prefill(self, slot: int, tokens: List[int], chunk: int = 64) -> torch.Tensor:
+        start = self.lengths[slot]
+        assert start + len(tokens) <= self.max_ctx - self.page
+        out = None
+        for o in range(0, len(tokens), chunk):
+            part = tokens[o:o + chunk]
+            t = torch.tensor(part, dtype=torch.int32, device=self.dev)
+            pos = torch.arange(start + o, start + o + len(part), dtype=torch.int32, device=self.dev)
+            req = torch.full((len(part),), slot, dtype=torch.int32, device=self.dev)
+            out = self.forward(t, pos, req)
+        self.lengths[slot] = start + len(tokens)
+        return out
+
+    @torch.no_grad()
+    def decode(self, slots: List[int], tokens: List[int]) -> torch.Tensor:
+        t = torch.tensor(tokens, dtype=torch.int32, device=self.dev)
+        pos = torch.tensor([self.lengths[s] for s in slots], dtype=torch.int32, device=self.dev)
+        req = torch.tensor(slots, dtype=torch.int32, device=self.dev)
+        out = self.forward(t, pos, req)
+        for s in slots:
+            self.lengths[s] += 1
+        return out

@@ -1,0 +1,49 @@
+"""MLA + MoE family on the GPU: the absorbed-attention kernel path (latent cache, sparse index, MoE block) against the
+plain-attention PyTorch oracle."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda:0")
+
+
+@pytest.mark.parametrize("moe,index", [(False, False), (True, False), (False, True)])
+def test_runner_matches_plain_attention_oracle(dev, moe, index):
+    from dgpp_b200.models.mla_moe import MlaMoeConfig, MlaMoeModel, MlaMoeRunner
+    from dgpp_b200.models.moe import MoEConfig
+    from dgpp_b200.ops import core as ops
+
+    cfg = MlaMoeConfig(layers=3, hidden=1024, heads=8, q_lora=256, kv_lora=128, nope=64, rope=32, v_dim=64, ffn=2048,
+                       vocab=2048, dense_layers=1,
+                       moe=MoEConfig(hidden=1024, experts=16, top_k=4, moe_ffn=512, shared_ffn=512) if moe else None,
+                       index_heads=4 if index else 0, index_dim=64, index_topk=48)
+    m = MlaMoeModel.random_init(cfg, dev, seed=3, std=0.04)
+    r = MlaMoeRunner(m, max_rows=64, slots=2, max_seq_len=512, device=dev)
+    g = torch.Generator().manual_seed(2)
+    a = torch.randint(0, cfg.vocab, (150,), generator=g).tolist()
+    b = torch.randint(0, cfg.vocab, (37,), generator=g).tolist()
+    la = r.prefill(0, a[:140], chunk=64).clone()
+    lb = r.prefill(1, b[:30], chunk=16).clone()
+    want_a = m.forward_reference(torch.tensor(a, device=dev))
+    want_b = m.forward_reference(torch.tensor(b, device=dev))
+    torch.cuda.synchronize()
+    ops.check_status()
+
+    def close(got, want, what):
+        err = (got - want).abs().max().item()
+        lim = (0.12 if index else 0.06) * want.abs().max().item() + 0.02     # a top-k boundary may differ by one position
+        assert err <= lim, (what, err, lim)
+
+    close(la[-1], want_a[139], "prefill a")
+    close(lb[-1], want_b[29], "prefill b")
+    for s in range(4):                                   # batched decode, teacher-forced
+        out = r.decode([0, 1], [a[140 + s], b[30 + s]])
+        close(out[0], want_a[140 + s], f"decode a {s}")
+        close(out[1], want_b[30 + s], f"decode b {s}")
+    assert r.lengths == [144, 34]
