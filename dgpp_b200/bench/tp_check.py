@@ -1,0 +1,133 @@
+"""Multi-GPU collective check and timing (run under torchrun, one rank per GPU):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m dgpp_b200.bench.tp_check
+
+Checks, on N ranks: the peer-memory one-shot all-reduce against a fixed-order fp32 fold and NCCL (values and time), the
+vocab-sharded pick merge, the fused GEMM -> reduce-scatter -> all-gather path against GEMM + fold, and a tensor-parallel
+engine run (fused and separate collectives, twice each) for bit-identical tokens across ranks and runs.  All times are
+CUDA-event times, maximum over ranks.  TP_HEADS sets the tiny model's head count (default 8).
+(reference counterparts: apps/bus_check.cpp, apps/nic_regress.cpp.)
+"""
+
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"]); local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local); dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from dgpp_b200.parallel.peer import PeerReducer
+    from dgpp_b200.parallel.tp import NcclReducer
+    from dgpp_b200.ops import core as ops
+    BF = torch.bfloat16
+    red = PeerReducer(5120, 2048, dev)
+    torch.manual_seed(rank)
+    for rows in (1, 8, 64, 2048, 3000):
+        x = torch.randn(rows, 5120, device=dev).to(BF)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        want = sum(p.float() for p in parts).to(BF)   # ascending-rank fp32 fold
+        y = x.clone(); red.all_reduce(y); torch.cuda.synchronize(); ops.check_status()
+        same = torch.equal(y, want)
+        ys = [torch.empty_like(y) for _ in range(world)]; dist.all_gather(ys, y)
+        ident = all(torch.equal(ys[0], q) for q in ys)
+        if rank == 0: print(f"all_reduce rows={rows}: matches fixed-order fold={same} identical across ranks={ident}", flush=True)
+    # timing vs NCCL (graph-captured, 50 calls)
+    for rows in (1, 8, 64):
+        x = torch.randn(rows, 5120, device=dev).to(BF)
+        for name, fn in (("peer", lambda: red.all_reduce(x)), ("nccl", lambda: dist.all_reduce(x))):
+            for _ in range(5): fn()
+            torch.cuda.synchronize(); dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(50): fn()
+            g.replay(); torch.cuda.synchronize(); dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); g.replay(); g.replay(); b.record(); torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / 100 * 1000], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if rank == 0: print(f"  {name} all_reduce rows={rows} (x5120 bf16): {t.item():.1f} us (max over ranks)", flush=True)
+    ops.check_status()
+    # pick merge
+    ids = torch.arange(8, device=dev, dtype=torch.int32) + 1000 * rank
+    vals = torch.tensor([float((i * 7 + rank * 3) % 5) for i in range(8)], device=dev)
+    gv = [torch.empty_like(vals) for _ in range(world)]; gi = [torch.empty_like(ids) for _ in range(world)]
+    dist.all_gather(gv, vals); dist.all_gather(gi, ids)
+    red.merge_picks(ids, vals); torch.cuda.synchronize(); ops.check_status()
+    GV = torch.stack(gv); GI = torch.stack(gi); best = torch.argmax(GV, 0)
+    ok = torch.equal(ids, GI.gather(0, best[None])[0])
+    if rank == 0: print("pick merge ok:", ok, flush=True)
+    # fused GEMM -> reduce-scatter -> all-gather vs GEMM + fixed-order fold
+    from dgpp_b200.quant.formats import random_quant_linear
+    for T in (100, 128, 300, 2048):
+        torch.manual_seed(100 + rank)
+        w = random_quant_linear(5120, 1024, "nvfp4", dev)
+        a = torch.randn(T, 1024, device=dev).to(BF)
+        torch.manual_seed(7)
+        x0 = torch.randn(T, 5120, device=dev).to(BF)
+        part = ops.gemm_tc(a, w)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        want = (x0.float() + sum(p.float() for p in parts).to(BF).float()).to(BF)
+        for rep in range(3):
+            x = x0.clone()
+            bn = ops.gemm_tc_push(a, w, red.comm)
+            red.rs_ag(x, bn)
+            torch.cuda.synchronize(); ops.check_status()
+            ok = torch.equal(x, want)
+            xs = [torch.empty_like(x) for _ in range(world)]; dist.all_gather(xs, x)
+            ident = all(torch.equal(xs[0], q) for q in xs)
+            if rank == 0: print(f"rs_ag T={T} rep={rep}: matches fold={ok} identical across ranks={ident} maxdiff={(x.float()-want.float()).abs().max().item():.4f}", flush=True)
+        # mixed with the one-shot all-reduce (shared epoch / slots)
+        y = part.clone(); red.all_reduce(y); torch.cuda.synchronize(); ops.check_status()
+    # timing: GEMM + all_reduce vs GEMM-push + rs_ag at a prefill chunk
+    T = 2048
+    w = random_quant_linear(5120, 5120 // world // 256 * 256 or 256, "nvfp4", dev)
+    a = torch.randn(T, w.k, device=dev).to(BF)
+    x = torch.randn(T, 5120, device=dev).to(BF)
+    d = torch.empty(T, 5120, device=dev, dtype=BF)
+    def unfused():
+        ops.gemm_tc(a, w, out=d); red.all_reduce(d)
+    def fused():
+        red.rs_ag(x, ops.gemm_tc_push(a, w, red.comm))
+    for name, fn in (("gemm + all_reduce", unfused), ("gemm_push + rs_ag", fused)):
+        for _ in range(3): fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10): fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / 10 * 1000], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0: print(f"  {name} T={T} N=5120 K={w.k}: {t.item():.1f} us (max over ranks)", flush=True)
+    ops.check_status()
+    # TP engine vs reference tokens; fused GEMM->all-reduce vs separate all-reduce kernel, each run twice
+    from dgpp_b200.engine.llm_engine import LLMEngine
+    from dgpp_b200.models.dense import DenseConfig, DenseModel
+    heads = int(os.environ.get("TP_HEADS", "8"))
+    cfg = DenseConfig.tiny(hidden=512, q_heads=heads, kv_heads=heads, head_dim=128, ffn=2048, vocab=4096, layers=3)
+    model = DenseModel.random_init(cfg, device=dev, seed=0, std=0.05, tp_rank=rank, tp_size=world)
+    if rank == 0: print("local q heads (padded):", model.hq_local, "o.k", model.layers[0].o.k, "down.k", model.layers[0].down.k, flush=True)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (150, 33)]
+    runs = []
+    for fuse in (False, True, False, True):
+        eng = LLMEngine(model, max_batch=2, max_seq_len=512, prefill_chunk=128, reducer=red, fuse_ar=fuse)
+        runs.append(eng.generate(prompts, max_tokens=12))
+        ops.check_status()
+        del eng
+    objs = [None] * world; dist.all_gather_object(objs, runs)
+    if rank == 0:
+        print("tokens identical across ranks:", all(o == objs[0] for o in objs), flush=True)
+        print("unfused run1 == run2:", runs[0] == runs[2], " fused run1 == run2:", runs[1] == runs[3], " fused == unfused:", runs[0] == runs[1], flush=True)
+        for i, r in enumerate(runs): print("  run", i, "fused" if i % 2 else "unfused", r[0], flush=True)
+    dist.barrier(); red.close(); dist.destroy_process_group()
+
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

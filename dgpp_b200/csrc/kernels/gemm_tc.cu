@@ -297,7 +297,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
               if (splits > 1) {
                 wsp[static_cast<size_t>(m) * p.N + n] = v;
               } else if (p.push) {
-                push_dst[static_cast<size_t>(m0 + m) * p.N + n] = f32_to_bf16(v * p.alpha);
+                // stage the tile in shared memory (the operand rings are idle once the accumulator is complete) so
+                // that the peer stores below are 16-byte vectors in 256-byte runs instead of 2-byte scalars
+                reinterpret_cast<bf16*>(sB)[m * kBM + (q * 32 + lane)] = f32_to_bf16(v * p.alpha);
               } else {
                 const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
                 float y = v * p.alpha;
@@ -313,6 +315,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
       }
     }
     if (p.push) {
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok && !*abort_flag) {
+        const int et = static_cast<int>(threadIdx.x) - 64;            // 0..127 over the four epilogue warps
+        const uint4* tile = reinterpret_cast<const uint4*>(sB);
+        for (int cidx = et; cidx < cols * (kBM / 8); cidx += 128) {
+          const int m = cidx / (kBM / 8), seg = cidx % (kBM / 8);
+          st_v4_global(push_dst + static_cast<size_t>(m0 + m) * p.N + n0 + seg * 8, tile[m * (kBM / 8) + seg]);
+        }
+      }
       // make the tile visible at system scope, then count it in at the owner (also after a failed wait: the owner's
       // bounded wait reports the missing data through the status block of THIS rank, not by stalling there)
       __threadfence_system();
