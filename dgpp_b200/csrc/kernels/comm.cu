@@ -199,7 +199,8 @@ rs_ag_kernel(CommState c, bf16* __restrict__ x, int T, int H, int tile_rows, int
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
         for (int s = 0; s < c.world; ++s) {
           Pack16 pk;
-          pk.u = ld_v4_global_volatile(payload(c, c.rank, parity, s) + off);
+          // L2 is the coherence point of the peers' stores: .cg loads skip L1 and, unlike volatile ones, pipeline
+          pk.u = __ldcg(reinterpret_cast<const uint4*>(payload(c, c.rank, parity, s) + off));
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] += bf16_to_f32(pk.h[j]);
         }
@@ -237,7 +238,7 @@ rs_ag_kernel(CommState c, bf16* __restrict__ x, int T, int H, int tile_rows, int
       for (int i = threadIdx.x; i < rows * vec; i += blockDim.x) {
         const int r = r0 + i / vec, v = i % vec;
         const size_t off = (static_cast<size_t>(r) * H + c0) * 2 + static_cast<size_t>(v) * 16;
-        const uint4 val = ld_v4_global_volatile(payload(c, c.rank, parity, owner) + off);
+        const uint4 val = __ldcg(reinterpret_cast<const uint4*>(payload(c, c.rank, parity, owner) + off));
         *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(x) + off) = val;
       }
     }

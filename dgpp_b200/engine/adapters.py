@@ -88,6 +88,17 @@ class ReferenceEngine(rt.SchedulerEngine):
         self.filled[slot] = 0
         self.pending[slot] = None
 
+    # ---- cold tier hooks (engine.spill.SpillingEngine)
+    def read_block(self, b: int) -> bytes:
+        return torch.stack([self.k[:, b], self.v[:, b]]).contiguous().cpu().numpy().tobytes()
+
+    def write_block(self, b: int, data: bytes) -> None:
+        t = torch.frombuffer(bytearray(data), dtype=torch.float32).view(2, *self.k[:, b].shape).to(self.k.device)
+        self.k[:, b], self.v[:, b] = t[0], t[1]
+
+    def advance(self, slot: int, tokens: int) -> None:
+        self.filled[slot] += tokens
+
     # ---- compute
     def _run(self, slot: int, tokens: List[int]) -> int:
         c = self.m.cfg
@@ -228,6 +239,29 @@ class KernelEngine(rt.SchedulerEngine):
         self.filled[slot] = 0
         self.pending[slot] = None
         self.slot_cfg[slot] = None
+
+    # ------------------------------------------------------------------ cold tier hooks (engine.spill.SpillingEngine)
+    def read_block(self, b: int) -> bytes:
+        parts = []
+        for L in self.kv.layers:
+            for t in (L.k, L.v, L.k_scale, L.v_scale):
+                if t is not None:
+                    parts.append(t[b].contiguous().view(torch.uint8).reshape(-1))
+        return torch.cat(parts).cpu().numpy().tobytes()
+
+    def write_block(self, b: int, data: bytes) -> None:
+        flat = torch.frombuffer(bytearray(data), dtype=torch.uint8).to(self.e.dev)
+        o = 0
+        for L in self.kv.layers:
+            for t in (L.k, L.v, L.k_scale, L.v_scale):
+                if t is not None:
+                    n = t[b].numel() * t.element_size()
+                    t[b].copy_(flat[o:o + n].view(t.dtype).view(t[b].shape))
+                    o += n
+        assert o == flat.numel(), "block image does not match this cache geometry"
+
+    def advance(self, slot: int, tokens: int) -> None:
+        self.filled[slot] += tokens
 
     # ------------------------------------------------------------------ sampling / constraints
     def configure(self, request_id: str, params=None, grammar=None, prompt_ids=None) -> None:
