@@ -70,8 +70,11 @@ def test_closed_runtime_calls_are_not_named():
     names = ["cudaMemcpy" + "BatchAsync", "cudaMemcpy3D" + "BatchAsync", "cuMemcpy" + "BatchAsync", "cuMemcpy3D" + "BatchAsync"]
     repo = os.path.dirname(os.path.dirname(ROOT))
     hits = []
-    for dirpath, dirnames, files in os.walk(repo):
-        dirnames[:] = [d for d in dirnames if d not in (".git", "gpurun_out", "_work", "build", "__pycache__", "baseline")]
+    roots = [os.path.join(repo, d) for d in ("dgpp_b200", "tests", "deploy")]
+    walk = [(repo, [], [f for f in os.listdir(repo) if os.path.isfile(os.path.join(repo, f))])]
+    for r in roots:
+        walk += [(dp, dn, fs) for dp, dn, fs in os.walk(r) if "__pycache__" not in dp and os.sep + "build" not in dp]
+    for dirpath, dirnames, files in walk:
         for f in files:
             if f.endswith((".cu", ".cuh", ".h", ".cpp", ".py", ".sh")):
                 text = open(os.path.join(dirpath, f), errors="ignore").read()
