@@ -14,6 +14,9 @@
 //   2  FP8 e4m3 [N, K] with one fp32 scale per 128x128 block [N/128, K/128]
 //        converter warps write bf16(e4m3 * scale).
 //   3  MXFP4: e2m1 pairs + e8m0 scale per 32 [N, K/32]   (scales read with plain loads)
+//   4  MXFP8: e4m3 [N, K] + e8m0 scale per 32 [N, K/32]   bf16(e4m3 * 2^e) is exact
+//   5  int8 and 6 int4 (two per byte, low nibble first): offset-binary codes (code - 128 / code - 8) with one bf16
+//        scale per 64 [N, K/64]; converter warps write bf16(int * scale)
 //
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
 // warps 2..9 = converters (quantised modes), warps 2..5 = epilogue (TMEM -> registers -> global).
@@ -48,7 +51,8 @@ struct GemmParams {
   float* ws;               // split-K partials [splits, T, N] fp32
   uint32_t* counters;      // split-K tile counters [n_tiles * m_tiles], zero at rest
   const float* blk_scale;  // WMODE 2: [ceil(N/128), K/128] fp32
-  const uint8_t* sf_plain; // WMODE 3: e8m0 scales [N, K/32]
+  const uint8_t* sf_plain; // WMODE 3 / 4: e8m0 scales [N, K/32]
+  const bf16* sf_bf16;     // WMODE 5 / 6: bf16 scales [N, K/64]
   DeviceStatus* status;
   int T, N, K, ldc;
   int kb_per_split;        // k64 blocks per split
@@ -67,7 +71,9 @@ struct GemmSmem {
   static constexpr int kStageSf = kBM * 16;                // 2 KB
 };
 
-// WMODE: 0 bf16, 1 nvfp4, 2 fp8 block, 3 mxfp4.  Converted operands are bf16 (kind::f16 requires A and B
+// WMODE: 0 bf16, 1 nvfp4, 2 fp8 block, 3 mxfp4, 4 mxfp8 (e4m3 + e8m0 per 32), 5 int8 and 6 int4 (offset-binary codes,
+// bf16 scale per 64).  Byte-per-element sources (2, 4, 5) stage 128 K per raw row, nibble sources (1, 3, 6) 256 K.
+// Converted operands are bf16 (kind::f16 requires A and B
 // to have the same 16-bit type; mixing an f16 A with a bf16 B is an illegal instruction on sm_100a).
 template <int BN, int WMODE, int SB, int SA, int SR>
 __global__ void __launch_bounds__(kGemmThreads, (WMODE != 0 && BN <= 32) ? 2 : 1)
@@ -135,14 +141,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
         const int kb = kb_begin + i;
         if (kQuant) {
           // raw weight stage: WMODE 1/3 cover 256 K (4 k64 blocks), WMODE 2 covers 128 K (2 k64 blocks)
-          constexpr int kSubs = (WMODE == 2) ? 2 : 4;
+          constexpr bool kByteSrc = WMODE == 2 || WMODE == 4 || WMODE == 5;
+          constexpr int kSubs = kByteSrc ? 2 : 4;
           if (i % kSubs == 0) {
             const int r = i / kSubs, sr = r % SR;
             if (!wait_bar(&raw_empty[sr], ((r / SR) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 1); *abort_flag = 1; break; }
             const uint32_t bytes = L::kStageRaw + (WMODE == 1 ? L::kStageSf : 0);
             mbar_expect_tx(&raw_full[sr], bytes);
             // packed bytes: x in bytes. fp4: kb*32 bytes; fp8: kb*64 bytes
-            const int xb = (WMODE == 2) ? kb * 64 : kb * 32;
+            const int xb = kByteSrc ? kb * 64 : kb * 32;
             tma_load_2d(sRaw + sr * L::kStageRaw, &tmA, xb, n0, &raw_full[sr]);
             if (WMODE == 1) tma_load_2d(sSf + sr * L::kStageSf, &tmSf, kb * 4, n0, &raw_full[sr]);
           }
@@ -187,7 +194,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
     // ------------------------------------------------------------------ converters (warps 2..9)
     const int ct = threadIdx.x - 64;       // 0..255
     const int row = ct >> 1, half = ct & 1;
-    constexpr int kSubs = (WMODE == 2) ? 2 : 4;
+    constexpr bool kByteSrc = WMODE == 2 || WMODE == 4 || WMODE == 5;
+    constexpr int kSubs = kByteSrc ? 2 : 4;
     for (int i = 0; i < nkb; ++i) {
       const int r = i / kSubs, sub = i % kSubs, sr = r % SR, sa = i % SA;
       bool ok = true;
@@ -197,7 +205,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
       const unsigned char* raw = sRaw + sr * L::kStageRaw + row * 128;
       unsigned char* dst = sA + sa * L::kStageA + row * 128;
       const int kb = kb_begin + i;
-      if (WMODE == 1 || WMODE == 3) {
+      if (WMODE == 6) {
+        // packed int4, offset binary: 32 weights = 16 bytes at logical chunk (sub*2 + half); one bf16 scale per 64
+        const int cl = sub * 2 + half;
+        Pack16 w;
+        w.u = *reinterpret_cast<const uint4*>(raw + ((cl ^ (row & 7)) << 4));
+        const int nrow = min(n0 + row, p.N - 1);
+        const float sc = bf16_to_f32(p.sf_bf16[static_cast<size_t>(nrow) * (p.K / 64) + kb]);
+        Pack16 o[4];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int lo = static_cast<int>(w.b[j] & 15) - 8, hi = static_cast<int>(w.b[j] >> 4) - 8;
+          bf162 v = __floats2bfloat162_rn(static_cast<float>(lo) * sc, static_cast<float>(hi) * sc);
+          o[j >> 2].w[j & 3] = *reinterpret_cast<uint32_t*>(&v);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4*>(dst + (((half * 4 + c) ^ (row & 7)) << 4)) = o[c].u;
+      } else if (WMODE == 1 || WMODE == 3) {
         // 32 weights = 16 packed bytes at logical 16-byte chunk (sub*2 + half) of the swizzled 128-byte row
         const int cl = sub * 2 + half;
         Pack16 w;
@@ -231,7 +256,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
           *reinterpret_cast<uint4*>(dst + (((half * 4 + c) ^ (row & 7)) << 4)) = o[c].u;
       } else {
         // FP8: 128-byte raw row holds 128 K; this k64 block is bytes [sub*64, sub*64+64); thread takes 32 of them
-        const float sc = p.blk_scale[static_cast<size_t>(blockIdx.x) * (p.K / 128) + (kb >> 1)];
+        // (this thread's 32 elements are one e8m0 group of 32, half of a bf16-scale group of 64)
+        float sc;
+        if (WMODE == 2) {
+          sc = p.blk_scale[static_cast<size_t>(blockIdx.x) * (p.K / 128) + (kb >> 1)];
+        } else {
+          const int nrow = min(n0 + row, p.N - 1);
+          sc = WMODE == 4 ? e8m0_to_f32(p.sf_plain[static_cast<size_t>(nrow) * (p.K / 32) + kb * 2 + half])
+                          : bf16_to_f32(p.sf_bf16[static_cast<size_t>(nrow) * (p.K / 64) + kb]);
+        }
         Pack16 o[4];
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {
@@ -240,7 +273,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
           w.u = *reinterpret_cast<const uint4*>(raw + ((cl ^ (row & 7)) << 4));
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float2 f = __half22float2(e4m3x2_to_h2(w.s[j]));
+            float2 f;
+            if (WMODE == 5) {
+              f.x = static_cast<float>(static_cast<int>(w.b[2 * j]) - 128);
+              f.y = static_cast<float>(static_cast<int>(w.b[2 * j + 1]) - 128);
+            } else {
+              f = __half22float2(e4m3x2_to_h2(w.s[j]));
+            }
             bf162 v = __floats2bfloat162_rn(f.x * sc, f.y * sc);
             o[c2 * 2 + (j >> 2)].w[j & 3] = *reinterpret_cast<uint32_t*>(&v);
           }
@@ -412,15 +451,17 @@ using namespace dgpp;
 
 // Scratch sizes for split-K: ws = splits * T * N floats; counters = ceil(N/128) * ceil(T/BN) uint32 (zeroed once).
 //
-// wmode: 0 bf16, 1 nvfp4, 2 fp8-block, 3 mxfp4.   a_f16 is ignored (kept for ABI stability).
+// wmode: 0 bf16, 1 nvfp4, 2 fp8-block, 3 mxfp4, 4 mxfp8, 5 int8 g64, 6 int4 g64.   a_f16 is ignored (ABI stability).
 // bn: token tile (16, 32, 64, 128, 256).  splits >= 1; K/64 blocks are divided evenly (4-block aligned for fp4).
 static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
                         const void* w_scale, float alpha, void* out, void* out32, const void* resid, int ldc,
                         int T, int N, int K, int splits, void* ws, void* counters, void* comm_push, cudaStream_t st) {
   DGPP_REQUIRE(T >= 1 && N >= 1, "gemm_tc: empty problem");
   DGPP_REQUIRE(K % 64 == 0, "gemm_tc: K %d must be a multiple of 64", K);
-  if (wmode == 1 || wmode == 3) DGPP_REQUIRE(K % 256 == 0, "gemm_tc: fp4 weights need K %% 256 == 0 (K=%d)", K);
-  if (wmode == 2) DGPP_REQUIRE(K % 128 == 0, "gemm_tc: fp8 block weights need K %% 128 == 0 (K=%d)", K);
+  const bool nibble_src = wmode == 1 || wmode == 3 || wmode == 6;
+  const bool byte_src = wmode == 2 || wmode == 4 || wmode == 5;
+  if (nibble_src) DGPP_REQUIRE(K % 256 == 0, "gemm_tc: 4-bit weights need K %% 256 == 0 (K=%d)", K);
+  if (byte_src) DGPP_REQUIRE(K % 128 == 0, "gemm_tc: 8-bit weights need K %% 128 == 0 (K=%d)", K);
   DGPP_REQUIRE(splits >= 1, "gemm_tc: splits must be >= 1");
   DGPP_REQUIRE(splits == 1 || (ws && counters), "gemm_tc: split-K needs workspace and counters");
   DGPP_REQUIRE(out || out32 || comm_push, "gemm_tc: no output");
@@ -444,11 +485,12 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
   p.ws = static_cast<float*>(ws);
   p.counters = static_cast<uint32_t*>(counters);
   p.blk_scale = wmode == 2 ? static_cast<const float*>(w_scale) : nullptr;
-  p.sf_plain = wmode == 3 ? static_cast<const uint8_t*>(w_scale) : nullptr;
+  p.sf_plain = (wmode == 3 || wmode == 4) ? static_cast<const uint8_t*>(w_scale) : nullptr;
+  p.sf_bf16 = (wmode == 5 || wmode == 6) ? static_cast<const bf16*>(w_scale) : nullptr;
   p.status = device_status_ptr();
   p.T = T; p.N = N; p.K = K; p.ldc = ldc;
   const int num_kb = K / 64;
-  const int align = (wmode == 1 || wmode == 3) ? 4 : (wmode == 2 ? 2 : 1);
+  const int align = nibble_src ? 4 : (byte_src ? 2 : 1);
   int per = dgpp_ceil_div(num_kb, splits);
   per = dgpp_ceil_div(per, align) * align;
   p.kb_per_split = per;
@@ -462,7 +504,7 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
     if (make_tmap_2d(&tA, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, static_cast<uint64_t>(K) * 2, 64, kBM,
                      CU_TENSOR_MAP_SWIZZLE_128B))
       return -1;
-  } else if (wmode == 2) {
+  } else if (byte_src) {
     if (make_tmap_2d(&tA, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, 128, kBM, CU_TENSOR_MAP_SWIZZLE_128B))
       return -1;
   } else {
@@ -479,6 +521,9 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
     if (wmode == 1) return launch_gemm<BNV, 1>(tA, tB, tSf, p, splits, st);      \
     if (wmode == 2) return launch_gemm<BNV, 2>(tA, tB, tSf, p, splits, st);      \
     if (wmode == 3) return launch_gemm<BNV, 3>(tA, tB, tSf, p, splits, st);      \
+    if (wmode == 4) return launch_gemm<BNV, 4>(tA, tB, tSf, p, splits, st);      \
+    if (wmode == 5) return launch_gemm<BNV, 5>(tA, tB, tSf, p, splits, st);      \
+    if (wmode == 6) return launch_gemm<BNV, 6>(tA, tB, tSf, p, splits, st);      \
   }
   DGPP_GEMM_BN(16) DGPP_GEMM_BN(32) DGPP_GEMM_BN(64) DGPP_GEMM_BN(128) DGPP_GEMM_BN(256)
 #undef DGPP_GEMM_BN

@@ -79,8 +79,12 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Opt
 def dense_config_from_hf(cfg: dict, weight_fmt: Optional[str] = None) -> DenseConfig:
     cfg = cfg.get("text_config", cfg)
     q = cfg.get("quantization_config") or {}
-    fmt = weight_fmt or {"nvfp4": "nvfp4", "mxfp4": "mxfp4", "fp8": "fp8"}.get(
+    fmt = weight_fmt or {"nvfp4": "nvfp4", "mxfp4": "mxfp4", "fp8": "fp8", "mxfp8": "mxfp8", "int4": "int4", "int8": "int8"}.get(
         str(q.get("quant_algo") or q.get("quant_method") or q.get("format") or "").lower().replace("-", ""), "bf16")
+    if not weight_fmt and str(q.get("format", "")).lower() == "pack-quantized":
+        groups = q.get("config_groups") or {}
+        bits = next((g.get("weights", {}).get("num_bits") for g in groups.values() if g.get("weights")), 4)
+        fmt = "int8" if bits == 8 else "int4"
     heads = cfg["num_attention_heads"]
     rope = cfg.get("rope_scaling") or {}
     hd = cfg.get("head_dim") or cfg["hidden_size"] // heads
@@ -96,12 +100,30 @@ def dense_config_from_hf(cfg: dict, weight_fmt: Optional[str] = None) -> DenseCo
         name=str(cfg.get("_name_or_path") or cfg.get("model_type") or "dense"))
 
 
-_GROUP = {"nvfp4": 16, "mxfp4": 32, "fp8": 128, "bf16": 1, "fp32": 1}
+_GROUP = {"nvfp4": 16, "mxfp4": 32, "fp8": 128, "mxfp8": 32, "int8": 64, "int4": 64, "bf16": 1, "fp32": 1}
 
 
 def _read_linear(ck: OpenCheckpoint, prefix: str, fmt: str, rows: Optional[Tuple[int, int]], cols: Optional[Tuple[int, int]],
                  device) -> QuantLinear:
     """One [N, K] projection sliced to rows [r0, r1) and / or K columns [c0, c1), still in storage format."""
+    if fmt in ("int4", "int8"):
+        # pack-quantized release: offset-binary codes packed little-endian into int32 words (8 or 4 per word) in
+        # `.weight_packed` (or plain bytes in `.weight`), one bf16 scale per 64 in `.weight_scale`
+        name = prefix + (".weight_packed" if ck.has(prefix + ".weight_packed") else ".weight")
+        raw = ck.tensor(name)
+        per_byte = 2 if fmt == "int4" else 1
+        by = raw.view(torch.uint8).view(raw.shape[0], -1)
+        n_full, k_full = by.shape[0], by.shape[1] * per_byte
+        r0, r1 = rows or (0, n_full)
+        c0, c1 = cols or (0, k_full)
+        if c0 % 64 or c1 % 64:
+            raise ValueError(f"{prefix}: K slice [{c0}, {c1}) does not start / end on a 64-wide scale group")
+        payload = by[r0:r1, c0 // per_byte:c1 // per_byte].contiguous().to(device)
+        sc = ck.tensor(prefix + ".weight_scale")
+        if sc.shape[1] * 64 != k_full:
+            raise ValueError(f"{prefix}: scales of group size {k_full // sc.shape[1]}; this engine streams group 64")
+        s = sc[r0:r1, c0 // 64:c1 // 64].to(torch.bfloat16).contiguous().to(device)
+        return QuantLinear(fmt, r1 - r0, c1 - c0, payload, s)
     w = ck.tensor(prefix + ".weight")
     n_full = w.shape[0]
     r0, r1 = rows or (0, n_full)
@@ -124,6 +146,10 @@ def _read_linear(ck: OpenCheckpoint, prefix: str, fmt: str, rows: Optional[Tuple
             elif ck.has(prefix + ".weight_global_scale"):
                 alpha = 1.0 / float(ck.tensor(prefix + ".weight_global_scale").float().reshape(-1)[0])
         return QuantLinear(fmt, r1 - r0, c1 - c0, payload, s, alpha)
+    if fmt == "mxfp8":
+        payload = w.view(torch.uint8)[r0:r1, c0:c1].contiguous().to(device)
+        s = ck.tensor(prefix + ".weight_scale").view(torch.uint8)[r0:r1, c0 // 32:c1 // 32].contiguous().to(device)
+        return QuantLinear(fmt, r1 - r0, c1 - c0, payload, s)
     if fmt == "fp8":
         if r0 % 128 or (r1 % 128 and r1 != n_full):
             raise ValueError(f"{prefix}: fp8 block rows [{r0}, {r1}) must be aligned to 128")
@@ -227,7 +253,11 @@ def save_dense(model: DenseModel, out_dir: str, shard_layers: int = 0) -> None:
             g[prefix + ".weight"] = w.payload[r0:r1].view(torch.float8_e4m3fn)
             g[prefix + ".weight_scale_inv"] = w.scale[r0 // 128:(r1 + 127) // 128]
             return
-        g[prefix + ".weight"] = w.payload[r0:r1]
+        if w.fmt in ("int4", "int8"):
+            g[prefix + ".weight_packed"] = w.payload[r0:r1].contiguous().view(torch.int32)
+            g[prefix + ".weight_scale"] = w.scale.view(w.n, -1)[r0:r1]
+            return
+        g[prefix + ".weight"] = w.payload[r0:r1].view(torch.float8_e4m3fn) if w.fmt == "mxfp8" else w.payload[r0:r1]
         sc = w.scale.view(w.n, -1)[r0:r1]
         g[prefix + ".weight_scale"] = sc.view(torch.float8_e4m3fn) if w.fmt == "nvfp4" else sc
         if w.fmt == "nvfp4":

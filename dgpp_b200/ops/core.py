@@ -11,7 +11,7 @@ from . import _lib
 from ._lib import call, ptr, stream_ptr
 
 _FMT_GEMV = {"nvfp4": 0, "mxfp4": 1, "bf16": 2}
-_FMT_GEMM = {"bf16": 0, "nvfp4": 1, "fp8": 2, "mxfp4": 3}
+_FMT_GEMM = {"bf16": 0, "nvfp4": 1, "fp8": 2, "mxfp4": 3, "mxfp8": 4, "int8": 5, "int4": 6}
 
 # The converted-weight operand is always bf16: tcgen05 kind::f16 takes A and B of one 16-bit type.
 A_F16_DEFAULT = 0

@@ -90,7 +90,8 @@ def test_shard_slices_cover_extent_without_overlap():
         rt.shard_slice(rt.Split.Cols, 2, 0, 100, 16)
 
 
-@pytest.mark.parametrize("fmt,shard_layers", [("bf16", 0), ("nvfp4", 1), ("mxfp4", 0), ("fp8", 2)])
+@pytest.mark.parametrize("fmt,shard_layers", [("bf16", 0), ("nvfp4", 1), ("mxfp4", 0), ("fp8", 2), ("mxfp8", 0), ("int4", 1),
+                                              ("int8", 0)])
 def test_dense_checkpoint_round_trip_and_tp_slices(tmp_path, fmt, shard_layers):
     heads = (8, 4) if fmt == "fp8" else (4, 2)       # fp8 128 x 128 blocks: rank slices must stay block aligned
     cfg = DenseConfig.tiny(hidden=256, q_heads=heads[0], kv_heads=heads[1], head_dim=64, ffn=512, vocab=512, layers=3, weight_fmt=fmt)

@@ -71,7 +71,8 @@ def test_gemv(dev, fmt, rows):
     _close(y, ref.linear(x, w), 2 ** -6, 2e-3)
 
 
-@pytest.mark.parametrize("fmt,a_f16", [("bf16", 0), ("nvfp4", 0), ("fp8", 0), ("mxfp4", 0)])
+@pytest.mark.parametrize("fmt,a_f16", [("bf16", 0), ("nvfp4", 0), ("fp8", 0), ("mxfp4", 0), ("mxfp8", 0), ("int8", 0),
+                                       ("int4", 0)])
 @pytest.mark.parametrize("rows,bn,splits", [(1, 16, 1), (8, 16, 4), (37, 64, 1), (130, 128, 2), (300, 256, 1)])
 def test_gemm_tc(dev, fmt, a_f16, rows, bn, splits):
     from dgpp_b200.ops import core as ops, reference as ref
@@ -84,7 +85,8 @@ def test_gemm_tc(dev, fmt, a_f16, rows, bn, splits):
     y = ops.gemm_tc(x, w, bn=bn, splits=splits, a_f16=a_f16)
     ops.check_status()
     # fp8 block weights reach the tensor core as bf16(e4m3 * scale): compare against that operand
-    wr = w if fmt != "fp8" else quantize(w.dequant().to(BF).float(), "bf16")
+    # (likewise int8 / int4: bf16(code * scale))
+    wr = w if fmt not in ("fp8", "int8", "int4") else quantize(w.dequant().to(BF).float(), "bf16")
     yr = ref.linear(x, wr)
     _close(y, yr, 2 ** -6, 4e-3)
     # fp32 output + fused residual
