@@ -94,7 +94,12 @@ def main() -> int:
         ops.gemm_tc(a, w, out=d); red.all_reduce(d)
     def fused():
         red.rs_ag(x, ops.gemm_tc_push(a, w, red.comm))
-    for name, fn in (("gemm + all_reduce", unfused), ("gemm_push + rs_ag", fused)):
+    def gemm_only():
+        ops.gemm_tc(a, w, out=d)
+    def ar_only():
+        red.all_reduce(d)
+    for name, fn in (("gemm alone", gemm_only), ("all_reduce alone", ar_only), ("gemm + all_reduce", unfused),
+                     ("gemm_push + rs_ag", fused)):
         for _ in range(3): fn()
         torch.cuda.synchronize(); dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -261,6 +261,11 @@ __device__ __forceinline__ uint4 ld_v4_global_volatile(const void* p) {
 }
 
 // Programmatic dependent launch: let the next kernel's prologue start / wait for the previous grid.
+// Ask L2 to fetch [p, p + bytes) (16-byte aligned, bytes % 16 == 0); returns at once, completion is not observable.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // pdl_wait(): block until the preceding grid has completed and its memory is visible, THEN allow the next grid
 // in the stream / graph to start launching.  Triggering only after the wait keeps the overlap to one kernel deep:
 // a grid's prologue can run under its immediate predecessor only, never under an older, still running grid.

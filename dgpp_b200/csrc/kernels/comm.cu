@@ -191,27 +191,42 @@ rs_ag_kernel(CommState c, bf16* __restrict__ x, int T, int H, int tile_rows, int
     }
     __syncthreads();
     if (ok_s) {
-      for (int i = threadIdx.x; i < rows * vec; i += blockDim.x) {
-        const int r = r0 + i / vec, v = i % vec;
-        const size_t off = (static_cast<size_t>(r) * H + c0) * 2 + static_cast<size_t>(v) * 16;
-        float acc[8];
+      // four independent 16-byte vectors per thread and iteration: the loop is bound by memory latency, not by math
+      constexpr int U = 4;
+      const int items = rows * vec;
+      for (int i0 = threadIdx.x; i0 < items; i0 += blockDim.x * U) {
+        size_t off[U];
+        float acc[U][8];
+        Pack16 xr[U];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int s = 0; s < c.world; ++s) {
-          Pack16 pk;
-          // L2 is the coherence point of the peers' stores: .cg loads skip L1 and, unlike volatile ones, pipeline
-          pk.u = __ldcg(reinterpret_cast<const uint4*>(payload(c, c.rank, parity, s) + off));
+        for (int u = 0; u < U; ++u) {
+          const int i = min(i0 + u * static_cast<int>(blockDim.x), items - 1);      // clamped: tail lanes repeat an item
+          off[u] = (static_cast<size_t>(r0 + i / vec) * H + c0) * 2 + static_cast<size_t>(i % vec) * 16;
+          xr[u].u = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(x) + off[u]);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] += bf16_to_f32(pk.h[j]);
+          for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
         }
-        Pack16 xr;
-        xr.u = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(x) + off);
+        for (int s = 0; s < c.world; ++s) {
+          Pack16 pk[U];
+          // L2 is the coherence point of the peers' stores: .cg loads skip L1 and, unlike volatile ones, pipeline
 #pragma unroll
-        for (int j = 0; j < 8; ++j) xr.h[j] = f32_to_bf16(bf16_to_f32(xr.h[j]) + bf16_to_f32(f32_to_bf16(acc[j])));
-        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(x) + off) = xr.u;
-        for (int d = 1; d < c.world; ++d) {
-          const int dst = (c.rank + d) % c.world;
-          st_v4_global(payload(c, dst, parity, c.rank) + off, xr.u);
+          for (int u = 0; u < U; ++u) pk[u].u = __ldcg(reinterpret_cast<const uint4*>(payload(c, c.rank, parity, s) + off[u]));
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[u][j] += bf16_to_f32(pk[u].h[j]);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + u * static_cast<int>(blockDim.x) >= items) break;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            xr[u].h[j] = f32_to_bf16(bf16_to_f32(xr[u].h[j]) + bf16_to_f32(f32_to_bf16(acc[u][j])));
+          *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(x) + off[u]) = xr[u].u;
+          for (int d = 1; d < c.world; ++d) {
+            const int dst = (c.rank + d) % c.world;
+            st_v4_global(payload(c, dst, parity, c.rank) + off[u], xr[u].u);
+          }
         }
       }
     }
@@ -235,11 +250,21 @@ rs_ag_kernel(CommState c, bf16* __restrict__ x, int T, int H, int tile_rows, int
     }
     __syncthreads();
     if (ok_s) {
-      for (int i = threadIdx.x; i < rows * vec; i += blockDim.x) {
-        const int r = r0 + i / vec, v = i % vec;
-        const size_t off = (static_cast<size_t>(r) * H + c0) * 2 + static_cast<size_t>(v) * 16;
-        const uint4 val = __ldcg(reinterpret_cast<const uint4*>(payload(c, c.rank, parity, owner) + off));
-        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(x) + off) = val;
+      constexpr int U = 4;
+      const int items = rows * vec;
+      for (int i0 = threadIdx.x; i0 < items; i0 += blockDim.x * U) {
+        size_t off[U];
+        uint4 val[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = min(i0 + u * static_cast<int>(blockDim.x), items - 1);
+          off[u] = (static_cast<size_t>(r0 + i / vec) * H + c0) * 2 + static_cast<size_t>(i % vec) * 16;
+          val[u] = __ldcg(reinterpret_cast<const uint4*>(payload(c, c.rank, parity, owner) + off[u]));
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * static_cast<int>(blockDim.x) < items)
+            *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(x) + off[u]) = val[u];
       }
     }
   }

@@ -67,6 +67,11 @@ struct Fp4Params {
   const float* group_alpha;    // per-expert tensor scale, replaces alpha
   int group_tiles, group_b, grid_x;
   int64_t group_out_stride;
+  // L2 prefetch of what the NEXT weight-streaming kernel will read (decode): once this CTA's own loads are issued,
+  // its producer warp asks L2 for a slice of [pf_ptr, pf_ptr + pf_bytes).  The small kernels between two projections
+  // (quantiser, RoPE, attention over a short context) leave HBM idle; the prefetch fills that time.  A hint only.
+  const unsigned char* pf_ptr;
+  int64_t pf_bytes;
 };
 
 // One bf16 of the finished output tile -> slot `rank` of every rank (destinations staggered by rank).
@@ -184,6 +189,16 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
           bulk_load_1d(sSfb + (s * RMAX + r) * kSfbBytes, sfb, kSfbBytes, &full[s]);
         }
         if (*abort_flag) break;
+      }
+    }
+    __syncwarp();
+    if (p.pf_bytes > 0) {
+      constexpr int64_t kChunk = 16384;
+      const int64_t ctas = static_cast<int64_t>(gridDim.x) * gridDim.y * gridDim.z;
+      const int64_t cta = (static_cast<int64_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+      for (int64_t off = (cta * 32 + lane) * kChunk; off < p.pf_bytes; off += ctas * 32 * kChunk) {
+        const uint32_t n = static_cast<uint32_t>(min(kChunk, p.pf_bytes - off)) & ~15u;
+        if (n) l2_prefetch_bulk(p.pf_ptr + off, n);
       }
     }
   } else if (warp == 1) {
@@ -535,6 +550,17 @@ DGPP_API int dgpp_act_quant_nvfp4(int mode, const void* in, int64_t in_stride, c
 }
 
 // out[T, N] = alpha * g[t] * sum_r Wq . Xq_r^T.   xq: [R, T_pad, K/2]; xsf / wsf_tiled: tiled scale factors; g: [T].
+// One-shot hint for the NEXT dgpp_gemm_fp4 / dgpp_gemm_fp4_grouped call of this thread: the bytes its CTAs ask L2
+// to fetch once their own loads are issued (normally the packed weights of the projection that runs next).
+static thread_local const unsigned char* g_pf_ptr = nullptr;
+static thread_local int64_t g_pf_bytes = 0;
+DGPP_API int dgpp_gemm_fp4_set_prefetch(const void* ptr, int64_t bytes) {
+  DGPP_REQUIRE(bytes >= 0 && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0, "gemm_fp4 prefetch: unaligned range");
+  g_pf_ptr = static_cast<const unsigned char*>(ptr);
+  g_pf_bytes = ptr ? bytes : 0;
+  return 0;
+}
+
 DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* g, int R, int T_pad, const void* wq,
                            const void* wsf_tiled, float alpha, void* out, void* out32, const void* resid, int ldc,
                            int T, int N, int K, int splits, void* ws, void* counters, void* comm_push,
@@ -558,6 +584,8 @@ DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* 
   p.status = device_status_ptr();
   p.T = T; p.T_pad = T_pad; p.N = N; p.K = K; p.ldc = ldc; p.R = R;
   p.push = 0;
+  p.pf_ptr = g_pf_ptr; p.pf_bytes = g_pf_bytes;
+  g_pf_ptr = nullptr; g_pf_bytes = 0;
   p.group_list = nullptr; p.group_alpha = nullptr; p.group_tiles = 0; p.group_b = 0; p.grid_x = 0; p.group_out_stride = 0;
   memset(&p.comm, 0, sizeof(p.comm));
   if (comm_push) {
@@ -624,6 +652,8 @@ DGPP_API int dgpp_gemm_fp4_grouped(int bn, const void* xq, const void* xsf, cons
   p.status = device_status_ptr();
   p.T = T; p.T_pad = bn; p.N = N; p.K = K; p.ldc = ldc; p.R = R;
   p.push = 0;
+  p.pf_ptr = g_pf_ptr; p.pf_bytes = g_pf_bytes;
+  g_pf_ptr = nullptr; g_pf_bytes = 0;
   memset(&p.comm, 0, sizeof(p.comm));
   p.group_list = static_cast<const int32_t*>(group_list);
   p.group_alpha = static_cast<const float*>(group_alpha);

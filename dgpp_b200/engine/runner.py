@@ -50,6 +50,11 @@ class DenseRunner:
         self.act_terms = act_terms
         self.chunk = None
         self._li = 0
+        # decode: a projection can ask L2 for the next projection's weights while the small kernels between them
+        # leave HBM idle.  Measured on the 27B-class model at C8 the hint LOSES (7.70 vs 7.43 ms per step: the requests
+        # compete with the issuing kernel's own weight stream), so it is off unless DGPP_L2_PREFETCH=1.
+        import os
+        self.l2_prefetch = os.environ.get("DGPP_L2_PREFETCH", "0") == "1"
         # fused GEMM -> all-reduce (peer-memory push in the GEMM epilogue, fold in the next norm kernel)
         self.fuse_ar = fuse_ar and reducer is not None and getattr(reducer, "comm", None) is not None and \
             model.cfg.hidden % 128 == 0 and model.cfg.hidden // 128 <= 64
@@ -107,7 +112,8 @@ class DenseRunner:
         else:
             xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta if have_delta else None,
                                      norm_w=L.in_norm, eps=c.eps, x_out=xn)
-        ops.gemm_fp4(xa, L.qkv, out=qkv)
+        pf = self.l2_prefetch
+        ops.gemm_fp4(xa, L.qkv, out=qkv, prefetch=L.o if pf else None)
         if lora is not None:
             lora.apply(li, "qkv", xn, qkv, self.lora_scratch)
         ops.rope_kv_write(qkv, positions, row_req, self.kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
@@ -118,26 +124,27 @@ class DenseRunner:
         # add + RMSNorm + quantise kernel folds them (no separate all-reduce launch)
         fuse = getattr(self.reducer, "comm", None) if (self.fuse_ar and lora is None) else None
         if fuse:
-            ops.gemm_fp4(xa, L.o, push_comm=fuse)
+            ops.gemm_fp4(xa, L.o, push_comm=fuse, prefetch=L.gate_up if pf else None)
             xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", norm_w=L.post_norm, eps=c.eps, fold_comm=fuse)
         else:
-            ops.gemm_fp4(xa, L.o, out=delta)
+            ops.gemm_fp4(xa, L.o, out=delta, prefetch=L.gate_up if pf else None)
             if lora is not None:
                 lora.apply(li, "o", attn, delta, self.lora_scratch)
             if self.reducer is not None:
                 self.reducer.all_reduce(delta)
             xa = ops.act_quant_nvfp4(x, out=self.qa[H], mode="rmsnorm", delta=delta, norm_w=L.post_norm, eps=c.eps,
                                      x_out=xn)
-        ops.gemm_fp4(xa, L.gate_up, out=gu)
+        ops.gemm_fp4(xa, L.gate_up, out=gu, prefetch=L.down if pf else None)
         act = None
         if lora is not None:
             lora.apply(li, "gate_up", xn, gu, self.lora_scratch)
             act = self.act[:rows]
         xa = ops.act_quant_nvfp4(gu, out=self.qa[gu.shape[1] // 2], mode="swiglu", x_out=act)
+        nxt = self.layers_fp4[li + 1].qkv if (pf and li + 1 < len(self.layers_fp4)) else None
         if fuse and not last:
-            ops.gemm_fp4(xa, L.down, push_comm=fuse)
+            ops.gemm_fp4(xa, L.down, push_comm=fuse, prefetch=nxt)
             return True            # the next layer's first kernel folds the pushed tiles
-        ops.gemm_fp4(xa, L.down, out=delta)
+        ops.gemm_fp4(xa, L.down, out=delta, prefetch=nxt)
         if lora is not None:
             lora.apply(li, "down", act, delta, self.lora_scratch)
         if self.reducer is not None:

@@ -224,8 +224,11 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
 
 def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
              out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
-             splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, push_comm=None) -> torch.Tensor:
+             splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, push_comm=None,
+             prefetch: Optional[QuantLinear] = None) -> torch.Tensor:
     """Block-scaled NVFP4 tensor-core linear on pre-quantised activations (token tile = xa.bn).
+    prefetch: the projection that runs next; its packed weights are requested into L2 by this kernel's CTAs once
+    their own loads are issued (fills the HBM-idle time of the small kernels in between; a hint, never needed).
     push_comm: native peer-communicator handle; the finished bf16 tiles are then stored into every rank's
     symmetric region (with per-tile flags) instead of `out` -- the first half of a fused all-reduce."""
     assert w.fmt == "nvfp4" and xa.k == w.k
@@ -243,6 +246,8 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
             splits = 1
         else:
             wsp, cnt = ws.partials, ws.counters
+    if prefetch is not None:
+        call("dgpp_gemm_fp4_set_prefetch", ptr(prefetch.payload), prefetch.payload.numel() // 16 * 16)
     call("dgpp_gemm_fp4", bn, ptr(xa.q), ptr(xa.sf), ptr(xa.g), xa.terms, xa.rows_pad, ptr(w.payload),
          ptr(w.tiled_scales()), float(w.alpha), ptr(out), ptr(out32), ptr(resid), ldc, rows, w.n, w.k, splits,
          ptr(wsp), ptr(cnt), push_comm, stream_ptr())
