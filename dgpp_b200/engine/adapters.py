@@ -276,8 +276,6 @@ class KernelEngine(rt.SchedulerEngine):
         if cfg is None or (cfg[0] is None and cfg[1] is None):
             return
         params, grammar, prompt_ids = cfg
-        if self.e.model.tp_size > 1:
-            raise RuntimeError("sampled / constrained decoding needs the full vocabulary on one rank (tp_size 1)")
         from ..sampling.device import DeviceSampler, SamplingParams
         if self.sampler is None:
             self.sampler = DeviceSampler(self.e.model.cfg.vocab, self.e.max_batch, self.e.max_batch, self.e.dev)
@@ -306,6 +304,14 @@ class KernelEngine(rt.SchedulerEngine):
                     m[r, :] = 0
                     m[r, :min(words, gm.shape[0])] = gm[:words]
             masks = torch.from_numpy(m.view(np.int32)).to(self.e.dev)
+        if self.e.model.tp_size > 1:
+            # vocabulary-sharded head: gather the ranks' logit slices (in rank order = vocabulary order) so that
+            # every rank runs the same sampler on the same full rows and draws the same token
+            import torch.distributed as dist
+            part = logits[:rows].contiguous()
+            parts = [torch.empty_like(part) for _ in range(self.e.model.tp_size)]
+            dist.all_gather(parts, part)
+            logits = torch.cat(parts, dim=1)
         picked = self.sampler.sample(logits, params, [s if self.slot_cfg[s] else -1 for s in slots],
                                      [self.filled[s] for s in slots], masks=masks)
         for r, s in enumerate(slots):

@@ -244,13 +244,17 @@ class Server:
             if (params is not None or schema is not None or tool_mode is not None) and hasattr(self.engine, "configure"):
                 if params is not None and r["n"] > 1 and r["seed"] is not None:
                     params = type(params)(**{**params.__dict__, "seed": int(r["seed"]) + i})
-                grammar = None
+                grammar, spec = None, None
                 if tool_mode is not None:
                     required, only = tool_mode
-                    grammar = rt.ToolGrammar(r["tools_json"], required, bool(r.get("parallel_tool_calls", True)),
-                                             self._token_table(), self.eos_ids, only)
+                    par = bool(r.get("parallel_tool_calls", True))
+                    grammar = rt.ToolGrammar(r["tools_json"], required, par, self._token_table(), self.eos_ids, only)
+                    spec = ["tools", r["tools_json"], required, par, only]
                 elif schema is not None:
                     grammar = rt.JsonGrammar(schema, self._token_table(), self.eos_ids)
+                    spec = ["json", schema]
+                if self.world is not None:
+                    self.world.configure(rid, None if params is None else dict(params.__dict__), spec, ids)
                 self.engine.configure(rid, params, grammar, ids)
             self.live[rid] = _Live(rid, conn, r, i, group, len(ids), created, rt.StreamDecoder(self.tok, True),
                                    rt.StopScanner(list(r["stop"])), t_submit=time.time())
@@ -479,19 +483,27 @@ def main(argv=None) -> int:
 
 
 def serve_deployment(config_path: str) -> int:
-    """Serve the checkpoint a deployment JSON names: weights through the native loader (or this rank's resident
-    image), tokenizer.json and the chat template of the checkpoint directory, engine sized by the config.
-    `model` may also be "fake" / "tiny" (no checkpoint: the launcher's smoke deployments)."""
+    """Serve what a deployment JSON names: weights through the native loader (or this rank's resident image),
+    tokenizer.json and the chat template of the checkpoint directory, engine sized by the config.  `model` may also be
+    "fake" / "tiny" (no checkpoint: the launcher's smoke deployments).
+
+    tensor_parallel > 1: start one process per GPU (``python -m torch.distributed.run --nproc-per-node W -m
+    dgpp_b200.serve.app --config <json>``).  Rank 0 runs the HTTP front end and journals every scheduler input to the
+    other ranks (journal port = port + 1 unless DGPP_JOURNAL_PORT is set), which replay it into their own scheduler and
+    engine shard; collectives go through the peer-memory reducer.  A follower exits with status 3 when the leader
+    goes away."""
     import os
 
     text = open(config_path).read()
     cfg_json, digest = rt.parse_cluster_config(text)
     cfg = json.loads(cfg_json)
     rt.set_log_level(cfg["log_level"])
-    rt.log("info", "serve", f"config: {cfg_json} digest={digest:016x}")
+    world = int(cfg["tensor_parallel"])
+    rank = int(os.environ.get("RANK", "0")) if world > 1 else 0
+    rt.log("info", "serve", f"rank {rank}/{world} config: {cfg_json} digest={digest:016x}")
     eos = [257]
     template = DEFAULT_TEMPLATE
-    if cfg["model"] in ("fake", "tiny"):
+    if cfg["model"] == "fake" or (cfg["model"] == "tiny" and world == 1):
         return main(["--model", cfg["model"], "--host", cfg["host"], "--port", str(cfg["port"]),
                      "--slots", str(cfg["max_concurrency"])])
     import torch
@@ -500,35 +512,77 @@ def serve_deployment(config_path: str) -> int:
     from ..engine.llm_engine import LLMEngine
     from ..loaders import resident_image
     from ..loaders.checkpoint import dense_config_from_hf, load_dense, open_checkpoint
+    from ..models.dense import DenseConfig, DenseModel
 
-    if cfg["tensor_parallel"] != 1:
-        raise SystemExit("the HTTP front end drives one rank; tensor-parallel serving is started through bench.py / "
-                         "the engine API (sampling needs the full vocabulary on one rank)")
-    ck = open_checkpoint(cfg["model"])
-    dcfg = dense_config_from_hf(ck.config)
-    cache_dir = os.environ.get("DGPP_RESIDENT_CACHE_DIR", "")
-    build = lambda: load_dense(cfg["model"], device="cuda")
-    if cache_dir:
-        model, hit = resident_image.load_or_build(build, cache_dir, f"{ck.dir}", dcfg, device="cuda")
-        rt.log("info", "serve", f"weights from {'the resident image' if hit else 'the checkpoint (image written)'}")
+    reducer = None
+    dev = "cuda"
+    if world > 1:
+        import torch.distributed as dist
+
+        from ..parallel.peer import PeerReducer
+        if int(os.environ.get("WORLD_SIZE", "1")) != world:
+            raise SystemExit(f"tensor_parallel {world} wants {world} ranks (torchrun --nproc-per-node {world})")
+        local = int(os.environ.get("LOCAL_RANK", rank))
+        torch.cuda.set_device(local)
+        dev = f"cuda:{local}"
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    if cfg["model"] == "tiny":
+        dcfg = DenseConfig.tiny(hidden=512, q_heads=8, kv_heads=8, head_dim=128, ffn=2048, vocab=4096, layers=2)
+        model = DenseModel.random_init(dcfg, device=dev, seed=0, std=0.05, tp_rank=rank, tp_size=world)
+        tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)], rt.SplitPattern.Qwen2)
+        name = "dgpp-b200-tiny"
     else:
-        model = build()
-    tok = rt.Tokenizer.from_file(os.path.join(ck.dir, "tokenizer.json"))
-    tc_path = os.path.join(ck.dir, "tokenizer_config.json")
-    if os.path.exists(tc_path):
-        tc = json.load(open(tc_path))
-        template = tc.get("chat_template") or template
-        e = tc.get("eos_token")
-        e = e.get("content") if isinstance(e, dict) else e
-        if e and tok.token_to_id(e) >= 0:
-            eos = [tok.token_to_id(e)]
-    gen = ck.config.get("eos_token_id")
-    if gen is not None:
-        eos = sorted(set(eos + (list(gen) if isinstance(gen, list) else [gen])))
+        ck = open_checkpoint(cfg["model"])
+        dcfg = dense_config_from_hf(ck.config)
+        cache_dir = os.environ.get("DGPP_RESIDENT_CACHE_DIR", "")
+        build = lambda: load_dense(cfg["model"], device=dev, tp_rank=rank, tp_size=world)
+        if cache_dir:
+            model, hit = resident_image.load_or_build(build, cache_dir, f"{ck.dir}", dcfg, device=dev, tp_rank=rank,
+                                                      tp_size=world)
+            rt.log("info", "serve", f"weights from {'the resident image' if hit else 'the checkpoint (image written)'}")
+        else:
+            model = build()
+        tok = rt.Tokenizer.from_file(os.path.join(ck.dir, "tokenizer.json"))
+        tc_path = os.path.join(ck.dir, "tokenizer_config.json")
+        if os.path.exists(tc_path):
+            tc = json.load(open(tc_path))
+            template = tc.get("chat_template") or template
+            e = tc.get("eos_token")
+            e = e.get("content") if isinstance(e, dict) else e
+            if e and tok.token_to_id(e) >= 0:
+                eos = [tok.token_to_id(e)]
+        gen = ck.config.get("eos_token_id")
+        if gen is not None:
+            eos = sorted(set(eos + (list(gen) if isinstance(gen, list) else [gen])))
+        name = os.path.basename(os.path.normpath(ck.dir))
+    if world > 1:
+        reducer = PeerReducer(dcfg.hidden, cfg["prefill_chunk"], torch.device(dev))
     eng = KernelEngine(LLMEngine(model, max_batch=cfg["max_concurrency"], max_seq_len=cfg["max_context"],
-                                 prefill_chunk=cfg["prefill_chunk"]))
-    srv = Server(eng, tok, template_src=template, model_name=os.path.basename(os.path.normpath(ck.dir)),
-                 host=cfg["host"], port=cfg["port"], eos_ids=eos)
+                                 prefill_chunk=cfg["prefill_chunk"], reducer=reducer, fuse_ar=cfg["fuse_all_reduce"]))
+    leader = None
+    if world > 1:
+        from .world import WorldLeader, run_follower
+        jport = int(os.environ.get("DGPP_JOURNAL_PORT", cfg["port"] + 1))
+        if rank != 0:
+            table = [b"" if tok.is_special(i) else tok.token_bytes(i) for i in range(tok.vocab_size())]
+
+            def configure(rid, params, grammar_spec, ids):
+                from ..sampling.device import SamplingParams
+                g = None
+                if grammar_spec and grammar_spec[0] == "json":
+                    g = rt.JsonGrammar(grammar_spec[1], table, eos)
+                elif grammar_spec and grammar_spec[0] == "tools":
+                    g = rt.ToolGrammar(grammar_spec[1], grammar_spec[2], grammar_spec[3], table, eos, grammar_spec[4])
+                if params is not None:
+                    params = SamplingParams(**{**params, "logit_bias": {int(k): v for k, v in params.get("logit_bias", {}).items()}})
+                eng.configure(rid, params, g, ids)
+
+            return run_follower(eng, os.environ.get("MASTER_ADDR", "127.0.0.1"), jport, config_digest=digest,
+                                on_configure=configure)
+        leader = WorldLeader(world, jport, config_digest=digest)
+        leader.wait_for_followers()
+    srv = Server(eng, tok, template_src=template, model_name=name, host=cfg["host"], port=cfg["port"], eos_ids=eos,
+                 world_leader=leader)
     print(f"listening on http://{cfg['host']}:{srv.start()}", flush=True)
     try:
         while True:

@@ -55,6 +55,13 @@ class WorldLeader:
         self._send(self.journal.append("submit", rid, list(ids), int(max_tokens), extra))
         sched.submit(rid, list(ids), max_tokens, **kw)
 
+    def configure(self, rid: str, params: Optional[dict], grammar_spec, prompt_ids) -> None:
+        """Sampling parameters / grammar of a request, sent ahead of its submit record so that every rank binds the
+        same sampler state to the request (grammar_spec: ["json", schema] or ["tools", tools_json, required,
+        parallel, only-function] -- each rank compiles its own copy)."""
+        extra = json.dumps({"params": params, "grammar": grammar_spec}, sort_keys=True)
+        self._send(self.journal.append("configure", rid, list(prompt_ids or []), 0, extra))
+
     def cancel(self, sched, rid: str) -> None:
         self._send(self.journal.append("cancel", rid))
         sched.cancel(rid)
@@ -114,7 +121,8 @@ class RankMetrics:
 
 
 def run_follower(engine, host: str, port: int, sched_config=None, config_digest: int = 0, on_events=None,
-                 idle_timeout_ms: int = 1000, max_idle_s: float = 0.0, metrics: Optional[RankMetrics] = None) -> int:
+                 idle_timeout_ms: int = 1000, max_idle_s: float = 0.0, metrics: Optional[RankMetrics] = None,
+                 on_configure=None) -> int:
     """Replay the leader's journal into a local scheduler + engine until a `shutdown` record (returns 0) or until
     the leader goes away (returns 3).  A digest mismatch raises.  `on_events(list)` receives the scheduler's events
     after every tick (followers normally drop them: rank 0 answers the clients)."""
@@ -150,6 +158,10 @@ def run_follower(engine, host: str, port: int, sched_config=None, config_digest:
         if op == "submit":
             kw = json.loads(rec["extra"]) if rec["extra"] else {}
             sched.submit(rec["id"], list(rec["tokens"]), rec["arg"], **kw)
+        elif op == "configure":
+            if on_configure is not None:
+                d = json.loads(rec["extra"])
+                on_configure(rec["id"], d.get("params"), d.get("grammar"), list(rec["tokens"]))
         elif op == "cancel":
             sched.cancel(rec["id"])
         elif op == "tick":

@@ -142,3 +142,26 @@ def test_follower_rank_metrics_listener():
     assert out["rc"] == 0
     assert 'dgpp_rank_up{rank="1"} 1' in text and 'dgpp_rank_tokens_total{rank="1"} 5' in text
     assert 'dgpp_rank_submits_total{rank="1"} 1' in text
+
+
+def test_configure_records_reach_the_follower_before_the_submit():
+    leader = WorldLeader(world=2)
+    seen = []
+    out = {}
+
+    def follow():
+        out["rc"] = run_follower(_engine(), "127.0.0.1", leader.port,
+                                 on_configure=lambda rid, params, grammar, ids: seen.append((rid, params, grammar, ids)))
+
+    t = threading.Thread(target=follow)
+    t.start()
+    leader.wait_for_followers()
+    sched = rt.Scheduler(_engine(), rt.SchedulerConfig())
+    leader.configure("r1", {"temperature": 0.7, "seed": 3}, ["json", "{}"], [5, 6, 7])
+    leader.submit(sched, "r1", [5, 6, 7], 3)
+    while not sched.idle():
+        leader.tick(sched)
+    leader.shutdown()
+    t.join(10)
+    assert out["rc"] == 0
+    assert seen == [("r1", {"seed": 3, "temperature": 0.7}, ["json", "{}"], [5, 6, 7])]
