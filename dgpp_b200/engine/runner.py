@@ -67,7 +67,11 @@ class DenseRunner:
         self.qkv_cols = (self.hq + 2 * self.hkv) * d
         H, I = c.hidden, model.layers[0].down.k       # local intermediate width (padded to the GEMM's K granule)
         R = max_rows
-        e = lambda *s: torch.empty(*s, dtype=BF, device=dev)
+        # every activation buffer is a view into the runner's arena (no allocation after construction; the report()
+        # of the arena is the runner's activation footprint)
+        from ..utils.arena import Arena
+        self.arena = Arena(dev, slab_bytes=32 << 20)
+        e = lambda *s: self.arena.alloc(s, BF, "device_hot")
         self.x, self.xn, self.delta = e(R, H), e(R, H), e(R, H)
         self.qkv, self.attn = e(R, self.qkv_cols), e(R, self.hq * d)
         self.gu, self.act = e(R, 2 * I), e(R, I)
