@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "rt/json.h"
+#include "rt/string_constraint.h"
 
 namespace dgpp {
 namespace grammar {
@@ -36,6 +37,7 @@ struct SchemaNode {
   int items = -1;                                         // node index or -1: any
   int64_t min_items = 0, max_items = -1;
   std::vector<std::string> literals;                      // enum / const, serialised JSON texts
+  int str = -1;                                           // index of the string-body constraint (lengths, pattern, format)
 };
 
 class Schema {
@@ -55,6 +57,7 @@ class Schema {
     return s;
   }
   const SchemaNode& node(int i) const { return nodes_[i]; }
+  const StringConstraint& str(int i) const { return strs_[i]; }
   int root() const { return root_; }
 
  private:
@@ -65,7 +68,7 @@ class Schema {
       return 0;
     }
     if (!v.is_object()) throw std::runtime_error("json_schema: a schema must be an object");
-    for (const char* bad : {"anyOf", "oneOf", "allOf", "not", "$ref", "pattern", "patternProperties", "if"})
+    for (const char* bad : {"anyOf", "oneOf", "allOf", "not", "$ref", "patternProperties", "if"})
       if (v.has(bad)) throw std::runtime_error(std::string("json_schema: keyword '") + bad + "' is not supported");
     SchemaNode n;
     if (const json::Value* t = v.find("type")) {
@@ -93,6 +96,20 @@ class Schema {
       for (const auto& x : e->items()) n.literals.push_back(x.dump());
     }
     if (const json::Value* c = v.find("const")) n.literals.push_back(c->dump());
+    if (n.literals.empty() && (n.types & kString) && (v.has("pattern") || v.has("minLength") || v.has("maxLength") || v.has("format"))) {
+      std::string pat = v.get_string("pattern");
+      if (pat.empty()) pat = StringConstraint::format_pattern(v.get_string("format"));   // unknown formats are annotations
+      const int64_t lo = v.get_int("minLength", 0), hi = v.get_int("maxLength", -1);
+      if (hi >= 0 && hi < lo) throw std::runtime_error("json_schema: maxLength below minLength");
+      if (!pat.empty() || lo > 0 || hi >= 0) {
+        try {
+          strs_.push_back(StringConstraint::compile(pat, lo, hi));
+        } catch (const std::runtime_error& e) {
+          throw std::runtime_error(std::string("json_schema: ") + e.what());
+        }
+        n.str = static_cast<int>(strs_.size()) - 1;
+      }
+    }
     const int idx = static_cast<int>(nodes_.size());
     nodes_.push_back(n);
     if (const json::Value* p = v.find("properties")) {
@@ -119,6 +136,7 @@ class Schema {
     return idx;
   }
   std::vector<SchemaNode> nodes_;
+  std::vector<StringConstraint> strs_;
   int root_ = 0;
 };
 
@@ -259,7 +277,11 @@ class Machine {
     const int t = n.types;
     if (c == '{' && (t & kObject)) { f.kind = Frame::ObjFirst; f.text.clear(); return true; }
     if (c == '[' && (t & kArray)) { f.kind = Frame::ArrFirst; f.count = 0; return true; }
-    if (c == '"' && (t & kString)) { f.kind = Frame::Str; f.sub = 0; f.is_key = false; return true; }
+    if (c == '"' && (t & kString)) {
+      f.kind = Frame::Str; f.sub = 0; f.is_key = false; f.count = 0;
+      f.text = n.str >= 0 ? schema_->str(n.str).initial() : std::string();
+      return true;
+    }
     if ((c == '-' || (c >= '0' && c <= '9')) && (t & (kNumber | kInteger))) {
       f.kind = Frame::Num;
       f.count = 0;
@@ -270,13 +292,31 @@ class Machine {
     if (c == 'n' && (t & kNull)) { f.kind = Frame::Lit; f.count = 2; f.sub = 1; return true; }
     return false;
   }
+  // One decoded character byte of a constrained string value: length limits (in code points) and the pattern NFA.
+  bool body_byte(Frame& f, const StringConstraint& sc, unsigned char c) {
+    if ((c & 0xC0) != 0x80) {
+      if (sc.max_len >= 0 && f.count + 1 > sc.max_len) return false;
+      ++f.count;
+    }
+    return sc.step(f.text, c);
+  }
   bool in_string(unsigned char c) {
     Frame& f = stack_.back();
+    const int sci = f.is_key ? -1 : schema_->node(f.node).str;
     if (f.sub == 1) {                                       // after a backslash
-      if (c == 'u') { f.sub = 5; return !f.is_key || key_free(); }
+      if (c == 'u') {
+        if (sci >= 0) return false;                         // constrained bodies take the character itself
+        f.sub = 5;
+        return !f.is_key || key_free();
+      }
       static const std::string esc = "\"\\/bfnrt";
-      if (esc.find(static_cast<char>(c)) == std::string::npos) return false;
+      const size_t which = esc.find(static_cast<char>(c));
+      if (which == std::string::npos) return false;
       f.sub = 0;
+      if (sci >= 0) {
+        static const char decoded[] = {'"', '\\', '/', '\b', '\f', '\n', '\r', '\t'};
+        return body_byte(f, schema_->str(sci), static_cast<unsigned char>(decoded[which]));
+      }
       return !f.is_key || key_free();                       // escaped keys only where any key is allowed
     }
     if (f.sub >= 2) {                                       // hex digits of \uXXXX
@@ -285,7 +325,20 @@ class Machine {
       f.sub = f.sub == 2 ? 0 : f.sub - 1;
       return true;
     }
-    if (c == '\\') { f.sub = 1; return true; }
+    if (c == '\\') {
+      if (sci >= 0) {
+        // a backslash is viable only if one of the escapes it can start is
+        const StringConstraint& sc = schema_->str(sci);
+        bool any = false;
+        for (unsigned char d : {'"', '\\', '/', '\b', '\f', '\n', '\r', '\t'}) {
+          Frame trial = f;
+          if (body_byte(trial, sc, d)) { any = true; break; }
+        }
+        if (!any) return false;
+      }
+      f.sub = 1;
+      return true;
+    }
     if (c < 0x20) return false;
     if (c == '"') {
       if (f.is_key) {
@@ -298,6 +351,10 @@ class Machine {
         obj.kind = Frame::ObjColon;
         return true;
       }
+      if (sci >= 0) {
+        const StringConstraint& sc = schema_->str(sci);
+        if (f.count < sc.min_len || !sc.accepting(f.text)) return false;
+      }
       stack_.pop_back();
       value_done();
       return true;
@@ -306,6 +363,7 @@ class Machine {
       f.text.push_back(static_cast<char>(c));
       return key_allowed(stack_[stack_.size() - 2], f.text, /*complete=*/false);
     }
+    if (sci >= 0) return body_byte(f, schema_->str(sci), c);
     return true;
   }
   bool key_free() const { return schema_->node(stack_[stack_.size() - 2].node).additional; }

@@ -81,3 +81,59 @@ def test_token_masks_drive_a_valid_generation():
     # masks are cached per state: same object state -> identical mask
     g3 = rt.JsonGrammar("", vocab, [eos])
     assert np.array_equal(g3.mask(), g3.mask())
+
+
+def _chk(schema, text):
+    return rt.json_machine_check(json.dumps(schema), text.encode())
+
+
+def test_string_lengths_patterns_and_formats():
+    s = {"type": "string", "minLength": 2, "maxLength": 4}
+    assert _chk(s, '"ab"') == (True, True) and _chk(s, '"a"') == (False, False) and _chk(s, '"abcd"') == (True, True)
+    assert _chk(s, '"abcde') == (False, False) and _chk(s, '"a') == (True, False)
+    assert _chk(s, '"héé"') == (True, True) and _chk(s, '"ééééé') == (False, False)      # code points, not bytes
+    # anchored pattern: prefix viability is exact
+    p = {"type": "string", "pattern": "^[A-Z]{2}-\\d{3}(x|yz)?$"}
+    assert _chk(p, '"AB-123"') == (True, True) and _chk(p, '"AB-123yz"') == (True, True)
+    assert _chk(p, '"AB-12') == (True, False) and _chk(p, '"AB-12"') == (False, False)
+    assert _chk(p, '"Ab') == (False, False) and _chk(p, '"AB-123y"') == (False, False) and _chk(p, '"AB-123yzz') == (False, False)
+    # unanchored pattern matches anywhere
+    u = {"type": "string", "pattern": "ca+t"}
+    assert _chk(u, '"a caaat!"') == (True, True) and _chk(u, '"dog"') == (False, False) and _chk(u, '"dog') == (True, False)
+    # escapes are decoded before the pattern sees them; \\u is not accepted in a constrained body
+    q = {"type": "string", "pattern": '^a"b\\nc$'}                     # regex: a " b newline c
+    body = '"a' + chr(92) + '"b' + chr(92) + 'nc"'                    # JSON text: "a\"b\nc"
+    assert _chk(q, body) == (True, True) and _chk(q, '"a"') == (False, False)
+    assert _chk({"type": "string", "maxLength": 3}, '"' + chr(92) + 'u0041"') == (False, False)
+    # formats
+    assert _chk({"type": "string", "format": "date"}, '"2026-11-25"') == (True, True)
+    assert _chk({"type": "string", "format": "date"}, '"2026/') == (False, False)
+    assert _chk({"type": "string", "format": "uuid"}, '"123e4567-e89b-12d3-a456-426614174000"') == (True, True)
+    assert _chk({"type": "string", "format": "date-time"}, '"2026-11-25T10:20:30.5+01:00"') == (True, True)
+    assert _chk({"type": "string", "format": "hostname"}, '"anything"') == (True, True)          # unknown: annotation
+    # inside an object, other properties are unaffected
+    o = {"type": "object", "properties": {"id": {"type": "string", "pattern": "^\\d+$"}, "n": {"type": "string"}},
+         "required": ["id"], "additionalProperties": False}
+    assert _chk(o, '{"id": "42", "n": "free text"}') == (True, True) and _chk(o, '{"id": "4x') == (False, False)
+    # outside the subset -> schema error at compile time
+    for bad in ("(?=x)", "a{2,1}", "(", chr(92) + "1", "*a"):
+        with pytest.raises(RuntimeError):
+            rt.json_machine_check(json.dumps({"type": "string", "pattern": bad}), b'"')
+
+
+def test_token_masks_follow_the_pattern():
+    vocab = [bytes([i]) for i in range(256)] + [b"12", b"ab", b'"}', b""]
+    eos = len(vocab) - 1
+    schema = {"type": "object", "properties": {"zip": {"type": "string", "pattern": "^\\d{5}$"}}, "required": ["zip"],
+              "additionalProperties": False}
+    g = rt.JsonGrammar(json.dumps(schema), vocab, [eos])
+    for b in b'{"zip": "12':
+        assert g.accept(b)
+    m = np.asarray(g.mask())
+    allowed = {i for i in range(len(vocab)) if m[i >> 5] >> (i & 31) & 1}
+    assert allowed == {ord(c) for c in "0123456789"} | {256}            # digits and the token "12"; not "ab", not '"'
+    for b in b"345":
+        assert g.accept(b)
+    m = np.asarray(g.mask())
+    allowed = {i for i in range(len(vocab)) if m[i >> 5] >> (i & 31) & 1}
+    assert allowed == {ord('"'), 258}                                   # five digits written: only the closing quote
