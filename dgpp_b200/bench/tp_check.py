@@ -129,6 +129,27 @@ def main() -> int:
         print("tokens identical across ranks:", all(o == objs[0] for o in objs), flush=True)
         print("unfused run1 == run2:", runs[0] == runs[2], " fused run1 == run2:", runs[1] == runs[3], " fused == unfused:", runs[0] == runs[1], flush=True)
         for i, r in enumerate(runs): print("  run", i, "fused" if i % 2 else "unfused", r[0], flush=True)
+    # scheduler + kernel engine on every rank: the same prompt three times (prefix cache off, then on) must give the
+    # same tokens every time on every rank (the cached runs attach shared KV blocks and prefill only the tail)
+    from dgpp_b200.engine.adapters import KernelEngine
+    from dgpp_b200.runtime import rt
+    for prefix in (False, True):
+        keng = KernelEngine(LLMEngine(model, max_batch=4, max_seq_len=1024, prefill_chunk=256, reducer=red))
+        sc = rt.SchedulerConfig(); sc.prefix_cache = prefix; sc.prefix_min_tokens = 16
+        sched = rt.Scheduler(keng, sc)
+        outs = []
+        for rid in ("a", "b", "c"):
+            sched.submit(rid, list(range(100, 400)), 12)
+            sched.run(100000)
+            outs.append([a for kind, r, a, b in sched.events() if kind == "token"])
+        ops.check_status()
+        allo = [None] * world; dist.all_gather_object(allo, outs)
+        if rank == 0:
+            print(f"scheduler prefix_cache={prefix}: runs equal={outs[0] == outs[1] == outs[2]} ranks equal={all(o == allo[0] for o in allo)} "
+                  f"hit tokens={sched.meters()['prefix_hit_tokens']}", flush=True)
+            if not (outs[0] == outs[1] == outs[2]):
+                for o in outs: print("   ", o, flush=True)
+        del sched, keng
     dist.barrier(); red.close(); dist.destroy_process_group()
 
     return 0

@@ -63,6 +63,7 @@ class LLMEngine:
         self.h_step_out = torch.zeros(max_batch, dtype=torch.int32).pin_memory() if self.dev.type == "cuda" else None
         self.h_step_in = torch.zeros(max_batch, dtype=torch.int32).pin_memory() if self.dev.type == "cuda" else None
         self.graphs = {}
+        self._h2d_done = None
         self.lengths = [0] * max_batch
         self.kernel_launches = 0
 
@@ -81,8 +82,14 @@ class LLMEngine:
         while done < n:
             t = min(self.prefill_chunk, n - done)
             if self.h_tokens is not None:
+                # the pinned staging buffer is reused by every chunk: wait until the previous chunk's copy has left it
+                if self._h2d_done is not None:
+                    self._h2d_done.synchronize()
                 self.h_tokens[:t].copy_(host[done:done + t])
                 self.p_tokens[:t].copy_(self.h_tokens[:t], non_blocking=True)
+                if self._h2d_done is None:
+                    self._h2d_done = torch.cuda.Event()
+                self._h2d_done.record()
             else:
                 self.p_tokens[:t].copy_(host[done:done + t])
             torch.arange(start_pos + done, start_pos + done + t, dtype=torch.int32, device=self.dev,

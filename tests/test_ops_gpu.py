@@ -315,3 +315,31 @@ def test_speculative_lookup_decode_equals_plain_greedy(dev):
     # fewer decode passes than tokens when drafts land (a random-init model repeats itself often enough after a
     # repetitive prompt; the equality above is the contract, this only checks that the path is live)
     assert m1["decode_passes"] <= m0["decode_passes"]
+
+
+@pytest.mark.parametrize("plen", [300, 77])
+def test_prefix_cache_hit_reproduces_the_uncached_tokens(dev, plen):
+    """The same prompt twice through scheduler + kernel engine: the second run attaches the cached KV blocks, prefills
+    only the tail, and emits exactly the first run's tokens."""
+    from dgpp_b200.engine.adapters import KernelEngine
+    from dgpp_b200.engine.llm_engine import LLMEngine
+    from dgpp_b200.models.dense import DenseConfig, DenseModel
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.runtime import rt
+
+    cfg = DenseConfig.tiny(hidden=512, q_heads=8, kv_heads=8, head_dim=128, ffn=2048, vocab=4096, layers=2)
+    model = DenseModel.random_init(cfg, device=dev, seed=0, std=0.05)
+    eng = KernelEngine(LLMEngine(model, max_batch=4, max_seq_len=1024, prefill_chunk=256))
+    sc = rt.SchedulerConfig()
+    sc.prefix_min_tokens = 16
+    s = rt.Scheduler(eng, sc)
+    prompt = list(range(100, 100 + plen))
+    outs = []
+    for rid in ("a", "b", "c"):
+        s.submit(rid, prompt, 12)
+        s.run(100000)
+        outs.append([a for kind, r, a, b in s.events() if kind == "token"])
+    ops.check_status()
+    m = s.meters()
+    assert m["prefix_hit_tokens"] >= 2 * (plen // 64) * 64
+    assert outs[1] == outs[0] and outs[2] == outs[0], outs
