@@ -2,9 +2,10 @@
 //
 // A decode batch has only a handful of rows, so one CTA per row leaves the GPU idle; here the K columns of a row
 // are split over the CTAs of a cluster (up to 8), and the two row-wide reductions (sum of squares for RMSNorm,
-// max |x| for the activation scale) go through distributed shared memory: every CTA publishes its partial in
-// its own shared memory, the cluster synchronises, and every CTA folds the partials in ascending CTA order
-// (so all CTAs compute bit-identical row statistics).
+// max |x| for the activation scale) go through distributed shared memory: every CTA stores its partial into the
+// shared memory of every CTA of the cluster, the cluster synchronises, and every CTA folds its own copy of the
+// partials in ascending CTA order (so all CTAs compute bit-identical row statistics, and nobody reads a peer's
+// shared memory after the barrier).
 //
 // Modes, output layout and arithmetic are those of fused_act_quant_kernel in gemm_fp4.cu:
 //   0 plain rows, 1 swiglu([gate | up]), 2 rmsnorm(resid + delta) * w
@@ -64,7 +65,10 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* seg = reinterpret_cast<bf16*>(smem_raw);  // this CTA's K / cl columns
   __shared__ float wred[kAqThreads / 32];
-  __shared__ float part[2];                       // [0] sum of squares, [1] max |x| of this CTA's segment
+  // partials of every CTA of the cluster, PUSHED here by their owners before the cluster barrier: [0][i] sum of
+  // squares, [1][i] max |x| of CTA i's segment.  After the barrier a CTA reads only its own copy, so no CTA's shared
+  // memory is touched by a peer once the barrier has passed and no closing barrier is needed.
+  __shared__ float part[2][8];
   cg::cluster_group cluster = cg::this_cluster();
   pdl_wait();
   const int c = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
@@ -79,13 +83,12 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
     __syncthreads();
     return r;
   };
+  auto cluster_push = [&](int slot, float v) {
+    if (tid < cl) *cluster.map_shared_rank(&part[slot][c], tid) = v;
+  };
   auto cluster_fold = [&](int slot, bool is_max) {
-    float r = is_max ? 0.f : 0.f;
-    for (int i = 0; i < cl; ++i) {
-      const float* remote = cluster.map_shared_rank(part, i);
-      const float v = remote[slot];
-      r = is_max ? fmaxf(r, v) : r + v;
-    }
+    float r = 0.f;
+    for (int i = 0; i < cl; ++i) r = is_max ? fmaxf(r, part[slot][i]) : r + part[slot][i];
     return r;
   };
   float amax = 0.f;
@@ -136,7 +139,7 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
       reinterpret_cast<uint4*>(seg)[i] = x.u;
     }
     ss = cta_reduce(ss, false);
-    if (tid == 0) part[0] = ss;
+    cluster_push(0, ss);
     cluster.sync();
     const float rstd = rsqrtf(cluster_fold(0, false) / static_cast<float>(K) + a.eps);
     for (int i = tid; i < nvec; i += kAqThreads) {
@@ -177,7 +180,7 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
     }
   }
   amax = cta_reduce(amax, true);
-  if (tid == 0) part[1] = amax;
+  cluster_push(1, amax);
   cluster.sync();
   amax = cluster_fold(1, true);
   const float gs = amax > 0.f ? amax / (6.f * 256.f) : 1.f;
@@ -218,7 +221,6 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
       a.sf[atom_idx * kAqAtom + (mm & 31) * 16 + (mm >> 5) * 4 + fi] = sb;
     }
   }
-  cluster.sync();  // keep every CTA's shared memory alive until all remote reads are done
   if (MODE == 2 && a.fold && tid == 0) {
     __threadfence();
     if (atomicAdd(a.comm.done_ctas, 1u) == gridDim.x * gridDim.y - 1) {
