@@ -42,7 +42,9 @@ class LLMEngine:
         self.kv = PagedKV(c.layers, model.hkv_local, c.head_dim, kv_blocks, max_batch, max_blocks_per_req, page,
                           c.kv_fp8, self.dev)
         rows = max(prefill_chunk, max_batch)
-        splits = max(1, min(16, round(296 / max(1, model.hkv_local * max_batch))))
+        # split-KV decode attention: one wave of CTAs (two resident per SM) is the sweet spot -- measured at 8 rows x 8 kv
+        # heads: 13.6 us with 4 splits at ctx 2048 (17.6 us with 8), 33 us with 4 at ctx 8192 (49 us with 16)
+        splits = max(1, min(16, 296 // max(1, model.hkv_local * max_batch)))
         self.decode_pdl = decode_pdl
         self.runner = DenseRunner(model, self.kv, rows, reducer=reducer, decode_splits=splits, decode_rows=max_batch,
                                   act_terms=act_terms, fuse_ar=fuse_ar)
