@@ -261,6 +261,21 @@ __device__ __forceinline__ uint4 ld_v4_global_volatile(const void* p) {
 }
 
 // Programmatic dependent launch: let the next kernel's prologue start / wait for the previous grid.
+// ---- thread-block clusters: barrier over all threads of all CTAs, distributed shared memory stores
+__device__ __forceinline__ void cluster_barrier() {
+  __syncwarp();   // the .aligned forms want the whole warp at the instruction (callers come out of elected-lane code)
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Shared-memory address of `addr` (a shared::cta address of this CTA's window) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
 // Ask L2 to fetch [p, p + bytes) (16-byte aligned, bytes % 16 == 0); returns at once, completion is not observable.
 __device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");

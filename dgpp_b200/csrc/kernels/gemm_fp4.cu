@@ -72,6 +72,11 @@ struct Fp4Params {
   // (quantiser, RoPE, attention over a short context) leave HBM idle; the prefetch fills that time.  A hint only.
   const unsigned char* pf_ptr;
   int64_t pf_bytes;
+  // Split-K inside a thread-block cluster (decode projections with few output tiles): the gridDim.z CTAs of one output
+  // tile form a cluster (1, 1, splits); each runs its share of the K stages, then the partial accumulators of ranks
+  // 1.. travel through distributed shared memory into rank 0's (by then idle) operand ring and rank 0 adds them in
+  // ascending rank order.  No workspace, no global counters; two cluster barriers.
+  int cluster_split;
 };
 
 // One bf16 of the finished output tile -> slot `rank` of every rank (destinations staggered by rank).
@@ -170,6 +175,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   const size_t sfb_grp = p.group_b ? static_cast<size_t>(grp) * (p.T_pad / bn_tok) * total_stages * kSfbBytes : 0;
   const float* gvec = p.g + (p.group_b ? grp * p.T_pad : 0);
 
+  bool acc_ok = true;      // epilogue warps: the accumulator completed within the wait bound
   if (warp == 0) {
     // ------------------------------------------------------------------ producer: weights, activations, scales
     if (elect_one()) {
@@ -236,11 +242,91 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
       umma_commit(acc_full);
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int q = warp & 3;
-    const bool ok = nst > 0 ? wait_bar(acc_full, 0) : true;
-    if (!ok) { report(p.status, kTimeoutAccum, 15); *abort_flag = 1; }
+    // ------------------------------------------------------------------ epilogue (warps 2..5): wait for the accumulator
+    acc_ok = nst > 0 ? wait_bar(acc_full, 0) : true;
+    if (!acc_ok) { report(p.status, kTimeoutAccum, 15); *abort_flag = 1; }
+    acc_ok = __all_sync(0xffffffffu, acc_ok);            // the TMEM loads below stay warp-uniform
     tc_fence_after();
+  }
+  if (p.cluster_split) {
+    // Every thread of every CTA of the cluster passes the same two barriers, whatever happened before (a CTA that
+    // gave up on a wait still arrives), so the cluster cannot block on a peer.
+    const int q = warp & 3;
+    const int cols = min(bn_tok, p.T - m0);
+    float* red = reinterpret_cast<float*>(sA);          // rank 0: [splits - 1][bn_tok][128] partials of the peers
+    cluster_barrier();                                   // every CTA's mainloop is over: rank 0's operand ring is idle
+    if (warp >= 2 && split > 0 && acc_ok && !*abort_flag) {
+      for (int c0 = 0; c0 < bn_tok; c0 += 16) {
+        if (c0 >= cols) break;
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        if (nst > 0) {
+          for (int r = 0; r < p.R; ++r) {
+            uint32_t rr[16];
+            tmem_ld_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + r * bn_tok + c0, rr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(rr[j]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = c0 + j;
+          if (m < cols)
+            st_shared_cluster_f32(mapa_shared(smem_u32(red + (static_cast<size_t>(split - 1) * bn_tok + m) * kF4BM + q * 32 + lane), 0u),
+                                  v[j]);
+        }
+      }
+    }
+    cluster_barrier();                                   // the partials have landed in rank 0
+    if (warp >= 2 && split == 0) {
+      const int n = n0 + q * 32 + lane;
+      const uint32_t push_epoch = p.push ? *p.comm.epoch + 1 : 0u;
+      const int push_parity = push_epoch & 1;
+      if (acc_ok && !*abort_flag) {
+        for (int c0 = 0; c0 < bn_tok; c0 += 16) {
+          if (c0 >= cols) break;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          if (nst > 0) {
+            for (int r = 0; r < p.R; ++r) {
+              uint32_t rr[16];
+              tmem_ld_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + r * bn_tok + c0, rr);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(rr[j]);
+            }
+          }
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = c0 + j;
+              if (m < cols) {
+                float acc = v[j];
+                for (int s2 = 1; s2 < splits; ++s2) acc += red[(static_cast<size_t>(s2 - 1) * bn_tok + m) * kF4BM + q * 32 + lane];
+                const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
+                float y = acc * alpha * gvec[m0 + m];
+                if (p.push) {
+                  push_value(p, push_parity, static_cast<size_t>(m0 + m) * p.N + n, f32_to_bf16(y));
+                  continue;
+                }
+                if (p.out32) p.out32[o] = y;
+                if (p.out) {
+                  if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
+                  p.out[o] = f32_to_bf16(y);
+                }
+              }
+            }
+          }
+        }
+      }
+      if (p.push) push_flags(p, push_parity, push_epoch, warp, lane);
+    }
+  } else if (warp >= 2) {
+    const int q = warp & 3;
+    const bool ok = acc_ok;
     // n: output column (within the expert in grouped mode); n_ws: column in the split-K workspace
     const int n = (p.group_list ? (blockIdx.x % p.group_tiles) * kF4BM : n0) + q * 32 + lane;
     const int n_ws = blockIdx.x * kF4BM + q * 32 + lane, N_ws = p.group_list ? gridDim.x * kF4BM : p.N;
@@ -323,6 +409,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
         if (p.push) push_flags(p, push_parity, push_epoch, warp, lane);
       }
     }
+  
   }
   tc_fence_before();
   __syncthreads();
@@ -501,6 +588,25 @@ static int launch_fp4(const CUtensorMap& tA, const CUtensorMap& tB, const Fp4Par
   }
   const int bn_tok = BN / p.R;
   dim3 grid(p.grid_x > 0 ? p.grid_x : dgpp_ceil_div(p.N, kF4BM), dgpp_ceil_div(p.T, bn_tok), splits);
+  if (p.cluster_split) {
+    DGPP_REQUIRE(splits >= 2 && splits <= 8, "gemm_fp4: cluster split-K takes 2..8 splits, got %d", splits);
+    DGPP_REQUIRE(static_cast<size_t>(splits - 1) * bn_tok * kF4BM * 4 <= static_cast<size_t>(C::S) * kF4StageA,
+                 "gemm_fp4: %d splits x %d tokens do not fit the operand ring for the cluster fold", splits, bn_tok);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kF4Threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = static_cast<unsigned>(splits);
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    DGPP_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tA, tB, p));
+    return 0;
+  }
   kern<<<grid, kF4Threads, smem, st>>>(tA, tB, p);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
@@ -601,6 +707,9 @@ DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* 
   const int per = dgpp_ceil_div(stages, splits);
   p.stages_per_split = per;
   splits = dgpp_ceil_div(stages, per);
+  // split-K without a workspace = the cluster form (partials through distributed shared memory)
+  p.cluster_split = (splits > 1 && ws == nullptr) ? 1 : 0;
+  DGPP_REQUIRE(splits == 1 || p.cluster_split || counters != nullptr, "gemm_fp4: split-K needs workspace and counters");
   CUtensorMap tA, tB;
   if (make_tmap_2d(&tA, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, K / 2, 128, kF4BM, CU_TENSOR_MAP_SWIZZLE_128B))
     return -1;
@@ -660,6 +769,7 @@ DGPP_API int dgpp_gemm_fp4_grouped(int bn, const void* xq, const void* xsf, cons
   p.group_tiles = N / 128;
   p.group_b = group_b;
   p.grid_x = slots * p.group_tiles;
+  p.cluster_split = 0;
   p.group_out_stride = group_out_stride;
   const int stages = K / 256;
   const int per = dgpp_ceil_div(stages, splits);

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -225,8 +226,11 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
 def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
              out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
              splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, push_comm=None,
-             prefetch: Optional[QuantLinear] = None) -> torch.Tensor:
+             prefetch: Optional[QuantLinear] = None, cluster: Optional[bool] = None) -> torch.Tensor:
     """Block-scaled NVFP4 tensor-core linear on pre-quantised activations (token tile = xa.bn).
+    splits > 1: split K.  cluster (default: on): the CTAs of one output tile form a thread-block cluster and fold
+    their partial accumulators through distributed shared memory (no workspace); off: partials go through a global
+    workspace and the last CTA of a tile folds them.
     prefetch: the projection that runs next; its packed weights are requested into L2 by this kernel's CTAs once
     their own loads are issued (fills the HBM-idle time of the small kernels in between; a hint, never needed).
     push_comm: native peer-communicator handle; the finished bf16 tiles are then stored into every rank's
@@ -237,10 +241,13 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
     if out is None and out32 is None and not push_comm:
         out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=dev)
     ldc = w.n if push_comm and out is None and out32 is None else (out if out is not None else out32).stride(0)
+    if cluster is None:
+        cluster = CLUSTER_SPLITK
     if splits is None:
-        splits = pick_splits_fp4(rows, w.n, w.k, bn)
+        splits = pick_cluster_splits(rows, w.n, w.k, bn) if cluster else pick_splits_fp4(rows, w.n, w.k, bn)
+    cluster = cluster and 2 <= splits <= 8 and (splits - 1) * bn * 512 <= 65536
     wsp = cnt = None
-    if splits > 1:
+    if splits > 1 and not cluster:
         ws = ws or default_workspace(dev)
         if splits * rows * w.n > ws.partials.numel():
             splits = 1
@@ -252,6 +259,25 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
          ptr(w.tiled_scales()), float(w.alpha), ptr(out), ptr(out32), ptr(resid), ldc, rows, w.n, w.k, splits,
          ptr(wsp), ptr(cnt), push_comm, stream_ptr())
     return out if out is not None else out32
+
+
+# DGPP_CLUSTER_SPLITK=0 falls back to the workspace split-K policy (A/B measurements)
+CLUSTER_SPLITK = os.environ.get("DGPP_CLUSTER_SPLITK", "1") != "0"
+
+
+def pick_cluster_splits(rows: int, n: int, k: int, bn: int) -> int:
+    """Cluster split-K for projections with few output tiles (decode qkv / o / down): a CTA that walks 20+ K stages
+    alone is bound by the latency of its own scale-copy -> MMA -> commit chain, not by bandwidth; splitting K over the
+    CTAs of a cluster shortens the chain and puts two CTAs on every SM.  At least 4 stages per CTA, at most 8 CTAs, and
+    about two resident CTAs per SM in total."""
+    tiles = math.ceil(n / 128) * math.ceil(rows / bn)
+    stages = k // 256
+    if rows > 64 or tiles > 74 or stages < 8:
+        return 1
+    s = min(8, max(1, 296 // tiles), stages // 4)
+    while s > 1 and (s - 1) * bn * 512 > 65536:
+        s -= 1
+    return max(1, s)
 
 
 def pick_splits_fp4(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:

@@ -31,7 +31,9 @@ def test_act_quant_residual_terms_round_trip(dev, terms, tol):
 
 @pytest.mark.parametrize("rows,bn,terms,splits,n,k", [(4, 16, 1, 1, 384, 1024), (4, 16, 3, 1, 384, 1024), (8, 16, 3, 2, 448, 2048),
                                                        (40, 64, 3, 1, 256, 1024), (100, 128, 1, 1, 256, 1024),
-                                                       (300, 256, 1, 1, 384, 1024), (30, 32, 2, 2, 256, 2048)])
+                                                       (300, 256, 1, 1, 384, 1024), (30, 32, 2, 2, 256, 2048),
+                                                       (8, 16, 3, 5, 640, 5120), (1, 16, 3, 7, 256, 17408),
+                                                       (13, 16, 3, 8, 128, 4096)])
 def test_gemm_fp4_matches_fp32_reference(dev, rows, bn, terms, splits, n, k):
     from dgpp_b200.ops import core as ops, reference as ref
     from dgpp_b200.quant.formats import quantize
@@ -43,6 +45,14 @@ def test_gemm_fp4_matches_fp32_reference(dev, rows, bn, terms, splits, n, k):
     y = ops.gemm_fp4(xa, w, splits=splits)
     torch.cuda.synchronize()
     ops.check_status()
+    if splits > 1:
+        # both split-K forms (cluster fold through distributed shared memory, workspace fold by the last CTA) add
+        # the same partials in the same order: identical bits, and repeatable
+        y_ws = ops.gemm_fp4(xa, w, splits=splits, cluster=False)
+        y_cl = ops.gemm_fp4(xa, w, splits=splits, cluster=True)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert torch.equal(y_cl, y) and torch.equal(y_ws, y_cl)
     # against the product of the operands the kernel actually saw (exact up to fp32 order + one bf16 rounding)
     yq = xa.dequant() @ w.dequant().t()
     assert (y.float() - yq).abs().max().item() <= 1e-2 * yq.abs().max().item()
