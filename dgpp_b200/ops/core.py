@@ -261,23 +261,24 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
     return out if out is not None else out32
 
 
-# DGPP_CLUSTER_SPLITK=0 falls back to the workspace split-K policy (A/B measurements)
-CLUSTER_SPLITK = os.environ.get("DGPP_CLUSTER_SPLITK", "1") != "0"
+# DGPP_CLUSTER_SPLITK=1 selects the cluster split-K policy (off until its launch path is validated)
+CLUSTER_SPLITK = os.environ.get("DGPP_CLUSTER_SPLITK", "0") == "1"
 
 
 def pick_cluster_splits(rows: int, n: int, k: int, bn: int) -> int:
     """Cluster split-K for projections with few output tiles (decode qkv / o / down): a CTA that walks 20+ K stages
     alone is bound by the latency of its own scale-copy -> MMA -> commit chain, not by bandwidth; splitting K over the
-    CTAs of a cluster shortens the chain and puts two CTAs on every SM.  At least 4 stages per CTA, at most 8 CTAs, and
-    about two resident CTAs per SM in total."""
+    CTAs of a cluster shortens the chain and puts two CTAs on every SM.  At least 4 stages per CTA, cluster sizes 2 / 4 /
+    8, and two to three resident CTAs per SM in total."""
     tiles = math.ceil(n / 128) * math.ceil(rows / bn)
     stages = k // 256
     if rows > 64 or tiles > 74 or stages < 8:
         return 1
-    s = min(8, max(1, 296 // tiles), stages // 4)
-    while s > 1 and (s - 1) * bn * 512 > 65536:
-        s -= 1
-    return max(1, s)
+    want = min(8, max(1, 444 // tiles), stages // 4)
+    s = 1
+    while s * 2 <= want and (s * 2 - 1) * bn * 512 <= 65536:      # cluster sizes 2 / 4 / 8
+        s *= 2
+    return s
 
 
 def pick_splits_fp4(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:
