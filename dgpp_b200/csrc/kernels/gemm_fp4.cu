@@ -674,7 +674,7 @@ DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* 
   DGPP_REQUIRE(K % 256 == 0, "gemm_fp4: K %d must be a multiple of 256", K);
   DGPP_REQUIRE(R >= 1 && R <= 4, "gemm_fp4: R %d outside 1..4", R);
   DGPP_REQUIRE(splits >= 1, "gemm_fp4: splits must be >= 1");
-  DGPP_REQUIRE(splits == 1 || (ws && counters), "gemm_fp4: split-K needs workspace and counters");
+  DGPP_REQUIRE(splits == 1 || (ws && counters) || (!ws && !counters), "gemm_fp4: split-K takes a workspace with counters, or neither (cluster form)");
   DGPP_REQUIRE(out || out32 || comm_push, "gemm_fp4: no output");
   DGPP_REQUIRE(T_pad >= T && T_pad % bn == 0, "gemm_fp4: T_pad %d must cover T and be a multiple of bn %d", T_pad, bn);
   Fp4Params p;
