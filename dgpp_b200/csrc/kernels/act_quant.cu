@@ -49,6 +49,12 @@ struct ClusterQuantArgs {
   // and rows t % bn >= group_rows are skipped.
   const int32_t* group_list;
   int group_rows;
+  // MODE 3: the row is the decode-attention output, folded here from the split-KV partials (max / sum pairs and
+  // unnormalised accumulators per (row, head, split)) in the arithmetic of the stand-alone combine kernel, so the
+  // combine launch and one round trip of the attention output disappear.
+  const float* part_ml;
+  const float* part_acc;
+  int splits, hq, D;
 };
 
 __device__ __forceinline__ float warp_red(float v, bool is_max) {
@@ -152,6 +158,33 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
         float gw = bf16_to_f32(ww.h[j]);
         if (a.one_plus_w) gw += 1.f;
         x.h[j] = f32_to_bf16(nrm * gw);
+        amax = fmaxf(amax, fabsf(bf16_to_f32(x.h[j])));
+      }
+      reinterpret_cast<uint4*>(seg)[i] = x.u;
+      if (a.x_out) reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(t) * K + k0)[i] = x.u;
+    }
+  } else if (MODE == 3) {
+    for (int i = tid; i < nvec; i += kAqThreads) {
+      const int col = k0 + i * 8, h = col / a.D, d0 = col % a.D;
+      const size_t rh = static_cast<size_t>(t) * a.hq + h;
+      float mm = -INFINITY;
+      for (int sp = 0; sp < a.splits; ++sp) mm = fmaxf(mm, a.part_ml[(rh * a.splits + sp) * 2]);
+      float ll = 0.f, acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int sp = 0; sp < a.splits; ++sp) {
+        const float ms = a.part_ml[(rh * a.splits + sp) * 2];
+        const float cw = ms == -INFINITY ? 0.f : __expf(ms - mm);
+        ll += a.part_ml[(rh * a.splits + sp) * 2 + 1] * cw;
+        const float4* pa = reinterpret_cast<const float4*>(a.part_acc + (rh * a.splits + sp) * a.D + d0);
+        const float4 p0 = pa[0], p1 = pa[1];
+        acc[0] += p0.x * cw; acc[1] += p0.y * cw; acc[2] += p0.z * cw; acc[3] += p0.w * cw;
+        acc[4] += p1.x * cw; acc[5] += p1.y * cw; acc[6] += p1.z * cw; acc[7] += p1.w * cw;
+      }
+      Pack16 x;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        x.h[j] = f32_to_bf16(ll > 0.f ? acc[j] / ll : 0.f);
         amax = fmaxf(amax, fabsf(bf16_to_f32(x.h[j])));
       }
       reinterpret_cast<uint4*>(seg)[i] = x.u;
@@ -298,4 +331,33 @@ DGPP_API int dgpp_act_quant_nvfp4_cluster(int mode, const void* in, int64_t in_s
   if (mode == 2) return launch_cluster<2>(a, st);
   dgpp_set_error("act_quant: unknown mode %d", mode);
   return -1;
+}
+
+// Decode attention epilogue: fold the split-KV partials of dgpp_attn_decode_tc / dgpp_attn_decode (called with a null
+// output) and quantise the rows for the o projection in one launch.  K = hq * d; x_out (optional) receives the bf16
+// attention output [T, K].
+DGPP_API int dgpp_attn_combine_quant(const void* part_ml, const void* part_acc, int splits, int hq, int d, void* x_out,
+                                     void* q, void* sf, void* g, int T, int T_pad, int R, int bn, int cl,
+                                     cudaStream_t st) {
+  const int K = hq * d;
+  DGPP_REQUIRE(part_ml && part_acc && splits >= 1, "attn_combine_quant: partials required");
+  DGPP_REQUIRE(K % 256 == 0 && d % 8 == 0, "attn_combine_quant: hq %d x d %d must give K %% 256 == 0", hq, d);
+  DGPP_REQUIRE(cl == 1 || cl == 2 || cl == 4 || cl == 8, "attn_combine_quant: cluster size %d not in {1,2,4,8}", cl);
+  DGPP_REQUIRE((K / cl) % 16 == 0 && K % cl == 0, "attn_combine_quant: K %d does not split over %d CTAs", K, cl);
+  DGPP_REQUIRE(R >= 1 && R <= 4 && R * bn <= 256, "attn_combine_quant: bad terms %d / tile %d", R, bn);
+  DGPP_REQUIRE(T_pad % bn == 0 && T_pad >= T, "attn_combine_quant: T_pad %d must be a multiple of bn %d and >= T", T_pad, bn);
+  DGPP_REQUIRE(static_cast<size_t>(K / cl) * 2 <= 48 * 1024, "attn_combine_quant: segment too large");
+  if (T == 0) return 0;
+  ClusterQuantArgs a;
+  memset(&a, 0, sizeof(a));
+  a.x_out = static_cast<bf16*>(x_out);
+  a.q = static_cast<uint8_t*>(q);
+  a.sf = static_cast<uint8_t*>(sf);
+  a.g = static_cast<float*>(g);
+  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.cl = cl; a.eps = 0.f; a.limit = 0.f;
+  a.status = device_status_ptr();
+  a.part_ml = static_cast<const float*>(part_ml);
+  a.part_acc = static_cast<const float*>(part_acc);
+  a.splits = splits; a.hq = hq; a.D = d;
+  return launch_cluster<3>(a, st);
 }

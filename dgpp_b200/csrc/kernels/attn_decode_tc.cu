@@ -403,7 +403,7 @@ static int launch_attn_tc(const CUtensorMap& tK, const CUtensorMap& tV, const At
   dim3 grid(p.hkv, p.splits, p.rows);
   attn_decode_tc_kernel<G><<<grid, kAdThreads, smem, st>>>(tK, tV, p);
   DGPP_CUDA_OK(cudaGetLastError());
-  if (p.splits > 1) {
+  if (p.splits > 1 && p.out != nullptr) {   // out == nullptr: the caller folds the partials itself (dgpp_attn_combine_quant)
     attn_tc_combine_kernel<<<p.rows * p.hq, 128, 0, st>>>(p.part_ml, p.part_acc, p.out, p.splits);
     DGPP_CUDA_OK(cudaGetLastError());
   }
@@ -425,6 +425,7 @@ DGPP_API int dgpp_attn_decode_tc(const void* q, int64_t q_stride, const void* k_
   DGPP_REQUIRE(hkv > 0 && hq % hkv == 0 && hq / hkv <= 8, "attn_decode_tc: unsupported head grouping %d/%d", hq, hkv);
   DGPP_REQUIRE(page == 16 || page == 32 || page == 64 || page == 128, "attn_decode_tc: page %d unsupported", page);
   DGPP_REQUIRE(splits >= 1 && (splits == 1 || (part_ml && part_acc)), "attn_decode_tc: scratch required for splits");
+  DGPP_REQUIRE(out != nullptr || splits > 1, "attn_decode_tc: an output buffer is required without splits");
   if (rows == 0) return 0;
   AttnTcParams p;
   p.q = static_cast<const bf16*>(q);

@@ -17,6 +17,12 @@
 //   4  MXFP8: e4m3 [N, K] + e8m0 scale per 32 [N, K/32]   bf16(e4m3 * 2^e) is exact
 //   5  int8 and 6 int4 (two per byte, low nibble first): offset-binary codes (code - 128 / code - 8) with one bf16
 //        scale per 64 [N, K/64]; converter warps write bf16(int * scale)
+//   7  BF12: a lossless 12-bit resident form of a bf16 matrix.  A weight's sign + mantissa byte is stored as is
+//        ([N, K] bytes); its exponent becomes a 4-bit code against a per-row base ([N, K/2] nibbles, low nibble =
+//        even column).  Code 15 escapes to a per-row, column-sorted side table holding the true bf16 bits (a few
+//        weights in ten thousand fall outside a window of 15 exponents).  TMA streams both planes as stored (0.75
+//        of the bf16 bytes), converter warps rebuild the exact bf16 bits in the MMA stage, so the result is bitwise
+//        the bf16 kernel's.
 //
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
 // warps 2..9 = converters (quantised modes), warps 2..5 = epilogue (TMEM -> registers -> global).
@@ -53,6 +59,9 @@ struct GemmParams {
   const float* blk_scale;  // WMODE 2: [ceil(N/128), K/128] fp32
   const uint8_t* sf_plain; // WMODE 3 / 4: e8m0 scales [N, K/32]
   const bf16* sf_bf16;     // WMODE 5 / 6: bf16 scales [N, K/64]
+  const uint8_t* bf12_base;   // WMODE 7: exponent window base per row [N]
+  const uint32_t* bf12_rows;  // WMODE 7: [N + 1] first escape of each row
+  const uint32_t* bf12_esc;   // WMODE 7: (column << 16) | bf16 bits, column-sorted within a row
   DeviceStatus* status;
   int T, N, K, ldc;
   int kb_per_split;        // k64 blocks per split
@@ -69,7 +78,18 @@ struct GemmSmem {
   static constexpr int kStageA = kBM * 128;                // 16 KB
   static constexpr int kStageRaw = kBM * 128;              // 16 KB packed fp4 (256 K per row) / fp8 (128 K per row)
   static constexpr int kStageSf = kBM * 16;                // 2 KB
+  static constexpr int kStageEx = kBM * 64;                // 8 KB exponent nibbles of 128 K per row (BF12)
 };
+
+// True bf16 bits of an escaped BF12 weight: binary search of the row's column-sorted side table.
+__device__ __forceinline__ uint32_t bf12_escape(const uint32_t* __restrict__ esc, uint32_t lo, uint32_t hi, uint32_t col) {
+  while (lo < hi) {
+    const uint32_t mid = (lo + hi) >> 1, v = __ldg(esc + mid), c = v >> 16;
+    if (c == col) return v & 0xFFFFu;
+    if (c < col) lo = mid + 1; else hi = mid;
+  }
+  return 0u;   // not listed (cannot happen for an encoder-produced matrix): a zero weight
+}
 
 // WMODE: 0 bf16, 1 nvfp4, 2 fp8 block, 3 mxfp4, 4 mxfp8 (e4m3 + e8m0 per 32), 5 int8 and 6 int4 (offset-binary codes,
 // bf16 scale per 64).  Byte-per-element sources (2, 4, 5) stage 128 K per raw row, nibble sources (1, 3, 6) 256 K.
@@ -89,7 +109,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
   unsigned char* sB = sp;                   sp += SB * L::kStageB;
   unsigned char* sA = sp;                   sp += (kQuant ? SA : SB) * L::kStageA;
   unsigned char* sRaw = sp;                 sp += kQuant ? SR * L::kStageRaw : 0;
-  unsigned char* sSf = sp;                  sp += (WMODE == 1) ? SR * L::kStageSf : 0;
+  unsigned char* sSf = sp;                  sp += (WMODE == 1) ? SR * L::kStageSf : (WMODE == 7 ? SR * L::kStageEx : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sp);
   uint64_t* b_full = bars;                  // [SB]
   uint64_t* b_empty = b_full + SB;          // [SB]
@@ -122,7 +142,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
-    if (WMODE == 1) tma_prefetch_desc(&tmSf);
+    if (WMODE == 1 || WMODE == 7) tma_prefetch_desc(&tmSf);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -141,17 +161,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
         const int kb = kb_begin + i;
         if (kQuant) {
           // raw weight stage: WMODE 1/3 cover 256 K (4 k64 blocks), WMODE 2 covers 128 K (2 k64 blocks)
-          constexpr bool kByteSrc = WMODE == 2 || WMODE == 4 || WMODE == 5;
+          constexpr bool kByteSrc = WMODE == 2 || WMODE == 4 || WMODE == 5 || WMODE == 7;
           constexpr int kSubs = kByteSrc ? 2 : 4;
           if (i % kSubs == 0) {
             const int r = i / kSubs, sr = r % SR;
             if (!wait_bar(&raw_empty[sr], ((r / SR) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 1); *abort_flag = 1; break; }
-            const uint32_t bytes = L::kStageRaw + (WMODE == 1 ? L::kStageSf : 0);
+            const uint32_t bytes = L::kStageRaw + (WMODE == 1 ? L::kStageSf : (WMODE == 7 ? L::kStageEx : 0));
             mbar_expect_tx(&raw_full[sr], bytes);
             // packed bytes: x in bytes. fp4: kb*32 bytes; fp8: kb*64 bytes
             const int xb = kByteSrc ? kb * 64 : kb * 32;
             tma_load_2d(sRaw + sr * L::kStageRaw, &tmA, xb, n0, &raw_full[sr]);
             if (WMODE == 1) tma_load_2d(sSf + sr * L::kStageSf, &tmSf, kb * 4, n0, &raw_full[sr]);
+            if (WMODE == 7) tma_load_2d(sSf + sr * L::kStageEx, &tmSf, kb * 32, n0, &raw_full[sr]);
           }
         }
         const int sb = i % SB;
@@ -194,8 +215,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
     // ------------------------------------------------------------------ converters (warps 2..9)
     const int ct = threadIdx.x - 64;       // 0..255
     const int row = ct >> 1, half = ct & 1;
-    constexpr bool kByteSrc = WMODE == 2 || WMODE == 4 || WMODE == 5;
+    constexpr bool kByteSrc = WMODE == 2 || WMODE == 4 || WMODE == 5 || WMODE == 7;
     constexpr int kSubs = kByteSrc ? 2 : 4;
+    uint32_t bf12_b = 0, esc_lo = 0, esc_hi = 0;
+    if (WMODE == 7) {
+      const int nrow = min(n0 + row, p.N - 1);
+      bf12_b = p.bf12_base[nrow];
+      esc_lo = p.bf12_rows[nrow];
+      esc_hi = p.bf12_rows[nrow + 1];
+    }
     for (int i = 0; i < nkb; ++i) {
       const int r = i / kSubs, sub = i % kSubs, sr = r % SR, sa = i % SA;
       bool ok = true;
@@ -218,6 +246,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
           const int lo = static_cast<int>(w.b[j] & 15) - 8, hi = static_cast<int>(w.b[j] >> 4) - 8;
           bf162 v = __floats2bfloat162_rn(static_cast<float>(lo) * sc, static_cast<float>(hi) * sc);
           o[j >> 2].w[j & 3] = *reinterpret_cast<uint32_t*>(&v);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4*>(dst + (((half * 4 + c) ^ (row & 7)) << 4)) = o[c].u;
+      } else if (WMODE == 7) {
+        // this k64 block: sign+mantissa bytes [sub*64, +64) of the raw row and nibble bytes [sub*32, +32) of the
+        // exponent row; the thread rebuilds its 32 weights (bytes half*32.., nibble bytes half*16..)
+        Pack16 e;
+        e.u = *reinterpret_cast<const uint4*>(sSf + sr * L::kStageEx + row * 64 + sub * 32 + half * 16);
+        Pack16 o[4];
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          const int cl = sub * 4 + half * 2 + c2;
+          Pack16 w;
+          w.u = *reinterpret_cast<const uint4*>(raw + ((cl ^ (row & 7)) << 4));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t s0 = w.b[2 * j], s1 = w.b[2 * j + 1], eb = e.b[c2 * 8 + j];
+            const uint32_t e0 = eb & 15u, e1 = eb >> 4;
+            uint32_t lo = ((s0 & 0x80u) << 8) | ((bf12_b + e0) << 7) | (s0 & 0x7Fu);
+            uint32_t hi = ((s1 & 0x80u) << 8) | ((bf12_b + e1) << 7) | (s1 & 0x7Fu);
+            if (e0 == 15u || e1 == 15u) {
+              const uint32_t col = static_cast<uint32_t>(kb) * 64 + half * 32 + c2 * 16 + 2 * j;
+              if (e0 == 15u) lo = bf12_escape(p.bf12_esc, esc_lo, esc_hi, col);
+              if (e1 == 15u) hi = bf12_escape(p.bf12_esc, esc_lo, esc_hi, col + 1);
+            }
+            o[c2 * 2 + (j >> 2)].w[j & 3] = lo | (hi << 16);
+          }
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -412,7 +468,9 @@ struct GemmCfg {
   static constexpr int kBf16Depth = (200 * 1024) / (BN * 128 + kBM * 128);
   // Quantised weights with a small token tile run two CTAs per SM (<= 113 KB each): the second CTA hides
   // the converter <-> tensor-core handshakes of the first while both keep HBM requests in flight.
+  // (BF12 carries an 8 KB exponent plane per raw stage; its B ring is shallower to stay under two CTAs per SM)
   static constexpr int SB = !kQuant ? (kBf16Depth > 8 ? 8 : kBf16Depth)
+                            : WMODE == 7 && BN <= 32 ? (BN <= 16 ? 6 : 3)
                                     : (BN <= 16 ? 8 : (BN <= 32 ? 6 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4))));
   static constexpr int SA = kQuant ? (BN <= 32 ? 3 : (BN <= 128 ? 4 : 3)) : 1;
   static constexpr int SR = kQuant ? (BN <= 32 ? 2 : (BN <= 64 ? 4 : 2)) : 1;
@@ -422,6 +480,7 @@ struct GemmCfg {
     s += static_cast<size_t>(kQuant ? SA : SB) * kBM * 128;
     if (kQuant) s += static_cast<size_t>(SR) * kBM * 128;
     if (WMODE == 1) s += static_cast<size_t>(SR) * kBM * 16;
+    if (WMODE == 7) s += static_cast<size_t>(SR) * kBM * 64;
     s += (2 * SB + 2 * SA + 2 * SR + 1) * 8 + 64;
     return s;
   }
@@ -451,7 +510,9 @@ using namespace dgpp;
 
 // Scratch sizes for split-K: ws = splits * T * N floats; counters = ceil(N/128) * ceil(T/BN) uint32 (zeroed once).
 //
-// wmode: 0 bf16, 1 nvfp4, 2 fp8-block, 3 mxfp4, 4 mxfp8, 5 int8 g64, 6 int4 g64.   a_f16 is ignored (ABI stability).
+// wmode: 0 bf16, 1 nvfp4, 2 fp8-block, 3 mxfp4, 4 mxfp8, 5 int8 g64, 6 int4 g64, 7 bf12.   a_f16 is ignored (ABI
+// stability).  bf12: w = sign+mantissa bytes [N, K]; w_scale = one buffer holding, each 16-byte aligned and in this
+// order, the exponent nibbles [N, K/2], the row bases [N], the escape row starts [N + 1] uint32 and the escapes.
 // bn: token tile (16, 32, 64, 128, 256).  splits >= 1; K/64 blocks are divided evenly (4-block aligned for fp4).
 static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
                         const void* w_scale, float alpha, void* out, void* out32, const void* resid, int ldc,
@@ -459,7 +520,7 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
   DGPP_REQUIRE(T >= 1 && N >= 1, "gemm_tc: empty problem");
   DGPP_REQUIRE(K % 64 == 0, "gemm_tc: K %d must be a multiple of 64", K);
   const bool nibble_src = wmode == 1 || wmode == 3 || wmode == 6;
-  const bool byte_src = wmode == 2 || wmode == 4 || wmode == 5;
+  const bool byte_src = wmode == 2 || wmode == 4 || wmode == 5 || wmode == 7;
   if (nibble_src) DGPP_REQUIRE(K % 256 == 0, "gemm_tc: 4-bit weights need K %% 256 == 0 (K=%d)", K);
   if (byte_src) DGPP_REQUIRE(K % 128 == 0, "gemm_tc: 8-bit weights need K %% 128 == 0 (K=%d)", K);
   DGPP_REQUIRE(splits >= 1, "gemm_tc: splits must be >= 1");
@@ -487,6 +548,18 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
   p.blk_scale = wmode == 2 ? static_cast<const float*>(w_scale) : nullptr;
   p.sf_plain = (wmode == 3 || wmode == 4) ? static_cast<const uint8_t*>(w_scale) : nullptr;
   p.sf_bf16 = (wmode == 5 || wmode == 6) ? static_cast<const bf16*>(w_scale) : nullptr;
+  p.bf12_base = nullptr; p.bf12_rows = nullptr; p.bf12_esc = nullptr;
+  if (wmode == 7) {
+    DGPP_REQUIRE(w_scale != nullptr && K <= 65536, "gemm_tc: bf12 needs its side buffer and K <= 65536");
+    auto up16 = [](size_t v) { return (v + 15) & ~size_t(15); };
+    const uint8_t* aux = static_cast<const uint8_t*>(w_scale);
+    const size_t off_base = up16(static_cast<size_t>(N) * (K / 2));
+    const size_t off_rows = off_base + up16(static_cast<size_t>(N));
+    const size_t off_esc = off_rows + up16((static_cast<size_t>(N) + 1) * 4);
+    p.bf12_base = aux + off_base;
+    p.bf12_rows = reinterpret_cast<const uint32_t*>(aux + off_rows);
+    p.bf12_esc = reinterpret_cast<const uint32_t*>(aux + off_esc);
+  }
   p.status = device_status_ptr();
   p.T = T; p.N = N; p.K = K; p.ldc = ldc;
   const int num_kb = K / 64;
@@ -507,6 +580,10 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
   } else if (byte_src) {
     if (make_tmap_2d(&tA, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, K, 128, kBM, CU_TENSOR_MAP_SWIZZLE_128B))
       return -1;
+    if (wmode == 7 &&
+        make_tmap_2d(&tSf, w_scale, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, K / 2, 64, kBM,
+                     CU_TENSOR_MAP_SWIZZLE_NONE))
+      return -1;
   } else {
     if (make_tmap_2d(&tA, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K / 2, N, K / 2, 128, kBM, CU_TENSOR_MAP_SWIZZLE_128B))
       return -1;
@@ -524,6 +601,7 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
     if (wmode == 4) return launch_gemm<BNV, 4>(tA, tB, tSf, p, splits, st);      \
     if (wmode == 5) return launch_gemm<BNV, 5>(tA, tB, tSf, p, splits, st);      \
     if (wmode == 6) return launch_gemm<BNV, 6>(tA, tB, tSf, p, splits, st);      \
+    if (wmode == 7) return launch_gemm<BNV, 7>(tA, tB, tSf, p, splits, st);      \
   }
   DGPP_GEMM_BN(16) DGPP_GEMM_BN(32) DGPP_GEMM_BN(64) DGPP_GEMM_BN(128) DGPP_GEMM_BN(256)
 #undef DGPP_GEMM_BN

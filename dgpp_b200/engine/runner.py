@@ -55,6 +55,9 @@ class DenseRunner:
         # compete with the issuing kernel's own weight stream), so it is off unless DGPP_L2_PREFETCH=1.
         import os
         self.l2_prefetch = os.environ.get("DGPP_L2_PREFETCH", "0") == "1"
+        # fold the split-KV partials of decode attention inside the o projection's quantiser (one launch per layer
+        # less); DGPP_FUSE_COMBINE=0 keeps the stand-alone combine kernel
+        self.fuse_combine = os.environ.get("DGPP_FUSE_COMBINE", "1") == "1"
         # fused GEMM -> all-reduce (peer-memory push in the GEMM epilogue, fold in the next norm kernel)
         self.fuse_ar = fuse_ar and reducer is not None and getattr(reducer, "comm", None) is not None and \
             model.cfg.hidden % 128 == 0 and model.cfg.hidden // 128 <= 64
@@ -122,8 +125,16 @@ class DenseRunner:
             lora.apply(li, "qkv", xn, qkv, self.lora_scratch)
         ops.rope_kv_write(qkv, positions, row_req, self.kv.block_table, m.inv_freq, cache, self.hq, self.hkv, self.d,
                           rot_dim=c.rot_dim or self.d, mscale=m.mscale, q_norm_w=L.q_norm, k_norm_w=L.k_norm, eps=c.eps)
-        self.attention(qkv, cache, row_req, positions, rows, splits, attn, L)
-        xa = ops.act_quant_nvfp4(attn, out=self.qa[self.hq * self.d], mode="plain")
+        if self.fuse_combine and splits > 1 and self.attn_tc and self.chunk is None and L.sink is None:
+            # split-KV decode attention leaves its partials; the quantiser of the o projection folds them
+            ops.attn_decode_tc(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, self.hq, self.hkv,
+                               self.d, self.scale, splits=splits, scratch=(self.att_ml, self.att_acc),
+                               window=L.window, partials_only=True)
+            xa = ops.attn_combine_quant((self.att_ml, self.att_acc), rows, splits, self.hq, self.d,
+                                        out=self.qa[self.hq * self.d], x_out=attn if lora is not None else None)
+        else:
+            self.attention(qkv, cache, row_req, positions, rows, splits, attn, L)
+            xa = ops.act_quant_nvfp4(attn, out=self.qa[self.hq * self.d], mode="plain")
         # tensor parallel, peer memory: the GEMM epilogue pushes its tiles to every rank and the next
         # add + RMSNorm + quantise kernel folds them (no separate all-reduce launch)
         fuse = getattr(self.reducer, "comm", None) if (self.fuse_ar and lora is None) else None

@@ -37,6 +37,7 @@ _SIGNATURES = {
     "dgpp_attn_prefill_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_decode_advance": [P, P, P, P, P, I, I, P],
     "dgpp_act_quant_nvfp4": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+    "dgpp_attn_combine_quant": [P, P, I, I, I, P, P, P, P, I, I, I, I, I, P],
     "dgpp_act_quant_nvfp4_cluster": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P, P, I, P],
     "dgpp_gemm_fp4_set_prefetch": [P, L],
     "dgpp_gemm_fp4": [I, P, P, P, I, I, P, P, F, P, P, P, I, I, I, I, I, P, P, P, P],

@@ -223,6 +223,20 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
     return out
 
 
+def attn_combine_quant(scratch, rows: int, splits: int, hq: int, d: int, out: QuantAct, x_out=None) -> QuantAct:
+    """Fold the split-KV partials of a decode-attention pass (attn_decode_tc(..., partials_only=True)) and quantise
+    the attention output rows [rows, hq * d] to residual NVFP4 terms in one launch; same arithmetic as the stand-alone
+    combine followed by the plain quantiser.  x_out (optional, bf16 [rows, hq * d]) also receives the rows."""
+    ml, acc = scratch
+    k = hq * d
+    assert out.k == k and rows <= out.rows_pad and k % 256 == 0
+    out.rows = rows
+    cl = next(c for c in (8, 4, 2, 1) if k % c == 0 and (k // c) % 16 == 0 and (k // c) * 2 <= 48 * 1024)
+    call("dgpp_attn_combine_quant", ptr(ml), ptr(acc), splits, hq, d, ptr(x_out), ptr(out.q), ptr(out.sf), ptr(out.g),
+         rows, out.rows_pad, out.terms, out.bn, cl, stream_ptr())
+    return out
+
+
 def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
              out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
              splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, push_comm=None,
@@ -340,17 +354,24 @@ def check_status() -> None:
 
 
 def attn_decode_tc(q, q_stride: int, cache, block_table, row_req, positions, hq: int, hkv: int, d: int,
-                   scale: float, splits: int = 1, scratch=None, out=None, window: int = 0):
-    """Tensor-core (tcgen05, FP8 operands) decode attention over an FP8 paged cache; head_dim 128."""
+                   scale: float, splits: int = 1, scratch=None, out=None, window: int = 0,
+                   partials_only: bool = False):
+    """Tensor-core (tcgen05, FP8 operands) decode attention over an FP8 paged cache; head_dim 128.
+    partials_only (splits > 1): stop after the split-KV pass and leave the (max, sum) pairs and unnormalised
+    accumulators in `scratch` for attn_combine_quant, which folds them while it quantises; returns None."""
     assert cache.fp8, "the tensor-core decode path reads e4m3 caches"
     rows = positions.numel()
-    if out is None:
-        out = torch.empty(rows, hq * d, dtype=torch.bfloat16, device=positions.device)
+    dev = positions.device
+    if partials_only:
+        assert splits > 1 and scratch is not None
+        out = None
+    elif out is None:
+        out = torch.empty(rows, hq * d, dtype=torch.bfloat16, device=dev)
     ml = acc = None
     if splits > 1:
         if scratch is None:
-            scratch = (torch.empty(rows * hq * splits * 2, dtype=torch.float32, device=out.device),
-                       torch.empty(rows * hq * splits * d, dtype=torch.float32, device=out.device))
+            scratch = (torch.empty(rows * hq * splits * 2, dtype=torch.float32, device=dev),
+                       torch.empty(rows * hq * splits * d, dtype=torch.float32, device=dev))
         ml, acc = scratch
     call("dgpp_attn_decode_tc", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale),
          ptr(cache.v_scale), ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq,

@@ -135,6 +135,34 @@ def test_attn_decode_tc(dev, hq, hkv, ctx, page, splits):
     assert (out.float() - want).abs().max().item() < 0.02
 
 
+@pytest.mark.parametrize("hq,hkv,ctx,splits", [(40, 8, 2048, 4), (16, 2, 700, 3), (8, 8, 333, 2)])
+def test_attn_combine_quant_matches_unfused(dev, hq, hkv, ctx, splits):
+    """The quantiser that folds the split-KV partials itself writes the same bf16 rows and the same NVFP4 terms
+    (payload, block scales, row scales) as the stand-alone combine kernel followed by the plain quantiser."""
+    from dgpp_b200.ops import core as ops
+
+    torch.manual_seed(14)
+    kv, qkv, pos, req = _filled_cache(dev, hq, hkv, ctx, 64, slot=2)
+    scale = 1.0 / math.sqrt(128)
+    sel = torch.tensor([ctx - 1, ctx // 2, 5, ctx // 3, 64], device=dev)
+    q, p_, r_ = qkv[sel].contiguous(), pos[sel].contiguous(), req[sel].contiguous()
+    rows, k = sel.numel(), hq * 128
+    scratch = (torch.empty(rows * hq * splits * 2, dtype=torch.float32, device=dev),
+               torch.empty(rows * hq * splits * 128, dtype=torch.float32, device=dev))
+    want_x = ops.attn_decode_tc(q, q.stride(0), kv.layers[0], kv.block_table, r_, p_, hq, hkv, 128, scale,
+                                splits=splits, scratch=scratch)
+    want = ops.act_quant_nvfp4(want_x, terms=3, bn=16, mode="plain")
+    assert ops.attn_decode_tc(q, q.stride(0), kv.layers[0], kv.block_table, r_, p_, hq, hkv, 128, scale,
+                              splits=splits, scratch=scratch, partials_only=True) is None
+    got = ops.QuantAct(want.rows_pad, k, 3, 16, dev)
+    got_x = torch.zeros(rows, k, dtype=torch.bfloat16, device=dev)
+    ops.attn_combine_quant(scratch, rows, splits, hq, 128, out=got, x_out=got_x)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(got_x, want_x)
+    assert torch.equal(got.g, want.g) and torch.equal(got.q, want.q) and torch.equal(got.sf, want.sf)
+
+
 @pytest.mark.parametrize("hq,hkv,ctx,page,pos0,T", [(10, 2, 256, 64, 0, 256), (10, 2, 700, 64, 0, 700),
                                                    (40, 8, 1000, 64, 300, 513), (8, 2, 400, 16, 77, 200),
                                                    (4, 4, 130, 128, 1, 129)])
