@@ -84,6 +84,8 @@ def main():
     ap.add_argument("--reducer", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--prefill-lens", default="", help="comma list of cold-prefill lengths to time as extras")
     ap.add_argument("--also-c1", action="store_true", help="also time C=1 decode as an extra")
+    ap.add_argument("--bf12-head", action="store_true",
+                    help="keep the bf16 lm head in its lossless 12-bit resident form (same logits bit for bit)")
     ap.add_argument("--no-fuse-ar", action="store_true",
                     help="tensor parallel: separate all-reduce kernels instead of the GEMM-epilogue push + fold")
     args = ap.parse_args()
@@ -112,6 +114,8 @@ def main():
     cfg = DenseConfig.dense_27b(layers=args.layers)
     t_init = time.time()
     model = DenseModel.random_init(cfg, device=dev, seed=0, tp_rank=rank, tp_size=world)
+    if args.bf12_head:
+        model.pack_bf12()
     torch.cuda.synchronize()
     t_init = time.time() - t_init
 

@@ -98,6 +98,19 @@ def bench_gemm_fp4(args, dev):
     fns = [(lambda w=w: ops.gemm_fp4(xa, w, out=out, splits=splits)) for w in ws]
     ms = run(fns, args)
     ops.check_status()
+    if args.trace:
+        # phase timestamps of CTA (0,0,0) of one cold launch (weights not in L2), ns since kernel entry
+        from ..ops._lib import call, ptr
+        t = torch.zeros(8, dtype=torch.int64, device=dev)
+        call("dgpp_gemm_fp4_set_trace", ptr(t))
+        fns[1 % len(fns)]()
+        torch.cuda.synchronize()
+        call("dgpp_gemm_fp4_set_trace", None)
+        v = t.tolist()
+        names = ["entry", "prologue_done", "prev_grid_done", "first_stage_landed", "last_mma_issued", "acc_complete",
+                 "epilogue_done"]
+        print(json.dumps({"kernel": "gemm_fp4_trace", "n": n, "k": k, "ns_since_entry":
+                          {nm: v[i] - v[0] for i, nm in enumerate(names)}}))
     report(args, "gemm_fp4", ms, bytes_=w_bytes + rows * k * terms // 2 + rows * n * 2, flops=2.0 * rows * n * k,
            rows=rows, n=n, k=k, terms=terms, weight_copies=copies)
 
@@ -234,6 +247,7 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--moe-ffn", type=int, default=1536)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--trace", action="store_true", help="gemm_fp4: print the phase timestamps of one CTA")
     ap.add_argument("--once", action="store_true", help="a few plain launches, no graph, no timing (for profilers)")
     args = ap.parse_args(argv)
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))

@@ -8,6 +8,9 @@
 //   swiglu:   a = bf16( bf16(silu(g)) * u )
 // (reference behaviour: src/kernels/add_rmsnorm.cu:28, src/kernels/kernels.cu:19,58,98,142 of the
 // reference tree describe the same operator set.)
+#include <cooperative_groups.h>
+#include <string.h>
+
 #include "common/common.h"
 #include "common/dtypes.cuh"
 #include "common/ptx.cuh"
@@ -166,6 +169,94 @@ argmax_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab, int i
   }
 }
 
+// The same pick with one row spread over a thread-block cluster (decode: a handful of rows of a 150K vocabulary would
+// otherwise keep a handful of SMs busy): CTA c scans slice c of the row, pushes its (value, index) into CTA 0's
+// shared memory, and after the cluster barrier CTA 0 picks among the slices in the same order rule (largest value,
+// lowest index), so the result is the single-CTA kernel's.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+argmax_cluster_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab, int id_base,
+                      int32_t* __restrict__ out_id, float* __restrict__ out_val) {
+  namespace cg = cooperative_groups;
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float cv[8];
+  __shared__ int ci[8];
+  cg::cluster_group cluster = cg::this_cluster();
+  pdl_wait();
+  const int c = blockIdx.x, ncl = gridDim.x;
+  const T* row = logits + static_cast<size_t>(blockIdx.y) * row_stride;
+  const int chunk = ((vocab + ncl - 1) / ncl + 3) & ~3;
+  const int lo = c * chunk, hi = min(vocab, lo + chunk);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    float v = static_cast<float>(row[i]);
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) {
+    sv[w] = best;
+    si[w] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (blockDim.x >> 5); ++i) {
+      if (sv[i] > best || (sv[i] == best && si[i] < bi)) {
+        best = sv[i];
+        bi = si[i];
+      }
+    }
+    *cluster.map_shared_rank(&cv[c], 0) = best;
+    *cluster.map_shared_rank(&ci[c], 0) = bi;
+  }
+  cluster.sync();
+  if (c == 0 && threadIdx.x == 0) {
+    best = cv[0];
+    bi = ci[0];
+    for (int i = 1; i < ncl; ++i) {
+      if (cv[i] > best || (cv[i] == best && ci[i] < bi)) {
+        best = cv[i];
+        bi = ci[i];
+      }
+    }
+    out_id[blockIdx.y] = bi + id_base;
+    if (out_val) out_val[blockIdx.y] = best;
+  }
+}
+
+template <typename T>
+static int launch_argmax_cluster(const T* logits, int64_t row_stride, int rows, int vocab, int id_base, int32_t* out_id,
+                                 float* out_val, cudaStream_t st) {
+  constexpr int kCl = 8;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(kCl, rows, 1);
+  cfg.blockDim = dim3(1024, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCl;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  DGPP_CUDA_OK(cudaLaunchKernelEx(&cfg, argmax_cluster_kernel<T>, logits, row_stride, vocab, id_base, out_id, out_val));
+  return 0;
+}
+
 // dst[i] = src[i] (bf16 rows), used for snapshots and gathers inside graphs (no memcpy nodes).
 __global__ void copy_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int64_t nvec) {
   pdl_wait();
@@ -246,6 +337,13 @@ DGPP_API int dgpp_swiglu(const void* gate_up, void* out, int rows, int inter, fl
 DGPP_API int dgpp_argmax(const void* logits, int dtype, int64_t row_stride, int rows, int vocab, int id_base,
                          void* out_id, void* out_val, cudaStream_t st) {
   if (rows == 0) return 0;
+  if (rows <= 64 && vocab >= 16384) {   // few long rows: one cluster of 8 CTAs per row
+    if (dtype == 0)
+      return launch_argmax_cluster<bf16>(static_cast<const bf16*>(logits), row_stride, rows, vocab, id_base,
+                                         static_cast<int32_t*>(out_id), static_cast<float*>(out_val), st);
+    return launch_argmax_cluster<float>(static_cast<const float*>(logits), row_stride, rows, vocab, id_base,
+                                        static_cast<int32_t*>(out_id), static_cast<float*>(out_val), st);
+  }
   if (dtype == 0)
     argmax_kernel<bf16><<<rows, 1024, 0, st>>>(static_cast<const bf16*>(logits), row_stride, vocab, id_base,
                                               static_cast<int32_t*>(out_id), static_cast<float*>(out_val));

@@ -72,6 +72,8 @@ struct Fp4Params {
   // (quantiser, RoPE, attention over a short context) leave HBM idle; the prefetch fills that time.  A hint only.
   const unsigned char* pf_ptr;
   int64_t pf_bytes;
+  unsigned long long* trace;  // debug: CTA (0,0,0) stores %globaltimer at 7 points of its life (see dgpp_gemm_fp4_set_trace)
+  int preload;             // dense mode: issue the weight half of the first ring stages before waiting on the preceding grid
   // Split-K inside a thread-block cluster (decode projections with few output tiles): the gridDim.z CTAs of one output
   // tile form a cluster (1, 1, splits); each runs its share of the K stages, then the partial accumulators of ranks
   // 1.. travel through distributed shared memory into rank 0's (by then idle) operand ring and rank 0 adds them in
@@ -121,6 +123,15 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  auto stamp = [&](int slot) {
+    if (tracing) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      p.trace[slot] = t;
+    }
+  };
+  if (threadIdx.x == 0) stamp(0);
   const int bn_tok = BN / p.R;             // tokens per tile
   const int m0 = blockIdx.y * bn_tok;
   const int split = blockIdx.z, splits = gridDim.z;
@@ -157,7 +168,27 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_sfa = tmem_base + kColD;
   const uint32_t tmem_sfb = tmem_sfa + 2 * kColSfa;
+  if (threadIdx.x == 0) stamp(1);
+  // Weights never depend on the preceding grid.  In dense mode the producer therefore fills the first ring stages
+  // with weight tiles and their scales BEFORE it waits for that grid: under programmatic dependent launch this CTA
+  // is already resident while the small kernel in front of it (the activation quantiser) still runs, so the weight
+  // stream of up to S stages per CTA overlaps with it and the first MMA no longer pays an HBM round trip.  The
+  // activation half of each of those stages is issued after the wait, onto the same barrier.  (Grouped mode picks
+  // its weight tile from the routing result and cannot start early.)
+  const int pre = (p.group_list || !p.preload) ? 0 : min(max(0, st_end - st_begin), S);
+  if (warp == 0 && pre > 0) {
+    if (elect_one()) {
+      const uint8_t* sfa_pre = p.sfa + static_cast<size_t>(blockIdx.x) * total_stages * kSfaBytes;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full[i], kF4StageA + kSfaBytes + R * (kStageB + kSfbBytes));
+        tma_load_2d(sA + i * kF4StageA, &tmA, (st_begin + i) * 128, blockIdx.x * kF4BM, &full[i]);
+        bulk_load_1d(sSfa + i * kSfaBytes, sfa_pre + static_cast<size_t>(st_begin + i) * kSfaBytes, kSfaBytes, &full[i]);
+      }
+    }
+    __syncwarp();
+  }
   pdl_wait();
+  if (threadIdx.x == 0) stamp(2);
   // tile of the (stacked) weight matrix, output / activation group
   int tile_x = blockIdx.x, grp = 0;
   bool active = true;
@@ -184,11 +215,13 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
       for (int i = 0; i < nst; ++i) {
         const int s = i % S;
         const int st = st_begin + i;
-        if (!wait_bar(&empty[s], ((i / S) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 11); *abort_flag = 1; break; }
-        mbar_expect_tx(&full[s], kF4StageA + kSfaBytes + R * (kStageB + kSfbBytes));
         const int xb = st * 128;  // byte column of this stage
-        tma_load_2d(sA + s * kF4StageA, &tmA, xb, n0, &full[s]);
-        bulk_load_1d(sSfa + s * kSfaBytes, sfa_tile + static_cast<size_t>(st) * kSfaBytes, kSfaBytes, &full[s]);
+        if (i >= pre) {           // (the weight half of the first `pre` stages is already in flight)
+          if (!wait_bar(&empty[s], ((i / S) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 11); *abort_flag = 1; break; }
+          mbar_expect_tx(&full[s], kF4StageA + kSfaBytes + R * (kStageB + kSfbBytes));
+          tma_load_2d(sA + s * kF4StageA, &tmA, xb, n0, &full[s]);
+          bulk_load_1d(sSfa + s * kSfaBytes, sfa_tile + static_cast<size_t>(st) * kSfaBytes, kSfaBytes, &full[s]);
+        }
         for (int r = 0; r < R; ++r) {
           tma_load_2d(sB + (s * RMAX + r) * kStageB, &tmB, xb, b_row0, &full[s]);
           const uint8_t* sfb = p.sfb + sfb_grp + ((static_cast<size_t>(r) * token_tiles + blockIdx.y) * total_stages + st) * kSfbBytes;
@@ -214,6 +247,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
       for (int i = 0; i < nst; ++i) {
         const int s = i % S;
         if (!wait_bar(&full[s], (i / S) & 1)) { report(p.status, kTimeoutTmaFull, 12); *abort_flag = 1; break; }
+        if (i == 0) stamp(3);
         tc_fence_after();
         const uint32_t buf = i & 1;
         const uint32_t t_sfa = tmem_sfa + buf * kColSfa;
@@ -240,12 +274,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
         if (*abort_flag) break;
       }
       umma_commit(acc_full);
+      stamp(4);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5): wait for the accumulator
     acc_ok = nst > 0 ? wait_bar(acc_full, 0) : true;
     if (!acc_ok) { report(p.status, kTimeoutAccum, 15); *abort_flag = 1; }
     acc_ok = __all_sync(0xffffffffu, acc_ok);            // the TMEM loads below stay warp-uniform
+    if (warp == 2 && lane == 0) stamp(5);
     tc_fence_after();
   }
   if (p.cluster_split) {
@@ -413,6 +449,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) stamp(6);
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
@@ -658,6 +695,20 @@ DGPP_API int dgpp_act_quant_nvfp4(int mode, const void* in, int64_t in_stride, c
 // out[T, N] = alpha * g[t] * sum_r Wq . Xq_r^T.   xq: [R, T_pad, K/2]; xsf / wsf_tiled: tiled scale factors; g: [T].
 // One-shot hint for the NEXT dgpp_gemm_fp4 / dgpp_gemm_fp4_grouped call of this thread: the bytes its CTAs ask L2
 // to fetch once their own loads are issued (normally the packed weights of the projection that runs next).
+static unsigned long long* g_trace = nullptr;
+// Debug aid: while a device buffer of 8 uint64 is set, CTA (0,0,0) of every dgpp_gemm_fp4 launch stores %globaltimer
+// (ns) at: 0 entry, 1 prologue done, 2 preceding grid complete, 3 first stage landed, 4 last MMA issued,
+// 5 accumulator complete, 6 epilogue done.  Pass null to switch it off.
+DGPP_API int dgpp_gemm_fp4_set_trace(void* dev_u64x8) {
+  g_trace = static_cast<unsigned long long*>(dev_u64x8);
+  return 0;
+}
+static int g_preload = 1;
+// Process-wide switch of the pre-wait weight preload (on by default; off for A/B measurements).
+DGPP_API int dgpp_gemm_fp4_set_preload(int on) {
+  g_preload = on ? 1 : 0;
+  return 0;
+}
 static thread_local const unsigned char* g_pf_ptr = nullptr;
 static thread_local int64_t g_pf_bytes = 0;
 DGPP_API int dgpp_gemm_fp4_set_prefetch(const void* ptr, int64_t bytes) {
@@ -691,6 +742,8 @@ DGPP_API int dgpp_gemm_fp4(int bn, const void* xq, const void* xsf, const void* 
   p.T = T; p.T_pad = T_pad; p.N = N; p.K = K; p.ldc = ldc; p.R = R;
   p.push = 0;
   p.pf_ptr = g_pf_ptr; p.pf_bytes = g_pf_bytes;
+  p.preload = g_preload;
+  p.trace = g_trace;
   g_pf_ptr = nullptr; g_pf_bytes = 0;
   p.group_list = nullptr; p.group_alpha = nullptr; p.group_tiles = 0; p.group_b = 0; p.grid_x = 0; p.group_out_stride = 0;
   memset(&p.comm, 0, sizeof(p.comm));
@@ -762,6 +815,8 @@ DGPP_API int dgpp_gemm_fp4_grouped(int bn, const void* xq, const void* xsf, cons
   p.T = T; p.T_pad = bn; p.N = N; p.K = K; p.ldc = ldc; p.R = R;
   p.push = 0;
   p.pf_ptr = g_pf_ptr; p.pf_bytes = g_pf_bytes;
+  p.preload = g_preload;
+  p.trace = g_trace;
   g_pf_ptr = nullptr; g_pf_bytes = 0;
   memset(&p.comm, 0, sizeof(p.comm));
   p.group_list = static_cast<const int32_t*>(group_list);

@@ -246,6 +246,9 @@ def save_dense(model: DenseModel, out_dir: str, shard_layers: int = 0) -> None:
 
     def put(file: str, prefix: str, w: QuantLinear, r0: int, r1: int):
         g = groups.setdefault(file, {})
+        if w.fmt == "bf12":      # a resident form only: checkpoints carry the bf16 tensor it stands for
+            from ..quant.formats import bf12_decode
+            w = QuantLinear("bf16", w.n, w.k, bf12_decode(w))
         if w.fmt in ("bf16", "fp32"):
             g[prefix + ".weight"] = w.payload[r0:r1]
             return

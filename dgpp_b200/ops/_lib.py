@@ -40,6 +40,8 @@ _SIGNATURES = {
     "dgpp_attn_combine_quant": [P, P, I, I, I, P, P, P, P, I, I, I, I, I, P],
     "dgpp_act_quant_nvfp4_cluster": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P, P, I, P],
     "dgpp_gemm_fp4_set_prefetch": [P, L],
+    "dgpp_gemm_fp4_set_preload": [I],
+    "dgpp_gemm_fp4_set_trace": [P],
     "dgpp_gemm_fp4": [I, P, P, P, I, I, P, P, F, P, P, P, I, I, I, I, I, P, P, P, P],
     "dgpp_graph_begin_capture": [P],
     "dgpp_graph_launch": [P, P],

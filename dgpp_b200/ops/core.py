@@ -12,7 +12,7 @@ from . import _lib
 from ._lib import call, ptr, stream_ptr
 
 _FMT_GEMV = {"nvfp4": 0, "mxfp4": 1, "bf16": 2}
-_FMT_GEMM = {"bf16": 0, "nvfp4": 1, "fp8": 2, "mxfp4": 3, "mxfp8": 4, "int8": 5, "int4": 6}
+_FMT_GEMM = {"bf16": 0, "nvfp4": 1, "fp8": 2, "mxfp4": 3, "mxfp8": 4, "int8": 5, "int4": 6, "bf12": 7}
 
 # The converted-weight operand is always bf16: tcgen05 kind::f16 takes A and B of one 16-bit type.
 A_F16_DEFAULT = 0
@@ -275,6 +275,10 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
     return out if out is not None else out32
 
 
+# DGPP_FP4_PRELOAD=0 turns off the pre-wait weight preload of the block-scaled GEMM (A/B measurements)
+if os.environ.get("DGPP_FP4_PRELOAD", "1") == "0":
+    call("dgpp_gemm_fp4_set_preload", 0)
+
 # DGPP_CLUSTER_SPLITK=1 selects the cluster split-K policy (off until its launch path is validated)
 CLUSTER_SPLITK = os.environ.get("DGPP_CLUSTER_SPLITK", "0") == "1"
 
@@ -295,10 +299,20 @@ def pick_cluster_splits(rows: int, n: int, k: int, bn: int) -> int:
     return s
 
 
+# Split-K policy of the block-scaled GEMM in the weight-streaming regime.  "resident": split until one resident wave
+# (two CTAs per SM) covers the problem, so that with the pre-wait weight preload most of a CTA's K range is already
+# in its ring when the activations arrive; "legacy": split only long-K, few-tile problems.
+FP4_SPLIT_POLICY = os.environ.get("DGPP_FP4_SPLITS", "legacy")
+
+
 def pick_splits_fp4(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:
-    """Split K only for long-K, few-tile problems (the deterministic fold costs a few microseconds)."""
+    """Split K for few-tile problems (the deterministic fold costs a few microseconds)."""
     tiles = math.ceil(n / 128) * math.ceil(rows / bn)
     stages = k // 256
+    if FP4_SPLIT_POLICY == "resident":
+        if tiles > sms:
+            return 1
+        return max(1, min(2 * sms // tiles, stages // 2, 8))
     if tiles >= sms // 2 + 1 or stages <= 24:
         return 1 if (rows > 1 or tiles >= sms // 2 + 1) else max(1, min(3, stages // 4))
     return max(1, min(math.ceil(sms / tiles), stages // 8))

@@ -14,6 +14,9 @@ format      payload                         scales
 ``int4``    offset-binary, 2 codes/byte     bf16 per 64 along K [N, K/64]
 ``int8``    offset-binary bytes [N, K]      bf16 per 64 along K [N, K/64]
 ``bf16``    bf16 [N, K]                     --
+``bf12``    sign + mantissa bytes [N, K]    one side buffer: exponent nibbles [N, K/2], row bases
+            (lossless resident form of       [N], escape row starts [N + 1] uint32, escapes
+            a bf16 matrix, see bf12_encode)  ((column << 16) | bf16 bits)
 ==========  ==============================  =============================================
 
 The quantisers here are used to build random-init models of a given format and as the oracle the
@@ -115,6 +118,8 @@ class QuantLinear:
         if f == "mxfp8":
             v = self.payload.view(torch.float8_e4m3fn).float().view(n, k // 32, 32)
             return (v * e8m0_decode(self.scale).view(n, k // 32, 1)).view(n, k)
+        if f == "bf12":
+            return bf12_decode(self).float()
         if f in ("int4", "int8"):
             bits = 4 if f == "int4" else 8
             codes = unpack_nibbles(self.payload) if bits == 4 else self.payload
@@ -128,6 +133,96 @@ class QuantLinear:
         if self.fmt == "nvfp4":
             return (self.dequant() / self.alpha).to(torch.bfloat16)
         return self.dequant().to(torch.bfloat16)
+
+
+def _up16(v: int) -> int:
+    return (v + 15) & ~15
+
+
+def bf12_layout(n: int, k: int):
+    """Byte offsets of (row bases, escape row starts, escapes) inside a BF12 side buffer; the exponent nibbles
+    start at 0.  Every part starts on a 16-byte boundary (the nibble plane is a TMA source)."""
+    off_base = _up16(n * (k // 2))
+    off_rows = off_base + _up16(n)
+    off_esc = off_rows + _up16((n + 1) * 4)
+    return off_base, off_rows, off_esc
+
+
+def bf12_encode(w: torch.Tensor, max_escape_fraction: float = 1.0 / 64) -> Optional["QuantLinear"]:
+    """Pack a bf16 matrix [N, K] (K % 128 == 0, K <= 65536) into the lossless 12-bit resident form.
+
+    A bf16 weight's sign and mantissa do not compress, its exponent does: almost every weight of a trained row lies
+    inside a window of 15 consecutive exponents.  Stored per weight: the sign + mantissa byte as is, and a 4-bit
+    exponent code against the row's base (the window start that covers most of the row).  Code 15 is the escape:
+    the weight's true bits sit in a per-row, column-sorted side table.  0.75 of the bf16 bytes, every value
+    bit-for-bit the original.  Returns None when more than `max_escape_fraction` of the weights would escape (the
+    packing would not pay; the matrix keeps its bf16 form).
+    (reference counterpart: src/kernels/bf12_gemv.hpp -- same idea, a lane-owned layout for a CUDA-core GEMV there;
+     here two TMA planes feeding the converter warps of the tensor-core GEMM.)"""
+    assert w.dtype == torch.bfloat16 and w.dim() == 2
+    n, k = w.shape
+    assert k % 128 == 0 and k <= 65536, "bf12: K must be a multiple of 128 and at most 65536"
+    dev = w.device
+    off_base, off_rows, off_esc = bf12_layout(n, k)
+    sm = torch.empty(n, k, dtype=torch.uint8, device=dev)
+    ex = torch.empty(n, k // 2, dtype=torch.uint8, device=dev)
+    base = torch.empty(n, dtype=torch.uint8, device=dev)
+    counts = torch.zeros(n, dtype=torch.int64, device=dev)
+    esc_parts = []
+    step = max(1, (1 << 24) // k)                          # rows per pass: bounds the int32 temporaries
+    for r0 in range(0, n, step):
+        bits = w[r0:r0 + step].contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+        e = (bits >> 7) & 0xFF
+        rows = bits.shape[0]
+        hist = torch.zeros(rows, 256 + 15, dtype=torch.int64, device=dev)
+        hist.scatter_add_(1, e.long(), torch.ones_like(e, dtype=torch.int64))
+        cs = torch.cat((torch.zeros(rows, 1, dtype=torch.int64, device=dev), hist.cumsum(1)), 1)
+        inside = cs[:, 15:15 + 256] - cs[:, 0:256]         # weights with exponent in [b, b + 14], b = 0..255
+        # exponent 255 + code must stay a byte: bases above 241 gain nothing
+        b = inside[:, :242].argmax(1).to(torch.int32)
+        code = e - b.unsqueeze(1)
+        out = (code < 0) | (code > 14)
+        code = torch.where(out, torch.full_like(code, 15), code).to(torch.uint8)
+        sm[r0:r0 + rows] = (((bits >> 8) & 0x80) | (bits & 0x7F)).to(torch.uint8)
+        ex[r0:r0 + rows] = pack_nibbles(code)
+        base[r0:r0 + rows] = b.to(torch.uint8)
+        counts[r0:r0 + rows] = out.sum(1)
+        rr, cc = out.nonzero(as_tuple=True)                # row-major: column-sorted within each row
+        esc_parts.append(((cc.to(torch.int64) << 16) | bits[rr, cc].to(torch.int64)).to(torch.int64))
+    total = int(counts.sum())
+    if total > max_escape_fraction * n * k:
+        return None
+    esc = torch.cat(esc_parts) if esc_parts else torch.zeros(0, dtype=torch.int64, device=dev)
+    starts = torch.zeros(n + 1, dtype=torch.int64, device=dev)
+    starts[1:] = counts.cumsum(0)
+    aux = torch.zeros(off_esc + max(16, _up16(total * 4)), dtype=torch.uint8, device=dev)
+    aux[:n * (k // 2)] = ex.flatten()
+    aux[off_base:off_base + n] = base
+    aux[off_rows:off_rows + (n + 1) * 4] = starts.to(torch.int32).view(torch.uint8)
+    if total:
+        # (values above 2^31 wrap to the same 32 bits through int64 -> int32)
+        aux[off_esc:off_esc + total * 4] = esc.to(torch.int32).view(torch.uint8)
+    return QuantLinear("bf12", n, k, sm, aux)
+
+
+def bf12_decode(q: "QuantLinear") -> torch.Tensor:
+    """The bf16 matrix a BF12 form holds, bit for bit."""
+    assert q.fmt == "bf12"
+    n, k = q.n, q.k
+    off_base, off_rows, off_esc = bf12_layout(n, k)
+    aux = q.scale
+    code = unpack_nibbles(aux[:n * (k // 2)].view(n, k // 2)).to(torch.int32)
+    base = aux[off_base:off_base + n].to(torch.int32).unsqueeze(1)
+    s = q.payload.to(torch.int32)
+    bits = ((s & 0x80) << 8) | ((base + code) << 7) | (s & 0x7F)
+    starts = aux[off_rows:off_rows + (n + 1) * 4].view(torch.int32).to(torch.int64)
+    total = int(starts[-1])
+    if total:
+        esc = aux[off_esc:off_esc + total * 4].view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+        rows = torch.repeat_interleave(torch.arange(n, device=aux.device), starts[1:] - starts[:-1])
+        bits[rows, esc >> 16] = (esc & 0xFFFF).to(torch.int32)
+    bits = torch.where(bits >= 0x8000, bits - 0x10000, bits).to(torch.int16)
+    return bits.view(torch.bfloat16)
 
 
 def mxfp4_as_nvfp4(w: "QuantLinear") -> Optional["QuantLinear"]:
@@ -191,6 +286,9 @@ def quantize(w: torch.Tensor, fmt: str) -> QuantLinear:
         return QuantLinear("bf16", n, k, w.to(torch.bfloat16).contiguous())
     if fmt == "fp32":
         return QuantLinear("fp32", n, k, wf.contiguous())
+    if fmt == "bf12":
+        wb = w.to(torch.bfloat16).contiguous()
+        return bf12_encode(wb) or QuantLinear("bf16", n, k, wb)
     if fmt == "nvfp4":
         assert k % 16 == 0
         amax = wf.abs().max().clamp_min(1e-12)
@@ -259,6 +357,10 @@ def random_quant_linear(n: int, k: int, fmt: str, device, std: float = 0.02,
             payloads.append(pack_nibbles(codes.view(r, k)))
             scales.append(sb8.view(torch.uint8))
         return QuantLinear("nvfp4", n, k, torch.cat(payloads).contiguous(), torch.cat(scales).contiguous(), gs)
+    if fmt == "bf12":      # the side tables index the whole matrix: encode once, over the assembled bf16 rows
+        w = torch.cat([(torch.randn(min(chunk_rows, n - r0), k, device=device, dtype=torch.float32,
+                                    generator=generator) * std).to(torch.bfloat16) for r0 in range(0, n, chunk_rows)])
+        return bf12_encode(w) or QuantLinear("bf16", n, k, w)
     if fmt == "fp8":
         chunk_rows = max(128, chunk_rows // 128 * 128)
     parts = []

@@ -57,6 +57,28 @@ def test_embed_rmsnorm_swiglu_argmax(dev):
     assert torch.equal(i2, ref.argmax(logits.to(BF), 1000)[0])
 
 
+@pytest.mark.parametrize("rows,vocab", [(8, 151936), (1, 16384), (3, 18991), (64, 32000), (70, 32000), (5, 4096)])
+def test_argmax_cluster_and_single_cta_agree(dev, rows, vocab):
+    """Few long rows take the cluster kernel (a row spread over 8 CTAs), the rest one CTA per row; both follow
+    'largest value, lowest index', also when the tie straddles two CTAs' slices or a row is constant."""
+    from dgpp_b200.ops import core as ops, reference as ref
+
+    torch.manual_seed(21)
+    logits = torch.randn(rows, vocab, device=dev)
+    logits[0, vocab - 1] = 60.0
+    logits[0, vocab // 8 + 5] = 60.0                      # the same maximum in slice 1 and in the last slice
+    if rows > 2:
+        logits[1] = 0.25                                   # constant row: index 0
+        logits[2] = float("-inf")                          # fully masked row: index 0
+    i, v = ops.argmax(logits, id_base=7)
+    ir, vr = ref.argmax(logits, 7)
+    torch.cuda.synchronize()
+    assert torch.equal(i, ir) and torch.equal(v, vr)
+    assert int(i[0]) == vocab // 8 + 5 + 7
+    ib, _ = ops.argmax(logits.to(BF))
+    assert torch.equal(ib, ref.argmax(logits.to(BF))[0])
+
+
 @pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4", "bf16"])
 @pytest.mark.parametrize("rows", [1, 3, 4])
 def test_gemv(dev, fmt, rows):
@@ -94,6 +116,36 @@ def test_gemm_tc(dev, fmt, a_f16, rows, bn, splits):
     y2 = ops.gemm_tc(x, w, resid=res, bn=bn, splits=splits, a_f16=a_f16)
     ops.check_status()
     _close(y2, ref.linear(x, wr, resid=res), 2 ** -6, 8e-3)
+
+
+@pytest.mark.parametrize("rows,bn,splits", [(1, 16, 1), (8, 16, 4), (37, 64, 1), (130, 128, 2), (300, 256, 1)])
+def test_gemm_tc_bf12_is_bitwise_the_bf16_kernel(dev, rows, bn, splits):
+    """The 12-bit resident form feeds the tensor cores the exact bf16 bits (escaped outliers included), so the
+    converter path returns what the plain bf16 kernel returns, bit for bit."""
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.quant.formats import QuantLinear, bf12_decode, bf12_encode
+
+    torch.manual_seed(12)
+    n, k = 384 + 64, 1024
+    wb = (torch.randn(n, k, device=dev) * 0.05).to(BF)
+    # outliers far outside every row's exponent window: first / last column, row tile edges, a zero, a whole zero row
+    wb[0, 0], wb[0, k - 1], wb[127, 513], wb[128, 64], wb[n - 1, k - 1] = 3e20, -1e-30, 0.0, 7e15, -2e-25
+    wb[200] = 0
+    wb[300, ::3] = 1e-28                                  # a row with hundreds of escapes (binary search depth)
+    q = bf12_encode(wb)
+    assert q is not None and torch.equal(bf12_decode(q).view(torch.int16), wb.view(torch.int16))
+    w16 = QuantLinear("bf16", n, k, wb)
+    x = torch.randn(rows, k, device=dev).to(BF)
+    y = ops.gemm_tc(x, q, bn=bn, splits=splits)
+    y32 = torch.empty(rows, n, device=dev, dtype=torch.float32)
+    ops.gemm_tc(x, q, out32=y32, bn=bn, splits=splits)
+    want = ops.gemm_tc(x, w16, bn=bn, splits=splits)
+    want32 = torch.empty(rows, n, device=dev, dtype=torch.float32)
+    ops.gemm_tc(x, w16, out32=want32, bn=bn, splits=splits)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(y32, want32)
 
 
 def test_gemm_tc_is_deterministic_and_row_independent(dev):
