@@ -127,7 +127,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
   auto stamp = [&](int slot) {
     if (tracing) {
       unsigned long long t;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t) :: "memory");
       p.trace[slot] = t;
     }
   };
@@ -424,20 +424,44 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA,   // packed weights as 
       if (*last_flag) {
         __threadfence();
         if (n < p.N) {
-          for (int m = 0; m < cols; ++m) {
-            float acc = 0.f;
-            for (int s2 = 0; s2 < splits; ++s2)
-              acc += __ldcg(p.ws + (static_cast<size_t>(s2) * p.T + m0 + m) * N_ws + n_ws);
-            const size_t o = out_grp + static_cast<size_t>(m0 + m) * p.ldc + n;
-            float y = acc * alpha * gvec[m0 + m];
-            if (p.push) {
-              push_value(p, push_parity, static_cast<size_t>(m0 + m) * p.N + n, f32_to_bf16(y));
-              continue;
+          // The partials of 4 rows x 4 splits are requested together (16 independent L2 loads in flight per thread)
+          // and then added in ascending split order: the sum is the one a plain loop gives, without one L2 round
+          // trip per (row, split).
+          for (int mb = 0; mb < cols; mb += 4) {
+            float acc[4];
+#pragma unroll
+            for (int mm = 0; mm < 4; ++mm) acc[mm] = 0.f;
+            for (int s0 = 0; s0 < splits; s0 += 4) {
+              float t[4][4];
+#pragma unroll
+              for (int mm = 0; mm < 4; ++mm) {
+#pragma unroll
+                for (int ss = 0; ss < 4; ++ss) {
+                  const bool live = mb + mm < cols && s0 + ss < splits;
+                  t[mm][ss] = live ? __ldcg(p.ws + (static_cast<size_t>(s0 + ss) * p.T + m0 + mb + mm) * N_ws + n_ws) : 0.f;
+                }
+              }
+#pragma unroll
+              for (int mm = 0; mm < 4; ++mm) {
+#pragma unroll
+                for (int ss = 0; ss < 4; ++ss) acc[mm] += t[mm][ss];
+              }
             }
-            if (p.out32) p.out32[o] = y;
-            if (p.out) {
-              if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
-              p.out[o] = f32_to_bf16(y);
+#pragma unroll
+            for (int mm = 0; mm < 4; ++mm) {
+              const int m = mb + mm;
+              if (m >= cols) break;
+              const size_t o = out_grp + static_cast<size_t>(m0 + m) * p.ldc + n;
+              float y = acc[mm] * alpha * gvec[m0 + m];
+              if (p.push) {
+                push_value(p, push_parity, static_cast<size_t>(m0 + m) * p.N + n, f32_to_bf16(y));
+                continue;
+              }
+              if (p.out32) p.out32[o] = y;
+              if (p.out) {
+                if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
+                p.out[o] = f32_to_bf16(y);
+              }
             }
           }
         }

@@ -438,16 +438,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
       if (*last_flag) {
         __threadfence();
         if (n < p.N) {
-          for (int m = 0; m < cols; ++m) {
-            float acc = 0.f;
-            for (int s = 0; s < splits; ++s)
-              acc += __ldcg(p.ws + (static_cast<size_t>(s) * p.T + m0 + m) * p.N + n);
-            const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
-            float y = acc * p.alpha;
-            if (p.out32) p.out32[o] = y;
-            if (p.out) {
-              if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
-              p.out[o] = f32_to_bf16(y);
+          // 4 rows x 4 splits of partials are requested together and added in ascending split order (the sum of a
+          // plain loop, without one L2 round trip per (row, split))
+          for (int mb = 0; mb < cols; mb += 4) {
+            float acc[4];
+#pragma unroll
+            for (int mm = 0; mm < 4; ++mm) acc[mm] = 0.f;
+            for (int s0 = 0; s0 < splits; s0 += 4) {
+              float t[4][4];
+#pragma unroll
+              for (int mm = 0; mm < 4; ++mm) {
+#pragma unroll
+                for (int ss = 0; ss < 4; ++ss) {
+                  const bool live = mb + mm < cols && s0 + ss < splits;
+                  t[mm][ss] = live ? __ldcg(p.ws + (static_cast<size_t>(s0 + ss) * p.T + m0 + mb + mm) * p.N + n) : 0.f;
+                }
+              }
+#pragma unroll
+              for (int mm = 0; mm < 4; ++mm) {
+#pragma unroll
+                for (int ss = 0; ss < 4; ++ss) acc[mm] += t[mm][ss];
+              }
+            }
+#pragma unroll
+            for (int mm = 0; mm < 4; ++mm) {
+              const int m = mb + mm;
+              if (m >= cols) break;
+              const size_t o = static_cast<size_t>(m0 + m) * p.ldc + n;
+              float y = acc[mm] * p.alpha;
+              if (p.out32) p.out32[o] = y;
+              if (p.out) {
+                if (p.resid) y = bf16_to_f32(p.resid[o]) + bf16_to_f32(f32_to_bf16(y));
+                p.out[o] = f32_to_bf16(y);
+              }
             }
           }
         }

@@ -21,7 +21,35 @@ from ..models.dense import DenseModel
 from ..runtime import rt
 
 
-class ReferenceEngine(rt.SchedulerEngine):
+class EmbedSplice:
+    """Per-request input-embedding overrides (image rows), shared by the engines behind the scheduler.
+
+    The serving layer computes an image's rows with the vision tower and registers them under the request id before it
+    submits the request; the scheduler's `open(slot, id)` binds them to the slot, and every prefill chunk of the slot
+    hands the spans to the model, which writes them over the token embeddings of the covered positions.  Towards the
+    scheduler an image position carries a pseudo token id >= vocab derived from the image's content hash, so that the
+    prefix cache tells two images apart; `_real_ids` maps those ids to the family's image pad id before they reach
+    the embedding table.  (reference counterparts: src/models/*/image_prefill.cpp, the image embedding splice in
+    run_rows, src/serve/vision_frontend.cpp span bookkeeping.)"""
+
+    def _splice_init(self, slots: int, vocab: int, pad_id: int = 0) -> None:
+        self._embeds_by_id = {}
+        self._slot_embeds = [None] * slots
+        self._vocab, self._pad_id = vocab, pad_id
+
+    def set_embeds(self, request_id: str, spans) -> None:
+        """spans: [(start position in the prompt, rows [n, hidden])]."""
+        self._embeds_by_id[request_id] = list(spans)
+
+    def _splice_open(self, slot: int, request_id: str) -> None:
+        self._slot_embeds[slot] = self._embeds_by_id.pop(request_id, None)
+
+    def _real_ids(self, tokens):
+        v, pad = self._vocab, self._pad_id
+        return [t if t < v else pad for t in tokens]
+
+
+class ReferenceEngine(EmbedSplice, rt.SchedulerEngine):
     def __init__(self, model: DenseModel, slots: int = 4, num_blocks: int = 256, block_tokens: int = 16,
                  max_context: int = 1024, all_reduce=None):
         super().__init__()
@@ -36,6 +64,10 @@ class ReferenceEngine(rt.SchedulerEngine):
         self.filled = [0] * slots
         self.pending: List[Optional[int]] = [None] * slots
         self.all_reduce = all_reduce
+        self._splice_init(slots, c.vocab)
+
+    def open(self, slot, request_id):
+        self._splice_open(slot, request_id)
 
     # ---- geometry
     def max_concurrent(self):
@@ -112,8 +144,8 @@ class ReferenceEngine(rt.SchedulerEngine):
                 kv.append((k, v))
             else:
                 kv.append(None)
-        logits, kv = self.m.forward_reference(torch.tensor(tokens, device=self.k.device), start_pos=n0, kv=kv,
-                                              all_reduce=self.all_reduce)
+        logits, kv = self.m.forward_reference(torch.tensor(self._real_ids(tokens), device=self.k.device), start_pos=n0,
+                                              kv=kv, all_reduce=self.all_reduce, embed_spans=self._slot_embeds[slot])
         n1 = n0 + len(tokens)
         pos = torch.arange(n0, n1, device=self.k.device)
         blk = idx[pos // self.bt]
@@ -158,7 +190,7 @@ class ReferenceEngine(rt.SchedulerEngine):
         return out
 
 
-class KernelEngine(rt.SchedulerEngine):
+class KernelEngine(EmbedSplice, rt.SchedulerEngine):
     """The CUDA engine behind the scheduler: chunked prefill and graph-replayed decode for arbitrary slot sets."""
 
     def __init__(self, engine, spec_drafts: int = 0):
@@ -178,6 +210,7 @@ class KernelEngine(rt.SchedulerEngine):
         self.spec_graphs = {}
         self.spec_proposed = self.spec_accepted = 0
         self.pending = [None] * engine.max_batch
+        self._splice_init(engine.max_batch, engine.model.cfg.vocab)
         self.filled = [0] * engine.max_batch
         b = engine.max_batch
         hb = max(b, engine.runner.max_logit_rows if self.spec_k else b)
@@ -270,6 +303,7 @@ class KernelEngine(rt.SchedulerEngine):
         self.by_id[request_id] = (params, grammar, prompt_ids)
 
     def open(self, slot, request_id):
+        self._splice_open(slot, request_id)
         cfg = self.by_id.pop(request_id, None)
         self.slot_cfg[slot] = None
         self.last_logprobs[slot] = None
@@ -324,7 +358,7 @@ class KernelEngine(rt.SchedulerEngine):
 
     def prefill(self, slot, tokens, pos, last):
         with self.timer.phase("prefill"):
-            first = self.e.prefill(slot, list(tokens), start_pos=pos)
+            first = self.e.prefill(slot, self._real_ids(tokens), start_pos=pos, embed_spans=self._slot_embeds[slot])
         self.filled[slot] = pos + len(tokens)
         if self.spec_k:
             if pos == 0:

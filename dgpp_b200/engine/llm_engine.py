@@ -71,10 +71,13 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
-    def prefill(self, slot: int, tokens: Sequence[int] | torch.Tensor, start_pos: int = 0) -> torch.Tensor:
+    def prefill(self, slot: int, tokens: Sequence[int] | torch.Tensor, start_pos: int = 0,
+                embed_spans=None) -> torch.Tensor:
         """Prefill request `slot` with `tokens` (host ints) at positions start_pos.. ; returns the device
-        tensor holding the greedy first token (int32, shape [1])."""
+        tensor holding the greedy first token (int32, shape [1]).  embed_spans: [(absolute start position, bf16 rows
+        [n, hidden] on the device)] whose rows replace the token embeddings of the positions they cover (images)."""
         n = len(tokens)
+        self.runner.embed_spans = embed_spans
         assert start_pos + n <= self.max_seq_len
         if not self.kv.reserve(slot, start_pos + n):
             raise RuntimeError("KV pool exhausted")
@@ -101,6 +104,7 @@ class LLMEngine:
                       chunk=(slot, start_pos + done))
             done += t
         self.lengths[slot] = start_pos + n
+        r.embed_spans = None
         return r.pick_id[:1]
 
     # ------------------------------------------------------------------ decode

@@ -49,6 +49,7 @@ class DenseRunner:
                 self.layers_fp4 = views
         self.act_terms = act_terms
         self.chunk = None
+        self.embed_spans = None        # [(absolute start position, bf16 rows [n, hidden])] of the request in prefill
         self._li = 0
         # decode: a projection can ask L2 for the next projection's weights while the small kernels between them
         # leave HBM idle.  Measured on the 27B-class model at C8 the hint LOSES (7.70 vs 7.43 ms per step: the requests
@@ -178,6 +179,13 @@ class DenseRunner:
         x, xn, delta = self.x[:rows], self.xn[:rows], self.delta[:rows]
         qkv, attn, gu, act = self.qkv[:rows], self.attn[:rows], self.gu[:rows], self.act[:rows]
         ops.embed_gather(tokens, m.embed, out=x)
+        if self.embed_spans and self.chunk is not None:
+            # precomputed input rows (image tokens) replace the gathered embeddings of the positions they cover
+            pos0 = self.chunk[1]
+            for p0, src in self.embed_spans:
+                a, b = max(p0, pos0), min(p0 + src.shape[0], pos0 + rows)
+                if a < b:
+                    x[a - pos0:b - pos0].copy_(src[a - p0:b - p0])
         have_delta = False
         pending = False
         splits = self.decode_splits if (decode and rows <= 256) else 1

@@ -207,7 +207,7 @@ class DenseModel:
     # ------------------------------------------------------------------ PyTorch oracle
     @torch.no_grad()
     def forward_reference(self, tokens: torch.Tensor, start_pos: int = 0, kv: Optional[list] = None,
-                          all_reduce=None, return_hidden: bool = False, lora=None):
+                          all_reduce=None, return_hidden: bool = False, lora=None, embed_spans=None):
         """Full-precision-accumulate reference of one request: tokens [T] at positions start_pos.. .
         `kv` is a list (per layer) of (k, v) fp32 tensors [Tk, hkv, d] that is extended in place; KV
         values go through the same FP8 round trip as the paged cache when cfg.kv_fp8.  `lora`: a bound
@@ -227,6 +227,12 @@ class DenseModel:
         d, hq, hkv = c.head_dim, self.hq_local, self.hkv_local
         pos = torch.arange(start_pos, start_pos + T, device=dev)
         x = ref.embed_gather(tokens.to(dev), self.embed)
+        # embed_spans: [(absolute start position, rows [n, hidden])] -- rows of an image (or any precomputed input
+        # embedding) replace the token embeddings of the positions they cover
+        for p0, rows in embed_spans or ():
+            a, b = max(p0, start_pos), min(p0 + rows.shape[0], start_pos + T)
+            if a < b:
+                x[a - start_pos:b - start_pos] = rows[a - p0:b - p0].to(x.dtype).to(dev)
         delta = None
         if kv is None:
             kv = [None] * c.layers

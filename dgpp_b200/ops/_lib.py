@@ -41,6 +41,11 @@ _SIGNATURES = {
     "dgpp_act_quant_nvfp4_cluster": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P, P, I, P],
     "dgpp_gemm_fp4_set_prefetch": [P, L],
     "dgpp_gemm_fp4_set_preload": [I],
+    "dgpp_vis_patchify": [P, P, I, I, I, I, P, P, P],
+    "dgpp_layernorm": [P, P, P, P, I, I, F, P],
+    "dgpp_bias_act": [P, P, P, I, I, I, P],
+    "dgpp_vis_qkv_split_rope": [P, P, P, P, P, P, P, I, I, I, I, F, P],
+    "dgpp_softmax_rows": [P, I, I, I, P],
     "dgpp_gemm_fp4_set_trace": [P],
     "dgpp_gemm_fp4": [I, P, P, P, I, I, P, P, F, P, P, P, I, I, I, I, I, P, P, P, P],
     "dgpp_graph_begin_capture": [P],

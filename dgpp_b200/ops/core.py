@@ -302,14 +302,17 @@ def pick_cluster_splits(rows: int, n: int, k: int, bn: int) -> int:
 # Split-K policy of the block-scaled GEMM in the weight-streaming regime.  "resident": split until one resident wave
 # (two CTAs per SM) covers the problem, so that with the pre-wait weight preload most of a CTA's K range is already
 # in its ring when the activations arrive; "legacy": split only long-K, few-tile problems.
-FP4_SPLIT_POLICY = os.environ.get("DGPP_FP4_SPLITS", "legacy")
+# Measured on the 27B-class decode step: C8 7.14 ms legacy / 7.34 ms resident, C1 165.7 / 169.8 tok/s -- the fold's
+# fences and counter round trip cost more than the shorter K range saves once 8 rows share the weights, so "auto"
+# takes resident for a single row and legacy otherwise.
+FP4_SPLIT_POLICY = os.environ.get("DGPP_FP4_SPLITS", "auto")
 
 
 def pick_splits_fp4(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:
     """Split K for few-tile problems (the deterministic fold costs a few microseconds)."""
     tiles = math.ceil(n / 128) * math.ceil(rows / bn)
     stages = k // 256
-    if FP4_SPLIT_POLICY == "resident":
+    if FP4_SPLIT_POLICY == "resident" or (FP4_SPLIT_POLICY == "auto" and rows == 1):
         if tiles > sms:
             return 1
         return max(1, min(2 * sms // tiles, stages // 2, 8))
@@ -405,6 +408,50 @@ def attn_prefill_tc(q, q_stride: int, cache, block_table_row, pos0: int, hq: int
          ptr(block_table_row), ptr(out), T, pos0, hq, hkv, d, cache.page, block_table_row.numel(), cache.k.shape[0],
          float(scale), window, stream_ptr())
     return out
+
+
+# ---------------------------------------------------------------------------------------------- vision tower
+def vis_patchify(canvas: torch.Tensor, out: torch.Tensor, patch: int, merge: int, mean, std) -> torch.Tensor:
+    """uint8 canvas [H, W, 3] -> normalised bf16 patch rows [patches, 3 * patch^2] (merge groups contiguous)."""
+    import ctypes
+    assert canvas.dtype == torch.uint8 and canvas.is_contiguous() and out.is_contiguous()
+    H, W, _ = canvas.shape
+    m3, s3 = (ctypes.c_float * 3)(*mean), (ctypes.c_float * 3)(*std)
+    call("dgpp_vis_patchify", ptr(canvas), ptr(out), H, W, patch, merge, ctypes.addressof(m3), ctypes.addressof(s3),
+         stream_ptr())
+    return out
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float = 1e-6,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(x, torch.bfloat16, "x")
+    assert x.is_contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    call("dgpp_layernorm", ptr(x), ptr(w), ptr(b), ptr(out), x.shape[0], x.shape[1], float(eps), stream_ptr())
+    return out
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], resid: Optional[torch.Tensor] = None, act: int = 0):
+    """In place: x = resid + act(x + bias); act 0 none, 1 GELU (erf), 2 GELU (tanh)."""
+    _chk(x, torch.bfloat16, "x")
+    assert x.is_contiguous() and (resid is None or resid.is_contiguous())
+    call("dgpp_bias_act", ptr(x), ptr(bias), ptr(resid), x.shape[0], x.shape[1], act, stream_ptr())
+    return x
+
+
+def vis_qkv_split_rope(qkv, bias, pos_y, pos_x, q_h, k_h, vt_h, heads: int, d: int, theta: float) -> None:
+    """[T, 3 * heads * d] -> head-major q / k with 2-D RoPE and V transposed [heads, d, T_pad]."""
+    T = qkv.shape[0]
+    call("dgpp_vis_qkv_split_rope", ptr(qkv), ptr(bias), ptr(pos_y), ptr(pos_x), ptr(q_h), ptr(k_h), ptr(vt_h), T,
+         vt_h.shape[2], heads, d, float(theta), stream_ptr())
+
+
+def softmax_rows(s: torch.Tensor, cols: int) -> torch.Tensor:
+    """In-place softmax over the first `cols` columns of every row of the bf16 matrix s; the rest becomes zero."""
+    _chk(s, torch.bfloat16, "s")
+    call("dgpp_softmax_rows", ptr(s), s.shape[0], cols, s.stride(0), stream_ptr())
+    return s
 
 
 # ---------------------------------------------------------------------------------------------- mixture of experts

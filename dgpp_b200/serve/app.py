@@ -74,8 +74,9 @@ class Server:
     def __init__(self, engine, tokenizer, template_src: str = DEFAULT_TEMPLATE, model_name: str = "dgpp-b200",
                  host: str = "127.0.0.1", port: int = 0, eos_ids: Optional[List[int]] = None,
                  default_max_tokens: int = 256, sched_config=None, tool_format=None, constrain_tools: bool = False,
-                 world_leader=None):
+                 world_leader=None, vision=None):
         self.engine, self.tok = engine, tokenizer
+        self.vision = vision                 # serve.vision_frontend.VisionFrontend: image parts of chat messages
         self.template = rt.ChatTemplate(template_src)
         self.model_name = model_name
         self.eos_ids = eos_ids or []
@@ -209,6 +210,7 @@ class Server:
 
     def _submit(self, conn: int, body: str, chat: bool) -> None:
         r = rt.parse_chat_request(body) if chat else rt.parse_completion_request(body)
+        prepared = None                      # vision: prompt ids + the images' embedding spans
         if chat:
             ctx = {"messages": json.loads(r["messages_json"]), "add_generation_prompt": True}
             tools = json.loads(r["tools_json"])
@@ -217,7 +219,23 @@ class Server:
             kw = json.loads(r["chat_template_kwargs_json"])
             if kw:
                 ctx.update(kw)
-            ids = self.tok.encode(self.template.render_json(json.dumps(ctx)))
+            if self.vision is not None and self.vision.has_images(ctx["messages"]):
+                from .image_inputs import ImageInputError
+                if self.world is not None:
+                    raise rt.ApiError(400, rt.error_json(400, "images are not served by multi-rank deployments yet",
+                                                         param="messages"))
+                try:
+                    prepared = self.vision.prepare_chat(
+                        ctx["messages"], lambda msgs: self.template.render_json(json.dumps({**ctx, "messages": msgs})),
+                        self.tok.encode)
+                except ImageInputError as e:
+                    raise rt.ApiError(400, rt.error_json(400, str(e), param=e.param)) from None
+                ids = prepared.ids
+            else:
+                if any(m.get("parts") for m in ctx["messages"]):
+                    raise rt.ApiError(400, rt.error_json(400, "this model does not accept image, audio, video or file "
+                                                         "content parts", param="messages"))
+                ids = self.tok.encode(self.template.render_json(json.dumps(ctx)))
         elif r["prompt_ids"]:
             ids = list(r["prompt_ids"])
         else:
@@ -238,8 +256,13 @@ class Server:
         if r["stream"]:
             self.http.stream_begin(conn)
         params, schema = self._sampling_of(r)
+        real_ids = prepared.real_ids if prepared is not None else ids
+        if prepared is not None:
+            self.groups[group]["image_tokens"] = prepared.image_tokens
         for i in range(r["n"]):
             rid = f"{group}-{i}"
+            if prepared is not None:
+                self.engine.set_embeds(rid, prepared.spans)
             tool_mode = self._tool_constraint(r) if chat else None
             if (params is not None or schema is not None or tool_mode is not None) and hasattr(self.engine, "configure"):
                 if params is not None and r["n"] > 1 and r["seed"] is not None:
@@ -255,7 +278,7 @@ class Server:
                     spec = ["json", schema]
                 if self.world is not None:
                     self.world.configure(rid, None if params is None else dict(params.__dict__), spec, ids)
-                self.engine.configure(rid, params, grammar, ids)
+                self.engine.configure(rid, params, grammar, real_ids)
             self.live[rid] = _Live(rid, conn, r, i, group, len(ids), created, rt.StreamDecoder(self.tok, True),
                                    rt.StopScanner(list(r["stop"])), t_submit=time.time())
             if chat and r["tools_json"] not in ("null", "[]") and json.loads(r["tool_choice_json"]) != "none":
@@ -440,6 +463,8 @@ def main(argv=None) -> int:
     ap.add_argument("--model", default="tiny", choices=["tiny", "fake", "hybrid-tiny"])
     ap.add_argument("--slots", type=int, default=8)
     ap.add_argument("--config", default="", help="deployment JSON (see dgpp_b200.cli resolve); overrides the flags above")
+    ap.add_argument("--vision", action="store_true",
+                    help="tiny model only: attach a random-init vision tower so that chat messages accept image_url parts")
     args = ap.parse_args(argv)
     if args.config:
         return serve_deployment(args.config)
@@ -472,7 +497,11 @@ def main(argv=None) -> int:
         else:
             cfg = DenseConfig.tiny(vocab=4096, weight_fmt="bf16")
             eng = ReferenceEngine(DenseModel.random_init(cfg, device="cpu", seed=0, std=0.05), slots=args.slots)
-    srv = Server(eng, tok, model_name=f"dgpp-b200-{args.model}", host=args.host, port=args.port, eos_ids=[257])
+    vision = None
+    if args.vision and args.model == "tiny":
+        vision = tiny_vision_frontend(cfg, "cuda" if torch.cuda.is_available() else "cpu")
+    srv = Server(eng, tok, model_name=f"dgpp-b200-{args.model}", host=args.host, port=args.port, eos_ids=[257],
+                 vision=vision)
     print(f"listening on http://{args.host}:{srv.start()}", flush=True)
     try:
         while True:
@@ -480,6 +509,19 @@ def main(argv=None) -> int:
     except KeyboardInterrupt:
         srv.stop()
     return 0
+
+
+def tiny_vision_frontend(cfg, device: str, seed: int = 0):
+    """A random-init vision tower sized for a text config (smoke deployments and tests): 14-pixel patches, 2 x 2 merge,
+    image delimiters / pad on ids 1, 2, 3 of the text vocabulary."""
+    from ..models.vision import VisionConfig, VisionTower
+    from .image_inputs import ImagePreprocess
+    from .vision_frontend import VisionFrontend, VisionSpec
+
+    vc = VisionConfig(hidden=256, heads=4, layers=2, mlp=512, out_hidden=cfg.hidden)
+    tower = VisionTower.random_init(vc, device=device, seed=seed)
+    spec = VisionSpec(start_id=1, pad_id=2, end_id=3, preprocess=ImagePreprocess(grid=vc.grid, min_tokens=4, max_tokens=256))
+    return VisionFrontend(tower, spec, cfg.vocab)
 
 
 def serve_deployment(config_path: str) -> int:
