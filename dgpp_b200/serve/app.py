@@ -74,9 +74,11 @@ class Server:
     def __init__(self, engine, tokenizer, template_src: str = DEFAULT_TEMPLATE, model_name: str = "dgpp-b200",
                  host: str = "127.0.0.1", port: int = 0, eos_ids: Optional[List[int]] = None,
                  default_max_tokens: int = 256, sched_config=None, tool_format=None, constrain_tools: bool = False,
-                 world_leader=None, vision=None):
+                 world_leader=None, vision=None, files=None):
         self.engine, self.tok = engine, tokenizer
         self.vision = vision                 # serve.vision_frontend.VisionFrontend: image parts of chat messages
+        from .file_inputs import FileInputs
+        self.files = files or FileInputs()   # the /v1/files store and `file` content parts
         self.template = rt.ChatTemplate(template_src)
         self.model_name = model_name
         self.eos_ids = eos_ids or []
@@ -201,12 +203,68 @@ class Server:
             self.http.respond(conn, 200, "application/json", body.encode())
         elif method == "GET" and path == "/metrics/prometheus":
             self.http.respond(conn, 200, "text/plain; version=0.0.4", self.metrics.prometheus(self.sched.meters()).encode())
+        elif path == "/v1/files" or path.startswith("/v1/files/"):
+            self._files_route(conn, method, path, req)
         elif method == "POST" and path in ("/v1/chat/completions", "/v1/completions"):
             self._submit(conn, req["body"].decode("utf-8", "replace"), chat=path.endswith("chat/completions"))
         elif path in ("/v1/chat/completions", "/v1/completions", "/health", "/v1/models"):
             self.http.respond(conn, 405, "application/json", rt.error_json(405, "method not allowed").encode())
         else:
             self.http.respond(conn, 404, "application/json", rt.error_json(404, f"unknown route {path}").encode())
+
+    def _files_route(self, conn: int, method: str, path: str, req: dict) -> None:
+        """/v1/files: upload (multipart: file, purpose), list, metadata, content, delete."""
+        from .file_inputs import FileInputError, parse_multipart
+        try:
+            if path == "/v1/files" and method == "POST":
+                hdrs = {str(k).lower(): v for k, v in dict(req.get("headers") or {}).items()}
+                fields = parse_multipart(req["body"], hdrs.get("content-type", ""))
+                if "file" not in fields:
+                    raise FileInputError("the upload has no 'file' field", "file")
+                name, data = fields["file"]
+                purpose = fields.get("purpose", (None, b"user_data"))[1].decode("utf-8", "replace")
+                out = self.files.upload(data, name or "upload", purpose)
+            elif path == "/v1/files" and method == "GET":
+                out = {"object": "list", "data": self.files.list()}
+            elif method == "GET" and path.endswith("/content"):
+                fid = path[len("/v1/files/"):-len("/content")]
+                self.http.respond(conn, 200, "application/octet-stream", self.files.content(fid))
+                return
+            elif method == "GET":
+                out = self.files.get(path[len("/v1/files/"):])
+            elif method == "DELETE":
+                out = self.files.delete(path[len("/v1/files/"):])
+            else:
+                self.http.respond(conn, 405, "application/json", rt.error_json(405, "method not allowed").encode())
+                return
+            self.http.respond(conn, 200, "application/json", json.dumps(out).encode())
+        except FileInputError as e:
+            self.http.respond(conn, e.status, "application/json",
+                              rt.error_json(e.status, str(e), param=e.param, code=e.code).encode())
+
+    def _inline_files(self, messages: list) -> None:
+        """Replace every `file` content part by the file's text, in place and in order."""
+        from .file_inputs import FileInputError
+        budget = [self.files.cfg.max_request_bytes]
+        for mi, m in enumerate(messages):
+            parts = m.get("parts")
+            if not parts or not any(p.get("type") == "file" for p in parts):
+                continue
+            new = []
+            for pi, part in enumerate(parts):
+                if part.get("type") == "file":
+                    try:
+                        text = self.files.part_text(part, f"messages[{mi}].content[{pi}]", budget)
+                    except FileInputError as e:
+                        raise rt.ApiError(e.status, rt.error_json(e.status, str(e), param=e.param, code=e.code)) from None
+                    new.append({"type": "text", "text": text})
+                else:
+                    new.append(part)
+            if all(p.get("type") == "text" for p in new):
+                m["content"] = "".join(p["text"] for p in new)
+                m.pop("parts", None)
+            else:
+                m["parts"] = new
 
     def _submit(self, conn: int, body: str, chat: bool) -> None:
         r = rt.parse_chat_request(body) if chat else rt.parse_completion_request(body)
@@ -219,6 +277,7 @@ class Server:
             kw = json.loads(r["chat_template_kwargs_json"])
             if kw:
                 ctx.update(kw)
+            self._inline_files(ctx["messages"])
             if self.vision is not None and self.vision.has_images(ctx["messages"]):
                 from .image_inputs import ImageInputError
                 if self.world is not None:
