@@ -206,10 +206,23 @@ def main(argv=None) -> int:
             p.add_argument("--run-dir", default=DEFAULT_RUN_DIR)
     p = sub.add_parser("doctor")
     p.add_argument("--cache-dir", default="")
-    for name in ("status", "down"):
+    for name in ("status", "down", "metrics", "api-check"):
         p = sub.add_parser(name)
         p.add_argument("--run-dir", default=DEFAULT_RUN_DIR)
+        if name == "metrics":
+            p.add_argument("--prometheus", action="store_true")
     a = ap.parse_args(argv)
+    if a.cmd in ("metrics", "api-check"):
+        # the running deployment's own endpoints (its address comes from the run directory's resolved config)
+        cfg = json.load(open(os.path.join(a.run_dir, "resolved.json")))
+        base = f"http://{cfg['host']}:{cfg['port']}"
+        if a.cmd == "api-check":
+            from .tools import api_check
+            return api_check.main(["--url", base])
+        with urllib.request.urlopen(base + ("/metrics/prometheus" if a.prometheus else "/metrics"), timeout=5) as r:
+            body = r.read().decode()
+        print(body if a.prometheus else json.dumps(json.loads(body), indent=1))
+        return 0
     if a.cmd == "resolve":
         cfg, digest = resolve(a.deployment, a.env, a.overrides)
         print(json.dumps({"config": cfg, "digest": f"{digest:016x}"}, indent=1))
