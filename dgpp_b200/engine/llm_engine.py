@@ -45,6 +45,9 @@ class LLMEngine:
         # split-KV decode attention: one wave of CTAs (two resident per SM) is the sweet spot -- measured at 8 rows x 8 kv
         # heads: 13.6 us with 4 splits at ctx 2048 (17.6 us with 8), 33 us with 4 at ctx 8192 (49 us with 16)
         splits = max(1, min(16, 296 // max(1, model.hkv_local * max_batch)))
+        import os
+        if os.environ.get("DGPP_DECODE_SPLITS"):           # measurement override
+            splits = max(1, int(os.environ["DGPP_DECODE_SPLITS"]))
         self.decode_pdl = decode_pdl
         self.runner = DenseRunner(model, self.kv, rows, reducer=reducer, decode_splits=splits, decode_rows=max_batch,
                                   act_terms=act_terms, fuse_ar=fuse_ar)
