@@ -4,8 +4,10 @@
 
 Checks, on N ranks: the peer-memory one-shot all-reduce against a fixed-order fp32 fold and NCCL (values and time), the
 vocab-sharded pick merge, the fused GEMM -> reduce-scatter -> all-gather path against GEMM + fold, and a tensor-parallel
-engine run (fused and separate collectives, twice each) for bit-identical tokens across ranks and runs.  All times are
-CUDA-event times, maximum over ranks.  TP_HEADS sets the tiny model's head count (default 8).
+engine run (separate collectives, the GEMM-epilogue push + fold, and the persistent decode-layer kernel with its
+in-kernel cross-rank fold; twice each) for bit-identical tokens across ranks and runs.  All times are CUDA-event times,
+maximum over ranks.  TP_HEADS sets the tiny model's head count (default 8).  Every check that prints False makes
+the process exit 1; `--out FILE` also appends rank 0's result lines to FILE.
 (reference counterparts: apps/bus_check.cpp, apps/nic_regress.cpp.)
 """
 
@@ -17,7 +19,26 @@ import torch
 import torch.distributed as dist
 
 
+FAILS = []
+OUT = None
+
+
+def say(*parts, ok=True) -> None:
+    """Print a result line on rank 0 (and append it to the --out file); ok=False records a failed check."""
+    line = " ".join(str(p) for p in parts)
+    if not ok:
+        FAILS.append(line)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(line, flush=True)
+        if OUT:
+            with open(OUT, "a") as f:
+                f.write(line + "\n")
+
+
 def main() -> int:
+    global OUT
+    if "--out" in sys.argv:
+        OUT = sys.argv[sys.argv.index("--out") + 1]
     rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"]); local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local); dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
@@ -36,7 +57,7 @@ def main() -> int:
         same = torch.equal(y, want)
         ys = [torch.empty_like(y) for _ in range(world)]; dist.all_gather(ys, y)
         ident = all(torch.equal(ys[0], q) for q in ys)
-        if rank == 0: print(f"all_reduce rows={rows}: matches fixed-order fold={same} identical across ranks={ident}", flush=True)
+        say(f"all_reduce rows={rows}: matches fixed-order fold={same} identical across ranks={ident}", ok=same and ident)
     # timing vs NCCL (graph-captured, 50 calls)
     for rows in (1, 8, 64):
         x = torch.randn(rows, 5120, device=dev).to(BF)
@@ -50,7 +71,7 @@ def main() -> int:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(); g.replay(); g.replay(); b.record(); torch.cuda.synchronize()
             t = torch.tensor([a.elapsed_time(b) / 100 * 1000], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            if rank == 0: print(f"  {name} all_reduce rows={rows} (x5120 bf16): {t.item():.1f} us (max over ranks)", flush=True)
+            say(f"  {name} all_reduce rows={rows} (x5120 bf16): {t.item():.1f} us (max over ranks)")
     ops.check_status()
     # pick merge
     ids = torch.arange(8, device=dev, dtype=torch.int32) + 1000 * rank
@@ -60,7 +81,7 @@ def main() -> int:
     red.merge_picks(ids, vals); torch.cuda.synchronize(); ops.check_status()
     GV = torch.stack(gv); GI = torch.stack(gi); best = torch.argmax(GV, 0)
     ok = torch.equal(ids, GI.gather(0, best[None])[0])
-    if rank == 0: print("pick merge ok:", ok, flush=True)
+    say("pick merge ok:", ok, ok=ok)
     # fused GEMM -> reduce-scatter -> all-gather vs GEMM + fixed-order fold
     from dgpp_b200.quant.formats import random_quant_linear
     for T in (100, 128, 300, 2048):
@@ -81,7 +102,7 @@ def main() -> int:
             ok = torch.equal(x, want)
             xs = [torch.empty_like(x) for _ in range(world)]; dist.all_gather(xs, x)
             ident = all(torch.equal(xs[0], q) for q in xs)
-            if rank == 0: print(f"rs_ag T={T} rep={rep}: matches fold={ok} identical across ranks={ident} maxdiff={(x.float()-want.float()).abs().max().item():.4f}", flush=True)
+            say(f"rs_ag T={T} rep={rep}: matches fold={ok} identical across ranks={ident} maxdiff={(x.float()-want.float()).abs().max().item():.4f}", ok=ok and ident)
         # mixed with the one-shot all-reduce (shared epoch / slots)
         y = part.clone(); red.all_reduce(y); torch.cuda.synchronize(); ops.check_status()
     # timing: GEMM + all_reduce vs GEMM-push + rs_ag at a prefill chunk
@@ -107,7 +128,7 @@ def main() -> int:
         for _ in range(10): fn()
         e1.record(); torch.cuda.synchronize()
         t = torch.tensor([e0.elapsed_time(e1) / 10 * 1000], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        if rank == 0: print(f"  {name} T={T} N=5120 K={w.k}: {t.item():.1f} us (max over ranks)", flush=True)
+        say(f"  {name} T={T} N=5120 K={w.k}: {t.item():.1f} us (max over ranks)")
     ops.check_status()
     # TP engine vs reference tokens; fused GEMM->all-reduce vs separate all-reduce kernel, each run twice
     from dgpp_b200.engine.llm_engine import LLMEngine
@@ -115,20 +136,29 @@ def main() -> int:
     heads = int(os.environ.get("TP_HEADS", "8"))
     cfg = DenseConfig.tiny(hidden=512, q_heads=heads, kv_heads=heads, head_dim=128, ffn=2048, vocab=4096, layers=3)
     model = DenseModel.random_init(cfg, device=dev, seed=0, std=0.05, tp_rank=rank, tp_size=world)
-    if rank == 0: print("local q heads (padded):", model.hq_local, "o.k", model.layers[0].o.k, "down.k", model.layers[0].down.k, flush=True)
+    say("local q heads (padded):", model.hq_local, "o.k", model.layers[0].o.k, "down.k", model.layers[0].down.k)
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (150, 33)]
+    # (GEMM-epilogue push + fold, persistent decode-layer kernel): separate collectives, push + fold, layer kernel
+    modes = [("separate", False, False), ("push+fold", True, False), ("layer kernel", True, True)]
     runs = []
-    for fuse in (False, True, False, True):
-        eng = LLMEngine(model, max_batch=2, max_seq_len=512, prefill_chunk=128, reducer=red, fuse_ar=fuse)
+    for name, fuse, fused in modes + modes:
+        eng = LLMEngine(model, max_batch=2, max_seq_len=512, prefill_chunk=128, reducer=red, fuse_ar=fuse,
+                        fused_decode=fused)
+        if fused and not eng.runner._fused_ok(2):
+            say("layer kernel does not apply to this shard shape (skipped)")
         runs.append(eng.generate(prompts, max_tokens=12))
         ops.check_status()
         del eng
     objs = [None] * world; dist.all_gather_object(objs, runs)
-    if rank == 0:
-        print("tokens identical across ranks:", all(o == objs[0] for o in objs), flush=True)
-        print("unfused run1 == run2:", runs[0] == runs[2], " fused run1 == run2:", runs[1] == runs[3], " fused == unfused:", runs[0] == runs[1], flush=True)
-        for i, r in enumerate(runs): print("  run", i, "fused" if i % 2 else "unfused", r[0], flush=True)
+    k = len(modes)
+    same_ranks = all(o == objs[0] for o in objs)
+    say("tokens identical across ranks:", same_ranks, ok=same_ranks)
+    for i, (name, _, _) in enumerate(modes):
+        rep = runs[i] == runs[i + k]
+        agree = runs[i] == runs[0]
+        say(f"{name}: run1 == run2: {rep}  == separate collectives: {agree}", ok=rep and agree)
+    for i, r in enumerate(runs[:k]): say("  ", modes[i][0], r[0])
     # scheduler + kernel engine on every rank: the same prompt three times (prefix cache off, then on) must give the
     # same tokens every time on every rank (the cached runs attach shared KV blocks and prefill only the tail)
     from dgpp_b200.engine.adapters import KernelEngine
@@ -144,14 +174,16 @@ def main() -> int:
             outs.append([a for kind, r, a, b in sched.events() if kind == "token"])
         ops.check_status()
         allo = [None] * world; dist.all_gather_object(allo, outs)
-        if rank == 0:
-            print(f"scheduler prefix_cache={prefix}: runs equal={outs[0] == outs[1] == outs[2]} ranks equal={all(o == allo[0] for o in allo)} "
-                  f"hit tokens={sched.meters()['prefix_hit_tokens']}", flush=True)
-            if not (outs[0] == outs[1] == outs[2]):
-                for o in outs: print("   ", o, flush=True)
+        eq, req = outs[0] == outs[1] == outs[2], all(o == allo[0] for o in allo)
+        say(f"scheduler prefix_cache={prefix}: runs equal={eq} ranks equal={req} "
+            f"hit tokens={sched.meters()['prefix_hit_tokens']}", ok=eq and req)
+        if not eq:
+            for o in outs: say("   ", o)
         del sched, keng
     dist.barrier(); red.close(); dist.destroy_process_group()
-
+    if FAILS:
+        print(f"rank {rank}: {len(FAILS)} check(s) failed", file=sys.stderr, flush=True)
+        return 1
     return 0
 
 

@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
   }
   if (MODE == 2) {
     const bf16* rr = a.in + static_cast<size_t>(t) * a.in_stride + k0;
-    float ss = 0.f;
+    float ss = 0.f, pm = 0.f;
     for (int i = tid; i < nvec; i += kAqThreads) {
       Pack16 x;
       x.u = reinterpret_cast<const uint4*>(rr)[i];
@@ -140,14 +140,28 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
         for (int j = 0; j < 8; ++j) x.h[j] = f32_to_bf16(bf16_to_f32(x.h[j]) + bf16_to_f32(d.h[j]));
         reinterpret_cast<uint4*>(a.resid_out + static_cast<size_t>(t) * K + k0)[i] = x.u;
       }
+      Pack16 wv;
+      wv.u = reinterpret_cast<const uint4*>(a.w + k0)[i];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { const float f = bf16_to_f32(x.h[j]); ss += f * f; }
+      for (int j = 0; j < 8; ++j) {
+        const float f = bf16_to_f32(x.h[j]);
+        ss += f * f;
+        float gw = bf16_to_f32(wv.h[j]);
+        if (a.one_plus_w) gw += 1.f;
+        pm = fmaxf(pm, fabsf(f * gw));
+      }
       reinterpret_cast<uint4*>(seg)[i] = x.u;
     }
     ss = cta_reduce(ss, false);
+    pm = cta_reduce(pm, true);
     cluster_push(0, ss);
+    cluster_push(1, pm);
     cluster.sync();
     const float rstd = rsqrtf(cluster_fold(0, false) / static_cast<float>(K) + a.eps);
+    // Row scale from a bound instead of the exact maximum of the normalised row: |bf16(bf16(x rstd) w)| <=
+    // |x w| rstd (1 + 2^-8)^2, so max |x w| * rstd * 1.0079 covers every element (at most 0.8 % above the true
+    // maximum) and is known from this single pass: no second row-wide reduction.
+    amax = cluster_fold(1, true) * rstd * 1.0079f;
     for (int i = tid; i < nvec; i += kAqThreads) {
       Pack16 x, ww;
       x.u = reinterpret_cast<const uint4*>(seg)[i];
@@ -158,7 +172,6 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
         float gw = bf16_to_f32(ww.h[j]);
         if (a.one_plus_w) gw += 1.f;
         x.h[j] = f32_to_bf16(nrm * gw);
-        amax = fmaxf(amax, fabsf(bf16_to_f32(x.h[j])));
       }
       reinterpret_cast<uint4*>(seg)[i] = x.u;
       if (a.x_out) reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(t) * K + k0)[i] = x.u;
@@ -212,10 +225,14 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
       if (a.x_out) reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(t) * K + k0)[i] = x.u;
     }
   }
-  amax = cta_reduce(amax, true);
-  cluster_push(1, amax);
-  cluster.sync();
-  amax = cluster_fold(1, true);
+  if (MODE != 2) {
+    amax = cta_reduce(amax, true);
+    cluster_push(1, amax);
+    cluster.sync();
+    amax = cluster_fold(1, true);
+  } else {
+    __syncthreads();      // the normalised segment is complete in shared memory
+  }
   const float gs = amax > 0.f ? amax / (6.f * 256.f) : 1.f;
   if (c == 0 && tid == 0) a.g[t] = gs;
   const float inv_g = 1.f / gs;

@@ -524,10 +524,10 @@ __global__ void __launch_bounds__(256) fused_act_quant_kernel(QuantArgs a) {
     __syncthreads();
     return r;
   };
-  float amax = 0.f;
+  float amax = 0.f, bound = 0.f;
   if (MODE == 2) {
     const bf16* rr = a.in + static_cast<size_t>(t) * a.in_stride;
-    float ss = 0.f;
+    float ss = 0.f, pm = 0.f;
     for (int i = tid; i < nvec; i += 256) {
       Pack16 x;
       x.u = reinterpret_cast<const uint4*>(rr)[i];
@@ -538,11 +538,21 @@ __global__ void __launch_bounds__(256) fused_act_quant_kernel(QuantArgs a) {
         for (int j = 0; j < 8; ++j) x.h[j] = f32_to_bf16(bf16_to_f32(x.h[j]) + bf16_to_f32(d.h[j]));
         reinterpret_cast<uint4*>(a.resid_out + static_cast<size_t>(t) * K)[i] = x.u;
       }
+      Pack16 wv;
+      wv.u = reinterpret_cast<const uint4*>(a.w)[i];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { const float f = bf16_to_f32(x.h[j]); ss += f * f; }
+      for (int j = 0; j < 8; ++j) {
+        const float f = bf16_to_f32(x.h[j]);
+        ss += f * f;
+        float gw = bf16_to_f32(wv.h[j]);
+        if (a.one_plus_w) gw += 1.f;
+        pm = fmaxf(pm, fabsf(f * gw));
+      }
       reinterpret_cast<uint4*>(row_s)[i] = x.u;
     }
     const float rstd = rsqrtf(block_reduce(ss, false) / static_cast<float>(K) + a.eps);
+    // row scale from the bound max |x w| * rstd * 1.0079 (see act_quant_cluster_kernel): no second reduction pass
+    bound = block_reduce(pm, true) * rstd * 1.0079f;
     for (int i = tid; i < nvec; i += 256) {
       Pack16 x, ww;
       x.u = reinterpret_cast<const uint4*>(row_s)[i];
@@ -553,7 +563,6 @@ __global__ void __launch_bounds__(256) fused_act_quant_kernel(QuantArgs a) {
         float gw = bf16_to_f32(ww.h[j]);
         if (a.one_plus_w) gw += 1.f;
         x.h[j] = f32_to_bf16(nrm * gw);
-        amax = fmaxf(amax, fabsf(bf16_to_f32(x.h[j])));
       }
       reinterpret_cast<uint4*>(row_s)[i] = x.u;
       if (a.x_out) reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(t) * K)[i] = x.u;
@@ -581,7 +590,7 @@ __global__ void __launch_bounds__(256) fused_act_quant_kernel(QuantArgs a) {
     }
   }
   __syncthreads();
-  amax = block_reduce(amax, true);
+  amax = MODE == 2 ? bound : block_reduce(amax, true);
   const float gs = amax > 0.f ? amax / (6.f * 256.f) : 1.f;
   if (tid == 0) a.g[t] = gs;
   const float inv_g = 1.f / gs;

@@ -30,7 +30,7 @@ from .runner import DenseRunner
 class LLMEngine:
     def __init__(self, model: DenseModel, max_batch: int = 8, max_seq_len: int = 4096, prefill_chunk: int = 2048,
                  kv_blocks: Optional[int] = None, reducer=None, use_graphs: bool = True, ring_steps: int = 1024,
-                 decode_pdl: bool = True, act_terms: int = 3, fuse_ar: bool = True):
+                 decode_pdl: bool = True, act_terms: int = 3, fuse_ar: bool = True, fused_decode: bool = True):
         c = model.cfg
         self.model, self.max_batch, self.max_seq_len = model, max_batch, max_seq_len
         self.prefill_chunk = prefill_chunk
@@ -50,7 +50,7 @@ class LLMEngine:
             splits = max(1, int(os.environ["DGPP_DECODE_SPLITS"]))
         self.decode_pdl = decode_pdl
         self.runner = DenseRunner(model, self.kv, rows, reducer=reducer, decode_splits=splits, decode_rows=max_batch,
-                                  act_terms=act_terms, fuse_ar=fuse_ar)
+                                  act_terms=act_terms, fuse_ar=fuse_ar, fused_decode=fused_decode)
         self.use_graphs = use_graphs
         self.ring_steps = ring_steps
         i32 = dict(dtype=torch.int32, device=self.dev)

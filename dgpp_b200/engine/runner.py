@@ -24,7 +24,7 @@ BF = torch.bfloat16
 class DenseRunner:
     def __init__(self, model: DenseModel, kv: PagedKV, max_rows: int, reducer=None, decode_splits: int = 8,
                  decode_fp4: bool = True, act_terms: int = 3, attn_tc: bool = True,
-                 decode_rows: Optional[int] = None, fuse_ar: bool = True):
+                 decode_rows: Optional[int] = None, fuse_ar: bool = True, fused_decode: bool = True):
         self.m, self.kv, self.max_rows, self.reducer = model, kv, max_rows, reducer
         # decode rows (<= 64) run the linears on the block-scaled FP4 tensor-core path with the activations
         # expanded into `act_terms` residual NVFP4 terms; attention reads the FP8 cache through tcgen05
@@ -94,11 +94,117 @@ class DenseRunner:
         self.lora = None
         self.lora_scratch = torch.empty(R * 256, dtype=torch.float32, device=dev)
         self.qa = {}
+        # decode through the persistent per-layer kernel (ops.decode_layer) where it applies
+        self.fused_decode = fused_decode
+        self._fused_plans, self._fused_bufs = {}, None
         self.fp4_rows = min(64, decode_rows or max_rows)
         if self.decode_fp4:
             bn = min(64, ops.pick_bn(self.fp4_rows))
             for k in {H, self.hq * d, I}:
                 self.qa[k] = ops.QuantAct(bn, k, act_terms, bn, dev)
+
+    # ------------------------------------------------------------------ persistent decode-layer kernel
+    def _fused_ok(self, rows: int) -> bool:
+        """The persistent per-layer kernel serves decode batches of up to 16 rows of NVFP4 models with head_dim 128
+        and an FP8 cache; everything else (adapters, sink layers, NCCL reducer, wider batches) keeps the per-operator
+        launch sequence."""
+        m, c = self.m, self.m.cfg
+        if not (self.fused_decode and self.decode_fp4 and self.attn_tc and self.lora is None):
+            return False
+        if rows > 16 or self.d != 128 or not c.kv_fp8:
+            return False
+        if self.reducer is not None and getattr(self.reducer, "comm", None) is None:
+            return False
+        L0 = self.layers_fp4[0]
+        H, A, I = c.hidden, self.hq * self.d, L0.down.k
+        if any(k % 256 or k > 16384 for k in (H, A)) or I % 256 or L0.gate_up.n != 2 * I:
+            return False
+        return all(L.sink is None and w.fmt == "nvfp4" for L in self.layers_fp4
+                   for w in (L.qkv, L.o, L.gate_up, L.down))
+
+    def _fused_plan(self, rows: int, positions, row_req, splits: int):
+        key = (rows, positions.data_ptr(), row_req.data_ptr(), splits)
+        plan = self._fused_plans.get(key)
+        if plan is not None:
+            return plan
+        from ..ops.decode_layer import LayerLaunch
+        m, c, kv = self.m, self.m.cfg, self.kv
+        dev = m.embed.device
+        H, A, I = c.hidden, self.hq * self.d, self.layers_fp4[0].down.k
+        if self._fused_bufs is None:
+            qa = {nm: ops.QuantAct(16, k, 3, 16, dev) for nm, k in (("a", A), ("h", H), ("i", I))}
+            f32 = dict(dtype=torch.float32, device=dev)
+            self._fused_bufs = dict(qa=qa, ws=torch.empty(16 * 160 * 128, **f32), stats=torch.zeros(256, **f32),
+                                    hbuf=torch.empty(16, I, dtype=BF, device=dev),
+                                    amax=torch.zeros((I // 128) * 16, **f32))
+        fb = self._fused_bufs
+        qa = fb["qa"]
+        comm = getattr(self.reducer, "comm", None) if self.reducer is not None else None
+        tp = comm is not None
+        x, xn, qkv, attn = self.x[:rows], self.xn[:rows], self.qkv[:rows], self.attn[:rows]
+        layers = self.layers_fp4
+        n = len(layers)
+
+        def new():
+            ll = LayerLaunch(rows, x, H, c.eps, fb["ws"], fb["stats"], comm=comm)
+            ll.set_act(0, qa["a"]); ll.set_act(1, qa["h"]); ll.set_act(2, qa["i"])
+            return ll
+
+        def qkv_tail(ll, li):
+            """... in_norm of layer li -> qkv projection -> RoPE + KV append"""
+            L = layers[li]
+            ll.set_gemm(3, L.qkv, act=1)
+            ll.gemm(3)
+            ll.rope(3, qkv, positions, row_req, kv.block_table, m.inv_freq, kv.layers[li], self.hq, self.hkv, self.d,
+                    c.rot_dim or self.d, m.mscale, L.q_norm, L.k_norm)
+
+        launches = []
+        head = new()
+        head.rowq(2, mode=2, out_act=1, norm_w=layers[0].in_norm)
+        qkv_tail(head, 0)
+        launches.append(head)
+        for li, L in enumerate(layers):
+            ll = new()
+            if splits > 1:
+                ll.set_attention(self.att_ml, self.att_acc, splits, self.hq, self.d)
+                ll.rowq(0, mode=3, out_act=0)
+            else:
+                ll.set_attention(None, None, 1, self.hq, self.d)
+                ll.rowq(0, mode=0, out_act=0, inp=attn)
+            ll.set_gemm(0, L.o, act=0)
+            ll.gemm(0)
+            ll.rowq(1, mode=2, out_act=1, src_gemm=0, tp_fold=tp, norm_w=L.post_norm)
+            ll.set_gemm(1, L.gate_up, act=1, pair=True)
+            ll.set_swiglu(fb["hbuf"], fb["amax"], I, 2)
+            ll.gemm(1)
+            ll.unitq()
+            ll.set_gemm(2, L.down, act=2)
+            ll.gemm(2)
+            if li + 1 < n:
+                ll.rowq(2, mode=2, out_act=1, src_gemm=2, tp_fold=tp, norm_w=layers[li + 1].in_norm)
+                qkv_tail(ll, li + 1)
+            else:
+                ll.rowq(2, mode=2, out_act=-1, src_gemm=2, tp_fold=tp, norm_w=m.final_norm, x_out=xn)
+            launches.append(ll)
+        self._fused_plans[key] = launches
+        return launches
+
+    def _forward_fused(self, rows: int, tokens, positions, row_req, splits: int):
+        """Decode pass through the persistent per-layer kernels: 2 launches per layer (attention + everything
+        else).  Leaves the final-norm output in self.xn[:rows]."""
+        m, kv = self.m, self.kv
+        plan = self._fused_plan(rows, positions, row_req, splits)
+        plan[0].launch()                      # (self.x[:rows] already holds the gathered embeddings)
+        qkv, attn = self.qkv[:rows], self.attn[:rows]
+        for li, L in enumerate(self.layers_fp4):
+            if splits > 1:
+                ops.attn_decode_tc(qkv, qkv.stride(0), kv.layers[li], kv.block_table, row_req, positions, self.hq,
+                                   self.hkv, self.d, self.scale, splits=splits, scratch=(self.att_ml, self.att_acc),
+                                   window=L.window, partials_only=True)
+            else:
+                ops.attn_decode_tc(qkv, qkv.stride(0), kv.layers[li], kv.block_table, row_req, positions, self.hq,
+                                   self.hkv, self.d, self.scale, splits=1, out=attn, window=L.window)
+            plan[li + 1].launch()
 
     def linear(self, x, w, out, fp4: bool):
         if fp4 and w.fmt == "nvfp4" and w.k % 256 == 0:
@@ -192,7 +298,10 @@ class DenseRunner:
         fp4 = self.decode_fp4 and decode and rows <= self.fp4_rows and all(
             w.k % 256 == 0 for w in (m.layers[0].qkv, m.layers[0].o, m.layers[0].down))
         lora = self.lora
-        for li, L in enumerate(m.layers):
+        fused = fp4 and decode and self.embed_spans is None and self._fused_ok(rows)
+        if fused:
+            self._forward_fused(rows, tokens, positions, row_req, splits)
+        for li, L in enumerate(m.layers if not fused else ()):
             self._li = li
             if fp4:
                 pending = self._layer_fp4(self.layers_fp4[li], kv.layers[li], x, delta, have_delta, qkv, attn, gu, positions, row_req,
@@ -236,7 +345,8 @@ class DenseRunner:
             if self.reducer is not None:
                 self.reducer.all_reduce(delta)
             have_delta = True
-        ops.rmsnorm(x, m.final_norm, c.eps, delta=delta if have_delta else None, out=xn)
+        if not fused:
+            ops.rmsnorm(x, m.final_norm, c.eps, delta=delta if have_delta else None, out=xn)
         if logits_rows is None:
             logits_rows = slice(0, rows) if decode else slice(rows - 1, rows)
         hx = xn[logits_rows]
