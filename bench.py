@@ -86,6 +86,8 @@ def main():
     ap.add_argument("--also-c1", action="store_true", help="also time C=1 decode as an extra")
     ap.add_argument("--bf12-head", action="store_true",
                     help="keep the bf16 lm head in its lossless 12-bit resident form (same logits bit for bit)")
+    ap.add_argument("--layer-kernel", action="store_true",
+                    help="decode through the persistent decode-layer kernel instead of the per-operator launch sequence")
     ap.add_argument("--no-fuse-ar", action="store_true",
                     help="tensor parallel: separate all-reduce kernels instead of the GEMM-epilogue push + fold")
     args = ap.parse_args()
@@ -132,7 +134,7 @@ def main():
     prefill_lens = [int(x) for x in args.prefill_lens.split(",") if x]
     max_len = max([L + K + W + 8] + [p + 8 for p in prefill_lens])
     eng = LLMEngine(model, max_batch=C, max_seq_len=max_len, prefill_chunk=2048, reducer=reducer,
-                    fuse_ar=not args.no_fuse_ar)
+                    fuse_ar=not args.no_fuse_ar, fused_decode=args.layer_kernel)
 
     g = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab, (L,), generator=g).tolist() for _ in range(C)]

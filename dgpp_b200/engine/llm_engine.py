@@ -30,7 +30,7 @@ from .runner import DenseRunner
 class LLMEngine:
     def __init__(self, model: DenseModel, max_batch: int = 8, max_seq_len: int = 4096, prefill_chunk: int = 2048,
                  kv_blocks: Optional[int] = None, reducer=None, use_graphs: bool = True, ring_steps: int = 1024,
-                 decode_pdl: bool = True, act_terms: int = 3, fuse_ar: bool = True, fused_decode: bool = True):
+                 decode_pdl: bool = True, act_terms: int = 3, fuse_ar: bool = True, fused_decode: bool = False):
         c = model.cfg
         self.model, self.max_batch, self.max_seq_len = model, max_batch, max_seq_len
         self.prefill_chunk = prefill_chunk

@@ -24,7 +24,7 @@ BF = torch.bfloat16
 class DenseRunner:
     def __init__(self, model: DenseModel, kv: PagedKV, max_rows: int, reducer=None, decode_splits: int = 8,
                  decode_fp4: bool = True, act_terms: int = 3, attn_tc: bool = True,
-                 decode_rows: Optional[int] = None, fuse_ar: bool = True, fused_decode: bool = True):
+                 decode_rows: Optional[int] = None, fuse_ar: bool = True, fused_decode: bool = False):
         self.m, self.kv, self.max_rows, self.reducer = model, kv, max_rows, reducer
         # decode rows (<= 64) run the linears on the block-scaled FP4 tensor-core path with the activations
         # expanded into `act_terms` residual NVFP4 terms; attention reads the FP8 cache through tcgen05
@@ -94,7 +94,10 @@ class DenseRunner:
         self.lora = None
         self.lora_scratch = torch.empty(R * 256, dtype=torch.float32, device=dev)
         self.qa = {}
-        # decode through the persistent per-layer kernel (ops.decode_layer) where it applies
+        # decode through the persistent per-layer kernel (ops.decode_layer) where it applies.  Off by default: measured
+        # on the 27B-class model at 8 rows it is slower than the per-operator sequence (7.67 vs 7.10 ms per step on one
+        # GPU, 8.33 vs 7.74 ms on two, 7.39 vs 7.10 ms on eight); every grid-barrier phase costs about as much as a
+        # programmatic-launch kernel boundary, so only fewer dependent steps per layer can make it pay
         self.fused_decode = fused_decode
         self._fused_plans, self._fused_bufs = {}, None
         self.fp4_rows = min(64, decode_rows or max_rows)
