@@ -7,6 +7,7 @@
     python -m dgpp_b200.bench.micro act_quant --rows 8 --k 5120 [--mode rmsnorm]
     python -m dgpp_b200.bench.micro gdn --rows 8192 [--hv 32]
     python -m dgpp_b200.bench.micro moe --rows 8 [--experts 128 --top-k 8]
+    python -m dgpp_b200.bench.micro decode_layer --rows 8 --ctx 2048     (phase timeline of one layer-boundary launch)
 
 Timing: the launches are captured in a CUDA graph, replayed `--reps` times between CUDA events after a warm-up replay.
 Weight-streaming kernels rotate over enough weight copies to exceed the 126 MB L2, so every launch reads its
@@ -229,9 +230,64 @@ def bench_moe(args, dev):
            active_experts=active)
 
 
+def bench_decode_layer(args, dev):
+    """One launch of the persistent decode-layer kernel on the 27B-class layer shapes (3-layer model, prefilled to
+    --ctx): CUDA-event time and the %globaltimer phase stamps of CTA 0 and of the last CTA, weights rotated out of L2
+    before every launch."""
+    import ctypes as C
+
+    from ..engine.llm_engine import LLMEngine
+    from ..models.dense import DenseConfig, DenseModel
+    from ..ops import _lib, core as ops
+
+    rows, ctx = args.rows, args.ctx
+    cfg = DenseConfig.dense_27b(layers=3)
+    model = DenseModel.random_init(cfg, device=dev, seed=0)
+    eng = LLMEngine(model, max_batch=rows, max_seq_len=ctx + 256, prefill_chunk=2048, use_graphs=False,
+                    fused_decode=True)
+    g = torch.Generator().manual_seed(1)
+    firsts = torch.zeros(rows, dtype=torch.int32, device=dev)
+    for s_ in range(rows):
+        assert eng.kv.reserve(s_, ctx + 64)
+        firsts[s_:s_ + 1].copy_(eng.prefill(s_, torch.randint(0, cfg.vocab, (ctx,), generator=g).tolist()))
+    eng.start_decode(list(range(rows)), firsts)
+    for _ in range(3):
+        eng.decode_step(rows)
+    torch.cuda.synchronize()
+    tr = torch.zeros(64, dtype=torch.int64, device=dev)
+    _lib.declare("dgpp_decode_layer_set_trace", [C.c_void_p])
+    _lib.call("dgpp_decode_layer_set_trace", tr.data_ptr())
+    r = eng.runner
+    launch = r._fused_plan(rows, eng.d_positions[:rows], eng.d_row_req[:rows], r.decode_splits)[1]
+    names = {1: "row_a", 2: "gemm", 3: "unitq", 4: "rope", 5: "row_c"}
+    out = []
+    for _ in range(max(2, min(args.reps, 5))):
+        junk = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+        junk.fill_(1)
+        del junk
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        launch.launch()
+        e1.record()
+        torch.cuda.synchronize()
+        t, a = tr.cpu().tolist(), launch.a
+        rec = {"event_us": e0.elapsed_time(e1) * 1000.0}
+        for sel, nm in ((0, "cta0"), (1, "cta_last")):
+            b = t[sel * 32 + 30]
+            rec[nm] = [[f"{names[a.ph_type[ph]]}{a.ph_idx[ph]}", t[sel * 32 + 2 * ph] - b, t[sel * 32 + 2 * ph + 1] - b]
+                       for ph in range(a.nphase)]
+        out.append(rec)
+    _lib.call("dgpp_decode_layer_set_trace", None)
+    ops.check_status()
+    print(json.dumps({"kernel": "decode_layer", "rows": rows, "ctx": ctx, "unit": "ns since kernel entry [phase, start, end]",
+                      "launches": out}))
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm_fp4", "gemm_tc", "attn_decode", "attn_prefill", "act_quant", "gdn", "moe"])
+    ap.add_argument("kernel", choices=["gemm_fp4", "gemm_tc", "attn_decode", "attn_prefill", "act_quant", "gdn", "moe",
+                                       "decode_layer"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
@@ -254,7 +310,8 @@ def main(argv=None) -> int:
     torch.cuda.set_device(dev)
     torch.manual_seed(0)
     {"gemm_fp4": bench_gemm_fp4, "gemm_tc": bench_gemm_tc, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill,
-     "act_quant": bench_act_quant, "gdn": bench_gdn, "moe": bench_moe}[args.kernel](args, dev)
+     "act_quant": bench_act_quant, "gdn": bench_gdn, "moe": bench_moe,
+     "decode_layer": bench_decode_layer}[args.kernel](args, dev)
     return 0
 
 
