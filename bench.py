@@ -1,20 +1,29 @@
 #!/usr/bin/env python
-"""Headline benchmark: decode tok/s (and cold prefill seconds) of the dense 27B-class NVFP4 GQA
-decoder, 64 layers / hidden 5120 / 40 q + 8 kv heads x 128 / FFN 17408 / vocab 151936, FP8 KV cache,
-random-init N(0, 0.02) weights quantised to NVFP4, synthetic uniform-random prompts.
+"""Headline benchmark: decode tok/s (C8 and C1) and cold prefill seconds (2K / 8K / 32K) of the dense 27B-class NVFP4
+GQA decoder, 64 layers / hidden 5120 / 40 q + 8 kv heads x 128 / FFN 17408 / vocab 151936, FP8 KV cache, random-init
+N(0, 0.02) weights quantised to NVFP4, synthetic uniform-random prompts.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--concurrency C] [--prompt-len L]
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...   (N > 1, tensor parallel)
+    python bench.py --impl reference [--steps K]          (the reference's own decode harness, built for sm_100a)
 
-A step is one decode pass of C concurrent sequences (C tokens).  K steps are timed on the device
-with CUDA events between barrier + synchronize, max over ranks; rank 0 prints one JSON line.
-`--impl reference` reports why the reference engine cannot run on this machine.
+A step is one decode pass of C concurrent sequences (C tokens).  The headline value is the median of >= 5 repeats of
+exactly K steps each (the repeats cover >= 1 s), every repeat timed on the device with CUDA events between barrier +
+synchronize, max over ranks; rank 0 prints one JSON line.  `extras` carries C1 decode and the cold prefill times, each
+timed the same way with its own clock sample.
+
+`--impl reference` runs the reference's synthetic decode harness (`apps/gpt_doll.cpp`, unmodified sources compiled
+out of tree for sm_100a by baseline/build_ref.py): bf16 weights, one sequence, greedy, CUDA-graph decode.  That is
+the only part of the reference that builds for this GPU (its NVFP4 / FP8 kernels are block-scaled mma.sync for
+sm_121a and its tensor parallelism is RoCE verbs), so its line says `same_config: false` and names what differs.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -22,16 +31,18 @@ import time
 
 # Reference numbers (tok/s, high end of the published range) for the closest published model:
 # Qwen3.8-27B NVFP4 on 1 / 2 / 4 GB10 nodes, C1 and C8 decode, cold prefill seconds at 2K/8K/32K.
+# The reference publishes nothing beyond 4 nodes: the 8-GPU entries repeat the 4-node figures.
 PUBLISHED = {
     "c8": {1: 244.0, 2: 368.9, 4: 430.5, 8: 430.5},
     "c1": {1: 59.8, 2: 105.4, 4: 165.5, 8: 165.5},
     "prefill_s": {1: (1.198, 3.943, 16.634), 2: (1.198, 4.232, 17.285), 4: (1.058, 3.897, 15.646),
                   8: (1.058, 3.897, 15.646)},
 }
+HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -52,7 +63,12 @@ class ClockSampler(threading.Thread):
                 pass
             time.sleep(0.2)
 
-    def summary(self):
+    def finish(self) -> dict:
+        self.stop_flag = True
+        self.join(timeout=3)
+        return self.summary()
+
+    def summary(self) -> dict:
         sm = sorted(int(float(r[1])) for r in self.rows if len(r) > 2 and r[1].replace(".", "").isdigit())
         mx = [int(float(r[2])) for r in self.rows if len(r) > 2 and r[2].replace(".", "").isdigit()]
         reasons = set()
@@ -65,25 +81,86 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(reasons), "samples": len(self.rows)}
 
 
-def reference_arm(args):
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "reference is a CMake C++/CUDA 13 project for sm_121a + libibverbs with no Python package "
-                      "(pip install: 'neither setup.py nor pyproject.toml found'); it has no sm_100 build"}))
+def sampled(gpu: int):
+    s = ClockSampler(gpu)
+    s.start()
+    return s
+
+
+# ---------------------------------------------------------------------------------------------- reference arm
+DOLL_SHAPE = dict(hidden=4096, layers=64, inter=17408, vocab=151936, heads=32, kv_heads=8, head_dim=128)
+
+
+def reference_arm(args) -> int:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    if world > 1 or args.gpus > 1:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference's tensor parallelism is RoCE verbs between GB10 nodes (libibverbs); it has "
+                          "no NVLink / NCCL path, so only its single-GPU harness runs here"}))
+        return 0
+    sys.path.insert(0, os.path.join(HERE, "baseline"))
+    try:
+        import build_ref
+        binary = build_ref.build(build_ref.default_source())
+    except Exception as e:  # noqa: BLE001 - any build problem is reported as the reason
+        print(json.dumps({"impl": "reference", "unavailable": f"out-of-tree sm_100a build failed: {str(e)[:300]}"}))
+        return 0
+    K, W = max(1, args.steps), 24           # the harness runs 24 untimed decode steps of its own before it times K
+    s = DOLL_SHAPE
+    cmd = [binary, "--bench", str(K), "--hidden", str(s["hidden"]), "--layers", str(s["layers"]), "--inter",
+           str(s["inter"]), "--vocab", str(s["vocab"]), "--max-seq", "4096"]
+    smp = sampled(int(os.environ.get("LOCAL_RANK", "0")))
+    try:
+        p = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+    except subprocess.TimeoutExpired:
+        smp.finish()
+        print(json.dumps({"impl": "reference", "unavailable": "the reference harness did not finish in 1500 s"}))
+        return 0
+    clocks = smp.finish()
+    m = re.search(r"BENCH mode=sync steps=(\d+) tok/s=([0-9.]+) step_ms=([0-9.]+)", p.stdout + p.stderr)
+    if not m:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference harness printed no BENCH line: " + (p.stdout + p.stderr)[-300:].replace("\n", " | ")}))
+        return 0
+    tok_s, step_ms = float(m.group(2)), float(m.group(3))
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_tok_s_c1", "value": tok_s, "unit": "tok/s", "n_gpus": 1, "steps": K,
+        "warmup": W, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "reference gpt_doll harness: dense GQA decoder 64L/4096h/32q8kv/128d/17408ffn/151936v, bf16 "
+                            "weights (fp8 lm head), bf16 KV, no RoPE, random-init", "global_batch": 1, "seq_len": 32 + K // 2,
+                   "parallelism": "tp1", "decode": "greedy, CUDA-graph, host-timed by the harness itself (wall clock "
+                                                   "around enqueue + poll of every step)",
+                   "same_config": False,
+                   "differs": "one sequence instead of 8, bf16 instead of NVFP4 weights, hidden 4096 (its attention "
+                              "output is added without an o projection, so hidden = heads x 128), context ~64"},
+        "clocks": clocks,
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8,
+                "note": "the harness's own number is end to end: each step enqueues the token id and polls the sampled id"},
+        "gpu_launches": 646 * K,
+        "note": "ours on the same shape and weight format: extras.doll_shape_bf16_c1_tok_s of the default arm",
+    }))
     return 0
 
 
-def main():
+# ---------------------------------------------------------------------------------------------- our arm
+def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--concurrency", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=64, help="debug only: a run with fewer layers is not a valid number")
     ap.add_argument("--reducer", default="peer", choices=["peer", "nccl"])
-    ap.add_argument("--prefill-lens", default="", help="comma list of cold-prefill lengths to time as extras")
-    ap.add_argument("--also-c1", action="store_true", help="also time C=1 decode as an extra")
+    ap.add_argument("--prefill-lens", default="2048,8192,32768", help="cold-prefill lengths timed as extras ('' = none)")
+    ap.add_argument("--no-c1", action="store_true", help="skip the C=1 decode extra")
+    ap.add_argument("--no-doll-shape", action="store_true",
+                    help="skip the extra that runs this engine on the reference harness's shape (bf16 weights, C1)")
     ap.add_argument("--bf12-head", action="store_true",
                     help="keep the bf16 lm head in its lossless 12-bit resident form (same logits bit for bit)")
     ap.add_argument("--layer-kernel", action="store_true",
@@ -130,10 +207,15 @@ def main():
             from dgpp_b200.parallel.tp import NcclReducer
             reducer = NcclReducer()
 
-    C, L, K, W = args.concurrency, args.prompt_len, args.steps, args.warmup
+    C, L, K, W = args.concurrency, args.prompt_len, args.steps, max(args.warmup, 3)
     prefill_lens = [int(x) for x in args.prefill_lens.split(",") if x]
-    max_len = max([L + K + W + 8] + [p + 8 for p in prefill_lens])
-    eng = LLMEngine(model, max_batch=C, max_seq_len=max_len, prefill_chunk=2048, reducer=reducer,
+    REPEATS_MIN, TARGET_S = 5, 1.0
+    max_repeats = 40
+    decode_room = L + 2 * W + K * (2 * max_repeats + 2) + 16     # C8 repeats, C1 repeats, the end-to-end run
+    max_len = max([decode_room] + [p + 8 for p in prefill_lens])
+    page = cfg.page
+    blocks = C * math.ceil(decode_room / page) + (math.ceil(max_len / page) if prefill_lens else 0) + 8
+    eng = LLMEngine(model, max_batch=C, max_seq_len=max_len, prefill_chunk=2048, reducer=reducer, kv_blocks=blocks,
                     fuse_ar=not args.no_fuse_ar, fused_decode=args.layer_kernel)
 
     g = torch.Generator().manual_seed(1234)
@@ -144,91 +226,131 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed_decode(engine, b: int):
+        """Repeats of exactly K decode steps of batch width b; returns (per-repeat ms (max over ranks), clocks)."""
+        for _ in range(W):
+            engine.decode_step(b)
+        barrier()
+        smp = sampled(local)
+        times = []
+        total = 0.0
+        while len(times) < max_repeats and (len(times) < REPEATS_MIN or total < TARGET_S * 1000.0):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(K):
+                engine.decode_step(b)
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1))
+            times.append(ms)
+            total += ms
+        return times, smp.finish()
+
     # ---- prefill all sequences (cold), then arm decode
     firsts = torch.zeros(C, dtype=torch.int32, device=dev)
     barrier()
     t0 = time.perf_counter()
     for s, p in enumerate(prompts):
-        assert eng.kv.reserve(s, L + K + W + 8)
+        assert eng.kv.reserve(s, decode_room)
         firsts[s:s + 1].copy_(eng.prefill(s, p))
     barrier()
     prefill_all_s = time.perf_counter() - t0
     eng.start_decode(list(range(C)), firsts)
 
-    # ---- device-timed decode steps
-    for _ in range(max(W, 3)):
-        eng.decode_step(C)
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(K):
-        eng.decode_step(C)
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
+    # ---- headline: device-timed decode, C sequences
+    times, clocks = timed_decode(eng, C)
     ops.check_status()
+    med = sorted(times)[len(times) // 2]
+    extras = {"repeats": len(times), "ms_per_step_min": min(times) / K, "ms_per_step_max": max(times) / K,
+              "timed_s": sum(times) / 1000.0, "prefill_all_s": prefill_all_s, "init_s": t_init,
+              "published_8gpu_is_4node_figure": True}
+    launches = eng.launches_per_step() * K
 
-    # ---- end-to-end: the public generate() API, host tokens in pinned memory, per-step readback
+    # ---- C1 decode (row 0 keeps decoding alone)
+    if not args.no_c1:
+        t1, c1 = timed_decode(eng, 1)
+        m1 = sorted(t1)[len(t1) // 2]
+        extras["c1_decode_tok_s"] = 1000.0 * K / m1
+        extras["c1_ms_per_step"] = m1 / K
+        extras["c1_clocks"] = c1
+        extras["c1_vs_published"] = extras["c1_decode_tok_s"] / PUBLISHED["c1"][world] if world in PUBLISHED["c1"] else None
+
+    # ---- end to end: the public generate() API, host tokens in pinned memory, per-step readback
     barrier()
     e2e_t = {}
-    t0 = time.perf_counter()
     eng.generate(prompts, max_tokens=K + 1, stream_tokens=True, timings=e2e_t)
     barrier()
-    e2e_decode_s = e2e_t["decode_s"]
-    sampler.stop_flag = True
-    sampler.join(timeout=2)
+    e2e_ms = max_over_ranks(e2e_t["decode_s"] * 1000.0)
+    extras["e2e_prefill_s"] = e2e_t.get("prefill_s")
 
-    extras = {"prefill_all_s": prefill_all_s, "init_s": t_init, "e2e_prefill_s": e2e_t.get("prefill_s")}
-    if args.also_c1:
-        eng.start_decode([0], firsts[:1])
-        for _ in range(3):
-            eng.decode_step(1)
-        barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(K):
-            eng.decode_step(1)
-        b.record()
-        barrier()
-        extras["c1_decode_tok_s"] = 1000.0 * K / a.elapsed_time(b)
+    # ---- cold prefill of one sequence
     for pl in prefill_lens:
         p = torch.randint(0, cfg.vocab, (pl,), generator=g).tolist()
-        eng.kv.release(0)
+        for s in range(C):
+            eng.kv.release(s)
         barrier()
+        smp = sampled(local)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         eng.prefill(0, p)
         b.record()
         barrier()
-        extras[f"prefill_s_{pl}"] = a.elapsed_time(b) / 1000.0
+        extras[f"prefill_s_{pl}"] = max_over_ranks(a.elapsed_time(b)) / 1000.0
+        extras[f"prefill_clocks_{pl}"] = smp.finish()
+        pub = PUBLISHED["prefill_s"].get(world)
+        if pub and pl in (2048, 8192, 32768):
+            extras[f"prefill_published_s_{pl}"] = pub[(2048, 8192, 32768).index(pl)]
+    ops.check_status()
 
-    vals = torch.tensor([ms, e2e_decode_s * 1000.0], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = vals.tolist()
+    # ---- this engine on the reference harness's shape and weight format (bf16, one sequence): the like-for-like number
+    if world == 1 and not args.no_doll_shape and args.layers == 64:
+        del eng, model
+        torch.cuda.empty_cache()
+        s = DOLL_SHAPE
+        dcfg = DenseConfig(layers=s["layers"], hidden=s["hidden"], q_heads=s["heads"], kv_heads=s["kv_heads"],
+                           head_dim=s["head_dim"], ffn=s["inter"], vocab=s["vocab"], weight_fmt="bf16", name="doll-shape")
+        dmodel = DenseModel.random_init(dcfg, device=dev, seed=0)
+        deng = LLMEngine(dmodel, max_batch=1, max_seq_len=32 + W + K * (max_repeats + 2) + 16, prefill_chunk=64)
+        first = deng.prefill(0, torch.randint(0, dcfg.vocab, (32,), generator=g).tolist())
+        deng.start_decode([0], first)
+        td, cd = timed_decode(deng, 1)
+        md = sorted(td)[len(td) // 2]
+        extras["doll_shape_bf16_c1_tok_s"] = 1000.0 * K / md
+        extras["doll_shape_bf16_c1_ms_per_step"] = md / K
+        extras["doll_shape_clocks"] = cd
+        ops.check_status()
+
     if rank == 0:
-        tok_s = 1000.0 * C * K / ms
+        tok_s = 1000.0 * C * K / med
         e2e_tok_s = 1000.0 * C * K / e2e_ms
         key = "c8" if C >= 8 else "c1"
         base = PUBLISHED[key].get(world)
         line = {
             "metric": f"decode_tok_s_c{C}", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K,
-            "warmup": max(W, 3), "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+            "warmup": W, "ms_per_step": med / K, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": (tok_s / base) if base else None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {"model": "dense-27B-class GQA decoder, NVFP4 weights (e2m1 + e4m3/16 + fp32), bf16 "
                                 "activations, FP8 e4m3 KV, 64L/5120h/40q8kv/128d/17408ffn/151936v",
                        "global_batch": C, "seq_len": L, "parallelism": f"tp{world}", "decode": "greedy, no spec",
                        "layers": cfg.layers,
-                       "l2": "inputs larger than L2: every step streams all weights (>14 GB) from HBM"},
-            "clocks": sampler.summary(),
+                       "l2": "inputs larger than L2: every step streams all weights (>14 GB) from HBM",
+                       "timing": f"median of {len(times)} repeats of exactly {K} steps, CUDA events, max over ranks",
+                       "baseline": "published Qwen3.8-27B NVFP4 on GB10 nodes; the 8-GPU entry reuses the 4-node figure"},
+            "clocks": clocks,
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": C * 4, "d2h_bytes_per_step": C * 4,
                     "note": "generate(stream_tokens=True): prompt ids H2D from pinned memory at prefill; every decode "
                             "step copies its input ids H2D from pinned memory and reads the picked ids back D2H "
                             "before the next launch"},
-            "gpu_launches": eng.launches_per_step() * K,
+            "gpu_launches": launches,
             "extras": extras,
         }
         print(json.dumps(line))
