@@ -3,7 +3,8 @@
 //   begin_capture(stream)  -> everything launched on `stream` until end_capture() is recorded, not run
 //   end_capture(stream)    -> the captured graph is checked (kernel nodes only: a memcpy / memset / host node in
 //                             a decode graph would serialise against other work and is rejected unless allowed),
-//                             its kernel -> kernel edges are rewritten as PROGRAMMATIC dependencies (so the next
+//                             its kernel -> kernel edges INTO kernels of this library are rewritten as PROGRAMMATIC
+//                             dependencies (so the next
 //                             kernel's prologue -- barrier init, TMEM allocation, descriptor prefetch -- overlaps
 //                             the previous kernel's tail; every kernel of this library executes
 //                             griddepcontrol.wait before touching global data), and an executable is instantiated
@@ -26,6 +27,24 @@ struct GraphExec {
   int other_nodes = 0;
   int programmatic_edges = 0;
 };
+
+// True when the kernel node runs a kernel of this library (namespace dgpp).  Only those execute griddepcontrol.wait
+// before they touch global data, so only edges INTO them may become programmatic: CUDA makes the predecessor's writes
+// visible to a programmatic dependent at that wait, and a kernel without it could read stale data.
+static bool own_kernel(cudaGraphNode_t node) {
+  cudaKernelNodeParams kp;
+  memset(&kp, 0, sizeof(kp));
+  if (cudaGraphKernelNodeGetParams(node, &kp) != cudaSuccess || !kp.func) {
+    cudaGetLastError();
+    return false;
+  }
+  const char* name = nullptr;
+  if (cudaFuncGetName(&name, kp.func) != cudaSuccess || !name) {
+    cudaGetLastError();
+    return false;
+  }
+  return strstr(name, "4dgpp") != nullptr;   // Itanium mangling of namespace dgpp
+}
 
 }  // namespace
 
@@ -70,6 +89,7 @@ DGPP_API void* dgpp_graph_end_capture(cudaStream_t st, int pdl, int allow_non_ke
         cudaGraphNodeGetType(to[e], &tt);
         if (tf != cudaGraphNodeTypeKernel || tt != cudaGraphNodeTypeKernel) continue;
         if (data[e].type == cudaGraphDependencyTypeProgrammatic) continue;
+        if (!own_kernel(to[e])) continue;   // a foreign kernel (NCCL, torch) never executes griddepcontrol.wait
         cudaGraphEdgeData nd;
         memset(&nd, 0, sizeof(nd));
         nd.from_port = cudaGraphKernelNodePortProgrammatic;

@@ -116,6 +116,7 @@ class PyScheduler {
     d["queue_peak"] = m.queue_peak; d["active_peak"] = m.active_peak;
     d["prefix_lookups"] = p.lookups; d["prefix_hits"] = p.hits; d["prefix_inserts"] = p.inserts;
     d["prefix_evictions"] = p.evictions; d["prefix_ghost_hits"] = p.ghost_hits;
+    d["prefix_check_rejects"] = p.check_rejects;
     return d;
   }
 

@@ -42,7 +42,15 @@ class EmbedSplice:
         self._embeds_by_id[request_id] = list(spans)
 
     def _splice_open(self, slot: int, request_id: str) -> None:
-        self._slot_embeds[slot] = self._embeds_by_id.pop(request_id, None)
+        # kept until forget(): a request shed back to the queue is opened again under the same id
+        self._slot_embeds[slot] = self._embeds_by_id.get(request_id)
+
+    def _splice_forget(self, request_id: str) -> None:
+        self._embeds_by_id.pop(request_id, None)
+
+    def forget(self, request_id: str) -> None:
+        """Drops the per-request registrations of a retired request."""
+        self._splice_forget(request_id)
 
     def _real_ids(self, tokens):
         v, pad = self._vocab, self._pad_id
@@ -224,6 +232,8 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
             self.s_pos = torch.zeros(hb, dtype=torch.int32, device=dev)
             self.s_req = torch.zeros(hb, dtype=torch.int32, device=dev)
         self.by_id = {}
+        self.emitted = {}                              # request id -> tokens the sampler picked for it so far
+        self.slot_req = [None] * b
         self.slot_cfg = [None] * b
         self.last_logprobs = [None] * b
         self.sampler = None
@@ -302,10 +312,20 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
         (for the penalties' token counts) of a request before it is submitted to the scheduler."""
         self.by_id[request_id] = (params, grammar, prompt_ids)
 
+    def forget(self, request_id: str) -> None:
+        """Drops what configure() / set_embeds() registered for a request.  The owner of the request calls it when
+        the request retires (or is rejected / cancelled while still queued); until then the entries stay, because a
+        request shed back to the queue is opened again under the same id and must get the same sampling parameters,
+        its grammar in the state its generated tokens left it in, and its image rows."""
+        self.by_id.pop(request_id, None)
+        self.emitted.pop(request_id, None)
+        self._splice_forget(request_id)
+
     def open(self, slot, request_id):
         self._splice_open(slot, request_id)
-        cfg = self.by_id.pop(request_id, None)
+        cfg = self.by_id.get(request_id)
         self.slot_cfg[slot] = None
+        self.slot_req[slot] = request_id
         self.last_logprobs[slot] = None
         if cfg is None or (cfg[0] is None and cfg[1] is None):
             return
@@ -315,8 +335,12 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
             self.sampler = DeviceSampler(self.e.model.cfg.vocab, self.e.max_batch, self.e.max_batch, self.e.dev)
         self.sampler.reset_slot(slot)
         params = params or SamplingParams()
-        if prompt_ids and (params.repetition_penalty != 1.0 or params.presence_penalty or params.frequency_penalty):
-            self.sampler.count(slot, prompt_ids)
+        if params.repetition_penalty != 1.0 or params.presence_penalty or params.frequency_penalty:
+            # token counts of the prompt and, for a re-admitted request, of what it had generated before it was shed
+            seen = list(prompt_ids or []) + self.emitted.get(request_id, [])
+            if seen:
+                self.sampler.count(slot, seen)
+        # (the grammar object itself has consumed every token picked so far, so it resumes where the request stopped)
         self.slot_cfg[slot] = (params, grammar)
 
     def _sample_rows(self, logits, slots):
@@ -354,6 +378,7 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
                 self.last_logprobs[s] = (picked[r].logprob, picked[r].top)
                 if cfg[1] is not None:
                     cfg[1].accept(picked[r].token)
+                self.emitted.setdefault(self.slot_req[s], []).append(picked[r].token)
         return [p.token for p in picked]
 
     def prefill(self, slot, tokens, pos, last):
@@ -546,7 +571,8 @@ class HybridEngine(rt.SchedulerEngine):
     def _snapshot(self, slot, tokens_done):
         block = self.kv.req_blocks[slot][tokens_done // self.kv.page - 1]
         if len(self.snaps) >= self.max_snapshots:
-            dead = [b for b in self.snaps if self._live(b) is None]
+            for b in list(self.snaps):          # (a copy: _live drops dead entries from the dict as it goes)
+                self._live(b)
             if len(self.snaps) >= self.max_snapshots:
                 oldest = min(self.snaps, key=lambda b: self.snaps[b][2])
                 del self.snaps[oldest]

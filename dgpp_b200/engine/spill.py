@@ -14,20 +14,57 @@ and attached prefix blocks carry the hash recorded when they were filled.
   hash the bytes are written into the slot's (already reserved) block and the tokens are skipped.  At least one token
   is always left to run, because the scheduler wants the logits of the last prompt position.
 A restored block is byte-identical to the one that was computed (CRC-checked pages), so generation is unchanged.
+
+Keys on disk are the chain hash mixed with a 64-bit FINGERPRINT of what computed the block (`cache_fingerprint`: model
+configuration, a digest of the weights, KV format and layout, tensor-parallel rank and size, adapter).  A tier
+directory adopted by a server with other weights, another quantisation or another shard therefore holds nothing
+under this engine's keys, instead of handing back KV that another model computed.
 (reference counterparts: src/engine/nvme_tier.hpp spill / restore of KV pages, src/sched/scheduler.cpp disk pump,
  src/sched/disk_cache.cpp.)
 """
 from __future__ import annotations
 
+import hashlib
+import json
 from typing import Dict, List, Optional
 
 from ..runtime import rt
 
+_M64 = (1 << 64) - 1
+
+
+def cache_fingerprint(**identity) -> int:
+    """64-bit digest of everything that determines the bytes of a KV block besides its tokens.  Pass whatever
+    applies, e.g. ``cache_fingerprint(config=dataclasses.asdict(cfg), weights=weights_digest(model), kv="fp8-e4m3/64",
+    tp=(rank, size), adapter=adapter_sha)``; values must be JSON-serialisable (tuples become lists)."""
+    blob = json.dumps(identity, sort_keys=True, default=str).encode()
+    return int.from_bytes(hashlib.blake2b(blob, digest_size=8).digest(), "little")
+
+
+def weights_digest(tensors, sample_bytes: int = 1 << 16) -> str:
+    """Cheap identity of a set of weight tensors: shapes, dtypes and the first / last `sample_bytes` of each."""
+    import torch
+
+    h = hashlib.blake2b(digest_size=16)
+    for t in tensors:
+        if t is None:
+            continue
+        h.update(repr((tuple(t.shape), str(t.dtype))).encode())
+        flat = t.detach().reshape(-1).view(torch.uint8)
+        n = min(sample_bytes, flat.numel())
+        h.update(flat[:n].cpu().numpy().tobytes())
+        h.update(flat[flat.numel() - n:].cpu().numpy().tobytes())
+    return h.hexdigest()
+
 
 class SpillingEngine(rt.SchedulerEngine):
-    def __init__(self, base, tier):
+    def __init__(self, base, tier, fingerprint: Optional[int] = None):
         super().__init__()
         self.b, self.tier = base, tier
+        if fingerprint is None:
+            f = getattr(base, "cache_fingerprint", None)
+            fingerprint = f() if f else 0
+        self.fp = int(fingerprint) & _M64
         self.bt = base.block_tokens()
         n = base.max_concurrent()
         self.block_hash: Dict[int, int] = {}          # physical block -> chain hash of the prefix ending with it
@@ -58,6 +95,12 @@ class SpillingEngine(rt.SchedulerEngine):
         f = getattr(self.b, "open", None)
         if f:
             f(slot, request_id)
+
+    def key(self, h: int) -> int:
+        """Disk key of the block whose chain hash is h: the hash mixed with this engine's fingerprint."""
+        x = (h ^ self.fp) & _M64
+        x = (x * 0x9E3779B97F4A7C15 + (self.fp >> 7)) & _M64
+        return x ^ (x >> 29)
 
     # ---- hashing of what a slot holds
     def _note(self, slot: int, tokens: List[int]) -> None:
@@ -91,8 +134,8 @@ class SpillingEngine(rt.SchedulerEngine):
         h = self.block_hash.get(block)
         if h is None or self.b.block_refcount(block) != 1:
             return
-        if not self.tier.contains(h):
-            self.tier.put_async(h, self.b.read_block(block))
+        if not self.tier.contains(self.key(h)):
+            self.tier.put_async(self.key(h), self.b.read_block(block))
             self.spilled += 1
         del self.block_hash[block]
 
@@ -121,9 +164,9 @@ class SpillingEngine(rt.SchedulerEngine):
                 ids = tokens[skip:skip + self.bt]
                 hb = rt.chain_hash(h, ids)
                 idx = (pos + skip) // self.bt
-                if idx >= len(blocks) or not self.tier.contains(hb):
+                if idx >= len(blocks) or not self.tier.contains(self.key(hb)):
                     break
-                data = self.tier.get(hb)
+                data = self.tier.get(self.key(hb))
                 if data is None:                      # failed its checks on the way back: compute instead
                     break
                 self.b.write_block(blocks[idx], data)

@@ -431,6 +431,8 @@ class Server:
                         self.sched.cancel(rid)
             elif kind.startswith("retire"):
                 why = kind.split(":", 1)[1]
+                if why != "shed" and hasattr(self.engine, "forget"):
+                    self.engine.forget(rid)          # (a shed request comes back under the same id)
                 if not lv.finish:
                     tail = lv.scanner.feed(lv.decoder.flush())
                     tail += lv.scanner.flush()

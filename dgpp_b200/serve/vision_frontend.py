@@ -31,6 +31,14 @@ class VisionSpec:
     preprocess: ImagePreprocess = field(default_factory=ImagePreprocess)
 
 
+def _remix(digest48: int, j: int) -> int:
+    """30 bits of splitmix64(digest + golden * (j + 1))."""
+    x = (digest48 + 0x9E3779B97F4A7C15 * (j + 1)) & ((1 << 64) - 1)
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & ((1 << 64) - 1)
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & ((1 << 64) - 1)
+    return (x ^ (x >> 31)) & ((1 << 30) - 1)
+
+
 @dataclass
 class PreparedChat:
     ids: List[int]                       # scheduler-side ids (image positions carry pseudo ids >= vocab)
@@ -106,7 +114,9 @@ class VisionFrontend:
             ids.append(sp.start_id)
             real.append(sp.start_id)
             spans.append((len(ids), rows))
-            ids += [self.vocab + (h + j) % (1 << 30) for j in range(n)]
+            # position j carries 30 bits of a position-dependent remix of the FULL 48-bit content digest, so the block
+            # hashes of the span depend on all of its bits (a single 30-bit id per image would truncate it)
+            ids += [self.vocab + _remix(h, j) for j in range(n)]
             real += [sp.pad_id] * n
             ids.append(sp.end_id)
             real.append(sp.end_id)

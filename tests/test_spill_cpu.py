@@ -65,7 +65,45 @@ def test_corrupted_page_falls_back_to_computing(tmp_path):
     eng = SpillingEngine(inner, tier)
     first, _ = _run(eng, [("a1", A), ("b1", B)], prefix_cache=True)
     tier.flush()
-    key = rt.chain_hash(rt.FNV_SEED, A[:16])
+    key = eng.key(rt.chain_hash(rt.FNV_SEED, A[:16]))
     assert tier.contains(key) and tier.corrupt_for_test(key)
     again, _ = _run(eng, [("a2", A)], prefix_cache=True)
     assert again["a2"] == first["a1"] and tier.stats()["crc_failures"] == 1
+
+
+def test_adopted_tier_of_another_model_gives_no_hits(tmp_path):
+    """A tier directory reopened by an engine with another fingerprint (other weights, quantisation, shard ...) must
+    not hand back the blocks the first engine spilled, although tokens and page geometry are the same."""
+    from dgpp_b200.engine.spill import cache_fingerprint, weights_digest
+
+    mcfg = DenseConfig.plumbing_fp32()
+    g = torch.Generator().manual_seed(3)
+    A = torch.randint(0, mcfg.vocab, (70,), generator=g).tolist()
+    B = torch.randint(0, mcfg.vocab, (66,), generator=g).tolist()
+
+    def engine(seed):
+        model = DenseModel.random_init(mcfg, device="cpu", seed=seed)
+        inner = Counting(model, slots=1, num_blocks=8, block_tokens=16, max_context=256)
+        tier = rt.DiskTier(str(tmp_path), page_bytes=1 << 16, pages=64)          # adopts what is there
+        fp = cache_fingerprint(config=mcfg.name, weights=weights_digest([L.qkv.payload for L in model.layers]),
+                               kv="fp32", tp=(0, 1))
+        return SpillingEngine(inner, tier, fingerprint=fp), tier, inner
+
+    e0, t0, _ = engine(0)
+    _run(e0, [("a1", A), ("b1", B)], prefix_cache=True)
+    t0.flush()
+    t0.commit()
+    assert e0.spilled >= 4
+    del e0, t0
+    # same weights: the adopted blocks are found
+    e1, t1, i1 = engine(0)
+    assert t1.blobs() >= 4
+    _run(e1, [("a2", A)], prefix_cache=True)
+    assert e1.restored == 4
+    t1.flush()
+    t1.commit()
+    del e1, t1
+    # other weights, same tokens, same geometry: nothing may be restored
+    e2, t2, i2 = engine(1)
+    _run(e2, [("a3", A)], prefix_cache=True)
+    assert e2.restored == 0 and i2.computed >= len(A)
