@@ -227,6 +227,15 @@ struct ClusterConfig {
   int mtp_depth = 0;
   int sampling_candidates = 128;
   bool fuse_all_reduce = true;
+  // Everything that changes what the engine computes or which kernels run is a key here (covered by digest()), never
+  // an environment variable: ranks that disagree on one of these refuse to serve together.
+  int engine_decode_splits = 0;             // split-KV factor of decode attention; 0 = one resident wave
+  bool engine_fuse_combine = true;          // fold the split-KV partials inside the o projection's quantiser
+  bool engine_l2_prefetch = false;          // GEMMs ask L2 for the next projection's weights
+  std::string engine_fp4_splits = "auto";   // split-K policy of the block-scaled GEMM: auto | resident | legacy
+  bool engine_cluster_splitk = false;       // split-K through distributed shared memory instead of the workspace
+  bool engine_fp4_preload = true;           // weight half of the first ring stages issued before the grid dependency
+  bool engine_layer_kernel = false;         // decode through the persistent decode-layer kernel
   std::string log_level = "info";
 
   static ClusterConfig parse(const std::string& text) {
@@ -235,7 +244,8 @@ struct ClusterConfig {
     static const std::set<std::string> known = {
         "model", "host", "port", "tensor_parallel", "expert_parallel", "max_concurrency", "max_context", "prefill_chunk",
         "kv_dtype", "kv_headroom_mib", "prefix_cache", "prefix_min_tokens", "scheduler_policy", "mtp_depth",
-        "sampling_candidates", "fuse_all_reduce", "log_level"};
+        "sampling_candidates", "fuse_all_reduce", "log_level", "engine_decode_splits", "engine_fuse_combine",
+        "engine_l2_prefetch", "engine_fp4_splits", "engine_cluster_splitk", "engine_fp4_preload", "engine_layer_kernel"};
     for (const auto& kv : v.members())
       if (!known.count(kv.first)) throw std::runtime_error("config: unknown key '" + kv.first + "'");
     ClusterConfig c;
@@ -257,6 +267,13 @@ struct ClusterConfig {
     c.sampling_candidates = static_cast<int>(v.get_int("sampling_candidates", 128));
     c.fuse_all_reduce = v.get_bool("fuse_all_reduce", true);
     c.log_level = v.get_string("log_level", c.log_level);
+    c.engine_decode_splits = static_cast<int>(v.get_int("engine_decode_splits", 0));
+    c.engine_fuse_combine = v.get_bool("engine_fuse_combine", true);
+    c.engine_l2_prefetch = v.get_bool("engine_l2_prefetch", false);
+    c.engine_fp4_splits = v.get_string("engine_fp4_splits", c.engine_fp4_splits);
+    c.engine_cluster_splitk = v.get_bool("engine_cluster_splitk", false);
+    c.engine_fp4_preload = v.get_bool("engine_fp4_preload", true);
+    c.engine_layer_kernel = v.get_bool("engine_layer_kernel", false);
     auto need = [](bool ok, const std::string& what) { if (!ok) throw std::runtime_error("config: " + what); };
     need(c.port > 0 && c.port < 65536, "port out of range");
     need(c.tensor_parallel == 1 || c.tensor_parallel == 2 || c.tensor_parallel == 4 || c.tensor_parallel == 8,
@@ -269,6 +286,9 @@ struct ClusterConfig {
     need(c.scheduler_policy == "grow" || c.scheduler_policy == "reserve", "scheduler_policy must be grow or reserve");
     need(c.mtp_depth >= 0 && c.mtp_depth <= 5, "mtp_depth must be 0..5");
     need(c.sampling_candidates >= 1 && c.sampling_candidates <= 256, "sampling_candidates must be 1..256");
+    need(c.engine_decode_splits >= 0 && c.engine_decode_splits <= 64, "engine_decode_splits must be 0..64");
+    need(c.engine_fp4_splits == "auto" || c.engine_fp4_splits == "resident" || c.engine_fp4_splits == "legacy",
+         "engine_fp4_splits must be auto, resident or legacy");
     return c;
   }
   json::Value to_json() const {
@@ -280,6 +300,10 @@ struct ClusterConfig {
     v.set("prefix_cache", prefix_cache); v.set("prefix_min_tokens", prefix_min_tokens);
     v.set("sampling_candidates", sampling_candidates); v.set("scheduler_policy", scheduler_policy);
     v.set("tensor_parallel", tensor_parallel);
+    v.set("engine_decode_splits", engine_decode_splits); v.set("engine_fuse_combine", engine_fuse_combine);
+    v.set("engine_l2_prefetch", engine_l2_prefetch); v.set("engine_fp4_splits", engine_fp4_splits);
+    v.set("engine_cluster_splitk", engine_cluster_splitk); v.set("engine_fp4_preload", engine_fp4_preload);
+    v.set("engine_layer_kernel", engine_layer_kernel);
     return v;
   }
   // Same on every rank iff the engine-relevant settings agree (host / port / log level are per process).

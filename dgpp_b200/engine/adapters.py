@@ -57,6 +57,11 @@ class EmbedSplice:
         return [t if t < v else pad for t in tokens]
 
 
+class EngineFailure(RuntimeError):
+    """The device reported a failed bounded wait (or another unrecoverable condition): the engine's buffers are not
+    trustworthy any more.  The serving loop answers every open request with an engine_failure error and stops."""
+
+
 class ReferenceEngine(EmbedSplice, rt.SchedulerEngine):
     def __init__(self, model: DenseModel, slots: int = 4, num_blocks: int = 256, block_tokens: int = 16,
                  max_context: int = 1024, all_reduce=None):
@@ -231,6 +236,7 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
             self.s_tok = torch.zeros(hb, dtype=torch.int32, device=dev)
             self.s_pos = torch.zeros(hb, dtype=torch.int32, device=dev)
             self.s_req = torch.zeros(hb, dtype=torch.int32, device=dev)
+        self.poll_status = True                        # read the device status block after every step (see _poll_device)
         self.by_id = {}
         self.emitted = {}                              # request id -> tokens the sampler picked for it so far
         self.slot_req = [None] * b
@@ -381,9 +387,27 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
                 self.emitted.setdefault(self.slot_req[s], []).append(picked[r].token)
         return [p.token for p in picked]
 
+    def _poll_device(self) -> None:
+        """Every bounded device wait (pipeline barriers, accumulators, peer flags, grid barriers) reports its expiry
+        into the per-device status block instead of trapping.  The serving path reads the block after every prefill
+        chunk and decode pass: a non-zero code means that what the kernels left behind cannot be trusted (a peer that
+        stopped answering, a lost copy), so the step raises and the owner of the loop fails the engine instead of
+        streaming tokens picked from stale buffers.
+        (reference behaviour: engine_failure events and exit 2 / 3, src/serve/generation_service.cpp:4300-4486.)"""
+        if not self.poll_status or self.e.dev.type != "cuda":
+            return
+        import ctypes as C
+        from ..ops import _lib
+        buf = (C.c_int * 4)()
+        _lib.call("dgpp_status_read", C.cast(buf, C.c_void_p))
+        if buf[0] != 0:
+            raise EngineFailure(f"device status code={buf[0]} count={buf[1]} detail={buf[2]} "
+                                f"(a bounded device wait gave up; see common.h StatusCode)")
+
     def prefill(self, slot, tokens, pos, last):
         with self.timer.phase("prefill"):
             first = self.e.prefill(slot, self._real_ids(tokens), start_pos=pos, embed_spans=self._slot_embeds[slot])
+        self._poll_device()
         self.filled[slot] = pos + len(tokens)
         if self.spec_k:
             if pos == 0:
@@ -444,6 +468,7 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
                 r.forward(rows, self.s_tok[:rows], self.s_pos[:rows], self.s_req[:rows], decode=True)
         self.h_out[:rows].copy_(r.pick_id[:rows], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self._poll_device()
         out = []
         for s, row0, d in plan:
             if self.slot_cfg[s]:
@@ -486,6 +511,7 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
         self.h_out[:b].copy_(e.d_tokens[:b], non_blocking=True)
         t_sync = time.perf_counter() if self.timer.enabled else 0.0
         torch.cuda.current_stream().synchronize()
+        self._poll_device()
         if self.timer.enabled:
             self.timer.total_ms["sync"] += (time.perf_counter() - t_sync) * 1e3
             self.timer.count["sync"] += 1
@@ -621,10 +647,22 @@ class HybridEngine(rt.SchedulerEngine):
             return tok
         return -1
 
+    def _poll_device(self) -> None:
+        """See KernelEngine._poll_device: a non-zero device status after a step fails the engine."""
+        if torch.device(getattr(self.r, "dev", "cpu")).type != "cuda":
+            return
+        import ctypes as C
+        from ..ops import _lib
+        buf = (C.c_int * 4)()
+        _lib.call("dgpp_status_read", C.cast(buf, C.c_void_p))
+        if buf[0] != 0:
+            raise EngineFailure(f"device status code={buf[0]} count={buf[1]} detail={buf[2]}")
+
     def step_batch(self, slots):
         slots = list(slots)
         logits = self.r.decode(slots, [self.pending[s] for s in slots])
         toks = torch.argmax(logits[:len(slots)], dim=-1).tolist()
+        self._poll_device()
         out = []
         for s, t in zip(slots, toks):
             self.pending[s] = int(t)

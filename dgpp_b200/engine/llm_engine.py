@@ -30,7 +30,8 @@ from .runner import DenseRunner
 class LLMEngine:
     def __init__(self, model: DenseModel, max_batch: int = 8, max_seq_len: int = 4096, prefill_chunk: int = 2048,
                  kv_blocks: Optional[int] = None, reducer=None, use_graphs: bool = True, ring_steps: int = 1024,
-                 decode_pdl: bool = True, act_terms: int = 3, fuse_ar: bool = True, fused_decode: bool = False):
+                 decode_pdl: bool = True, act_terms: int = 3, fuse_ar: bool = True, fused_decode: Optional[bool] = None,
+                 options=None):
         c = model.cfg
         self.model, self.max_batch, self.max_seq_len = model, max_batch, max_seq_len
         self.prefill_chunk = prefill_chunk
@@ -45,12 +46,17 @@ class LLMEngine:
         # split-KV decode attention: one wave of CTAs (two resident per SM) is the sweet spot -- measured at 8 rows x 8 kv
         # heads: 13.6 us with 4 splits at ctx 2048 (17.6 us with 8), 33 us with 4 at ctx 8192 (49 us with 16)
         splits = max(1, min(16, 296 // max(1, model.hkv_local * max_batch)))
-        import os
-        if os.environ.get("DGPP_DECODE_SPLITS"):           # measurement override
-            splits = max(1, int(os.environ["DGPP_DECODE_SPLITS"]))
+        from .options import EngineOptions
+        self.options = options or EngineOptions()
+        self.options.apply_process_wide()
+        if self.options.decode_splits > 0:
+            splits = self.options.decode_splits
+        if fused_decode is None:
+            fused_decode = self.options.layer_kernel
         self.decode_pdl = decode_pdl
         self.runner = DenseRunner(model, self.kv, rows, reducer=reducer, decode_splits=splits, decode_rows=max_batch,
-                                  act_terms=act_terms, fuse_ar=fuse_ar, fused_decode=fused_decode)
+                                  act_terms=act_terms, fuse_ar=fuse_ar, fused_decode=fused_decode,
+                                  l2_prefetch=self.options.l2_prefetch, fuse_combine=self.options.fuse_combine)
         self.use_graphs = use_graphs
         self.ring_steps = ring_steps
         i32 = dict(dtype=torch.int32, device=self.dev)

@@ -24,7 +24,8 @@ BF = torch.bfloat16
 class DenseRunner:
     def __init__(self, model: DenseModel, kv: PagedKV, max_rows: int, reducer=None, decode_splits: int = 8,
                  decode_fp4: bool = True, act_terms: int = 3, attn_tc: bool = True,
-                 decode_rows: Optional[int] = None, fuse_ar: bool = True, fused_decode: bool = False):
+                 decode_rows: Optional[int] = None, fuse_ar: bool = True, fused_decode: bool = False,
+                 l2_prefetch: bool = False, fuse_combine: bool = True):
         self.m, self.kv, self.max_rows, self.reducer = model, kv, max_rows, reducer
         # decode rows (<= 64) run the linears on the block-scaled FP4 tensor-core path with the activations
         # expanded into `act_terms` residual NVFP4 terms; attention reads the FP8 cache through tcgen05
@@ -53,12 +54,11 @@ class DenseRunner:
         self._li = 0
         # decode: a projection can ask L2 for the next projection's weights while the small kernels between them
         # leave HBM idle.  Measured on the 27B-class model at C8 the hint LOSES (7.70 vs 7.43 ms per step: the requests
-        # compete with the issuing kernel's own weight stream), so it is off unless DGPP_L2_PREFETCH=1.
-        import os
-        self.l2_prefetch = os.environ.get("DGPP_L2_PREFETCH", "0") == "1"
+        # compete with the issuing kernel's own weight stream), so it is off unless the engine options turn it on.
+        self.l2_prefetch = l2_prefetch
         # fold the split-KV partials of decode attention inside the o projection's quantiser (one launch per layer
-        # less); DGPP_FUSE_COMBINE=0 keeps the stand-alone combine kernel
-        self.fuse_combine = os.environ.get("DGPP_FUSE_COMBINE", "1") == "1"
+        # less); off keeps the stand-alone combine kernel
+        self.fuse_combine = fuse_combine
         # fused GEMM -> all-reduce (peer-memory push in the GEMM epilogue, fold in the next norm kernel)
         self.fuse_ar = fuse_ar and reducer is not None and getattr(reducer, "comm", None) is not None and \
             model.cfg.hidden % 128 == 0 and model.cfg.hidden // 128 <= 64

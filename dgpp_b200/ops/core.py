@@ -275,12 +275,22 @@ def gemm_fp4(xa: QuantAct, w: QuantLinear, out: Optional[torch.Tensor] = None,
     return out if out is not None else out32
 
 
-# DGPP_FP4_PRELOAD=0 turns off the pre-wait weight preload of the block-scaled GEMM (A/B measurements)
-if os.environ.get("DGPP_FP4_PRELOAD", "1") == "0":
-    call("dgpp_gemm_fp4_set_preload", 0)
+# Policies of the block-scaled GEMM, set by `configure` (from engine.options.EngineOptions; never from the environment).
+CLUSTER_SPLITK = False
 
-# DGPP_CLUSTER_SPLITK=1 selects the cluster split-K policy (off until its launch path is validated)
-CLUSTER_SPLITK = os.environ.get("DGPP_CLUSTER_SPLITK", "0") == "1"
+
+def configure(fp4_splits: Optional[str] = None, cluster_splitk: Optional[bool] = None,
+              fp4_preload: Optional[bool] = None) -> None:
+    """Process-wide GEMM policies: split-K policy ("auto" | "resident" | "legacy"), split-K through a thread-block
+    cluster, and the pre-wait weight preload."""
+    global CLUSTER_SPLITK, FP4_SPLIT_POLICY
+    if fp4_splits is not None:
+        assert fp4_splits in ("auto", "resident", "legacy")
+        FP4_SPLIT_POLICY = fp4_splits
+    if cluster_splitk is not None:
+        CLUSTER_SPLITK = bool(cluster_splitk)
+    if fp4_preload is not None and _lib.available() and torch.cuda.is_available():
+        call("dgpp_gemm_fp4_set_preload", int(bool(fp4_preload)))
 
 
 def pick_cluster_splits(rows: int, n: int, k: int, bn: int) -> int:
@@ -305,7 +315,7 @@ def pick_cluster_splits(rows: int, n: int, k: int, bn: int) -> int:
 # Measured on the 27B-class decode step: C8 7.14 ms legacy / 7.34 ms resident, C1 165.7 / 169.8 tok/s -- the fold's
 # fences and counter round trip cost more than the shorter K range saves once 8 rows share the weights, so "auto"
 # takes resident for a single row and legacy otherwise.
-FP4_SPLIT_POLICY = os.environ.get("DGPP_FP4_SPLITS", "auto")
+FP4_SPLIT_POLICY = "auto"
 
 
 def pick_splits_fp4(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:

@@ -95,6 +95,7 @@ class Server:
         self.metrics = Metrics()
         self.started = int(time.time())
         self._stop = threading.Event()
+        self.failed_event = threading.Event()        # set by _fail_engine; the process entry point turns it into exit 2
         self._thread: Optional[threading.Thread] = None
         self.failed: Optional[str] = None
         self._tok_bytes = None
@@ -138,7 +139,7 @@ class Server:
         while not self._stop.is_set():
             if time.time() - self._tp_t >= self.throughput_log_s:
                 self._throughput_line(time.time())
-            busy = not self.sched.idle()
+            busy = not self.sched.idle() and not self.failed
             for req in self.http.poll(0 if busy else 50):
                 try:
                     self._route(req)
@@ -156,20 +157,24 @@ class Server:
                             self.world.cancel(self.sched, lv.rid)
                         else:
                             self.sched.cancel(lv.rid)
-            if not self.sched.idle():
+            if not self.sched.idle() and not self.failed:
                 try:
                     if self.world is not None:
                         self.world.tick(self.sched)
                     else:
                         self.sched.tick()
                 except Exception as e:
+                    # the loop keeps serving the sockets: the error events must leave, later requests get a 503
                     self._fail_engine(str(e))
-                    return
+                    continue
                 self._drain_events()
 
     def _fail_engine(self, why: str) -> None:
-        """Engine failure: every open request gets an error, the server stops accepting work."""
+        """Engine failure: every open request gets an engine_failure error, the server stops accepting work and, when
+        it runs as a process (`main`), the leader exits with status 2 (followers see the closed journal and exit 3)."""
         self.failed = why
+        self.failed_event.set()
+        rt.log("error", "serve", f"engine failure: {why}")
         err = rt.error_json(500, f"engine failure: {why}", type="engine_failure")
         for lv in list(self.live.values()):
             g = self.groups.get(lv.group)
@@ -660,8 +665,10 @@ def serve_deployment(config_path: str) -> int:
         name = os.path.basename(os.path.normpath(ck.dir))
     if world > 1:
         reducer = PeerReducer(dcfg.hidden, cfg["prefill_chunk"], torch.device(dev))
+    from ..engine.options import EngineOptions
     eng = KernelEngine(LLMEngine(model, max_batch=cfg["max_concurrency"], max_seq_len=cfg["max_context"],
-                                 prefill_chunk=cfg["prefill_chunk"], reducer=reducer, fuse_ar=cfg["fuse_all_reduce"]))
+                                 prefill_chunk=cfg["prefill_chunk"], reducer=reducer, fuse_ar=cfg["fuse_all_reduce"],
+                                 options=EngineOptions.from_config(cfg)))
     leader = None
     if world > 1:
         from .world import WorldLeader, run_follower
@@ -688,8 +695,11 @@ def serve_deployment(config_path: str) -> int:
                  world_leader=leader)
     print(f"listening on http://{cfg['host']}:{srv.start()}", flush=True)
     try:
-        while True:
-            time.sleep(3600)
+        while not srv.failed_event.wait(1.0):
+            pass
+        time.sleep(0.5)            # let the error responses leave the sockets
+        srv.stop()
+        return 2
     except KeyboardInterrupt:
         srv.stop()
     return 0

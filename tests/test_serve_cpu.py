@@ -197,3 +197,44 @@ def test_tool_choice_naming_an_unknown_function_is_rejected(server):
     assert st == 400 and json.loads(data)["error"]["param"] == "tool_choice"
     req["tool_choice"] = {"type": "function", "function": {"name": "f"}}
     assert _req(port, "POST", "/v1/chat/completions", json.dumps(req))[0] == 200
+
+
+def _failing_engine(ok_steps):
+    """A CPU reference engine that, after `ok_steps` decode passes, raises what KernelEngine raises when the device
+    status block reports a failed bounded wait (made on the host: nothing faults or hangs)."""
+    from dgpp_b200.engine.adapters import EngineFailure, ReferenceEngine
+    from dgpp_b200.models.dense import DenseConfig, DenseModel
+
+    class FailsAfter(ReferenceEngine):
+        left = ok_steps
+
+        def step_batch(self, slots):
+            if self.left <= 0:
+                raise EngineFailure("device status code=4 count=1 detail=1 (a bounded device wait gave up)")
+            self.left -= 1
+            return super().step_batch(slots)
+
+    model = DenseModel.random_init(DenseConfig.plumbing_fp32(vocab=256), device="cpu", seed=0)
+    return FailsAfter(model, slots=2, num_blocks=64, block_tokens=16, max_context=256)
+
+
+def test_engine_failure_reaches_open_streams_and_stops_the_server():
+    tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)], rt.SplitPattern.Qwen2)
+    eng = _failing_engine(ok_steps=3)
+    srv = Server(eng, tok, model_name="fake", eos_ids=[257])
+    port = srv.start()
+    try:
+        body = json.dumps({"model": "fake", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 50, "stream": True})
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=20)
+        c.request("POST", "/v1/chat/completions", body, {"Content-Type": "application/json"})
+        data = c.getresponse().read().decode()
+        c.close()
+        events = [json.loads(l[6:]) for l in data.splitlines() if l.startswith("data: {")]
+        assert any("choices" in e for e in events)                                   # some tokens were streamed
+        err = [e for e in events if "error" in e]
+        assert err and err[-1]["error"]["type"] == "engine_failure" and "device status" in err[-1]["error"]["message"]
+        assert srv.failed_event.wait(5.0)                                            # what main() turns into exit status 2
+        st, b = _req(port, "GET", "/health")
+        assert st == 503 and json.loads(b)["error"]["type"] == "engine_failure"
+    finally:
+        srv.stop()

@@ -88,3 +88,26 @@ def test_kv_memory_plan():
     assert blocks == (158 * gib) // per_block and nbytes == blocks * per_block and tokens == blocks * 64
     assert rt.plan_kv(2 * gib, 4 * gib, 0, 64, 8, 128, 64) == (0, 0, 0)
     assert rt.plan_kv(170 * gib, 0, 0, 64, 8, 128, 64, True, 1000)[0] == 1000
+
+
+def test_engine_options_are_config_keys_covered_by_the_digest():
+    """Switches that change what the engine computes are `engine_*` keys of the deployment configuration: the
+    digest that ranks compare moves with each of them, unknown values are refused, and EngineOptions reads them."""
+    from dgpp_b200.engine.options import EngineOptions
+
+    base = {"model": "tiny"}
+    text, d0 = rt.parse_cluster_config(json.dumps(base))
+    cfg = json.loads(text)
+    assert cfg["engine_fp4_splits"] == "auto" and cfg["engine_layer_kernel"] is False
+    seen = {d0}
+    for k, v in (("engine_decode_splits", 4), ("engine_fuse_combine", False), ("engine_l2_prefetch", True),
+                 ("engine_fp4_splits", "resident"), ("engine_cluster_splitk", True), ("engine_fp4_preload", False),
+                 ("engine_layer_kernel", True)):
+        t, d = rt.parse_cluster_config(json.dumps({**base, k: v}))
+        assert d not in seen, k
+        seen.add(d)
+        o = EngineOptions.from_config(json.loads(t))
+        assert getattr(o, k[len("engine_"):]) == v
+    for bad in ({"engine_fp4_splits": "fast"}, {"engine_decode_splits": -1}, {"engine_unknown": 1}):
+        with pytest.raises(Exception):
+            rt.parse_cluster_config(json.dumps({**base, **bad}))
