@@ -208,10 +208,26 @@ def bench_gdn(args, dev):
     layer, st = GdnLayer(w, args.rows, dev), GdnState(cfg, 1, dev)
     x = torch.randn(args.rows, cfg.hidden, device=dev).to(BF)
     out = torch.empty_like(x)
+    from ..ops import core as ops
     fn = lambda: layer.forward(x, st, out, slot=0)
-    ms = run([fn], args)
-    report(args, "gdn_layer_prefill", ms * 1.0, rows=args.rows, v_heads=args.hv,
-           note="in_proj + conv + recurrence + gated norm + out_proj of one layer; sequential recurrence")
+    res = {}
+    for name, chunked in (("chunked", True), ("sequential", False)):
+        ops.GDN_CHUNKED = chunked
+        res[name + "_layer_ms"] = run([fn], args)
+        # the scan alone: preparation + recurrence on the layer's convolution output
+        c = cfg
+        nq = c.k_heads * c.dk
+        conv = torch.randn(args.rows, 2 * nq + c.v_heads * c.dv, device=dev).to(BF)
+        ab = torch.randn(args.rows, 2 * c.v_heads, device=dev).to(BF)
+        o = torch.empty(args.rows, c.v_heads * c.dv, device=dev, dtype=BF)
+        scan = lambda: ops.gdn_recurrent(conv[:, :nq], conv[:, nq:2 * nq], conv[:, 2 * nq:], ab[:, :c.v_heads],
+                                         ab[:, c.v_heads:], w.A_log, w.dt_bias, st.ssm, o, c.k_heads, c.v_heads, c.dk,
+                                         c.dv, None, 0, True)
+        res[name + "_scan_ms"] = run([scan], args)
+    ops.GDN_CHUNKED = True
+    report(args, "gdn_layer_prefill", res["chunked_layer_ms"], rows=args.rows, v_heads=args.hv,
+           note="in_proj + conv + recurrence + gated norm + out_proj of one layer; *_scan_ms: preparation + recurrence only",
+           **res)
 
 
 def bench_moe(args, dev):

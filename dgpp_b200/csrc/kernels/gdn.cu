@@ -13,6 +13,7 @@
 //     g_t = -exp(A_log[h]) * softplus(alpha_t + dt_bias[h]),  b_t = sigmoid(beta_t)
 // (reference counterparts: src/kernels/gdn_chunk.cu chunked scan, src/kernels/kda.cu recurrent step.)
 #include <math.h>
+#include <string.h>
 
 #include "common/common.h"
 #include "common/dtypes.cuh"
@@ -259,6 +260,30 @@ DGPP_API int dgpp_gdn_recurrent(const void* q, int64_t q_stride, const void* k, 
   if (dk == 64) gdn_recurrent_kernel<64><<<grid, kGdnThreads, 0, st>>>(a);
   else if (dk == 128) gdn_recurrent_kernel<128><<<grid, kGdnThreads, 0, st>>>(a);
   else gdn_recurrent_kernel<256><<<grid, kGdnThreads, 0, st>>>(a);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Token-parallel preparation alone (unit-norm q / k, decay, write strength into `prep`); the chunked scan
+// (gdn_chunk.cu) consumes the same scratch layout.
+DGPP_API int dgpp_gdn_prep(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* alpha,
+                           const void* beta, int64_t ab_stride, const void* A_log, const void* dt_bias, void* prep, int T,
+                           int hk, int hv, int dk, cudaStream_t st) {
+  DGPP_REQUIRE(dk == 64 || dk == 128 || dk == 256, "gdn: key dim %d unsupported", dk);
+  DGPP_REQUIRE(prep != nullptr, "gdn: scratch of T * (2 * hk * dk + 2 * hv) floats required");
+  if (T == 0) return 0;
+  GdnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.q = static_cast<const bf16*>(q); a.k = static_cast<const bf16*>(k);
+  a.q_stride = q_stride; a.k_stride = k_stride;
+  a.alpha = static_cast<const bf16*>(alpha); a.beta = static_cast<const bf16*>(beta); a.ab_stride = ab_stride;
+  a.A_log = static_cast<const float*>(A_log); a.dt_bias = static_cast<const float*>(dt_bias);
+  a.prep = static_cast<float*>(prep);
+  a.T = T; a.hk = hk; a.hv = hv; a.dk = dk;
+  dim3 pgrid(T, hk + 1);
+  if (dk == 64) gdn_prep_kernel<64><<<pgrid, 64, 0, st>>>(a);
+  else if (dk == 128) gdn_prep_kernel<128><<<pgrid, 128, 0, st>>>(a);
+  else gdn_prep_kernel<256><<<pgrid, 256, 0, st>>>(a);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }

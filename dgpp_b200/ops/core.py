@@ -538,6 +538,24 @@ _lib.declare("dgpp_gdn_conv", [P, L, P, P, P, P, I, P, I, I, I, I, P])
 _lib.declare("dgpp_gated_rmsnorm", [P, P, L, P, P, I, I, I, F, P])
 
 
+_lib.declare("dgpp_gdn_prep", [P, L, P, L, P, P, L, P, P, P, I, I, I, I, P])
+_lib.declare("dgpp_gdn_chunk_scan", [P, P, P, P, P, L, P, P, P, L, I, I, I, I, I, P])
+# Sequential runs of at least this many rows take the chunked scan; shorter ones (and decode) the token recurrence.
+GDN_CHUNKED = True
+GDN_CHUNK_MIN_ROWS = 64
+_GDN_SCRATCH: dict = {}
+
+
+def _gdn_scratch(device, floats: int) -> torch.Tensor:
+    """Scratch of the chunked scan (W, U0, P, G per chunk and head), grown on demand and kept per device."""
+    key = str(device)
+    t = _GDN_SCRATCH.get(key)
+    if t is None or t.numel() < floats:
+        t = torch.empty(floats, dtype=torch.float32, device=device)
+        _GDN_SCRATCH[key] = t
+    return t
+
+
 def gdn_conv(x, w, bias, state, out, row_slot=None, slot: int = 0, sequential: bool = True):
     """Causal depthwise conv (width w.shape[1]) + SiLU.  x: [T, C] bf16 rows (may be a strided column view);
     state: [slots, W - 1, C] fp32, updated in place."""
@@ -556,6 +574,19 @@ def gdn_recurrent(q, k, v, alpha, beta, A_log, dt_bias, state, out, hk: int, hv:
     need = T * (2 * hk * dk + 2 * hv)
     if prep is None or prep.numel() < need:
         prep = torch.empty(need, dtype=torch.float32, device=q.device)
+    if sequential and GDN_CHUNKED and T >= GDN_CHUNK_MIN_ROWS and dk in (64, 128) and dv % 32 == 0:
+        # prefill: chunked scan (64-token chunks as small GEMMs) instead of T dependent token steps
+        chunks = (T + 63) // 64
+        floats = chunks * hv * 64 * (dk + dv + 65)
+        scr = _gdn_scratch(q.device, floats)
+        call("dgpp_gdn_prep", ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(alpha), ptr(beta), alpha.stride(0),
+             ptr(A_log), ptr(dt_bias), ptr(prep), T, hk, hv, dk, stream_ptr())
+        qn, kn = prep, prep[T * hk * dk:]
+        dec = prep[2 * T * hk * dk:]
+        bet = dec[T * hv:]
+        call("dgpp_gdn_chunk_scan", ptr(qn), ptr(kn), ptr(dec), ptr(bet), ptr(v), v.stride(0), ptr(state[slot]), ptr(out),
+             ptr(scr), scr.numel(), T, hk, hv, dk, dv, stream_ptr())
+        return out
     call("dgpp_gdn_recurrent", ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0), ptr(alpha), ptr(beta),
          alpha.stride(0), ptr(A_log), ptr(dt_bias), ptr(state), ptr(row_slot), slot, ptr(out), ptr(prep), T, hk, hv, dk,
          dv, int(sequential), stream_ptr())
