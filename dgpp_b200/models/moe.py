@@ -229,8 +229,39 @@ class MoEBlock:
         return ops.moe_combine(self.y, sh, self.ids[:rows], self.wts[:rows], self.slot_of, out, rows)
 
     def forward_gathered(self, xn: torch.Tensor) -> torch.Tensor:
-        """Prefill-sized batches: route on the device, then one GEMM pair per active expert over its gathered rows
-        (W4A16 converter GEMM, exact bf16 activations), ordered accumulation in fp32."""
+        """Prefill-sized batches, all on the device: router, counting sort of the (token, k) pairs by expert into tiles
+        of 64 rows, row gather, then the decode path's kernels with every tile as one slot -- residual-term quantiser,
+        grouped block-scaled gate/up GEMM, SwiGLU quantiser, grouped down GEMM -- and the ordered combine.  The tile
+        buffers are shared by all blocks of a device (one MoE block runs at a time).
+        (reference counterparts: src/kernels/glm_moe.cu:1382 segment count, :1553 tile list, :1121 grouped MMA.)"""
+        c, w = self.c, self.w
+        T = xn.shape[0]
+        bn, R = 64, self.terms
+        max_tiles = (T * c.top_k + bn - 1) // bn + self.local_experts
+        ws = _prefill_workspace(xn.device, max_tiles, bn, c.hidden, c.moe_ffn, R)
+        ids, wts = ops.moe_route(xn, w.gate, w.bias, c.top_k, c.n_group, c.topk_group, c.router == "softmax",
+                                 c.norm_topk_prob, c.routed_scaling)
+        tiles = ws["tile_expert"][:max_tiles]
+        pair_row, _, _ = ops.moe_segment_sort(ids, bn, max_tiles, self.e0, self.e1, ws["pair_row"][:T * c.top_k], tiles,
+                                              ws["n_tiles"])
+        rows = max_tiles * bn
+        xs, h, y = ws["xs"][:rows], ws["h"][:max_tiles], ws["y"][:max_tiles]
+        ops.moe_gather_rows(xn, pair_row, xs, c.top_k)
+        xa = ops.act_quant_nvfp4(xs, R, out=ws["qa_x"], group_list=tiles, group_rows=bn)
+        ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, h, bn, 2 * c.moe_ffn, c.hidden, self.local_experts, tiles,
+                             group_b=True)
+        xm = ops.act_quant_nvfp4(h.view(rows, 2 * c.moe_ffn), R, out=ws["qa_mid"], mode="swiglu", limit=c.swiglu_limit,
+                                 group_list=tiles, group_rows=bn)
+        ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, y, bn, c.hidden, c.moe_ffn, self.local_experts, tiles,
+                             group_b=True)
+        sh = None
+        if w.shared_gu is not None:
+            sh = ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu), limit=c.swiglu_limit), w.shared_down)
+        out = torch.empty(T, c.hidden, dtype=BF, device=xn.device)
+        return ops.moe_combine_rows(y.view(rows, c.hidden), sh, pair_row, wts, out)
+
+    def forward_looped(self, xn: torch.Tensor) -> torch.Tensor:
+        """Oracle of forward_gathered: one exact W4A16 GEMM pair per active expert over its gathered rows (host loop)."""
         c, w = self.c, self.w
         ids, wts = ops.moe_route(xn, w.gate, w.bias, c.top_k, c.n_group, c.topk_group, c.router == "softmax",
                                  c.norm_topk_prob, c.routed_scaling)
@@ -247,3 +278,25 @@ class MoEBlock:
         if w.shared_gu is not None:
             acc += ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu), limit=c.swiglu_limit), w.shared_down).float()
         return acc.to(BF)
+
+
+_PREFILL_WS: dict = {}
+
+
+def _prefill_workspace(device, max_tiles: int, bn: int, hidden: int, ffn: int, terms: int) -> dict:
+    """Tile buffers of MoEBlock.forward_gathered, kept per (device, geometry) and grown to the largest tile count."""
+    key = (str(device), bn, hidden, ffn, terms)
+    ws = _PREFILL_WS.get(key)
+    if ws is None or ws["max_tiles"] < max_tiles:
+        rows = max_tiles * bn
+        i32 = dict(dtype=torch.int32, device=device)
+        ws = dict(max_tiles=max_tiles,
+                  pair_row=torch.empty(rows, **i32), tile_expert=torch.full((max_tiles,), -1, **i32),
+                  n_tiles=torch.zeros(1, **i32),
+                  xs=torch.zeros(rows, hidden, dtype=BF, device=device),
+                  h=torch.zeros(max_tiles, bn, 2 * ffn, dtype=BF, device=device),
+                  y=torch.zeros(max_tiles, bn, hidden, dtype=BF, device=device),
+                  qa_x=ops.QuantAct(rows, hidden, terms, bn, device),
+                  qa_mid=ops.QuantAct(rows, ffn, terms, bn, device))
+        _PREFILL_WS[key] = ws
+    return ws

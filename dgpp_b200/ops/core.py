@@ -514,6 +514,39 @@ def moe_combine_push(y, shared, ids, weights, slot_of, comm, rows: int):
          ids.shape[1], y.shape[1], stream_ptr())
 
 
+_lib.declare("dgpp_moe_segment_sort", [P, P, P, P, I, I, I, I, I, I, P])
+_lib.declare("dgpp_moe_gather_rows", [P, L, P, P, I, I, I, P])
+_lib.declare("dgpp_moe_combine_rows", [P, P, P, P, P, I, I, I, P])
+
+
+def moe_segment_sort(ids, bn: int, max_tiles: int, e_begin: int, e_end: int, pair_row=None, tile_expert=None, n_tiles=None):
+    """Counting sort of the (token, k) pairs of `ids` [T, k] by local expert into tiles of bn rows (stable: pairs keep
+    their order inside an expert).  Returns pair_row [T * k] (row of the pair in the tiled buffer, -1 if its expert is
+    not in [e_begin, e_end)), tile_expert [max_tiles] (local expert id per tile, -1 beyond the last), n_tiles [1]."""
+    T, k = ids.shape
+    dev = ids.device
+    if pair_row is None:
+        pair_row = torch.empty(T * k, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+        n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    call("dgpp_moe_segment_sort", ptr(ids), ptr(pair_row), ptr(tile_expert), ptr(n_tiles), T, k, e_begin, e_end, bn,
+         max_tiles, stream_ptr())
+    return pair_row, tile_expert, n_tiles
+
+
+def moe_gather_rows(x, pair_row, xs, k: int):
+    """xs[pair_row[p]] = x[p // k] for every pair with a row."""
+    call("dgpp_moe_gather_rows", ptr(x), x.stride(0), ptr(pair_row), ptr(xs), x.shape[0], x.shape[1], k, stream_ptr())
+    return xs
+
+
+def moe_combine_rows(y, shared, pair_row, weights, out):
+    """out[t] = sum_j weights[t, j] * y[pair_row[t * k + j]] (+ shared[t]); y: [rows, H] bf16."""
+    T, k = weights.shape
+    call("dgpp_moe_combine_rows", ptr(y), ptr(shared), ptr(pair_row), ptr(weights), ptr(out), T, y.shape[-1], k, stream_ptr())
+    return out
+
+
 def gemm_fp4_grouped(xa: "QuantAct", wq, wsf_tiled, alphas, out, rows: int, n: int, k: int, experts: int, group_list,
                      group_b: bool, splits: int = 1, ws: Optional["GemmWorkspace"] = None):
     """Grouped block-scaled NVFP4 GEMM over stacked expert matrices (see dgpp_gemm_fp4_grouped).
