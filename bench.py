@@ -161,6 +161,9 @@ def main() -> int:
     ap.add_argument("--no-c1", action="store_true", help="skip the C=1 decode extra")
     ap.add_argument("--no-doll-shape", action="store_true",
                     help="skip the extra that runs this engine on the reference harness's shape (bf16 weights, C1)")
+    ap.add_argument("--config", type=int, default=1,
+                    help="1: the dense 27B-class headline (default); 2 / 3 / 4: end-to-end timings of the MLA + MoE, the "
+                         "sparse-index MLA + MoE and the hybrid GDN + MoE families at their named shapes (one GPU)")
     ap.add_argument("--bf12-head", action="store_true",
                     help="keep the bf16 lm head in its lossless 12-bit resident form (same logits bit for bit)")
     ap.add_argument("--layer-kernel", action="store_true",
@@ -170,6 +173,9 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.config != 1:
+        from dgpp_b200.bench import configs
+        return configs.run(args.config, args)
 
     import torch
     import torch.distributed as dist

@@ -1,0 +1,152 @@
+"""End-to-end timings of the MoE model families at their named shapes (random-init weights, synthetic prompts).
+
+    python bench.py --config 4 [--steps K] [--warmup W] [--layers L]     hybrid GDN + gated attention + MoE (Qwen-Next style)
+    python bench.py --config 2 [--steps K] [--warmup W] [--layers L]     MLA + MoE (DeepSeek-V3-style Flash)
+    python bench.py --config 3 ...                                       config 2 + lightning indexer, sparse MLA
+
+Each run builds the model at the named shape, prefills C sequences, times `K` decode steps at C = 1 and C = 8 (CUDA
+events around the whole step loop, host work of the runner included: these runners launch kernel by kernel, no captured
+graph) and cold prefills at the named lengths.  One JSON line per run.  `--layers` below the named depth is a debugging
+aid; its numbers are marked `"valid": false`.
+(reference counterparts: docs/benchmarks.md method section; the per-family forward checks under apps/.)
+"""
+from __future__ import annotations
+
+import json
+import time
+from typing import List
+
+import torch
+
+
+def _time_decode(runner, vocab: int, slots: List[int], steps: int, warmup: int, gen) -> float:
+    """ms per decode step for the listed request slots (greedy: feeds back argmax ids)."""
+    toks = torch.randint(0, vocab, (len(slots),), generator=gen).tolist()
+    for _ in range(max(warmup, 3)):
+        logits = runner.decode(slots, toks)
+        toks = torch.argmax(logits[:len(slots)], -1).tolist()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        logits = runner.decode(slots, toks)
+        toks = torch.argmax(logits[:len(slots)], -1).tolist()      # the step's result is read back every step
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def _time_prefill(runner, vocab: int, slot: int, n: int, gen, chunk: int) -> float:
+    runner.reset(slot)
+    toks = torch.randint(0, vocab, (n,), generator=gen).tolist()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    runner.prefill(slot, toks, chunk=chunk)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1000.0
+
+
+def _lean_experts() -> None:
+    """The grouped kernels read the stacked expert tensors; the per-expert copies (oracle inputs) are not kept."""
+    from ..models.moe import MoEWeights
+    MoEWeights.KEEP_EXPERT_LISTS = False
+
+
+def run_config4(args, dev) -> dict:
+    from ..models.hybrid import HybridConfig, HybridModel, HybridRunner
+    from ..models.moe import MoEConfig
+
+    layers = args.layers if args.layers < 48 else 48
+    cfg = HybridConfig(layers=layers, hidden=2048, full_every=4, q_heads=16, kv_heads=2, head_dim=256, gdn_k_heads=16,
+                       gdn_v_heads=16, gdn_dk=128, gdn_dv=128, vocab=151936,
+                       moe=MoEConfig(hidden=2048, experts=512, top_k=10, moe_ffn=512, shared_ffn=512, router="softmax"))
+    t0 = time.time()
+    _lean_experts()
+    model = HybridModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4")
+    torch.cuda.synchronize()
+    init_s = time.time() - t0
+    C, chunk = 8, 2048
+    prefix, suffix = 16384, 512
+    runner = HybridRunner(model, max_rows=chunk, slots=C, max_seq_len=prefix + suffix + 4096, device=dev)
+    g = torch.Generator().manual_seed(4)
+    out = {"config": 4, "model": "hybrid GDN(16v/16qk x128, chunked scan) 3:1 gated GQA(16q/2kv x256) + MoE 512e top-10 + shared, "
+                                 f"hidden 2048, {layers} layers, NVFP4 weights, FP8 KV", "layers": layers,
+           "valid": layers == 48, "init_s": round(init_s, 1), "mtp": "off (the MTP head is not drafted by this runner)"}
+    out["prefill_s_2048"] = _time_prefill(runner, cfg.vocab, 0, 2048, g, chunk)
+    # the trace's shape: a 16K shared prefix, then a unique suffix.  A prefix hit restores the prefix's KV blocks and
+    # recurrent-state snapshot, so its prefill cost is the suffix run on top of the resident prefix.
+    out["prefill_s_16384"] = _time_prefill(runner, cfg.vocab, 0, prefix, g, chunk)
+    toks = torch.randint(0, cfg.vocab, (suffix,), generator=g).tolist()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    runner.prefill(0, toks, chunk=chunk)
+    e1.record()
+    torch.cuda.synchronize()
+    out["prefix_hit_prefill_s_16k_plus_512"] = e0.elapsed_time(e1) / 1000.0
+    for s in range(1, C):
+        runner.reset(s)
+        runner.prefill(s, torch.randint(0, cfg.vocab, (2048,), generator=g).tolist(), chunk=chunk)
+    ms1 = _time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g)
+    ms8 = _time_decode(runner, cfg.vocab, list(range(C)), args.steps, args.warmup, g)
+    out.update(c1_decode_tok_s=1000.0 / ms1, c1_ms_per_step=ms1, c8_decode_tok_s=1000.0 * C / ms8, c8_ms_per_step=ms8,
+               steps=args.steps, context="slot 0 at ~17K, slots 1-7 at 2K")
+    return out
+
+
+def run_config2(args, dev, indexer: bool = False) -> dict:
+    from ..models.mla_moe import MlaMoeConfig, MlaMoeModel, MlaMoeRunner
+    from ..models.moe import MoEConfig
+
+    layers = args.layers if args.layers < 48 else 48
+    cfg = MlaMoeConfig(layers=layers, hidden=4096, heads=32, q_lora=1024, kv_lora=512, nope=128, rope=64, v_dim=128,
+                       ffn=12288, dense_layers=min(2, layers), vocab=129280,
+                       moe=MoEConfig(hidden=4096, experts=256, top_k=8, moe_ffn=1536, shared_ffn=1536, n_group=8,
+                                     topk_group=4, router="sigmoid", routed_scaling=2.5),
+                       index_heads=64 if indexer else 0, index_dim=128, index_topk=2048)
+    t0 = time.time()
+    _lean_experts()
+    model = MlaMoeModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4")
+    torch.cuda.synchronize()
+    init_s = time.time() - t0
+    C = 8
+    max_len = args.prompt_len + 512
+    runner = MlaMoeRunner(model, max_rows=256, slots=C, max_seq_len=max_len, device=dev)
+    g = torch.Generator().manual_seed(2)
+    out = {"config": 3 if indexer else 2,
+           "model": "MLA (q_lora 1024, kv_lora 512, nope 128 + rope 64, v 128, 32 heads) + MoE 256e top-8 (8 groups, top-4) + shared, "
+                    f"hidden 4096, {layers} layers ({cfg.dense_layers} dense FFN 12288), NVFP4 weights, bf16 latent cache"
+                    + (", lightning indexer 64 x 128, top-2048 sparse attention" if indexer else ""),
+           "layers": layers, "valid": layers == 48, "init_s": round(init_s, 1),
+           "note": "weights NVFP4 throughout (the family's MXFP4 experts and FP8 128x128 attention weights map onto the same "
+                   "block-scaled / converter kernels); attention through the absorbed-latent decode kernel for prefill rows too"}
+    L = args.prompt_len
+    out[f"prefill_s_{L}"] = _time_prefill(runner, cfg.vocab, 0, L, g, 256)
+    for s in range(1, C):
+        runner.reset(s)
+        runner.prefill(s, torch.randint(0, cfg.vocab, (L,), generator=g).tolist(), chunk=256)
+    ms1 = _time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g)
+    ms8 = _time_decode(runner, cfg.vocab, list(range(C)), args.steps, args.warmup, g)
+    out.update(c1_decode_tok_s=1000.0 / ms1, c1_ms_per_step=ms1, c8_decode_tok_s=1000.0 * C / ms8, c8_ms_per_step=ms8,
+               steps=args.steps, context=L)
+    return out
+
+
+def run(config: int, args) -> int:
+    from ..ops import core as ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if config == 4:
+        res = run_config4(args, dev)
+    elif config in (2, 3):
+        res = run_config2(args, dev, indexer=config == 3)
+    else:
+        raise SystemExit(f"--config {config}: 2, 3 or 4")
+    ops.check_status()
+    res["n_gpus"] = 1
+    res["data"] = "synthetic"
+    print(json.dumps(res))
+    return 0

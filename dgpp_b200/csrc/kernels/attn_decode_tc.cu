@@ -55,18 +55,22 @@ __device__ __forceinline__ uint32_t sw128_byte(uint32_t row, uint32_t byte_in_ro
   return row * 128u + ((((byte_in_row >> 4) ^ (row & 7u)) << 4) | (byte_in_row & 15u));
 }
 
-// G = query heads per kv head (<= 8); head_dim fixed at 128.
-template <int G>
+// G = query heads per kv head (<= 8); D = head_dim, 128 or 256.  A 256-wide head is handled as two 128-byte halves:
+// K / V / q tiles hold half 0 then half 1 (each [rows, 128 B], 128-byte swizzle), MMA1 runs 8 k-steps over both
+// halves, MMA2 writes one 16-column accumulator per half and thread `idx` owns output dims idx and 128 + idx.
+template <int G, int D>
 __global__ void __launch_bounds__(kAdThreads, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       AttnTcParams p) {
-  constexpr int D = 128;
-  constexpr int kStage = kAdTile * D;  // 16 KB of e4m3
+  constexpr int NH = D / 128;          // 128-byte halves of a head
+  constexpr int kHalf = kAdTile * 128;  // 16 KB: one half of a K or V tile
+  constexpr int kStage = kAdTile * D;
+  constexpr int kTmemCols = NH == 1 ? 64 : 128;
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   unsigned char* sp = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* sK = sp;  sp += kAdStages * kStage;
   unsigned char* sV = sp;  sp += kAdStages * kStage;
-  unsigned char* sQ = sp;  sp += kAdCols * 128;        // 2 KB
+  unsigned char* sQ = sp;  sp += NH * kAdCols * 128;   // 2 KB per half
   unsigned char* sP = sp;  sp += 2 * kAdCols * 128;    // 2 x 2 KB
   float* red = reinterpret_cast<float*>(sp);  sp += 2 * 4 * 12 * sizeof(float);   // [parity][warp][G + 1 (+pad)]
   float* redl = reinterpret_cast<float*>(sp); sp += 4 * 8 * sizeof(float);
@@ -99,7 +103,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     tma_prefetch_desc(&tmV);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 64);
+    tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   pdl_wait();
@@ -107,13 +111,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   float q_scale[G];
   if (warp >= 2) {
     const int d = threadIdx.x - 64;  // 0..127
-    float qv[G];
-#pragma unroll
-    for (int h = 0; h < G; ++h)
-      qv[h] = bf16_to_f32(p.q[static_cast<size_t>(row) * p.q_stride + (kvh * G + h) * D + d]);
 #pragma unroll
     for (int h = 0; h < G; ++h) {
-      float a = fabsf(qv[h]);
+      float a = 0.f;
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf)
+        a = fmaxf(a, fabsf(bf16_to_f32(p.q[static_cast<size_t>(row) * p.q_stride + (kvh * G + h) * D + hf * 128 + d])));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
       if (lane == 0) redl[(warp - 2) * 8 + h] = a;
@@ -124,17 +127,23 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const int d = threadIdx.x - 64;
 #pragma unroll
     for (int h = 0; h < 8; ++h) {
-      uint8_t b1 = 0, b2 = 0;
+      float sc = 1.f;
       if (h < G) {
         const float am = fmaxf(fmaxf(redl[h], redl[8 + h]), fmaxf(redl[16 + h], redl[24 + h]));
-        const float sc = am > 0.f ? am / 448.f : 1.f;
+        sc = am > 0.f ? am / 448.f : 1.f;
         q_scale[h < G ? h : 0] = sc;
-        const float v = bf16_to_f32(p.q[static_cast<size_t>(row) * p.q_stride + (kvh * G + h) * D + d]) / sc;
-        b1 = f32_to_e4m3(v);
-        b2 = f32_to_e4m3((v - e4m3_value_f32(v)) * 16.f);   // residual against the VALUE of b1 (no fp8 decode of b1)
       }
-      sQ[sw128_byte(h, d)] = b1;
-      sQ[sw128_byte(8 + h, d)] = b2;
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+        uint8_t b1 = 0, b2 = 0;
+        if (h < G) {
+          const float v = bf16_to_f32(p.q[static_cast<size_t>(row) * p.q_stride + (kvh * G + h) * D + hf * 128 + d]) / sc;
+          b1 = f32_to_e4m3(v);
+          b2 = f32_to_e4m3((v - e4m3_value_f32(v)) * 16.f);   // residual against the VALUE of b1 (no fp8 decode of b1)
+        }
+        sQ[hf * kAdCols * 128 + sw128_byte(h, d)] = b1;
+        sQ[hf * kAdCols * 128 + sw128_byte(8 + h, d)] = b2;
+      }
     }
     fence_proxy_async_smem();
   }
@@ -143,7 +152,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base;        // 2 x 16 columns
-  const uint32_t tmem_o = tmem_base + 32;   // 2 x 16 columns
+  const uint32_t tmem_o = tmem_base + 32;   // 2 x NH x 16 columns
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -158,8 +167,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
           const int pi = min(page0 + pg, p.max_blocks - 1);
           const int blk = bt[pi];
           const int r0 = (blk * p.hkv + kvh) * p.page;
-          tma_load_2d(sK + s * kStage + pg * p.page * D, &tmK, 0, r0, &kv_full[s]);
-          tma_load_2d(sV + s * kStage + pg * p.page * D, &tmV, 0, r0, &kv_full[s]);
+#pragma unroll
+          for (int hf = 0; hf < NH; ++hf) {
+            tma_load_2d(sK + s * kStage + hf * kHalf + pg * p.page * 128, &tmK, hf * 128, r0, &kv_full[s]);
+            tma_load_2d(sV + s * kStage + hf * kHalf + pg * p.page * 128, &tmV, hf * 128, r0, &kv_full[s]);
+          }
         }
         if (*abort_flag) break;
       }
@@ -176,9 +188,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         const uint32_t v_addr = smem_u32(sV + s * kStage);
         const uint32_t p_addr = smem_u32(sP + b * kAdCols * 128);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)  // 32 tokens per step: 4 groups of 8 token rows (1024 bytes each)
-          umma_f8f6f4(tmem_o + b * 16, umma_desc_sw128(v_addr + k * 4096), umma_desc_sw128(p_addr + k * 32), idesc2,
-                      k > 0 ? 1u : 0u);
+        for (int hf = 0; hf < NH; ++hf)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // 32 tokens per step: 4 groups of 8 token rows (1024 bytes each)
+            umma_f8f6f4(tmem_o + (b * NH + hf) * 16, umma_desc_sw128(v_addr + hf * kHalf + k * 4096),
+                        umma_desc_sw128(p_addr + k * 32), idesc2, k > 0 ? 1u : 0u);
         umma_commit(&o_full[b]);
         umma_commit(&kv_empty[s]);
       };
@@ -189,9 +203,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sK + s * kStage);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)  // 32 bytes of d per step
-          umma_f8f6f4(tmem_s + b * 16, umma_desc_sw128(k_addr + k * 32), umma_desc_sw128(q_addr + k * 32), idesc1,
-                      k > 0 ? 1u : 0u);
+        for (int k = 0; k < 4 * NH; ++k)  // 32 bytes of d per step, half k / 4
+          umma_f8f6f4(tmem_s + b * 16, umma_desc_sw128(k_addr + (k >> 2) * kHalf + (k & 3) * 32),
+                      umma_desc_sw128(q_addr + (k >> 2) * kAdCols * 128 + (k & 3) * 32), idesc1, k > 0 ? 1u : 0u);
         umma_commit(&s_full[b]);
         if (i > 0) {
           if (!wait_bar(&p_full[(i - 1) & 1], ((i - 1) >> 1) & 1)) { report(p.status, kTimeoutConvert, 23); *abort_flag = 1; ok = false; break; }
@@ -218,9 +232,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int wslot = warp - 2;
     const float sm = p.scale * 1.4426950408889634f;  // scores in log2 units
-    float m_run[G], l_thr[G], o_acc[G];
+    float m_run[G], l_thr[G], o_acc[NH][G];
 #pragma unroll
-    for (int h = 0; h < G; ++h) { m_run[h] = -INFINITY; l_thr[h] = 0.f; o_acc[h] = 0.f; }
+    for (int h = 0; h < G; ++h) {
+      m_run[h] = -INFINITY; l_thr[h] = 0.f;
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) o_acc[hf][h] = 0.f;
+    }
     float inv_c_prev = 0.f;
     bool ok = true;
     // token scales of the first tile
@@ -309,19 +327,24 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         const int bp = (i - 1) & 1;
         if (wait_bar(&o_full[bp], ((i - 1) >> 1) & 1)) {
           tc_fence_after();
-          uint32_t oc[16];
-          tmem_ld_x16(tmem_o + bp * 16 + lane_addr, oc);
-          tmem_ld_wait();
 #pragma unroll
-          for (int h = 0; h < G; ++h)
-            o_acc[h] += (__uint_as_float(oc[h]) + __uint_as_float(oc[8 + h]) * 0.0625f) * inv_c_prev;
+          for (int hf = 0; hf < NH; ++hf) {
+            uint32_t oc[16];
+            tmem_ld_x16(tmem_o + (bp * NH + hf) * 16 + lane_addr, oc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int h = 0; h < G; ++h)
+              o_acc[hf][h] += (__uint_as_float(oc[h]) + __uint_as_float(oc[8 + h]) * 0.0625f) * inv_c_prev;
+          }
         } else {
           report(p.status, kTimeoutAccum, 26);
           *abort_flag = 1;  // agreed on at the next tile's barrier
         }
       }
 #pragma unroll
-      for (int h = 0; h < G; ++h) o_acc[h] *= corr[h];
+      for (int h = 0; h < G; ++h)
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) o_acc[hf][h] *= corr[h];
       inv_c_prev = c_tile > 0.f ? 1.f / c_tile : 0.f;
       tc_fence_before();
     }
@@ -329,12 +352,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       const int j = ntiles - 1, bp = j & 1;
       if (wait_bar(&o_full[bp], (j >> 1) & 1)) {
         tc_fence_after();
-        uint32_t oc[16];
-        tmem_ld_x16(tmem_o + bp * 16 + lane_addr, oc);
-        tmem_ld_wait();
 #pragma unroll
-        for (int h = 0; h < G; ++h)
-          o_acc[h] += (__uint_as_float(oc[h]) + __uint_as_float(oc[8 + h]) * 0.0625f) * inv_c_prev;
+        for (int hf = 0; hf < NH; ++hf) {
+          uint32_t oc[16];
+          tmem_ld_x16(tmem_o + (bp * NH + hf) * 16 + lane_addr, oc);
+          tmem_ld_wait();
+#pragma unroll
+          for (int h = 0; h < G; ++h)
+            o_acc[hf][h] += (__uint_as_float(oc[h]) + __uint_as_float(oc[8 + h]) * 0.0625f) * inv_c_prev;
+        }
       } else {
         report(p.status, kTimeoutAccum, 27);
         *abort_flag = 1;
@@ -355,10 +381,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       const float l = redl[h] + redl[8 + h] + redl[16 + h] + redl[24 + h];
       const int hh = kvh * G + h;
       if (p.splits == 1) {
-        p.out[(static_cast<size_t>(row) * p.hq + hh) * D + idx] = f32_to_bf16(l > 0.f ? o_acc[h] / l : 0.f);
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf)
+          p.out[(static_cast<size_t>(row) * p.hq + hh) * D + hf * 128 + idx] = f32_to_bf16(l > 0.f ? o_acc[hf][h] / l : 0.f);
       } else {
         const size_t pi = (static_cast<size_t>(row) * p.hq + hh) * p.splits + split;
-        p.part_acc[pi * D + idx] = o_acc[h];
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) p.part_acc[pi * D + hf * 128 + idx] = o_acc[hf][h];
         if (idx == 0) {
           // running max is kept in log2 units; the combine kernel works in natural-log units
           p.part_ml[pi * 2] = m_run[h] * 0.6931471805599453f;
@@ -369,7 +398,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 64);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 __global__ void attn_tc_combine_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc,
@@ -390,21 +419,22 @@ __global__ void attn_tc_combine_kernel(const float* __restrict__ part_ml, const 
   out[rh * D + d] = f32_to_bf16(ll > 0.f ? a / ll : 0.f);
 }
 
-template <int G>
+template <int G, int D>
 static int launch_attn_tc(const CUtensorMap& tK, const CUtensorMap& tV, const AttnTcParams& p, cudaStream_t st) {
-  constexpr size_t smem = 1024 + 2 * kAdStages * kAdTile * 128 + kAdCols * 128 * 3 + 2 * 4 * 12 * 4 + 4 * 8 * 4 +
+  constexpr size_t smem = 1024 + 2 * kAdStages * kAdTile * D + kAdCols * 128 * (2 + D / 128) + 2 * 4 * 12 * 4 + 4 * 8 * 4 +
                           (2 * kAdStages + 6) * 8 + 64;
+  static_assert(smem <= 227 * 1024, "attn_decode_tc: shared memory over the per-CTA limit");
   static bool attr = false;
   if (!attr) {
-    DGPP_CUDA_OK(cudaFuncSetAttribute(attn_decode_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    DGPP_CUDA_OK(cudaFuncSetAttribute(attn_decode_tc_kernel<G, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
     attr = true;
   }
   dim3 grid(p.hkv, p.splits, p.rows);
-  attn_decode_tc_kernel<G><<<grid, kAdThreads, smem, st>>>(tK, tV, p);
+  attn_decode_tc_kernel<G, D><<<grid, kAdThreads, smem, st>>>(tK, tV, p);
   DGPP_CUDA_OK(cudaGetLastError());
   if (p.splits > 1 && p.out != nullptr) {   // out == nullptr: the caller folds the partials itself (dgpp_attn_combine_quant)
-    attn_tc_combine_kernel<<<p.rows * p.hq, 128, 0, st>>>(p.part_ml, p.part_acc, p.out, p.splits);
+    attn_tc_combine_kernel<<<p.rows * p.hq, D, 0, st>>>(p.part_ml, p.part_acc, p.out, p.splits);
     DGPP_CUDA_OK(cudaGetLastError());
   }
   return 0;
@@ -414,14 +444,14 @@ static int launch_attn_tc(const CUtensorMap& tK, const CUtensorMap& tV, const At
 
 using namespace dgpp;
 
-// Tensor-core decode attention over an FP8 paged cache; head_dim 128, hq / hkv <= 8, page in {16, 32, 64, 128}.
+// Tensor-core decode attention over an FP8 paged cache; head_dim 128 or 256, hq / hkv <= 8, page in {16, 32, 64, 128}.
 // num_blocks = blocks in the pool (extent of the TMA descriptors).
 DGPP_API int dgpp_attn_decode_tc(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                  const void* k_scale, const void* v_scale, const void* block_table,
                                  const void* row_req, const void* positions, void* part_ml, void* part_acc,
                                  void* out, int rows, int hq, int hkv, int d, int page, int max_blocks,
                                  int num_blocks, int splits, float scale, int window, cudaStream_t st) {
-  DGPP_REQUIRE(d == 128, "attn_decode_tc: head_dim %d != 128", d);
+  DGPP_REQUIRE(d == 128 || d == 256, "attn_decode_tc: head_dim %d (128 or 256)", d);
   DGPP_REQUIRE(hkv > 0 && hq % hkv == 0 && hq / hkv <= 8, "attn_decode_tc: unsupported head grouping %d/%d", hq, hkv);
   DGPP_REQUIRE(page == 16 || page == 32 || page == 64 || page == 128, "attn_decode_tc: page %d unsupported", page);
   DGPP_REQUIRE(splits >= 1 && (splits == 1 || (part_ml && part_acc)), "attn_decode_tc: scratch required for splits");
@@ -443,19 +473,28 @@ DGPP_API int dgpp_attn_decode_tc(const void* q, int64_t q_stride, const void* k_
   p.window = window; p.scale = scale;
   const uint64_t total_rows = static_cast<uint64_t>(num_blocks) * hkv * page;
   CUtensorMap tK, tV;
-  if (make_tmap_2d(&tK, k_cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 128, total_rows, 128, 128, page,
+  if (make_tmap_2d(&tK, k_cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d, total_rows, d, 128, page,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return -1;
-  if (make_tmap_2d(&tV, v_cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 128, total_rows, 128, 128, page,
+  if (make_tmap_2d(&tV, v_cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d, total_rows, d, 128, page,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return -1;
-  switch (hq / hkv) {
-    case 1: return launch_attn_tc<1>(tK, tV, p, st);
-    case 2: return launch_attn_tc<2>(tK, tV, p, st);
-    case 4: return launch_attn_tc<4>(tK, tV, p, st);
-    case 5: return launch_attn_tc<5>(tK, tV, p, st);
-    case 8: return launch_attn_tc<8>(tK, tV, p, st);
+  if (d == 256) {
+    switch (hq / hkv) {
+      case 1: return launch_attn_tc<1, 256>(tK, tV, p, st);
+      case 2: return launch_attn_tc<2, 256>(tK, tV, p, st);
+      case 4: return launch_attn_tc<4, 256>(tK, tV, p, st);
+      case 8: return launch_attn_tc<8, 256>(tK, tV, p, st);
+    }
+  } else {
+    switch (hq / hkv) {
+      case 1: return launch_attn_tc<1, 128>(tK, tV, p, st);
+      case 2: return launch_attn_tc<2, 128>(tK, tV, p, st);
+      case 4: return launch_attn_tc<4, 128>(tK, tV, p, st);
+      case 5: return launch_attn_tc<5, 128>(tK, tV, p, st);
+      case 8: return launch_attn_tc<8, 128>(tK, tV, p, st);
+    }
   }
-  dgpp_set_error("attn_decode_tc: group size %d not instantiated", hq / hkv);
+  dgpp_set_error("attn_decode_tc: group size %d at head_dim %d not instantiated", hq / hkv, d);
   return -1;
 }

@@ -195,6 +195,26 @@ class HybridRunner:
         self.logits = torch.empty(max_rows, c.vocab, dtype=torch.float32, device=device)
         self.lengths = [0] * slots
         self.scale = 1.0 / math.sqrt(d)
+        self.use_graphs, self._graphs, self._static = True, {}, {}
+        # tensor-core attention (FP8 cache as stored): head_dim 128 / 256, up to 8 query heads per kv head
+        self.tc_attn = (torch.device(device).type == "cuda" and d in (128, 256)
+                        and c.q_heads // c.kv_heads in (1, 2, 4, 8))
+        self.max_splits = 32
+        if self.tc_attn:
+            r = min(max_rows, 16)
+            self.att_scratch = (torch.empty(r * c.q_heads * self.max_splits * 2, dtype=torch.float32, device=device),
+                                torch.empty(r * c.q_heads * self.max_splits * d, dtype=torch.float32, device=device))
+
+    def _decode_splits(self, rows: int) -> int:
+        """KV splits of a decode pass: enough CTAs (kv heads x rows x splits) to cover the SMs; fixed per batch width,
+        so a captured pass stays valid at every context length (a split past the end writes an empty partial)."""
+        if rows > 16:
+            return 1
+        return max(1, min(self.max_splits, -(-160 // (self.c.kv_heads * rows))))
+
+    def _state_tensors(self):
+        """Tensors a decode pass updates in place besides the KV cache (recurrent layers' state)."""
+        return [t for st in self.gdn_state.values() for t in (st.conv, st.ssm)]
 
     def reset(self, slot: int) -> None:
         self.kv.release(slot)
@@ -216,9 +236,10 @@ class HybridRunner:
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, chunk_slot: Optional[int] = None,
-                all_logits: bool = True) -> torch.Tensor:
+                all_logits: bool = True, pos0: Optional[int] = None) -> torch.Tensor:
         """tokens / positions / row_req: int32 [rows] on the device.  chunk_slot given: the rows are consecutive
-        tokens of that request (prefill chunk); otherwise one decode token per row.  Returns fp32 logits [rows, V]."""
+        tokens of that request starting at position pos0 (prefill chunk); otherwise one decode token per row.
+        Returns fp32 logits [rows, V]."""
         m, c = self.m, self.c
         rows = tokens.shape[0]
         x, xn, delta = self.x[:rows], self.xn[:rows], self.delta[:rows]
@@ -235,8 +256,16 @@ class HybridRunner:
                 ops.linear(xn, L.qkv, out=qkv)
                 ops.rope_kv_write(qkv, positions, row_req, self.kv.block_table, m.inv_freq, cache, c.q_heads, c.kv_heads,
                                   c.head_dim)
-                ops.attn_decode(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, c.q_heads, c.kv_heads,
-                                c.head_dim, self.scale, out=attn)
+                if self.tc_attn and chunk_slot is not None and pos0 is not None:
+                    ops.attn_prefill_tc(qkv, qkv.stride(0), cache, self.kv.block_table[chunk_slot], pos0, c.q_heads,
+                                        c.kv_heads, c.head_dim, self.scale, out=attn, rows=rows)
+                elif self.tc_attn and rows <= 16:
+                    ops.attn_decode_tc(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, c.q_heads,
+                                       c.kv_heads, c.head_dim, self.scale, splits=self._decode_splits(rows),
+                                       scratch=self.att_scratch, out=attn)
+                else:
+                    ops.attn_decode(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, c.q_heads,
+                                    c.kv_heads, c.head_dim, self.scale, out=attn)
                 ops.linear(attn, L.o, out=delta)
             have = True
             ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
@@ -256,8 +285,42 @@ class HybridRunner:
             t = torch.tensor(part, dtype=torch.int32, device=self.dev)
             pos = torch.arange(start + o, start + o + len(part), dtype=torch.int32, device=self.dev)
             req = torch.full((len(part),), slot, dtype=torch.int32, device=self.dev)
-            out = self.forward(t, pos, req, chunk_slot=slot, all_logits=False)
+            out = self.forward(t, pos, req, chunk_slot=slot, all_logits=False, pos0=start + o)
         self.lengths[slot] = start + len(tokens)
+        return out
+
+    def _decode_rows(self, slots: List[int], tokens: List[int], positions: List[int]) -> torch.Tensor:
+        """One decode pass.  On a GPU the pass is captured once per batch width into a CUDA graph over static id /
+        position / request tensors and replayed (a pass is hundreds of small launches; replay removes the host's
+        launch cost from every step); `use_graphs = False` launches kernel by kernel."""
+        b = len(slots)
+        host = torch.tensor([tokens, positions, slots], dtype=torch.int32)
+        if not (self.use_graphs and torch.device(self.dev).type == "cuda"):
+            d = host.to(self.dev)
+            return self.forward(d[0], d[1], d[2])
+        st = self._static.get(b)
+        if st is None:
+            st = self._static[b] = torch.zeros(3, b, dtype=torch.int32, device=self.dev)
+        st.copy_(host, non_blocking=True)
+        g = self._graphs.get(b)
+        if g is None:
+            # warm-up outside capture (lazy kernel attributes, workspaces); state-carrying layers are advanced by it,
+            # so their state is saved before and put back after: only replays move the model forward
+            saved = [t.clone() for t in self._state_tensors()]
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.forward(st[0], st[1], st[2])
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.forward(st[0], st[1], st[2])
+            for t, s0 in zip(self._state_tensors(), saved):
+                t.copy_(s0)
+            g = self._graphs[b] = (graph, out)
+        graph, out = g
+        graph.replay()
         return out
 
     @torch.no_grad()
@@ -265,10 +328,7 @@ class HybridRunner:
         """One token for every listed request; returns logits [len(slots), V]."""
         for s in slots:
             assert self.kv.reserve(s, self.lengths[s] + 1), "KV pool exhausted"
-        t = torch.tensor(tokens, dtype=torch.int32, device=self.dev)
-        pos = torch.tensor([self.lengths[s] for s in slots], dtype=torch.int32, device=self.dev)
-        req = torch.tensor(slots, dtype=torch.int32, device=self.dev)
-        out = self.forward(t, pos, req)
+        out = self._decode_rows(slots, tokens, [self.lengths[s] for s in slots])
         for s in slots:
             self.lengths[s] += 1
         return out

@@ -187,10 +187,14 @@ class MlaMoeRunner:
         self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
                     if L.moe is not None and L.moe.gu_q is not None}
         self.scale = 1.0 / math.sqrt(c.nope + c.rope)
+        self.use_graphs, self._graphs, self._static = True, {}, {}
         self.scores = torch.empty(max_rows, self.max_ctx, dtype=torch.float32, device=device) if c.index_heads else None
 
     def reset(self, slot: int) -> None:
         self.lengths[slot] = 0
+
+    def _state_tensors(self):
+        return []          # the latent / index-key cache writes of a pass are idempotent
 
     def _append(self, cache: torch.Tensor, rows: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor) -> None:
         blk = self.block_table[row_req.long(), (positions // self.page).long()].long()
@@ -257,12 +261,43 @@ class MlaMoeRunner:
         self.lengths[slot] = start + len(tokens)
         return out
 
+    def _decode_rows(self, slots: List[int], tokens: List[int], positions: List[int]) -> torch.Tensor:
+        """One decode pass.  On a GPU the pass is captured once per batch width into a CUDA graph over static id /
+        position / request tensors and replayed (a pass is hundreds of small launches; replay removes the host's
+        launch cost from every step); `use_graphs = False` launches kernel by kernel."""
+        b = len(slots)
+        host = torch.tensor([tokens, positions, slots], dtype=torch.int32)
+        if not (self.use_graphs and torch.device(self.dev).type == "cuda"):
+            d = host.to(self.dev)
+            return self.forward(d[0], d[1], d[2])
+        st = self._static.get(b)
+        if st is None:
+            st = self._static[b] = torch.zeros(3, b, dtype=torch.int32, device=self.dev)
+        st.copy_(host, non_blocking=True)
+        g = self._graphs.get(b)
+        if g is None:
+            # warm-up outside capture (lazy kernel attributes, workspaces); state-carrying layers are advanced by it,
+            # so their state is saved before and put back after: only replays move the model forward
+            saved = [t.clone() for t in self._state_tensors()]
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.forward(st[0], st[1], st[2])
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.forward(st[0], st[1], st[2])
+            for t, s0 in zip(self._state_tensors(), saved):
+                t.copy_(s0)
+            g = self._graphs[b] = (graph, out)
+        graph, out = g
+        graph.replay()
+        return out
+
     @torch.no_grad()
     def decode(self, slots: List[int], tokens: List[int]) -> torch.Tensor:
-        t = torch.tensor(tokens, dtype=torch.int32, device=self.dev)
-        pos = torch.tensor([self.lengths[s] for s in slots], dtype=torch.int32, device=self.dev)
-        req = torch.tensor(slots, dtype=torch.int32, device=self.dev)
-        out = self.forward(t, pos, req)
+        out = self._decode_rows(slots, tokens, [self.lengths[s] for s in slots])
         for s in slots:
             self.lengths[s] += 1
         return out

@@ -62,6 +62,9 @@ class MoEWeights:
     # router weights are replicated; the shared expert lives on rank 0
     e_begin: int = 0
     e_end: int = 0
+    # False: `stack` drops the per-expert tensors once the stacked device tensors exist (large models: the lists would
+    # double the expert memory; only the PyTorch oracles and the expert-loop check read them)
+    KEEP_EXPERT_LISTS = True
 
     @staticmethod
     def random_init(cfg: MoEConfig, device, seed: int = 0, std: float = 0.02, fmt: str = "nvfp4", ep_rank: int = 0,
@@ -108,7 +111,11 @@ class MoEWeights:
             al = torch.tensor([w.alpha for w in ws], dtype=torch.float32, device=q.device)
             return q, sf, al
         self.gu_q, self.gu_sf, self.gu_alpha = cat(self.experts_gu)
+        if self.gu_q is not None and not MoEWeights.KEEP_EXPERT_LISTS:
+            self.experts_gu = []                    # (the per-expert tensors only serve the oracles)
         self.down_q, self.down_sf, self.down_alpha = cat(self.experts_down)
+        if self.down_q is not None and not MoEWeights.KEEP_EXPERT_LISTS:
+            self.experts_down = []
         if self.gu_q is None or self.down_q is None:
             self.gu_q = self.down_q = None          # a scale range too wide to re-express: the oracle path serves it
         # kernel views of the shared expert (the stored MXFP4 tensors stay the oracle's)

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "dgpp_attn_decode_sink": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
     "dgpp_attn_decode_tc": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_prefill_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "dgpp_attn_prefill_tc256": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_decode_advance": [P, P, P, P, P, I, I, P],
     "dgpp_act_quant_nvfp4": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
     "dgpp_attn_combine_quant": [P, P, I, I, I, P, P, P, P, I, I, I, I, I, P],

@@ -383,7 +383,7 @@ def check_status() -> None:
 def attn_decode_tc(q, q_stride: int, cache, block_table, row_req, positions, hq: int, hkv: int, d: int,
                    scale: float, splits: int = 1, scratch=None, out=None, window: int = 0,
                    partials_only: bool = False):
-    """Tensor-core (tcgen05, FP8 operands) decode attention over an FP8 paged cache; head_dim 128.
+    """Tensor-core (tcgen05, FP8 operands) decode attention over an FP8 paged cache; head_dim 128 or 256.
     partials_only (splits > 1): stop after the split-KV pass and leave the (max, sum) pairs and unnormalised
     accumulators in `scratch` for attn_combine_quant, which folds them while it quantises; returns None."""
     assert cache.fp8, "the tensor-core decode path reads e4m3 caches"
@@ -409,12 +409,12 @@ def attn_decode_tc(q, q_stride: int, cache, block_table, row_req, positions, hq:
 def attn_prefill_tc(q, q_stride: int, cache, block_table_row, pos0: int, hq: int, hkv: int, d: int, scale: float,
                     out=None, window: int = 0, rows: Optional[int] = None):
     """Causal tensor-core flash attention of a prefill chunk (rows at positions pos0.. of one request) against the
-    FP8 paged cache that already holds those positions.  head_dim 128."""
+    FP8 paged cache that already holds those positions.  head_dim 128 or 256 (a kernel each)."""
     assert cache.fp8
     T = rows if rows is not None else q.shape[0]
     if out is None:
         out = torch.empty(T, hq * d, dtype=torch.bfloat16, device=q.device)
-    call("dgpp_attn_prefill_tc", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale),
+    call("dgpp_attn_prefill_tc256" if d == 256 else "dgpp_attn_prefill_tc", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale),
          ptr(block_table_row), ptr(out), T, pos0, hq, hkv, d, cache.page, block_table_row.numel(), cache.k.shape[0],
          float(scale), window, stream_ptr())
     return out

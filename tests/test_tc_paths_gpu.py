@@ -84,11 +84,10 @@ def test_fused_producers_match_reference(dev):
     assert ((xa.dequant() - ar.float()).abs().max() / ar.float().abs().max()).item() < 1e-2
 
 
-def _filled_cache(dev, hq, hkv, ctx, page, slot):
+def _filled_cache(dev, hq, hkv, ctx, page, slot, d=128):
     from dgpp_b200.engine.kv_cache import PagedKV
     from dgpp_b200.ops import core as ops, reference as ref
 
-    d = 128
     kv = PagedKV(1, hkv, d, max(64, 4 * (ctx // page + 2)), 4, ctx // page + 2, page, True, dev)
     inv_freq, _ = ref.rope_inv_freq(d, 1e4, dev)
     qkv = torch.randn(ctx, (hq + 2 * hkv) * d, device=dev).to(BF)
@@ -99,11 +98,11 @@ def _filled_cache(dev, hq, hkv, ctx, page, slot):
     return kv, qkv, pos, req
 
 
-def _torch_attention(kv, qkv, slot, rows_pos, hq, hkv, scale):
+def _torch_attention(kv, qkv, slot, rows_pos, hq, hkv, scale, d=128):
     """fp32 attention over the dequantised cache contents for the query rows at positions rows_pos."""
     from dgpp_b200.ops import reference as ref
 
-    cache, d = kv.layers[0], 128
+    cache = kv.layers[0]
     ctx = int(rows_pos.max().item()) + 1
     blocks = kv.block_table[slot].long()
     page = cache.page
@@ -184,4 +183,47 @@ def test_attn_prefill_tc(dev, hq, hkv, ctx, page, pos0, T):
     # and every row against the CUDA-core decode kernel
     base = ops.attn_decode(q, q.stride(0), kv.layers[0], kv.block_table, req[pos0:pos0 + T].contiguous(),
                            pos[pos0:pos0 + T].contiguous(), hq, hkv, 128, scale, splits=1)
+    assert (out.float() - base.float()).abs().max().item() < 0.03
+
+
+@pytest.mark.parametrize("hq,hkv,ctx,page,splits", [(16, 2, 333, 64, 1), (16, 2, 1500, 64, 5), (8, 2, 700, 16, 2),
+                                                    (4, 4, 130, 128, 3), (16, 2, 300, 64, 16)])
+def test_attn_decode_tc_head_dim_256(dev, hq, hkv, ctx, page, splits):
+    """head_dim 256: two 128-byte halves per K / V / q tile; splits past the end of a short context write empty partials."""
+    from dgpp_b200.ops import core as ops
+
+    torch.manual_seed(14)
+    d = 256
+    kv, qkv, pos, req = _filled_cache(dev, hq, hkv, ctx, page, slot=2, d=d)
+    scale = 1.0 / math.sqrt(d)
+    sel = torch.tensor([ctx - 1, ctx // 2, 5], device=dev)
+    q, p_, r_ = qkv[sel].contiguous(), pos[sel].contiguous(), req[sel].contiguous()
+    out = ops.attn_decode_tc(q, q.stride(0), kv.layers[0], kv.block_table, r_, p_, hq, hkv, d, scale, splits=splits)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = _torch_attention(kv, qkv, 2, sel, hq, hkv, scale, d=d)
+    assert (out.float() - want).abs().max().item() < 0.02
+
+
+@pytest.mark.parametrize("hq,hkv,ctx,page,pos0,T", [(16, 2, 256, 64, 0, 256), (16, 2, 700, 64, 0, 700),
+                                                   (8, 2, 1000, 64, 300, 513), (8, 2, 400, 16, 77, 200),
+                                                   (4, 4, 130, 128, 1, 129)])
+def test_attn_prefill_tc_head_dim_256(dev, hq, hkv, ctx, page, pos0, T):
+    """head_dim 256 prefill kernel (two softmax sets, one per output half) against fp32 attention and the CUDA-core rows."""
+    from dgpp_b200.ops import core as ops
+
+    torch.manual_seed(15)
+    d = 256
+    kv, qkv, pos, req = _filled_cache(dev, hq, hkv, ctx, page, slot=1, d=d)
+    scale = 1.0 / math.sqrt(d)
+    q = qkv[pos0:pos0 + T]
+    out = ops.attn_prefill_tc(q, q.stride(0), kv.layers[0], kv.block_table[1], pos0, hq, hkv, d, scale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    rows = sorted({0, 1, min(T - 1, 127), min(T - 1, 128), T // 2, T - 1})
+    want = _torch_attention(kv, qkv, 1, torch.tensor([pos0 + r for r in rows], device=dev), hq, hkv, scale, d=d)
+    got = out[torch.tensor(rows, device=dev)].float()
+    assert (got - want).abs().max().item() < 0.02
+    base = ops.attn_decode(q, q.stride(0), kv.layers[0], kv.block_table, req[pos0:pos0 + T].contiguous(),
+                           pos[pos0:pos0 + T].contiguous(), hq, hkv, d, scale, splits=1)
     assert (out.float() - base.float()).abs().max().item() < 0.03
