@@ -205,6 +205,17 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
   d |= static_cast<uint64_t>(2) << 61;                   // layout type: SWIZZLE_128B
   return d;
 }
+// The same swizzle for an MN-major operand whose M/N extent spans several 128-byte atoms (16-bit types: 64 elements
+// per atom): `lbo` = byte distance between atoms adjacent in M/N; 8 K-rows of 128 bytes form one 1024-byte group.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t saddr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
 // Descriptor for unswizzled K-major data: core matrices of 8 rows x 16 bytes stored as 128
 // contiguous bytes; lbo = byte distance between core matrices adjacent in K, sbo = in M/N.
 __device__ __forceinline__ uint64_t umma_desc_nosw(uint32_t saddr, uint32_t lbo, uint32_t sbo) {

@@ -1,7 +1,8 @@
 // Mixture-of-experts control kernels: router, active-expert list, ordered combine.
 //
-//   moe_router_kernel   one CTA per token: fp32 logits = hidden . gate^T (bf16 operands, fp32 accumulation, warp per
-//                       expert, fixed shuffle tree), scores = sigmoid (or softmax) of the logits, selection on
+//   moe_router_logits_kernel / moe_router_select_kernel
+//                       fp32 logits = hidden . gate^T (bf16 operands, fp32 accumulation, warp per expert and 8 tokens,
+//                       fixed shuffle tree); then one CTA per token: scores = sigmoid (or softmax) of the logits, selection on
 //                       score + correction bias (group-limited when n_group > 1: a group's rank is the sum of its
 //                       two best selection values, the best topk_group groups stay), weights from the UNCORRECTED
 //                       scores, optional normalisation by (sum + 1e-20), times the routed scaling factor.  Ties go
@@ -37,41 +38,86 @@ struct RouterArgs {
   float scaling;
 };
 
-__global__ void __launch_bounds__(kRouterThreads) moe_router_kernel(RouterArgs a) {
+constexpr int kRouterRowsPerCta = 8;
+
+// Router logits: grid (ceil(E / 8), ceil(T / 8)), 8 warps.  A warp owns one expert and up to 8 token rows: it walks the
+// expert's gate row once (lane-strided 16-byte loads) and keeps one fp32 accumulator per row, so the gate matrix is
+// read T / 8 times instead of T times and the work of a decode step spreads over E / 8 CTAs instead of T.  The
+// accumulation order of every (token, expert) dot product (lane-strided fmaf chain, xor-shuffle tree) does not depend on
+// the grid, so logits are identical for every batch composition.
+__global__ void __launch_bounds__(kRouterThreads) moe_router_logits_kernel(RouterArgs a) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int e = blockIdx.x * (kRouterThreads / 32) + wid;
+  const int t0 = blockIdx.y * kRouterRowsPerCta;
+  if (e >= a.E) return;
+  const int nt = min(kRouterRowsPerCta, a.T - t0);
+  const bf16* gr = a.gate + static_cast<size_t>(e) * a.H;
+  float acc[kRouterRowsPerCta];
+#pragma unroll
+  for (int r = 0; r < kRouterRowsPerCta; ++r) acc[r] = 0.f;
+  for (int i = lane * 8; i < a.H; i += 32 * 8) {
+    Pack16 gv;
+    gv.u = *reinterpret_cast<const uint4*>(gr + i);
+    float g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] = bf16_to_f32(gv.h[j]);
+#pragma unroll
+    for (int r = 0; r < kRouterRowsPerCta; ++r) {
+      if (r < nt) {
+        Pack16 xv;
+        xv.u = *reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(t0 + r) * a.x_stride + i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[r] = fmaf(bf16_to_f32(xv.h[j]), g[j], acc[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kRouterRowsPerCta; ++r) {
+    float v = acc[r];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0 && r < nt) a.logits_out[static_cast<size_t>(t0 + r) * a.E + e] = v;
+  }
+}
+
+// Selection: one CTA per token over its row of logits.
+__global__ void __launch_bounds__(kRouterThreads) moe_router_select_kernel(RouterArgs a) {
   __shared__ float score[kMoeMaxExperts];   // uncorrected
   __shared__ float sel[kMoeMaxExperts];     // selection value
   __shared__ float grp[64];
+  __shared__ float wred[kRouterThreads / 32];
   __shared__ int pick_id[kMoeMaxTopK];
   pdl_wait();
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  const bf16* xr = a.x + static_cast<size_t>(t) * a.x_stride;
-  for (int e = wid; e < a.E; e += kRouterThreads / 32) {
-    const bf16* gr = a.gate + static_cast<size_t>(e) * a.H;
-    float acc = 0.f;
-    for (int i = lane * 8; i < a.H; i += 32 * 8) {
-      Pack16 xv, gv;
-      xv.u = *reinterpret_cast<const uint4*>(xr + i);
-      gv.u = *reinterpret_cast<const uint4*>(gr + i);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc = fmaf(bf16_to_f32(xv.h[j]), bf16_to_f32(gv.h[j]), acc);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
-      score[e] = acc;
-      if (a.logits_out) a.logits_out[static_cast<size_t>(t) * a.E + e] = acc;
-    }
-  }
+  for (int e = tid; e < a.E; e += kRouterThreads) score[e] = a.logits_out[static_cast<size_t>(t) * a.E + e];
   __syncthreads();
   if (a.softmax) {
-    // softmax over all experts: max and sum by thread 0 in index order (E <= 512)
+    // softmax over all experts: max, then the sum of exp, each by a fixed tree (thread-strided partials, xor-shuffle
+    // within the warp, the 8 warp results in warp order), so the value does not depend on timing
     __shared__ float mx_s, sum_s;
+    float m = -INFINITY;
+    for (int e = tid; e < a.E; e += kRouterThreads) m = fmaxf(m, score[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) wred[wid] = m;
+    __syncthreads();
     if (tid == 0) {
-      float m = -INFINITY;
-      for (int e = 0; e < a.E; ++e) m = fmaxf(m, score[e]);
-      float s = 0.f;
-      for (int e = 0; e < a.E; ++e) s += expf(score[e] - m);
-      mx_s = m; sum_s = s;
+      float mm = wred[0];
+      for (int w = 1; w < kRouterThreads / 32; ++w) mm = fmaxf(mm, wred[w]);
+      mx_s = mm;
+    }
+    __syncthreads();
+    float sp = 0.f;
+    for (int e = tid; e < a.E; e += kRouterThreads) sp += expf(score[e] - mx_s);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sp += __shfl_xor_sync(0xffffffffu, sp, o);
+    if (lane == 0) wred[wid] = sp;
+    __syncthreads();
+    if (tid == 0) {
+      float ss = 0.f;
+      for (int w = 0; w < kRouterThreads / 32; ++w) ss += wred[w];
+      sum_s = ss;
     }
     __syncthreads();
     for (int e = tid; e < a.E; e += kRouterThreads) score[e] = expf(score[e] - mx_s) / sum_s;
@@ -163,15 +209,27 @@ __global__ void __launch_bounds__(512) moe_active_kernel(const int32_t* ids, int
     if (e >= 0 && e < E) flag[e] = 1;
   }
   __syncthreads();
-  if (tid == 0) {
-    int n = 0;
-    for (int e = 0; e < E; ++e) {
-      // expert parallelism: only experts [e_begin, e_end) live here; the list holds LOCAL indices (e - e_begin)
-      if (flag[e] && e >= e_begin && e < e_end && n < slots) { list[n] = e - e_begin; slot_of[e] = n; ++n; } else { slot_of[e] = -1; }
-    }
-    *n_active = n;
-    for (int s = n; s < slots; ++s) list[s] = -1;
+  // expert parallelism: only experts [e_begin, e_end) live here; the list holds LOCAL indices (e - e_begin).
+  // Ascending positions by a block-wide exclusive scan of the flags (thread e <-> expert e; E <= 512 = blockDim).
+  __shared__ int warp_cnt[16];
+  const int lane = tid & 31, wid = tid >> 5;
+  const bool on = tid < E && flag[tid] && tid >= e_begin && tid < e_end;
+  const unsigned bal = __ballot_sync(0xffffffffu, on);
+  if (lane == 0) warp_cnt[wid] = __popc(bal);
+  __syncthreads();
+  int before = __popc(bal & ((1u << lane) - 1u)), total = 0;
+  for (int w = 0; w < 16; ++w) {
+    if (w < wid) before += warp_cnt[w];
+    total += warp_cnt[w];
   }
+  if (tid < E) {
+    const bool listed = on && before < slots;
+    slot_of[tid] = listed ? before : -1;
+    if (listed) list[before] = tid - e_begin;
+  }
+  const int n = min(total, slots);
+  if (tid == 0) *n_active = n;
+  for (int sidx = n + tid; sidx < slots; sidx += blockDim.x) list[sidx] = -1;
 }
 
 // y: [slots, rows_per_slot, H] bf16; shared (optional): [T, H] bf16; out: [T, H] bf16.
@@ -277,7 +335,11 @@ DGPP_API int dgpp_moe_route(const void* x, int64_t x_stride, const void* gate, c
   a.logits_out = static_cast<float*>(logits_out);
   a.T = T; a.H = H; a.E = E; a.k = k; a.n_group = n_group; a.topk_group = topk_group;
   a.softmax = softmax; a.norm_topk = norm_topk; a.scaling = scaling;
-  moe_router_kernel<<<T, kRouterThreads, 0, st>>>(a);
+  DGPP_REQUIRE(logits_out != nullptr, "moe_route: a [T, E] fp32 logits buffer is required");
+  dim3 grid(dgpp_ceil_div(E, kRouterThreads / 32), dgpp_ceil_div(T, kRouterRowsPerCta));
+  moe_router_logits_kernel<<<grid, kRouterThreads, 0, st>>>(a);
+  DGPP_CUDA_OK(cudaGetLastError());
+  moe_router_select_kernel<<<T, kRouterThreads, 0, st>>>(a);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }

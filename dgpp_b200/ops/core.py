@@ -482,6 +482,8 @@ def moe_route(x, gate, bias, k: int, n_group: int = 1, topk_group: int = 1, soft
     if ids is None:
         ids = torch.empty(T, k, dtype=torch.int32, device=x.device)
         weights = torch.empty(T, k, dtype=torch.float32, device=x.device)
+    if logits_out is None:
+        logits_out = torch.empty(T, E, dtype=torch.float32, device=x.device)
     call("dgpp_moe_route", ptr(x), x.stride(0), ptr(gate), ptr(bias), ptr(ids), ptr(weights), ptr(logits_out), T, H, E, k,
          n_group, topk_group, int(softmax), int(norm_topk), float(scaling), stream_ptr())
     return ids, weights
@@ -634,15 +636,17 @@ def gated_rmsnorm(o, z, w, out, heads: int, d: int, eps: float = 1e-6):
 
 # ---------------------------------------------------------------------------------------------- latent attention
 _lib.declare("dgpp_mla_decode", [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P])
+_lib.declare("dgpp_mla_decode_tc", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
 _lib.declare("dgpp_dsa_index", [P, P, P, P, P, P, P, I, I, I, I, I, I, P])
 _lib.declare("dgpp_topk_select", [P, L, P, P, I, I, P])
 
 
 def mla_decode(q, cache, block_table, row_req, positions, scale: float, dc: int, dr: int, sel=None, splits: int = 1,
-               out=None):
+               out=None, tensor_cores: Optional[bool] = None):
     """Absorbed multi-head latent attention.  q: [rows, heads, dc + dr] bf16; cache: [blocks, page, dc + dr] bf16;
     sel: optional [rows, n_sel] int32 selected token positions (ascending, -1 padded) for sparse attention.
-    Returns the latent outputs [rows, heads, dc] bf16."""
+    Returns the latent outputs [rows, heads, dc] bf16.  The dense form at the 512 + 64 geometry runs on the tensor
+    cores (tensor_cores=False keeps the CUDA-core kernel, which is also the sparse path)."""
     rows, heads, _ = q.shape
     dev = q.device
     if out is None:
@@ -651,6 +655,14 @@ def mla_decode(q, cache, block_table, row_req, positions, scale: float, dc: int,
     if splits > 1:
         ml = torch.empty(rows * heads * splits * 2, dtype=torch.float32, device=dev)
         acc = torch.empty(rows * heads * splits * dc, dtype=torch.float32, device=dev)
+    if tensor_cores is None:
+        tensor_cores = sel is None and dc == 512 and dr == 64 and cache.shape[1] in (16, 32, 64, 128)
+    if tensor_cores:
+        assert sel is None, "the tensor-core latent attention kernel is dense"
+        call("dgpp_mla_decode_tc", ptr(q), ptr(cache), ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc),
+             ptr(out), rows, heads, dc, dr, cache.shape[1], block_table.shape[1], cache.shape[0], splits, float(scale),
+             stream_ptr())
+        return out
     call("dgpp_mla_decode", ptr(q), ptr(cache), ptr(block_table), ptr(row_req), ptr(positions), ptr(sel),
          0 if sel is None else sel.shape[1], ptr(ml), ptr(acc), ptr(out), rows, heads, dc, dr, cache.shape[1],
          block_table.shape[1], splits, float(scale), stream_ptr())

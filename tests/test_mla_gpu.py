@@ -53,6 +53,30 @@ def test_mla_decode_dense_and_sparse(dev, heads, dc, dr, page, splits):
         assert (out[r].float() - want).abs().max().item() < 1e-2
 
 
+@pytest.mark.parametrize("heads,page,splits,ctxs", [(32, 64, 1, [700, 33, 257, 128]), (32, 64, 4, [2048, 129, 1, 640]),
+                                                    (20, 128, 3, [700, 33, 257, 500]), (40, 16, 2, [300, 64, 65, 1000])])
+def test_mla_decode_tensor_cores(dev, heads, page, splits, ctxs):
+    """tcgen05 latent attention (one tile feeds both products, MN-major second operand) against the fp32 oracle and the
+    CUDA-core kernel; head groups of 32, partial groups, splits that fall beyond short contexts."""
+    from dgpp_b200.models.mla import gather_rows, mla_reference
+    from dgpp_b200.ops import core as ops
+
+    dc, dr = 512, 64
+    cache, table = _pool(dev, len(ctxs), ctxs, page, dc + dr, seed=3)
+    q = (torch.randn(len(ctxs), heads, dc + dr, device=dev) * 0.3).to(BF)
+    row_req = torch.arange(len(ctxs), dtype=torch.int32, device=dev)
+    pos = torch.tensor([c - 1 for c in ctxs], dtype=torch.int32, device=dev)
+    scale = 1.0 / math.sqrt(128 + dr)
+    out = ops.mla_decode(q, cache, table, row_req, pos, scale, dc, dr, splits=splits, tensor_cores=True)
+    base = ops.mla_decode(q, cache, table, row_req, pos, scale, dc, dr, splits=splits, tensor_cores=False)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for r, n in enumerate(ctxs):
+        want = mla_reference(q[r], gather_rows(cache, table[r], n), scale, dc)
+        assert (out[r].float() - want).abs().max().item() < 1.5e-2, (r, n)
+    assert (out.float() - base.float()).abs().max().item() < 2e-2
+
+
 def test_indexer_scores_and_topk(dev):
     from dgpp_b200.models.mla import gather_rows, index_scores_reference, topk_reference
     from dgpp_b200.ops import core as ops
