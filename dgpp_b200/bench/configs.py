@@ -5,8 +5,8 @@
     python bench.py --config 3 ...                                       config 2 + lightning indexer, sparse MLA
 
 Each run builds the model at the named shape, prefills C sequences, times `K` decode steps at C = 1 and C = 8 (CUDA
-events around the whole step loop, host work of the runner included: these runners launch kernel by kernel, no captured
-graph) and cold prefills at the named lengths.  One JSON line per run.  `--layers` below the named depth is a debugging
+events around the whole step loop, host work of the runner included; a decode pass is one captured CUDA graph per batch
+width) and cold prefills at the named lengths.  One JSON line per run.  `--layers` below the named depth is a debugging
 aid; its numbers are marked `"valid": false`.
 (reference counterparts: docs/benchmarks.md method section; the per-family forward checks under apps/.)
 """
@@ -48,10 +48,13 @@ def _time_prefill(runner, vocab: int, slot: int, n: int, gen, chunk: int) -> flo
     return e0.elapsed_time(e1) / 1000.0
 
 
-def _lean_experts() -> None:
-    """The grouped kernels read the stacked expert tensors; the per-expert copies (oracle inputs) are not kept."""
-    from ..models.moe import MoEWeights
+def _lean_experts(args) -> int:
+    """The grouped kernels read the stacked expert tensors; the per-expert copies (oracle inputs) are not kept.
+    Returns the activation terms used by the expert GEMMs at prefill sizes (--moe-prefill-terms, default 1 = W4A4)."""
+    from ..models.moe import MoEBlock, MoEWeights
     MoEWeights.KEEP_EXPERT_LISTS = False
+    MoEBlock.PREFILL_TERMS = int(getattr(args, "moe_prefill_terms", 1) or 1)
+    return MoEBlock.PREFILL_TERMS
 
 
 def run_config4(args, dev) -> dict:
@@ -63,7 +66,7 @@ def run_config4(args, dev) -> dict:
                        gdn_v_heads=16, gdn_dk=128, gdn_dv=128, vocab=151936,
                        moe=MoEConfig(hidden=2048, experts=512, top_k=10, moe_ffn=512, shared_ffn=512, router="softmax"))
     t0 = time.time()
-    _lean_experts()
+    terms = _lean_experts(args)
     model = HybridModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4")
     torch.cuda.synchronize()
     init_s = time.time() - t0
@@ -73,7 +76,8 @@ def run_config4(args, dev) -> dict:
     g = torch.Generator().manual_seed(4)
     out = {"config": 4, "model": "hybrid GDN(16v/16qk x128, chunked scan) 3:1 gated GQA(16q/2kv x256) + MoE 512e top-10 + shared, "
                                  f"hidden 2048, {layers} layers, NVFP4 weights, FP8 KV", "layers": layers,
-           "valid": layers == 48, "init_s": round(init_s, 1), "mtp": "off (the MTP head is not drafted by this runner)"}
+           "valid": layers == 48, "init_s": round(init_s, 1), "mtp": "off (the MTP head is not drafted by this runner)",
+           "moe_prefill_act_terms": terms}
     out["prefill_s_2048"] = _time_prefill(runner, cfg.vocab, 0, 2048, g, chunk)
     # the trace's shape: a 16K shared prefix, then a unique suffix.  A prefix hit restores the prefix's KV blocks and
     # recurrent-state snapshot, so its prefill cost is the suffix run on top of the resident prefix.
@@ -107,26 +111,27 @@ def run_config2(args, dev, indexer: bool = False) -> dict:
                                      topk_group=4, router="sigmoid", routed_scaling=2.5),
                        index_heads=64 if indexer else 0, index_dim=128, index_topk=2048)
     t0 = time.time()
-    _lean_experts()
+    terms = _lean_experts(args)
     model = MlaMoeModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4")
     torch.cuda.synchronize()
     init_s = time.time() - t0
     C = 8
     max_len = args.prompt_len + 512
-    runner = MlaMoeRunner(model, max_rows=256, slots=C, max_seq_len=max_len, device=dev)
+    chunk = 256 if indexer else 2048     # the indexer keeps a [chunk, context] score matrix
+    runner = MlaMoeRunner(model, max_rows=chunk, slots=C, max_seq_len=max_len, device=dev)
     g = torch.Generator().manual_seed(2)
     out = {"config": 3 if indexer else 2,
            "model": "MLA (q_lora 1024, kv_lora 512, nope 128 + rope 64, v 128, 32 heads) + MoE 256e top-8 (8 groups, top-4) + shared, "
                     f"hidden 4096, {layers} layers ({cfg.dense_layers} dense FFN 12288), NVFP4 weights, bf16 latent cache"
                     + (", lightning indexer 64 x 128, top-2048 sparse attention" if indexer else ""),
-           "layers": layers, "valid": layers == 48, "init_s": round(init_s, 1),
+           "layers": layers, "valid": layers == 48, "init_s": round(init_s, 1), "moe_prefill_act_terms": terms,
            "note": "weights NVFP4 throughout (the family's MXFP4 experts and FP8 128x128 attention weights map onto the same "
                    "block-scaled / converter kernels); attention through the absorbed-latent decode kernel for prefill rows too"}
     L = args.prompt_len
-    out[f"prefill_s_{L}"] = _time_prefill(runner, cfg.vocab, 0, L, g, 256)
+    out[f"prefill_s_{L}"] = _time_prefill(runner, cfg.vocab, 0, L, g, chunk)
     for s in range(1, C):
         runner.reset(s)
-        runner.prefill(s, torch.randint(0, cfg.vocab, (L,), generator=g).tolist(), chunk=256)
+        runner.prefill(s, torch.randint(0, cfg.vocab, (L,), generator=g).tolist(), chunk=chunk)
     ms1 = _time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g)
     ms8 = _time_decode(runner, cfg.vocab, list(range(C)), args.steps, args.warmup, g)
     out.update(c1_decode_tok_s=1000.0 / ms1, c1_ms_per_step=ms1, c8_decode_tok_s=1000.0 * C / ms8, c8_ms_per_step=ms8,

@@ -201,7 +201,9 @@ class MlaMoeRunner:
         cache[blk, (positions % self.page).long()] = rows
 
     @torch.no_grad()
-    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor) -> torch.Tensor:
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor,
+                all_logits: bool = True) -> torch.Tensor:
+        """int32 [rows] device tensors -> fp32 logits [rows, V] (all_logits=False: of the last row only, [1, V])."""
         m, c = self.m, self.c
         rows = tokens.shape[0]
         x = torch.empty(rows, c.hidden, dtype=BF, device=self.dev)
@@ -213,13 +215,10 @@ class MlaMoeRunner:
             cq = ops.rmsnorm(ops.linear(xn, L.q_a), L.q_a_norm, c.eps)
             q = ops.linear(cq, L.q_b).view(rows, c.heads, c.nope + c.rope)
             kv = ops.linear(xn, L.kv_a)
-            ckv = ops.rmsnorm(kv[:, :c.kv_lora].contiguous(), L.kv_a_norm, c.eps)
-            k_r = _rope(kv[:, c.kv_lora:].float(), positions, m.inv_freq).to(BF)
-            self._append(self.latent[i], torch.cat([ckv, k_r], -1), row_req, positions)
-            # absorbed query: [heads, nope] x [heads, nope, dc] -> [heads, dc], rotated rope part appended
-            q_abs = torch.einsum("thn,hnd->thd", q[..., :c.nope].float(), L.w_uk.float())
-            q_r = _rope(q[..., c.nope:].float(), positions, m.inv_freq).to(BF).float()
-            q_full = torch.cat([q_abs, q_r], -1).to(BF).contiguous()
+            # latent norm + rotary key -> cache slot; key up-projection folded into the query, rotary part appended
+            ops.mla_kv_prep(kv, L.kv_a_norm, c.eps, m.inv_freq, positions, row_req, self.block_table, self.latent[i],
+                            c.kv_lora, c.rope)
+            q_full = ops.mla_q_absorb(q, L.w_uk, m.inv_freq, positions, c.kv_lora, c.rope)
             sel = None
             if L.idx_q is not None:
                 self._append(self.kidx[i], ops.linear(xn, L.idx_k), row_req, positions)
@@ -230,7 +229,7 @@ class MlaMoeRunner:
                 sel = ops.topk_select(sc, positions, c.index_topk)
             lat = ops.mla_decode(q_full, self.latent[i], self.block_table, row_req, positions, self.scale, c.kv_lora,
                                  c.rope, sel=sel, splits=4 if rows <= 16 else 1)
-            a = torch.einsum("thd,hvd->thv", lat.float(), L.w_uv.float()).to(BF).reshape(rows, c.heads * c.v_dim)
+            a = ops.mla_v_up(lat, L.w_uv)
             ops.linear(a, L.o, out=delta)
             ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
             have = True
@@ -245,7 +244,8 @@ class MlaMoeRunner:
             else:
                 ops.linear(ops.swiglu(ops.linear(xn, L.gate_up)), L.down, out=delta)
         ops.rmsnorm(x, m.final_norm, c.eps, delta=delta, out=xn)
-        return ops.gemm_tc(xn, m.head, out32=torch.empty(rows, c.vocab, dtype=torch.float32, device=self.dev))
+        sel_rows = xn if all_logits else xn[rows - 1:rows]
+        return ops.gemm_tc(sel_rows, m.head, out32=torch.empty(sel_rows.shape[0], c.vocab, dtype=torch.float32, device=self.dev))
 
     @torch.no_grad()
     def prefill(self, slot: int, tokens: List[int], chunk: int = 64) -> torch.Tensor:
@@ -257,7 +257,7 @@ class MlaMoeRunner:
             t = torch.tensor(part, dtype=torch.int32, device=self.dev)
             pos = torch.arange(start + o, start + o + len(part), dtype=torch.int32, device=self.dev)
             req = torch.full((len(part),), slot, dtype=torch.int32, device=self.dev)
-            out = self.forward(t, pos, req)
+            out = self.forward(t, pos, req, all_logits=False)
         self.lengths[slot] = start + len(tokens)
         return out
 

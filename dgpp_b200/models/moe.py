@@ -177,10 +177,16 @@ def moe_reference(x: torch.Tensor, w: MoEWeights, ids=None, wts=None) -> torch.T
 class MoEBlock:
     """Device buffers + launch sequence of one MoE block for up to `max_rows` decode rows."""
 
-    def __init__(self, w: MoEWeights, max_rows: int, device, act_terms: int = 3):
+    # residual NVFP4 terms of the activations at prefill sizes (tiles of 64 rows).  3 = the decode path's arithmetic
+    # (near-bf16 activations); 1 = plain W4A4 (4-bit activations, a third of the tensor-core and quantiser work).
+    # Class-wide so one deployment key sets it for every block.
+    PREFILL_TERMS = 3
+
+    def __init__(self, w: MoEWeights, max_rows: int, device, act_terms: int = 3, prefill_terms: Optional[int] = None):
         c = w.cfg
         assert w.gu_q is not None, "call MoEWeights.stack() on the device first"
         self.w, self.c, self.dev, self.terms = w, c, device, act_terms
+        self.prefill_terms = prefill_terms or self.PREFILL_TERMS
         self.bn = 16 if max_rows <= 16 else (32 if max_rows <= 32 else 64)
         assert max_rows <= self.bn and act_terms * self.bn <= 256
         self.max_rows = max_rows
@@ -243,7 +249,7 @@ class MoEBlock:
         (reference counterparts: src/kernels/glm_moe.cu:1382 segment count, :1553 tile list, :1121 grouped MMA.)"""
         c, w = self.c, self.w
         T = xn.shape[0]
-        bn, R = 64, self.terms
+        bn, R = 64, self.prefill_terms
         max_tiles = (T * c.top_k + bn - 1) // bn + self.local_experts
         ws = _prefill_workspace(xn.device, max_tiles, bn, c.hidden, c.moe_ffn, R)
         ids, wts = ops.moe_route(xn, w.gate, w.bias, c.top_k, c.n_group, c.topk_group, c.router == "softmax",

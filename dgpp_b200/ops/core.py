@@ -210,7 +210,11 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
     m = {"plain": 0, "swiglu": 1, "rmsnorm": 2}[mode]
     if m == 2 and (delta is not None or fold_comm) and resid_out is None:
         resid_out = x
-    cl = next((c for c in (8, 4, 2, 1) if k % c == 0 and (k // c) % 16 == 0 and (k // c) * 2 <= 48 * 1024), 0)
+    # a cluster per row spreads a decode batch over the SMs; bulk rows (prefill tiles) take one CTA per row instead.
+    # Modes 0 / 1 reduce with max only, so their result does not depend on the split; the norm's sum of squares does,
+    # and keeps the decode split at every row count.
+    order = (1, 2, 4, 8) if (rows > 64 and m != 2) else (8, 4, 2, 1)
+    cl = next((c for c in order if k % c == 0 and (k // c) % 16 == 0 and (k // c) * 2 <= 48 * 1024), 0)
     if cl:
         call("dgpp_act_quant_nvfp4_cluster", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out),
              ptr(x_out), ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, cl,
@@ -666,6 +670,39 @@ def mla_decode(q, cache, block_table, row_req, positions, scale: float, dc: int,
     call("dgpp_mla_decode", ptr(q), ptr(cache), ptr(block_table), ptr(row_req), ptr(positions), ptr(sel),
          0 if sel is None else sel.shape[1], ptr(ml), ptr(acc), ptr(out), rows, heads, dc, dr, cache.shape[1],
          block_table.shape[1], splits, float(scale), stream_ptr())
+    return out
+
+
+_lib.declare("dgpp_mla_kv_prep", [P, L, P, F, P, P, P, P, I, I, P, I, I, I, P])
+_lib.declare("dgpp_mla_q_absorb", [P, P, P, P, P, I, I, I, I, I, P])
+_lib.declare("dgpp_mla_v_up", [P, P, P, I, I, I, I, P])
+
+
+def mla_kv_prep(kv, norm_w, eps: float, inv_freq, positions, row_req, block_table, cache, dc: int, dr: int) -> None:
+    """kv [rows, dc + dr] bf16 (projection output): RMSNorm of the latent part, RoPE of the rotary key, both written to
+    the rows' slots of the paged latent cache [blocks, page, dc + dr]."""
+    call("dgpp_mla_kv_prep", ptr(kv), kv.stride(0), ptr(norm_w), float(eps), ptr(inv_freq), ptr(positions), ptr(row_req),
+         ptr(block_table), block_table.shape[1], cache.shape[1], ptr(cache), kv.shape[0], dc, dr, stream_ptr())
+
+
+def mla_q_absorb(q, w_uk, inv_freq, positions, dc: int, dr: int, out=None):
+    """q [rows, heads, nope + dr] bf16, w_uk [heads, nope, dc] bf16 -> [rows, heads, dc + dr]: absorbed latent query
+    with the rotated rotary part appended."""
+    rows, heads, dq = q.shape
+    if out is None:
+        out = torch.empty(rows, heads, dc + dr, dtype=torch.bfloat16, device=q.device)
+    call("dgpp_mla_q_absorb", ptr(q), ptr(w_uk), ptr(inv_freq), ptr(positions), ptr(out), rows, heads, dq - dr, dc, dr,
+         stream_ptr())
+    return out
+
+
+def mla_v_up(lat, w_uv, out=None):
+    """lat [rows, heads, dc] bf16, w_uv [heads, v, dc] bf16 -> [rows, heads * v] bf16."""
+    rows, heads, dc = lat.shape
+    v = w_uv.shape[1]
+    if out is None:
+        out = torch.empty(rows, heads * v, dtype=torch.bfloat16, device=lat.device)
+    call("dgpp_mla_v_up", ptr(lat), ptr(w_uv), ptr(out), rows, heads, v, dc, stream_ptr())
     return out
 
 

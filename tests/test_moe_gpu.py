@@ -46,7 +46,7 @@ def test_moe_block_matches_reference(dev, rows, shared):
     torch.manual_seed(3)
     cfg = MoEConfig(hidden=1024, experts=32, top_k=4, moe_ffn=512, shared_ffn=shared, routed_scaling=1.5)
     w = MoEWeights.random_init(cfg, dev, seed=4, std=0.05)
-    blk = MoEBlock(w, max_rows=16, device=dev)
+    blk = MoEBlock(w, max_rows=16, device=dev, prefill_terms=3)
     x = torch.randn(rows, cfg.hidden, device=dev).to(BF)
     out = torch.empty(rows, cfg.hidden, dtype=BF, device=dev)
     blk.forward(x, out)
@@ -121,17 +121,19 @@ def test_segment_sort_is_a_stable_counting_sort_into_tiles(dev, T, k, E, e0, e1)
         assert rows[p] == (want_rows[p] if e0 <= x < e1 else -1)
 
 
-@pytest.mark.parametrize("rows,shared", [(100, 512), (700, 0)])
-def test_moe_prefill_path_matches_the_expert_loop(dev, rows, shared):
+@pytest.mark.parametrize("rows,shared,terms,tol", [(100, 512, 3, 2e-2), (700, 0, 3, 2e-2), (700, 512, 1, 1.2e-1),
+                                                   (300, 0, 2, 4e-2)])
+def test_moe_prefill_path_matches_the_expert_loop(dev, rows, shared, terms, tol):
     """Prefill-sized rows through the sort + tile list + grouped block-scaled GEMMs against the per-expert host loop
-    (exact W4A16 GEMMs) and, on a few rows, against the PyTorch oracle."""
+    (exact W4A16 GEMMs) and, on a few rows, against the PyTorch oracle.  terms = residual NVFP4 terms of the activations:
+    1 is plain W4A4 (4-bit activation error), 3 is the decode path's near-bf16 form."""
     from dgpp_b200.models.moe import MoEBlock, MoEConfig, MoEWeights, moe_reference
     from dgpp_b200.ops import core as ops
 
     torch.manual_seed(7)
     cfg = MoEConfig(hidden=1024, experts=32, top_k=4, moe_ffn=512, shared_ffn=shared, routed_scaling=1.5)
     w = MoEWeights.random_init(cfg, dev, seed=8, std=0.05)
-    blk = MoEBlock(w, max_rows=16, device=dev)
+    blk = MoEBlock(w, max_rows=16, device=dev, prefill_terms=terms)
     x = torch.randn(rows, cfg.hidden, device=dev).to(BF)
     got = blk.forward_gathered(x)
     got2 = blk.forward_gathered(x)
@@ -140,7 +142,7 @@ def test_moe_prefill_path_matches_the_expert_loop(dev, rows, shared):
     ops.check_status()
     assert torch.equal(got, got2)                                         # deterministic, buffers reusable
     scale = loop.float().abs().max().item()
-    assert (got.float() - loop.float()).abs().max().item() <= 2e-2 * scale + 2e-3
+    assert (got.float() - loop.float()).abs().max().item() <= tol * scale + 2e-3
     ids, wts = ops.moe_route(x[:9], w.gate, w.bias, cfg.top_k, cfg.n_group, cfg.topk_group, False, True, 1.5)
     want = moe_reference(x[:9], w, ids=ids.long(), wts=wts)
-    assert (got[:9].float() - want.float()).abs().max().item() <= 2e-2 * want.float().abs().max().item() + 2e-3
+    assert (got[:9].float() - want.float()).abs().max().item() <= tol * want.float().abs().max().item() + 2e-3
