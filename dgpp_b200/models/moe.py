@@ -68,9 +68,10 @@ class MoEWeights:
 
     @staticmethod
     def random_init(cfg: MoEConfig, device, seed: int = 0, std: float = 0.02, fmt: str = "nvfp4", ep_rank: int = 0,
-                    ep_size: int = 1) -> "MoEWeights":
+                    ep_size: int = 1, shared_everywhere: bool = False) -> "MoEWeights":
         """Every rank draws all experts from the same seed and keeps its contiguous block, so the union over ranks
-        is the model a single rank would build."""
+        is the model a single rank would build.  The shared expert lives on rank 0 when every rank sees every token
+        (its output is summed once), on every rank when the tokens are sharded (shared_everywhere)."""
         from ..runtime import rt
 
         g = torch.Generator(device=device)
@@ -88,7 +89,7 @@ class MoEWeights:
         sgu = sdn = None
         if cfg.shared_ffn:
             a, b = rnd(2 * cfg.shared_ffn, cfg.hidden), rnd(cfg.hidden, cfg.shared_ffn)
-            if ep_rank == 0:
+            if ep_rank == 0 or shared_everywhere:
                 sgu, sdn = quantize_like_random(a, fmt, std), quantize_like_random(b, fmt, std)
         w = MoEWeights(cfg, gate, bias, gu, dn, sgu, sdn, e_begin=e0, e_end=e1)
         if fmt in ("nvfp4", "mxfp4") and torch.device(device).type == "cuda":
