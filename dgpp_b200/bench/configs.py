@@ -36,6 +36,24 @@ def _time_decode(runner, vocab: int, slots: List[int], steps: int, warmup: int, 
     return e0.elapsed_time(e1) / steps
 
 
+def _time_spec(runner, vocab: int, slots: List[int], steps: int, warmup: int, gen):
+    """(ms per speculative step, tokens emitted per step over all listed requests)."""
+    pend = torch.randint(0, vocab, (len(slots),), generator=gen).tolist()
+    for _ in range(max(warmup, 3)):
+        pend = [o[-1] for o in runner.spec_step(slots, pend)]
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    emitted = 0
+    e0.record()
+    for _ in range(steps):
+        outs = runner.spec_step(slots, pend)                      # reads the verdict back every step
+        pend = [o[-1] for o in outs]
+        emitted += sum(len(o) for o in outs)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps, emitted / steps
+
+
 def _time_prefill(runner, vocab: int, slot: int, n: int, gen, chunk: int) -> float:
     runner.reset(slot)
     toks = torch.randint(0, vocab, (n,), generator=gen).tolist()
@@ -62,8 +80,9 @@ def run_config4(args, dev) -> dict:
     from ..models.moe import MoEConfig
 
     layers = args.layers if args.layers < 48 else 48
+    depth = int(getattr(args, "mtp", 0) or 0)
     cfg = HybridConfig(layers=layers, hidden=2048, full_every=4, q_heads=16, kv_heads=2, head_dim=256, gdn_k_heads=16,
-                       gdn_v_heads=16, gdn_dk=128, gdn_dv=128, vocab=151936,
+                       gdn_v_heads=16, gdn_dk=128, gdn_dv=128, vocab=151936, mtp=depth > 0,
                        moe=MoEConfig(hidden=2048, experts=512, top_k=10, moe_ffn=512, shared_ffn=512, router="softmax"))
     t0 = time.time()
     terms = _lean_experts(args)
@@ -73,10 +92,13 @@ def run_config4(args, dev) -> dict:
     C, chunk = 8, 2048
     prefix, suffix = 16384, 512
     runner = HybridRunner(model, max_rows=chunk, slots=C, max_seq_len=prefix + suffix + 4096, device=dev)
+    if depth:
+        runner.enable_spec(depth)
     g = torch.Generator().manual_seed(4)
     out = {"config": 4, "model": "hybrid GDN(16v/16qk x128, chunked scan) 3:1 gated GQA(16q/2kv x256) + MoE 512e top-10 + shared, "
                                  f"hidden 2048, {layers} layers, NVFP4 weights, FP8 KV", "layers": layers,
-           "valid": layers == 48, "init_s": round(init_s, 1), "mtp": "off (the MTP head is not drafted by this runner)",
+           "valid": layers == 48, "init_s": round(init_s, 1),
+           "mtp": f"depth {depth}: MTP head drafts, 1 + {depth} rows verified per step, device commit / rollback" if depth else "off",
            "moe_prefill_act_terms": terms}
     out["prefill_s_2048"] = _time_prefill(runner, cfg.vocab, 0, 2048, g, chunk)
     # the trace's shape: a 16K shared prefix, then a unique suffix.  A prefix hit restores the prefix's KV blocks and
@@ -93,6 +115,15 @@ def run_config4(args, dev) -> dict:
     for s in range(1, C):
         runner.reset(s)
         runner.prefill(s, torch.randint(0, cfg.vocab, (2048,), generator=g).tolist(), chunk=chunk)
+    if depth:
+        ms1, tps1 = _time_spec(runner, cfg.vocab, [0], args.steps, args.warmup, g)
+        ms8, tps8 = _time_spec(runner, cfg.vocab, list(range(C)), args.steps, args.warmup, g)
+        out.update(c1_decode_tok_s=1000.0 * tps1 / ms1, c1_ms_per_step=ms1, c1_tokens_per_step=tps1,
+                   c8_decode_tok_s=1000.0 * tps8 / ms8, c8_ms_per_step=ms8, c8_tokens_per_step=tps8 / C,
+                   acceptance="random-init weights: the head's drafts are almost never the model's pick, so a step emits "
+                              "~1 token and pays for the drafts and the extra verify rows; tokens per step is measured",
+                   steps=args.steps, context="slot 0 at ~17K, slots 1-7 at 2K")
+        return out
     ms1 = _time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g)
     ms8 = _time_decode(runner, cfg.vocab, list(range(C)), args.steps, args.warmup, g)
     out.update(c1_decode_tok_s=1000.0 / ms1, c1_ms_per_step=ms1, c8_decode_tok_s=1000.0 * C / ms8, c8_ms_per_step=ms8,

@@ -43,6 +43,11 @@ struct GdnArgs {
   float* prep;            // scratch: qn [T, hk, dk] | kn [T, hk, dk] | decay [T, hv] | beta [T, hv]
   int T, hk, hv, dk, dv;
   int sequential;         // 1: rows are consecutive tokens of ONE request (prefill); 0: one token per request
+  // speculative verify rows: seg > 0 = the rows come in runs of `seg` consecutive tokens, run r belonging to state slot
+  // row_slot[r * seg]; snap (optional): [T, hv, dk, dv] receives the state after every row, so a partial accept can
+  // roll the slot back to any row of its run without replaying it
+  int seg;
+  float* snap;
 };
 
 // Token-parallel part: unit-norm q (scaled by dk^-1/2) and k per key head, decay and write strength per value head.
@@ -96,8 +101,8 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_recurrent_kernel(GdnArgs a) {
   const int col = tid / kGdnParts, part = tid % kGdnParts;
   const int h = blockIdx.y, j = blockIdx.x * kGdnCols + col;
   const int hk_idx = h / (a.hv / a.hk);        // value heads share key heads in groups
-  const int first = a.sequential ? 0 : blockIdx.z;
-  const int last = a.sequential ? a.T : blockIdx.z + 1;
+  const int first = a.seg > 0 ? blockIdx.z * a.seg : (a.sequential ? 0 : blockIdx.z);
+  const int last = a.seg > 0 ? first + a.seg : (a.sequential ? a.T : blockIdx.z + 1);
   const int slot0 = a.row_slot ? a.row_slot[first] : a.slot;
   const float* qn = a.prep;
   const float* kn = qn + static_cast<size_t>(a.T) * a.hk * DK;
@@ -145,6 +150,11 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_recurrent_kernel(GdnArgs a) {
 #pragma unroll
       for (int o = kGdnParts / 2; o > 0; o >>= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
       if (part == 0) a.out[static_cast<size_t>(t0 + tt) * a.hv * a.dv + h * a.dv + j] = f32_to_bf16(ov);
+      if (a.snap) {
+        float* np = a.snap + ((static_cast<size_t>(t0 + tt) * a.hv + h) * DK) * a.dv + j;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) np[static_cast<size_t>(part + kGdnParts * i) * a.dv] = s[i];
+      }
     }
   }
 #pragma unroll
@@ -163,6 +173,8 @@ struct ConvArgs {
   int slot;
   bf16* out;            // [T, C]
   int T, C, W, sequential;
+  int seg;              // > 0: runs of `seg` consecutive tokens per request (see GdnArgs::seg)
+  float* snap;          // optional [T, W - 1, C]: the tail after every row of a run
 };
 
 // Output pass, parallel over tokens and channels: out[t, c] = silu(b + sum_i w[i] * X(t - (W - 1) + i)), where X(u)
@@ -172,13 +184,14 @@ __global__ void __launch_bounds__(256) gdn_conv_kernel(ConvArgs a) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= a.C) return;
   const int t = blockIdx.y;
-  const int slot = a.row_slot ? a.row_slot[t] : a.slot;
+  const int run0 = a.seg > 0 ? t - t % a.seg : (a.sequential ? 0 : t);     // first row of this row's run
+  const int slot = a.row_slot ? a.row_slot[run0] : a.slot;
   const float* st = a.state + static_cast<size_t>(slot) * (a.W - 1) * a.C + c;
   float acc = a.bias ? bf16_to_f32(a.bias[c]) : 0.f;
   for (int i = 0; i < a.W; ++i) {
-    const int u = (a.sequential ? t : 0) - (a.W - 1) + i;       // batched single tokens: only the row itself is new
+    const int u = (t - run0) - (a.W - 1) + i;                   // index inside the run; batched single tokens: only the row itself is new
     float xv;
-    if (u >= 0) xv = bf16_to_f32(a.x[static_cast<size_t>(a.sequential ? u : t) * a.x_stride + c]);
+    if (u >= 0) xv = bf16_to_f32(a.x[static_cast<size_t>(run0 + u) * a.x_stride + c]);
     else xv = st[static_cast<size_t>(a.W - 1 + u) * a.C];
     acc = fmaf(bf16_to_f32(a.w[c * a.W + i]), xv, acc);
   }
@@ -191,14 +204,25 @@ __global__ void __launch_bounds__(256) gdn_conv_state_kernel(ConvArgs a) {
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= a.C) return;
-  const int r = blockIdx.y;                                     // row (batched mode) or 0
-  const int n = a.sequential ? a.T : 1;                         // new inputs of this request
-  const int slot = a.row_slot ? a.row_slot[r] : a.slot;
+  const int r = blockIdx.y;                                     // run (segment / batched mode) or 0
+  const int n = a.seg > 0 ? a.seg : (a.sequential ? a.T : 1);   // new inputs of this request
+  const int run0 = a.seg > 0 ? r * a.seg : (a.sequential ? 0 : r);
+  const int slot = a.row_slot ? a.row_slot[run0] : a.slot;
   float* st = a.state + static_cast<size_t>(slot) * (a.W - 1) * a.C + c;
   float nv[3] = {0.f, 0.f, 0.f};
+  if (a.snap) {
+    // the tail after the first j inputs of the run, j = 1..n (a rollback target for every row)
+    for (int j = 1; j <= n; ++j)
+      for (int i = 0; i < a.W - 1; ++i) {
+        const int u = j - (a.W - 1) + i;
+        const float v = u >= 0 ? bf16_to_f32(a.x[static_cast<size_t>(run0 + u) * a.x_stride + c])
+                               : st[static_cast<size_t>(a.W - 1 + u) * a.C];
+        a.snap[(static_cast<size_t>(run0 + j - 1) * (a.W - 1) + i) * a.C + c] = v;
+      }
+  }
   for (int i = 0; i < a.W - 1; ++i) {
     const int u = n - (a.W - 1) + i;                            // input index that lands in tail position i
-    nv[i] = u >= 0 ? bf16_to_f32(a.x[static_cast<size_t>(a.sequential ? u : r) * a.x_stride + c])
+    nv[i] = u >= 0 ? bf16_to_f32(a.x[static_cast<size_t>(run0 + u) * a.x_stride + c])
                    : st[static_cast<size_t>(a.W - 1 + u) * a.C];
   }
   for (int i = 0; i < a.W - 1; ++i) st[static_cast<size_t>(i) * a.C] = nv[i];
@@ -230,11 +254,12 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const bf16* __restri
 
 using namespace dgpp;
 
-DGPP_API int dgpp_gdn_recurrent(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+static int gdn_recurrent_launch(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
                                 int64_t v_stride, const void* alpha, const void* beta, int64_t ab_stride,
                                 const void* A_log, const void* dt_bias, void* state, const void* row_slot, int slot,
-                                void* out, void* prep, int T, int hk, int hv, int dk, int dv, int sequential,
-                                cudaStream_t st) {
+                                void* out, void* prep, int T, int hk, int hv, int dk, int dv, int sequential, int seg,
+                                void* snap, cudaStream_t st) {
+  DGPP_REQUIRE(seg == 0 || (row_slot && T % seg == 0 && !sequential), "gdn: runs of %d rows need row_slot and T %% seg == 0", seg);
   DGPP_REQUIRE(dk == 64 || dk == 128 || dk == 256, "gdn: key dim %d unsupported", dk);
   DGPP_REQUIRE(dv % kGdnCols == 0 && hk > 0 && hv % hk == 0, "gdn: bad head geometry hk %d hv %d dv %d", hk, hv, dv);
   DGPP_REQUIRE(sequential || row_slot, "gdn: batched single-token rows need row_slot");
@@ -251,17 +276,38 @@ DGPP_API int dgpp_gdn_recurrent(const void* q, int64_t q_stride, const void* k, 
   a.out = static_cast<bf16*>(out);
   a.prep = static_cast<float*>(prep);
   a.T = T; a.hk = hk; a.hv = hv; a.dk = dk; a.dv = dv; a.sequential = sequential;
+  a.seg = seg; a.snap = static_cast<float*>(snap);
   dim3 pgrid(T, hk + 1);
   if (dk == 64) gdn_prep_kernel<64><<<pgrid, 64, 0, st>>>(a);
   else if (dk == 128) gdn_prep_kernel<128><<<pgrid, 128, 0, st>>>(a);
   else gdn_prep_kernel<256><<<pgrid, 256, 0, st>>>(a);
   DGPP_CUDA_OK(cudaGetLastError());
-  dim3 grid(dv / kGdnCols, hv, sequential ? 1 : T);
+  dim3 grid(dv / kGdnCols, hv, seg > 0 ? T / seg : (sequential ? 1 : T));
   if (dk == 64) gdn_recurrent_kernel<64><<<grid, kGdnThreads, 0, st>>>(a);
   else if (dk == 128) gdn_recurrent_kernel<128><<<grid, kGdnThreads, 0, st>>>(a);
   else gdn_recurrent_kernel<256><<<grid, kGdnThreads, 0, st>>>(a);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+DGPP_API int dgpp_gdn_recurrent(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                int64_t v_stride, const void* alpha, const void* beta, int64_t ab_stride,
+                                const void* A_log, const void* dt_bias, void* state, const void* row_slot, int slot,
+                                void* out, void* prep, int T, int hk, int hv, int dk, int dv, int sequential,
+                                cudaStream_t st) {
+  return gdn_recurrent_launch(q, q_stride, k, k_stride, v, v_stride, alpha, beta, ab_stride, A_log, dt_bias, state, row_slot,
+                              slot, out, prep, T, hk, hv, dk, dv, sequential, 0, nullptr, st);
+}
+
+// Runs of `seg` consecutive rows per request (speculative verify), with per-row state snapshots in `snap` (may be null).
+DGPP_API int dgpp_gdn_recurrent_runs(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                     int64_t v_stride, const void* alpha, const void* beta, int64_t ab_stride,
+                                     const void* A_log, const void* dt_bias, void* state, const void* row_slot, void* out,
+                                     void* prep, int T, int hk, int hv, int dk, int dv, int seg, void* snap,
+                                     cudaStream_t st) {
+  DGPP_REQUIRE(seg >= 1, "gdn_recurrent_runs: run length %d", seg);
+  return gdn_recurrent_launch(q, q_stride, k, k_stride, v, v_stride, alpha, beta, ab_stride, A_log, dt_bias, state, row_slot,
+                              0, out, prep, T, hk, hv, dk, dv, 0, seg, snap, st);
 }
 
 // Token-parallel preparation alone (unit-norm q / k, decay, write strength into `prep`); the chunked scan
@@ -288,9 +334,10 @@ DGPP_API int dgpp_gdn_prep(const void* q, int64_t q_stride, const void* k, int64
   return 0;
 }
 
-DGPP_API int dgpp_gdn_conv(const void* x, int64_t x_stride, const void* w, const void* bias, void* state,
-                           const void* row_slot, int slot, void* out, int T, int C, int W, int sequential,
-                           cudaStream_t st) {
+static int gdn_conv_launch(const void* x, int64_t x_stride, const void* w, const void* bias, void* state,
+                           const void* row_slot, int slot, void* out, int T, int C, int W, int sequential, int seg,
+                           void* snap, cudaStream_t st) {
+  DGPP_REQUIRE(seg == 0 || (row_slot && T % seg == 0 && !sequential), "gdn_conv: runs of %d rows need row_slot and T %% seg == 0", seg);
   DGPP_REQUIRE(W >= 1 && W <= 4, "gdn_conv: kernel width %d outside 1..4", W);
   DGPP_REQUIRE(sequential || row_slot, "gdn_conv: batched single-token rows need row_slot");
   if (T == 0) return 0;
@@ -302,13 +349,26 @@ DGPP_API int dgpp_gdn_conv(const void* x, int64_t x_stride, const void* w, const
   a.slot = slot;
   a.out = static_cast<bf16*>(out);
   a.T = T; a.C = C; a.W = W; a.sequential = sequential;
+  a.seg = seg; a.snap = static_cast<float*>(snap);
   gdn_conv_kernel<<<dim3(dgpp_ceil_div(C, 256), T), 256, 0, st>>>(a);
   DGPP_CUDA_OK(cudaGetLastError());
   if (W > 1) {
-    gdn_conv_state_kernel<<<dim3(dgpp_ceil_div(C, 256), sequential ? 1 : T), 256, 0, st>>>(a);
+    gdn_conv_state_kernel<<<dim3(dgpp_ceil_div(C, 256), seg > 0 ? T / seg : (sequential ? 1 : T)), 256, 0, st>>>(a);
     DGPP_CUDA_OK(cudaGetLastError());
   }
   return 0;
+}
+
+DGPP_API int dgpp_gdn_conv(const void* x, int64_t x_stride, const void* w, const void* bias, void* state,
+                           const void* row_slot, int slot, void* out, int T, int C, int W, int sequential,
+                           cudaStream_t st) {
+  return gdn_conv_launch(x, x_stride, w, bias, state, row_slot, slot, out, T, C, W, sequential, 0, nullptr, st);
+}
+
+DGPP_API int dgpp_gdn_conv_runs(const void* x, int64_t x_stride, const void* w, const void* bias, void* state,
+                                const void* row_slot, void* out, int T, int C, int W, int seg, void* snap, cudaStream_t st) {
+  DGPP_REQUIRE(seg >= 1, "gdn_conv_runs: run length %d", seg);
+  return gdn_conv_launch(x, x_stride, w, bias, state, row_slot, 0, out, T, C, W, 0, seg, snap, st);
 }
 
 DGPP_API int dgpp_gated_rmsnorm(const void* o, const void* z, int64_t z_stride, const void* w, void* out, int rows,

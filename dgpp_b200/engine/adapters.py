@@ -540,9 +540,15 @@ class HybridEngine(rt.SchedulerEngine):
     the blocks and restores that snapshot.  (reference counterparts: src/engine/prefix_arena.hpp state snapshots at
     cut positions, src/models/kda_snapshot.hpp, src/sched/prefix_cache.cpp.)"""
 
-    def __init__(self, runner, snapshot_every: int = 1024, max_snapshots: int = 64, prefill_chunk: int = 256):
+    def __init__(self, runner, snapshot_every: int = 1024, max_snapshots: int = 64, prefill_chunk: int = 256,
+                 mtp_depth: int = 0):
+        """mtp_depth > 0: every decode step drafts that many tokens with the model's MTP head and verifies them in the
+        same pass as the pending token (greedy: the emitted sequence does not change, only how many tokens a step emits)."""
         super().__init__()
         self.r = runner
+        self.mtp_depth = mtp_depth
+        if mtp_depth:
+            runner.enable_spec(mtp_depth)
         self.kv = runner.kv
         page = self.kv.page
         self.snapshot_every = max(page, snapshot_every // page * page)
@@ -660,6 +666,12 @@ class HybridEngine(rt.SchedulerEngine):
 
     def step_batch(self, slots):
         slots = list(slots)
+        if self.mtp_depth:
+            outs = self.r.spec_step(slots, [self.pending[s] for s in slots])
+            self._poll_device()
+            for s, o in zip(slots, outs):
+                self.pending[s] = int(o[-1])
+            return [[int(t) for t in o] for o in outs]
         logits = self.r.decode(slots, [self.pending[s] for s in slots])
         toks = torch.argmax(logits[:len(slots)], dim=-1).tolist()
         self._poll_device()

@@ -64,9 +64,13 @@ class GdnWeights:
 class GdnState:
     """Per-slot recurrent state: convolution tail + delta-rule memory (fp32)."""
 
-    def __init__(self, cfg: GdnConfig, slots: int, device):
-        self.conv = torch.zeros(slots, cfg.conv_width - 1, cfg.conv_channels, dtype=torch.float32, device=device)
-        self.ssm = torch.zeros(slots, cfg.v_heads, cfg.dk, cfg.dv, dtype=torch.float32, device=device)
+    def __init__(self, cfg: GdnConfig, slots: int, device, conv: Optional[torch.Tensor] = None,
+                 ssm: Optional[torch.Tensor] = None):
+        """conv / ssm: views into a pool shared by all recurrent layers (one commit kernel then serves every layer)."""
+        self.conv = conv if conv is not None else torch.zeros(slots, cfg.conv_width - 1, cfg.conv_channels,
+                                                              dtype=torch.float32, device=device)
+        self.ssm = ssm if ssm is not None else torch.zeros(slots, cfg.v_heads, cfg.dk, cfg.dv, dtype=torch.float32,
+                                                           device=device)
 
     def reset(self, slot: int) -> None:
         self.conv[slot].zero_()
@@ -137,16 +141,20 @@ class GdnLayer:
         self.prep = torch.empty(max_rows * (2 * c.k_heads * c.dk + 2 * c.v_heads), dtype=torch.float32, device=device)
 
     def forward(self, x: torch.Tensor, state: GdnState, out: torch.Tensor, slot: int = 0,
-                row_slot: Optional[torch.Tensor] = None) -> torch.Tensor:
+                row_slot: Optional[torch.Tensor] = None, seg: int = 0, snap=None) -> torch.Tensor:
         """x [rows, hidden] bf16.  row_slot None: the rows are consecutive tokens of request `slot` (prefill chunk);
-        otherwise one decode token per row, row r belonging to state slot row_slot[r]."""
+        otherwise one decode token per row, row r belonging to state slot row_slot[r].  seg > 0 (with row_slot): runs of
+        `seg` consecutive tokens per request (speculative verify rows); snap = (conv_snap [rows, W - 1, C], ssm_snap
+        [rows, hv, dk, dv]) then receives the state after every row."""
         c, w = self.c, self.w
         rows = x.shape[0]
         seq = row_slot is None
         proj = ops.linear(x, w.in_proj, out=self.proj[:rows])
         mixed, z, al, be, nq, nv = _split(c, proj)
-        conv = ops.gdn_conv(mixed, w.conv_w, w.conv_b, state.conv, self.conv[:rows], row_slot, slot, seq)
+        cs, ss = snap if snap is not None else (None, None)
+        conv = ops.gdn_conv(mixed, w.conv_w, w.conv_b, state.conv, self.conv[:rows], row_slot, slot, seq, seg=seg, snap=cs)
         ops.gdn_recurrent(conv[:, :nq], conv[:, nq:2 * nq], conv[:, 2 * nq:], al, be, w.A_log, w.dt_bias, state.ssm,
-                          self.o[:rows], c.k_heads, c.v_heads, c.dk, c.dv, row_slot, slot, seq, prep=self.prep)
+                          self.o[:rows], c.k_heads, c.v_heads, c.dk, c.dv, row_slot, slot, seq, prep=self.prep, seg=seg,
+                          snap=ss)
         ops.gated_rmsnorm(self.o[:rows], z, w.norm_w, self.gated[:rows], c.v_heads, c.dv, c.eps)
         return ops.linear(self.gated[:rows], w.out_proj, out=out)

@@ -182,11 +182,21 @@ class HybridRunner:
         n_full = sum(1 for i in range(c.layers) if c.is_full(i))
         blocks_per = (max_seq_len + c.page - 1) // c.page + 1
         self.kv = PagedKV(max(n_full, 1), c.kv_heads, c.head_dim, slots * blocks_per + 2, slots, blocks_per, c.page, True, device)
-        self.gdn_state = {i: GdnState(c.gdn_cfg(), slots, device) for i in range(c.layers) if not c.is_full(i)}
+        # recurrent state of all GDN layers in two pools (layer-major), so one kernel commits a speculative step
+        gc = c.gdn_cfg()
+        gdn_ids = [i for i in range(c.layers) if not c.is_full(i)]
+        self.gdn_index = {i: j for j, i in enumerate(gdn_ids)}
+        self.ssm_pool = torch.zeros(max(len(gdn_ids), 1), slots, gc.v_heads, gc.dk, gc.dv, dtype=torch.float32, device=device)
+        self.conv_pool = torch.zeros(max(len(gdn_ids), 1), slots, gc.conv_width - 1, gc.conv_channels, dtype=torch.float32,
+                                     device=device)
+        self.gdn_state = {i: GdnState(gc, slots, device, conv=self.conv_pool[j], ssm=self.ssm_pool[j])
+                          for i, j in self.gdn_index.items()}
         self.gdn = {i: GdnLayer(model.layers[i].gdn, max_rows, device) for i in self.gdn_state}
         self.full_index = {i: j for j, i in enumerate(i for i in range(c.layers) if c.is_full(i))}
         self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
                     if L.moe is not None and L.moe.gu_q is not None}
+        self.slots = slots
+        self.spec_rows = 0          # rows per speculative run (1 + draft depth); 0 = speculation off
         e = lambda *s: torch.empty(*s, dtype=BF, device=device)
         H, d = c.hidden, c.head_dim
         self.x, self.xn, self.delta = e(max_rows, H), e(max_rows, H), e(max_rows, H)
@@ -201,24 +211,29 @@ class HybridRunner:
                         and c.q_heads // c.kv_heads in (1, 2, 4, 8))
         self.max_splits = 32
         if self.tc_attn:
-            r = min(max_rows, 16)
+            r = min(max_rows, 32)
             self.att_scratch = (torch.empty(r * c.q_heads * self.max_splits * 2, dtype=torch.float32, device=device),
                                 torch.empty(r * c.q_heads * self.max_splits * d, dtype=torch.float32, device=device))
 
     def _decode_splits(self, rows: int) -> int:
         """KV splits of a decode pass: enough CTAs (kv heads x rows x splits) to cover the SMs; fixed per batch width,
         so a captured pass stays valid at every context length (a split past the end writes an empty partial)."""
-        if rows > 16:
+        if rows > 32:
             return 1
+        if self.spec_rows:
+            rows = 1      # verify rows must fold their KV range exactly like a plain decode row does
         return max(1, min(self.max_splits, -(-160 // (self.c.kv_heads * rows))))
 
     def _state_tensors(self):
         """Tensors a decode pass updates in place besides the KV cache (recurrent layers' state)."""
-        return [t for st in self.gdn_state.values() for t in (st.conv, st.ssm)]
+        return [self.conv_pool, self.ssm_pool]
 
     def reset(self, slot: int) -> None:
         self.kv.release(slot)
         self.lengths[slot] = 0
+        if self.spec_rows:
+            self.mtp_kv.release(slot)
+            self.mtp_prev[slot], self.mtp_tok[slot], self.mtp_len[slot] = None, [], 0
         for st in self.gdn_state.values():
             st.reset(slot)
 
@@ -236,10 +251,12 @@ class HybridRunner:
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, chunk_slot: Optional[int] = None,
-                all_logits: bool = True, pos0: Optional[int] = None) -> torch.Tensor:
+                all_logits: bool = True, pos0: Optional[int] = None, seg: int = 0, snap: bool = False) -> torch.Tensor:
         """tokens / positions / row_req: int32 [rows] on the device.  chunk_slot given: the rows are consecutive
         tokens of that request starting at position pos0 (prefill chunk); otherwise one decode token per row.
-        Returns fp32 logits [rows, V]."""
+        seg > 0: the rows are runs of `seg` consecutive tokens per request (speculative verify); snap: the recurrent
+        layers save their state after every row.  Returns fp32 logits [rows, V]; the residual stream before the final
+        norm (the MTP head's input) stays in self.x[:rows]."""
         m, c = self.m, self.c
         rows = tokens.shape[0]
         x, xn, delta = self.x[:rows], self.xn[:rows], self.delta[:rows]
@@ -248,8 +265,10 @@ class HybridRunner:
         for i, L in enumerate(m.layers):
             ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have else None, out=xn)
             if L.gdn is not None:
+                j = self.gdn_index[i]
                 self.gdn[i].forward(xn, self.gdn_state[i], delta, slot=chunk_slot or 0,
-                                    row_slot=None if chunk_slot is not None else row_req)
+                                    row_slot=None if chunk_slot is not None else row_req, seg=seg,
+                                    snap=(self.conv_snap[j], self.ssm_snap[j]) if snap else None)
             else:
                 cache = self.kv.layers[self.full_index[i]]
                 qkv, attn = self.qkv[:rows], self.attn[:rows]
@@ -259,7 +278,7 @@ class HybridRunner:
                 if self.tc_attn and chunk_slot is not None and pos0 is not None:
                     ops.attn_prefill_tc(qkv, qkv.stride(0), cache, self.kv.block_table[chunk_slot], pos0, c.q_heads,
                                         c.kv_heads, c.head_dim, self.scale, out=attn, rows=rows)
-                elif self.tc_attn and rows <= 16:
+                elif self.tc_attn and rows <= 32:
                     ops.attn_decode_tc(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, c.q_heads,
                                        c.kv_heads, c.head_dim, self.scale, splits=self._decode_splits(rows),
                                        scratch=self.att_scratch, out=attn)
@@ -286,23 +305,39 @@ class HybridRunner:
             pos = torch.arange(start + o, start + o + len(part), dtype=torch.int32, device=self.dev)
             req = torch.full((len(part),), slot, dtype=torch.int32, device=self.dev)
             out = self.forward(t, pos, req, chunk_slot=slot, all_logits=False, pos0=start + o)
+            if self.spec_rows:
+                self._mtp_after_prefill(slot, self.x[:len(part)].clone(), part, start + o)
         self.lengths[slot] = start + len(tokens)
+        if self.spec_rows:
+            self.mtp_tok[slot] = []
         return out
 
-    def _decode_rows(self, slots: List[int], tokens: List[int], positions: List[int]) -> torch.Tensor:
+    def _decode_rows(self, slots: List[int], tokens: List[int], positions: List[int], seg: int = 0) -> torch.Tensor:
         """One decode pass.  On a GPU the pass is captured once per batch width into a CUDA graph over static id /
         position / request tensors and replayed (a pass is hundreds of small launches; replay removes the host's
         launch cost from every step); `use_graphs = False` launches kernel by kernel."""
         b = len(slots)
-        host = torch.tensor([tokens, positions, slots], dtype=torch.int32)
+        snap = seg > 0
+        on_dev = isinstance(tokens, torch.Tensor)          # speculative drafts never visit the host
+        if on_dev:
+            host = torch.tensor([positions, slots], dtype=torch.int32)
+        else:
+            host = torch.tensor([tokens, positions, slots], dtype=torch.int32)
         if not (self.use_graphs and torch.device(self.dev).type == "cuda"):
             d = host.to(self.dev)
-            return self.forward(d[0], d[1], d[2])
-        st = self._static.get(b)
+            if on_dev:
+                return self.forward(tokens, d[0], d[1], seg=seg, snap=snap)
+            return self.forward(d[0], d[1], d[2], seg=seg, snap=snap)
+        key = (b, seg)
+        st = self._static.get(key)
         if st is None:
-            st = self._static[b] = torch.zeros(3, b, dtype=torch.int32, device=self.dev)
-        st.copy_(host, non_blocking=True)
-        g = self._graphs.get(b)
+            st = self._static[key] = torch.zeros(3, b, dtype=torch.int32, device=self.dev)
+        if on_dev:
+            st[0].copy_(tokens)
+            st[1:].copy_(host, non_blocking=True)
+        else:
+            st.copy_(host, non_blocking=True)
+        g = self._graphs.get(key)
         if g is None:
             # warm-up outside capture (lazy kernel attributes, workspaces); state-carrying layers are advanced by it,
             # so their state is saved before and put back after: only replays move the model forward
@@ -310,15 +345,15 @@ class HybridRunner:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                self.forward(st[0], st[1], st[2])
+                self.forward(st[0], st[1], st[2], seg=seg, snap=snap)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                out = self.forward(st[0], st[1], st[2])
+                out = self.forward(st[0], st[1], st[2], seg=seg, snap=snap)
             for t, s0 in zip(self._state_tensors(), saved):
                 t.copy_(s0)
-            g = self._graphs[b] = (graph, out)
+            g = self._graphs[key] = (graph, out)
         graph, out = g
         graph.replay()
         return out
@@ -331,4 +366,154 @@ class HybridRunner:
         out = self._decode_rows(slots, tokens, [self.lengths[s] for s in slots])
         for s in slots:
             self.lengths[s] += 1
+        return out
+
+    # ------------------------------------------------------------------ multi-token prediction: draft, verify, commit
+    def enable_spec(self, depth: int) -> None:
+        """Turn on speculative decoding with `depth` drafts per step from the MTP head (1 <= depth <= 3).  Call before the
+        first prefill: the head keeps its own one-layer KV cache, filled alongside the model's.
+        (reference counterparts: src/models/qwen/model35.cpp:1909 mtp_run_rows, src/engine/speculative.hpp:155.)"""
+        from ..engine.kv_cache import PagedKV
+
+        m, c = self.m, self.c
+        assert m.mtp_layer is not None, "the model has no MTP head"
+        assert 1 <= depth <= 3 and all(n == 0 for n in self.lengths)
+        V = depth + 1
+        self.spec_rows = V
+        rows = self.slots * V
+        gc = c.gdn_cfg()
+        Lg = self.ssm_pool.shape[0]
+        self.ssm_snap = torch.zeros(Lg, rows, gc.v_heads, gc.dk, gc.dv, dtype=torch.float32, device=self.dev)
+        self.conv_snap = torch.zeros(Lg, rows, gc.conv_width - 1, gc.conv_channels, dtype=torch.float32, device=self.dev)
+        self.mtp_kv = PagedKV(1, c.kv_heads, c.head_dim, self.kv.num_blocks, self.slots, self.kv.max_blocks, c.page, True,
+                              self.dev)
+        L = m.mtp_layer
+        self.mtp_moe = MoEBlock(L.moe, 16, self.dev) if (L.moe is not None and L.moe.gu_q is not None) else None
+        self.mtp_prev = [None] * self.slots      # main-model hidden rows whose MTP pair still waits for its next token
+        self.mtp_tok = [[] for _ in range(self.slots)]   # tokens after those rows, the newest excepted (it is the pending one)
+        self.mtp_len = [0] * self.slots          # MTP cache filled for positions < mtp_len
+        i32 = dict(dtype=torch.int32, device=self.dev)
+        self.n_acc, self.emitted = torch.zeros(self.slots, **i32), torch.zeros(self.slots * V, **i32)
+        self._graphs.clear()                     # decode splits are pinned once speculation is on
+        ops.PIN_SPLIT_ROWS = True                # (process-wide: plain passes of this process pick the same splits)
+
+    def _mtp_rows(self, hidden: torch.Tensor, next_tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor,
+                  chunk_slot: Optional[int] = None, pos0: Optional[int] = None):
+        """MTP head over the pairs (hidden_t, token_{t+1}) at MTP positions `positions` (its own KV cache is appended at
+        those positions).  Returns (fp32 logits [rows, V] for token_{t+2}, the head's residual stream [rows, H])."""
+        m, c = self.m, self.c
+        rows = hidden.shape[0]
+        L = m.mtp_layer
+        hn = ops.rmsnorm(hidden, m.mtp_norm_h, c.eps)
+        emb = ops.embed_gather(next_tokens, m.embed, out=torch.empty(rows, c.hidden, dtype=BF, device=self.dev))
+        en = ops.rmsnorm(emb, m.mtp_norm_e, c.eps)
+        x = ops.linear(torch.cat([hn, en], -1), m.mtp_proj)
+        xn = ops.rmsnorm(x, L.in_norm, c.eps)
+        cache = self.mtp_kv.layers[0]
+        qkv = ops.linear(xn, L.qkv)
+        ops.rope_kv_write(qkv, positions, row_req, self.mtp_kv.block_table, m.inv_freq, cache, c.q_heads, c.kv_heads, c.head_dim)
+        if self.tc_attn and chunk_slot is not None and pos0 is not None and rows > 32:
+            attn = ops.attn_prefill_tc(qkv, qkv.stride(0), cache, self.mtp_kv.block_table[chunk_slot], pos0, c.q_heads,
+                                       c.kv_heads, c.head_dim, self.scale, rows=rows)
+        elif self.tc_attn and rows <= 32:
+            attn = ops.attn_decode_tc(qkv, qkv.stride(0), cache, self.mtp_kv.block_table, row_req, positions, c.q_heads,
+                                      c.kv_heads, c.head_dim, self.scale, splits=self._decode_splits(rows),
+                                      scratch=self.att_scratch)
+        else:
+            attn = ops.attn_decode(qkv, qkv.stride(0), cache, self.mtp_kv.block_table, row_req, positions, c.q_heads,
+                                   c.kv_heads, c.head_dim, self.scale)
+        delta = ops.linear(attn, L.o)
+        xn = ops.rmsnorm(x, L.post_norm, c.eps, delta=delta)
+        if L.moe is not None:
+            if self.mtp_moe is not None and rows <= self.mtp_moe.max_rows:
+                self.mtp_moe.forward(xn, delta)
+            elif self.mtp_moe is not None:
+                delta = self.mtp_moe.forward_gathered(xn)
+            else:
+                delta = moe_reference(xn, L.moe)
+        else:
+            delta = ops.linear(ops.swiglu(ops.linear(xn, L.gate_up)), L.down)
+        xn = ops.rmsnorm(x, m.final_norm, c.eps, delta=delta)
+        logits = ops.gemm_tc(xn, m.head, out32=torch.empty(rows, c.vocab, dtype=torch.float32, device=self.dev))
+        return logits, x
+
+    def _mtp_after_prefill(self, slot: int, hidden: torch.Tensor, tokens: List[int], start: int) -> None:
+        """Feed the MTP cache with the pairs a prefill chunk completes: (hidden_{t}, token_{t+1}) for every t whose next
+        token is known; the chunk's last hidden row waits for the next token."""
+        T = hidden.shape[0]
+        rows, toks, p0 = hidden[:T - 1], tokens[1:], start
+        if self.mtp_prev[slot] is not None:
+            rows, toks, p0 = torch.cat([self.mtp_prev[slot], rows]), tokens, start - self.mtp_prev[slot].shape[0]
+        n = rows.shape[0]
+        if n:
+            assert self.mtp_kv.reserve(slot, p0 + n), "MTP KV pool exhausted"
+            t = torch.tensor(toks, dtype=torch.int32, device=self.dev)
+            pos = torch.arange(p0, p0 + n, dtype=torch.int32, device=self.dev)
+            req = torch.full((n,), slot, dtype=torch.int32, device=self.dev)
+            self._mtp_rows(rows.contiguous(), t, pos, req, chunk_slot=slot, pos0=p0)
+            self.mtp_len[slot] = p0 + n
+        self.mtp_prev[slot] = hidden[T - 1:T].clone()
+
+    @torch.no_grad()
+    def spec_step(self, slots: List[int], pending: List[int], drafts: Optional[List[List[int]]] = None) -> List[List[int]]:
+        """One speculative step for the listed requests.  pending[i]: the token emitted last for slots[i] (not yet in the
+        caches).  Drafts come from the MTP head (or from `drafts`, depth tokens per request, for tests).  Returns the new
+        tokens of every request (1 .. depth + 1 of them); the last one is its new pending token.  Greedy: the emitted
+        sequence is the one plain decoding emits."""
+        V, R = self.spec_rows, len(slots)
+        assert V >= 2, "enable_spec first"
+        depth = V - 1
+        dev = self.dev
+        i32 = dict(dtype=torch.int32, device=dev)
+        if drafts is None:
+            # round 0: every pair that waits (hidden rows of the last step, their next tokens ending in the pending one)
+            hid, toks, pos, req, last = [], [], [], [], []
+            for s, p in zip(slots, pending):
+                h = self.mtp_prev[s]
+                n = h.shape[0]
+                known = self.mtp_tok[s][:n - 1]
+                hid.append(h)
+                toks += list(known) + [p]
+                p0 = self.lengths[s] - n
+                pos += list(range(p0, p0 + n))
+                req += [s] * n
+                last.append(len(toks) - 1)
+                assert self.mtp_kv.reserve(s, self.lengths[s] + V), "MTP KV pool exhausted"
+            logits, hm = self._mtp_rows(torch.cat(hid), torch.tensor(toks, **i32), torch.tensor(pos, **i32),
+                                        torch.tensor(req, **i32))
+            sel = torch.tensor(last, dtype=torch.long, device=dev)
+            d = torch.argmax(logits[sel], -1).to(torch.int32)
+            cols = [d]
+            hm = hm[sel].contiguous()
+            rreq = torch.tensor(slots, **i32)
+            base = torch.tensor([self.lengths[s] for s in slots], **i32)
+            for j in range(1, depth):
+                logits, hm = self._mtp_rows(hm, cols[-1], base - 1 + j, rreq)
+                cols.append(torch.argmax(logits, -1).to(torch.int32))
+            dr = torch.stack(cols, 1)                                   # [R, depth] on the device
+        else:
+            dr = torch.tensor(drafts, **i32).view(R, depth)
+        tok = torch.cat([torch.tensor(pending, **i32).view(R, 1), dr], 1).reshape(-1)        # [R * V]
+        for s in slots:
+            assert self.kv.reserve(s, self.lengths[s] + V), "KV pool exhausted"
+        positions = [self.lengths[s] + i for s in slots for i in range(V)]
+        row_slots = [s for s in slots for _ in range(V)]
+        req_d = torch.tensor(row_slots, **i32)
+        logits = self._decode_rows(row_slots, tok, positions, seg=V)      # tokens stay on the device
+        picks = torch.argmax(logits[:R * V], -1).to(torch.int32)
+        hidden = self.x[:R * V].clone()
+        ops.spec_accept(tok, picks, self.n_acc, self.emitted, R, V)
+        ops.spec_commit(self.ssm_pool, self.ssm_snap, self.conv_pool, self.conv_snap, req_d, self.n_acc, R, V)
+        host = torch.cat([self.n_acc[:R], self.emitted[:R * V], tok]).tolist()       # the step's one device -> host read
+        n_acc, emitted, tok_h = host[:R], host[R:R + R * V], host[R + R * V:]
+        out = []
+        for r, s in enumerate(slots):
+            n = n_acc[r]
+            new = emitted[r * V:r * V + n]
+            self.lengths[s] += n
+            self.mtp_prev[s] = hidden[r * V:r * V + n]
+            self.mtp_tok[s] = tok_h[r * V + 1:r * V + n] + [new[-1]]
+            out.append(new)
+        self.spec_steps = getattr(self, "spec_steps", 0) + R
+        self.spec_tokens = getattr(self, "spec_tokens", 0) + sum(len(o) for o in out)
         return out

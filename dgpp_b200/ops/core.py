@@ -322,8 +322,15 @@ def pick_cluster_splits(rows: int, n: int, k: int, bn: int) -> int:
 FP4_SPLIT_POLICY = "auto"
 
 
+# True: the split-K choice of the block-scaled GEMM ignores whether a pass has one row or several, so a row computes the
+# same bits in a plain decode pass and among speculative verify rows (set by speculation; the one-row tuning is lost).
+PIN_SPLIT_ROWS = False
+
+
 def pick_splits_fp4(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:
     """Split K for few-tile problems (the deterministic fold costs a few microseconds)."""
+    if PIN_SPLIT_ROWS:
+        rows = max(rows, 2)
     tiles = math.ceil(n / 128) * math.ceil(rows / bn)
     stages = k // 256
     if FP4_SPLIT_POLICY == "resident" or (FP4_SPLIT_POLICY == "auto" and rows == 1):
@@ -577,6 +584,10 @@ _lib.declare("dgpp_gdn_conv", [P, L, P, P, P, P, I, P, I, I, I, I, P])
 _lib.declare("dgpp_gated_rmsnorm", [P, P, L, P, P, I, I, I, F, P])
 
 
+_lib.declare("dgpp_gdn_recurrent_runs", [P, L, P, L, P, L, P, P, L, P, P, P, P, P, P, I, I, I, I, I, I, P, P])
+_lib.declare("dgpp_gdn_conv_runs", [P, L, P, P, P, P, P, I, I, I, I, P, P])
+_lib.declare("dgpp_spec_accept", [P, P, P, P, I, I, P])
+_lib.declare("dgpp_spec_commit", [P, P, P, P, P, P, I, I, I, I, I, L, L, P])
 _lib.declare("dgpp_gdn_prep", [P, L, P, L, P, P, L, P, P, P, I, I, I, I, P])
 _lib.declare("dgpp_gdn_chunk_scan", [P, P, P, P, P, L, P, P, P, L, I, I, I, I, I, P])
 # Sequential runs of at least this many rows take the chunked scan; shorter ones (and decode) the token recurrence.
@@ -595,24 +606,36 @@ def _gdn_scratch(device, floats: int) -> torch.Tensor:
     return t
 
 
-def gdn_conv(x, w, bias, state, out, row_slot=None, slot: int = 0, sequential: bool = True):
+def gdn_conv(x, w, bias, state, out, row_slot=None, slot: int = 0, sequential: bool = True, seg: int = 0, snap=None):
     """Causal depthwise conv (width w.shape[1]) + SiLU.  x: [T, C] bf16 rows (may be a strided column view);
-    state: [slots, W - 1, C] fp32, updated in place."""
+    state: [slots, W - 1, C] fp32, updated in place.  seg > 0: the rows are runs of `seg` consecutive tokens, run r
+    belonging to slot row_slot[r * seg]; snap [T, W - 1, C] (optional) receives the tail after every row."""
     T, C = x.shape
+    if seg > 0:
+        call("dgpp_gdn_conv_runs", ptr(x), x.stride(0), ptr(w), ptr(bias), ptr(state), ptr(row_slot), ptr(out), T, C,
+             w.shape[1], seg, ptr(snap), stream_ptr())
+        return out
     call("dgpp_gdn_conv", ptr(x), x.stride(0), ptr(w), ptr(bias), ptr(state), ptr(row_slot), slot, ptr(out), T, C,
          w.shape[1], int(sequential), stream_ptr())
     return out
 
 
 def gdn_recurrent(q, k, v, alpha, beta, A_log, dt_bias, state, out, hk: int, hv: int, dk: int, dv: int, row_slot=None,
-                  slot: int = 0, sequential: bool = True, prep=None):
+                  slot: int = 0, sequential: bool = True, prep=None, seg: int = 0, snap=None):
     """Gated delta-rule recurrence.  q/k: [T, hk*dk], v: [T, hv*dv] (column views allowed), alpha/beta: [T, hv]
-    views with a common row stride; state [slots, hv, dk, dv] fp32 updated in place; out [T, hv*dv] bf16."""
+    views with a common row stride; state [slots, hv, dk, dv] fp32 updated in place; out [T, hv*dv] bf16.
+    seg > 0: runs of `seg` consecutive tokens per request (slot row_slot[r * seg]); snap [T, hv, dk, dv] (optional)
+    receives the state after every row."""
     T = q.shape[0]
     assert alpha.stride(0) == beta.stride(0)
     need = T * (2 * hk * dk + 2 * hv)
     if prep is None or prep.numel() < need:
         prep = torch.empty(need, dtype=torch.float32, device=q.device)
+    if seg > 0:
+        call("dgpp_gdn_recurrent_runs", ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0), ptr(alpha), ptr(beta),
+             alpha.stride(0), ptr(A_log), ptr(dt_bias), ptr(state), ptr(row_slot), ptr(out), ptr(prep), T, hk, hv, dk, dv,
+             seg, ptr(snap), stream_ptr())
+        return out
     if sequential and GDN_CHUNKED and T >= GDN_CHUNK_MIN_ROWS and dk in (64, 128) and dv % 32 == 0:
         # prefill: chunked scan (64-token chunks as small GEMMs) instead of T dependent token steps
         chunks = (T + 63) // 64
@@ -630,6 +653,22 @@ def gdn_recurrent(q, k, v, alpha, beta, A_log, dt_bias, state, out, hk: int, hv:
          alpha.stride(0), ptr(A_log), ptr(dt_bias), ptr(state), ptr(row_slot), slot, ptr(out), ptr(prep), T, hk, hv, dk,
          dv, int(sequential), stream_ptr())
     return out
+
+
+def spec_accept(tokens, picks, n_acc, emitted, runs: int, run_rows: int) -> None:
+    """Greedy verdict of speculative runs: tokens / picks [runs * run_rows] int32 -> n_acc [runs], emitted [runs, run_rows]."""
+    call("dgpp_spec_accept", ptr(tokens), ptr(picks), ptr(n_acc), ptr(emitted), runs, run_rows, stream_ptr())
+
+
+def spec_commit(ssm, ssm_snap, conv, conv_snap, run_slot, n_acc, runs: int, run_rows: int) -> None:
+    """Roll the recurrent state of partially accepted runs back to the snapshot after their last kept row.
+    ssm [layers, slots, ...] / ssm_snap [layers, rows, ...] fp32 (same for the convolution tails)."""
+    layers, slots = ssm.shape[0], ssm.shape[1]
+    rows = ssm_snap.shape[1]
+    S = ssm[0, 0].numel()
+    Cc = conv[0, 0].numel()
+    call("dgpp_spec_commit", ptr(ssm), ptr(ssm_snap), ptr(conv), ptr(conv_snap), ptr(run_slot), ptr(n_acc), layers, slots,
+         rows, runs, run_rows, S, Cc, stream_ptr())
 
 
 def gated_rmsnorm(o, z, w, out, heads: int, d: int, eps: float = 1e-6):

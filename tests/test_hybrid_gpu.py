@@ -86,3 +86,67 @@ def test_hybrid_engine_behind_the_scheduler_with_state_snapshots(dev):
     # the chain matches 256 + tokens (4 blocks of 64), snapshots exist at 128 and 256 -> 256 tokens are reused
     assert m1["prefix_hit_tokens"] == 256 and eng.snapshots_restored == 1 and eng.snapshots_taken >= 2
     assert cached == plain and all(len(v) == 6 for v in cached.values())
+
+
+@pytest.mark.parametrize("moe,depth", [(False, 3), (True, 2)])
+def test_mtp_speculation_emits_the_plain_greedy_sequence(dev, moe, depth):
+    """Draft with the MTP head, verify 1 + depth rows in one pass, commit / roll back on the device: the emitted tokens
+    equal plain greedy decoding token for token, whatever was accepted.  Forced drafts cover full and partial accepts."""
+    from dgpp_b200.models.hybrid import HybridConfig, HybridModel, HybridRunner
+    from dgpp_b200.models.moe import MoEConfig
+    from dgpp_b200.ops import core as ops
+
+    ops.PIN_SPLIT_ROWS = True
+    cfg = HybridConfig(layers=4, hidden=512, full_every=4, q_heads=4, kv_heads=2, head_dim=128, gdn_k_heads=2,
+                       gdn_v_heads=4, gdn_dk=128, gdn_dv=128, ffn=1024, vocab=2048, mtp=True,
+                       moe=MoEConfig(experts=16, top_k=2, moe_ffn=512, shared_ffn=512) if moe else None)
+    m = HybridModel.random_init(cfg, dev, seed=9, std=0.05)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (45, 70)]
+    N = 18
+
+    plain = HybridRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+    want = []
+    for s, p in enumerate(prompts):
+        tok = int(torch.argmax(plain.prefill(s, p, chunk=32)[0]))
+        seq = [tok]
+        for _ in range(N + 4):
+            tok = int(torch.argmax(plain.decode([s], [tok])[0]))
+            seq.append(tok)
+        want.append(seq)
+
+    def run(forced):
+        r = HybridRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+        r.enable_spec(depth)
+        pend, got = [], []
+        for s, p in enumerate(prompts):
+            pend.append(int(torch.argmax(r.prefill(s, p, chunk=32)[0])))
+            got.append([pend[-1]])
+        step = 0
+        while min(len(x) for x in got) < N:
+            drafts = None
+            if forced:
+                drafts = []
+                for s in range(2):
+                    nxt = want[s][len(got[s]):len(got[s]) + depth]
+                    nxt = nxt + [0] * (depth - len(nxt))
+                    keep = (step + s) % (depth + 1)               # accept `keep` drafts, then a wrong one
+                    drafts.append([t if i < keep else (t + 1) % cfg.vocab for i, t in enumerate(nxt)])
+            outs = r.spec_step([0, 1], pend, drafts=drafts)
+            for s in range(2):
+                assert 1 <= len(outs[s]) <= depth + 1
+                if forced:
+                    assert len(outs[s]) == (step + s) % (depth + 1) + 1, (step, s, outs[s])
+                got[s] += outs[s]
+                pend[s] = outs[s][-1]
+            step += 1
+        torch.cuda.synchronize()
+        ops.check_status()
+        return got, r
+
+    for forced in (True, False):
+        got, r = run(forced)
+        for s in range(2):
+            n = min(len(got[s]), len(want[s]))
+            assert got[s][:n] == want[s][:n], (forced, s)
+            assert r.lengths[s] == len(prompts[s]) + len(got[s]) - 1
