@@ -131,11 +131,51 @@ def bench_gemm_tc(args, dev):
            fmt=args.fmt)
 
 
-def _cache(dev, hq, hkv, ctx, page=64, slots=1):
+def bench_gemm_fp8(args, dev):
+    """Native FP8 linear (activation quantiser timed separately) against the converter path on the same weights."""
+    from ..ops import core as ops
+    from ..quant.formats import random_quant_linear
+
+    n, k, rows = args.n, args.k, args.rows
+    copies = max(2, min(16, math.ceil(2 * L2_BYTES / (n * k)))) if rows <= 64 else 2
+    ws = [random_quant_linear(n, k, "fp8", dev) for _ in range(copies)]
+    x = torch.randn(rows, k, device=dev).to(BF)
+    xa = ops.fp8_act_quant(x)
+    out = torch.empty(rows, n, device=dev, dtype=BF)
+    splits = args.splits or None
+    ms = run([(lambda w=w: ops.gemm_fp8(xa, w, out=out, splits=splits)) for w in ws], args)
+    ops.check_status()
+    report(args, "gemm_fp8", ms, bytes_=n * k + rows * k + rows * n * 2, flops=2.0 * rows * n * k, rows=rows, n=n, k=k)
+    ms = run([lambda: ops.fp8_act_quant(x, out=xa)], args)
+    report(args, "fp8_act_quant", ms, bytes_=rows * k * 3, rows=rows, k=k)
+    ms = run([(lambda w=w: ops.gemm_tc(x, w, out=out)) for w in ws], args)
+    report(args, "gemm_tc (fp8 weights through the converter warps)", ms, bytes_=n * k + rows * k * 2 + rows * n * 2,
+           flops=2.0 * rows * n * k, rows=rows, n=n, k=k)
+
+
+def bench_mla(args, dev):
+    """Latent attention decode: tensor-core kernel against the CUDA-core kernel (rows requests at context ctx)."""
+    from ..ops import core as ops
+
+    rows, ctx, heads, page = args.rows, args.ctx, args.hq, 64
+    blocks_per = ctx // page + 2
+    cache = (torch.randn(rows * blocks_per + 1, page, 576, device=dev) * 0.3).to(BF)
+    table = (1 + torch.arange(rows * blocks_per, device=dev, dtype=torch.int32)).view(rows, blocks_per).contiguous()
+    q = (torch.randn(rows, heads, 576, device=dev) * 0.3).to(BF)
+    req = torch.arange(rows, dtype=torch.int32, device=dev)
+    pos = torch.full((rows,), ctx - 1, dtype=torch.int32, device=dev)
+    sp = args.splits or 4
+    for tc in (True, False):
+        ms = run([lambda tc=tc: ops.mla_decode(q, cache, table, req, pos, 0.07, 512, 64, splits=sp, tensor_cores=tc)], args)
+        ops.check_status()
+        report(args, "mla_decode_tc" if tc else "mla_decode (CUDA cores)", ms, bytes_=rows * ctx * 576 * 2.0,
+               flops=2.0 * rows * heads * ctx * (576 + 512), rows=rows, ctx=ctx, heads=heads, splits=sp)
+
+
+def _cache(dev, hq, hkv, ctx, page=64, slots=1, d=128):
     from ..engine.kv_cache import PagedKV
     from ..ops import core as ops, reference as ref
 
-    d = 128
     per = ctx // page + 2
     kv = PagedKV(1, hkv, d, slots * per + 2, slots, per, page, True, dev)
     inv_freq, _ = ref.rope_inv_freq(d, 1e4, dev)
@@ -151,33 +191,33 @@ def _cache(dev, hq, hkv, ctx, page=64, slots=1):
 def bench_attn_decode(args, dev):
     from ..ops import core as ops
 
-    hq, hkv, ctx, rows = args.hq, args.hkv, args.ctx, args.rows
-    kv, _ = _cache(dev, hq, hkv, ctx, slots=rows)
-    q = torch.randn(rows, (hq + 2 * hkv) * 128, device=dev).to(BF)
+    hq, hkv, ctx, rows, d = args.hq, args.hkv, args.ctx, args.rows, args.head_dim
+    kv, _ = _cache(dev, hq, hkv, ctx, slots=rows, d=d)
+    q = torch.randn(rows, (hq + 2 * hkv) * d, device=dev).to(BF)
     pos = torch.full((rows,), ctx - 1, device=dev, dtype=torch.int32)
     req = torch.arange(rows, device=dev, dtype=torch.int32)
-    out = torch.empty(rows, hq * 128, device=dev, dtype=BF)
+    out = torch.empty(rows, hq * d, device=dev, dtype=BF)
     sp = args.splits or 4
-    scratch = (torch.empty(rows * hq * sp * 2, device=dev), torch.empty(rows * hq * sp * 128, device=dev))
-    fn = lambda: ops.attn_decode_tc(q, q.stride(0), kv.layers[0], kv.block_table, req, pos, hq, hkv, 128, 0.088, splits=sp,
+    scratch = (torch.empty(rows * hq * sp * 2, device=dev), torch.empty(rows * hq * sp * d, device=dev))
+    fn = lambda: ops.attn_decode_tc(q, q.stride(0), kv.layers[0], kv.block_table, req, pos, hq, hkv, d, 0.088, splits=sp,
                                     scratch=scratch, out=out)
     ms = run([fn] * 4, args)
     ops.check_status()
-    report(args, "attn_decode_tc", ms, bytes_=2.0 * rows * ctx * hkv * 128, flops=4.0 * rows * hq * ctx * 128, rows=rows, ctx=ctx,
-           hq=hq, hkv=hkv, splits=sp)
+    report(args, "attn_decode_tc", ms, bytes_=2.0 * rows * ctx * hkv * d, flops=4.0 * rows * hq * ctx * d, rows=rows, ctx=ctx,
+           hq=hq, hkv=hkv, head_dim=d, splits=sp)
 
 
 def bench_attn_prefill(args, dev):
     from ..ops import core as ops
 
-    hq, hkv, ctx = args.hq, args.hkv, args.ctx
-    kv, qkv = _cache(dev, hq, hkv, ctx)
-    out = torch.empty(ctx, hq * 128, device=dev, dtype=BF)
-    fn = lambda: ops.attn_prefill_tc(qkv, qkv.stride(0), kv.layers[0], kv.block_table[0], 0, hq, hkv, 128, 0.088, out=out)
+    hq, hkv, ctx, d = args.hq, args.hkv, args.ctx, args.head_dim
+    kv, qkv = _cache(dev, hq, hkv, ctx, d=d)
+    out = torch.empty(ctx, hq * d, device=dev, dtype=BF)
+    fn = lambda: ops.attn_prefill_tc(qkv, qkv.stride(0), kv.layers[0], kv.block_table[0], 0, hq, hkv, d, 0.088, out=out)
     ms = run([fn] * 2, args)
     ops.check_status()
-    report(args, "attn_prefill_tc", ms, flops=4.0 * ctx * ctx / 2 * 128 * hq, bytes_=2.0 * ctx * hkv * 128 + 4.0 * ctx * hq * 128,
-           ctx=ctx, hq=hq, hkv=hkv, note="causal, bf16-equivalent FLOPs (two-term fp8 operands issue 4x the MMAs)")
+    report(args, "attn_prefill_tc", ms, flops=4.0 * ctx * ctx / 2 * d * hq, bytes_=2.0 * ctx * hkv * d + 4.0 * ctx * hq * d,
+           ctx=ctx, hq=hq, hkv=hkv, head_dim=d, note="causal, bf16-equivalent FLOPs (two-term fp8 operands issue 4x the MMAs)")
 
 
 def bench_act_quant(args, dev):
@@ -302,8 +342,8 @@ def bench_decode_layer(args, dev):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm_fp4", "gemm_tc", "attn_decode", "attn_prefill", "act_quant", "gdn", "moe",
-                                       "decode_layer"])
+    ap.add_argument("kernel", choices=["gemm_fp4", "gemm_tc", "gemm_fp8", "attn_decode", "attn_prefill", "act_quant", "gdn",
+                                       "moe", "mla", "decode_layer"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
@@ -313,6 +353,7 @@ def main(argv=None) -> int:
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--hq", type=int, default=40)
     ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128, choices=(128, 256))
     ap.add_argument("--hv", type=int, default=32)
     ap.add_argument("--mode", default="rmsnorm", choices=["plain", "rmsnorm", "swiglu"])
     ap.add_argument("--experts", type=int, default=128)
@@ -325,7 +366,7 @@ def main(argv=None) -> int:
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     torch.manual_seed(0)
-    {"gemm_fp4": bench_gemm_fp4, "gemm_tc": bench_gemm_tc, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill,
+    {"gemm_fp4": bench_gemm_fp4, "gemm_tc": bench_gemm_tc, "gemm_fp8": bench_gemm_fp8, "mla": bench_mla, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill,
      "act_quant": bench_act_quant, "gdn": bench_gdn, "moe": bench_moe,
      "decode_layer": bench_decode_layer}[args.kernel](args, dev)
     return 0

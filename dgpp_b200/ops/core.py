@@ -578,6 +578,62 @@ def gemm_fp4_grouped(xa: "QuantAct", wq, wsf_tiled, alphas, out, rows: int, n: i
     return out
 
 
+# ---------------------------------------------------------------------------------------------- native FP8 linear
+_lib.declare("dgpp_fp8_act_quant", [P, L, P, P, I, I, I, P])
+_lib.declare("dgpp_gemm_fp8", [P, P, P, P, P, P, I, I, I, I, I, I, I, P])
+
+
+class Fp8Act:
+    """Activations as e4m3 bytes [rows_pad, K] with one fp32 scale per token and 128 columns (stored [K / 128, rows_pad])."""
+
+    def __init__(self, rows_pad: int, k: int, device):
+        self.q = torch.zeros(rows_pad, k, dtype=torch.uint8, device=device)
+        self.scale = torch.ones(k // 128, rows_pad, dtype=torch.float32, device=device)
+        self.rows, self.rows_pad, self.k = 0, rows_pad, k
+
+    def dequant(self) -> torch.Tensor:
+        v = self.q[:self.rows].view(torch.float8_e4m3fn).float().view(self.rows, self.k // 128, 128)
+        return (v * self.scale[:, :self.rows].t().unsqueeze(-1)).reshape(self.rows, self.k)
+
+
+def fp8_act_quant(x: torch.Tensor, out: Optional[Fp8Act] = None, bn: Optional[int] = None) -> Fp8Act:
+    """Per-token, per-128-column e4m3 quantisation of bf16 rows (scale = amax / 448)."""
+    _chk(x, torch.bfloat16, "x")
+    rows, k = x.shape
+    if out is None:
+        bn = bn or min(pick_bn(rows), 128)
+        out = Fp8Act((rows + bn - 1) // bn * bn, k, x.device)
+    assert rows <= out.rows_pad and out.k == k
+    out.rows = rows
+    call("dgpp_fp8_act_quant", ptr(x), x.stride(0), ptr(out.q), ptr(out.scale), rows, out.rows_pad, k, stream_ptr())
+    return out
+
+
+def gemm_fp8(xa: Fp8Act, w: QuantLinear, out: Optional[torch.Tensor] = None, splits: Optional[int] = None) -> torch.Tensor:
+    """Block-scaled FP8 weights (128 x 128 blocks) x FP8 activations on tcgen05 kind::f8f6f4, scales promoted per K block."""
+    assert w.fmt == "fp8" and xa.k == w.k and w.alpha == 1.0
+    rows = xa.rows
+    bn = min(pick_bn(rows), 128)
+    while xa.rows_pad % bn:
+        bn //= 2
+    if out is None:
+        out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=xa.q.device)
+    if splits is None:
+        tiles = math.ceil(w.n / 128) * math.ceil(rows / bn)
+        splits = 1 if (tiles >= 96 or rows > 128) else max(1, min(148 // tiles, (w.k // 128) // 4, 8))
+    partial = None
+    if splits > 1:
+        partial = torch.empty(splits * rows * w.n, dtype=torch.float32, device=xa.q.device)
+    call("dgpp_gemm_fp8", ptr(w.payload), ptr(w.scale), ptr(xa.q), ptr(xa.scale), ptr(out), ptr(partial), out.stride(0), rows,
+         xa.rows_pad, w.n, w.k, bn, splits, stream_ptr())
+    return out
+
+
+def linear_fp8(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """FP8 linear end to end: quantise the rows, run the native FP8 GEMM."""
+    return gemm_fp8(fp8_act_quant(x), w, out=out)
+
+
 # ---------------------------------------------------------------------------------------------- gated delta net
 _lib.declare("dgpp_gdn_recurrent", [P, L, P, L, P, L, P, P, L, P, P, P, P, I, P, P, I, I, I, I, I, I, P])
 _lib.declare("dgpp_gdn_conv", [P, L, P, P, P, P, I, P, I, I, I, I, P])
