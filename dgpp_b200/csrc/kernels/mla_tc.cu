@@ -33,6 +33,9 @@ constexpr int kMtBlk = kMtTile * 128;   // 16 KB: one 64-element column block of
 
 struct MlaTcParams {
   const bf16* q;               // [rows, heads, dc + dr] absorbed query, rotary part rotated
+  const bf16* cache;           // [blocks, page, dc + dr] (the sparse form gathers rows itself)
+  const int32_t* sel;          // sparse form: [rows, sel_stride] selected token positions, ascending, -1 padded
+  int sel_stride;
   const int32_t* block_table;  // [requests, max_blocks]
   const int32_t* row_req;      // [rows]
   const int32_t* positions;    // [rows] position of the row's own token (already in the cache)
@@ -44,7 +47,10 @@ struct MlaTcParams {
   float scale;
 };
 
-template <int DC, int DR>
+// SPARSE: the tokens of a tile come from the row's selection list instead of consecutive positions; the four softmax
+// warps (idle while a tile loads: it is single buffered) gather them, thread = token: 72 16-byte chunks of the token's
+// latent row into the swizzled column blocks, then a proxy fence and one arrival per warp on the tile barrier.
+template <int DC, int DR, bool SPARSE>
 __global__ void __launch_bounds__(kMtThreads, 1)
 mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tmC, MlaTcParams p) {
   constexpr int D = DC + DR;
@@ -74,7 +80,18 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tmC, MlaTcParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, row = blockIdx.y, hg = blockIdx.z;
   const int req = p.row_req[row];
-  const int len = p.positions[row] + 1;
+  int len = p.positions[row] + 1;
+  const int32_t* sel = nullptr;
+  if (SPARSE) {
+    // listed tokens at or before the row's own position (lists are ascending, so they form a prefix of the list)
+    sel = p.sel + static_cast<size_t>(row) * p.sel_stride;
+    int n = 0;
+    for (int i0 = 0; i0 < p.sel_stride; i0 += kMtThreads) {
+      const int i = i0 + threadIdx.x;
+      n += __syncthreads_count(i < p.sel_stride && sel[i] >= 0 && sel[i] < len);
+    }
+    len = n;
+  }
   const int total_tiles = (len + kMtTile - 1) / kMtTile;
   const int per = (total_tiles + p.splits - 1) / p.splits;
   const int tile_begin = split * per;
@@ -83,7 +100,7 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tmC, MlaTcParams p) {
   const int nheads = min(kMtNQ, p.heads - hg * kMtNQ);
 
   if (threadIdx.x == 0) {
-    mbar_init(c_full, 1); mbar_init(c_empty, 1);
+    mbar_init(c_full, SPARSE ? 4 : 1); mbar_init(c_empty, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&o_full[i], 1); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -116,8 +133,8 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tmC, MlaTcParams p) {
   const uint32_t tmem_o = tmem_base + 64;    // 2 x MB x 32 columns
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
+    // ------------------------------------------------------------------ TMA producer (dense form)
+    if (!SPARSE && elect_one()) {
       const int ppt = kMtTile / p.page;
       for (int i = 0; i < ntiles; ++i) {
         if (!wait_bar(c_empty, (i & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 51); *abort_flag = 1; break; }
@@ -205,11 +222,50 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tmC, MlaTcParams p) {
     bool ok = true;
     for (int i = 0; i < ntiles; ++i) {
       const int b = i & 1;
+      const int t = (tile_begin + i) * kMtTile + idx;
+      const bool valid = t < len;
+      if (SPARSE) {
+        if (wait_bar(c_empty, (i & 1) ^ 1)) {
+          // a warp gathers its 32 tokens one after the other: lanes take the 72 chunks of a token's row in turns, so the
+          // row is read with coalesced 512-byte requests; four tokens are in flight at a time
+          const int my_tok = valid ? sel[t] : -1;
+#pragma unroll 1
+          for (int t4 = 0; t4 < 32; t4 += 4) {
+            uint4 v[4][3];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int tok = __shfl_sync(0xffffffffu, my_tok, t4 + u);
+              const uint4* src = tok >= 0 ? reinterpret_cast<const uint4*>(
+                                                p.cache + (static_cast<size_t>(bt[tok / p.page]) * p.page + tok % p.page) * D)
+                                          : nullptr;
+#pragma unroll
+              for (int j = 0; j < 3; ++j) {
+                const int c = lane + 32 * j;
+                v[u][j] = (src != nullptr && c < D / 8) ? src[c] : make_uint4(0u, 0u, 0u, 0u);   // unlisted rows: zeros (0 x NaN)
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int r = quad * 32 + t4 + u;
+#pragma unroll
+              for (int j = 0; j < 3; ++j) {
+                const int c = lane + 32 * j;
+                if (c < D / 8)
+                  *reinterpret_cast<uint4*>(sC + (c >> 3) * kMtBlk + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v[u][j];
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(c_full);
+        } else {
+          report(p.status, kTimeoutStageEmpty, 57);
+          *abort_flag = 1;
+        }
+      }
       bool okw = ok && wait_bar(&s_full[b], (i >> 1) & 1);
       if (!okw && ok) { report(p.status, kTimeoutAccum, 54); *abort_flag = 1; }
       tc_fence_after();
-      const int t = (tile_begin + i) * kMtTile + idx;
-      const bool valid = t < len;
       float s[kMtNQ];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -332,13 +388,13 @@ __global__ void mla_tc_combine_kernel(const float* __restrict__ part_ml, const f
 
 using namespace dgpp;
 
-// Dense absorbed latent attention on the tensor cores.  cache: [num_blocks, page, dc + dr] bf16 pages; q: [rows, heads,
+// Absorbed latent attention on the tensor cores, dense or over per-row selection lists (sel [rows, sel_stride] int32).  cache: [num_blocks, page, dc + dr] bf16 pages; q: [rows, heads,
 // dc + dr]; out: [rows, heads, dc].  dc = 512, dr = 64; page in {16, 32, 64, 128}.  Rows of a prefill chunk are simply
 // rows whose positions differ (the causal limit is the row's own position).
 DGPP_API int dgpp_mla_decode_tc(const void* q, const void* cache, const void* block_table, const void* row_req,
-                                const void* positions, void* part_ml, void* part_acc, void* out, int rows, int heads,
-                                int dc, int dr, int page, int max_blocks, int num_blocks, int splits, float scale,
-                                cudaStream_t st) {
+                                const void* positions, const void* sel, int sel_stride, void* part_ml, void* part_acc,
+                                void* out, int rows, int heads, int dc, int dr, int page, int max_blocks, int num_blocks,
+                                int splits, float scale, cudaStream_t st) {
   DGPP_REQUIRE(dc == 512 && dr == 64, "mla_decode_tc: latent geometry %d + %d (512 + 64 only)", dc, dr);
   DGPP_REQUIRE(page == 16 || page == 32 || page == 64 || page == 128, "mla_decode_tc: page %d unsupported", page);
   DGPP_REQUIRE(splits >= 1 && (splits == 1 || (part_ml && part_acc)), "mla_decode_tc: scratch required for splits");
@@ -346,6 +402,9 @@ DGPP_API int dgpp_mla_decode_tc(const void* q, const void* cache, const void* bl
   if (rows == 0) return 0;
   MlaTcParams p;
   p.q = static_cast<const bf16*>(q);
+  p.cache = static_cast<const bf16*>(cache);
+  p.sel = static_cast<const int32_t*>(sel);
+  p.sel_stride = sel_stride;
   p.block_table = static_cast<const int32_t*>(block_table);
   p.row_req = static_cast<const int32_t*>(row_req);
   p.positions = static_cast<const int32_t*>(positions);
@@ -365,12 +424,15 @@ DGPP_API int dgpp_mla_decode_tc(const void* q, const void* cache, const void* bl
   static_assert(smem <= 227 * 1024, "mla_decode_tc: shared memory over the per-CTA limit");
   static bool attr = false;
   if (!attr) {
-    DGPP_CUDA_OK(cudaFuncSetAttribute(mla_decode_tc_kernel<512, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    DGPP_CUDA_OK(cudaFuncSetAttribute(mla_decode_tc_kernel<512, 64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(smem)));
+    DGPP_CUDA_OK(cudaFuncSetAttribute(mla_decode_tc_kernel<512, 64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
     attr = true;
   }
   dim3 grid(splits, rows, dgpp_ceil_div(heads, kMtNQ));
-  mla_decode_tc_kernel<512, 64><<<grid, kMtThreads, smem, st>>>(tC, p);
+  if (sel) mla_decode_tc_kernel<512, 64, true><<<grid, kMtThreads, smem, st>>>(tC, p);
+  else mla_decode_tc_kernel<512, 64, false><<<grid, kMtThreads, smem, st>>>(tC, p);
   DGPP_CUDA_OK(cudaGetLastError());
   if (splits > 1) {
     mla_tc_combine_kernel<<<rows * heads, 256, 0, st>>>(p.part_ml, p.part_acc, p.out, splits, dc);

@@ -108,7 +108,7 @@ class MlaMoeModel:
             else:
                 L.gate_up, L.down = lin(2 * c.ffn, H), lin(H, c.ffn)
             if cfg.index_heads:
-                L.idx_q = quantize(rnd(c.index_heads * c.index_dim, H) * 4, "bf16")
+                L.idx_q = quantize(rnd(c.index_heads * c.index_dim, H) * 4, fmt)
                 L.idx_k = quantize(rnd(c.index_dim, H) * 4, "bf16")
                 L.idx_w = quantize(rnd(c.index_heads, H), "bf16")
             layers.append(L)
@@ -202,8 +202,10 @@ class MlaMoeRunner:
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor,
-                all_logits: bool = True) -> torch.Tensor:
-        """int32 [rows] device tensors -> fp32 logits [rows, V] (all_logits=False: of the last row only, [1, V])."""
+                all_logits: bool = True, select: bool = True) -> torch.Tensor:
+        """int32 [rows] device tensors -> fp32 logits [rows, V] (all_logits=False: of the last row only, [1, V]).
+        select=False (indexed models): the caller knows that no row's context exceeds the selection size, so every
+        token is selected and the dense attention kernel runs; the index keys are still appended."""
         m, c = self.m, self.c
         rows = tokens.shape[0]
         x = torch.empty(rows, c.hidden, dtype=BF, device=self.dev)
@@ -222,6 +224,7 @@ class MlaMoeRunner:
             sel = None
             if L.idx_q is not None:
                 self._append(self.kidx[i], ops.linear(xn, L.idx_k), row_req, positions)
+            if L.idx_q is not None and select:
                 qi = ops.linear(xn, L.idx_q).view(rows, c.index_heads, c.index_dim)
                 wi = ops.linear(xn, L.idx_w).float().contiguous()
                 sc = ops.dsa_index(qi, wi, self.kidx[i], self.block_table, row_req, positions, self.max_ctx,
@@ -257,7 +260,7 @@ class MlaMoeRunner:
             t = torch.tensor(part, dtype=torch.int32, device=self.dev)
             pos = torch.arange(start + o, start + o + len(part), dtype=torch.int32, device=self.dev)
             req = torch.full((len(part),), slot, dtype=torch.int32, device=self.dev)
-            out = self.forward(t, pos, req, all_logits=False)
+            out = self.forward(t, pos, req, all_logits=False, select=start + o + len(part) > self.c.index_topk)
         self.lengths[slot] = start + len(tokens)
         return out
 
@@ -266,15 +269,17 @@ class MlaMoeRunner:
         position / request tensors and replayed (a pass is hundreds of small launches; replay removes the host's
         launch cost from every step); `use_graphs = False` launches kernel by kernel."""
         b = len(slots)
+        select = bool(self.c.index_heads) and max(positions) + 1 > self.c.index_topk
         host = torch.tensor([tokens, positions, slots], dtype=torch.int32)
         if not (self.use_graphs and torch.device(self.dev).type == "cuda"):
             d = host.to(self.dev)
-            return self.forward(d[0], d[1], d[2])
-        st = self._static.get(b)
+            return self.forward(d[0], d[1], d[2], select=select)
+        key = (b, select)
+        st = self._static.get(key)
         if st is None:
-            st = self._static[b] = torch.zeros(3, b, dtype=torch.int32, device=self.dev)
+            st = self._static[key] = torch.zeros(3, b, dtype=torch.int32, device=self.dev)
         st.copy_(host, non_blocking=True)
-        g = self._graphs.get(b)
+        g = self._graphs.get(key)
         if g is None:
             # warm-up outside capture (lazy kernel attributes, workspaces); state-carrying layers are advanced by it,
             # so their state is saved before and put back after: only replays move the model forward
@@ -282,15 +287,15 @@ class MlaMoeRunner:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                self.forward(st[0], st[1], st[2])
+                self.forward(st[0], st[1], st[2], select=select)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                out = self.forward(st[0], st[1], st[2])
+                out = self.forward(st[0], st[1], st[2], select=select)
             for t, s0 in zip(self._state_tensors(), saved):
                 t.copy_(s0)
-            g = self._graphs[b] = (graph, out)
+            g = self._graphs[key] = (graph, out)
         graph, out = g
         graph.replay()
         return out

@@ -578,6 +578,44 @@ def gemm_fp4_grouped(xa: "QuantAct", wq, wsf_tiled, alphas, out, rows: int, n: i
     return out
 
 
+# ---------------------------------------------------------------------------------------------- table routing, Hadamard-32
+_lib.declare("dgpp_moe_hash_routes", [P, P, P, P, P, I, I, I, I, F, I, P])
+_lib.declare("dgpp_hadamard32_rows", [P, L, P, L, I, I, I, P])
+_lib.declare("dgpp_hadamard32_quant_int8", [P, L, P, L, P, L, I, I, I, P])
+
+
+def moe_hash_routes(tokens, tid2eid, scores, scaling: float = 1.0, norm_topk: bool = True):
+    """Table routing: ids[t] = tid2eid[tokens[t]] ([vocab, k] int32, ascending per row), weights from `scores` [T, E] fp32."""
+    T, E = scores.shape
+    vocab, k = tid2eid.shape
+    ids = torch.empty(T, k, dtype=torch.int32, device=scores.device)
+    w = torch.empty(T, k, dtype=torch.float32, device=scores.device)
+    call("dgpp_moe_hash_routes", ptr(tokens), ptr(tid2eid), ptr(scores), ptr(ids), ptr(w), T, vocab, E, k, float(scaling),
+         int(norm_topk), stream_ptr())
+    return ids, w
+
+
+def hadamard32_rows(x: torch.Tensor, out: Optional[torch.Tensor] = None, period: int = 0) -> torch.Tensor:
+    """Normalised block-32 Walsh-Hadamard rotation of bf16 rows (in place when out is x); rows r with
+    r % period == period - 1 are not touched (period 0: all rows)."""
+    _chk(x, torch.bfloat16, "x")
+    if out is None:
+        out = torch.empty_like(x) if period == 0 else x.clone()
+    call("dgpp_hadamard32_rows", ptr(x), x.stride(0), ptr(out), out.stride(0), x.shape[0], x.shape[1], period, stream_ptr())
+    return out
+
+
+def hadamard32_quant_int8(x: torch.Tensor, period: int = 0):
+    """Rotated rows as int8 codes [rows, K] + fp32 scales [rows, K / 128] (skipped rows keep zeros)."""
+    _chk(x, torch.bfloat16, "x")
+    rows, k = x.shape
+    codes = torch.zeros(rows, k, dtype=torch.int8, device=x.device)
+    scales = torch.zeros(rows, k // 128, dtype=torch.float32, device=x.device)
+    call("dgpp_hadamard32_quant_int8", ptr(x), x.stride(0), ptr(codes), codes.stride(0), ptr(scales), scales.stride(0), rows, k,
+         period, stream_ptr())
+    return codes, scales
+
+
 # ---------------------------------------------------------------------------------------------- native FP8 linear
 _lib.declare("dgpp_fp8_act_quant", [P, L, P, P, I, I, I, P])
 _lib.declare("dgpp_gemm_fp8", [P, P, P, P, P, P, I, I, I, I, I, I, I, P])
@@ -735,7 +773,7 @@ def gated_rmsnorm(o, z, w, out, heads: int, d: int, eps: float = 1e-6):
 
 # ---------------------------------------------------------------------------------------------- latent attention
 _lib.declare("dgpp_mla_decode", [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P])
-_lib.declare("dgpp_mla_decode_tc", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
+_lib.declare("dgpp_mla_decode_tc", [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P])
 _lib.declare("dgpp_dsa_index", [P, P, P, P, P, P, P, I, I, I, I, I, I, P])
 _lib.declare("dgpp_topk_select", [P, L, P, P, I, I, P])
 
@@ -744,8 +782,8 @@ def mla_decode(q, cache, block_table, row_req, positions, scale: float, dc: int,
                out=None, tensor_cores: Optional[bool] = None):
     """Absorbed multi-head latent attention.  q: [rows, heads, dc + dr] bf16; cache: [blocks, page, dc + dr] bf16;
     sel: optional [rows, n_sel] int32 selected token positions (ascending, -1 padded) for sparse attention.
-    Returns the latent outputs [rows, heads, dc] bf16.  The dense form at the 512 + 64 geometry runs on the tensor
-    cores (tensor_cores=False keeps the CUDA-core kernel, which is also the sparse path)."""
+    Returns the latent outputs [rows, heads, dc] bf16.  The 512 + 64 geometry runs on the tensor cores, dense or sparse
+    (tensor_cores=False keeps the CUDA-core kernel)."""
     rows, heads, _ = q.shape
     dev = q.device
     if out is None:
@@ -755,12 +793,11 @@ def mla_decode(q, cache, block_table, row_req, positions, scale: float, dc: int,
         ml = torch.empty(rows * heads * splits * 2, dtype=torch.float32, device=dev)
         acc = torch.empty(rows * heads * splits * dc, dtype=torch.float32, device=dev)
     if tensor_cores is None:
-        tensor_cores = sel is None and dc == 512 and dr == 64 and cache.shape[1] in (16, 32, 64, 128)
+        tensor_cores = dc == 512 and dr == 64 and cache.shape[1] in (16, 32, 64, 128)
     if tensor_cores:
-        assert sel is None, "the tensor-core latent attention kernel is dense"
-        call("dgpp_mla_decode_tc", ptr(q), ptr(cache), ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc),
-             ptr(out), rows, heads, dc, dr, cache.shape[1], block_table.shape[1], cache.shape[0], splits, float(scale),
-             stream_ptr())
+        call("dgpp_mla_decode_tc", ptr(q), ptr(cache), ptr(block_table), ptr(row_req), ptr(positions), ptr(sel),
+             0 if sel is None else sel.shape[1], ptr(ml), ptr(acc), ptr(out), rows, heads, dc, dr, cache.shape[1],
+             block_table.shape[1], cache.shape[0], splits, float(scale), stream_ptr())
         return out
     call("dgpp_mla_decode", ptr(q), ptr(cache), ptr(block_table), ptr(row_req), ptr(positions), ptr(sel),
          0 if sel is None else sel.shape[1], ptr(ml), ptr(acc), ptr(out), rows, heads, dc, dr, cache.shape[1],
@@ -801,12 +838,23 @@ def mla_v_up(lat, w_uv, out=None):
     return out
 
 
-def dsa_index(q_idx, w_idx, k_idx, block_table, row_req, positions, max_ctx: int, scores=None):
+_lib.declare("dgpp_dsa_index_tc", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P])
+
+
+def dsa_index(q_idx, w_idx, k_idx, block_table, row_req, positions, max_ctx: int, scores=None,
+              tensor_cores: Optional[bool] = None):
     """Lightning-indexer scores [rows, max_ctx] fp32 (-inf beyond each row's position).
-    q_idx: [rows, hi, di] bf16, w_idx: [rows, hi] fp32, k_idx: paged [blocks, page, di] bf16."""
+    q_idx: [rows, hi, di] bf16, w_idx: [rows, hi] fp32, k_idx: paged [blocks, page, di] bf16.
+    Index dims of 128 with up to 64 heads run on the tensor cores (tensor_cores=False: the CUDA-core kernel)."""
     rows, hi, di = q_idx.shape
     if scores is None:
         scores = torch.empty(rows, max_ctx, dtype=torch.float32, device=q_idx.device)
+    if tensor_cores is None:
+        tensor_cores = di == 128 and hi <= 64 and k_idx.shape[1] in (16, 32, 64, 128)
+    if tensor_cores:
+        call("dgpp_dsa_index_tc", ptr(q_idx), ptr(w_idx), ptr(k_idx), ptr(block_table), ptr(row_req), ptr(positions),
+             ptr(scores), rows, hi, di, k_idx.shape[1], block_table.shape[1], k_idx.shape[0], scores.shape[1], stream_ptr())
+        return scores
     call("dgpp_dsa_index", ptr(q_idx), ptr(w_idx), ptr(k_idx), ptr(block_table), ptr(row_req), ptr(positions),
          ptr(scores), rows, hi, di, k_idx.shape[1], block_table.shape[1], scores.shape[1], stream_ptr())
     return scores

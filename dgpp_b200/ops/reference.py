@@ -149,3 +149,36 @@ def attention(q, k, v, scale, causal_offset: Optional[int] = None, window: int =
     else:
         p = torch.softmax(s, -1)
     return torch.einsum("hqk,khd->qhd", p, vv)
+
+
+def hadamard32(x: torch.Tensor) -> torch.Tensor:
+    """Oracle of ops.hadamard32_rows: five butterfly stages at strides 1, 2, 4, 8, 16 in fp32 (element j takes
+    v_j + v_{j^s} when bit s of j is clear, v_{j^s} - v_j when set), times fp32(1 / sqrt(32)), one bf16 rounding."""
+    rows, k = x.shape
+    v = x.float().view(rows, k // 32, 32).clone()
+    j = torch.arange(32, device=x.device)
+    for s in (1, 2, 4, 8, 16):
+        o = v[..., j ^ s]
+        v = torch.where((j & s) != 0, o - v, v + o)
+    return (v * torch.tensor(0.17677669529663687, dtype=torch.float32, device=x.device)).to(torch.bfloat16).view(rows, k)
+
+
+def hadamard32_quant_int8(x: torch.Tensor):
+    """Oracle of ops.hadamard32_quant_int8: rotated bf16 values, per 128: scale = max(amax / 127, 1e-30), rint codes."""
+    rows, k = x.shape
+    r = hadamard32(x).float().view(rows, k // 128, 128)
+    sc = (r.abs().amax(-1) / 127.0).clamp_min(1e-30)
+    codes = torch.clamp(torch.round(r / sc.unsqueeze(-1)), -128, 127).to(torch.int8).view(rows, k)
+    return codes, sc
+
+
+def moe_hash_routes(tokens, tid2eid, scores, scaling: float = 1.0, norm_topk: bool = True):
+    """Oracle of ops.moe_hash_routes."""
+    ids = tid2eid[tokens.long().clamp(0, tid2eid.shape[0] - 1)].long()
+    w = scores.gather(1, ids)
+    if norm_topk:
+        denom = torch.zeros(w.shape[0], dtype=torch.float32, device=w.device)
+        for i in range(w.shape[1]):
+            denom = denom + w[:, i]
+        w = w / (denom + 1e-20).unsqueeze(-1)
+    return ids.to(torch.int32), w * scaling

@@ -1,0 +1,56 @@
+"""Table routing and the block-32 Hadamard rotation (plain and int8-coded) against their PyTorch oracles, bit for bit."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda:0")
+
+
+def test_hadamard32_rows_bitwise_and_involution(dev):
+    from dgpp_b200.ops import core as ops, reference as ref
+
+    torch.manual_seed(1)
+    x = (torch.randn(21, 1024, device=dev) * 3).to(BF)
+    got = ops.hadamard32_rows(x)
+    assert torch.equal(got, ref.hadamard32(x))
+    # H32 / sqrt(32) is its own inverse (up to the two bf16 roundings)
+    back = ops.hadamard32_rows(got)
+    assert (back.float() - x.float()).abs().max().item() <= 0.05 * x.float().abs().max().item()
+    # decode slot layout: every (period)-th row keeps its staged content
+    y = ops.hadamard32_rows(x, period=3)
+    want = ref.hadamard32(x)
+    skip = torch.arange(21, device=dev) % 3 == 2
+    assert torch.equal(y[skip], x[skip]) and torch.equal(y[~skip], want[~skip])
+
+
+def test_hadamard32_int8_codes_bitwise(dev):
+    from dgpp_b200.ops import core as ops, reference as ref
+
+    torch.manual_seed(2)
+    x = (torch.randn(9, 512, device=dev) * torch.rand(9, 1, device=dev) * 10).to(BF)
+    x[4] = 0
+    codes, scales = ops.hadamard32_quant_int8(x)
+    wc, ws = ref.hadamard32_quant_int8(x)
+    assert torch.equal(scales, ws) and torch.equal(codes, wc)
+
+
+def test_moe_hash_routes(dev):
+    from dgpp_b200.ops import core as ops, reference as ref
+
+    torch.manual_seed(3)
+    T, E, k, vocab = 50, 64, 6, 300
+    tid2eid = torch.stack([torch.sort(torch.randperm(E, device=dev)[:k]).values for _ in range(vocab)]).to(torch.int32)
+    tokens = torch.randint(0, vocab, (T,), device=dev, dtype=torch.int32)
+    tokens[7] = -1                                   # padding rows read table row 0
+    scores = torch.sigmoid(torch.randn(T, E, device=dev))
+    for norm in (True, False):
+        ids, w = ops.moe_hash_routes(tokens, tid2eid, scores, scaling=2.5, norm_topk=norm)
+        wi, ww = ref.moe_hash_routes(tokens, tid2eid, scores, scaling=2.5, norm_topk=norm)
+        assert torch.equal(ids, wi) and torch.allclose(w, ww, rtol=1e-6, atol=0)

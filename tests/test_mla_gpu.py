@@ -75,6 +75,17 @@ def test_mla_decode_tensor_cores(dev, heads, page, splits, ctxs):
         want = mla_reference(q[r], gather_rows(cache, table[r], n), scale, dc)
         assert (out[r].float() - want).abs().max().item() < 1.5e-2, (r, n)
     assert (out.float() - base.float()).abs().max().item() < 2e-2
+    # sparse form: the softmax warps gather the listed tokens themselves
+    from dgpp_b200.models.mla import topk_reference
+    k = 200
+    sc = torch.randn(len(ctxs), max(ctxs), device=dev)
+    sel = torch.stack([topk_reference(sc[r, :n], k) for r, n in enumerate(ctxs)]).contiguous()
+    out = ops.mla_decode(q, cache, table, row_req, pos, scale, dc, dr, sel=sel, splits=min(splits, 2), tensor_cores=True)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for r, n in enumerate(ctxs):
+        want = mla_reference(q[r], gather_rows(cache, table[r], n), scale, dc, sel=sel[r])
+        assert (out[r].float() - want).abs().max().item() < 1.5e-2, ("sparse", r, n)
 
 
 def test_indexer_scores_and_topk(dev):
@@ -88,12 +99,14 @@ def test_indexer_scores_and_topk(dev):
     w = torch.rand(3, hi, device=dev)
     row_req = torch.tensor([0, 1, 2], dtype=torch.int32, device=dev)
     pos = torch.tensor([c - 1 for c in ctxs], dtype=torch.int32, device=dev)
-    scores = ops.dsa_index(q, w, kidx, table, row_req, pos, max(ctxs))
-    torch.cuda.synchronize()
-    for r, n in enumerate(ctxs):
-        want = index_scores_reference(q[r], w[r], gather_rows(kidx, table[r], n))
-        assert torch.allclose(scores[r, :n], want, rtol=2e-3, atol=2e-2)
-        assert torch.isinf(scores[r, n:]).all()
+    for tc in (False, True):                     # CUDA-core kernel, then the tcgen05 kernel (tiles of 128 tokens)
+        scores = ops.dsa_index(q, w, kidx, table, row_req, pos, max(ctxs), tensor_cores=tc)
+        torch.cuda.synchronize()
+        ops.check_status()
+        for r, n in enumerate(ctxs):
+            want = index_scores_reference(q[r], w[r], gather_rows(kidx, table[r], n))
+            assert torch.allclose(scores[r, :n], want, rtol=2e-3, atol=2e-2), (tc, r)
+            assert torch.isinf(scores[r, n:]).all(), (tc, r)
     # ties: quantise the scores so that equal values exist
     scores = (scores * 2).round() / 2
     k = 512
