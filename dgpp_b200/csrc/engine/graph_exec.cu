@@ -139,3 +139,99 @@ DGPP_API int dgpp_graph_destroy(void* handle) {
   delete g;
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Native decode loop: replays one captured decode-step graph `steps` times with at most `inflight` (1..4) steps
+// outstanding.  The step graph feeds itself on the device (its last kernel writes the picked ids where its first kernel
+// reads the input ids), so the host never sits between two steps.  After every replay the step's picked ids and the
+// device status block are copied into a pinned mailbox slot and an event is recorded; the host retires the slots in
+// order: ids go to `out[step * b ..]`, rows that produced one of `stop_ids` are marked, a non-zero status code ends the
+// loop with an error.  Once every row is marked no further step is launched; steps already in flight are drained and
+// their ids dropped.  Returns 0, or -1 with dgpp_last_error() set (status code / CUDA error).
+//   d_tokens   device int32 [>= b]: the step graph's token mailbox (input of the next step = output of this one)
+//   out        host int32 [steps * b]; row_stop host int32 [b]: index of the step at which the row stopped, or -1
+//   steps_run  host int [2]: steps whose ids were delivered to `out`, steps launched (the device state advanced that far)
+// (behavioural spec: src/engine/graph_engine.hpp:2860-2995 launch / settle_front with two replays in flight.)
+namespace dgpp { DeviceStatus* device_status_ptr(); }
+
+namespace {
+
+struct Mailbox {
+  int32_t* host = nullptr;     // pinned [slots][kMaxBatch + 4]
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  int dev = -1;
+};
+constexpr int kLoopMaxBatch = 512;
+
+static Mailbox* mailbox() {
+  static thread_local Mailbox mb;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (mb.host && mb.dev == dev) return &mb;
+  if (mb.host) {
+    cudaFreeHost(mb.host);
+    for (auto& e : mb.ev) if (e) { cudaEventDestroy(e); e = nullptr; }
+    mb.host = nullptr;
+  }
+  if (cudaHostAlloc(reinterpret_cast<void**>(&mb.host), 4 * (kLoopMaxBatch + 4) * sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess)
+    return nullptr;
+  for (auto& e : mb.ev)
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  mb.dev = dev;
+  return &mb;
+}
+
+}  // namespace
+
+DGPP_API int dgpp_decode_loop(void* graph, const void* d_tokens, int b, int steps, int inflight, const int32_t* stop_ids,
+                              int n_stop, int32_t* out, int32_t* row_stop, int* steps_run, cudaStream_t st) {
+  GraphExec* g = static_cast<GraphExec*>(graph);
+  DGPP_REQUIRE(g && g->exec, "decode_loop: empty graph handle");
+  DGPP_REQUIRE(b >= 1 && b <= kLoopMaxBatch && steps >= 0 && inflight >= 1 && inflight <= 4, "decode_loop: bad sizes (b %d inflight %d)",
+               b, inflight);
+  Mailbox* mb = mailbox();
+  DGPP_REQUIRE(mb != nullptr, "decode_loop: pinned mailbox allocation failed");
+  dgpp::DeviceStatus* status = dgpp::device_status_ptr();
+  DGPP_REQUIRE(status != nullptr, "decode_loop: no status block");
+  const int stride = kLoopMaxBatch + 4;
+  for (int r = 0; r < b; ++r) row_stop[r] = -1;
+  int launched = 0, retired = 0, delivered = 0, live = b;
+  bool stop_launching = false;
+  while (retired < launched || (!stop_launching && launched < steps)) {
+    while (!stop_launching && launched < steps && launched - retired < inflight) {
+      const int slot = launched % 4;
+      DGPP_CUDA_OK(cudaGraphLaunch(g->exec, st));
+      DGPP_CUDA_OK(cudaMemcpyAsync(mb->host + slot * stride, d_tokens, b * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+      DGPP_CUDA_OK(cudaMemcpyAsync(mb->host + slot * stride + kLoopMaxBatch, status, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+      DGPP_CUDA_OK(cudaEventRecord(mb->ev[slot], st));
+      ++launched;
+    }
+    if (retired < launched) {
+      const int slot = retired % 4;
+      DGPP_CUDA_OK(cudaEventSynchronize(mb->ev[slot]));
+      const int32_t* ids = mb->host + slot * stride;
+      const int32_t* stt = ids + kLoopMaxBatch;
+      if (stt[0] != 0) {
+        cudaStreamSynchronize(st);
+        steps_run[0] = delivered;
+        steps_run[1] = launched;
+        dgpp_set_error("decode_loop: device status code=%d count=%d detail=%d at step %d", stt[0], stt[1], stt[2], retired);
+        return -1;
+      }
+      if (!stop_launching) {
+        for (int r = 0; r < b; ++r) {
+          out[static_cast<size_t>(retired) * b + r] = ids[r];
+          if (row_stop[r] < 0)
+            for (int k = 0; k < n_stop; ++k)
+              if (ids[r] == stop_ids[k]) { row_stop[r] = retired; --live; break; }
+        }
+        ++delivered;
+        if (live == 0) stop_launching = true;
+      }
+      ++retired;
+    }
+  }
+  steps_run[0] = delivered;
+  steps_run[1] = launched;
+  return 0;
+}

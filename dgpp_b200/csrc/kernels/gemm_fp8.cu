@@ -8,7 +8,10 @@
 // block (128 columns = four MMA k-steps) is accumulated in TMEM without scales; the epilogue warps then read it and add
 // it, scaled by the block's two scales, to fp32 registers ("promotion") while the tensor core already works on the next
 // block in the other TMEM buffer.  Nothing converts the e4m3 bytes: HBM -> TMA -> shared memory -> tensor core.
-// Warps: 0 = TMA producer, 1 = MMA issuer / TMEM owner, 2..5 = promotion + store.  Bounded waits throughout.
+// Warps: 0 = TMA producer (tiles + the block's activation scales, which ride a ring twice as deep as the tile ring:
+// an epilogue may still read them after the MMAs have released the tile stage), 1 = MMA issuer / TMEM owner, 2..5 and
+// 6..9 = two promotion sets, each covering all 128 weight rows and half of the token columns (token tiles of 16 use
+// one set).  Bounded waits throughout.
 // Split K (grid z): fp32 partials [z][T][N], folded in ascending z by fp8_splitk_fold_kernel.
 // (reference counterparts: src/kernels/fp8_gemm.cu:23-111 activation quantisers, :199 fp8_gemm_kernel with in-loop
 //  promotion, src/kernels/scale_gemm.cu block-scaled FP8 weights.)
@@ -23,7 +26,7 @@
 
 namespace dgpp {
 
-constexpr int kF8Threads = 192;
+constexpr int kF8Threads = 320;   // TMA warp, MMA warp, two epilogue sets of four warps
 constexpr int kF8BM = 128;      // weight rows per tile
 constexpr int kF8BK = 128;      // K columns per scale block = bytes per tile row
 
@@ -65,10 +68,14 @@ __global__ void __launch_bounds__(kF8Threads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, F8Params p) {
   constexpr int kABytes = kF8BM * kF8BK, kBBytes = BN * kF8BK;
   constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr int kSets = BN >= 32 ? 2 : 1;        // promotion sets in use
+  constexpr int CH = BN / kSets;                 // token columns per set
+  constexpr int kXsSlots = 2 * STAGES;
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   unsigned char* sp = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* sA = sp;  sp += STAGES * kABytes;
   unsigned char* sB = sp;  sp += STAGES * kBBytes;
+  float* sXs = reinterpret_cast<float*>(sp);  sp += kXsSlots * BN * sizeof(float);
   uint64_t* full = reinterpret_cast<uint64_t*>(sp);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;   // [2]
@@ -85,7 +92,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4 * kSets); }
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmW);
@@ -107,10 +114,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       for (int i = 0; i < nkb; ++i) {
         const int s = i % STAGES;
         if (!wait_bar(&empty[s], ((i / STAGES) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 61); *abort_flag = 1; break; }
-        mbar_expect_tx(&full[s], kABytes + kBBytes);
+        mbar_expect_tx(&full[s], kABytes + kBBytes + BN * sizeof(float));
         tma_load_2d(sA + s * kABytes, &tmW, (kb0 + i) * kF8BK, n0, &full[s]);
         if (!waited) { pdl_wait(); waited = true; }
         tma_load_2d(sB + s * kBBytes, &tmX, (kb0 + i) * kF8BK, t0, &full[s]);
+        bulk_load_1d(sXs + (i % kXsSlots) * BN, p.xs + static_cast<size_t>(kb0 + i) * p.T_pad + t0, BN * sizeof(float), &full[s]);
         if (*abort_flag) break;
       }
     }
@@ -132,14 +140,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         if (*abort_flag) break;
       }
     }
-  } else {
+  } else if ((warp - 2) / 4 < kSets) {
     pdl_wait();
+    const int set = (warp - 2) / 4;
     const int quad = warp & 3;
     const int row = quad * 32 + lane;                    // weight row inside the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    float acc[BN];
+    const int col0 = set * CH;
+    float acc[CH];
 #pragma unroll
-    for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+    for (int c = 0; c < CH; ++c) acc[c] = 0.f;
     const float* wsr = p.ws + static_cast<size_t>(blockIdx.x) * KB;
     bool ok = true;
     for (int i = 0; i < nkb && ok; ++i) {
@@ -147,11 +157,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       if (!wait_bar(&acc_full[b], (i >> 1) & 1)) { report(p.status, kTimeoutAccum, 64); *abort_flag = 1; ok = false; break; }
       tc_fence_after();
       const float wsc = wsr[kb];
-      const float* xsr = p.xs + static_cast<size_t>(kb) * p.T_pad + t0;
+      const float* xsr = sXs + (i % kXsSlots) * BN + col0;
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+      for (int c0 = 0; c0 < CH; c0 += 16) {
         uint32_t raw[16];
-        tmem_ld_x16(tmem_base + b * BN + c0 + lane_addr, raw);
+        tmem_ld_x16(tmem_base + b * BN + col0 + c0 + lane_addr, raw);
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 16; ++c) acc[c0 + c] = fmaf(__uint_as_float(raw[c]), wsc * xsr[c0 + c], acc[c0 + c]);
@@ -164,13 +174,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     if (ok && n < p.N) {
       if (p.splits == 1) {
 #pragma unroll
-        for (int c = 0; c < BN; ++c)
-          if (t0 + c < p.T) p.out[static_cast<size_t>(t0 + c) * p.ldc + n] = f32_to_bf16(acc[c]);
+        for (int c = 0; c < CH; ++c)
+          if (t0 + col0 + c < p.T) p.out[static_cast<size_t>(t0 + col0 + c) * p.ldc + n] = f32_to_bf16(acc[c]);
       } else {
         float* dst = p.partial + static_cast<size_t>(z) * p.T * p.N;
 #pragma unroll
-        for (int c = 0; c < BN; ++c)
-          if (t0 + c < p.T) dst[static_cast<size_t>(t0 + c) * p.N + n] = acc[c];
+        for (int c = 0; c < CH; ++c)
+          if (t0 + col0 + c < p.T) dst[static_cast<size_t>(t0 + col0 + c) * p.N + n] = acc[c];
       }
     }
   }
@@ -191,7 +201,7 @@ __global__ void fp8_splitk_fold_kernel(const float* __restrict__ partial, bf16* 
 
 template <int BN, int STAGES>
 static int launch_f8(const CUtensorMap& tW, const CUtensorMap& tX, const F8Params& p, cudaStream_t st) {
-  constexpr size_t smem = 1024 + STAGES * (kF8BM * kF8BK + BN * kF8BK) + (2 * STAGES + 4) * 8 + 64;
+  constexpr size_t smem = 1024 + STAGES * (kF8BM * kF8BK + BN * kF8BK) + 2 * STAGES * BN * 4 + (2 * STAGES + 4) * 8 + 64;
   static_assert(smem <= 227 * 1024, "gemm_fp8: shared memory over the per-CTA limit");
   static bool attr = false;
   if (!attr) {

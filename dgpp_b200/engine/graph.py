@@ -33,6 +33,20 @@ class NativeGraph:
     def replay(self) -> None:
         call("dgpp_graph_launch", self.handle, torch.cuda.current_stream().cuda_stream)
 
+    def decode_loop(self, d_tokens: torch.Tensor, b: int, steps: int, inflight: int = 2, stop_ids=()):
+        """Native step loop (csrc/engine/graph_exec.cu dgpp_decode_loop): `steps` replays with at most `inflight`
+        outstanding, ids and the device status read back per step through a pinned mailbox, rows watched for stop ids.
+        Returns (ids as a [delivered, b] int32 tensor on the host, per-row stop step or -1, steps launched)."""
+        from ..ops._lib import I, ptr
+        _lib.declare("dgpp_decode_loop", [P, P, I, I, I, P, I, P, P, P, P])
+        out = torch.zeros(max(steps, 1), b, dtype=torch.int32)
+        row_stop = torch.zeros(b, dtype=torch.int32)
+        ran = (C.c_int * 2)()
+        stops = (C.c_int32 * max(len(stop_ids), 1))(*stop_ids)
+        call("dgpp_decode_loop", self.handle, ptr(d_tokens), b, steps, inflight, C.cast(stops, P), len(stop_ids),
+             out.data_ptr(), row_stop.data_ptr(), C.cast(ran, P), torch.cuda.current_stream().cuda_stream)
+        return out[:ran[0]], row_stop.tolist(), ran[1]
+
     def __del__(self):
         try:
             if getattr(self, "handle", None):

@@ -186,9 +186,12 @@ class LLMEngine:
 
     @torch.no_grad()
     def generate(self, prompts: List[List[int]], max_tokens: int = 32, stream_tokens: bool = False,
-                 timings: Optional[dict] = None) -> List[List[int]]:
+                 timings: Optional[dict] = None, native_loop: bool = False, stop_ids=(), inflight: int = 2) -> List[List[int]]:
         """Greedy generation for up to max_batch prompts.  With `stream_tokens` every step's ids are read
-        back through pinned memory before the next step is launched (what a streaming server does)."""
+        back through pinned memory before the next step is launched (what a streaming server does).
+        native_loop: the step loop runs in the native executor (no per-token Python): up to `inflight` graph replays
+        outstanding, ids and device status read back per step, rows watched for `stop_ids` (a row's output ends with
+        its stop id; the loop ends when every row has stopped)."""
         b = len(prompts)
         assert 1 <= b <= self.max_batch
         for s in range(b):
@@ -206,7 +209,14 @@ class LLMEngine:
         self.start_decode(list(range(b)), firsts)
         steps = max_tokens - 1
         t1 = time.perf_counter()
-        if stream_tokens and self.h_step_out is not None:
+        if native_loop and self.use_graphs and self.dev.type == "cuda" and steps > 0:
+            ids, row_stop, launched = self._graph(b).decode_loop(self.d_tokens, b, steps, inflight, tuple(stop_ids))
+            ids = ids.tolist()
+            for s in range(b):
+                last = row_stop[s] if row_stop[s] >= 0 else len(ids) - 1
+                out[s] += [ids[i][s] for i in range(last + 1)]
+            steps = launched            # the device bookkeeping advanced once per launched step
+        elif stream_tokens and self.h_step_out is not None:
             # host-owned token stream: each step's input ids go host -> device from pinned memory (the host
             # may have rewritten them, e.g. grammar or stop handling), the picked ids come back the same way
             for s in range(b):
