@@ -103,6 +103,25 @@ def main() -> int:
             xs = [torch.empty_like(x) for _ in range(world)]; dist.all_gather(xs, x)
             ident = all(torch.equal(xs[0], q) for q in xs)
             say(f"rs_ag T={T} rep={rep}: matches fold={ok} identical across ranks={ident} maxdiff={(x.float()-want.float()).abs().max().item():.4f}", ok=ok and ident)
+        # sequence-parallel boundary: fold + residual + RMSNorm at the owner, normed rows all-gathered INTO the next GEMM
+        nw = (1 + 0.1 * torch.randn(5120, device=dev, generator=torch.Generator(device=dev).manual_seed(3))).to(BF)
+        torch.manual_seed(300)
+        w2 = random_quant_linear(1024, 5120, "nvfp4", dev)
+        bn0 = ops.pick_bn(T)
+        y_want = ops.gemm_tc(ops.rmsnorm(want, nw, 1e-6), w2, bn=bn0, splits=1)
+        tiles = (T + bn0 - 1) // bn0
+        tpr = (tiles + world - 1) // world
+        r0, r1 = min(rank * tpr, tiles) * bn0, min(min((rank + 1) * tpr, tiles) * bn0, T)
+        for rep in range(2):
+            x = x0.clone()
+            bn = ops.gemm_tc_push(a, w, red.comm)
+            red.rs_norm_push(x, nw, 1e-6, bn)
+            y = ops.gemm_tc_ag(w2, red.comm, T, bn=bn)
+            torch.cuda.synchronize(); ops.check_status()
+            ok_y = torch.equal(y, y_want)
+            ok_x = torch.equal(x[r0:r1], want[r0:r1])
+            say(f"rs_norm_push + ag GEMM T={T} rep={rep}: GEMM output == unfused={ok_y} own residual rows == fold={ok_x} "
+                f"maxdiff={(y.float() - y_want.float()).abs().max().item():.4f}", ok=ok_y and ok_x)
         # mixed with the one-shot all-reduce (shared epoch / slots)
         y = part.clone(); red.all_reduce(y); torch.cuda.synchronize(); ops.check_status()
     # timing: GEMM + all_reduce vs GEMM-push + rs_ag at a prefill chunk
@@ -113,14 +132,23 @@ def main() -> int:
     d = torch.empty(T, 5120, device=dev, dtype=BF)
     def unfused():
         ops.gemm_tc(a, w, out=d); red.all_reduce(d)
+    nw = torch.ones(5120, device=dev, dtype=BF)
+    w2 = random_quant_linear(2048, 5120, "nvfp4", dev)
+    d2 = torch.empty(T, 2048, device=dev, dtype=BF)
+    xn = torch.empty(T, 5120, device=dev, dtype=BF)
     def fused():
         red.rs_ag(x, ops.gemm_tc_push(a, w, red.comm))
+    def fused_next():
+        red.rs_ag(x, ops.gemm_tc_push(a, w, red.comm)); ops.rmsnorm(x, nw, 1e-6, out=xn); ops.gemm_tc(xn, w2, out=d2)
+    def seqpar_next():
+        bn = ops.gemm_tc_push(a, w, red.comm); red.rs_norm_push(x, nw, 1e-6, bn); ops.gemm_tc_ag(w2, red.comm, T, out=d2, bn=bn)
     def gemm_only():
         ops.gemm_tc(a, w, out=d)
     def ar_only():
         red.all_reduce(d)
     for name, fn in (("gemm alone", gemm_only), ("all_reduce alone", ar_only), ("gemm + all_reduce", unfused),
-                     ("gemm_push + rs_ag", fused)):
+                     ("gemm_push + rs_ag", fused), ("gemm_push + rs_ag + norm + next GEMM (N=2048)", fused_next),
+                     ("gemm_push + rs_norm_push + all-gather GEMM (N=2048)", seqpar_next)):
         for _ in range(3): fn()
         torch.cuda.synchronize(); dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -140,11 +168,14 @@ def main() -> int:
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (150, 33)]
     # (GEMM-epilogue push + fold, persistent decode-layer kernel): separate collectives, push + fold, layer kernel
-    modes = [("separate", False, False), ("push+fold", True, False), ("layer kernel", True, True)]
+    from dgpp_b200.engine.options import EngineOptions
+    modes = [("separate", False, False), ("push+fold", True, False), ("layer kernel", True, True),
+             ("push+fold, residual rows gathered (no sequence-parallel boundary)", True, None)]
     runs = []
     for name, fuse, fused in modes + modes:
+        opts = EngineOptions(seq_parallel=fused is not None)
         eng = LLMEngine(model, max_batch=2, max_seq_len=512, prefill_chunk=128, reducer=red, fuse_ar=fuse,
-                        fused_decode=fused)
+                        fused_decode=bool(fused), options=opts)
         if fused and not eng.runner._fused_ok(2):
             say("layer kernel does not apply to this shard shape (skipped)")
         runs.append(eng.generate(prompts, max_tokens=12))

@@ -279,6 +279,129 @@ rs_ag_kernel(CommState c, bf16* __restrict__ x, int T, int H, int tile_rows, int
   }
 }
 
+// Sequence-parallel boundary: reduce-scatter fold + residual add + RMSNorm at the owner, all-gather of the NORMED rows.
+// One CTA per row of this rank's OWN token tiles (the residual stream stays sharded by token tile: a rank only ever
+// needs the residual of the rows it folds).  The CTA waits (bounded) until every rank has delivered all `n_tiles` output
+// tiles of the row's token tile, folds the W partial rows in ascending rank order (fp32, one bf16 rounding), adds the
+// residual, stores the new residual row locally, normalises it with the arithmetic of rmsnorm_kernel (same thread ->
+// element map and reduction tree, so the fused and the separate path agree bit for bit) and stores the normed row into
+// slot `rank` of EVERY rank's region (its own included) at the row's offset: rows of a source slot that the
+// reduce-scatter does not use.  The last CTA of a token tile raises the peers' all-gather flag of that tile; the consumer
+// GEMM (gemm_tc all-gather mode) waits for the flag in its TMA producer warp and reads the rows where they landed, so
+// there is no copy pass and local tiles start at once.
+__global__ void __launch_bounds__(256)
+rs_norm_push_kernel(CommState c, bf16* __restrict__ x, const bf16* __restrict__ w, float eps, int one_plus_w, int T, int H,
+                    int tile_rows, int tiles_per_rank, int n_tiles, int row_begin, DeviceStatus* status) {
+  extern __shared__ __align__(16) unsigned char rs_smem[];
+  bf16* row_s = reinterpret_cast<bf16*>(rs_smem);
+  __shared__ float scratch[32];
+  __shared__ int ok_s;
+  pdl_wait();
+  const uint32_t epoch = *c.epoch + 1;
+  const int parity = epoch & 1;
+  const int row = row_begin + blockIdx.x;
+  const int t = row / tile_rows;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    uint32_t* cnt = rs_counter(c, c.rank, parity, threadIdx.x, t);
+    bool got = false;
+    const long long t0 = clock64();
+    for (long long i = 0; !got; ++i) {
+      got = ld_acquire_sys(cnt) >= static_cast<uint32_t>(n_tiles);
+      if (!got) {
+        if (i > (1 << 14)) __nanosleep(64);
+        if ((i & 255) == 255 && clock64() - t0 > 4000000000ll) break;
+      }
+    }
+    if (!got) {
+      if (atomicCAS(&status->code, 0, kTimeoutPeerFlag) == 0) status->detail = 400 + threadIdx.x;
+      atomicAdd(&status->count, 1);
+      ok_s = 0;
+    }
+  }
+  __syncthreads();
+  const int nvec = H / 8;
+  const size_t off = static_cast<size_t>(row) * H * 2;
+  float ss = 0.f;
+  if (ok_s) {
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int s = 0; s < c.world; ++s) {
+        Pack16 pk;
+        pk.u = __ldcg(reinterpret_cast<const uint4*>(payload(c, c.rank, parity, s) + off) + i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += bf16_to_f32(pk.h[j]);
+      }
+      Pack16 a;
+      a.u = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(x) + off)[i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a.h[j] = f32_to_bf16(bf16_to_f32(a.h[j]) + bf16_to_f32(f32_to_bf16(acc[j])));
+        const float f = bf16_to_f32(a.h[j]);
+        ss += f * f;
+      }
+      reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(x) + off)[i] = a.u;
+      reinterpret_cast<uint4*>(row_s)[i] = a.u;
+    }
+  }
+  // block sum in the order of rmsnorm_kernel: lanes by xor tree, then warps ascending
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+  for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) total += scratch[i];
+  const float rstd = rsqrtf(total / static_cast<float>(H) + eps);
+  if (ok_s) {
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      Pack16 a, ww, o;
+      a.u = reinterpret_cast<const uint4*>(row_s)[i];
+      ww.u = reinterpret_cast<const uint4*>(w)[i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float n = bf16_to_f32(f32_to_bf16(bf16_to_f32(a.h[j]) * rstd));
+        float g = bf16_to_f32(ww.h[j]);
+        if (one_plus_w) g += 1.f;
+        o.h[j] = f32_to_bf16(n * g);
+      }
+      for (int d = 0; d < c.world; ++d) {
+        const int dst = (c.rank + d) % c.world;
+        st_v4_global(payload(c, dst, parity, c.rank) + off + static_cast<size_t>(i) * 16, o.u);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int rows_in_tile = min(tile_rows, T - t * tile_rows);
+    if (atomicAdd(rs_local_done(c, t), 1u) == static_cast<uint32_t>(rows_in_tile - 1)) {
+      *rs_local_done(c, t) = 0;
+      for (int s = 0; s < c.world; ++s) *rs_counter(c, c.rank, parity, s, t) = 0;
+      __threadfence_system();
+      if (ok_s)
+        for (int d = 1; d < c.world; ++d) st_release_sys(ag_flag(c, (c.rank + d) % c.world, parity, t, 0), epoch);
+    }
+    __threadfence();
+    if (atomicAdd(c.done_ctas, 1u) == gridDim.x - 1) {
+      *c.done_ctas = 0;
+      *c.epoch = epoch;
+      __threadfence();
+    }
+  }
+}
+
+// A rank that owns no row of this exchange still has to close the epoch.
+__global__ void rs_epoch_only_kernel(CommState c) {
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    *c.epoch = *c.epoch + 1;
+    __threadfence();
+  }
+}
+
 }  // namespace dgpp
 
 using namespace dgpp;
@@ -403,6 +526,37 @@ DGPP_API int dgpp_comm_rs_ag(void* comm, void* x, int T, int H, int tile_rows, c
   rs_ag_kernel<<<dim3(tiles, chunks), 256, 0, st>>>(c->st, static_cast<bf16*>(x), T, H, tile_rows,
                                                     rs_tiles_per_rank(T, tile_rows, c->st.world), H / 128,
                                                     device_status_ptr());
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Sequence-parallel form of the boundary (see rs_norm_push_kernel): x [T, H] keeps only this rank's token tiles up to
+// date; the normed rows of ALL tiles land in every rank's region, where dgpp_gemm_tc_ag reads them.
+DGPP_API int dgpp_comm_rs_norm_push(void* comm, void* x, const void* norm_w, float eps, int one_plus_w, int T, int H,
+                                    int tile_rows, cudaStream_t st) {
+  DgppComm* c = static_cast<DgppComm*>(comm);
+  const int tiles = dgpp_ceil_div(T, tile_rows);
+  DGPP_REQUIRE(T > 0 && tiles <= kCommMaxCtas, "rs_norm_push: %d rows in tiles of %d exceed %d token tiles", T, tile_rows, kCommMaxCtas);
+  DGPP_REQUIRE(H % 128 == 0 && H * 2 <= 96 * 1024, "rs_norm_push: hidden %d must be a multiple of 128 (<= 48K)", H);
+  DGPP_REQUIRE(static_cast<size_t>(T) * H * 2 <= c->st.slot_bytes, "rs_norm_push: %d x %d exceeds the slot", T, H);
+  const int tpr = rs_tiles_per_rank(T, tile_rows, c->st.world);
+  const int own0 = c->st.rank * tpr < tiles ? c->st.rank * tpr : tiles;
+  const int own1 = c->st.rank == c->st.world - 1 ? tiles : ((c->st.rank + 1) * tpr < tiles ? (c->st.rank + 1) * tpr : tiles);
+  const int r0 = own0 * tile_rows;
+  const int r1 = own1 * tile_rows < T ? own1 * tile_rows : T;
+  if (r1 <= r0) {
+    rs_epoch_only_kernel<<<1, 32, 0, st>>>(c->st);
+    DGPP_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
+  static bool attr = false;
+  if (!attr) {
+    DGPP_CUDA_OK(cudaFuncSetAttribute(rs_norm_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    attr = true;
+  }
+  rs_norm_push_kernel<<<r1 - r0, 256, static_cast<size_t>(H) * 2, st>>>(c->st, static_cast<bf16*>(x), static_cast<const bf16*>(norm_w),
+                                                                      eps, one_plus_w, T, H, tile_rows, tpr, H / 128, r0,
+                                                                      device_status_ptr());
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }

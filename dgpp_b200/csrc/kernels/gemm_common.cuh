@@ -61,5 +61,22 @@ static inline int make_tmap_2d(CUtensorMap* m, const void* base, CUtensorMapData
   return 0;
 }
 
+// 3-D tensor [slabs, rows, cols]: rows with pitch `pitch` bytes, slabs `slab_pitch` bytes apart; boxes are 2-D (one slab).
+static inline int make_tmap_3d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int esize, uint64_t cols, uint64_t rows,
+                 uint64_t slabs, uint64_t pitch, uint64_t slab_pitch, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  DGPP_REQUIRE(fn != nullptr, "cuTensorMapEncodeTiled is unavailable (no CUDA driver?)");
+  DGPP_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base %p is not 16-byte aligned", base);
+  DGPP_REQUIRE(pitch % 16 == 0 && slab_pitch % 16 == 0, "TMA pitches must be multiples of 16 bytes");
+  DGPP_REQUIRE((static_cast<uint64_t>(box_cols) * esize) % 16 == 0, "TMA box inner extent is not a multiple of 16 bytes");
+  cuuint64_t dims[3] = {cols, rows, slabs};
+  cuuint64_t strides[2] = {pitch, slab_pitch};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DGPP_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (3-D) failed with %d", (int)r);
+  return 0;
+}
 
 }  // namespace dgpp

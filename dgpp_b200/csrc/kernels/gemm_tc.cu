@@ -69,6 +69,11 @@ struct GemmParams {
   // `rank` of the rank that owns the tile's tokens (token tiles are dealt in runs of tiles_per_rank) and that
   // owner's arrival counter of (this rank, token tile) is bumped; dgpp_comm_rs_ag folds and redistributes.
   int push, tiles_per_rank;
+  // All-gather mode (the consumer side of the sequence-parallel boundary): the activations are the normed rows that
+  // rs_norm_push_kernel of every rank stored into this rank's region, token tile t in slot owner(t) of the current
+  // parity.  tmB is then a 3-D map [K, T, 2 * world slots]; a CTA takes its token tile in an order that starts with
+  // this rank's own tiles, and its producer warp waits (bounded) for the owner's flag before the first load.
+  int ag;
   CommState comm;
 };
 
@@ -124,7 +129,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kBM;
-  const int m0 = blockIdx.y * BN;
+  int my = blockIdx.y;
+  if (p.ag) my = (min(p.comm.rank * p.tiles_per_rank, static_cast<int>(gridDim.y)) + static_cast<int>(blockIdx.y)) % static_cast<int>(gridDim.y);
+  const int m0 = my * BN;
   const int split = blockIdx.z, splits = gridDim.z;
   const int num_kb_total = p.K / kBK;
   const int kb_begin = split * p.kb_per_split;
@@ -157,6 +164,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
+      int ag_z = 0;
+      bool ag_waited = !p.ag;
       for (int i = 0; i < nkb; ++i) {
         const int kb = kb_begin + i;
         if (kQuant) {
@@ -178,7 +187,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,   // bf16 weights, or pa
         const int sb = i % SB;
         if (!wait_bar(&b_empty[sb], ((i / SB) & 1) ^ 1)) { report(p.status, kTimeoutStageEmpty, 2); *abort_flag = 1; break; }
         mbar_expect_tx(&b_full[sb], L::kStageB + (kQuant ? 0 : L::kStageA));
-        tma_load_2d(sB + sb * L::kStageB, &tmB, kb * kBK, m0, &b_full[sb]);
+        if (!ag_waited) {
+          // the weight stages above are already in flight; only the activation tile waits for its owner
+          const uint32_t epoch = *p.comm.epoch;
+          const int parity = epoch & 1;
+          const int owner = min(my / p.tiles_per_rank, p.comm.world - 1);
+          ag_z = parity * p.comm.world + owner;
+          if (owner != p.comm.rank && !wait_flag(ag_flag(p.comm, p.comm.rank, parity, my, 0), epoch)) {
+            report(p.status, kTimeoutPeerFlag, 500 + owner);
+            *abort_flag = 1;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");     // the peer's stores, acquired above, before the bulk reads
+          ag_waited = true;
+        }
+        if (p.ag) tma_load_3d(sB + sb * L::kStageB, &tmB, kb * kBK, m0, ag_z, &b_full[sb]);
+        else tma_load_2d(sB + sb * L::kStageB, &tmB, kb * kBK, m0, &b_full[sb]);
         if (!kQuant) tma_load_2d(sA + sb * L::kStageA, &tmA, kb * kBK, n0, &b_full[sb]);
         if (*abort_flag) break;
       }
@@ -539,7 +563,8 @@ using namespace dgpp;
 // bn: token tile (16, 32, 64, 128, 256).  splits >= 1; K/64 blocks are divided evenly (4-block aligned for fp4).
 static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_stride, const void* w,
                         const void* w_scale, float alpha, void* out, void* out32, const void* resid, int ldc,
-                        int T, int N, int K, int splits, void* ws, void* counters, void* comm_push, cudaStream_t st) {
+                        int T, int N, int K, int splits, void* ws, void* counters, void* comm_push, cudaStream_t st,
+                        void* comm_ag = nullptr) {
   DGPP_REQUIRE(T >= 1 && N >= 1, "gemm_tc: empty problem");
   DGPP_REQUIRE(K % 64 == 0, "gemm_tc: K %d must be a multiple of 64", K);
   const bool nibble_src = wmode == 1 || wmode == 3 || wmode == 6;
@@ -551,7 +576,17 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
   DGPP_REQUIRE(out || out32 || comm_push, "gemm_tc: no output");
   GemmParams p;
   p.push = 0;
+  p.ag = 0;
   p.tiles_per_rank = 1;
+  if (comm_ag) {
+    const DgppComm* c = static_cast<const DgppComm*>(comm_ag);
+    DGPP_REQUIRE(!comm_push, "gemm_tc: all-gather input and reduce-scatter push are separate calls");
+    DGPP_REQUIRE(dgpp_ceil_div(T, bn) <= kCommMaxCtas, "gemm_tc ag: %d rows in tiles of %d exceed %d token tiles", T, bn, kCommMaxCtas);
+    DGPP_REQUIRE(static_cast<size_t>(T) * K * 2 <= c->st.slot_bytes, "gemm_tc ag: %d x %d exceeds the slot", T, K);
+    p.ag = 1;
+    p.comm = c->st;
+    p.tiles_per_rank = dgpp_ceil_div(dgpp_ceil_div(T, bn), c->st.world);
+  }
   if (comm_push) {
     const DgppComm* c = static_cast<const DgppComm*>(comm_push);
     DGPP_REQUIRE(splits == 1, "gemm_tc push: split-K is not combined with the reduce-scatter push");
@@ -594,7 +629,13 @@ static int gemm_tc_impl(int wmode, int a_f16, int bn, const void* x, int64_t x_s
 
   CUtensorMap tA, tB, tSf;
   memset(&tSf, 0, sizeof(tSf));
-  if (make_tmap_2d(&tB, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, T, x_stride * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (comm_ag) {
+    // [K, T, 2 * world] over this rank's payload slots: z = parity * world + owner
+    const DgppComm* c = static_cast<const DgppComm*>(comm_ag);
+    if (make_tmap_3d(&tB, c->st.peers[c->st.rank], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, T, 2 * c->st.world,
+                     static_cast<uint64_t>(K) * 2, c->st.slot_bytes, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B))
+      return -1;
+  } else if (make_tmap_2d(&tB, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, T, x_stride * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B))
     return -1;
   if (wmode == 0) {
     if (make_tmap_2d(&tA, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, static_cast<uint64_t>(K) * 2, 64, kBM,
@@ -637,6 +678,16 @@ DGPP_API int dgpp_gemm_tc(int wmode, int a_f16, int bn, const void* x, int64_t x
                           int T, int N, int K, int splits, void* ws, void* counters, cudaStream_t st) {
   return gemm_tc_impl(wmode, a_f16, bn, x, x_stride, w, w_scale, alpha, out, out32, resid, ldc, T, N, K, splits, ws,
                       counters, nullptr, st);
+}
+
+// Same GEMM whose activations are the normed rows of the sequence-parallel all-gather (dgpp_comm_rs_norm_push of every
+// rank, same token tile bn): x is not read; token tiles wait for their owner's flag inside the kernel.
+DGPP_API int dgpp_gemm_tc_ag(int wmode, int a_f16, int bn, void* comm_ag, const void* w, const void* w_scale, float alpha,
+                             void* out, void* out32, int ldc, int T, int N, int K, int splits, void* ws, void* counters,
+                             cudaStream_t st) {
+  DGPP_REQUIRE(comm_ag != nullptr, "gemm_tc_ag: communicator required");
+  return gemm_tc_impl(wmode, a_f16, bn, nullptr, K, w, w_scale, alpha, out, out32, nullptr, ldc, T, N, K, splits, ws, counters,
+                      nullptr, st, comm_ag);
 }
 
 // Same GEMM with the reduce-scatter push epilogue (see GemmParams::push); pair with dgpp_comm_rs_ag(comm, x, T, N, bn).

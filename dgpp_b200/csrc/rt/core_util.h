@@ -236,6 +236,10 @@ struct ClusterConfig {
   bool engine_cluster_splitk = false;       // split-K through distributed shared memory instead of the workspace
   bool engine_fp4_preload = true;           // weight half of the first ring stages issued before the grid dependency
   bool engine_layer_kernel = false;         // decode through the persistent decode-layer kernel
+  bool engine_seq_parallel = true;          // tensor-parallel prefill keeps the residual stream sharded by token tile
+  int engine_moe_prefill_terms = 3;         // residual NVFP4 terms of the activations in expert GEMMs at prefill sizes (1..3)
+  int engine_mtp_depth = 0;                 // speculative decoding: MTP drafts per step (0 = off, up to 3)
+  bool engine_pin_split_rows = false;       // split-K choices ignore one row vs several (plain == speculative bits)
   std::string log_level = "info";
 
   static ClusterConfig parse(const std::string& text) {
@@ -245,7 +249,8 @@ struct ClusterConfig {
         "model", "host", "port", "tensor_parallel", "expert_parallel", "max_concurrency", "max_context", "prefill_chunk",
         "kv_dtype", "kv_headroom_mib", "prefix_cache", "prefix_min_tokens", "scheduler_policy", "mtp_depth",
         "sampling_candidates", "fuse_all_reduce", "log_level", "engine_decode_splits", "engine_fuse_combine",
-        "engine_l2_prefetch", "engine_fp4_splits", "engine_cluster_splitk", "engine_fp4_preload", "engine_layer_kernel"};
+        "engine_l2_prefetch", "engine_fp4_splits", "engine_cluster_splitk", "engine_fp4_preload", "engine_layer_kernel",
+        "engine_seq_parallel", "engine_moe_prefill_terms", "engine_mtp_depth", "engine_pin_split_rows"};
     for (const auto& kv : v.members())
       if (!known.count(kv.first)) throw std::runtime_error("config: unknown key '" + kv.first + "'");
     ClusterConfig c;
@@ -274,6 +279,10 @@ struct ClusterConfig {
     c.engine_cluster_splitk = v.get_bool("engine_cluster_splitk", false);
     c.engine_fp4_preload = v.get_bool("engine_fp4_preload", true);
     c.engine_layer_kernel = v.get_bool("engine_layer_kernel", false);
+    c.engine_seq_parallel = v.get_bool("engine_seq_parallel", true);
+    c.engine_moe_prefill_terms = static_cast<int>(v.get_int("engine_moe_prefill_terms", 3));
+    c.engine_mtp_depth = static_cast<int>(v.get_int("engine_mtp_depth", 0));
+    c.engine_pin_split_rows = v.get_bool("engine_pin_split_rows", false);
     auto need = [](bool ok, const std::string& what) { if (!ok) throw std::runtime_error("config: " + what); };
     need(c.port > 0 && c.port < 65536, "port out of range");
     need(c.tensor_parallel == 1 || c.tensor_parallel == 2 || c.tensor_parallel == 4 || c.tensor_parallel == 8,
@@ -287,6 +296,8 @@ struct ClusterConfig {
     need(c.mtp_depth >= 0 && c.mtp_depth <= 5, "mtp_depth must be 0..5");
     need(c.sampling_candidates >= 1 && c.sampling_candidates <= 256, "sampling_candidates must be 1..256");
     need(c.engine_decode_splits >= 0 && c.engine_decode_splits <= 64, "engine_decode_splits must be 0..64");
+    need(c.engine_moe_prefill_terms >= 1 && c.engine_moe_prefill_terms <= 3, "engine_moe_prefill_terms must be 1..3");
+    need(c.engine_mtp_depth >= 0 && c.engine_mtp_depth <= 3, "engine_mtp_depth must be 0..3");
     need(c.engine_fp4_splits == "auto" || c.engine_fp4_splits == "resident" || c.engine_fp4_splits == "legacy",
          "engine_fp4_splits must be auto, resident or legacy");
     return c;
@@ -304,6 +315,8 @@ struct ClusterConfig {
     v.set("engine_l2_prefetch", engine_l2_prefetch); v.set("engine_fp4_splits", engine_fp4_splits);
     v.set("engine_cluster_splitk", engine_cluster_splitk); v.set("engine_fp4_preload", engine_fp4_preload);
     v.set("engine_layer_kernel", engine_layer_kernel);
+    v.set("engine_seq_parallel", engine_seq_parallel); v.set("engine_moe_prefill_terms", engine_moe_prefill_terms);
+    v.set("engine_mtp_depth", engine_mtp_depth); v.set("engine_pin_split_rows", engine_pin_split_rows);
     return v;
   }
   // Same on every rank iff the engine-relevant settings agree (host / port / log level are per process).

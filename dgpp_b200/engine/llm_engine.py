@@ -56,7 +56,8 @@ class LLMEngine:
         self.decode_pdl = decode_pdl
         self.runner = DenseRunner(model, self.kv, rows, reducer=reducer, decode_splits=splits, decode_rows=max_batch,
                                   act_terms=act_terms, fuse_ar=fuse_ar, fused_decode=fused_decode,
-                                  l2_prefetch=self.options.l2_prefetch, fuse_combine=self.options.fuse_combine)
+                                  l2_prefetch=self.options.l2_prefetch, fuse_combine=self.options.fuse_combine,
+                                  seq_parallel=self.options.seq_parallel)
         self.use_graphs = use_graphs
         self.ring_steps = ring_steps
         i32 = dict(dtype=torch.int32, device=self.dev)

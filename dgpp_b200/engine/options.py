@@ -20,6 +20,10 @@ class EngineOptions:
     cluster_splitk: bool = False      # split-K through distributed shared memory instead of the workspace
     fp4_preload: bool = True          # weight half of the first ring stages issued before the grid dependency
     layer_kernel: bool = False        # decode through the persistent decode-layer kernel
+    seq_parallel: bool = True         # tensor-parallel prefill: residual stream sharded by token tile between the blocks
+    moe_prefill_terms: int = 3        # residual NVFP4 terms of the activations in the expert GEMMs at prefill sizes
+    mtp_depth: int = 0                # speculative decoding with the MTP head: drafts per step (0 = off)
+    pin_split_rows: bool = False      # split-K choices ignore one row vs several (plain and speculative rows: same bits)
 
     @staticmethod
     def from_config(cfg: Optional[Mapping]) -> "EngineOptions":
@@ -37,3 +41,6 @@ class EngineOptions:
         """The kernel front end keeps the GEMM policies as module state (one engine per process)."""
         from ..ops import core as ops
         ops.configure(fp4_splits=self.fp4_splits, cluster_splitk=self.cluster_splitk, fp4_preload=self.fp4_preload)
+        ops.PIN_SPLIT_ROWS = bool(self.pin_split_rows or self.mtp_depth > 0)
+        from ..models.moe import MoEBlock
+        MoEBlock.PREFILL_TERMS = int(self.moe_prefill_terms)

@@ -25,8 +25,12 @@ class DenseRunner:
     def __init__(self, model: DenseModel, kv: PagedKV, max_rows: int, reducer=None, decode_splits: int = 8,
                  decode_fp4: bool = True, act_terms: int = 3, attn_tc: bool = True,
                  decode_rows: Optional[int] = None, fuse_ar: bool = True, fused_decode: bool = False,
-                 l2_prefetch: bool = False, fuse_combine: bool = True):
+                 l2_prefetch: bool = False, fuse_combine: bool = True, seq_parallel: bool = True):
         self.m, self.kv, self.max_rows, self.reducer = model, kv, max_rows, reducer
+        # tensor parallel at prefill sizes: keep the residual stream sharded by token tile between the blocks (fold +
+        # norm at the owner, normed rows all-gathered straight into the next projection); False: every boundary folds
+        # and gathers the residual rows themselves
+        self.seq_parallel = seq_parallel
         # decode rows (<= 64) run the linears on the block-scaled FP4 tensor-core path with the activations
         # expanded into `act_terms` residual NVFP4 terms; attention reads the FP8 cache through tcgen05
         self.decode_fp4 = decode_fp4 and model.cfg.weight_fmt in ("nvfp4", "mxfp4")
@@ -297,6 +301,7 @@ class DenseRunner:
                     x[a - pos0:b - pos0].copy_(src[a - p0:b - p0])
         have_delta = False
         pending = False
+        sp_in = False
         splits = self.decode_splits if (decode and rows <= 256) else 1
         fp4 = self.decode_fp4 and decode and rows <= self.fp4_rows and all(
             w.k % 256 == 0 for w in (m.layers[0].qkv, m.layers[0].o, m.layers[0].down))
@@ -311,8 +316,13 @@ class DenseRunner:
                                           rows, splits, pending_fold=pending, last=li == len(m.layers) - 1)
                 have_delta = True
                 continue
-            ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have_delta else None, out=xn)
-            self.linear(xn, L.qkv, qkv, fp4)
+            if sp_in:
+                # the previous block's boundary left the normed rows of every token tile in the symmetric region
+                ops.gemm_tc_ag(L.qkv, self.reducer.comm, rows, out=qkv)
+            else:
+                ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have_delta else None, out=xn)
+                self.linear(xn, L.qkv, qkv, fp4)
+            sp_in = False
             if lora is not None:
                 lora.apply(li, "qkv", xn, qkv, self.lora_scratch)
             cache = kv.layers[li]
@@ -323,7 +333,13 @@ class DenseRunner:
             # tensor parallel at prefill sizes: GEMM epilogue -> reduce-scatter push, fold at the owner + all-gather
             rs = (self.fuse_ar and lora is None and not fp4 and rows > 64 and
                   getattr(self.reducer, "can_rs", lambda *a: False)(rows, c.hidden, ops.pick_bn(rows)))
-            if rs:
+            sp = rs and self.seq_parallel and hasattr(self.reducer, "rs_norm_push")
+            if sp:
+                # sequence-parallel boundary: fold + residual + norm at the tile's owner, normed rows all-gathered into
+                # every rank's region, the gate / up projection waits per token tile inside its kernel
+                bn = ops.gemm_tc_push(attn, L.o, self.reducer.comm)
+                self.reducer.rs_norm_push(x, L.post_norm, c.eps, bn)
+            elif rs:
                 # (x already holds the residual stream: the input norm above folded the previous block's output in)
                 self.reducer.rs_ag(x, ops.gemm_tc_push(attn, L.o, self.reducer.comm))
                 ops.rmsnorm(x, L.post_norm, c.eps, out=xn)
@@ -334,11 +350,20 @@ class DenseRunner:
                 if self.reducer is not None:
                     self.reducer.all_reduce(delta)
                 ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
-            self.linear(xn, L.gate_up, gu, fp4)
+            if sp:
+                ops.gemm_tc_ag(L.gate_up, self.reducer.comm, rows, out=gu)
+            else:
+                self.linear(xn, L.gate_up, gu, fp4)
             if lora is not None:
                 lora.apply(li, "gate_up", xn, gu, self.lora_scratch)
             ops.swiglu(gu, out=act)
+            if sp and li + 1 < len(m.layers):
+                bn = ops.gemm_tc_push(act, L.down, self.reducer.comm)
+                self.reducer.rs_norm_push(x, m.layers[li + 1].in_norm, c.eps, bn)
+                have_delta, sp_in = False, True
+                continue
             if rs:
+                # (the last block gathers the residual rows themselves: the final norm needs the last row everywhere)
                 self.reducer.rs_ag(x, ops.gemm_tc_push(act, L.down, self.reducer.comm))
                 have_delta = False                     # the block's output is already in the residual stream
                 continue

@@ -54,6 +54,7 @@ _SIGNATURES = {
     "dgpp_graph_destroy": [P],
     "dgpp_gemm_tc": [I, I, I, P, L, P, P, F, P, P, P, I, I, I, I, I, P, P, P],
     "dgpp_gemm_tc_push": [I, I, I, P, L, P, P, F, I, I, I, P, P],
+    "dgpp_gemm_tc_ag": [I, I, I, P, P, P, F, P, P, I, I, I, I, I, P, P, P],
 }
 
 

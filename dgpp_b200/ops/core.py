@@ -168,6 +168,21 @@ def gemm_tc_push(x: torch.Tensor, w: QuantLinear, push_comm, bn: Optional[int] =
     return bn
 
 
+def gemm_tc_ag(w: QuantLinear, ag_comm, rows: int, out: Optional[torch.Tensor] = None, bn: Optional[int] = None,
+               splits: int = 1) -> torch.Tensor:
+    """The linear whose activations are the normed rows of the sequence-parallel all-gather: every rank's
+    ``PeerReducer.rs_norm_push`` (same token tile `bn`) stored them into this rank's symmetric region; a token tile of
+    another rank is waited for inside the kernel (its TMA producer warp), this rank's own tiles run first."""
+    assert w.fmt in _FMT_GEMM
+    bn = bn or pick_bn(rows)
+    if out is None:
+        out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=w.payload.device)
+    a_f16 = A_F16_DEFAULT if w.fmt == "nvfp4" else 0
+    call("dgpp_gemm_tc_ag", _FMT_GEMM[w.fmt], int(a_f16), bn, ag_comm, ptr(w.payload), ptr(w.scale), float(w.alpha), ptr(out),
+         None, out.stride(0), rows, w.n, w.k, 1, None, None, stream_ptr())
+    return out
+
+
 class QuantAct:
     """Activations quantised to R residual NVFP4 terms: x ~= g[t] * sum_r dequant(term r).
     Rows of `q` are ordered [token tile][term][token in tile] (the B operand of one MMA is a token tile with its

@@ -12,13 +12,14 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
-from ..ops._lib import I, L, P, call, ptr, stream_ptr
+from ..ops._lib import F, I, L, P, call, ptr, stream_ptr
 
 _lib.declare("dgpp_comm_connect", [P, P])
 _lib.declare("dgpp_comm_destroy", [P])
 _lib.declare("dgpp_comm_all_reduce", [P, P, P, L, I, P])
 _lib.declare("dgpp_comm_pick_merge", [P, P, P, I, P])
 _lib.declare("dgpp_comm_rs_ag", [P, P, I, I, I, P])
+_lib.declare("dgpp_comm_rs_norm_push", [P, P, P, F, I, I, I, I, P])
 
 
 class PeerReducer:
@@ -69,6 +70,14 @@ class PeerReducer:
         assert x.is_contiguous() and x.dtype == torch.bfloat16
         call("dgpp_comm_rs_ag", self.comm, ptr(x), x.shape[0], x.shape[1], tile_rows, stream_ptr())
         return x
+
+    def rs_norm_push(self, x: torch.Tensor, norm_w: torch.Tensor, eps: float, tile_rows: int, one_plus_w: bool = False) -> None:
+        """Sequence-parallel boundary after ``ops.gemm_tc_push``: this rank folds the partial tiles of ITS token tiles
+        into x (the other rows of x are left as they are: no rank needs them), normalises those rows and stores the
+        normed rows into every rank's region; the next projection reads them with ``ops.gemm_tc_ag``."""
+        assert x.is_contiguous() and x.dtype == torch.bfloat16
+        call("dgpp_comm_rs_norm_push", self.comm, ptr(x), ptr(norm_w), float(eps), int(one_plus_w), x.shape[0], x.shape[1],
+             tile_rows, stream_ptr())
 
     def can_rs(self, rows: int, hidden: int, tile_rows: int) -> bool:
         return (rows * hidden <= self.max_values and hidden % 128 == 0 and (rows + tile_rows - 1) // tile_rows <= 64)

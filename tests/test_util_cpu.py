@@ -102,12 +102,14 @@ def test_engine_options_are_config_keys_covered_by_the_digest():
     seen = {d0}
     for k, v in (("engine_decode_splits", 4), ("engine_fuse_combine", False), ("engine_l2_prefetch", True),
                  ("engine_fp4_splits", "resident"), ("engine_cluster_splitk", True), ("engine_fp4_preload", False),
-                 ("engine_layer_kernel", True)):
+                 ("engine_layer_kernel", True), ("engine_seq_parallel", False), ("engine_moe_prefill_terms", 1),
+                 ("engine_mtp_depth", 2), ("engine_pin_split_rows", True)):
         t, d = rt.parse_cluster_config(json.dumps({**base, k: v}))
         assert d not in seen, k
         seen.add(d)
         o = EngineOptions.from_config(json.loads(t))
         assert getattr(o, k[len("engine_"):]) == v
-    for bad in ({"engine_fp4_splits": "fast"}, {"engine_decode_splits": -1}, {"engine_unknown": 1}):
+    for bad in ({"engine_fp4_splits": "fast"}, {"engine_decode_splits": -1}, {"engine_unknown": 1}, {"engine_mtp_depth": 4},
+                {"engine_moe_prefill_terms": 0}):
         with pytest.raises(Exception):
             rt.parse_cluster_config(json.dumps({**base, **bad}))
