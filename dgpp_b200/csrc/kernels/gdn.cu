@@ -48,6 +48,11 @@ struct GdnArgs {
   // roll the slot back to any row of its run without replaying it
   int seg;
   float* snap;
+  // KDA form (per-channel decay): gate_k [T, hv * dk] raw gate rows, dt_bias then has hv * dk entries and the decay of key
+  // channel c of head h is exp(lower_bound / (1 + exp(-exp(A_log[h]) * (gate_k[t, h, c] + dt_bias[h, c])))); alpha unused
+  const bf16* gate_k;
+  int64_t gate_stride;
+  float lower_bound;
 };
 
 // Token-parallel part: unit-norm q (scaled by dk^-1/2) and k per key head, decay and write strength per value head.
@@ -61,6 +66,22 @@ __global__ void __launch_bounds__(DK) gdn_prep_kernel(GdnArgs a) {
   float* kn = qn + static_cast<size_t>(a.T) * a.hk * DK;
   float* dec = kn + static_cast<size_t>(a.T) * a.hk * DK;
   float* bet = dec + static_cast<size_t>(a.T) * a.hv;
+  if (static_cast<int>(blockIdx.y) > a.hk) {
+    // KDA: per-channel decay of value head (blockIdx.y - hk - 1), one thread per key channel
+    const int h = static_cast<int>(blockIdx.y) - a.hk - 1;
+    float* deck = bet + static_cast<size_t>(a.T) * a.hv;
+    const float x = bf16_to_f32(a.gate_k[static_cast<size_t>(t) * a.gate_stride + h * DK + tid]) + a.dt_bias[h * DK + tid];
+    const float g = a.lower_bound / (1.f + expf(-expf(a.A_log[h]) * x));
+    deck[(static_cast<size_t>(t) * a.hv + h) * DK + tid] = expf(g);
+    return;
+  }
+  if (blockIdx.y == static_cast<unsigned>(a.hk) && a.gate_k) {
+    for (int h = tid; h < a.hv; h += DK) {
+      dec[static_cast<size_t>(t) * a.hv + h] = 1.f;
+      bet[static_cast<size_t>(t) * a.hv + h] = 1.f / (1.f + expf(-bf16_to_f32(a.beta[static_cast<size_t>(t) * a.ab_stride + h])));
+    }
+    return;
+  }
   if (blockIdx.y == static_cast<unsigned>(a.hk)) {
     for (int h = tid; h < a.hv; h += DK) {
       const float al = bf16_to_f32(a.alpha[static_cast<size_t>(t) * a.ab_stride + h]) + a.dt_bias[h];
@@ -91,10 +112,11 @@ __global__ void __launch_bounds__(DK) gdn_prep_kernel(GdnArgs a) {
 
 // Sequential part.  Thread (column j, part p) keeps state rows p, p + 8, p + 16, ... of column j in registers; the
 // normalised keys / queries of kGdnChunk tokens are staged in shared memory (one block-wide sync pair per chunk).
-template <int DK>
+template <int DK, bool KDA = false>
 __global__ void __launch_bounds__(kGdnThreads) gdn_recurrent_kernel(GdnArgs a) {
   constexpr int PER = DK / kGdnParts;          // state rows per thread
   __shared__ float ks[kGdnChunk][DK], qs[kGdnChunk][DK];
+  __shared__ float dks[KDA ? kGdnChunk : 1][KDA ? DK : 1];     // KDA: per-channel decays of the staged tokens
   __shared__ float vs[kGdnChunk][kGdnCols], ds[kGdnChunk], bs[kGdnChunk];
   pdl_wait();
   const int tid = threadIdx.x;
@@ -108,6 +130,7 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_recurrent_kernel(GdnArgs a) {
   const float* kn = qn + static_cast<size_t>(a.T) * a.hk * DK;
   const float* dec = kn + static_cast<size_t>(a.T) * a.hk * DK;
   const float* bet = dec + static_cast<size_t>(a.T) * a.hv;
+  const float* deck = bet + static_cast<size_t>(a.T) * a.hv;
   float* sp = a.state + ((static_cast<size_t>(slot0) * a.hv + h) * DK) * a.dv + j;
   float s[PER];
 #pragma unroll
@@ -120,6 +143,7 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_recurrent_kernel(GdnArgs a) {
       const size_t o = (static_cast<size_t>(t0 + tt) * a.hk + hk_idx) * DK + d;
       ks[tt][d] = kn[o];
       qs[tt][d] = qn[o];
+      if (KDA) dks[tt][d] = deck[(static_cast<size_t>(t0 + tt) * a.hv + h) * DK + d];
     }
     for (int i = tid; i < n * kGdnCols; i += kGdnThreads) {
       const int tt = i / kGdnCols, c = i % kGdnCols;
@@ -135,7 +159,7 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_recurrent_kernel(GdnArgs a) {
       float m = 0.f;
 #pragma unroll
       for (int i = 0; i < PER; ++i) {
-        s[i] *= decay;
+        s[i] *= KDA ? dks[tt][part + kGdnParts * i] : decay;
         m = fmaf(s[i], ks[tt][part + kGdnParts * i], m);
       }
 #pragma unroll
@@ -258,7 +282,9 @@ static int gdn_recurrent_launch(const void* q, int64_t q_stride, const void* k, 
                                 int64_t v_stride, const void* alpha, const void* beta, int64_t ab_stride,
                                 const void* A_log, const void* dt_bias, void* state, const void* row_slot, int slot,
                                 void* out, void* prep, int T, int hk, int hv, int dk, int dv, int sequential, int seg,
-                                void* snap, cudaStream_t st) {
+                                void* snap, cudaStream_t st, const void* gate_k = nullptr, int64_t gate_stride = 0,
+                                float lower_bound = 0.f) {
+  DGPP_REQUIRE(gate_k == nullptr || dk == 64 || dk == 128, "kda: key dim %d unsupported (64 or 128)", dk);
   DGPP_REQUIRE(seg == 0 || (row_slot && T % seg == 0 && !sequential), "gdn: runs of %d rows need row_slot and T %% seg == 0", seg);
   DGPP_REQUIRE(dk == 64 || dk == 128 || dk == 256, "gdn: key dim %d unsupported", dk);
   DGPP_REQUIRE(dv % kGdnCols == 0 && hk > 0 && hv % hk == 0, "gdn: bad head geometry hk %d hv %d dv %d", hk, hv, dv);
@@ -277,12 +303,19 @@ static int gdn_recurrent_launch(const void* q, int64_t q_stride, const void* k, 
   a.prep = static_cast<float*>(prep);
   a.T = T; a.hk = hk; a.hv = hv; a.dk = dk; a.dv = dv; a.sequential = sequential;
   a.seg = seg; a.snap = static_cast<float*>(snap);
-  dim3 pgrid(T, hk + 1);
+  a.gate_k = static_cast<const bf16*>(gate_k); a.gate_stride = gate_stride; a.lower_bound = lower_bound;
+  dim3 pgrid(T, hk + 1 + (gate_k ? hv : 0));
   if (dk == 64) gdn_prep_kernel<64><<<pgrid, 64, 0, st>>>(a);
   else if (dk == 128) gdn_prep_kernel<128><<<pgrid, 128, 0, st>>>(a);
   else gdn_prep_kernel<256><<<pgrid, 256, 0, st>>>(a);
   DGPP_CUDA_OK(cudaGetLastError());
   dim3 grid(dv / kGdnCols, hv, seg > 0 ? T / seg : (sequential ? 1 : T));
+  if (gate_k) {
+    if (dk == 64) gdn_recurrent_kernel<64, true><<<grid, kGdnThreads, 0, st>>>(a);
+    else gdn_recurrent_kernel<128, true><<<grid, kGdnThreads, 0, st>>>(a);
+    DGPP_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
   if (dk == 64) gdn_recurrent_kernel<64><<<grid, kGdnThreads, 0, st>>>(a);
   else if (dk == 128) gdn_recurrent_kernel<128><<<grid, kGdnThreads, 0, st>>>(a);
   else gdn_recurrent_kernel<256><<<grid, kGdnThreads, 0, st>>>(a);
@@ -308,6 +341,20 @@ DGPP_API int dgpp_gdn_recurrent_runs(const void* q, int64_t q_stride, const void
   DGPP_REQUIRE(seg >= 1, "gdn_recurrent_runs: run length %d", seg);
   return gdn_recurrent_launch(q, q_stride, k, k_stride, v, v_stride, alpha, beta, ab_stride, A_log, dt_bias, state, row_slot,
                               0, out, prep, T, hk, hv, dk, dv, 0, seg, snap, st);
+}
+
+// KDA (per-channel decay) recurrence: gate [T, hv * dk] raw gate rows, dt_bias [hv * dk], beta [T, hv] raw write strengths,
+// lower_bound < 0; prep: T * (2 hk dk + 2 hv + hv dk) floats.  seg / snap as in dgpp_gdn_recurrent_runs (seg 0: `sequential`
+// decides between one request's consecutive tokens and one token per request).
+DGPP_API int dgpp_kda_recurrent(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                int64_t v_stride, const void* gate, int64_t gate_stride, const void* beta, int64_t beta_stride,
+                                const void* A_log, const void* dt_bias, float lower_bound, void* state, const void* row_slot,
+                                int slot, void* out, void* prep, int T, int hk, int hv, int dk, int dv, int sequential, int seg,
+                                void* snap, cudaStream_t st) {
+  DGPP_REQUIRE(gate != nullptr && lower_bound < 0.f, "kda: gate rows and a negative lower bound required");
+  return gdn_recurrent_launch(q, q_stride, k, k_stride, v, v_stride, beta, beta, beta_stride, A_log, dt_bias, state, row_slot,
+                              slot, out, prep, T, hk, hv, dk, dv, seg > 0 ? 0 : sequential, seg, snap, st, gate, gate_stride,
+                              lower_bound);
 }
 
 // Token-parallel preparation alone (unit-norm q / k, decay, write strength into `prep`); the chunked scan

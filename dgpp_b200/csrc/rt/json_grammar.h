@@ -38,6 +38,7 @@ struct SchemaNode {
   int64_t min_items = 0, max_items = -1;
   std::vector<std::string> literals;                      // enum / const, serialised JSON texts
   int str = -1;                                           // index of the string-body constraint (lengths, pattern, format)
+  int64_t multiple_of = 0;                                // integer nodes: the value must be a multiple of this (0: off)
 };
 
 class Schema {
@@ -126,6 +127,14 @@ class Schema {
       else throw std::runtime_error("json_schema: 'additionalProperties' must be a boolean");
     }
     if (const json::Value* it = v.find("items")) nodes_[idx].items = add(*it, depth + 1);
+    if (const json::Value* m = v.find("multipleOf")) {
+      // supported where it can be enforced while the digits are written: integer values, integer divisor
+      const double d = m->as_double();
+      const int t = nodes_[idx].types;
+      if (!((t & kInteger) && !(t & kNumber)) || d < 1 || d != static_cast<double>(static_cast<int64_t>(d)) || d > 1e15)
+        throw std::runtime_error("json_schema: 'multipleOf' is supported for integer values with a positive integer divisor");
+      nodes_[idx].multiple_of = static_cast<int64_t>(d);
+    }
     nodes_[idx].min_items = v.get_int("minItems", 0);
     nodes_[idx].max_items = v.get_int("maxItems", -1);
     for (const auto& r : nodes_[idx].required) {
@@ -149,6 +158,7 @@ struct Frame {
   bool is_key = false;   // Str: this string is an object key
   int count = 0;         // Arr: items so far; Choice: candidate bitmask; Lit: which literal (0 true, 1 false, 2 null)
   std::string text;      // ObjKey..ObjValueDone: '\n'-joined keys seen; Str key: key bytes so far (raw, unescaped only)
+  int64_t aux = 0;       // Num under multipleOf: the digits so far modulo the divisor
 };
 
 class Machine {
@@ -179,7 +189,7 @@ class Machine {
         case Frame::Str: return in_string(c);
         case Frame::Num:
           if (num_step(f, c)) return true;
-          if (!num_final(f.sub) || (integer_only(f.node) && f.count)) return false;
+          if (!num_final(f.sub) || (integer_only(f.node) && f.count) || !multiple_ok(f)) return false;
           stack_.pop_back();
           value_done();
           continue;                                          // re-dispatch c to the parent
@@ -222,6 +232,7 @@ class Machine {
       s.push_back(f.is_key ? 1 : 0);
       s.append(reinterpret_cast<const char*>(&f.count), 4);
       s.append(f.text);
+      if (f.aux) s.append(reinterpret_cast<const char*>(&f.aux), 8);
       s.push_back('\x1f');
     }
     return s;
@@ -236,8 +247,11 @@ class Machine {
   // Num lexer: 0 after '-', 1 after leading 0, 2 integer digits, 3 after '.', 4 fraction digits, 5 after e/E,
   // 6 after exponent sign, 7 exponent digits.  f.count = 1 once a '.', 'e' or 'E' was seen.
   static bool num_final(uint8_t s) { return s == 1 || s == 2 || s == 4 || s == 7; }
+  bool multiple_ok(const Frame& f) const { return schema_->node(f.node).multiple_of <= 0 || f.aux == 0; }
   bool num_step(Frame& f, unsigned char c) {
     const bool digit = c >= '0' && c <= '9';
+    const int64_t mo = schema_->node(f.node).multiple_of;
+    if (mo > 0 && digit && (f.sub == 0 || f.sub == 2)) f.aux = (f.aux * 10 + (c - '0')) % mo;   // integer digits only
     switch (f.sub) {
       case 0: if (c == '0') { f.sub = 1; return true; } if (digit) { f.sub = 2; return true; } return false;
       case 1: break;
@@ -255,7 +269,7 @@ class Machine {
     return false;
   }
   bool ends_here(const Frame& f) const {
-    if (f.kind == Frame::Num) return num_final(f.sub);
+    if (f.kind == Frame::Num) return num_final(f.sub) && multiple_ok(f);
     if (f.kind == Frame::Choice) {
       const auto& lits = schema_->node(f.node).literals;
       for (size_t i = 0; i < lits.size() && i < 31; ++i)
@@ -286,6 +300,7 @@ class Machine {
       f.kind = Frame::Num;
       f.count = 0;
       f.sub = c == '-' ? 0 : (c == '0' ? 1 : 2);
+      f.aux = (n.multiple_of > 0 && c > '0' && c <= '9') ? (c - '0') % n.multiple_of : 0;
       return true;
     }
     if ((c == 't' || c == 'f') && (t & kBool)) { f.kind = Frame::Lit; f.count = c == 't' ? 0 : 1; f.sub = 1; return true; }

@@ -764,6 +764,24 @@ def gdn_recurrent(q, k, v, alpha, beta, A_log, dt_bias, state, out, hk: int, hv:
     return out
 
 
+_lib.declare("dgpp_kda_recurrent", [P, L, P, L, P, L, P, L, P, L, P, P, F, P, P, I, P, P, I, I, I, I, I, I, I, P, P])
+
+
+def kda_recurrent(q, k, v, gate, beta, A_log, dt_bias, lower_bound: float, state, out, hk: int, hv: int, dk: int, dv: int,
+                  row_slot=None, slot: int = 0, sequential: bool = True, seg: int = 0, snap=None, prep=None):
+    """Delta-rule recurrence with per-channel decay (KDA): gate [T, hv * dk] raw gate rows, beta [T, hv] raw write
+    strengths, dt_bias [hv * dk]; decay of channel c = exp(lower_bound / (1 + exp(-exp(A_log[h]) (gate + dt_bias)))).
+    state [slots, hv, dk, dv] fp32 in place; out [T, hv * dv] bf16.  Rows / runs / snapshots as in gdn_recurrent."""
+    T = q.shape[0]
+    need = T * (2 * hk * dk + 2 * hv + hv * dk)
+    if prep is None or prep.numel() < need:
+        prep = torch.empty(need, dtype=torch.float32, device=q.device)
+    call("dgpp_kda_recurrent", ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0), ptr(gate), gate.stride(0),
+         ptr(beta), beta.stride(0), ptr(A_log), ptr(dt_bias), float(lower_bound), ptr(state), ptr(row_slot), slot, ptr(out),
+         ptr(prep), T, hk, hv, dk, dv, int(sequential), seg, ptr(snap), stream_ptr())
+    return out
+
+
 def spec_accept(tokens, picks, n_acc, emitted, runs: int, run_rows: int) -> None:
     """Greedy verdict of speculative runs: tokens / picks [runs * run_rows] int32 -> n_acc [runs], emitted [runs, run_rows]."""
     call("dgpp_spec_accept", ptr(tokens), ptr(picks), ptr(n_acc), ptr(emitted), runs, run_rows, stream_ptr())

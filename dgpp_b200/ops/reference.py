@@ -182,3 +182,28 @@ def moe_hash_routes(tokens, tid2eid, scores, scaling: float = 1.0, norm_topk: bo
             denom = denom + w[:, i]
         w = w / (denom + 1e-20).unsqueeze(-1)
     return ids.to(torch.int32), w * scaling
+
+
+def kda_recurrent(q, k, v, gate, beta, A_log, dt_bias, lower_bound: float, state, hk: int, hv: int, dk: int, dv: int):
+    """Oracle of ops.kda_recurrent for consecutive tokens of one request.  q / k [T, hk * dk], v [T, hv * dv], gate
+    [T, hv * dk], beta [T, hv]; state [hv, dk, dv] fp32 updated in place.  Returns bf16 [T, hv * dv]."""
+    T = q.shape[0]
+    rep = hv // hk
+    qf = q.float().view(T, hk, dk)
+    kf = k.float().view(T, hk, dk)
+    qf = (qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5).repeat_interleave(rep, 1)
+    kf = (kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(rep, 1)
+    vf = v.float().view(T, hv, dv)
+    x = gate.float().view(T, hv, dk) + dt_bias.float().view(1, hv, dk)
+    g = lower_bound / (1.0 + torch.exp(-torch.exp(A_log.float()).view(1, hv, 1) * x))
+    decay = torch.exp(g)
+    b = torch.sigmoid(beta.float())
+    out = torch.zeros(T, hv, dv, device=q.device)
+    S = state
+    for t in range(T):
+        S.mul_(decay[t].unsqueeze(-1))
+        mem = torch.einsum("hkv,hk->hv", S, kf[t])
+        u = b[t].unsqueeze(-1) * (vf[t] - mem)
+        S.add_(torch.einsum("hk,hv->hkv", kf[t], u))
+        out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
+    return out.to(torch.bfloat16).view(T, hv * dv)

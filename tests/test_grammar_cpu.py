@@ -47,6 +47,18 @@ def test_schema_subset():
         chk({"type": "object", "required": ["x"], "additionalProperties": False, "properties": {}}, "{}")
 
 
+def test_multiple_of_on_integers():
+    sch = {"type": "object", "properties": {"n": {"type": "integer", "multipleOf": 25}}, "required": ["n"],
+           "additionalProperties": False}
+    for good in ('{"n": 0}', '{"n": 25}', '{"n": -1250}', '{"n": 100 }'):
+        assert chk(sch, good) == (True, True), good
+    for bad in ('{"n": 7}', '{"n": 26}', '{"n": -30}'):
+        assert chk(sch, bad)[0] is False, bad
+    assert chk(sch, '{"n": 12') == (True, False)             # may still become 125
+    with pytest.raises(RuntimeError, match="multipleOf"):
+        chk({"type": "number", "multipleOf": 0.5}, "1")
+
+
 def test_token_masks_drive_a_valid_generation():
     # a toy vocabulary: single bytes plus a few multi-byte tokens and two specials
     vocab = [bytes([i]) for i in range(256)] + [b'{"', b'": ', b'", "', b'"}', b"true", b"null", b"name", b"age", b""]
