@@ -337,7 +337,8 @@ class Scheduler {
       }
       const int64_t want = cfg_.policy == AdmissionPolicy::FullReserve
                                ? total + eng_->max_tokens_per_step() - 1
-                               : seq_len + cfg_.grow_margin_tokens;
+                               : seq_len + cfg_.grow_margin_tokens + eng_->max_tokens_per_step() - 1;   // (a request may
+                               // finish its prefill and take its first decode pass in the tick that admitted it)
       if (!ensure_reserved(s, want)) {
         // not enough blocks even after evicting the prefix cache: wait for a retirement
         eng_->close(s);
