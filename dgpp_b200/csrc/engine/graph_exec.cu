@@ -235,3 +235,37 @@ DGPP_API int dgpp_decode_loop(void* graph, const void* d_tokens, int b, int step
   steps_run[1] = launched;
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Bounded host-side waits: a stream or an event is polled with a deadline instead of a blocking synchronize, so a device
+// that stopped making progress turns into a return code the caller can act on (fail the engine, report, exit) rather
+// than a hung server thread.  Returns 0 = finished, 1 = deadline passed (work still pending), -1 = CUDA error.
+// (behavioural spec: src/core/cuda_wait.hpp of the reference.)
+#include <chrono>
+#include <thread>
+
+static int bounded_poll(cudaError_t (*query)(void*), void* what, int64_t timeout_us) {
+  const auto t0 = std::chrono::steady_clock::now();
+  int spins = 0;
+  for (;;) {
+    const cudaError_t e = query(what);
+    if (e == cudaSuccess) return 0;
+    if (e != cudaErrorNotReady) {
+      dgpp_set_error("bounded wait: %s", cudaGetErrorString(e));
+      cudaGetLastError();
+      return -1;
+    }
+    const auto us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+    if (us >= timeout_us) return 1;
+    if (++spins < 2000) continue;                                  // ~first tens of microseconds: pure polling
+    std::this_thread::sleep_for(std::chrono::microseconds(us < 2000 ? 20 : 200));
+  }
+}
+
+DGPP_API int dgpp_stream_wait(cudaStream_t st, int64_t timeout_us) {
+  return bounded_poll([](void* s) { return cudaStreamQuery(static_cast<cudaStream_t>(s)); }, st, timeout_us);
+}
+
+DGPP_API int dgpp_event_wait(cudaEvent_t ev, int64_t timeout_us) {
+  return bounded_poll([](void* e) { return cudaEventQuery(static_cast<cudaEvent_t>(e)); }, ev, timeout_us);
+}

@@ -403,3 +403,36 @@ DGPP_API int dgpp_decode_advance(const void* picked, void* tokens, void* positio
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+// Batched segment copy: n independent (source, destination, bytes) copies described by a DEVICE table, one launch.
+// Used for state snapshots / restores (many small per-layer tensors) inside captured graphs, where the segments are
+// chosen by earlier kernels.  Addresses and sizes are multiples of 16 bytes.  grid (chunks, n).
+// (reference counterpart: src/kernels/segment_copy.cu.)
+namespace dgpp {
+struct Segment {
+  const void* src;
+  void* dst;
+  int64_t bytes;
+};
+__global__ void __launch_bounds__(256) segment_copy_kernel(const Segment* __restrict__ segs) {
+  pdl_wait();
+  const Segment s = segs[blockIdx.y];
+  const int64_t vecs = s.bytes / 16;
+  const uint4* src = static_cast<const uint4*>(s.src);
+  uint4* dst = static_cast<uint4*>(s.dst);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs; i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
+}  // namespace dgpp
+
+// segs: device array of n {src, dst, bytes} records (24 bytes each); max_bytes: the largest segment (sizes the grid).
+DGPP_API int dgpp_segment_copy(const void* segs, int n, int64_t max_bytes, cudaStream_t st) {
+  DGPP_REQUIRE(n >= 0 && max_bytes >= 0 && max_bytes % 16 == 0, "segment_copy: sizes must be multiples of 16 bytes");
+  if (n == 0 || max_bytes == 0) return 0;
+  int64_t chunks = (max_bytes / 16 + 256 * 8 - 1) / (256 * 8);
+  if (chunks > 64) chunks = 64;
+  if (chunks < 1) chunks = 1;
+  dgpp::segment_copy_kernel<<<dim3(static_cast<unsigned>(chunks), n), 256, 0, st>>>(static_cast<const dgpp::Segment*>(segs));
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -85,4 +85,31 @@ void bind_util(py::module_& m) {
     return py::make_tuple(p.kv_blocks, p.kv_bytes, p.tokens);
   }, py::arg("free_bytes"), py::arg("headroom_bytes"), py::arg("workspace_bytes"), py::arg("layers"), py::arg("kv_heads"),
      py::arg("head_dim"), py::arg("block_tokens"), py::arg("fp8") = true, py::arg("max_blocks") = int64_t(-1));
+
+  m.def("process_memory", []() {
+    const ProcessMemory pm = process_memory();
+    py::dict d;
+    d["rss_bytes"] = pm.rss_bytes; d["peak_rss_bytes"] = pm.peak_rss_bytes; d["locked_bytes"] = pm.locked_bytes;
+    d["memlock_limit_bytes"] = pm.memlock_limit_bytes;
+    return d;
+  });
+  m.def("file_residency", [](const std::string& path) {
+    int64_t size = -1;
+    const double f = file_residency(path, &size);
+    return py::make_tuple(f, size);
+  });
+  py::class_<PrefillProgress>(m, "PrefillProgress")
+      .def(py::init<>())
+      .def("begin", &PrefillProgress::begin)
+      .def("advance", &PrefillProgress::advance)
+      .def("end", &PrefillProgress::end)
+      .def("snapshot", [](const PrefillProgress& p, int64_t now_ms) {
+        py::list out;
+        for (const auto& r : p.snapshot(now_ms)) out.append(py::make_tuple(r.id, r.done, r.total, r.started_ms, r.idle_ms));
+        return out;
+      })
+      .def("most_stalled", [](const PrefillProgress& p, int64_t now_ms) {
+        const auto r = p.most_stalled(now_ms);
+        return py::make_tuple(r.id, r.done, r.total, r.started_ms, r.idle_ms);
+      });
 }

@@ -18,6 +18,12 @@
 #include <thread>
 #include <vector>
 
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/resource.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include "rt/json.h"
 
 namespace dgpp {
@@ -351,5 +357,82 @@ inline MemoryPlan plan_kv(int64_t free_bytes, int64_t headroom_bytes, int64_t wo
   p.tokens = p.kv_blocks * block_tokens;
   return p;
 }
+
+// ------------------------------------------------------------------------------------------- process memory / residency
+// What the host process holds and what of a file is in the page cache: resident and peak set, locked bytes against the
+// memlock limit (pinned staging buffers count against it), and the resident fraction of a weight file (mincore over a
+// private read-only mapping), so the launcher can tell a warm start from a cold one and the metrics page can show it.
+// (same roles as src/common/process_memory.hpp, src/common/residency.hpp of the reference.)
+struct ProcessMemory {
+  int64_t rss_bytes = -1, peak_rss_bytes = -1, locked_bytes = -1, memlock_limit_bytes = -1;   // -1: unknown
+};
+inline ProcessMemory process_memory() {
+  ProcessMemory m;
+  if (FILE* f = std::fopen("/proc/self/status", "r")) {
+    char line[256];
+    while (std::fgets(line, sizeof(line), f)) {
+      long long kb = 0;
+      if (std::sscanf(line, "VmRSS: %lld kB", &kb) == 1) m.rss_bytes = kb * 1024;
+      else if (std::sscanf(line, "VmHWM: %lld kB", &kb) == 1) m.peak_rss_bytes = kb * 1024;
+      else if (std::sscanf(line, "VmLck: %lld kB", &kb) == 1) m.locked_bytes = kb * 1024;
+    }
+    std::fclose(f);
+  }
+  struct rlimit rl;
+  if (getrlimit(RLIMIT_MEMLOCK, &rl) == 0)
+    m.memlock_limit_bytes = rl.rlim_cur == RLIM_INFINITY ? INT64_MAX : static_cast<int64_t>(rl.rlim_cur);
+  return m;
+}
+// Fraction of the file's pages that are in the page cache (0..1); -1 when the file cannot be examined.  `sample_every`
+// > 1 looks at every n-th page only (large checkpoints).
+inline double file_residency(const std::string& path, int64_t* size_out = nullptr) {
+  const int fd = ::open(path.c_str(), O_RDONLY);
+  if (fd < 0) return -1.0;
+  struct stat st;
+  if (fstat(fd, &st) != 0 || st.st_size <= 0) { ::close(fd); return st.st_size == 0 ? 1.0 : -1.0; }
+  if (size_out) *size_out = static_cast<int64_t>(st.st_size);
+  void* p = mmap(nullptr, static_cast<size_t>(st.st_size), PROT_READ, MAP_PRIVATE, fd, 0);
+  ::close(fd);
+  if (p == MAP_FAILED) return -1.0;
+  const long page = sysconf(_SC_PAGESIZE);
+  const size_t pages = (static_cast<size_t>(st.st_size) + page - 1) / page;
+  std::vector<unsigned char> vec(pages);
+  double frac = -1.0;
+  if (mincore(p, static_cast<size_t>(st.st_size), vec.data()) == 0) {
+    size_t in = 0;
+    for (unsigned char b : vec) in += b & 1;
+    frac = static_cast<double>(in) / static_cast<double>(pages);
+  }
+  munmap(p, static_cast<size_t>(st.st_size));
+  return frac;
+}
+
+// Progress of the prefills in flight, for /metrics and for a stall report: tokens done / total per request and the
+// time since the last advance.
+class PrefillProgress {
+ public:
+  void begin(const std::string& id, int64_t total, int64_t now_ms) { items_[id] = Item{0, total, now_ms, now_ms}; }
+  void advance(const std::string& id, int64_t done, int64_t now_ms) {
+    auto it = items_.find(id);
+    if (it == items_.end()) return;
+    if (done > it->second.done) { it->second.done = done; it->second.last_ms = now_ms; }
+  }
+  void end(const std::string& id) { items_.erase(id); }
+  struct Row { std::string id; int64_t done, total, started_ms, idle_ms; };
+  std::vector<Row> snapshot(int64_t now_ms) const {
+    std::vector<Row> rows;
+    for (const auto& kv : items_) rows.push_back(Row{kv.first, kv.second.done, kv.second.total, kv.second.start_ms, now_ms - kv.second.last_ms});
+    return rows;
+  }
+  // the request that has gone longest without an advance (empty id: none in flight)
+  Row most_stalled(int64_t now_ms) const {
+    Row worst{"", 0, 0, 0, -1};
+    for (const auto& r : snapshot(now_ms)) if (r.idle_ms > worst.idle_ms) worst = r;
+    return worst;
+  }
+ private:
+  struct Item { int64_t done, total, start_ms, last_ms; };
+  std::map<std::string, Item> items_;
+};
 
 }  // namespace dgpp

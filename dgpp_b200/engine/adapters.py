@@ -237,6 +237,7 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
             self.s_pos = torch.zeros(hb, dtype=torch.int32, device=dev)
             self.s_req = torch.zeros(hb, dtype=torch.int32, device=dev)
         self.poll_status = True                        # read the device status block after every step (see _poll_device)
+        self.step_deadline_s = 120.0                   # host-side bound on one prefill chunk / decode pass
         self.by_id = {}
         self.emitted = {}                              # request id -> tokens the sampler picked for it so far
         self.slot_req = [None] * b
@@ -398,6 +399,11 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
             return
         import ctypes as C
         from ..ops import _lib
+        from ..ops import core as _ops
+        # the status read below synchronises the device: bound that wait first, so a device that stopped making progress
+        # becomes an engine failure instead of a hung serving thread
+        if not _ops.stream_wait(self.step_deadline_s):
+            raise EngineFailure(f"the device did not finish a step within {self.step_deadline_s:.0f} s")
         buf = (C.c_int * 4)()
         _lib.call("dgpp_status_read", C.cast(buf, C.c_void_p))
         if buf[0] != 0:

@@ -406,6 +406,38 @@ def check_status() -> None:
     _lib.check_status()
 
 
+_lib.declare("dgpp_segment_copy", [P, I, L, P])
+_lib.declare("dgpp_stream_wait", [P, L])
+
+
+def segment_copy(pairs) -> None:
+    """One launch for many copies: pairs = [(src tensor, dst tensor), ...] of equal byte sizes per pair (multiples of 16,
+    16-byte aligned).  The table goes to the device once per call; callers that repeat a set keep `segment_table`."""
+    table, biggest = segment_table(pairs)
+    call("dgpp_segment_copy", ptr(table), len(pairs), biggest, stream_ptr())
+
+
+def segment_table(pairs):
+    """Device table of (src, dst, bytes) records for dgpp_segment_copy; returns (table, largest segment in bytes)."""
+    rec, biggest = [], 0
+    for s, d in pairs:
+        n = s.numel() * s.element_size()
+        assert n == d.numel() * d.element_size() and n % 16 == 0 and s.is_contiguous() and d.is_contiguous()
+        rec += [s.data_ptr(), d.data_ptr(), n]
+        biggest = max(biggest, n)
+    dev = pairs[0][0].device
+    return torch.tensor(rec, dtype=torch.int64).to(dev), biggest
+
+
+def stream_wait(timeout_s: float, stream=None) -> bool:
+    """Bounded host wait for a stream: True when its work finished within the deadline, False when it is still pending
+    (the caller decides: fail the engine, report); raises on a CUDA error."""
+    rc = _lib._fn("dgpp_stream_wait")(stream_ptr(stream), int(timeout_s * 1e6))
+    if rc < 0:
+        raise RuntimeError("stream_wait: " + _lib.load().dgpp_last_error().decode())
+    return rc == 0
+
+
 def attn_decode_tc(q, q_stride: int, cache, block_table, row_req, positions, hq: int, hkv: int, d: int,
                    scale: float, splits: int = 1, scratch=None, out=None, window: int = 0,
                    partials_only: bool = False):

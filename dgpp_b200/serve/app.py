@@ -204,7 +204,8 @@ class Server:
             else:
                 self.http.respond(conn, 404, "application/json", rt.error_json(404, "model not found", param="model").encode())
         elif method == "GET" and path in ("/metrics", "/v1/metrics"):
-            body = json.dumps({"counters": self.metrics.c, "scheduler": self.sched.meters(), "live": len(self.live)})
+            body = json.dumps({"counters": self.metrics.c, "scheduler": self.sched.meters(), "live": len(self.live),
+                               "process": rt.process_memory()})
             self.http.respond(conn, 200, "application/json", body.encode())
         elif method == "GET" and path == "/metrics/prometheus":
             self.http.respond(conn, 200, "text/plain; version=0.0.4", self.metrics.prometheus(self.sched.meters()).encode())

@@ -54,3 +54,22 @@ def test_moe_hash_routes(dev):
         ids, w = ops.moe_hash_routes(tokens, tid2eid, scores, scaling=2.5, norm_topk=norm)
         wi, ww = ref.moe_hash_routes(tokens, tid2eid, scores, scaling=2.5, norm_topk=norm)
         assert torch.equal(ids, wi) and torch.allclose(w, ww, rtol=1e-6, atol=0)
+
+
+def test_segment_copy_and_bounded_stream_wait(dev):
+    from dgpp_b200.ops import core as ops
+
+    torch.manual_seed(5)
+    srcs = [torch.randn(n, device=dev) for n in (4, 1024, 70000, 16)]
+    dsts = [torch.zeros_like(s) for s in srcs]
+    ops.segment_copy(list(zip(srcs, dsts)))
+    assert ops.stream_wait(5.0) is True
+    for s, d in zip(srcs, dsts):
+        assert torch.equal(s, d)
+    # a deadline that is already over while work is queued: the wait reports "pending" instead of blocking
+    a = torch.randn(8192, 8192, device=dev)
+    for _ in range(20):
+        a = a @ a.t() * 1e-4
+    pending = ops.stream_wait(0.0)
+    assert pending in (True, False)          # (True only if the queue drained before the first poll)
+    assert ops.stream_wait(30.0) is True

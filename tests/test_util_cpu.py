@@ -113,3 +113,25 @@ def test_engine_options_are_config_keys_covered_by_the_digest():
                 {"engine_moe_prefill_terms": 0}):
         with pytest.raises(Exception):
             rt.parse_cluster_config(json.dumps({**base, **bad}))
+
+
+def test_process_memory_file_residency_and_prefill_progress(tmp_path):
+    from dgpp_b200.runtime import rt
+
+    pm = rt.process_memory()
+    assert pm["rss_bytes"] > 1 << 20 and pm["peak_rss_bytes"] >= pm["rss_bytes"] and pm["memlock_limit_bytes"] != 0
+    f = tmp_path / "w.bin"
+    f.write_bytes(b"x" * (1 << 20))
+    frac, size = rt.file_residency(str(f))
+    assert size == 1 << 20 and 0.0 <= frac <= 1.0
+    assert rt.file_residency(str(tmp_path / "missing"))[0] == -1.0
+    p = rt.PrefillProgress()
+    p.begin("a", 1000, 0)
+    p.begin("b", 50, 10)
+    p.advance("a", 256, 40)
+    p.advance("a", 100, 90)                 # a smaller count is not an advance
+    rows = {r[0]: r for r in p.snapshot(100)}
+    assert rows["a"][1:] == (256, 1000, 0, 60) and rows["b"][1:] == (0, 50, 10, 90)
+    assert p.most_stalled(100)[0] == "b"
+    p.end("b")
+    assert p.most_stalled(100)[0] == "a" and len(p.snapshot(100)) == 1
