@@ -9,7 +9,7 @@ import torch
 
 from ..quant.formats import QuantLinear
 from . import _lib
-from ._lib import call, ptr, stream_ptr
+from ._lib import F, I, L, P, call, ptr, stream_ptr
 
 _FMT_GEMV = {"nvfp4": 0, "mxfp4": 1, "bf16": 2}
 _FMT_GEMM = {"bf16": 0, "nvfp4": 1, "fp8": 2, "mxfp4": 3, "mxfp8": 4, "int8": 5, "int4": 6, "bf12": 7}

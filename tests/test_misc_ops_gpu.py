@@ -73,3 +73,33 @@ def test_segment_copy_and_bounded_stream_wait(dev):
     pending = ops.stream_wait(0.0)
     assert pending in (True, False)          # (True only if the queue drained before the first poll)
     assert ops.stream_wait(30.0) is True
+
+
+def test_releasable_range_commit_release_keeps_addresses(dev):
+    from dgpp_b200.utils.vmm import ReleasableRange
+
+    r = ReleasableRange(64 << 20)
+    try:
+        g = r.granule
+        assert r.size >= 64 << 20 and r.size % g == 0 and r.committed() == 0
+        free0 = torch.cuda.mem_get_info()[0]
+        r.commit(0, 3 * g)
+        assert r.committed() == 3 * g
+        a = r.tensor(0, 3 * g, torch.float32)
+        a.fill_(1.5)
+        assert float(a.sum()) == 1.5 * (3 * g // 4)
+        ptr = a.data_ptr()
+        r.release(g, g)                                    # the middle granule goes back to the device
+        assert r.committed() == 2 * g
+        b = r.tensor(0, g, torch.float32)
+        assert b.data_ptr() == ptr and float(b[17]) == 1.5    # what stayed committed kept its contents and address
+        r.commit(g, g)                                     # recommit: fresh memory at the same address
+        c = r.tensor(g, g, torch.float32)
+        c.zero_()
+        assert float(c.sum()) == 0.0 and c.data_ptr() == ptr + g
+        torch.cuda.synchronize()
+        r.release(0, r.size)
+        assert r.committed() == 0
+        assert torch.cuda.mem_get_info()[0] >= free0 - (1 << 20)
+    finally:
+        r.close()
