@@ -190,6 +190,25 @@ def main() -> int:
         agree = runs[i] == runs[0]
         say(f"{name}: run1 == run2: {rep}  == separate collectives: {agree}", ok=rep and agree)
     for i, r in enumerate(runs[:k]): say("  ", modes[i][0], r[0])
+    # vocabulary-sharded sampling: candidate tables instead of a logits gather; same tokens on every rank and the tokens of
+    # the unsharded sampler on the gathered rows
+    from dgpp_b200.sampling.device import DeviceSampler, SamplingParams
+    vocab_l, rows_s = 4096, 6
+    smp = DeviceSampler(vocab_l * world, rows_s, slots=2, device=dev)
+    torch.manual_seed(900 + rank)
+    sl = (torch.randn(rows_s, vocab_l, device=dev) * 3).contiguous()
+    sp = [SamplingParams(), SamplingParams(top_logprobs=4), SamplingParams(temperature=0.8, top_k=40, seed=1),
+          SamplingParams(temperature=1.0, top_p=0.9, seed=2), SamplingParams(temperature=0.7, min_p=0.05, seed=3, top_logprobs=5),
+          SamplingParams(temperature=0.5, top_k=10, seed=4, logit_bias={7: 3.0, vocab_l * world - 2: 5.0})]
+    picks = smp.sample_sharded(sl, rank * vocab_l, sp, [-1] * rows_s, list(range(rows_s)), count_picks=False)
+    allsl = [torch.empty_like(sl) for _ in range(world)]; dist.all_gather(allsl, sl)
+    ref = smp.sample(torch.cat(allsl, 1).contiguous(), sp, [-1] * rows_s, list(range(rows_s)), count_picks=False)
+    toks = [p.token for p in picks]
+    allt = [None] * world; dist.all_gather_object(allt, toks)
+    same = all(t == allt[0] for t in allt)
+    eq = all(a.token == b.token for a, b in zip(picks, ref) if a.on_device and b.on_device)
+    say(f"sharded sampling: identical across ranks={same} == unsharded sampler on the gathered rows={eq} tokens={toks}",
+        ok=same and eq)
     # scheduler + kernel engine on every rank: the same prompt three times (prefix cache off, then on) must give the
     # same tokens every time on every rank (the cached runs attach shared KV blocks and prefill only the tail)
     from dgpp_b200.engine.adapters import KernelEngine

@@ -370,15 +370,17 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
                     m[r, :min(words, gm.shape[0])] = gm[:words]
             masks = torch.from_numpy(m.view(np.int32)).to(self.e.dev)
         if self.e.model.tp_size > 1:
-            # vocabulary-sharded head: gather the ranks' logit slices (in rank order = vocabulary order) so that
-            # every rank runs the same sampler on the same full rows and draws the same token
-            import torch.distributed as dist
-            part = logits[:rows].contiguous()
-            parts = [torch.empty_like(part) for _ in range(self.e.model.tp_size)]
-            dist.all_gather(parts, part)
-            logits = torch.cat(parts, dim=1)
-        picked = self.sampler.sample(logits, params, [s if self.slot_cfg[s] else -1 for s in slots],
-                                     [self.filled[s] for s in slots], masks=masks)
+            # vocabulary-sharded head: every rank builds the candidate table of its slice (a few KB per row), the tables
+            # are all-gathered and folded identically on every rank: no logits gather, the same token everywhere
+            vl = self.e.runner.vocab_local
+            base = self.e.model.tp_rank * vl
+            width = max(0, min(vl, self.e.model.cfg.vocab - base))
+            picked = self.sampler.sample_sharded(logits[:rows, :width], base, params,
+                                                 [s if self.slot_cfg[s] else -1 for s in slots],
+                                                 [self.filled[s] for s in slots], masks=masks)
+        else:
+            picked = self.sampler.sample(logits, params, [s if self.slot_cfg[s] else -1 for s in slots],
+                                         [self.filled[s] for s in slots], masks=masks)
         for r, s in enumerate(slots):
             cfg = self.slot_cfg[s]
             if cfg:

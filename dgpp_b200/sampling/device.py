@@ -14,6 +14,8 @@ from ..ops import _lib
 from ..ops._lib import I, L, P, call, ptr, stream_ptr
 
 _lib.declare("dgpp_sample", [P, L, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, P])
+_lib.declare("dgpp_sample_local", [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P])
+_lib.declare("dgpp_sample_merge", [P, P, P, P, P, P, P, P, P, P, I, I, I, P])
 _lib.declare("dgpp_sample_count_tokens", [P, I, I, P, I, I, P])
 _lib.declare("dgpp_sample_count_step", [P, I, P, P, I, P])
 
@@ -131,6 +133,92 @@ class DeviceSampler:
             for r, s in enumerate(out):
                 if slots[r] >= 0:
                     self.count(slots[r], [s.token])
+        return out
+
+    # ---- vocabulary-sharded head (tensor parallel): candidate tables instead of a logits gather
+    def _pack_rows(self, params, slots, positions) -> bool:
+        rows = len(params)
+        any_bias = any(p.logit_bias for p in params)
+        packed = bytearray()
+        for r, (p, slot, pos) in enumerate(zip(params, slots, positions)):
+            nb = min(len(p.logit_bias), MAX_BIAS)
+            packed += struct.pack(ROW_FMT, p.temperature, p.top_p, p.min_p, p.repetition_penalty, p.presence_penalty,
+                                  p.frequency_penalty, p.top_k, p.top_logprobs, slot, nb, p.seed & (2 ** 64 - 1), pos)
+            if nb:
+                items = sorted(p.logit_bias.items())[:nb]
+                self.bias_ids[r, :nb] = torch.tensor([k for k, _ in items], dtype=torch.int32)
+                self.bias_vals[r, :nb] = torch.tensor([v for _, v in items], dtype=torch.float32)
+        blob = torch.frombuffer(packed, dtype=torch.uint8).view(rows, ROW_BYTES)
+        if self.rows_host is not None:
+            self.rows_host[:rows].copy_(blob)
+            self.rows_dev[:rows].copy_(self.rows_host[:rows], non_blocking=True)
+        else:
+            self.rows_dev[:rows].copy_(blob)
+        return any_bias
+
+    def local_tables(self, logits_slice: torch.Tensor, id_base: int, params, slots, positions, masks=None):
+        """Step 1 on this rank's slice [id_base, id_base + width) of the vocabulary: returns (cand [rows, C] int64 keys,
+        ms [rows, 2] fp32, nt [rows] int32).  `self.vocab` is the FULL vocabulary (count table, bias ids, mask bits)."""
+        rows, width = len(params), logits_slice.shape[1]
+        any_bias = self._pack_rows(params, slots, positions)
+        cand = torch.zeros(rows, self.candidates, dtype=torch.int64, device=self.dev)
+        ms = torch.zeros(rows, 2, dtype=torch.float32, device=self.dev)
+        nt = torch.zeros(rows, dtype=torch.int32, device=self.dev)
+        call("dgpp_sample_local", ptr(logits_slice), logits_slice.stride(0), ptr(self.rows_dev), ptr(self.counts),
+             ptr(self.bias_ids) if any_bias else None, ptr(self.bias_vals) if any_bias else None, ptr(masks), ptr(self.z),
+             ptr(self.parts), ptr(cand), ptr(ms), ptr(nt), rows, width, id_base, self.vocab, self.candidates, stream_ptr())
+        return cand, ms, nt
+
+    def merge_tables(self, cands, mss, nts, params, slots, count_picks: bool = True) -> List[Sampled]:
+        """Step 2: the ranks' tables stacked in rank order ([world, rows, ...]); every rank computes the same picks.
+        A row whose draw does not resolve inside the candidate prefix comes back with resolved=False (the caller
+        gathers that row's logits and finishes it on the host)."""
+        world, rows = cands.shape[0], cands.shape[1]
+        call("dgpp_sample_merge", ptr(self.rows_dev), ptr(cands.contiguous()), ptr(mss.contiguous()), ptr(nts.contiguous()),
+             ptr(self.out_token), ptr(self.out_logprob), ptr(self.out_flags), ptr(self.out_top_ids), ptr(self.out_top_lp),
+             ptr(self.out_top_n), rows, world, self.candidates, stream_ptr())
+        tok, lp, flags = self.out_token[:rows].tolist(), self.out_logprob[:rows].tolist(), self.out_flags[:rows].tolist()
+        need_top = any(p.top_logprobs for p in params)
+        tn = self.out_top_n[:rows].tolist() if need_top else [0] * rows
+        tids = self.out_top_ids[:rows].tolist() if need_top else None
+        tlps = self.out_top_lp[:rows].tolist() if need_top else None
+        out = []
+        for r in range(rows):
+            top = [(tids[r][i], tlps[r][i]) for i in range(tn[r])] if (need_top and flags[r]) else []
+            out.append(Sampled(tok[r], lp[r], top, bool(flags[r])))
+        if count_picks:
+            for r, sm in enumerate(out):
+                if slots[r] >= 0 and sm.on_device:
+                    self.count(slots[r], [sm.token])
+        return out
+
+    def sample_sharded(self, logits_slice: torch.Tensor, id_base: int, params, slots, positions, group=None, masks=None,
+                       count_picks: bool = True) -> List[Sampled]:
+        """Sampling on a vocabulary-sharded head without gathering the logits: per-rank candidate tables (a few KB per
+        row) are all-gathered and folded identically on every rank.  Rows that do not resolve inside the candidate
+        prefix gather their logits and finish on the host (rare: top_p close to 1 on a flat distribution)."""
+        import torch.distributed as dist
+
+        world = dist.get_world_size(group)
+        cand, ms, nt = self.local_tables(logits_slice, id_base, params, slots, positions, masks)
+        gc = torch.empty(world, *cand.shape, dtype=cand.dtype, device=self.dev)
+        gm = torch.empty(world, *ms.shape, dtype=ms.dtype, device=self.dev)
+        gn = torch.empty(world, *nt.shape, dtype=nt.dtype, device=self.dev)
+        dist.all_gather_into_tensor(gc, cand, group=group)
+        dist.all_gather_into_tensor(gm, ms, group=group)
+        dist.all_gather_into_tensor(gn, nt, group=group)
+        out = self.merge_tables(gc, gm, gn, params, slots, count_picks=False)
+        for r, sm in enumerate(out):
+            if not sm.on_device:
+                part = logits_slice[r:r + 1].contiguous()
+                parts = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(parts, part, group=group)
+                full = torch.cat(parts, dim=1)[0]
+                out[r] = self._host_finish(full[:self.vocab], params[r], slots[r], positions[r], None if masks is None else masks[r])
+        if count_picks:
+            for r, sm in enumerate(out):
+                if slots[r] >= 0:
+                    self.count(slots[r], [sm.token])
         return out
 
     def _host_finish(self, logits_row, p: SamplingParams, slot: int, pos: int, mask_row) -> Sampled:

@@ -95,3 +95,46 @@ def test_device_sampler_mask_and_counts(dev):
         assert got[r].logprob == lp
     # the picks were counted for the slots
     assert int(s.counts[0, got[0].token]) == 1 and int(s.counts[1, got[1].token]) == 1
+
+
+@pytest.mark.parametrize("vocab,world", [(4096, 4), (151936, 8), (1000, 2)])
+def test_sharded_candidate_fold_picks_the_unsharded_tokens(dev, vocab, world):
+    """Vocabulary-sharded head: per-slice candidate tables (step 1 on every slice, emulated here by running the slices one
+    after the other on one GPU) folded by the merge kernel give the token of the unsharded sampler on the full row; the
+    log-probability differs only by the slice-wise order of the log-sum-exp fold."""
+    from dgpp_b200.sampling.device import DeviceSampler, SamplingParams
+
+    torch.manual_seed(vocab + world)
+    rows = 10
+    s = DeviceSampler(vocab, rows, slots=4, device=dev)
+    logits = (torch.randn(rows, vocab, device=dev) * 3.0).contiguous()
+    logits[3, 17] = logits[3, vocab - 5] = logits[3].max() + 1.0         # exact tie across two slices: lowest id wins
+    params = [
+        SamplingParams(), SamplingParams(top_logprobs=5), SamplingParams(temperature=0.7, top_k=40, seed=1),
+        SamplingParams(temperature=1.0, top_k=2, seed=2, top_logprobs=3), SamplingParams(temperature=0.9, top_p=0.9, seed=3),
+        SamplingParams(temperature=1.3, min_p=0.05, seed=4, top_logprobs=20),
+        SamplingParams(temperature=0.8, top_k=50, top_p=0.95, min_p=0.01, seed=5),
+        SamplingParams(temperature=0.6, top_k=20, repetition_penalty=1.3, presence_penalty=0.5, frequency_penalty=0.2, seed=7),
+        SamplingParams(temperature=0.5, top_k=10, seed=8, logit_bias={5: 4.0, vocab - 3: 6.0, 123: 2.5}),
+        SamplingParams(temperature=0.3, top_k=100, seed=10),
+    ]
+    slots = [-1, -1, 0, -1, 1, -1, 2, 3, -1, -1]
+    for sl in (0, 1, 2, 3):
+        s.count(sl, [int(logits[slots.index(sl)].argmax())] * 3 + [7, vocab - 1])
+    positions = [50 + r for r in range(rows)]
+    want = s.sample(logits, params, slots, positions, count_picks=False)
+    per = (vocab + world - 1) // world
+    tabs = []
+    for w in range(world):
+        lo, hi = w * per, min(vocab, (w + 1) * per)
+        c, m, n = s.local_tables(logits[:, lo:hi], lo, params, slots, positions)
+        tabs.append((c.clone(), m.clone(), n.clone()))
+    got = s.merge_tables(torch.stack([t[0] for t in tabs]), torch.stack([t[1] for t in tabs]),
+                         torch.stack([t[2] for t in tabs]), params, slots, count_picks=False)
+    for r in range(rows):
+        if not (want[r].on_device and got[r].on_device):
+            continue                                   # a row the candidate prefix does not resolve: host path in both
+        assert got[r].token == want[r].token, (r, got[r], want[r])
+        assert abs(got[r].logprob - want[r].logprob) < 1e-4, r
+        assert [a for a, _ in got[r].top] == [a for a, _ in want[r].top], r
+    assert sum(g.on_device for g in got) >= 8
