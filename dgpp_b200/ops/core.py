@@ -663,6 +663,50 @@ def hadamard32_quant_int8(x: torch.Tensor, period: int = 0):
     return codes, scales
 
 
+# ---------------------------------------------------------------------------------------------- family operators
+_lib.declare("dgpp_justnorm", [P, P, I, I, F, P])
+_lib.declare("dgpp_slerp_alpha", [P, P, P, F, P, I, I, F, P])
+_lib.declare("dgpp_gr_gate_act", [P, L, I, I, P])
+_lib.declare("dgpp_gr_mix_finish", [P, P, P, I, I, I, P])
+_lib.declare("dgpp_gr_combine", [P, P, P, P, P, I, I, I, P])
+
+
+def justnorm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """Unit-norm rows: bf16(x / sqrt(sum x^2 + eps)), the sum in fp64."""
+    _chk(x, torch.bfloat16, "x")
+    y = torch.empty_like(x)
+    call("dgpp_justnorm", ptr(x), ptr(y), x.shape[0], x.shape[1], float(eps), stream_ptr())
+    return y
+
+
+def slerp_alpha(a: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor, s: float, eps: float = 1e-6) -> torch.Tensor:
+    """Hypersphere residual: justnorm(an + |alpha s| (bn - an)) with an / bn the bf16 unit-norm rows of a / b."""
+    out = torch.empty_like(a)
+    call("dgpp_slerp_alpha", ptr(a), ptr(b), ptr(alpha), float(s), ptr(out), a.shape[0], a.shape[1], float(eps), stream_ptr())
+    return out
+
+
+def gr_gate_act(t: torch.Tensor, hc: int) -> torch.Tensor:
+    """In place: t = bf16(silu(bf16(t / hc)))."""
+    call("dgpp_gr_gate_act", ptr(t), t.shape[0], t.shape[1], hc, stream_ptr())
+    return t
+
+
+def gr_mix_finish(logits: torch.Tensor, rn: torch.Tensor, hc: int) -> torch.Tensor:
+    """logits, rn [rows, hc * H] -> x [rows, H]: gated mean over the hc branches."""
+    rows, H = logits.shape[0], logits.shape[1] // hc
+    x = torch.empty(rows, H, dtype=torch.bfloat16, device=logits.device)
+    call("dgpp_gr_mix_finish", ptr(logits), ptr(rn), ptr(x), rows, hc, H, stream_ptr())
+    return x
+
+
+def gr_combine(r_state: torch.Tensor, rn: torch.Tensor, w_inject: torch.Tensor, y: torch.Tensor, hc: int, gates=None) -> torch.Tensor:
+    """In place on r_state [rows, hc * H]: branch i += bf16(y * s_i), s_i = 2 sigmoid(<w_inject[i], rn[row]> / hc)."""
+    rows, H = y.shape
+    call("dgpp_gr_combine", ptr(r_state), ptr(rn), ptr(w_inject), ptr(y), ptr(gates), rows, hc, H, stream_ptr())
+    return r_state
+
+
 # ---------------------------------------------------------------------------------------------- native FP8 linear
 _lib.declare("dgpp_fp8_act_quant", [P, L, P, P, I, I, I, P])
 _lib.declare("dgpp_gemm_fp8", [P, P, P, P, P, P, I, I, I, I, I, I, I, P])

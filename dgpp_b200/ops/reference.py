@@ -207,3 +207,45 @@ def kda_recurrent(q, k, v, gate, beta, A_log, dt_bias, lower_bound: float, state
         S.add_(torch.einsum("hk,hv->hkv", kf[t], u))
         out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
     return out.to(torch.bfloat16).view(T, hv * dv)
+
+
+def _bf(x):
+    return x.to(torch.bfloat16).float()
+
+
+def justnorm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    xf = x.float()
+    rstd = 1.0 / torch.sqrt(xf.double().pow(2).sum(-1, keepdim=True).float() + eps)
+    return (xf * rstd).to(torch.bfloat16)
+
+
+def slerp_alpha(a, b, alpha, s: float, eps: float = 1e-6) -> torch.Tensor:
+    an, bn = justnorm(a, eps).float(), justnorm(b, eps).float()
+    lr = (alpha.float() * s).abs()
+    m = an + lr * (bn - an)
+    rstd = 1.0 / torch.sqrt(m.double().pow(2).sum(-1, keepdim=True).float() + eps)
+    return (m * rstd).to(torch.bfloat16)
+
+
+def gr_gate_act(t: torch.Tensor, hc: int) -> torch.Tensor:
+    v = _bf(t.float() / hc)
+    return (v * torch.sigmoid(v)).to(torch.bfloat16)
+
+
+def gr_mix_finish(logits, rn, hc: int) -> torch.Tensor:
+    rows = logits.shape[0]
+    H = logits.shape[1] // hc
+    g = _bf(torch.sigmoid(logits.float())).view(rows, hc, H)
+    prod = _bf(g * rn.float().view(rows, hc, H))
+    acc = torch.zeros(rows, H, device=logits.device)
+    for i in range(hc):
+        acc = acc + prod[:, i]
+    return (acc / hc).to(torch.bfloat16)
+
+
+def gr_combine(r_state, rn, w_inject, y, hc: int) -> torch.Tensor:
+    rows, H = y.shape
+    dots = rn.float() @ w_inject.float().t()                                   # [rows, hc]
+    s = 2.0 * _bf(torch.sigmoid(_bf(dots / hc)))
+    add = _bf(y.float().unsqueeze(1) * s.unsqueeze(-1))                        # [rows, hc, H]
+    return (r_state.float().view(rows, hc, H) + add).to(torch.bfloat16).view(rows, hc * H)

@@ -103,3 +103,26 @@ def test_releasable_range_commit_release_keeps_addresses(dev):
         assert torch.cuda.mem_get_info()[0] >= free0 - (1 << 20)
     finally:
         r.close()
+
+
+def test_ngpt_norms_and_gated_residual_kernels(dev):
+    from dgpp_b200.ops import core as ops, reference as ref
+
+    torch.manual_seed(9)
+    x = (torch.randn(13, 4096, device=dev) * 2).to(BF)
+    assert torch.equal(ops.justnorm(x), ref.justnorm(x))
+    a, b = (torch.randn(7, 7168, device=dev)).to(BF), (torch.randn(7, 7168, device=dev) * 3).to(BF)
+    alpha = (torch.rand(7168, device=dev) * 0.2).to(BF)
+    got, want = ops.slerp_alpha(a, b, alpha, 1.7), ref.slerp_alpha(a, b, alpha, 1.7)
+    assert (got.float() - want.float()).abs().max().item() <= 2 ** -9            # at most one bf16 ulp of a unit-norm row
+    assert (got != want).float().mean().item() < 0.01
+    hc, H, rows = 4, 1024, 9
+    t = torch.randn(rows, 64, device=dev).to(BF) * 4
+    assert torch.equal(ops.gr_gate_act(t.clone(), hc), ref.gr_gate_act(t, hc))
+    logits, rn = torch.randn(rows, hc * H, device=dev).to(BF), torch.randn(rows, hc * H, device=dev).to(BF)
+    gm, wm = ops.gr_mix_finish(logits, rn, hc), ref.gr_mix_finish(logits, rn, hc)
+    assert (gm.float() - wm.float()).abs().max().item() <= 2 ** -7 and (gm != wm).float().mean().item() < 0.01
+    R = torch.randn(rows, hc * H, device=dev).to(BF)
+    w_inj, y = (torch.randn(hc, hc * H, device=dev) * 0.02).to(BF), torch.randn(rows, H, device=dev).to(BF)
+    gc, wc = ops.gr_combine(R.clone(), rn, w_inj, y, hc), ref.gr_combine(R, rn, w_inj, y, hc)
+    assert (gc.float() - wc.float()).abs().max().item() <= 0.07 and (gc != wc).float().mean().item() < 0.02
