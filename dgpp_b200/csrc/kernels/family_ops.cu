@@ -183,3 +183,151 @@ DGPP_API int dgpp_gr_combine(void* r_state, const void* rn, const void* w_inject
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Manifold-constrained hyper-connections over n residual streams [tokens, n, D] (n <= 8):
+//   flat    = unweighted RMSNorm of the flattened streams (fp32, eps = norm_eps)
+//   logits  = flat . fn^T                       fn: bf16 [(2 + n) n, n D]
+//   pre     = sigmoid(logits[0:n] scale[0] + base[0:n]) + hc_eps                 stream-collapse weights
+//   post    = 2 sigmoid(logits[n:2n] scale[1] + base[n:2n])                      placement of the block output
+//   comb    = softmax over the last axis of (logits[2n:] scale[2] + base[2n:]) viewed [n, n], + hc_eps, then
+//             Sinkhorn-Knopp: one column normalisation, then (iters - 1) times (row, column); every division adds
+//             hc_eps to its denominator
+//   collapsed = bf16(sum_j pre[j] streams[j])   (fp32 accumulation)
+// and the fold of a block output h:  streams'[i] = bf16(bf16(post_i h) + bf16(sum_j comb[j, i] streams[j])) with post and
+// comb rounded to bf16 before the products.
+// One CTA per token; the (2 + n) n dots share one pass over the row (inv_rms applied to the finished sums).
+// (reference counterparts: src/kernels/glm_mhc.cu, semantics in src/models/glm/mhc.hpp.)
+namespace dgpp {
+
+constexpr int kMhcMaxN = 8;
+
+template <int N>
+__global__ void __launch_bounds__(kFamThreads) mhc_compute_kernel(const bf16* __restrict__ streams, const bf16* __restrict__ fn,
+                                                                  const float* __restrict__ base, const float* __restrict__ scale,
+                                                                  bf16* __restrict__ collapsed, bf16* __restrict__ post_out,
+                                                                  bf16* __restrict__ comb_out, int D, int iters, float hc_eps,
+                                                                  float norm_eps) {
+  constexpr int n = N, C = (2 + N) * N;
+  __shared__ float part[C + 1][kFamThreads / 32];
+  __shared__ float pre_s[N];
+  pdl_wait();
+  const size_t tok = blockIdx.x;
+  const int W = n * D;
+  const bf16* row = streams + tok * W;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // one pass: sum of squares and the C dots (each thread keeps C + 1 partials; C <= 80)
+  float ss = 0.f;
+  float dots[C];
+#pragma unroll
+  for (int c = 0; c < C; ++c) dots[c] = 0.f;
+  for (int k = threadIdx.x; k < W; k += kFamThreads) {
+    const float x = bf16_to_f32(row[k]);
+    ss = fmaf(x, x, ss);
+#pragma unroll
+    for (int c = 0; c < C; ++c) dots[c] = fmaf(x, bf16_to_f32(fn[static_cast<size_t>(c) * W + k]), dots[c]);
+  }
+#pragma unroll
+  for (int c = 0; c <= C; ++c) {
+    float v = c < C ? dots[c] : ss;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) part[c][warp] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot[C + 1];
+    for (int c = 0; c <= C; ++c) {
+      float t = 0.f;
+      for (int w = 0; w < kFamThreads / 32; ++w) t += part[c][w];
+      tot[c] = t;
+    }
+    const float inv_rms = rsqrtf(tot[C] / static_cast<float>(W) + norm_eps);
+    float comb[N][N];
+    for (int j = 0; j < n; ++j) {
+      pre_s[j] = 1.f / (1.f + expf(-(tot[j] * inv_rms * scale[0] + base[j]))) + hc_eps;
+      const float po = 2.f / (1.f + expf(-(tot[n + j] * inv_rms * scale[1] + base[n + j])));
+      post_out[tok * n + j] = f32_to_bf16(po);
+    }
+    for (int j = 0; j < n; ++j) {
+      float m = -INFINITY;
+      for (int i = 0; i < n; ++i) {
+        comb[j][i] = tot[2 * n + j * n + i] * inv_rms * scale[2] + base[2 * n + j * n + i];
+        m = fmaxf(m, comb[j][i]);
+      }
+      float s = 0.f;
+      for (int i = 0; i < n; ++i) { comb[j][i] = expf(comb[j][i] - m); s += comb[j][i]; }
+      for (int i = 0; i < n; ++i) comb[j][i] = comb[j][i] / s + hc_eps;
+    }
+    auto col_pass = [&]() {
+      for (int i = 0; i < n; ++i) {
+        float s = 0.f;
+        for (int j = 0; j < n; ++j) s += comb[j][i];
+        for (int j = 0; j < n; ++j) comb[j][i] = comb[j][i] / (s + hc_eps);
+      }
+    };
+    auto row_pass = [&]() {
+      for (int j = 0; j < n; ++j) {
+        float s = 0.f;
+        for (int i = 0; i < n; ++i) s += comb[j][i];
+        for (int i = 0; i < n; ++i) comb[j][i] = comb[j][i] / (s + hc_eps);
+      }
+    };
+    col_pass();
+    for (int it = 1; it < iters; ++it) { row_pass(); col_pass(); }
+    for (int j = 0; j < n; ++j)
+      for (int i = 0; i < n; ++i) comb_out[(tok * n + j) * n + i] = f32_to_bf16(comb[j][i]);
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += kFamThreads) {
+    float acc = 0.f;
+    for (int j = 0; j < n; ++j) acc = fmaf(pre_s[j], bf16_to_f32(row[static_cast<size_t>(j) * D + d]), acc);
+    collapsed[tok * D + d] = f32_to_bf16(acc);
+  }
+}
+
+// streams' [tokens, n, D] (may alias streams): grid (ceil(D / 256), tokens).
+__global__ void __launch_bounds__(256) mhc_fold_kernel(const bf16* __restrict__ streams, const bf16* __restrict__ h,
+                                                       const bf16* __restrict__ post, const bf16* __restrict__ comb,
+                                                       bf16* __restrict__ out, int n, int D) {
+  pdl_wait();
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  const size_t tok = blockIdx.y;
+  float s[kMhcMaxN];
+  for (int j = 0; j < n; ++j) s[j] = bf16_to_f32(streams[(tok * n + j) * D + d]);
+  const float hv = bf16_to_f32(h[tok * D + d]);
+  for (int i = 0; i < n; ++i) {
+    float mix = 0.f;
+    for (int j = 0; j < n; ++j) mix = fmaf(bf16_to_f32(comb[(tok * n + j) * n + i]), s[j], mix);
+    const float placed = bf16_to_f32(f32_to_bf16(bf16_to_f32(post[tok * n + i]) * hv));
+    out[(tok * n + i) * D + d] = f32_to_bf16(placed + bf16_to_f32(f32_to_bf16(mix)));
+  }
+}
+
+}  // namespace dgpp
+
+DGPP_API int dgpp_mhc_compute(const void* streams, const void* fn, const void* base, const void* scale, void* collapsed, void* post,
+                              void* comb, int tokens, int n, int D, int iters, float hc_eps, float norm_eps, cudaStream_t st) {
+  DGPP_REQUIRE((n == 2 || n == 4 || n == 8) && D >= 1 && iters >= 1, "mhc_compute: %d streams (2, 4 or 8), D %d, iters %d", n, D, iters);
+  if (tokens == 0) return 0;
+#define DGPP_MHC(NV)                                                                                                              \
+  dgpp::mhc_compute_kernel<NV><<<tokens, dgpp::kFamThreads, 0, st>>>(                                                            \
+      static_cast<const bf16*>(streams), static_cast<const bf16*>(fn), static_cast<const float*>(base), static_cast<const float*>(scale), \
+      static_cast<bf16*>(collapsed), static_cast<bf16*>(post), static_cast<bf16*>(comb), D, iters, hc_eps, norm_eps)
+  if (n == 2) DGPP_MHC(2); else if (n == 4) DGPP_MHC(4); else DGPP_MHC(8);
+#undef DGPP_MHC
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+DGPP_API int dgpp_mhc_fold(const void* streams, const void* h, const void* post, const void* comb, void* out, int tokens, int n, int D,
+                           cudaStream_t st) {
+  DGPP_REQUIRE(n >= 1 && n <= dgpp::kMhcMaxN, "mhc_fold: %d streams (1..8)", n);
+  if (tokens == 0) return 0;
+  dgpp::mhc_fold_kernel<<<dim3(dgpp_ceil_div(D, 256), tokens), 256, 0, st>>>(static_cast<const bf16*>(streams), static_cast<const bf16*>(h),
+                                                                           static_cast<const bf16*>(post), static_cast<const bf16*>(comb),
+                                                                           static_cast<bf16*>(out), n, D);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}

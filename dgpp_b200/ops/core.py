@@ -707,6 +707,32 @@ def gr_combine(r_state: torch.Tensor, rn: torch.Tensor, w_inject: torch.Tensor, 
     return r_state
 
 
+_lib.declare("dgpp_mhc_compute", [P, P, P, P, P, P, P, I, I, I, I, F, F, P])
+_lib.declare("dgpp_mhc_fold", [P, P, P, P, P, I, I, I, P])
+
+
+def mhc_compute(streams, fn, base, scale, iters: int = 20, hc_eps: float = 1e-6, norm_eps: float = 1e-5):
+    """Hyper-connection coefficients of n residual streams [tokens, n, D]: returns (collapsed [tokens, D], post [tokens, n],
+    comb [tokens, n, n]) in bf16.  fn: bf16 [(2 + n) n, n D]; base fp32 [(2 + n) n]; scale fp32 [3]."""
+    tokens, n, D = streams.shape
+    dev = streams.device
+    collapsed = torch.empty(tokens, D, dtype=torch.bfloat16, device=dev)
+    post = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
+    comb = torch.empty(tokens, n, n, dtype=torch.bfloat16, device=dev)
+    call("dgpp_mhc_compute", ptr(streams), ptr(fn), ptr(base), ptr(scale), ptr(collapsed), ptr(post), ptr(comb), tokens, n, D,
+         iters, float(hc_eps), float(norm_eps), stream_ptr())
+    return collapsed, post, comb
+
+
+def mhc_fold(streams, h, post, comb, out=None):
+    """streams'[i] = bf16(bf16(post_i h) + bf16(sum_j comb[j, i] streams[j])); out may be `streams` (in place)."""
+    tokens, n, D = streams.shape
+    if out is None:
+        out = torch.empty_like(streams)
+    call("dgpp_mhc_fold", ptr(streams), ptr(h), ptr(post), ptr(comb), ptr(out), tokens, n, D, stream_ptr())
+    return out
+
+
 # ---------------------------------------------------------------------------------------------- native FP8 linear
 _lib.declare("dgpp_fp8_act_quant", [P, L, P, P, I, I, I, P])
 _lib.declare("dgpp_gemm_fp8", [P, P, P, P, P, P, I, I, I, I, I, I, I, P])

@@ -249,3 +249,27 @@ def gr_combine(r_state, rn, w_inject, y, hc: int) -> torch.Tensor:
     s = 2.0 * _bf(torch.sigmoid(_bf(dots / hc)))
     add = _bf(y.float().unsqueeze(1) * s.unsqueeze(-1))                        # [rows, hc, H]
     return (r_state.float().view(rows, hc, H) + add).to(torch.bfloat16).view(rows, hc * H)
+
+
+def mhc_compute(streams, fn, base, scale, iters: int = 20, hc_eps: float = 1e-6, norm_eps: float = 1e-5):
+    """Oracle of ops.mhc_compute (fp32 throughout, bf16 at the outputs)."""
+    tokens, n, D = streams.shape
+    x = streams.float().view(tokens, n * D)
+    flat = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + norm_eps)
+    logits = flat @ fn.float().t()
+    pre = torch.sigmoid(logits[:, :n] * scale[0] + base[:n]) + hc_eps
+    post = 2.0 * torch.sigmoid(logits[:, n:2 * n] * scale[1] + base[n:2 * n])
+    comb = torch.softmax(logits[:, 2 * n:].view(tokens, n, n) * scale[2] + base[2 * n:].view(n, n), -1) + hc_eps
+    comb = comb / (comb.sum(-2, keepdim=True) + hc_eps)
+    for _ in range(iters - 1):
+        comb = comb / (comb.sum(-1, keepdim=True) + hc_eps)
+        comb = comb / (comb.sum(-2, keepdim=True) + hc_eps)
+    collapsed = torch.einsum("tj,tjd->td", pre, streams.float())
+    return collapsed.to(torch.bfloat16), post.to(torch.bfloat16), comb.to(torch.bfloat16)
+
+
+def mhc_fold(streams, h, post, comb):
+    """Oracle of ops.mhc_fold."""
+    placed = _bf(post.float().unsqueeze(-1) * h.float().unsqueeze(1))                      # [t, n, D]
+    mix = _bf(torch.einsum("tji,tjd->tid", comb.float(), streams.float()))
+    return (placed + mix).to(torch.bfloat16)

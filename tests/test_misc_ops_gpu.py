@@ -126,3 +126,29 @@ def test_ngpt_norms_and_gated_residual_kernels(dev):
     w_inj, y = (torch.randn(hc, hc * H, device=dev) * 0.02).to(BF), torch.randn(rows, H, device=dev).to(BF)
     gc, wc = ops.gr_combine(R.clone(), rn, w_inj, y, hc), ref.gr_combine(R, rn, w_inj, y, hc)
     assert (gc.float() - wc.float()).abs().max().item() <= 0.07 and (gc != wc).float().mean().item() < 0.02
+
+
+def test_hyper_connection_coefficients_and_fold(dev):
+    from dgpp_b200.ops import core as ops, reference as ref
+
+    torch.manual_seed(12)
+    tokens, n, D = 11, 4, 1024
+    streams = torch.randn(tokens, n, D, device=dev).to(BF)
+    fn = (torch.randn((2 + n) * n, n * D, device=dev) * 0.05).to(BF)
+    base = torch.randn((2 + n) * n, device=dev) * 0.5
+    scale = torch.tensor([0.7, 1.3, 2.0], device=dev)
+    col, post, comb = ops.mhc_compute(streams, fn, base, scale, iters=20)
+    wcol, wpost, wcomb = ref.mhc_compute(streams, fn, base, scale, iters=20)
+    assert (post.float() - wpost.float()).abs().max().item() <= 2 ** -6
+    assert (comb.float() - wcomb.float()).abs().max().item() <= 2 ** -7
+    assert (col.float() - wcol.float()).abs().max().item() <= 0.02 * wcol.float().abs().max().item()
+    # the mixer is close to doubly stochastic after the Sinkhorn passes
+    c = comb.float()
+    assert (c.sum(-2) - 1).abs().max().item() < 0.02 and (c.sum(-1) - 1).abs().max().item() < 0.05
+    h = torch.randn(tokens, D, device=dev).to(BF)
+    got = ops.mhc_fold(streams, h, post, comb)
+    want = ref.mhc_fold(streams, h, post, comb)
+    assert (got.float() - want.float()).abs().max().item() <= 2 ** -5 and (got != want).float().mean().item() < 0.01
+    inplace = streams.clone()
+    ops.mhc_fold(inplace, h, post, comb, out=inplace)
+    assert torch.equal(inplace, got)
