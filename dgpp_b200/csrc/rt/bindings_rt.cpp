@@ -39,6 +39,14 @@ class PyEngine : public SchedulerEngine {
     std::vector<int32_t> v(tokens, tokens + count);
     return f(slot, v, pos, last).cast<int32_t>();
   }
+  std::vector<int32_t> prefill_group(const std::vector<PrefillPiece>& pieces) override {
+    py::gil_scoped_acquire gil;
+    py::function f = py::get_override(static_cast<const SchedulerEngine*>(this), "prefill_group");
+    if (!f) return SchedulerEngine::prefill_group(pieces);       // one prefill() call per piece
+    py::list arg;
+    for (const auto& p : pieces) arg.append(py::make_tuple(p.slot, std::vector<int32_t>(p.tokens, p.tokens + p.count), p.pos, p.last));
+    return f(arg).cast<std::vector<int32_t>>();
+  }
   std::vector<std::vector<int32_t>> step_batch(const std::vector<int>& slots) override {
     PYBIND11_OVERRIDE_PURE(std::vector<std::vector<int32_t>>, SchedulerEngine, step_batch, slots);
   }
@@ -163,7 +171,8 @@ void bind_more(py::module_& m) {
       .def_readwrite("prefix_cache", &SchedulerConfig::prefix_cache)
       .def_readwrite("prefix_min_tokens", &SchedulerConfig::prefix_min_tokens)
       .def_readwrite("prefix_max_entries", &SchedulerConfig::prefix_max_entries)
-      .def_readwrite("grow_margin_tokens", &SchedulerConfig::grow_margin_tokens);
+      .def_readwrite("grow_margin_tokens", &SchedulerConfig::grow_margin_tokens)
+      .def_readwrite("prefill_group_max", &SchedulerConfig::prefill_group_max);
 
   py::class_<PyScheduler>(m, "Scheduler")
       .def(py::init<py::object, const SchedulerConfig&>())

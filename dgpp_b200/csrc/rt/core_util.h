@@ -225,6 +225,7 @@ struct ClusterConfig {
   int max_concurrency = 8;
   int64_t max_context = 32768;
   int prefill_chunk = 2048;
+  int prefill_group_max = 4;                // readers packed into one prefill pass (1 = one request per pass)
   std::string kv_dtype = "fp8";
   int64_t kv_headroom_mib = 4096;
   bool prefix_cache = true;
@@ -252,7 +253,7 @@ struct ClusterConfig {
     const json::Value v = json::parse(text, /*reject_duplicates=*/true);
     if (!v.is_object()) throw std::runtime_error("config: the top level must be an object");
     static const std::set<std::string> known = {
-        "model", "host", "port", "tensor_parallel", "expert_parallel", "max_concurrency", "max_context", "prefill_chunk",
+        "model", "host", "port", "tensor_parallel", "expert_parallel", "max_concurrency", "max_context", "prefill_chunk", "prefill_group_max",
         "kv_dtype", "kv_headroom_mib", "prefix_cache", "prefix_min_tokens", "scheduler_policy", "mtp_depth",
         "sampling_candidates", "fuse_all_reduce", "log_level", "engine_decode_splits", "engine_fuse_combine",
         "engine_l2_prefetch", "engine_fp4_splits", "engine_cluster_splitk", "engine_fp4_preload", "engine_layer_kernel",
@@ -269,6 +270,7 @@ struct ClusterConfig {
     c.max_concurrency = static_cast<int>(v.get_int("max_concurrency", c.max_concurrency));
     c.max_context = v.get_int("max_context", c.max_context);
     c.prefill_chunk = static_cast<int>(v.get_int("prefill_chunk", c.prefill_chunk));
+    c.prefill_group_max = static_cast<int>(v.get_int("prefill_group_max", c.prefill_group_max));
     c.kv_dtype = v.get_string("kv_dtype", c.kv_dtype);
     c.kv_headroom_mib = v.get_int("kv_headroom_mib", c.kv_headroom_mib);
     c.prefix_cache = v.get_bool("prefix_cache", true);
@@ -297,6 +299,7 @@ struct ClusterConfig {
     need(c.max_concurrency >= 1 && c.max_concurrency <= 64, "max_concurrency must be 1..64");
     need(c.max_context >= 16, "max_context too small");
     need(c.prefill_chunk >= 16 && c.prefill_chunk % 16 == 0, "prefill_chunk must be a positive multiple of 16");
+    need(c.prefill_group_max >= 1 && c.prefill_group_max <= 64, "prefill_group_max must be 1..64");
     need(c.kv_dtype == "fp8" || c.kv_dtype == "bf16", "kv_dtype must be fp8 or bf16");
     need(c.scheduler_policy == "grow" || c.scheduler_policy == "reserve", "scheduler_policy must be grow or reserve");
     need(c.mtp_depth >= 0 && c.mtp_depth <= 5, "mtp_depth must be 0..5");
@@ -313,7 +316,7 @@ struct ClusterConfig {
     v.set("expert_parallel", expert_parallel); v.set("fuse_all_reduce", fuse_all_reduce); v.set("host", host);
     v.set("kv_dtype", kv_dtype); v.set("kv_headroom_mib", kv_headroom_mib); v.set("log_level", log_level);
     v.set("max_concurrency", max_concurrency); v.set("max_context", max_context); v.set("model", model);
-    v.set("mtp_depth", mtp_depth); v.set("port", port); v.set("prefill_chunk", prefill_chunk);
+    v.set("mtp_depth", mtp_depth); v.set("port", port); v.set("prefill_chunk", prefill_chunk); v.set("prefill_group_max", prefill_group_max);
     v.set("prefix_cache", prefix_cache); v.set("prefix_min_tokens", prefix_min_tokens);
     v.set("sampling_candidates", sampling_candidates); v.set("scheduler_policy", scheduler_policy);
     v.set("tensor_parallel", tensor_parallel);

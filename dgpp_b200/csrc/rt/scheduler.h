@@ -50,6 +50,22 @@ class SchedulerEngine {
   virtual void attach_prefix(int slot, const std::vector<int32_t>& blocks) = 0;
   // Run prompt tokens [pos, pos+count) of the slot.  Returns the first generated token when `last`, else -1.
   virtual int32_t prefill(int slot, const int32_t* tokens, int64_t pos, int64_t count, bool last) = 0;
+  // Several readers in ONE engine call (group prefill): pieces of different slots, each a run of consecutive prompt
+  // positions.  Returns, per piece, the first generated token when the piece is `last`, else -1.  The default runs the
+  // pieces one after the other; an engine that can carry rows of several requests in one pass overrides it (the weights
+  // are then read once for all of them).
+  struct PrefillPiece {
+    int slot;
+    const int32_t* tokens;
+    int64_t pos, count;
+    bool last;
+  };
+  virtual std::vector<int32_t> prefill_group(const std::vector<PrefillPiece>& pieces) {
+    std::vector<int32_t> out;
+    out.reserve(pieces.size());
+    for (const auto& p : pieces) out.push_back(prefill(p.slot, p.tokens, p.pos, p.count, p.last));
+    return out;
+  }
   // One decode pass; result[i] holds the new tokens of slots[i] (one, or several with speculative decoding).
   virtual std::vector<std::vector<int32_t>> step_batch(const std::vector<int>& slots) = 0;
   virtual int max_tokens_per_step() const { return 1; }
@@ -109,6 +125,10 @@ struct SchedulerConfig {
   int64_t prefix_min_tokens = 16;
   int64_t prefix_max_entries = 1 << 20;
   int64_t grow_margin_tokens = 1;       // grow-on-demand keeps this many positions reserved ahead
+  // Group prefill: the readers of a tick are planned together and handed to the engine in calls of up to
+  // `prefill_group_max` pieces whose tokens sum to at most `prefill_chunk` (oldest reader first, every reader gets an
+  // equal share of what the budget leaves before the leftovers go to the oldest).  1 = one reader per engine call.
+  int prefill_group_max = 1;
 };
 
 struct SchedMeters {
@@ -371,6 +391,7 @@ class Scheduler {
     for (size_t s = 0; s < slots_.size(); ++s)
       if (slots_[s].live && slots_[s].phase == Phase::Prefill) order.push_back(static_cast<int>(s));
     std::sort(order.begin(), order.end(), [this](int a, int b) { return slots_[a].arrival < slots_[b].arrival; });
+    if (cfg_.prefill_group_max > 1 && order.size() > 1) return advance_prefill_group(order, budget);
     for (int s : order) {
       while (budget > 0 && slots_[s].live && slots_[s].phase == Phase::Prefill) {
         Slot& sl = slots_[s];
@@ -390,6 +411,72 @@ class Scheduler {
         }
       }
       if (budget <= 0) break;
+    }
+    return produced;
+  }
+
+  // Readers in `order` (oldest first) advance together: per engine call at most prefill_group_max pieces and
+  // prefill_chunk tokens; a call's token room is split evenly over its readers, what is left goes to the readers
+  // closest to the end of their prompt, so a long prompt cannot starve the short ones behind it.
+  int64_t advance_prefill_group(const std::vector<int>& order, int64_t budget) {
+    int64_t produced = 0;
+    for (;;) {
+      std::vector<int> readers;
+      for (int s : order)
+        if (slots_[s].live && slots_[s].phase == Phase::Prefill &&
+            static_cast<int>(readers.size()) < cfg_.prefill_group_max) readers.push_back(s);
+      int64_t room = std::min<int64_t>(budget, cfg_.prefill_chunk);
+      if (readers.empty() || room <= 0) break;
+      // even shares, then the leftovers to the oldest readers that still have prompt left
+      std::vector<int64_t> take(readers.size(), 0);
+      const int64_t share = std::max<int64_t>(1, room / static_cast<int64_t>(readers.size()));
+      int64_t used = 0;
+      for (size_t i = 0; i < readers.size() && used < room; ++i) {
+        const Slot& sl = slots_[readers[i]];
+        take[i] = std::min<int64_t>({sl.prompt_len - sl.prefilled, share, room - used});
+        used += take[i];
+      }
+      // leftovers: the reader closest to the end of its prompt first (it reaches its first token in this call), age
+      // breaks ties
+      std::vector<size_t> by_need(readers.size());
+      for (size_t i = 0; i < by_need.size(); ++i) by_need[i] = i;
+      std::stable_sort(by_need.begin(), by_need.end(), [&](size_t a, size_t b) {
+        const Slot& x = slots_[readers[a]];
+        const Slot& y = slots_[readers[b]];
+        return x.prompt_len - x.prefilled - take[a] < y.prompt_len - y.prefilled - take[b];
+      });
+      for (size_t k = 0; k < by_need.size() && used < room; ++k) {
+        const size_t i = by_need[k];
+        const Slot& sl = slots_[readers[i]];
+        const int64_t more = std::min<int64_t>(sl.prompt_len - sl.prefilled - take[i], room - used);
+        take[i] += more;
+        used += more;
+      }
+      std::vector<SchedulerEngine::PrefillPiece> pieces;
+      std::vector<int> who;
+      for (size_t i = 0; i < readers.size(); ++i) {
+        if (take[i] <= 0) continue;
+        const Slot& sl = slots_[readers[i]];
+        pieces.push_back({readers[i], sl.tokens.data() + sl.prefilled, sl.prefilled, take[i],
+                          take[i] == sl.prompt_len - sl.prefilled});
+        who.push_back(readers[i]);
+      }
+      if (pieces.empty()) break;
+      const std::vector<int32_t> firsts = eng_->prefill_group(pieces);
+      ++meters_.prefill_calls;
+      for (size_t i = 0; i < pieces.size(); ++i) {
+        const int s = who[i];
+        Slot& sl = slots_[s];
+        fold("prefill", sl.req.id, (sl.prefilled << 20) | pieces[i].count);
+        meters_.prefill_tokens += pieces[i].count;
+        sl.prefilled += pieces[i].count;
+        budget -= pieces[i].count;
+        if (pieces[i].last) {
+          sl.phase = Phase::Decode;
+          publish(s, sl.prompt_len);
+          produced += accept_token(s, firsts[i]) ? 1 : 0;
+        }
+      }
     }
     return produced;
   }

@@ -53,6 +53,7 @@ static void test_scheduler() {
     cfg.prefill_budget_busy = 48;
     cfg.prefill_chunk = 40;
     cfg.prefix_min_tokens = 16;
+    cfg.prefill_group_max = policy ? 3 : 1;
     Scheduler sched(&eng, cfg);
     std::mt19937 rng(7 + policy);
     std::vector<int32_t> shared(160);

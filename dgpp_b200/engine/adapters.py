@@ -432,6 +432,28 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
             return tok
         return -1
 
+    def prefill_group(self, pieces):
+        """Several readers in one pass (see LLMEngine.prefill_group).  Requests with sampling settings, speculative
+        drafts or embedding spans take the one-request path."""
+        pieces = [(s, list(t), p, bool(l)) for s, t, p, l in pieces]
+        plain = all(not self.slot_cfg[s] and self._slot_embeds[s] is None for s, _, _, _ in pieces) and not self.spec_k
+        if not plain or len(pieces) == 1 or sum(len(t) for _, t, _, _ in pieces) > self.e.prefill_chunk:
+            return [self.prefill(s, t, p, l) for s, t, p, l in pieces]
+        with self.timer.phase("prefill"):
+            firsts = self.e.prefill_group([(s, self._real_ids(t), p, l) for s, t, p, l in pieces])
+        self._poll_device()
+        firsts = firsts.tolist()
+        out, k = [], 0
+        for s, t, p, l in pieces:
+            self.filled[s] = p + len(t)
+            if l:
+                tok = int(firsts[k]); k += 1
+                self.pending[s] = tok
+                out.append(tok)
+            else:
+                out.append(-1)
+        return out
+
     def _spec_graph(self, rows: int):
         """One captured forward per row count (rows = requests + draft rows of this pass)."""
         g = self.spec_graphs.get(rows)

@@ -117,6 +117,37 @@ class LLMEngine:
         r.embed_spans = None
         return r.pick_id[:1]
 
+    @torch.no_grad()
+    def prefill_group(self, pieces) -> torch.Tensor:
+        """Runs of prompt tokens of SEVERAL requests in one pass: pieces = [(slot, tokens, start_pos, last), ...] with at
+        most `prefill_chunk` tokens in total.  Every row attends through the per-row attention kernel (its request, its
+        position), so the pass reads the weights once for all requests.  Returns the greedy first tokens of the pieces
+        marked `last`, in piece order (int32 device tensor)."""
+        total = sum(len(t) for _, t, _, _ in pieces)
+        assert 1 <= total <= self.prefill_chunk
+        toks, pos, req, lasts = [], [], [], []
+        for slot, t, start, last in pieces:
+            n = len(t)
+            assert start + n <= self.max_seq_len
+            if not self.kv.reserve(slot, start + n):
+                raise RuntimeError("KV pool exhausted")
+            toks += list(t)
+            pos += list(range(start, start + n))
+            req += [slot] * n
+            if last:
+                lasts.append(len(toks) - 1)
+            self.lengths[slot] = start + n
+        host = torch.tensor([toks, pos, req], dtype=torch.int32)
+        self.p_tokens[:total].copy_(host[0])
+        self.p_positions[:total].copy_(host[1])
+        self.p_row_req[:total].copy_(host[2])
+        r = self.runner
+        r.embed_spans = None
+        idx = torch.tensor(lasts or [total - 1], dtype=torch.long, device=self.dev)
+        r.forward(total, self.p_tokens[:total], self.p_positions[:total], self.p_row_req[:total], decode=False, chunk=None,
+                  logits_rows=idx)
+        return r.pick_id[:len(lasts)]
+
     # ------------------------------------------------------------------ decode
     def _decode_body(self, b: int):
         r = self.runner

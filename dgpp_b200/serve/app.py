@@ -670,6 +670,9 @@ def serve_deployment(config_path: str) -> int:
     eng = KernelEngine(LLMEngine(model, max_batch=cfg["max_concurrency"], max_seq_len=cfg["max_context"],
                                  prefill_chunk=cfg["prefill_chunk"], reducer=reducer, fuse_ar=cfg["fuse_all_reduce"],
                                  options=EngineOptions.from_config(cfg)))
+    sc = rt.SchedulerConfig()
+    sc.prefill_chunk = int(cfg["prefill_chunk"])
+    sc.prefill_group_max = int(cfg["prefill_group_max"])
     leader = None
     if world > 1:
         from .world import WorldLeader, run_follower
@@ -689,11 +692,11 @@ def serve_deployment(config_path: str) -> int:
                 eng.configure(rid, params, g, ids)
 
             return run_follower(eng, os.environ.get("MASTER_ADDR", "127.0.0.1"), jport, config_digest=digest,
-                                on_configure=configure)
+                                on_configure=configure, sched_config=sc)
         leader = WorldLeader(world, jport, config_digest=digest)
         leader.wait_for_followers()
     srv = Server(eng, tok, template_src=template, model_name=name, host=cfg["host"], port=cfg["port"], eos_ids=eos,
-                 world_leader=leader)
+                 world_leader=leader, sched_config=sc)
     print(f"listening on http://{cfg['host']}:{srv.start()}", flush=True)
     try:
         while not srv.failed_event.wait(1.0):

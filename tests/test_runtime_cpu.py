@@ -22,7 +22,7 @@ def _trace(seed=0, n=64, vocab=4096, shared_len=256):
     return reqs
 
 
-def _run(reqs, slots=4, blocks=200, policy=None, tokens_per_step=1, prefix=True, budget=None):
+def _run(reqs, slots=4, blocks=200, policy=None, tokens_per_step=1, prefix=True, budget=None, group=1):
     eng = rt.FakeEngine(slots=slots, block_tokens=16, blocks=blocks, max_context=1024, vocab=4096,
                         tokens_per_step=tokens_per_step)
     cfg = rt.SchedulerConfig()
@@ -31,6 +31,7 @@ def _run(reqs, slots=4, blocks=200, policy=None, tokens_per_step=1, prefix=True,
         cfg.policy = policy
     if budget is not None:
         cfg.prefill_budget_idle = cfg.prefill_budget_busy = cfg.prefill_chunk = budget
+    cfg.prefill_group_max = group
     s = rt.Scheduler(eng, cfg)
     for rid, p in reqs.items():
         s.submit(rid, p, 32)
@@ -77,10 +78,63 @@ def test_scheduler_is_deterministic_and_scheduling_invariant():
     s2, _, out2, _ = _run(reqs)
     assert out1 == out2 and s1.op_digest() == s2.op_digest() and s1.prefix_digest() == s2.prefix_digest()
     # different slot counts, budgets, cache off, multi-token steps: same tokens per request
-    for kw in (dict(slots=1), dict(slots=8, blocks=400), dict(prefix=False), dict(budget=48), dict(tokens_per_step=3)):
+    for kw in (dict(slots=1), dict(slots=8, blocks=400), dict(prefix=False), dict(budget=48), dict(tokens_per_step=3),
+               dict(group=4), dict(group=8, slots=8, blocks=400, budget=96), dict(group=3, prefix=False)):
         _, _, out3, _ = _run(reqs, **kw)
         for rid in reqs:
             assert out3[rid][:32] == out1[rid], (kw, rid)
+
+
+def test_group_prefill_packs_readers_into_fewer_engine_calls():
+    """Readers of a tick advance together: the engine sees fewer prefill calls for the same prompt tokens, short prompts
+    finish next to a long one instead of behind it, tokens per request do not change."""
+    rng = random.Random(5)
+    reqs = {f"r{i}": [rng.randrange(4096) for _ in range(n)] for i, n in enumerate((400, 20, 25, 30, 18, 22))}
+    s1, _, out1, _ = _run(reqs, slots=6, prefix=False, budget=128)
+    s4, _, out4, _ = _run(reqs, slots=6, prefix=False, budget=128, group=6)
+    assert out1 == out4
+    m1, m4 = s1.meters(), s4.meters()
+    assert m4["prefill_tokens"] == m1["prefill_tokens"] and m4["prefill_calls"] < m1["prefill_calls"]
+
+    # what the engine is handed: a Python engine (the CPU oracle model) records its group calls
+    import torch
+    from dgpp_b200.engine.adapters import ReferenceEngine
+    from dgpp_b200.models.dense import DenseConfig, DenseModel
+    from dgpp_b200.ops import reference as ref
+
+    class Recorder(ReferenceEngine):
+        calls = []
+
+        def prefill_group(self, pieces):
+            Recorder.calls.append([(s, len(t), p, l) for s, t, p, l in pieces])
+            return [self.prefill(s, t, p, l) for s, t, p, l in pieces]
+
+    m = DenseModel.random_init(DenseConfig.plumbing_fp32(), device="cpu", seed=0, std=0.02)
+    short = {rid: p[:60] if len(p) > 60 else p for rid, p in reqs.items()}
+    short["r0"] = reqs["r0"][:200]
+
+    def run(group):
+        Recorder.calls = []
+        with ref.activation_dtype(torch.float32):
+            eng = Recorder(m, slots=6, num_blocks=128, block_tokens=16, max_context=256)
+            cfg = rt.SchedulerConfig()
+            cfg.prefix_cache = False
+            cfg.prefill_budget_idle = cfg.prefill_budget_busy = cfg.prefill_chunk = 128
+            cfg.prefill_group_max = group
+            s = rt.Scheduler(eng, cfg)
+            for rid, p in short.items():
+                s.submit(rid, p, 3)
+            s.run(10000)
+        return {rid: [a for kind, r, a, b in s.events() if kind == "token" and r == rid] for rid in short}
+
+    base = run(1)
+    assert not Recorder.calls
+    grouped = run(6)
+    assert grouped == base
+    first = Recorder.calls[0]
+    assert len(first) == 6 and sum(n for _, n, _, _ in first) <= 128
+    assert sum(last for _, n, _, last in first[1:]) >= 4 and not first[0][3]    # the short prompts finish in call one
+    assert first[0][1] >= 128 // 6                                              # the long reader still got its share
 
 
 def test_grow_on_demand_sheds_youngest_and_recovers():
