@@ -23,9 +23,13 @@ from typing import Dict, List
 
 
 def make_trace(n: int, vocab: int, prefixes: int, prefix_tokens: int, shared: float, suffix_lo: int, suffix_hi: int,
-               seed: int = 0) -> List[List[int]]:
+               seed: int = 0, suffix_seed: int | None = None) -> List[List[int]]:
+    """`seed` fixes the shared prefixes; `suffix_seed` (default: the same stream) the suffixes and the draw of which
+    request gets which prefix, so that two traces can share prefixes without sharing anything else."""
     rnd = random.Random(seed)
     fixed = [[rnd.randrange(vocab) for _ in range(prefix_tokens)] for _ in range(prefixes)]
+    if suffix_seed is not None:
+        rnd = random.Random(suffix_seed)
     out = []
     for _ in range(n):
         suffix = [rnd.randrange(vocab) for _ in range(rnd.randint(suffix_lo, suffix_hi))]
@@ -113,12 +117,14 @@ def run_load(url: str, trace: List[List[int]], concurrency: int, max_tokens: int
     wall = time.perf_counter() - t0
     good = [r for r in results if r and r["ok"]]
     ttft = [r["ttft"] for r in good]
+    hit = [r["ttft"] for r in good if r["cached_tokens"] * 2 >= r["prompt_tokens"]]     # most of the prompt was resident
     gaps = [g for r in good for g in r["gaps"]]
     pt, ct = sum(r["prompt_tokens"] for r in good), sum(r["completion_tokens"] for r in good)
     return {"requests": len(trace), "ok": len(good), "failed": len(trace) - len(good), "concurrency": concurrency,
             "wall_s": round(wall, 3), "prompt_tok_s": round(pt / wall, 1), "completion_tok_s": round(ct / wall, 1),
             "prompt_tokens": pt, "completion_tokens": ct, "cached_tokens": sum(r["cached_tokens"] for r in good),
             "ttft_s": {"p50": round(_pct(ttft, 0.5), 4), "p90": round(_pct(ttft, 0.9), 4), "max": round(max(ttft or [0]), 4)},
+            "ttft_prefix_hit_s": {"n": len(hit), "p50": round(_pct(hit, 0.5), 4), "p90": round(_pct(hit, 0.9), 4)},
             "gap_s": {"p50": round(_pct(gaps, 0.5), 5), "p99": round(_pct(gaps, 0.99), 5)},
             "errors": [r["error"] for r in results if r and not r["ok"]][:3]}
 

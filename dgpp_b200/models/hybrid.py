@@ -193,10 +193,13 @@ class HybridRunner:
                           for i, j in self.gdn_index.items()}
         self.gdn = {i: GdnLayer(model.layers[i].gdn, max_rows, device) for i in self.gdn_state}
         self.full_index = {i: j for j, i in enumerate(i for i in range(c.layers) if c.is_full(i))}
+        self.moe_wide, self._moe_pool = {}, {}
         self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
                     if L.moe is not None and L.moe.gu_q is not None}
         self.slots = slots
         self.spec_rows = 0          # rows per speculative run (1 + draft depth); 0 = speculation off
+        if slots > 16:
+            self._ensure_wide()
         e = lambda *s: torch.empty(*s, dtype=BF, device=device)
         H, d = c.hidden, c.head_dim
         self.x, self.xn, self.delta = e(max_rows, H), e(max_rows, H), e(max_rows, H)
@@ -214,6 +217,15 @@ class HybridRunner:
             r = min(max_rows, 32)
             self.att_scratch = (torch.empty(r * c.q_heads * self.max_splits * 2, dtype=torch.float32, device=device),
                                 torch.empty(r * c.q_heads * self.max_splits * d, dtype=torch.float32, device=device))
+
+    def _ensure_wide(self) -> None:
+        """Decode blocks for 17..32 rows (more than 16 live requests, or speculative verify rows): the same kernels as
+        the 16-row blocks with a 32-row token tile, so a row's arithmetic does not depend on how many rows share its
+        pass.  Their large buffers are shared by all layers."""
+        if self.moe_wide or self.max_rows <= 16:
+            return
+        wide = min(self.max_rows, 32)
+        self.moe_wide = {i: MoEBlock(self.m.layers[i].moe, wide, self.dev, pool=self._moe_pool) for i in self.moe}
 
     def _decode_splits(self, rows: int) -> int:
         """KV splits of a decode pass: enough CTAs (kv heads x rows x splits) to cover the SMs; fixed per batch width,
@@ -240,8 +252,11 @@ class HybridRunner:
     def _ffn(self, i: int, L: HybridLayer, xn: torch.Tensor, out: torch.Tensor) -> None:
         if L.moe is not None:
             blk = self.moe.get(i)
+            wide = self.moe_wide.get(i)
             if blk is not None and xn.shape[0] <= blk.max_rows:
                 blk.forward(xn, out)
+            elif wide is not None and xn.shape[0] <= wide.max_rows:
+                wide.forward(xn, out)
             elif blk is not None:
                 out.copy_(blk.forward_gathered(xn))
             else:
@@ -389,6 +404,11 @@ class HybridRunner:
                               self.dev)
         L = m.mtp_layer
         self.mtp_moe = MoEBlock(L.moe, 16, self.dev) if (L.moe is not None and L.moe.gu_q is not None) else None
+        self.mtp_moe_wide = None
+        if rows > 16:
+            self._ensure_wide()
+            if self.mtp_moe is not None and self.max_rows > 16:
+                self.mtp_moe_wide = MoEBlock(L.moe, min(self.max_rows, 32), self.dev, pool=self._moe_pool)
         self.mtp_prev = [None] * self.slots      # main-model hidden rows whose MTP pair still waits for its next token
         self.mtp_tok = [[] for _ in range(self.slots)]   # tokens after those rows, the newest excepted (it is the pending one)
         self.mtp_len = [0] * self.slots          # MTP cache filled for positions < mtp_len
@@ -427,6 +447,8 @@ class HybridRunner:
         if L.moe is not None:
             if self.mtp_moe is not None and rows <= self.mtp_moe.max_rows:
                 self.mtp_moe.forward(xn, delta)
+            elif self.mtp_moe_wide is not None and rows <= self.mtp_moe_wide.max_rows:
+                self.mtp_moe_wide.forward(xn, delta)
             elif self.mtp_moe is not None:
                 delta = self.mtp_moe.forward_gathered(xn)
             else:

@@ -183,7 +183,11 @@ class MoEBlock:
     # Class-wide so one deployment key sets it for every block.
     PREFILL_TERMS = 3
 
-    def __init__(self, w: MoEWeights, max_rows: int, device, act_terms: int = 3, prefill_terms: Optional[int] = None):
+    def __init__(self, w: MoEWeights, max_rows: int, device, act_terms: int = 3, prefill_terms: Optional[int] = None,
+                 pool: Optional[dict] = None):
+        """pool: a dict shared by the blocks of one runner (same shapes, one block running at a time): the expert
+        output and quantiser buffers are then allocated once instead of once per layer.  The routing tables
+        (`ids`, `wts`, the active list) stay per block."""
         c = w.cfg
         assert w.gu_q is not None, "call MoEWeights.stack() on the device first"
         self.w, self.c, self.dev, self.terms = w, c, device, act_terms
@@ -200,15 +204,24 @@ class MoEBlock:
         self.group_list = torch.full((self.slots,), -1, **i32)
         self.slot_of = torch.full((c.experts,), -1, **i32)
         self.n_active = torch.zeros(1, **i32)
-        self.h = torch.zeros(self.slots, self.bn, 2 * c.moe_ffn, dtype=BF, device=device)
-        self.y = torch.zeros(self.slots, self.bn, c.hidden, dtype=BF, device=device)
-        self.qa_in = ops.QuantAct(self.bn, c.hidden, act_terms, self.bn, device)
-        self.qa_mid = ops.QuantAct(self.slots * self.bn, c.moe_ffn, act_terms, self.bn, device)
+
+        def shared(name, make):
+            if pool is None:
+                return make()
+            key = (name, self.slots, self.bn, max_rows, c.hidden, c.moe_ffn, c.shared_ffn, act_terms)
+            if key not in pool:
+                pool[key] = make()
+            return pool[key]
+
+        self.h = shared("h", lambda: torch.zeros(self.slots, self.bn, 2 * c.moe_ffn, dtype=BF, device=device))
+        self.y = shared("y", lambda: torch.zeros(self.slots, self.bn, c.hidden, dtype=BF, device=device))
+        self.qa_in = shared("qa_in", lambda: ops.QuantAct(self.bn, c.hidden, act_terms, self.bn, device))
+        self.qa_mid = shared("qa_mid", lambda: ops.QuantAct(self.slots * self.bn, c.moe_ffn, act_terms, self.bn, device))
         self.shared = None
         if w.shared_gu is not None:
-            self.shared = torch.zeros(max_rows, c.hidden, dtype=BF, device=device)
-            self.sh_gu = torch.zeros(max_rows, 2 * c.shared_ffn, dtype=BF, device=device)
-            self.qa_sh = ops.QuantAct(self.bn, c.shared_ffn, act_terms, self.bn, device)
+            self.shared = shared("shared", lambda: torch.zeros(max_rows, c.hidden, dtype=BF, device=device))
+            self.sh_gu = shared("sh_gu", lambda: torch.zeros(max_rows, 2 * c.shared_ffn, dtype=BF, device=device))
+            self.qa_sh = shared("qa_sh", lambda: ops.QuantAct(self.bn, c.shared_ffn, act_terms, self.bn, device))
 
     def forward(self, xn: torch.Tensor, out: Optional[torch.Tensor], xa: Optional[ops.QuantAct] = None,
                 push_comm=None) -> Optional[torch.Tensor]:

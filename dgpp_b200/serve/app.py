@@ -527,8 +527,15 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
-    ap.add_argument("--model", default="tiny", choices=["tiny", "fake", "hybrid-tiny"])
+    ap.add_argument("--model", default="tiny", choices=["tiny", "fake", "hybrid-tiny", "hybrid"])
     ap.add_argument("--slots", type=int, default=8)
+    ap.add_argument("--max-context", type=int, default=4096, help="hybrid models: tokens per request (prompt + output)")
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="hybrid models: rows per prefill pass (0: 256 tiny, 2048 full)")
+    ap.add_argument("--snapshot-every", type=int, default=0,
+                    help="hybrid models: recurrent-state snapshot spacing in tokens (0: 512 tiny, 2048 full)")
+    ap.add_argument("--mtp-depth", type=int, default=0,
+                    help="hybrid models: draft this many tokens per step with the MTP head and verify them in the same pass")
+    ap.add_argument("--layers", type=int, default=48, help="--model hybrid: layer count (fewer than 48 is a smoke run)")
     ap.add_argument("--config", default="", help="deployment JSON (see dgpp_b200.cli resolve); overrides the flags above")
     ap.add_argument("--vision", action="store_true",
                     help="tiny model only: attach a random-init vision tower so that chat messages accept image_url parts")
@@ -536,20 +543,41 @@ def main(argv=None) -> int:
     if args.config:
         return serve_deployment(args.config)
     tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)], rt.SplitPattern.Qwen2)
+    sched_config = None
     if args.model == "fake":
         eng = rt.FakeEngine(slots=args.slots, block_tokens=16, blocks=4096, max_context=8192, vocab=256)
-    elif args.model == "hybrid-tiny":
-        # Gated DeltaNet + gated attention + MoE family behind the same scheduler / HTTP surface (needs a GPU)
+    elif args.model in ("hybrid-tiny", "hybrid"):
+        # Gated DeltaNet + gated attention + MoE family behind the same scheduler / HTTP surface (needs a GPU).
+        # "hybrid" is the full shape (48 layers 3:1, hidden 2048, 512 experts top-10 + shared, head_dim 256, NVFP4
+        # weights, random-init); "hybrid-tiny" a four-layer smoke model.
         from ..engine.adapters import HybridEngine
         from ..models.hybrid import HybridConfig, HybridModel, HybridRunner
-        from ..models.moe import MoEConfig
+        from ..models.moe import MoEBlock, MoEConfig
 
-        hc = HybridConfig(layers=4, hidden=512, full_every=4, q_heads=4, kv_heads=2, head_dim=128, gdn_k_heads=2,
-                          gdn_v_heads=4, gdn_dk=128, gdn_dv=128, ffn=1024, vocab=4096,
-                          moe=MoEConfig(experts=16, top_k=2, moe_ffn=512, shared_ffn=512))
-        hm = HybridModel.random_init(hc, "cuda", seed=0, std=0.05)
-        eng = HybridEngine(HybridRunner(hm, max_rows=256, slots=args.slots, max_seq_len=4096, device="cuda"),
-                           snapshot_every=512)
+        full = args.model == "hybrid"
+        chunk = args.prefill_chunk or (2048 if full else 256)
+        every = args.snapshot_every or (2048 if full else 512)
+        if full:
+            hc = HybridConfig(layers=args.layers, hidden=2048, full_every=4, q_heads=16, kv_heads=2, head_dim=256,
+                              gdn_k_heads=16, gdn_v_heads=16, gdn_dk=128, gdn_dv=128, vocab=151936, mtp=args.mtp_depth > 0,
+                              moe=MoEConfig(hidden=2048, experts=512, top_k=10, moe_ffn=512, shared_ffn=512, router="softmax"))
+            MoEBlock.PREFILL_TERMS = 1
+            hm = HybridModel.random_init(hc, "cuda", seed=0, std=0.02, fmt="nvfp4")
+        else:
+            hc = HybridConfig(layers=4, hidden=512, full_every=4, q_heads=4, kv_heads=2, head_dim=128, gdn_k_heads=2,
+                              gdn_v_heads=4, gdn_dk=128, gdn_dv=128, ffn=1024, vocab=4096, mtp=args.mtp_depth > 0,
+                              moe=MoEConfig(experts=16, top_k=2, moe_ffn=512, shared_ffn=512))
+            hm = HybridModel.random_init(hc, "cuda", seed=0, std=0.05)
+        eng = HybridEngine(HybridRunner(hm, max_rows=max(chunk, 256), slots=args.slots, max_seq_len=args.max_context,
+                                        device="cuda"),
+                           snapshot_every=every, max_snapshots=256 if full else 64, prefill_chunk=chunk,
+                           mtp_depth=args.mtp_depth)
+        sched_config = rt.SchedulerConfig()
+        sched_config.prefill_chunk = chunk
+        sched_config.prefill_budget_busy = chunk      # a prefix hit's suffix goes through in one or two ticks
+        # ids above the byte vocabulary get a printable piece each, so that streamed chunks carry text for every token
+        tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)] +
+                                      [(f"<{i}>", i, False) for i in range(258, hc.vocab)], rt.SplitPattern.Qwen2)
     else:
         import torch
 
@@ -568,7 +596,7 @@ def main(argv=None) -> int:
     if args.vision and args.model == "tiny":
         vision = tiny_vision_frontend(cfg, "cuda" if torch.cuda.is_available() else "cpu")
     srv = Server(eng, tok, model_name=f"dgpp-b200-{args.model}", host=args.host, port=args.port, eos_ids=[257],
-                 vision=vision)
+                 vision=vision, sched_config=sched_config)
     print(f"listening on http://{args.host}:{srv.start()}", flush=True)
     try:
         while True:

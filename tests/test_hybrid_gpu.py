@@ -88,10 +88,11 @@ def test_hybrid_engine_behind_the_scheduler_with_state_snapshots(dev):
     assert cached == plain and all(len(v) == 6 for v in cached.values())
 
 
-@pytest.mark.parametrize("moe,depth", [(False, 3), (True, 2)])
-def test_mtp_speculation_emits_the_plain_greedy_sequence(dev, moe, depth):
+@pytest.mark.parametrize("moe,depth,P", [(False, 3, 2), (True, 2, 2), (True, 3, 5)])
+def test_mtp_speculation_emits_the_plain_greedy_sequence(dev, moe, depth, P):
     """Draft with the MTP head, verify 1 + depth rows in one pass, commit / roll back on the device: the emitted tokens
-    equal plain greedy decoding token for token, whatever was accepted.  Forced drafts cover full and partial accepts."""
+    equal plain greedy decoding token for token, whatever was accepted.  Forced drafts cover full and partial accepts; five requests at depth 3 make 20 verify rows
+    (the 32-row MoE blocks)."""
     from dgpp_b200.models.hybrid import HybridConfig, HybridModel, HybridRunner
     from dgpp_b200.models.moe import MoEConfig
     from dgpp_b200.ops import core as ops
@@ -102,10 +103,10 @@ def test_mtp_speculation_emits_the_plain_greedy_sequence(dev, moe, depth):
                        moe=MoEConfig(experts=16, top_k=2, moe_ffn=512, shared_ffn=512) if moe else None)
     m = HybridModel.random_init(cfg, dev, seed=9, std=0.05)
     g = torch.Generator().manual_seed(6)
-    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (45, 70)]
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (45, 70, 33, 51, 64)[:P]]
     N = 18
 
-    plain = HybridRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+    plain = HybridRunner(m, max_rows=64, slots=P, max_seq_len=256, device=dev)
     want = []
     for s, p in enumerate(prompts):
         tok = int(torch.argmax(plain.prefill(s, p, chunk=32)[0]))
@@ -116,7 +117,7 @@ def test_mtp_speculation_emits_the_plain_greedy_sequence(dev, moe, depth):
         want.append(seq)
 
     def run(forced):
-        r = HybridRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+        r = HybridRunner(m, max_rows=64, slots=P, max_seq_len=256, device=dev)
         r.enable_spec(depth)
         pend, got = [], []
         for s, p in enumerate(prompts):
@@ -127,13 +128,13 @@ def test_mtp_speculation_emits_the_plain_greedy_sequence(dev, moe, depth):
             drafts = None
             if forced:
                 drafts = []
-                for s in range(2):
+                for s in range(P):
                     nxt = want[s][len(got[s]):len(got[s]) + depth]
                     nxt = nxt + [0] * (depth - len(nxt))
                     keep = (step + s) % (depth + 1)               # accept `keep` drafts, then a wrong one
                     drafts.append([t if i < keep else (t + 1) % cfg.vocab for i, t in enumerate(nxt)])
-            outs = r.spec_step([0, 1], pend, drafts=drafts)
-            for s in range(2):
+            outs = r.spec_step(list(range(P)), pend, drafts=drafts)
+            for s in range(P):
                 assert 1 <= len(outs[s]) <= depth + 1
                 if forced:
                     assert len(outs[s]) == (step + s) % (depth + 1) + 1, (step, s, outs[s])
@@ -146,7 +147,38 @@ def test_mtp_speculation_emits_the_plain_greedy_sequence(dev, moe, depth):
 
     for forced in (True, False):
         got, r = run(forced)
-        for s in range(2):
+        for s in range(P):
             n = min(len(got[s]), len(want[s]))
             assert got[s][:n] == want[s][:n], (forced, s)
             assert r.lengths[s] == len(prompts[s]) + len(got[s]) - 1
+
+
+def test_decode_of_more_than_16_rows_uses_the_wide_blocks(dev):
+    """20 live requests decode in one pass (tensor-core attention, 32-row MoE blocks): the logits of every row equal
+    those of the same request decoded alone on a second runner."""
+    from dgpp_b200.models.hybrid import HybridConfig, HybridModel, HybridRunner
+    from dgpp_b200.models.moe import MoEConfig
+    from dgpp_b200.ops import core as ops
+
+    cfg = HybridConfig(layers=4, hidden=512, full_every=4, q_heads=4, kv_heads=2, head_dim=128, gdn_k_heads=2,
+                       gdn_v_heads=4, gdn_dk=128, gdn_dv=128, ffn=1024, vocab=2048,
+                       moe=MoEConfig(experts=16, top_k=2, moe_ffn=512, shared_ffn=512))
+    m = HybridModel.random_init(cfg, dev, seed=5, std=0.05)
+    n = 20
+    many = HybridRunner(m, max_rows=64, slots=n, max_seq_len=128, device=dev)
+    one = HybridRunner(m, max_rows=64, slots=1, max_seq_len=128, device=dev)
+    assert len(many.moe_wide) == len(many.moe) > 0 and not one.moe_wide
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (9 + 3 * s,), generator=g).tolist() for s in range(n)]
+    nxt = torch.randint(0, cfg.vocab, (2, n), generator=g).tolist()
+    for s, p in enumerate(prompts):
+        many.prefill(s, p, chunk=32)
+    got = [many.decode(list(range(n)), nxt[k]).clone() for k in range(2)]
+    for s in (0, 7, 19):
+        one.reset(0)
+        one.prefill(0, prompts[s], chunk=32)
+        for k in range(2):
+            want = one.decode([0], [nxt[k][s]])[0]
+            assert (got[k][s] - want).abs().max().item() <= 0.03 * want.abs().max().item() + 0.02, (s, k)
+    torch.cuda.synchronize()
+    ops.check_status()

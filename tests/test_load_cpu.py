@@ -27,3 +27,25 @@ def test_load_run_measures_streaming_and_cache_hits():
     assert rep["prompt_tokens"] == sum(len(p) for p in trace)
     assert rep["cached_tokens"] >= 128 * 8                  # most shared prefixes are served from the block cache
     assert rep["ttft_s"]["p50"] > 0 and rep["completion_tok_s"] > 0 and rep["gap_s"]["p50"] >= 0
+
+
+def test_suffix_seed_keeps_prefixes_and_changes_the_rest():
+    a = make_trace(20, 256, 2, 32, 1.0, 4, 8, seed=3, suffix_seed=10)
+    b = make_trace(20, 256, 2, 32, 1.0, 4, 8, seed=3, suffix_seed=11)
+    assert {tuple(p[:32]) for p in a} == {tuple(p[:32]) for p in b}
+    assert [p[32:] for p in a] != [p[32:] for p in b]
+
+
+def test_trace_runner_serves_a_child_and_reports_each_concurrency(tmp_path, capsys):
+    import json
+
+    from dgpp_b200.bench import trace
+
+    rc = trace.main(["--model", "fake", "--slots", "4", "--port", "8391", "--concurrency", "1,4", "--requests", "10",
+                     "--prefix-tokens", "128", "--suffix-tokens", "8,24", "--max-tokens", "6", "--vocab", "250",
+                     "--server-log", str(tmp_path / "srv.log"), "--startup-s", "120"])
+    assert rc == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert [r["concurrency"] for r in rep["runs"]] == [1, 4]
+    assert all(r["ok"] == 10 and r["completion_tokens"] == 60 for r in rep["runs"])
+    assert rep["runs"][1]["ttft_prefix_hit_s"]["n"] >= 1      # the second run finds the first run's prefixes resident

@@ -67,6 +67,39 @@ def test_moe_block_matches_reference(dev, rows, shared):
     assert (out.float() - want2.float()).abs().max().item() <= 2e-2 * want2.float().abs().max().item() + 2e-3
 
 
+@pytest.mark.parametrize("cap,rows", [(32, 24), (32, 32), (64, 40)])
+def test_wide_decode_blocks_match_the_oracle_and_the_16_row_block(dev, cap, rows):
+    """Token tiles of 32 / 64 rows on the decode path (more live requests, speculative verify rows), with the large
+    buffers drawn from a pool shared by two blocks: the oracle's values, and row for row the bits of the 16-row block."""
+    from dgpp_b200.models.moe import MoEBlock, MoEConfig, MoEWeights, moe_reference
+    from dgpp_b200.ops import core as ops
+
+    torch.manual_seed(13)
+    cfg = MoEConfig(hidden=1024, experts=32, top_k=4, moe_ffn=512, shared_ffn=512, routed_scaling=1.5)
+    w = MoEWeights.random_init(cfg, dev, seed=4, std=0.05)
+    w2 = MoEWeights.random_init(cfg, dev, seed=5, std=0.05)
+    pool = {}
+    wide, other = MoEBlock(w, max_rows=cap, device=dev, pool=pool), MoEBlock(w2, max_rows=cap, device=dev, pool=pool)
+    assert wide.y.data_ptr() == other.y.data_ptr() and wide.ids.data_ptr() != other.ids.data_ptr()
+    narrow = MoEBlock(w, max_rows=16, device=dev)
+    x = torch.randn(rows, cfg.hidden, device=dev).to(BF)
+    out = torch.empty(rows, cfg.hidden, dtype=BF, device=dev)
+    other.forward(x, out)                      # leaves its values in the shared buffers
+    wide.forward(x, out)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = moe_reference(x, w, ids=wide.ids[:rows].long(), wts=wide.wts[:rows])
+    err = (out.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * want.float().abs().max().item() + 2e-3, err
+    part = torch.empty(16, cfg.hidden, dtype=BF, device=dev)
+    for o in range(0, rows, 16):
+        n = min(16, rows - o)
+        narrow.forward(x[o:o + n], part[:n])
+        assert torch.equal(part[:n], out[o:o + n]), o
+    torch.cuda.synchronize()
+    ops.check_status()
+
+
 def test_mxfp4_experts_stream_through_the_block_scaled_grouped_gemm(dev):
     """MXFP4 expert weights (e8m0 scale per 32) are re-expressed exactly in the block-scaled layout and run on the
     same grouped tensor-core GEMM; the oracle decodes the stored MXFP4 tensors."""
