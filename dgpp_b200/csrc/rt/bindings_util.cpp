@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 
 #include "rt/core_util.h"
+#include "rt/jpeg.h"
 
 namespace py = pybind11;
 using namespace dgpp;
@@ -92,6 +93,22 @@ void bind_util(py::module_& m) {
     d["rss_bytes"] = pm.rss_bytes; d["peak_rss_bytes"] = pm.peak_rss_bytes; d["locked_bytes"] = pm.locked_bytes;
     d["memlock_limit_bytes"] = pm.memlock_limit_bytes;
     return d;
+  });
+  m.def("decode_jpeg", [](const py::bytes& data) {
+    // (width, height, channels, pixel bytes): interleaved 8-bit grey or RGB; raises ValueError naming what is wrong
+    const std::string buf = data;
+    rt::jpeg::Image img;
+    {
+      py::gil_scoped_release release;
+      try {
+        img = rt::jpeg::decode(reinterpret_cast<const uint8_t*>(buf.data()), buf.size());
+      } catch (const std::runtime_error& e) {
+        py::gil_scoped_acquire acquire;
+        throw py::value_error(e.what());
+      }
+    }
+    return py::make_tuple(img.width, img.height, img.channels,
+                          py::bytes(reinterpret_cast<const char*>(img.pixels.data()), img.pixels.size()));
   });
   m.def("file_residency", [](const std::string& path) {
     int64_t size = -1;

@@ -14,6 +14,7 @@
 #include "rt/control.h"
 #include "rt/core_util.h"
 #include "rt/fake_engine.h"
+#include "rt/jpeg.h"
 #include "rt/json.h"
 #include "rt/json_grammar.h"
 #include "rt/paged_blocks.h"
@@ -136,12 +137,102 @@ static void test_crc_and_journal() {
   CHECK(whole == parts);
 }
 
+// ---- JPEG decoder: two small files (sequential 4:2:0 with restart markers, progressive 4:2:0), then truncations and
+// random byte damage of both: every input either decodes or throws, nothing reads or writes out of bounds
+static const unsigned char kJpegSeq[] = {
+    255, 216, 255, 224, 0, 16, 74, 70, 73, 70, 0, 1, 1, 0, 0, 1, 0, 1, 0, 0, 255, 219, 0, 67,
+    0, 13, 9, 10, 11, 10, 8, 13, 11, 10, 11, 14, 14, 13, 15, 19, 32, 21, 19, 18, 18, 19, 39, 28,
+    30, 23, 32, 46, 41, 49, 48, 46, 41, 45, 44, 51, 58, 74, 62, 51, 54, 70, 55, 44, 45, 64, 87, 65,
+    70, 76, 78, 82, 83, 82, 50, 62, 90, 97, 90, 80, 96, 74, 81, 82, 79, 255, 219, 0, 67, 1, 14, 14,
+    14, 19, 17, 19, 38, 21, 21, 38, 79, 53, 45, 53, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79,
+    79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79,
+    79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 255, 192, 0, 17, 8, 0, 20, 0, 24, 3,
+    1, 34, 0, 2, 17, 1, 3, 17, 1, 255, 196, 0, 31, 0, 0, 1, 5, 1, 1, 1, 1, 1, 1, 0,
+    0, 0, 0, 0, 0, 0, 0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 255, 196, 0, 181, 16, 0,
+    2, 1, 3, 3, 2, 4, 3, 5, 5, 4, 4, 0, 0, 1, 125, 1, 2, 3, 0, 4, 17, 5, 18, 33,
+    49, 65, 6, 19, 81, 97, 7, 34, 113, 20, 50, 129, 145, 161, 8, 35, 66, 177, 193, 21, 82, 209, 240, 36,
+    51, 98, 114, 130, 9, 10, 22, 23, 24, 25, 26, 37, 38, 39, 40, 41, 42, 52, 53, 54, 55, 56, 57, 58,
+    67, 68, 69, 70, 71, 72, 73, 74, 83, 84, 85, 86, 87, 88, 89, 90, 99, 100, 101, 102, 103, 104, 105, 106,
+    115, 116, 117, 118, 119, 120, 121, 122, 131, 132, 133, 134, 135, 136, 137, 138, 146, 147, 148, 149, 150, 151, 152, 153,
+    154, 162, 163, 164, 165, 166, 167, 168, 169, 170, 178, 179, 180, 181, 182, 183, 184, 185, 186, 194, 195, 196, 197, 198,
+    199, 200, 201, 202, 210, 211, 212, 213, 214, 215, 216, 217, 218, 225, 226, 227, 228, 229, 230, 231, 232, 233, 234, 241,
+    242, 243, 244, 245, 246, 247, 248, 249, 250, 255, 196, 0, 31, 1, 0, 3, 1, 1, 1, 1, 1, 1, 1, 1,
+    1, 0, 0, 0, 0, 0, 0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 255, 196, 0, 181, 17, 0,
+    2, 1, 2, 4, 4, 3, 4, 7, 5, 4, 4, 0, 1, 2, 119, 0, 1, 2, 3, 17, 4, 5, 33, 49,
+    6, 18, 65, 81, 7, 97, 113, 19, 34, 50, 129, 8, 20, 66, 145, 161, 177, 193, 9, 35, 51, 82, 240, 21,
+    98, 114, 209, 10, 22, 36, 52, 225, 37, 241, 23, 24, 25, 26, 38, 39, 40, 41, 42, 53, 54, 55, 56, 57,
+    58, 67, 68, 69, 70, 71, 72, 73, 74, 83, 84, 85, 86, 87, 88, 89, 90, 99, 100, 101, 102, 103, 104, 105,
+    106, 115, 116, 117, 118, 119, 120, 121, 122, 130, 131, 132, 133, 134, 135, 136, 137, 138, 146, 147, 148, 149, 150, 151,
+    152, 153, 154, 162, 163, 164, 165, 166, 167, 168, 169, 170, 178, 179, 180, 181, 182, 183, 184, 185, 186, 194, 195, 196,
+    197, 198, 199, 200, 201, 202, 210, 211, 212, 213, 214, 215, 216, 217, 218, 226, 227, 228, 229, 230, 231, 232, 233, 234,
+    242, 243, 244, 245, 246, 247, 248, 249, 250, 255, 221, 0, 4, 0, 1, 255, 218, 0, 12, 3, 1, 0, 2, 17,
+    3, 17, 0, 63, 0, 189, 7, 136, 29, 97, 206, 58, 117, 226, 176, 245, 15, 17, 57, 147, 1, 70, 61, 125,
+    43, 164, 142, 194, 193, 163, 225, 151, 29, 171, 46, 235, 76, 178, 50, 245, 21, 131, 196, 210, 173, 83, 217, 211,
+    142, 129, 143, 150, 25, 97, 226, 220, 89, 255, 208, 110, 151, 174, 72, 64, 37, 78, 125, 104, 173, 93, 55, 78,
+    176, 84, 193, 96, 114, 59, 154, 42, 37, 67, 7, 77, 218, 113, 212, 236, 192, 213, 195, 58, 43, 221, 103, 255,
+    209, 205, 181, 185, 151, 102, 55, 145, 199, 175, 214, 169, 92, 220, 76, 126, 111, 49, 187, 255, 0, 65, 69, 21,
+    223, 148, 70, 60, 205, 216, 245, 115, 56, 175, 171, 199, 67, 255, 210, 198, 180, 187, 157, 83, 112, 144, 209, 69,
+    20, 241, 255, 0, 198, 103, 210, 96, 35, 31, 96, 180, 63, 255, 217,
+};
+static const unsigned char kJpegProg[] = {
+    255, 216, 255, 224, 0, 16, 74, 70, 73, 70, 0, 1, 1, 0, 0, 1, 0, 1, 0, 0, 255, 219, 0, 67,
+    0, 13, 9, 10, 11, 10, 8, 13, 11, 10, 11, 14, 14, 13, 15, 19, 32, 21, 19, 18, 18, 19, 39, 28,
+    30, 23, 32, 46, 41, 49, 48, 46, 41, 45, 44, 51, 58, 74, 62, 51, 54, 70, 55, 44, 45, 64, 87, 65,
+    70, 76, 78, 82, 83, 82, 50, 62, 90, 97, 90, 80, 96, 74, 81, 82, 79, 255, 219, 0, 67, 1, 14, 14,
+    14, 19, 17, 19, 38, 21, 21, 38, 79, 53, 45, 53, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79,
+    79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79,
+    79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 79, 255, 194, 0, 17, 8, 0, 20, 0, 24, 3,
+    1, 34, 0, 2, 17, 1, 3, 17, 1, 255, 196, 0, 24, 0, 1, 0, 3, 1, 0, 0, 0, 0, 0, 0,
+    0, 0, 0, 0, 0, 0, 0, 2, 3, 4, 5, 255, 196, 0, 23, 1, 1, 1, 1, 1, 0, 0, 0, 0,
+    0, 0, 0, 0, 0, 0, 0, 0, 3, 4, 0, 2, 255, 218, 0, 12, 3, 1, 0, 2, 16, 3, 16, 0,
+    0, 1, 191, 15, 75, 41, 232, 181, 58, 110, 109, 5, 41, 48, 20, 127, 255, 196, 0, 26, 16, 0, 2, 2,
+    3, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, 2, 0, 3, 4, 17, 33, 255, 218, 0, 8,
+    1, 1, 0, 1, 5, 2, 25, 28, 179, 35, 181, 94, 96, 68, 211, 86, 155, 174, 180, 138, 198, 51, 24, 172,
+    103, 255, 196, 0, 29, 17, 0, 2, 2, 1, 5, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, 3,
+    0, 18, 2, 4, 19, 33, 35, 49, 255, 218, 0, 8, 1, 3, 1, 1, 63, 1, 121, 94, 216, 226, 35, 37,
+    211, 201, 169, 29, 98, 32, 10, 79, 255, 196, 0, 29, 17, 0, 2, 2, 1, 5, 0, 0, 0, 0, 0, 0,
+    0, 0, 0, 0, 0, 1, 2, 0, 3, 4, 17, 18, 19, 49, 50, 255, 218, 0, 8, 1, 2, 1, 1, 63,
+    1, 228, 87, 109, 170, 33, 74, 87, 177, 49, 0, 214, 95, 238, 127, 255, 196, 0, 22, 16, 1, 1, 1, 0,
+    0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 49, 32, 255, 218, 0, 8, 1, 1, 0, 6, 63,
+    2, 221, 87, 255, 196, 0, 26, 16, 0, 3, 1, 0, 3, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0,
+    0, 1, 49, 17, 16, 65, 81, 255, 218, 0, 8, 1, 1, 0, 1, 63, 33, 114, 45, 232, 120, 6, 233, 113,
+    138, 170, 100, 165, 58, 23, 90, 63, 255, 218, 0, 12, 3, 1, 0, 2, 0, 3, 0, 0, 0, 16, 8, 231,
+    254, 255, 196, 0, 24, 17, 1, 1, 1, 1, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, 0,
+    33, 17, 49, 255, 218, 0, 8, 1, 3, 1, 1, 63, 16, 42, 42, 88, 212, 94, 23, 39, 47, 255, 196, 0,
+    24, 17, 0, 3, 1, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, 17, 49, 33, 255,
+    218, 0, 8, 1, 2, 1, 1, 63, 16, 121, 128, 105, 59, 22, 28, 54, 63, 255, 196, 0, 28, 16, 1, 0,
+    2, 2, 3, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, 0, 17, 33, 81, 49, 65, 113, 193, 255,
+    218, 0, 8, 1, 1, 0, 1, 63, 16, 186, 87, 28, 226, 38, 128, 173, 234, 32, 21, 94, 230, 25, 71, 81,
+    124, 201, 77, 67, 103, 108, 195, 220, 198, 253, 140, 244, 124, 37, 116, 167, 255, 217,
+};
+
+static void test_jpeg() {
+  std::mt19937 rng(99);
+  const std::pair<const unsigned char*, size_t> files[] = {{kJpegSeq, sizeof(kJpegSeq)}, {kJpegProg, sizeof(kJpegProg)}};
+  for (const auto& f : files) {
+    const auto img = dgpp::rt::jpeg::decode(f.first, f.second);
+    CHECK(img.width == 24 && img.height == 20 && img.channels == 3 && img.pixels.size() == 24u * 20u * 3u);
+    int ok = 0, refused = 0;
+    for (size_t cut = 0; cut < f.second; cut += 3) {
+      try { dgpp::rt::jpeg::decode(f.first, cut); ++ok; } catch (const std::runtime_error&) { ++refused; }
+    }
+    for (int it = 0; it < 3000; ++it) {
+      std::vector<unsigned char> buf(f.first, f.first + f.second);
+      const int hits = 1 + static_cast<int>(rng() % 4);
+      for (int h = 0; h < hits; ++h) buf[rng() % buf.size()] = static_cast<unsigned char>(rng());
+      try { dgpp::rt::jpeg::decode(buf.data(), buf.size()); ++ok; } catch (const std::runtime_error&) { ++refused; }
+    }
+    CHECK(ok > 0 && refused > 0);
+  }
+}
+
 int main() {
   test_blocks();
   test_scheduler();
   test_json();
   test_grammar();
   test_crc_and_journal();
+  test_jpeg();
   if (g_fail) { std::fprintf(stderr, "selftest: %d check(s) failed\n", g_fail); return 1; }
   std::puts("rt selftest ok");
   return 0;

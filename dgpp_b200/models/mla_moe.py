@@ -84,6 +84,43 @@ def _rope(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.T
     return torch.cat([a * c - b * s, b * c + a * s], -1)
 
 
+def mla_attention_reference(c, inv_freq: torch.Tensor, L: "MlaLayer", xn: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+    """Plain (non-absorbed) latent attention of consecutive tokens of one request from position 0, with the sparse
+    index when the layer has one.  c: any config with heads / q_lora / kv_lora / nope / rope / v_dim / index_* / eps.
+    xn [T, H] bf16 normed rows -> o [T, H] bf16 (after the output projection)."""
+    T = xn.shape[0]
+    scale = 1.0 / math.sqrt(c.nope + c.rope)
+    cq = ref.rmsnorm(ref.linear(xn, L.q_a), L.q_a_norm, c.eps)[0]
+    q = ref.linear(cq, L.q_b).float().view(T, c.heads, c.nope + c.rope)
+    q_n, q_r = q[..., :c.nope], ref._r(_rope(q[..., c.nope:], pos, inv_freq))
+    kv = ref.linear(xn, L.kv_a)
+    ckv = ref.rmsnorm(kv[:, :c.kv_lora].contiguous(), L.kv_a_norm, c.eps)[0].float()         # bf16 values
+    k_r = ref._r(_rope(kv[:, c.kv_lora:].float(), pos, inv_freq))                        # [T, dr]
+    k_n = torch.einsum("hnd,td->thn", L.w_uk.float(), ckv)                                    # [T, heads, nope]
+    v = torch.einsum("hvd,td->thv", L.w_uv.float(), ckv)                                      # [T, heads, v]
+    s = (torch.einsum("qhn,khn->hqk", q_n, k_n) + torch.einsum("qhr,kr->hqk", q_r, k_r)) * scale
+    mask = pos.unsqueeze(0) > pos.unsqueeze(1)                                                # [q, k]
+    if L.idx_q is not None:
+        qi = ref.linear(xn, L.idx_q).float().view(T, c.index_heads, c.index_dim)
+        ki = ref.linear(xn, L.idx_k).float()                                                  # [T, di]
+        wi = ref.linear(xn, L.idx_w).float()                                                  # [T, hi]
+        sc = (torch.relu(torch.einsum("qhd,kd->qhk", qi, ki)) * wi.unsqueeze(-1)).sum(1)      # [q, k]
+        sc = sc.masked_fill(mask, float("-inf"))
+        keep = torch.zeros_like(mask)
+        for t in range(T):
+            n = t + 1
+            if n <= c.index_topk:
+                keep[t, :n] = True
+            else:
+                order = torch.argsort(-sc[t, :n], stable=True)[:c.index_topk]                 # ties -> lower position
+                keep[t, order] = True
+        mask = mask | ~keep
+    p = torch.softmax(s.masked_fill(mask.unsqueeze(0), float("-inf")), -1)
+    a = ref._r(torch.einsum("hqk,khv->qhv", p, v)).reshape(T, c.heads * c.v_dim)
+    o = ref.linear(ref.act(a), L.o)
+    return o
+
+
 class MlaMoeModel:
     def __init__(self, cfg: MlaMoeConfig, embed, layers: List[MlaLayer], final_norm, head: QuantLinear, inv_freq):
         self.cfg, self.embed, self.layers, self.final_norm, self.head, self.inv_freq = cfg, embed, layers, final_norm, head, inv_freq
@@ -129,34 +166,7 @@ class MlaMoeModel:
         scale = 1.0 / math.sqrt(c.nope + c.rope)
         for L in self.layers:
             xn, x = ref.rmsnorm(x, L.in_norm, c.eps, delta)
-            cq = ref.rmsnorm(ref.linear(xn, L.q_a), L.q_a_norm, c.eps)[0]
-            q = ref.linear(cq, L.q_b).float().view(T, c.heads, c.nope + c.rope)
-            q_n, q_r = q[..., :c.nope], ref._r(_rope(q[..., c.nope:], pos, self.inv_freq))
-            kv = ref.linear(xn, L.kv_a)
-            ckv = ref.rmsnorm(kv[:, :c.kv_lora].contiguous(), L.kv_a_norm, c.eps)[0].float()         # bf16 values
-            k_r = ref._r(_rope(kv[:, c.kv_lora:].float(), pos, self.inv_freq))                        # [T, dr]
-            k_n = torch.einsum("hnd,td->thn", L.w_uk.float(), ckv)                                    # [T, heads, nope]
-            v = torch.einsum("hvd,td->thv", L.w_uv.float(), ckv)                                      # [T, heads, v]
-            s = (torch.einsum("qhn,khn->hqk", q_n, k_n) + torch.einsum("qhr,kr->hqk", q_r, k_r)) * scale
-            mask = pos.unsqueeze(0) > pos.unsqueeze(1)                                                # [q, k]
-            if L.idx_q is not None:
-                qi = ref.linear(xn, L.idx_q).float().view(T, c.index_heads, c.index_dim)
-                ki = ref.linear(xn, L.idx_k).float()                                                  # [T, di]
-                wi = ref.linear(xn, L.idx_w).float()                                                  # [T, hi]
-                sc = (torch.relu(torch.einsum("qhd,kd->qhk", qi, ki)) * wi.unsqueeze(-1)).sum(1)      # [q, k]
-                sc = sc.masked_fill(mask, float("-inf"))
-                keep = torch.zeros_like(mask)
-                for t in range(T):
-                    n = t + 1
-                    if n <= c.index_topk:
-                        keep[t, :n] = True
-                    else:
-                        order = torch.argsort(-sc[t, :n], stable=True)[:c.index_topk]                 # ties -> lower position
-                        keep[t, order] = True
-                mask = mask | ~keep
-            p = torch.softmax(s.masked_fill(mask.unsqueeze(0), float("-inf")), -1)
-            a = ref._r(torch.einsum("hqk,khv->qhv", p, v)).reshape(T, c.heads * c.v_dim)
-            o = ref.linear(ref.act(a), L.o)
+            o = mla_attention_reference(c, self.inv_freq, L, xn, pos)
             xn, x = ref.rmsnorm(x, L.post_norm, c.eps, o)
             if L.moe is not None:
                 delta = moe_reference(xn, L.moe)
@@ -166,6 +176,56 @@ class MlaMoeModel:
         return ref.linear(xn, self.head, out_fp32=True)
 
 
+class MlaCaches:
+    """Paged latent cache (+ index-key cache) of the MLA layers of a model and the absorbed-attention launch sequence
+    of one layer.  Shared by the families that contain MLA layers."""
+
+    def __init__(self, c, layers: int, indexed: List[bool], max_rows: int, slots: int, max_seq_len: int, device):
+        self.c, self.dev = c, device
+        self.page = c.page
+        self.max_blocks = (max_seq_len + c.page - 1) // c.page + 1
+        nblocks = slots * self.max_blocks + 1
+        self.max_ctx = self.max_blocks * c.page
+        self.latent = [torch.zeros(nblocks, c.page, c.kv_lora + c.rope, dtype=BF, device=device) for _ in range(layers)]
+        self.kidx = [torch.zeros(nblocks, c.page, c.index_dim, dtype=BF, device=device) if ix else None for ix in indexed]
+        # static block table: slot s owns blocks [1 + s * max_blocks, 1 + (s + 1) * max_blocks)
+        self.block_table = (1 + torch.arange(slots * self.max_blocks, device=device, dtype=torch.int32)
+                            ).view(slots, self.max_blocks).contiguous()
+        self.scale = 1.0 / math.sqrt(c.nope + c.rope)
+        self.scores = torch.empty(max_rows, self.max_ctx, dtype=torch.float32, device=device) if any(indexed) else None
+
+    def _append(self, cache: torch.Tensor, rows: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor) -> None:
+        blk = self.block_table[row_req.long(), (positions // self.page).long()].long()
+        cache[blk, (positions % self.page).long()] = rows
+
+    def attention(self, j: int, L: MlaLayer, inv_freq: torch.Tensor, xn: torch.Tensor, positions: torch.Tensor,
+                  row_req: torch.Tensor, select: bool, out: torch.Tensor) -> torch.Tensor:
+        """xn [rows, H] normed rows of MLA layer j -> out [rows, H] (after the output projection).  Appends the rows'
+        latent (and index key) to the cache first; every row attends up to its own position."""
+        c = self.c
+        rows = xn.shape[0]
+        cq = ops.rmsnorm(ops.linear(xn, L.q_a), L.q_a_norm, c.eps)
+        q = ops.linear(cq, L.q_b).view(rows, c.heads, c.nope + c.rope)
+        kv = ops.linear(xn, L.kv_a)
+        # latent norm + rotary key -> cache slot; key up-projection folded into the query, rotary part appended
+        ops.mla_kv_prep(kv, L.kv_a_norm, c.eps, inv_freq, positions, row_req, self.block_table, self.latent[j],
+                        c.kv_lora, c.rope)
+        q_full = ops.mla_q_absorb(q, L.w_uk, inv_freq, positions, c.kv_lora, c.rope)
+        sel = None
+        if L.idx_q is not None:
+            self._append(self.kidx[j], ops.linear(xn, L.idx_k), row_req, positions)
+        if L.idx_q is not None and select:
+            qi = ops.linear(xn, L.idx_q).view(rows, c.index_heads, c.index_dim)
+            wi = ops.linear(xn, L.idx_w).float().contiguous()
+            sc = ops.dsa_index(qi, wi, self.kidx[j], self.block_table, row_req, positions, self.max_ctx,
+                               scores=self.scores[:rows])
+            sel = ops.topk_select(sc, positions, c.index_topk)
+        lat = ops.mla_decode(q_full, self.latent[j], self.block_table, row_req, positions, self.scale, c.kv_lora,
+                             c.rope, sel=sel, splits=4 if rows <= 16 else 1)
+        a = ops.mla_v_up(lat, L.w_uv)
+        return ops.linear(a, L.o, out=out)
+
+
 class MlaMoeRunner:
     """Kernel execution: latent cache + index-key cache in pages, absorbed MLA decode kernel (dense or sparse), MoE
     block, tensor-core linears.  Rows may be a prefill chunk of one request or one decode token per request."""
@@ -173,32 +233,20 @@ class MlaMoeRunner:
     def __init__(self, model: MlaMoeModel, max_rows: int, slots: int, max_seq_len: int, device):
         c = model.cfg
         self.m, self.c, self.dev, self.max_rows = model, c, device, max_rows
-        self.page = c.page
-        self.max_blocks = (max_seq_len + c.page - 1) // c.page + 1
-        nblocks = slots * self.max_blocks + 1
-        self.max_ctx = self.max_blocks * c.page
-        self.latent = [torch.zeros(nblocks, c.page, c.kv_lora + c.rope, dtype=BF, device=device) for _ in model.layers]
-        self.kidx = [torch.zeros(nblocks, c.page, c.index_dim, dtype=BF, device=device) if c.index_heads else None
-                     for _ in model.layers]
-        # static block table: slot s owns blocks [1 + s * max_blocks, 1 + (s + 1) * max_blocks)
-        self.block_table = (1 + torch.arange(slots * self.max_blocks, device=device, dtype=torch.int32)
-                            ).view(slots, self.max_blocks).contiguous()
+        self.att = MlaCaches(c, len(model.layers), [L.idx_q is not None for L in model.layers], max_rows, slots,
+                             max_seq_len, device)
+        self.page, self.max_blocks, self.max_ctx = self.att.page, self.att.max_blocks, self.att.max_ctx
+        self.latent, self.kidx, self.block_table = self.att.latent, self.att.kidx, self.att.block_table
         self.lengths = [0] * slots
         self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
                     if L.moe is not None and L.moe.gu_q is not None}
-        self.scale = 1.0 / math.sqrt(c.nope + c.rope)
         self.use_graphs, self._graphs, self._static = True, {}, {}
-        self.scores = torch.empty(max_rows, self.max_ctx, dtype=torch.float32, device=device) if c.index_heads else None
 
     def reset(self, slot: int) -> None:
         self.lengths[slot] = 0
 
     def _state_tensors(self):
         return []          # the latent / index-key cache writes of a pass are idempotent
-
-    def _append(self, cache: torch.Tensor, rows: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor) -> None:
-        blk = self.block_table[row_req.long(), (positions // self.page).long()].long()
-        cache[blk, (positions % self.page).long()] = rows
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor,
@@ -214,26 +262,7 @@ class MlaMoeRunner:
         have = False
         for i, L in enumerate(m.layers):
             ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have else None, out=xn)
-            cq = ops.rmsnorm(ops.linear(xn, L.q_a), L.q_a_norm, c.eps)
-            q = ops.linear(cq, L.q_b).view(rows, c.heads, c.nope + c.rope)
-            kv = ops.linear(xn, L.kv_a)
-            # latent norm + rotary key -> cache slot; key up-projection folded into the query, rotary part appended
-            ops.mla_kv_prep(kv, L.kv_a_norm, c.eps, m.inv_freq, positions, row_req, self.block_table, self.latent[i],
-                            c.kv_lora, c.rope)
-            q_full = ops.mla_q_absorb(q, L.w_uk, m.inv_freq, positions, c.kv_lora, c.rope)
-            sel = None
-            if L.idx_q is not None:
-                self._append(self.kidx[i], ops.linear(xn, L.idx_k), row_req, positions)
-            if L.idx_q is not None and select:
-                qi = ops.linear(xn, L.idx_q).view(rows, c.index_heads, c.index_dim)
-                wi = ops.linear(xn, L.idx_w).float().contiguous()
-                sc = ops.dsa_index(qi, wi, self.kidx[i], self.block_table, row_req, positions, self.max_ctx,
-                                   scores=self.scores[:rows])
-                sel = ops.topk_select(sc, positions, c.index_topk)
-            lat = ops.mla_decode(q_full, self.latent[i], self.block_table, row_req, positions, self.scale, c.kv_lora,
-                                 c.rope, sel=sel, splits=4 if rows <= 16 else 1)
-            a = ops.mla_v_up(lat, L.w_uv)
-            ops.linear(a, L.o, out=delta)
+            self.att.attention(i, L, m.inv_freq, xn, positions, row_req, select, delta)
             ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
             have = True
             if L.moe is not None:

@@ -35,6 +35,16 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Ten
     return out
 
 
+def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = bf16(a + b), element by element (contiguous bf16 tensors of one shape; out may be a)."""
+    _chk(a, torch.bfloat16, "a")
+    _chk(b, torch.bfloat16, "b")
+    if out is None:
+        out = torch.empty_like(a)
+    call("dgpp_add_bf16", ptr(a), ptr(b), ptr(out), a.numel(), stream_ptr())
+    return out
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, delta: Optional[torch.Tensor] = None,
             resid_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
             one_plus_w: bool = False):
@@ -681,6 +691,9 @@ def justnorm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
 
 def slerp_alpha(a: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor, s: float, eps: float = 1e-6) -> torch.Tensor:
     """Hypersphere residual: justnorm(an + |alpha s| (bn - an)) with an / bn the bf16 unit-norm rows of a / b."""
+    _chk(a, torch.bfloat16, "a")
+    _chk(b, torch.bfloat16, "b")
+    _chk(alpha, torch.bfloat16, "alpha")
     out = torch.empty_like(a)
     call("dgpp_slerp_alpha", ptr(a), ptr(b), ptr(alpha), float(s), ptr(out), a.shape[0], a.shape[1], float(eps), stream_ptr())
     return out

@@ -3,8 +3,9 @@ turns decoded RGB into the patch canvas a vision tower expects.
 
 Only inline `data:` URIs are accepted: resolving remote URLs is deliberately not part of the serving path.  PNG is
 decoded here (zlib + the five scanline filters, 8 / 16-bit gray, RGB, palette, with or without alpha, non-interlaced);
-binary PPM / PGM as the trivial lossless carrier used by tests and tools.  JPEG and WebP need codecs this build does
-not carry and are refused with a 400 that names the content part.  A decode error carries the API field of the part.
+binary PPM / PGM as the trivial lossless carrier used by tests and tools; JPEG (sequential and progressive Huffman
+streams, grey / YCbCr / RGB) goes through the native decoder of the runtime library.  WebP needs a codec this build
+does not carry and is refused with a 400 that names the content part.  A decode error carries the API field of the part.
 (reference counterparts: src/serve/image_inputs.cpp prepare_image / resize_image, common/image_input.hpp; the
  reference decodes through stb_image / simplewebp.)
 """
@@ -189,16 +190,28 @@ def decode_ppm(data: bytes, param: str = "image_url") -> np.ndarray:
     return np.repeat(px, 3, axis=2) if ch == 1 else px.copy()
 
 
+def decode_jpeg(data: bytes, param: str = "image_url") -> np.ndarray:
+    """RGB uint8 [h, w, 3] through the runtime library's decoder (grey images are replicated to three channels)."""
+    from ..runtime import rt
+
+    try:
+        w, h, ch, px = rt.decode_jpeg(data)
+    except ValueError as e:
+        raise ImageInputError(str(e), param) from None
+    a = np.frombuffer(px, np.uint8).reshape(h, w, ch)
+    return np.repeat(a, 3, axis=2) if ch == 1 else a.copy()
+
+
 def decode_image(data: bytes, param: str = "image_url") -> np.ndarray:
     if data[:8] == b"\x89PNG\r\n\x1a\n":
         return decode_png(data, param)
     if data[:2] in (b"P6", b"P5"):
         return decode_ppm(data, param)
     if data[:3] == b"\xff\xd8\xff":
-        raise ImageInputError("JPEG images are not supported by this build (send PNG)", param)
+        return decode_jpeg(data, param)
     if data[:4] == b"RIFF" and data[8:12] == b"WEBP":
         raise ImageInputError("WebP images are not supported by this build (send PNG)", param)
-    raise ImageInputError("unrecognised image format (PNG and binary PPM are accepted)", param)
+    raise ImageInputError("unrecognised image format (PNG, JPEG and binary PPM are accepted)", param)
 
 
 def _round_half_even(x: float) -> int:

@@ -1,0 +1,76 @@
+"""Looped-hypersphere and gated-residual families on the GPU: kernel runners against their PyTorch oracles."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda:0")
+
+
+def _drive(r, m, vocab, dev, close):
+    """Two requests: chunked prefill, batched teacher-forced decode through the graph, reset and repeat."""
+    from dgpp_b200.ops import core as ops
+
+    g = torch.Generator().manual_seed(2)
+    a = torch.randint(0, vocab, (110,), generator=g).tolist()
+    b = torch.randint(0, vocab, (37,), generator=g).tolist()
+    la = r.prefill(1, a[:100], chunk=64).clone()
+    lb = r.prefill(0, b[:30], chunk=16).clone()
+    want_a = m.forward_reference(torch.tensor(a, device=dev))
+    want_b = m.forward_reference(torch.tensor(b, device=dev))
+    torch.cuda.synchronize()
+    ops.check_status()
+    close(la[-1], want_a[99], "prefill a")
+    close(lb[-1], want_b[29], "prefill b")
+    for s in range(4):
+        out = r.decode([1, 0], [a[100 + s], b[30 + s]])
+        close(out[0], want_a[100 + s], f"decode a {s}")
+        close(out[1], want_b[30 + s], f"decode b {s}")
+    assert r.lengths[:2] == [34, 104]
+    torch.cuda.synchronize()
+    ops.check_status()
+    r.reset(0)
+    assert torch.equal(r.prefill(0, b[:30], chunk=16), lb)
+
+
+def test_dory_loops_on_the_hypersphere(dev):
+    from dgpp_b200.models.dory import DoryConfig, DoryModel, DoryRunner
+
+    cfg = DoryConfig(layers=2, loops=3, hidden=512, q_heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2048)
+    m = DoryModel.random_init(cfg, dev, seed=4)
+    r = DoryRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+    assert len(r.kv.layers) == 6                     # one cache layer per (loop, layer)
+
+    def close(got, want, what):
+        err = (got - want).abs().max().item()
+        assert err <= 0.06 * want.abs().max().item() + 0.02, (what, err)
+
+    _drive(r, m, cfg.vocab, dev, close)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_flash_next_gated_residual_branches(dev, moe):
+    from dgpp_b200.models.flash_next import FlashNextConfig, FlashNextModel, FlashNextRunner
+    from dgpp_b200.models.moe import MoEConfig
+
+    cfg = FlashNextConfig(layers=4, hidden=512, full_every=2, hc=4, gr_rank=128, q_heads=4, kv_heads=2, head_dim=128,
+                          gdn_k_heads=2, gdn_v_heads=4, ffn=1024, vocab=2048, ple_rows=1024,
+                          moe=MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512, shared_ffn=512) if moe else None)
+    m = FlashNextModel.random_init(cfg, dev, seed=5)
+    r = FlashNextRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+
+    def close(got, want, what):
+        if moe:
+            cos = torch.nn.functional.cosine_similarity(got.float(), want.float(), dim=0).item()
+            assert cos >= 0.985, (what, cos)
+            return
+        err = (got - want).abs().max().item()
+        assert err <= 0.06 * want.abs().max().item() + 0.02, (what, err)
+
+    _drive(r, m, cfg.vocab, dev, close)
+    assert r.last_token[1] != 0                      # the bigram hash carries over between passes

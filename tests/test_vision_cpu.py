@@ -75,8 +75,10 @@ def test_image_errors_name_the_part():
     for bad in ("data:image/png;base64,@@@", "data:image/png,abcd", "data:image/png;base64"):
         with pytest.raises(ImageInputError):
             prepare_image(bad, ImagePreprocess(), "p")
-    with pytest.raises(ImageInputError, match="JPEG"):
+    with pytest.raises(ImageInputError, match="jpeg"):             # a JPEG signature with nothing decodable behind it
         decode_image(b"\xff\xd8\xff\xe0" + b"0" * 32)
+    with pytest.raises(ImageInputError, match="WebP"):
+        decode_image(b"RIFF\x00\x00\x00\x00WEBPVP8 ")
     good = encode_png(np.zeros((8, 8, 3), np.uint8))
     broken = bytearray(good)
     broken[40] ^= 1                      # inside IDAT: checksum mismatch
