@@ -155,6 +155,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--concurrency", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="--config 2 / 3: rows per prefill pass (0: 2048)")
+    ap.add_argument("--prompt-lens", default="", help="--config 2 / 3: several long prompt lengths in one run, e.g. 32768,131072")
     ap.add_argument("--mtp", type=int, default=0, choices=(0, 1, 2, 3),
                     help="--config 4: speculative decoding with this many MTP drafts per step (0 = off)")
     ap.add_argument("--moe-prefill-terms", type=int, default=1, choices=(1, 2, 3),

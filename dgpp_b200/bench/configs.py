@@ -140,33 +140,64 @@ def run_config2(args, dev, indexer: bool = False) -> dict:
                        ffn=12288, dense_layers=min(2, layers), vocab=129280,
                        moe=MoEConfig(hidden=4096, experts=256, top_k=8, moe_ffn=1536, shared_ffn=1536, n_group=8,
                                      topk_group=4, router="sigmoid", routed_scaling=2.5),
-                       index_heads=64 if indexer else 0, index_dim=128, index_topk=2048)
+                       index_heads=64 if indexer else 0, index_dim=128, index_topk=2048,
+                       yarn_factor=4.0 if indexer else 1.0, yarn_orig_ctx=32768)
     t0 = time.time()
     terms = _lean_experts(args)
     model = MlaMoeModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4")
     torch.cuda.synchronize()
     init_s = time.time() - t0
     C = 8
-    max_len = args.prompt_len + 512
-    chunk = 256 if indexer else 2048     # the indexer keeps a [chunk, context] score matrix
-    runner = MlaMoeRunner(model, max_rows=chunk, slots=C, max_seq_len=max_len, device=dev)
+    lens = [int(x) for x in str(getattr(args, "prompt_lens", "") or args.prompt_len).split(",")]
+    max_len = max(lens) + 512
+    # the indexer keeps a [chunk, context] fp32 score matrix (1 GB at 2048 x 131072)
+    chunk = int(getattr(args, "prefill_chunk", 0) or 0) or 2048
+    # cache bytes of C independent requests at the longest prompt; when they do not fit beside the weights, the other
+    # slots continue slot 0's prefix (shared blocks, private tails)
+    per_slot = max_len * ((cfg.kv_lora + cfg.rope) + (cfg.index_dim if indexer else 0)) * 2 * layers
+    shared = C * per_slot > 0.7 * torch.cuda.mem_get_info()[0]
+    runner = MlaMoeRunner(model, max_rows=chunk, slots=C, max_seq_len=max_len, device=dev,
+                          shared_tail_blocks=(512 // cfg.page + 1) if shared else 0)
     g = torch.Generator().manual_seed(2)
     out = {"config": 3 if indexer else 2,
            "model": "MLA (q_lora 1024, kv_lora 512, nope 128 + rope 64, v 128, 32 heads) + MoE 256e top-8 (8 groups, top-4) + shared, "
                     f"hidden 4096, {layers} layers ({cfg.dense_layers} dense FFN 12288), NVFP4 weights, bf16 latent cache"
-                    + (", lightning indexer 64 x 128, top-2048 sparse attention" if indexer else ""),
+                    + (", lightning indexer 64 x 128, top-2048 sparse attention, YaRN factor 4 over 32768" if indexer else ""),
            "layers": layers, "valid": layers == 48, "init_s": round(init_s, 1), "moe_prefill_act_terms": terms,
            "note": "weights NVFP4 throughout (the family's MXFP4 experts and FP8 128x128 attention weights map onto the same "
                    "block-scaled / converter kernels); attention through the absorbed-latent decode kernel for prefill rows too"}
-    L = args.prompt_len
-    out[f"prefill_s_{L}"] = _time_prefill(runner, cfg.vocab, 0, L, g, chunk)
-    for s in range(1, C):
-        runner.reset(s)
-        runner.prefill(s, torch.randint(0, cfg.vocab, (L,), generator=g).tolist(), chunk=chunk)
-    ms1 = _time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g)
-    ms8 = _time_decode(runner, cfg.vocab, list(range(C)), args.steps, args.warmup, g)
-    out.update(c1_decode_tok_s=1000.0 / ms1, c1_ms_per_step=ms1, c8_decode_tok_s=1000.0 * C / ms8, c8_ms_per_step=ms8,
-               steps=args.steps, context=L)
+    if len(lens) == 1 and lens[0] <= 8192:
+        L = lens[0]
+        out[f"prefill_s_{L}"] = _time_prefill(runner, cfg.vocab, 0, L, g, chunk)
+        for s in range(1, C):
+            runner.reset(s)
+            runner.prefill(s, torch.randint(0, cfg.vocab, (L,), generator=g).tolist(), chunk=chunk)
+        ms1 = _time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g)
+        ms8 = _time_decode(runner, cfg.vocab, list(range(C)), args.steps, args.warmup, g)
+        out.update(c1_decode_tok_s=1000.0 / ms1, c1_ms_per_step=ms1, c8_decode_tok_s=1000.0 * C / ms8, c8_ms_per_step=ms8,
+                   steps=args.steps, context=L)
+        return out
+    # long prompts: slot 0 is prefilled (timed); the other seven contexts are copies of its cache (or, when eight
+    # full-length caches do not fit, readers of its blocks), which costs a decode step what eight prompts would
+    out["contexts"] = ("slot 0 prefilled; slots 1-7 read its prefix blocks and append to private tails (8 full-length caches "
+                       "do not fit beside the weights on one GPU)" if shared else
+                       "slot 0 prefilled; its cache rows copied into the blocks of slots 1-7")
+    for L in lens:
+        for s in range(C):
+            runner.reset(s)
+        out[f"prefill_s_{L}"] = _time_prefill(runner, cfg.vocab, 0, L, g, chunk)
+        ms1 = _time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g)
+        base = runner.lengths[0] // cfg.page * cfg.page if shared else runner.lengths[0]
+        for s in range(1, C):
+            if shared:
+                runner.att.share_prefix(s, base)
+            else:
+                runner.att.clone_prefix(s, base)
+            runner.lengths[s] = base
+        ms8 = _time_decode(runner, cfg.vocab, list(range(C)), args.steps, args.warmup, g)
+        out[f"ctx_{L}"] = {"c1_decode_tok_s": 1000.0 / ms1, "c1_ms_per_step": ms1, "c8_decode_tok_s": 1000.0 * C / ms8,
+                           "c8_ms_per_step": ms8}
+    out["steps"] = args.steps
     return out
 
 

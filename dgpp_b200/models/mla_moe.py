@@ -45,6 +45,13 @@ class MlaMoeConfig:
     vocab: int = 4096
     eps: float = 1e-6
     rope_theta: float = 1e4
+    # YaRN context extension of the rotary part (factor 1 = plain RoPE): frequencies whose wavelength exceeds the
+    # original context are interpolated by `yarn_factor`, fast ones are kept, a linear ramp in between; the softmax
+    # scale is multiplied by (0.1 ln(factor) + 1)^2
+    yarn_factor: float = 1.0
+    yarn_orig_ctx: int = 4096
+    yarn_beta_fast: float = 32.0
+    yarn_beta_slow: float = 1.0
     page: int = 64
     moe: Optional[MoEConfig] = None
     # sparse index (0 heads = dense attention everywhere)
@@ -84,12 +91,31 @@ def _rope(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.T
     return torch.cat([a * c - b * s, b * c + a * s], -1)
 
 
+def yarn_inv_freq(dim: int, theta: float, factor: float, orig_ctx: int, beta_fast: float = 32.0, beta_slow: float = 1.0,
+                  device=None) -> torch.Tensor:
+    """Rotary inverse frequencies [dim / 2] under YaRN scaling (factor <= 1: the plain table)."""
+    extra = 1.0 / (theta ** (torch.arange(0, dim, 2, device=device).float() / dim))
+    if factor <= 1.0:
+        return extra
+    corr = lambda rot: dim * math.log(orig_ctx / (rot * 2 * math.pi)) / (2 * math.log(theta))
+    low, high = max(math.floor(corr(beta_fast)), 0), min(math.ceil(corr(beta_slow)), dim // 2 - 1)
+    ramp = ((torch.arange(dim // 2, device=device).float() - low) / max(high - low, 1e-3)).clamp(0, 1)
+    return extra / factor * ramp + extra * (1 - ramp)
+
+
+def softmax_scale(c) -> float:
+    """1 / sqrt(nope + rope), times the YaRN magnitude correction when the config extends the context."""
+    f = float(getattr(c, "yarn_factor", 1.0))
+    m = 0.1 * math.log(f) + 1.0 if f > 1.0 else 1.0
+    return m * m / math.sqrt(c.nope + c.rope)
+
+
 def mla_attention_reference(c, inv_freq: torch.Tensor, L: "MlaLayer", xn: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
     """Plain (non-absorbed) latent attention of consecutive tokens of one request from position 0, with the sparse
     index when the layer has one.  c: any config with heads / q_lora / kv_lora / nope / rope / v_dim / index_* / eps.
     xn [T, H] bf16 normed rows -> o [T, H] bf16 (after the output projection)."""
     T = xn.shape[0]
-    scale = 1.0 / math.sqrt(c.nope + c.rope)
+    scale = softmax_scale(c)
     cq = ref.rmsnorm(ref.linear(xn, L.q_a), L.q_a_norm, c.eps)[0]
     q = ref.linear(cq, L.q_b).float().view(T, c.heads, c.nope + c.rope)
     q_n, q_r = q[..., :c.nope], ref._r(_rope(q[..., c.nope:], pos, inv_freq))
@@ -150,7 +176,8 @@ class MlaMoeModel:
                 L.idx_w = quantize(rnd(c.index_heads, H), "bf16")
             layers.append(L)
         embed = (torch.randn(cfg.vocab, H, device=device, generator=g) * std).to(BF)
-        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.rope, 2, device=device).float() / cfg.rope))
+        inv = yarn_inv_freq(cfg.rope, cfg.rope_theta, cfg.yarn_factor, cfg.yarn_orig_ctx, cfg.yarn_beta_fast,
+                            cfg.yarn_beta_slow, device)
         return MlaMoeModel(cfg, embed, layers, ones(H), quantize(rnd(cfg.vocab, H), "bf16"), inv)
 
     # ------------------------------------------------------------------ oracle (plain, non-absorbed attention)
@@ -180,19 +207,48 @@ class MlaCaches:
     """Paged latent cache (+ index-key cache) of the MLA layers of a model and the absorbed-attention launch sequence
     of one layer.  Shared by the families that contain MLA layers."""
 
-    def __init__(self, c, layers: int, indexed: List[bool], max_rows: int, slots: int, max_seq_len: int, device):
+    def __init__(self, c, layers: int, indexed: List[bool], max_rows: int, slots: int, max_seq_len: int, device,
+                 shared_tail_blocks: int = 0):
+        """shared_tail_blocks > 0: memory for ONE full-length request plus that many private blocks for each further
+        slot; `share_prefix` then lets the other slots read the first slot's prefix (requests that continue a common
+        long prefix, when independent full-length caches would not fit)."""
         self.c, self.dev = c, device
         self.page = c.page
         self.max_blocks = (max_seq_len + c.page - 1) // c.page + 1
-        nblocks = slots * self.max_blocks + 1
+        self.tail_blocks = shared_tail_blocks
+        nblocks = (self.max_blocks + (slots - 1) * shared_tail_blocks if shared_tail_blocks else slots * self.max_blocks) + 1
         self.max_ctx = self.max_blocks * c.page
         self.latent = [torch.zeros(nblocks, c.page, c.kv_lora + c.rope, dtype=BF, device=device) for _ in range(layers)]
         self.kidx = [torch.zeros(nblocks, c.page, c.index_dim, dtype=BF, device=device) if ix else None for ix in indexed]
         # static block table: slot s owns blocks [1 + s * max_blocks, 1 + (s + 1) * max_blocks)
-        self.block_table = (1 + torch.arange(slots * self.max_blocks, device=device, dtype=torch.int32)
-                            ).view(slots, self.max_blocks).contiguous()
-        self.scale = 1.0 / math.sqrt(c.nope + c.rope)
+        if shared_tail_blocks:
+            self.block_table = torch.zeros(slots, self.max_blocks, dtype=torch.int32, device=device)
+            self.block_table[0] = 1 + torch.arange(self.max_blocks, device=device, dtype=torch.int32)
+        else:
+            self.block_table = (1 + torch.arange(slots * self.max_blocks, device=device, dtype=torch.int32)
+                                ).view(slots, self.max_blocks).contiguous()
+        self.scale = softmax_scale(c)
         self.scores = torch.empty(max_rows, self.max_ctx, dtype=torch.float32, device=device) if any(indexed) else None
+
+    def share_prefix(self, dst: int, tokens: int) -> None:
+        """Slot `dst` reads the first `tokens` positions (a multiple of the page) from slot 0's blocks and appends into
+        its own tail blocks."""
+        assert self.tail_blocks and dst > 0 and tokens % self.page == 0
+        n = tokens // self.page
+        assert n + self.tail_blocks <= self.max_blocks
+        first = 1 + self.max_blocks + (dst - 1) * self.tail_blocks
+        row = torch.zeros(self.max_blocks, dtype=torch.int32, device=self.dev)
+        row[:n] = self.block_table[0, :n]
+        row[n:n + self.tail_blocks] = first + torch.arange(self.tail_blocks, device=self.dev, dtype=torch.int32)
+        self.block_table[dst].copy_(row)
+
+    def clone_prefix(self, dst: int, tokens: int) -> None:
+        """Copies the cache rows of slot 0's first `tokens` positions into slot `dst`'s own blocks."""
+        assert not self.tail_blocks
+        n = (tokens + self.page - 1) // self.page
+        src, to = self.block_table[0, :n].long(), self.block_table[dst, :n].long()
+        for cache in list(self.latent) + [k for k in self.kidx if k is not None]:
+            cache.index_copy_(0, to, cache.index_select(0, src))
 
     def _append(self, cache: torch.Tensor, rows: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor) -> None:
         blk = self.block_table[row_req.long(), (positions // self.page).long()].long()
@@ -230,11 +286,11 @@ class MlaMoeRunner:
     """Kernel execution: latent cache + index-key cache in pages, absorbed MLA decode kernel (dense or sparse), MoE
     block, tensor-core linears.  Rows may be a prefill chunk of one request or one decode token per request."""
 
-    def __init__(self, model: MlaMoeModel, max_rows: int, slots: int, max_seq_len: int, device):
+    def __init__(self, model: MlaMoeModel, max_rows: int, slots: int, max_seq_len: int, device, shared_tail_blocks: int = 0):
         c = model.cfg
         self.m, self.c, self.dev, self.max_rows = model, c, device, max_rows
         self.att = MlaCaches(c, len(model.layers), [L.idx_q is not None for L in model.layers], max_rows, slots,
-                             max_seq_len, device)
+                             max_seq_len, device, shared_tail_blocks)
         self.page, self.max_blocks, self.max_ctx = self.att.page, self.att.max_blocks, self.att.max_ctx
         self.latent, self.kidx, self.block_table = self.att.latent, self.att.kidx, self.att.block_table
         self.lengths = [0] * slots

@@ -54,3 +54,38 @@ def test_runner_matches_plain_attention_oracle(dev, moe, index):
         close(out[0], want_a[140 + s], f"decode a {s}")
         close(out[1], want_b[30 + s], f"decode b {s}")
     assert r.lengths == [144, 34]
+
+
+def test_yarn_scaled_rotary_and_shared_or_cloned_prefixes(dev):
+    """YaRN factor 4 over a short original context (the oracle and the kernels read the same frequency table and
+    softmax scale); a second slot that reads the first slot's prefix blocks, or a copy of them, decodes to the same
+    logits as the first slot does."""
+    from dgpp_b200.models.mla_moe import MlaMoeConfig, MlaMoeModel, MlaMoeRunner, softmax_scale
+    from dgpp_b200.ops import core as ops
+
+    cfg = MlaMoeConfig(layers=2, hidden=1024, heads=8, q_lora=256, kv_lora=128, nope=64, rope=32, v_dim=64, ffn=2048,
+                       vocab=2048, dense_layers=2, index_heads=4, index_dim=128, index_topk=48, yarn_factor=4.0,
+                       yarn_orig_ctx=64)
+    assert softmax_scale(cfg) > 1.0 / (cfg.nope + cfg.rope) ** 0.5
+    m = MlaMoeModel.random_init(cfg, dev, seed=3, std=0.04)
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(0, cfg.vocab, (200,), generator=g).tolist()
+    want = m.forward_reference(torch.tensor(toks, device=dev))
+    for shared in (False, True):
+        r = MlaMoeRunner(m, max_rows=64, slots=3, max_seq_len=512, device=dev, shared_tail_blocks=2 if shared else 0)
+        last = r.prefill(0, toks[:192], chunk=64)
+        err = (last[-1] - want[191]).abs().max().item()
+        assert err <= 0.12 * want[191].abs().max().item() + 0.02, err
+        for s in (1, 2):
+            if shared:
+                r.att.share_prefix(s, 192)
+            else:
+                r.att.clone_prefix(s, 192)
+            r.lengths[s] = 192
+        out = r.decode([0, 1, 2], [toks[192]] * 3).clone()
+        assert torch.equal(out[0], out[1]) and torch.equal(out[0], out[2]), shared
+        out2 = r.decode([2, 0], [toks[193], toks[193]])
+        assert torch.equal(out2[0], out2[1])
+        assert (out2[0] - want[193]).abs().max().item() <= 0.12 * want[193].abs().max().item() + 0.02
+    torch.cuda.synchronize()
+    ops.check_status()
