@@ -276,8 +276,11 @@ class MlaCaches:
             sc = ops.dsa_index(qi, wi, self.kidx[j], self.block_table, row_req, positions, self.max_ctx,
                                scores=self.scores[:rows])
             sel = ops.topk_select(sc, positions, c.index_topk)
+        # decode rows: enough (row, head group, context split) CTAs to cover the SMs; a split beyond a short context
+        # writes an empty partial, so the count depends on the batch width only (a captured pass stays valid)
+        splits = max(1, min(64, -(-148 // (rows * -(-c.heads // 32))))) if rows <= 16 else 1
         lat = ops.mla_decode(q_full, self.latent[j], self.block_table, row_req, positions, self.scale, c.kv_lora,
-                             c.rope, sel=sel, splits=4 if rows <= 16 else 1)
+                             c.rope, sel=sel, splits=splits)
         a = ops.mla_v_up(lat, L.w_uv)
         return ops.linear(a, L.o, out=out)
 
