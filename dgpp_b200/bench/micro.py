@@ -121,6 +121,7 @@ def bench_gemm_tc(args, dev):
     from ..quant.formats import random_quant_linear
 
     n, k, rows = args.n, args.k, args.rows
+    ops.PAIR_GEMM = not args.no_pair
     ws = [random_quant_linear(n, k, args.fmt, dev) for _ in range(2)]
     x = torch.randn(rows, k, device=dev).to(BF)
     out = torch.empty(rows, n, device=dev, dtype=BF)
@@ -128,7 +129,8 @@ def bench_gemm_tc(args, dev):
     ms = run(fns, args)
     ops.check_status()
     report(args, "gemm_tc", ms, bytes_=ws[0].nbytes + rows * k * 2 + rows * n * 2, flops=2.0 * rows * n * k, rows=rows, n=n, k=k,
-           fmt=args.fmt)
+           fmt=args.fmt, cta_pairs=bool(ops.PAIR_GEMM and rows >= ops.PAIR_GEMM_MIN_ROWS and args.fmt in ("nvfp4", "mxfp4")
+                                        and n % 256 == 0))
 
 
 def bench_gemm_fp8(args, dev):
@@ -360,6 +362,7 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--moe-ffn", type=int, default=1536)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--no-pair", action="store_true", help="gemm_tc: keep 4-bit prefill GEMMs on the single-CTA kernel")
     ap.add_argument("--trace", action="store_true", help="gemm_fp4: print the phase timestamps of one CTA")
     ap.add_argument("--once", action="store_true", help="a few plain launches, no graph, no timing (for profilers)")
     args = ap.parse_args(argv)

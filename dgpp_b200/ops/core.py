@@ -132,6 +132,28 @@ def pick_splits(rows: int, n: int, k: int, bn: int, sms: int = 148) -> int:
     return max(1, min(want, kb // 8))
 
 
+# 4-bit weights at prefill sizes can run on CTA pairs (`gemm_tc_pair.cu`: 256 weight rows x 256 tokens per pair, each
+# SM loading half of the activation tile); results are bit-identical to the single-CTA kernel.  Off by default: it
+# measured slower (537 against 596-662 TFLOP/s at 2048 x 34816 x 5120).
+PAIR_GEMM = False
+PAIR_GEMM_MIN_ROWS = 512
+
+_lib.declare("dgpp_gemm_tc_pair", [I, P, L, P, P, F, P, P, I, I, I, I, P])
+
+
+def gemm_tc_pair(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
+                 resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The W4A16 linear on CTA pairs (NVFP4 / MXFP4 weights, N a multiple of 256)."""
+    _chk(x, torch.bfloat16, "x")
+    rows, k = x.shape
+    assert k == w.k and w.fmt in ("nvfp4", "mxfp4") and w.n % 256 == 0 and k % 256 == 0
+    if out is None:
+        out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=x.device)
+    call("dgpp_gemm_tc_pair", _FMT_GEMM[w.fmt], ptr(x), x.stride(0), ptr(w.payload), ptr(w.scale), float(w.alpha), ptr(out),
+         ptr(resid), out.stride(0), rows, w.n, k, stream_ptr())
+    return out
+
+
 def gemm_tc(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
             out32: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
             bn: Optional[int] = None, splits: Optional[int] = None, a_f16: Optional[int] = None,
@@ -141,6 +163,9 @@ def gemm_tc(x: torch.Tensor, w: QuantLinear, out: Optional[torch.Tensor] = None,
     rows, k = x.shape
     assert k == w.k, (k, w.k)
     assert w.fmt in _FMT_GEMM, w.fmt
+    if (PAIR_GEMM and out32 is None and bn is None and splits in (None, 1) and rows >= PAIR_GEMM_MIN_ROWS
+            and w.fmt in ("nvfp4", "mxfp4") and w.n % 256 == 0 and k % 256 == 0):
+        return gemm_tc_pair(x, w, out=out, resid=resid)
     if out is None and out32 is None:
         out = torch.empty(rows, w.n, dtype=torch.bfloat16, device=x.device)
     ldc = (out if out is not None else out32).stride(0)

@@ -227,3 +227,33 @@ def test_attn_prefill_tc_head_dim_256(dev, hq, hkv, ctx, page, pos0, T):
     base = ops.attn_decode(q, q.stride(0), kv.layers[0], kv.block_table, req[pos0:pos0 + T].contiguous(),
                            pos[pos0:pos0 + T].contiguous(), hq, hkv, d, scale, splits=1)
     assert (out.float() - base.float()).abs().max().item() < 0.03
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("rows,n,k", [(512, 512, 1024), (700, 1024, 512), (300, 256, 2048), (2048, 5120, 1024)])
+def test_pair_gemm_is_bit_identical_to_the_single_cta_kernel(fmt, rows, n, k):
+    """4-bit prefill GEMM on CTA pairs (one 256 x 256 MMA tile per pair, each CTA converting its own weight rows and
+    loading its own token half): same bits as the single-CTA kernel, with and without the residual add, for token
+    counts that leave the second CTA's half partly or wholly outside the matrix."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.quant.formats import random_quant_linear
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(rows + n)
+    w = random_quant_linear(n, k, fmt, dev)
+    x = torch.randn(rows, k, device=dev).to(torch.bfloat16)
+    resid = torch.randn(rows, n, device=dev).to(torch.bfloat16)
+    old = ops.PAIR_GEMM
+    try:
+        ops.PAIR_GEMM = False
+        want, want_r = ops.gemm_tc(x, w, splits=1), ops.gemm_tc(x, w, resid=resid, splits=1)
+    finally:
+        ops.PAIR_GEMM = old
+    got, got_r = ops.gemm_tc_pair(x, w), ops.gemm_tc_pair(x, w, resid=resid)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(got, want) and torch.equal(got_r, want_r)
+    ref = (x.float() @ w.dequant().float().t())
+    assert (got.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
