@@ -46,6 +46,44 @@ static bool own_kernel(cudaGraphNode_t node) {
   return strstr(name, "4dgpp") != nullptr;   // Itanium mangling of namespace dgpp
 }
 
+// Rewrites the kernel -> kernel edges of `graph` whose successor is a kernel of this library as programmatic edges;
+// returns how many were rewritten.
+static int rewrite_pdl_edges(cudaGraph_t graph) {
+  int rewritten = 0;
+  size_t ne = 0;
+  if (cudaGraphGetEdges_v2(graph, nullptr, nullptr, nullptr, &ne) != cudaSuccess || !ne) {
+    cudaGetLastError();
+    return 0;
+  }
+  std::vector<cudaGraphNode_t> from(ne), to(ne);
+  std::vector<cudaGraphEdgeData> data(ne);
+  cudaGraphGetEdges_v2(graph, from.data(), to.data(), data.data(), &ne);
+  for (size_t e = 0; e < ne; ++e) {
+    cudaGraphNodeType tf, tt;
+    cudaGraphNodeGetType(from[e], &tf);
+    cudaGraphNodeGetType(to[e], &tt);
+    if (tf != cudaGraphNodeTypeKernel || tt != cudaGraphNodeTypeKernel) continue;
+    if (data[e].type == cudaGraphDependencyTypeProgrammatic) continue;
+    if (!own_kernel(to[e])) continue;   // a foreign kernel (NCCL, torch) never executes griddepcontrol.wait
+    cudaGraphEdgeData nd;
+    memset(&nd, 0, sizeof(nd));
+    nd.from_port = cudaGraphKernelNodePortProgrammatic;
+    nd.to_port = 0;
+    nd.type = cudaGraphDependencyTypeProgrammatic;
+    if (cudaGraphRemoveDependencies_v2(graph, &from[e], &to[e], &data[e], 1) != cudaSuccess) {
+      cudaGetLastError();
+      continue;
+    }
+    if (cudaGraphAddDependencies_v2(graph, &from[e], &to[e], &nd, 1) != cudaSuccess) {
+      cudaGetLastError();
+      cudaGraphAddDependencies_v2(graph, &from[e], &to[e], &data[e], 1);  // put the plain edge back
+      continue;
+    }
+    ++rewritten;
+  }
+  return rewritten;
+}
+
 }  // namespace
 
 DGPP_API int dgpp_graph_begin_capture(cudaStream_t st) {
@@ -77,39 +115,7 @@ DGPP_API void* dgpp_graph_end_capture(cudaStream_t st, int pdl, int allow_non_ke
     delete g;
     return nullptr;
   }
-  if (pdl) {
-    size_t ne = 0;
-    if (cudaGraphGetEdges_v2(g->graph, nullptr, nullptr, nullptr, &ne) == cudaSuccess && ne) {
-      std::vector<cudaGraphNode_t> from(ne), to(ne);
-      std::vector<cudaGraphEdgeData> data(ne);
-      cudaGraphGetEdges_v2(g->graph, from.data(), to.data(), data.data(), &ne);
-      for (size_t e = 0; e < ne; ++e) {
-        cudaGraphNodeType tf, tt;
-        cudaGraphNodeGetType(from[e], &tf);
-        cudaGraphNodeGetType(to[e], &tt);
-        if (tf != cudaGraphNodeTypeKernel || tt != cudaGraphNodeTypeKernel) continue;
-        if (data[e].type == cudaGraphDependencyTypeProgrammatic) continue;
-        if (!own_kernel(to[e])) continue;   // a foreign kernel (NCCL, torch) never executes griddepcontrol.wait
-        cudaGraphEdgeData nd;
-        memset(&nd, 0, sizeof(nd));
-        nd.from_port = cudaGraphKernelNodePortProgrammatic;
-        nd.to_port = 0;
-        nd.type = cudaGraphDependencyTypeProgrammatic;
-        if (cudaGraphRemoveDependencies_v2(g->graph, &from[e], &to[e], &data[e], 1) != cudaSuccess) {
-          cudaGetLastError();
-          continue;
-        }
-        if (cudaGraphAddDependencies_v2(g->graph, &from[e], &to[e], &nd, 1) != cudaSuccess) {
-          cudaGetLastError();
-          cudaGraphAddDependencies_v2(g->graph, &from[e], &to[e], &data[e], 1);  // put the plain edge back
-          continue;
-        }
-        ++g->programmatic_edges;
-      }
-    } else {
-      cudaGetLastError();
-    }
-  }
+  if (pdl) g->programmatic_edges = rewrite_pdl_edges(g->graph);
   if (cudaGraphInstantiate(&g->exec, g->graph, 0) != cudaSuccess) {
     dgpp_set_error("graph: cudaGraphInstantiate failed: %s", cudaGetErrorString(cudaGetLastError()));
     cudaGraphDestroy(g->graph);
@@ -122,6 +128,30 @@ DGPP_API void* dgpp_graph_end_capture(cudaStream_t st, int pdl, int allow_non_ke
     info_out[2] = g->programmatic_edges;
   }
   return g;
+}
+
+// The same edge rewrite on a graph somebody else captured and will instantiate (a framework's graph object that keeps
+// its cudaGraph_t until the first replay).  info_out[0..2] = kernel nodes, other nodes, programmatic edges.
+DGPP_API int dgpp_graph_pdl_rewrite(void* raw_graph, int* info_out) {
+  DGPP_REQUIRE(raw_graph != nullptr, "graph_pdl_rewrite: null graph");
+  cudaGraph_t graph = static_cast<cudaGraph_t>(raw_graph);
+  size_t n = 0;
+  DGPP_CUDA_OK(cudaGraphGetNodes(graph, nullptr, &n));
+  std::vector<cudaGraphNode_t> nodes(n);
+  if (n) DGPP_CUDA_OK(cudaGraphGetNodes(graph, nodes.data(), &n));
+  int kernels = 0, others = 0;
+  for (size_t i = 0; i < n; ++i) {
+    cudaGraphNodeType t;
+    cudaGraphNodeGetType(nodes[i], &t);
+    if (t == cudaGraphNodeTypeKernel) ++kernels; else ++others;
+  }
+  const int edges = rewrite_pdl_edges(graph);
+  if (info_out) {
+    info_out[0] = kernels;
+    info_out[1] = others;
+    info_out[2] = edges;
+  }
+  return 0;
 }
 
 DGPP_API int dgpp_graph_launch(void* handle, cudaStream_t st) {

@@ -10,6 +10,24 @@ from ..ops import _lib
 from ..ops._lib import P, call
 
 
+def capture_with_pdl(body, pdl: bool = True):
+    """Captures `body()` into a torch CUDA graph (private memory pool, so tensors created inside stay valid) and, before
+    it is instantiated, rewrites the kernel -> kernel edges that end in a kernel of this library as programmatic
+    dependent launches: those kernels wait for their predecessor themselves, so their prologue overlaps its tail.
+    Edges into framework kernels stay plain.  Returns (graph, body's result, programmatic edge count)."""
+    graph = torch.cuda.CUDAGraph(keep_graph=True) if pdl else torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = body()
+    edges = 0
+    if pdl:
+        _lib.declare("dgpp_graph_pdl_rewrite", [P, P])
+        info = (C.c_int * 3)()
+        call("dgpp_graph_pdl_rewrite", graph.raw_cuda_graph(), C.cast(info, P))
+        edges = info[2]
+        graph.instantiate()
+    return graph, out, edges
+
+
 class NativeGraph:
     def __init__(self, body, pdl: bool = True, allow_non_kernel: bool = False):
         lib = _lib.load()

@@ -242,6 +242,7 @@ class GlmFlashRunner:
                                 device=device)
         self.lengths = [0] * slots
         self.use_graphs, self._graphs, self._static = True, {}, {}
+        self.pdl_graphs = True      # programmatic-dependent-launch edges between this library's kernels in captured passes
 
     def reset(self, slot: int) -> None:
         self.lengths[slot] = 0
@@ -353,9 +354,8 @@ class GlmFlashRunner:
                     self.forward(st[0], st[1], st[2], select=select)
                 torch.cuda.current_stream().wait_stream(side)
                 torch.cuda.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    out = self.forward(st[0], st[1], st[2], select=select)
+                from ..engine.graph import capture_with_pdl
+                graph, out, _ = capture_with_pdl(lambda: self.forward(st[0], st[1], st[2], select=select), self.pdl_graphs)
                 for t, s0 in zip(self._state_tensors(), saved):
                     t.copy_(s0)
                 g = self._graphs[key] = (graph, out)

@@ -209,6 +209,7 @@ class HybridRunner:
         self.lengths = [0] * slots
         self.scale = 1.0 / math.sqrt(d)
         self.use_graphs, self._graphs, self._static = True, {}, {}
+        self.pdl_graphs = True      # programmatic-dependent-launch edges between this library's kernels in captured passes
         # tensor-core attention (FP8 cache as stored): head_dim 128 / 256, up to 8 query heads per kv head
         self.tc_attn = (torch.device(device).type == "cuda" and d in (128, 256)
                         and c.q_heads // c.kv_heads in (1, 2, 4, 8))
@@ -363,9 +364,8 @@ class HybridRunner:
                 self.forward(st[0], st[1], st[2], seg=seg, snap=snap)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                out = self.forward(st[0], st[1], st[2], seg=seg, snap=snap)
+            from ..engine.graph import capture_with_pdl
+            graph, out, _ = capture_with_pdl(lambda: self.forward(st[0], st[1], st[2], seg=seg, snap=snap), self.pdl_graphs)
             for t, s0 in zip(self._state_tensors(), saved):
                 t.copy_(s0)
             g = self._graphs[key] = (graph, out)

@@ -300,6 +300,7 @@ class MlaMoeRunner:
         self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
                     if L.moe is not None and L.moe.gu_q is not None}
         self.use_graphs, self._graphs, self._static = True, {}, {}
+        self.pdl_graphs = True      # programmatic-dependent-launch edges between this library's kernels in captured passes
 
     def reset(self, slot: int) -> None:
         self.lengths[slot] = 0
@@ -378,9 +379,8 @@ class MlaMoeRunner:
                 self.forward(st[0], st[1], st[2], select=select)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                out = self.forward(st[0], st[1], st[2], select=select)
+            from ..engine.graph import capture_with_pdl
+            graph, out, _ = capture_with_pdl(lambda: self.forward(st[0], st[1], st[2], select=select), self.pdl_graphs)
             for t, s0 in zip(self._state_tensors(), saved):
                 t.copy_(s0)
             g = self._graphs[key] = (graph, out)

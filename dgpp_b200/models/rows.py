@@ -23,6 +23,7 @@ class RowRunner:
         self.dev, self.slots, self.max_rows = device, slots, max_rows
         self.lengths = [0] * slots
         self.use_graphs, self._graphs, self._static = True, {}, {}
+        self.pdl_graphs = True      # programmatic-dependent-launch edges between this library's kernels in captured passes
         self.kv = None
         if kv_layers:
             blocks_per = (max_seq_len + page - 1) // page + 1
@@ -128,9 +129,8 @@ class RowRunner:
                     self.forward(st[0], st[1], st[2], extra=rest(st))
                 torch.cuda.current_stream().wait_stream(side)
                 torch.cuda.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    out = self.forward(st[0], st[1], st[2], extra=rest(st))
+                from ..engine.graph import capture_with_pdl
+                graph, out, _ = capture_with_pdl(lambda: self.forward(st[0], st[1], st[2], extra=rest(st)), self.pdl_graphs)
                 for t, s0 in zip(self._state_tensors(), saved):
                     t.copy_(s0)
                 g = self._graphs[b] = (graph, out)
