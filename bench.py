@@ -156,6 +156,7 @@ def main() -> int:
     ap.add_argument("--concurrency", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--prefill-chunk", type=int, default=0, help="--config 2 / 3: rows per prefill pass (0: 2048)")
+    ap.add_argument("--index-bf16", action="store_true", help="--config 3: keep the index keys in bf16 (default: e4m3 + per-token scale)")
     ap.add_argument("--prompt-lens", default="", help="--config 2 / 3: several long prompt lengths in one run, e.g. 32768,131072")
     ap.add_argument("--mtp", type=int, default=0, choices=(0, 1, 2, 3),
                     help="--config 4: speculative decoding with this many MTP drafts per step (0 = off)")

@@ -141,7 +141,8 @@ def run_config2(args, dev, indexer: bool = False) -> dict:
                        moe=MoEConfig(hidden=4096, experts=256, top_k=8, moe_ffn=1536, shared_ffn=1536, n_group=8,
                                      topk_group=4, router="sigmoid", routed_scaling=2.5),
                        index_heads=64 if indexer else 0, index_dim=128, index_topk=2048,
-                       yarn_factor=4.0 if indexer else 1.0, yarn_orig_ctx=32768)
+                       yarn_factor=4.0 if indexer else 1.0, yarn_orig_ctx=32768,
+                       index_key_fp8=indexer and not getattr(args, "index_bf16", False))
     t0 = time.time()
     terms = _lean_experts(args)
     model = MlaMoeModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4")
@@ -162,7 +163,8 @@ def run_config2(args, dev, indexer: bool = False) -> dict:
     out = {"config": 3 if indexer else 2,
            "model": "MLA (q_lora 1024, kv_lora 512, nope 128 + rope 64, v 128, 32 heads) + MoE 256e top-8 (8 groups, top-4) + shared, "
                     f"hidden 4096, {layers} layers ({cfg.dense_layers} dense FFN 12288), NVFP4 weights, bf16 latent cache"
-                    + (", lightning indexer 64 x 128, top-2048 sparse attention, YaRN factor 4 over 32768" if indexer else ""),
+                    + (f", lightning indexer 64 x 128 ({'e4m3 keys with per-token scales' if cfg.index_key_fp8 else 'bf16 keys'}), "
+                       "top-2048 sparse attention, YaRN factor 4 over 32768" if indexer else ""),
            "layers": layers, "valid": layers == 48, "init_s": round(init_s, 1), "moe_prefill_act_terms": terms,
            "note": "weights NVFP4 throughout (the family's MXFP4 experts and FP8 128x128 attention weights map onto the same "
                    "block-scaled / converter kernels); attention through the absorbed-latent decode kernel for prefill rows too"}

@@ -10,7 +10,10 @@
 //                              untouched (period 0: every row is rotated)
 //   hadamard32_quant_int8_kernel   the same rotation followed by int8 codes per group of 128 rotated bf16 values:
 //                              scale = max(amax / 127, 1e-30), code = clamp(rint(x / scale), -128, 127)
-// (reference counterparts: src/kernels/glm_moe.cu:923 moe_hash_routes_kernel, src/kernels/hadamard32.cu.)
+//   ple_embed_add_kernel       hashed bigram embeddings: row r of x gets table[(prev[r] * 1000003 + token[r] * 7919 + 12345)
+//                              mod table rows] added (fp32 sum, one bf16 rounding); the ids never visit the host
+// (reference counterparts: src/kernels/glm_moe.cu:923 moe_hash_routes_kernel, src/kernels/hadamard32.cu,
+//  src/kernels/qwen_ple.cu hash ids + gather.)
 #include <math.h>
 
 #include "common/common.h"
@@ -38,6 +41,19 @@ __global__ void moe_hash_routes_kernel(const int32_t* __restrict__ tokens, const
     ids[static_cast<size_t>(t) * k + i] = row[i];
     weights[static_cast<size_t>(t) * k + i] = (norm_topk ? __fdiv_rn(s, sum) : s) * scaling;
   }
+}
+
+// grid (rows), 128 threads
+__global__ void __launch_bounds__(128) ple_embed_add_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ prev,
+                                                            const bf16* __restrict__ table, bf16* __restrict__ x, int hidden,
+                                                            int table_rows) {
+  pdl_wait();
+  const int r = blockIdx.x;
+  const long long id = (static_cast<long long>(prev[r]) * 1000003ll + static_cast<long long>(tokens[r]) * 7919ll + 12345ll) %
+                       static_cast<long long>(table_rows);
+  const bf16* src = table + static_cast<size_t>(id < 0 ? id + table_rows : id) * hidden;
+  bf16* dst = x + static_cast<size_t>(r) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += 128) dst[i] = f32_to_bf16(__fadd_rn(bf16_to_f32(dst[i]), bf16_to_f32(src[i])));
 }
 
 __device__ __forceinline__ float h32_lane(float v, int lane) {
@@ -101,6 +117,16 @@ DGPP_API int dgpp_moe_hash_routes(const void* tokens, const void* tid2eid, const
   moe_hash_routes_kernel<<<dgpp_ceil_div(T, 64), 64, 0, st>>>(static_cast<const int32_t*>(tokens), static_cast<const int32_t*>(tid2eid),
                                                               static_cast<const float*>(scores), static_cast<int32_t*>(ids),
                                                               static_cast<float*>(weights), T, vocab, E, k, scaling, norm_topk);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+DGPP_API int dgpp_ple_embed_add(const void* tokens, const void* prev, const void* table, void* x, int rows, int hidden,
+                                int table_rows, cudaStream_t st) {
+  DGPP_REQUIRE(hidden >= 1 && table_rows >= 1, "ple_embed_add: bad sizes");
+  if (rows == 0) return 0;
+  ple_embed_add_kernel<<<rows, 128, 0, st>>>(static_cast<const int32_t*>(tokens), static_cast<const int32_t*>(prev),
+                                             static_cast<const bf16*>(table), static_cast<bf16*>(x), hidden, table_rows);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -200,7 +200,7 @@ class FlashNextRunner(RowRunner):
         H = c.hidden
         self.R, self.rn, self.logits_g = e(max_rows, c.hc * H), e(max_rows, c.hc * H), e(max_rows, c.hc * H)
         self.t = e(max_rows, c.gr_rank)
-        self.x, self.y, self.pl = e(max_rows, H), e(max_rows, H), e(max_rows, H)
+        self.x, self.y = e(max_rows, H), e(max_rows, H)
         self.qkv = e(max_rows, (c.q_heads + 2 * c.kv_heads) * c.head_dim)
         self.attn = e(max_rows, c.q_heads * c.head_dim)
         self.last_token = [0] * slots
@@ -216,9 +216,10 @@ class FlashNextRunner(RowRunner):
     def _extra_rows(self, slots, tokens, prefill_slot=None):
         if self.m.ple is None:
             return []
+        # the previous token of every row; the bigram hash and the table gather run on the device
         if prefill_slot is not None:
-            return [self.m.ple_ids(tokens, self.last_token[prefill_slot])]
-        return [[self.c.ple_id(self.last_token[s], t) for s, t in zip(slots, tokens)]]
+            return [[self.last_token[prefill_slot]] + list(tokens[:-1])]
+        return [[self.last_token[s] for s in slots]]
 
     def _note_tokens(self, slot, tokens):
         self.last_token[slot] = tokens[-1]
@@ -253,7 +254,7 @@ class FlashNextRunner(RowRunner):
         rows = tokens.shape[0]
         x = ops.embed_gather(tokens, m.embed, out=self.x[:rows])
         if m.ple is not None:
-            ops.add(x, ops.embed_gather(extra[0], m.ple, out=self.pl[:rows]), out=x)
+            ops.ple_embed_add(tokens, extra[0], m.ple, x)
         self.R[:rows].view(rows, c.hc, c.hidden).copy_(x.unsqueeze(1).expand(rows, c.hc, c.hidden))
         for i, L in enumerate(m.layers):
             if L.gdn is not None:

@@ -58,6 +58,7 @@ class MlaMoeConfig:
     index_heads: int = 0
     index_dim: int = 64
     index_topk: int = 64
+    index_key_fp8: bool = False  # index keys cached as e4m3 with one scale per token (index_dim 128, tensor-core kernel)
 
 
 @dataclass
@@ -129,6 +130,10 @@ def mla_attention_reference(c, inv_freq: torch.Tensor, L: "MlaLayer", xn: torch.
     if L.idx_q is not None:
         qi = ref.linear(xn, L.idx_q).float().view(T, c.index_heads, c.index_dim)
         ki = ref.linear(xn, L.idx_k).float()                                                  # [T, di]
+        if getattr(c, "index_key_fp8", False):             # the cache holds e4m3(k / scale), scale = amax / 448 per token
+            sc = (ki.abs().amax(-1, keepdim=True) / 448.0).clamp_min(1e-30)
+            sc = torch.where(ki.abs().amax(-1, keepdim=True) > 0, sc, torch.ones_like(sc))
+            ki = (ki / sc).to(torch.float8_e4m3fn).float() * sc
         wi = ref.linear(xn, L.idx_w).float()                                                  # [T, hi]
         sc = (torch.relu(torch.einsum("qhd,kd->qhk", qi, ki)) * wi.unsqueeze(-1)).sum(1)      # [q, k]
         sc = sc.masked_fill(mask, float("-inf"))
@@ -219,7 +224,11 @@ class MlaCaches:
         nblocks = (self.max_blocks + (slots - 1) * shared_tail_blocks if shared_tail_blocks else slots * self.max_blocks) + 1
         self.max_ctx = self.max_blocks * c.page
         self.latent = [torch.zeros(nblocks, c.page, c.kv_lora + c.rope, dtype=BF, device=device) for _ in range(layers)]
-        self.kidx = [torch.zeros(nblocks, c.page, c.index_dim, dtype=BF, device=device) if ix else None for ix in indexed]
+        self.key_fp8 = bool(getattr(c, "index_key_fp8", False))
+        self.kidx = [torch.zeros(nblocks, c.page, c.index_dim, dtype=torch.uint8 if self.key_fp8 else BF, device=device)
+                     if ix else None for ix in indexed]
+        self.kscale = [torch.ones(nblocks, c.page, dtype=torch.float32, device=device) if ix and self.key_fp8 else None
+                       for ix in indexed]
         # static block table: slot s owns blocks [1 + s * max_blocks, 1 + (s + 1) * max_blocks)
         if shared_tail_blocks:
             self.block_table = torch.zeros(slots, self.max_blocks, dtype=torch.int32, device=device)
@@ -247,7 +256,7 @@ class MlaCaches:
         assert not self.tail_blocks
         n = (tokens + self.page - 1) // self.page
         src, to = self.block_table[0, :n].long(), self.block_table[dst, :n].long()
-        for cache in list(self.latent) + [k for k in self.kidx if k is not None]:
+        for cache in list(self.latent) + [k for k in self.kidx if k is not None] + [k for k in self.kscale if k is not None]:
             cache.index_copy_(0, to, cache.index_select(0, src))
 
     def _append(self, cache: torch.Tensor, rows: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor) -> None:
@@ -268,13 +277,15 @@ class MlaCaches:
                         c.kv_lora, c.rope)
         q_full = ops.mla_q_absorb(q, L.w_uk, inv_freq, positions, c.kv_lora, c.rope)
         sel = None
-        if L.idx_q is not None:
+        if L.idx_q is not None and self.key_fp8:
+            ops.dsa_key_append_fp8(ops.linear(xn, L.idx_k), positions, row_req, self.block_table, self.kidx[j], self.kscale[j])
+        elif L.idx_q is not None:
             self._append(self.kidx[j], ops.linear(xn, L.idx_k), row_req, positions)
         if L.idx_q is not None and select:
             qi = ops.linear(xn, L.idx_q).view(rows, c.index_heads, c.index_dim)
             wi = ops.linear(xn, L.idx_w).float().contiguous()
             sc = ops.dsa_index(qi, wi, self.kidx[j], self.block_table, row_req, positions, self.max_ctx,
-                               scores=self.scores[:rows])
+                               scores=self.scores[:rows], k_scale=self.kscale[j])
             sel = ops.topk_select(sc, positions, c.index_topk)
         # decode rows: enough (row, head group, context split) CTAs to cover the SMs; a split beyond a short context
         # writes an empty partial, so the count depends on the batch width only (a captured pass stays valid)

@@ -677,6 +677,19 @@ def moe_hash_routes(tokens, tid2eid, scores, scaling: float = 1.0, norm_topk: bo
     return ids, w
 
 
+_lib.declare("dgpp_ple_embed_add", [P, P, P, P, I, I, I, P])
+
+
+def ple_embed_add(tokens: torch.Tensor, prev: torch.Tensor, table: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """Hashed bigram embeddings, in place: x[r] += table[(prev[r] * 1000003 + tokens[r] * 7919 + 12345) % len(table)]."""
+    _chk(tokens, torch.int32, "tokens")
+    _chk(prev, torch.int32, "prev")
+    _chk(table, torch.bfloat16, "table")
+    _chk(x, torch.bfloat16, "x")
+    call("dgpp_ple_embed_add", ptr(tokens), ptr(prev), ptr(table), ptr(x), x.shape[0], x.shape[1], table.shape[0], stream_ptr())
+    return x
+
+
 def hadamard32_rows(x: torch.Tensor, out: Optional[torch.Tensor] = None, period: int = 0) -> torch.Tensor:
     """Normalised block-32 Walsh-Hadamard rotation of bf16 rows (in place when out is x); rows r with
     r % period == period - 1 are not touched (period 0: all rows)."""
@@ -1014,14 +1027,34 @@ def mla_v_up(lat, w_uv, out=None):
 _lib.declare("dgpp_dsa_index_tc", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P])
 
 
+_lib.declare("dgpp_dsa_index_tc_fp8", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P])
+_lib.declare("dgpp_dsa_key_append_fp8", [P, L, P, P, P, I, I, P, P, I, P])
+
+
+def dsa_key_append_fp8(k_rows, positions, row_req, block_table, cache, kscale) -> None:
+    """Index keys [rows, 128] bf16 of new tokens -> e4m3 bytes in the paged cache [blocks, page, 128] uint8 with one fp32
+    scale per token in kscale [blocks, page] (amax / 448)."""
+    _chk(k_rows, torch.bfloat16, "k_rows")
+    assert cache.dtype == torch.uint8 and k_rows.shape[1] == 128 and cache.shape[2] == 128
+    call("dgpp_dsa_key_append_fp8", ptr(k_rows), k_rows.stride(0), ptr(positions), ptr(row_req), ptr(block_table),
+         block_table.shape[1], cache.shape[1], ptr(cache), ptr(kscale), k_rows.shape[0], stream_ptr())
+
+
 def dsa_index(q_idx, w_idx, k_idx, block_table, row_req, positions, max_ctx: int, scores=None,
-              tensor_cores: Optional[bool] = None):
+              tensor_cores: Optional[bool] = None, k_scale=None):
     """Lightning-indexer scores [rows, max_ctx] fp32 (-inf beyond each row's position).
-    q_idx: [rows, hi, di] bf16, w_idx: [rows, hi] fp32, k_idx: paged [blocks, page, di] bf16.
+    q_idx: [rows, hi, di] bf16, w_idx: [rows, hi] fp32, k_idx: paged [blocks, page, di] bf16, or e4m3 bytes (uint8) with
+    k_scale [blocks, page] fp32 per-token scales (tensor-core kernel only, two-term e4m3 queries).
     Index dims of 128 with up to 64 heads run on the tensor cores (tensor_cores=False: the CUDA-core kernel)."""
     rows, hi, di = q_idx.shape
     if scores is None:
         scores = torch.empty(rows, max_ctx, dtype=torch.float32, device=q_idx.device)
+    if k_idx.dtype == torch.uint8:
+        assert k_scale is not None and di == 128 and hi <= 64 and k_idx.shape[1] in (16, 32, 64, 128)
+        call("dgpp_dsa_index_tc_fp8", ptr(q_idx), ptr(w_idx), ptr(k_idx), ptr(k_scale), ptr(block_table), ptr(row_req),
+             ptr(positions), ptr(scores), rows, hi, di, k_idx.shape[1], block_table.shape[1], k_idx.shape[0], scores.shape[1],
+             stream_ptr())
+        return scores
     if tensor_cores is None:
         tensor_cores = di == 128 and hi <= 64 and k_idx.shape[1] in (16, 32, 64, 128)
     if tensor_cores:

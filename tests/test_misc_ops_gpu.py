@@ -152,3 +152,21 @@ def test_hyper_connection_coefficients_and_fold(dev):
     inplace = streams.clone()
     ops.mhc_fold(inplace, h, post, comb, out=inplace)
     assert torch.equal(inplace, got)
+
+
+def test_hashed_bigram_embedding_add(dev):
+    """Device-side bigram hash + table gather + add against the host formula (64-bit product, modulo the table size)."""
+    from dgpp_b200.ops import core as ops
+
+    torch.manual_seed(4)
+    rows, hidden, table_rows = 77, 1024, 4099
+    tokens = torch.randint(0, 151936, (rows,), dtype=torch.int32, device=dev)
+    prev = torch.randint(0, 151936, (rows,), dtype=torch.int32, device=dev)
+    table = torch.randn(table_rows, hidden, device=dev).to(BF)
+    x = torch.randn(rows, hidden, device=dev).to(BF)
+    ids = (prev.long() * 1000003 + tokens.long() * 7919 + 12345) % table_rows
+    want = (x.float() + table[ids].float()).to(BF)
+    got = ops.ple_embed_add(tokens, prev, table, x.clone())
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(got, want)

@@ -115,3 +115,56 @@ def test_indexer_scores_and_topk(dev):
     ops.check_status()
     for r, n in enumerate(ctxs):
         assert torch.equal(got[r], topk_reference(scores[r, :n], k)), r
+
+
+def test_indexer_scores_over_fp8_keys(dev):
+    """Index keys cached as e4m3 with per-token scales: the append kernel's codes and scales equal the host
+    quantisation, and the tensor-core scores (two-term e4m3 queries) equal the oracle over the DEQUANTISED keys."""
+    from dgpp_b200.models.mla import index_scores_reference
+    from dgpp_b200.ops import core as ops
+
+    torch.manual_seed(8)
+    ctxs = [1500, 100, 513]
+    hi, di, page = 64, 128, 64
+    max_blocks = max(ctxs) // page + 2
+    blocks = len(ctxs) * max_blocks + 3
+    table = torch.randperm(blocks, device=dev)[:len(ctxs) * max_blocks].view(len(ctxs), max_blocks).to(torch.int32)
+    cache = torch.zeros(blocks, page, di, dtype=torch.uint8, device=dev)
+    kscale = torch.ones(blocks, page, dtype=torch.float32, device=dev)
+    keys = []
+    for r, n in enumerate(ctxs):
+        k = (torch.randn(n, di, device=dev) * (0.2 + torch.rand(n, 1, device=dev) * 3)).to(BF)
+        k[5] = 0                                                     # an all-zero key keeps scale 1
+        keys.append(k)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        ops.dsa_key_append_fp8(k, pos, torch.full((n,), r, dtype=torch.int32, device=dev), table, cache, kscale)
+    torch.cuda.synchronize()
+    deq = []
+    for r, n in enumerate(ctxs):
+        k = keys[r].float()
+        am = k.abs().amax(-1, keepdim=True)
+        sc = torch.where(am > 0, am / 448.0, torch.ones_like(am))
+        want_codes = (k / sc).to(torch.float8_e4m3fn)
+        blk = table[r, torch.arange(n, device=dev) // page].long()
+        got_codes = cache[blk, torch.arange(n, device=dev) % page].view(torch.float8_e4m3fn)
+        # same codes but for the odd value that sits on a rounding boundary of the division (one code step at most)
+        differ = got_codes.view(torch.uint8) != want_codes.view(torch.uint8)
+        assert differ.float().mean().item() < 2e-3, (r, differ.float().mean().item())
+        step = (got_codes.float() - want_codes.float()).abs() / want_codes.float().abs().clamp_min(2.0 ** -6)
+        assert step.max().item() <= 0.13, (r, step.max().item())
+        got_sc = kscale[blk, torch.arange(n, device=dev) % page]
+        assert torch.allclose(got_sc, sc[:, 0], rtol=1e-6, atol=0), r          # the device divides by reciprocal
+        assert float(got_sc[5]) == 1.0
+        deq.append(got_codes.float() * got_sc.unsqueeze(-1))
+    q = torch.randn(len(ctxs), hi, di, device=dev).to(BF)
+    w = torch.rand(len(ctxs), hi, device=dev)
+    row_req = torch.arange(len(ctxs), dtype=torch.int32, device=dev)
+    pos = torch.tensor([c - 1 for c in ctxs], dtype=torch.int32, device=dev)
+    scores = ops.dsa_index(q, w, cache, table, row_req, pos, max(ctxs), k_scale=kscale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for r, n in enumerate(ctxs):
+        want = index_scores_reference(q[r], w[r], deq[r])
+        err = (scores[r, :n] - want).abs().max().item()
+        assert err <= 6e-3 * want.abs().max().item() + 2e-2, (r, err, want.abs().max().item())
+        assert torch.isinf(scores[r, n:]).all(), r

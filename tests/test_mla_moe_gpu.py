@@ -13,7 +13,7 @@ def dev():
     return torch.device("cuda:0")
 
 
-@pytest.mark.parametrize("moe,index", [(False, False), (True, False), (False, True)])
+@pytest.mark.parametrize("moe,index", [(False, False), (True, False), (False, True), (False, "fp8")])
 def test_runner_matches_plain_attention_oracle(dev, moe, index):
     from dgpp_b200.models.mla_moe import MlaMoeConfig, MlaMoeModel, MlaMoeRunner
     from dgpp_b200.models.moe import MoEConfig
@@ -22,9 +22,11 @@ def test_runner_matches_plain_attention_oracle(dev, moe, index):
     cfg = MlaMoeConfig(layers=3, hidden=1024, heads=8, q_lora=256, kv_lora=128, nope=64, rope=32, v_dim=64, ffn=2048,
                        vocab=2048, dense_layers=1,
                        moe=MoEConfig(hidden=1024, experts=16, top_k=4, moe_ffn=512, shared_ffn=512) if moe else None,
-                       index_heads=4 if index else 0, index_dim=64, index_topk=48)
+                       index_heads=4 if index else 0, index_dim=128 if index == "fp8" else 64, index_topk=48,
+                       index_key_fp8=index == "fp8")
     m = MlaMoeModel.random_init(cfg, dev, seed=3, std=0.04)
     r = MlaMoeRunner(m, max_rows=64, slots=2, max_seq_len=512, device=dev)
+    assert (r.att.kidx[0].dtype == torch.uint8) == (index == "fp8") if index else True
     g = torch.Generator().manual_seed(2)
     a = torch.randint(0, cfg.vocab, (150,), generator=g).tolist()
     b = torch.randint(0, cfg.vocab, (37,), generator=g).tolist()
