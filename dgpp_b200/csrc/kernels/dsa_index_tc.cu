@@ -417,8 +417,10 @@ DGPP_API int dgpp_dsa_index_tc_fp8(const void* q, const void* w, const void* k, 
   p.status = device_status_ptr();
   p.rows = rows; p.hi = hi; p.page = page; p.max_blocks = max_blocks; p.ld = ld;
   const int max_tiles = dgpp_ceil_div(ld, kIxTile);
+  // about two CTAs per SM over all rows; up to 32 tiles each (the query split in a CTA's prologue costs about as much as
+  // ten tiles of its main loop, so long contexts take longer runs instead of more CTAs)
   int per = dgpp_ceil_div(max_tiles * rows, 296);
-  per = per < 1 ? 1 : (per > 8 ? 8 : per);
+  per = per < 1 ? 1 : (per > 32 ? 32 : per);
   p.tiles_per_cta = per;
   CUtensorMap tK;
   if (make_tmap_2d(&tK, k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 128, static_cast<uint64_t>(num_blocks) * page, 128, 128, page,
