@@ -234,55 +234,65 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restri
   }
   if (tid == 0) { prefix_s = 0ull; need_s = k; fill_s = 0; }
   __syncthreads();
+  const int lane = tid & 31, wid = tid >> 5;
+  unsigned long long thr = 0ull;
   for (int pass = 0; pass < 8; ++pass) {
     const int shift = 56 - 8 * pass;
     for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
     __syncthreads();
     const unsigned long long prefix = prefix_s;
-    for (int i = tid; i < n; i += blockDim.x) {
-      const unsigned long long key = topk_key(z[i], i);
-      if (pass == 0 || (key >> (shift + 8)) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1u);
+    // histogram of this digit over the keys that still match the prefix; the lanes of a warp that hit the same bin
+    // send ONE add (score rows are far from uniform in their leading digits: without this the first passes serialise)
+    for (int c0 = 0; c0 < n; c0 += blockDim.x) {
+      const int i = c0 + tid;
+      int bin = -1;
+      if (i < n) {
+        const unsigned long long key = topk_key(z[i], i);
+        if (pass == 0 || (key >> (shift + 8)) == prefix) bin = static_cast<int>((key >> shift) & 255);
+      }
+      const unsigned peers = __match_any_sync(0xffffffffu, bin);
+      if (bin >= 0 && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], static_cast<uint32_t>(__popc(peers)));
     }
     __syncthreads();
     if (tid == 0) {
-      int need = need_s, b = 255;
+      int need = need_s, bsel = 255;
       uint32_t cum = 0;
-      for (; b > 0; --b) {
-        if (cum + hist[b] >= static_cast<uint32_t>(need)) break;
-        cum += hist[b];
+      for (; bsel > 0; --bsel) {
+        if (cum + hist[bsel] >= static_cast<uint32_t>(need)) break;
+        cum += hist[bsel];
       }
       need_s = need - static_cast<int>(cum);
-      prefix_s = (prefix << 8) | static_cast<unsigned long long>(b);
+      prefix_s = (prefix << 8) | static_cast<unsigned long long>(bsel);
+      // every key of the chosen bin is needed: the lowest key with this prefix is the threshold, no digit below matters
+      fill_s = (hist[bsel] == static_cast<uint32_t>(need_s)) ? 1 : 0;
     }
     __syncthreads();
+    thr = prefix_s << shift;
+    if (fill_s) break;
   }
-  const unsigned long long thr = prefix_s;
-  // ascending output without a sort: position i lands at (number of selected positions below i)
-  // -> block-wide ordered compaction in chunks of blockDim.x
+  // ascending output without a sort: warp w owns the contiguous positions [w * seg, (w + 1) * seg); it counts its
+  // selected positions, the counts are scanned once, then it writes them in order from its base
   __shared__ int warp_cnt[32];
-  __shared__ int base_s;
-  if (tid == 0) base_s = 0;
-  __syncthreads();
-  for (int c0 = 0; c0 < n; c0 += blockDim.x) {
-    const int i = c0 + tid;
-    const bool take = i < n && topk_key(z[i], i) >= thr;
-    const unsigned ballot = __ballot_sync(0xffffffffu, take);
-    const int lane = tid & 31, wid = tid >> 5;
-    if (lane == 0) warp_cnt[wid] = __popc(ballot);
-    __syncthreads();
-    int before = base_s;
-    for (int w = 0; w < wid; ++w) before += warp_cnt[w];
-    before += __popc(ballot & ((1u << lane) - 1u));
-    if (take && before < k) o[before] = i;
-    __syncthreads();
-    if (tid == 0) {
-      int tot = 0;
-      for (int w = 0; w < (blockDim.x >> 5); ++w) tot += warp_cnt[w];
-      base_s += tot;
-    }
-    __syncthreads();
+  const int warps = blockDim.x >> 5;
+  const int seg = ((n + warps - 1) / warps + 31) & ~31;
+  const int lo = wid * seg, hi = min(n, lo + seg);
+  int cnt = 0;
+  for (int c0 = lo; c0 < hi; c0 += 32) {
+    const int i = c0 + lane;
+    cnt += __popc(__ballot_sync(0xffffffffu, i < hi && topk_key(z[i], i) >= thr));
   }
-  (void)fill_s;
+  if (lane == 0) warp_cnt[wid] = cnt;
+  __syncthreads();
+  int before = 0;
+  for (int w = 0; w < wid; ++w) before += warp_cnt[w];
+  for (int c0 = lo; c0 < hi; c0 += 32) {
+    const int i = c0 + lane;
+    const bool take = i < hi && topk_key(z[i], i) >= thr;
+    const unsigned ballot = __ballot_sync(0xffffffffu, take);
+    const int at = before + __popc(ballot & ((1u << lane) - 1u));
+    if (take && at < k) o[at] = i;
+    before += __popc(ballot);
+  }
 }
 
 template <int DC, int DR>
