@@ -714,3 +714,99 @@ class HybridEngine(rt.SchedulerEngine):
     def close(self, slot):
         self.r.reset(slot)
         self.pending[slot] = None
+
+
+class RunnerEngine(rt.SchedulerEngine):
+    """Any family runner with `prefill(slot, tokens, chunk)`, `decode(slots, tokens)`, `reset(slot)` and `lengths` behind
+    the scheduler (greedy decoding).  The runner's state (recurrent memories, caches laid out per slot) is not
+    addressable by block, so this engine never resumes from the prefix cache: it hands the scheduler a private block
+    table for admission arithmetic only and reports no usable prefix.  (reference counterparts: the per-family
+    SessionModel adapters of src/engine/session_model.hpp.)"""
+
+    def __init__(self, runner, max_context: int, block_tokens: int = 64, prefill_chunk: int = 256):
+        super().__init__()
+        self.r, self.bt, self.maxctx, self.prefill_chunk = runner, block_tokens, max_context, prefill_chunk
+        n = len(runner.lengths)
+        self.per_slot = (max_context + block_tokens - 1) // block_tokens + 1
+        self.table = rt.PagedBlockTable(n * self.per_slot + 1)
+        self.blocks: List[List[int]] = [[] for _ in range(n)]
+        self.pending: List[Optional[int]] = [None] * n
+
+    # ---- geometry
+    def max_concurrent(self):
+        return len(self.r.lengths)
+
+    def block_tokens(self):
+        return self.bt
+
+    def total_blocks(self):
+        return self.table.num_blocks()
+
+    def free_blocks(self):
+        return self.table.free_count()
+
+    def max_context(self):
+        return self.maxctx
+
+    # ---- blocks (accounting only)
+    def reserve(self, slot, tokens):
+        need = (tokens + self.bt - 1) // self.bt
+        if need > self.per_slot or need - len(self.blocks[slot]) > self.table.free_count():
+            return False
+        while len(self.blocks[slot]) < need:
+            self.blocks[slot].append(self.table.alloc())
+        return True
+
+    def slot_blocks(self, slot):
+        return list(self.blocks[slot])
+
+    def retain_block(self, b):
+        self.table.retain(b)
+
+    def release_block(self, b):
+        self.table.release(b)
+
+    def block_refcount(self, b):
+        return self.table.refcount(b)
+
+    def usable_prefix(self, blocks):
+        return 0
+
+    def attach_prefix(self, slot, blocks):
+        raise AssertionError("attach_prefix on an engine that reports no usable prefix")
+
+    # ---- execution
+    def prefill(self, slot, tokens, pos, last):
+        tokens = list(tokens)
+        if pos == 0 and self.r.lengths[slot] != 0:
+            self.r.reset(slot)
+        assert self.r.lengths[slot] == pos, (self.r.lengths[slot], pos)
+        logits = self.r.prefill(slot, tokens, chunk=self.prefill_chunk)
+        if last:
+            self.pending[slot] = int(torch.argmax(logits[-1]).item())
+            return self.pending[slot]
+        return -1
+
+    def step_batch(self, slots):
+        slots = list(slots)
+        logits = self.r.decode(slots, [self.pending[s] for s in slots])
+        toks = torch.argmax(logits[:len(slots)], dim=-1).tolist()
+        if torch.device(getattr(self.r, "dev", "cpu")).type == "cuda":
+            import ctypes as C
+            from ..ops import _lib
+            buf = (C.c_int * 4)()
+            _lib.call("dgpp_status_read", C.cast(buf, C.c_void_p))
+            if buf[0] != 0:
+                raise EngineFailure(f"device status code={buf[0]} count={buf[1]} detail={buf[2]}")
+        out = []
+        for s, t in zip(slots, toks):
+            self.pending[s] = int(t)
+            out.append([int(t)])
+        return out
+
+    def close(self, slot):
+        for b in self.blocks[slot]:
+            self.table.release(b)
+        self.blocks[slot] = []
+        self.pending[slot] = None
+        self.r.reset(slot)

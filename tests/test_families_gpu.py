@@ -74,3 +74,40 @@ def test_flash_next_gated_residual_branches(dev, moe):
 
     _drive(r, m, cfg.vocab, dev, close)
     assert r.last_token[1] != 0                      # the bigram hash carries over between passes
+
+
+def test_family_runner_behind_the_scheduler(dev):
+    """The generic runner adapter: three concurrent requests through the scheduler emit the tokens the runner emits for
+    each request alone."""
+    from dgpp_b200.engine.adapters import RunnerEngine
+    from dgpp_b200.models.dory import DoryConfig, DoryModel, DoryRunner
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.runtime import rt
+
+    cfg = DoryConfig(layers=2, loops=2, hidden=512, q_heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2048)
+    m = DoryModel.random_init(cfg, dev, seed=6)
+    g = torch.Generator().manual_seed(5)
+    reqs = {f"r{i}": torch.randint(0, cfg.vocab, (20 + 33 * i,), generator=g).tolist() for i in range(3)}
+    want = {}
+    for rid, p in reqs.items():
+        one = DoryRunner(m, max_rows=64, slots=1, max_seq_len=512, device=dev)
+        tok = int(torch.argmax(one.prefill(0, p, chunk=64)[-1]))
+        seq = [tok]
+        for _ in range(5):
+            tok = int(torch.argmax(one.decode([0], [tok])[0]))
+            seq.append(tok)
+        want[rid] = seq
+    eng = RunnerEngine(DoryRunner(m, max_rows=64, slots=3, max_seq_len=512, device=dev), max_context=384, prefill_chunk=64)
+    sc = rt.SchedulerConfig()
+    sc.prefix_cache = False
+    s = rt.Scheduler(eng, sc)
+    for rid, p in reqs.items():
+        s.submit(rid, p, 6)
+    s.run(100000)
+    got = {}
+    for kind, x, a, b in s.events():
+        if kind == "token":
+            got.setdefault(x, []).append(a)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert got == want
