@@ -98,6 +98,13 @@ void bind_grammar(py::module_& m) {
       .def("steps", &spec::VerifySchedule::steps)
       .def("proposed_total", &spec::VerifySchedule::proposed_total)
       .def("accepted_total", &spec::VerifySchedule::accepted_total);
+  py::class_<spec::ConfidenceDepth>(m, "ConfidenceDepth")
+      .def(py::init<double, double, double>(), py::arg("base_ms"), py::arg("row_ms"), py::arg("ema") = 0.1)
+      .def("lambda_", &spec::ConfidenceDepth::lambda)
+      .def("floor", &spec::ConfidenceDepth::floor)
+      .def("depth", &spec::ConfidenceDepth::depth, py::arg("conf"), py::arg("accept_scale") = 1.0)
+      .def("depth_batch", &spec::ConfidenceDepth::depth_batch, py::arg("conf"), py::arg("accept_scale") = std::vector<double>{})
+      .def("observe", &spec::ConfidenceDepth::observe);
   m.def("spec_judge", [](int64_t base, const std::vector<int32_t>& draft, const std::vector<int32_t>& target,
                          const std::vector<int32_t>& stop_ids, int64_t budget) {
     const spec::Verdict v = spec::judge(base, draft, target, stop_ids, budget);

@@ -15,6 +15,7 @@
 // (reference counterparts: src/engine/speculative.hpp, verify_schedule.hpp, lookup_draft.hpp; the reference tree's own DESIGN.md:1934-2123.)
 #pragma once
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include <unordered_map>
 #include <vector>
@@ -92,6 +93,73 @@ class VerifySchedule {
   double ema_ = 0.0;
   bool seen_ = false;
   int64_t steps_ = 0, proposed_ = 0, accepted_ = 0;
+};
+
+// Verify depth from the drafter's own confidence.  A drafter that emits, per draft position, a logit c_i of "this draft
+// survives given that the ones before it did" lets the engine decide how many of the block's drafts are worth a verify
+// row: with p_i = scale / (1 + exp(-c_i)) and S_i = p_1 .. p_i (non-increasing), verifying k drafts commits
+// 1 + S_1 + .. + S_k tokens in expectation and costs base + (1 + k) rows of time.  Throughput over a whole run is a
+// ratio of sums, whose optimum (Dinkelbach) is a linear trade per step at one multiplier lambda = the throughput the
+// run achieves (tokens per ms): draft i is verified while S_i > lambda * row_ms, and the first one that fails ends the
+// prefix.  lambda is tracked here as a moving average of committed tokens over MODELLED step time (base + rows * row,
+// never a clock: every rank must derive the same depth from the same replicated inputs) and is never allowed below the
+// rate of a plain one-token step, 1 / (base + row).  The depth changes how many rows a step verifies, never which
+// tokens it emits.
+class ConfidenceDepth {
+ public:
+  ConfidenceDepth(double base_ms, double row_ms, double ema = 0.1)
+      : base_(base_ms), row_(row_ms), ema_(ema), floor_(base_ms + row_ms > 0.0 ? 1.0 / (base_ms + row_ms) : 0.0),
+        lambda_(floor_) {}
+
+  double lambda() const { return lambda_; }
+  double floor() const { return floor_; }
+
+  // One request: leading drafts to verify, 0 .. conf.size().  accept_scale < 1 for a sampled request whose drafts are
+  // arg-max tokens (they are accepted with the target's probability of the draft, not whenever they are the arg-max).
+  int depth(const std::vector<float>& conf, double accept_scale = 1.0) const {
+    const double limit = lambda_ * row_;
+    double survive = 1.0;
+    int k = 0;
+    for (size_t i = 0; i < conf.size(); ++i) {
+      survive *= accept_scale / (1.0 + std::exp(-static_cast<double>(conf[i])));
+      if (!(survive > limit)) break;
+      k = static_cast<int>(i) + 1;
+    }
+    return k;
+  }
+
+  // A batch that replays ONE graph for all its requests shares one depth: a further position costs one row per request
+  // and yields the sum of their survivals there, so it is kept while the MEAN survival beats lambda * row.
+  int depth_batch(const std::vector<std::vector<float>>& conf, const std::vector<double>& accept_scale = {}) const {
+    if (conf.empty()) return 0;
+    size_t block = conf[0].size();
+    for (const auto& c : conf) block = std::min(block, c.size());
+    const double limit = lambda_ * row_;
+    std::vector<double> survive(conf.size(), 1.0);
+    int k = 0;
+    for (size_t i = 0; i < block; ++i) {
+      double sum = 0.0;
+      for (size_t s = 0; s < conf.size(); ++s) {
+        const double scale = s < accept_scale.size() ? accept_scale[s] : 1.0;
+        survive[s] *= scale / (1.0 + std::exp(-static_cast<double>(conf[s][i])));
+        sum += survive[s];
+      }
+      if (!(sum / static_cast<double>(conf.size()) > limit)) break;
+      k = static_cast<int>(i) + 1;
+    }
+    return k;
+  }
+
+  // After a step that ran `rows` verify rows in all and committed `committed` tokens in all.
+  void observe(int committed, int rows) {
+    const double t = base_ + static_cast<double>(rows) * row_;
+    if (!(t > 0.0) || committed < 0) return;
+    lambda_ += ema_ * (static_cast<double>(committed) / t - lambda_);
+    if (lambda_ < floor_) lambda_ = floor_;
+  }
+
+ private:
+  double base_, row_, ema_, floor_, lambda_;
 };
 
 struct Verdict {

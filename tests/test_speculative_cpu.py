@@ -77,3 +77,33 @@ def test_lookup_speculation_equals_plain_greedy():
         assert keep == len(seq) - 1 + (0 if emitted else 0) or keep <= len(seq)
     assert seq == plain
     assert passes < 24          # a tiny random model falls into loops: most drafts land
+
+
+def test_confidence_scheduled_verify_depth():
+    """Depth = leading drafts whose prefix survival still beats lambda * row; lambda never drops below the plain-step
+    rate and follows committed tokens over modelled time; a batch shares one depth by mean survival."""
+    import math
+
+    from dgpp_b200.runtime import rt
+
+    logit = lambda p: math.log(p / (1 - p))
+    d = rt.ConfidenceDepth(base_ms=20.0, row_ms=1.0, ema=0.5)
+    assert abs(d.lambda_() - 1 / 21.0) < 1e-12 and d.floor() == d.lambda_()
+    conf = [logit(0.9), logit(0.8), logit(0.5), logit(0.05), logit(0.99)]
+    # survivals 0.9, 0.72, 0.36, 0.018, ...; threshold 1/21 = 0.0476: three drafts pay, the fourth does not, and the
+    # confident fifth behind it cannot be reached
+    assert d.depth(conf) == 3
+    assert d.depth(conf, accept_scale=0.5) == 2                      # 0.45, 0.18, 0.045
+    assert d.depth([]) == 0 and d.depth([logit(0.01)]) == 0
+    # good steps raise lambda (4 tokens over 20 + 4 rows), which shortens the depth; bad steps cannot push it under the floor
+    for _ in range(20):
+        d.observe(4 * 8, 4 * 8)                                      # eight requests: 32 tokens over 20 + 32 ms
+    assert abs(d.lambda_() - 32 / 52.0) < 1e-3 and d.depth(conf) == 2          # threshold 0.615: 0.9, 0.72 pay, 0.36 does not
+    for _ in range(60):
+        d.observe(0, 4)
+    assert d.lambda_() == d.floor() and d.depth(conf) == 3
+    # batch: means 0.9, (0.72 + 0.09) / 2, ... against 0.0476
+    sure, unsure = [logit(0.9), logit(0.8), logit(0.9)], [logit(0.9), logit(0.1), logit(0.01)]
+    assert d.depth_batch([sure, unsure]) == 3 and d.depth(unsure) == 2
+    hi = rt.ConfidenceDepth(base_ms=1.0, row_ms=1.0)                 # threshold 0.5
+    assert hi.depth_batch([sure, unsure]) == 1 and hi.depth(sure) == 3 and hi.depth_batch([]) == 0
