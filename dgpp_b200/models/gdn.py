@@ -141,7 +141,7 @@ class GdnLayer:
         self.prep = torch.empty(max_rows * (2 * c.k_heads * c.dk + 2 * c.v_heads), dtype=torch.float32, device=device)
 
     def forward(self, x: torch.Tensor, state: GdnState, out: torch.Tensor, slot: int = 0,
-                row_slot: Optional[torch.Tensor] = None, seg: int = 0, snap=None) -> torch.Tensor:
+                row_slot: Optional[torch.Tensor] = None, seg: int = 0, snap=None, xa=None, dq=None) -> torch.Tensor:
         """x [rows, hidden] bf16.  row_slot None: the rows are consecutive tokens of request `slot` (prefill chunk);
         otherwise one decode token per row, row r belonging to state slot row_slot[r].  seg > 0 (with row_slot): runs of
         `seg` consecutive tokens per request (speculative verify rows); snap = (conv_snap [rows, W - 1, C], ssm_snap
@@ -149,7 +149,8 @@ class GdnLayer:
         c, w = self.c, self.w
         rows = x.shape[0]
         seq = row_slot is None
-        proj = ops.linear(x, w.in_proj, out=self.proj[:rows])
+        # xa / dq: the rows' NVFP4 terms and the decode quantiser (decode widths): both projections run block-scaled
+        proj = ops.gemm_fp4(xa, w.in_proj, out=self.proj[:rows]) if xa is not None else ops.linear(x, w.in_proj, out=self.proj[:rows])
         mixed, z, al, be, nq, nv = _split(c, proj)
         cs, ss = snap if snap is not None else (None, None)
         conv = ops.gdn_conv(mixed, w.conv_w, w.conv_b, state.conv, self.conv[:rows], row_slot, slot, seq, seg=seg, snap=cs)
@@ -157,4 +158,6 @@ class GdnLayer:
                           self.o[:rows], c.k_heads, c.v_heads, c.dk, c.dv, row_slot, slot, seq, prep=self.prep, seg=seg,
                           snap=ss)
         ops.gated_rmsnorm(self.o[:rows], z, w.norm_w, self.gated[:rows], c.v_heads, c.dv, c.eps)
+        if xa is not None and dq is not None and dq.usable(rows, w.out_proj):
+            return ops.gemm_fp4(dq.plain(self.gated[:rows], "g"), w.out_proj, out=out)
         return ops.linear(self.gated[:rows], w.out_proj, out=out)

@@ -208,6 +208,9 @@ class HybridRunner:
         self.logits = torch.empty(max_rows, c.vocab, dtype=torch.float32, device=device)
         self.lengths = [0] * slots
         self.scale = 1.0 / math.sqrt(d)
+        # decode-width passes: NVFP4 linears on the block-scaled path (three-term activations from the norm kernels); off
+        # under speculation, whose verify rows must see the arithmetic of plain rows at every batch width
+        self.decode_fp4, self.dq = True, ops.DecodeQuant(device)
         self.use_graphs, self._graphs, self._static = True, {}, {}
         self.pdl_graphs = True      # programmatic-dependent-launch edges between this library's kernels in captured passes
         # tensor-core attention (FP8 cache as stored): head_dim 128 / 256, up to 8 query heads per kv head
@@ -250,18 +253,21 @@ class HybridRunner:
         for st in self.gdn_state.values():
             st.reset(slot)
 
-    def _ffn(self, i: int, L: HybridLayer, xn: torch.Tensor, out: torch.Tensor) -> None:
+    def _ffn(self, i: int, L: HybridLayer, xn: torch.Tensor, out: torch.Tensor, xa=None) -> None:
         if L.moe is not None:
             blk = self.moe.get(i)
             wide = self.moe_wide.get(i)
             if blk is not None and xn.shape[0] <= blk.max_rows:
-                blk.forward(xn, out)
+                blk.forward(xn, out, xa=xa if (xa is not None and blk.bn == xa.bn and blk.terms == xa.terms) else None)
             elif wide is not None and xn.shape[0] <= wide.max_rows:
                 wide.forward(xn, out)
             elif blk is not None:
                 out.copy_(blk.forward_gathered(xn))
             else:
                 out.copy_(moe_reference(xn, L.moe))
+            return
+        if xa is not None and self.dq.usable(xn.shape[0], L.gate_up, L.down):
+            ops.gemm_fp4(self.dq.swiglu(ops.gemm_fp4(xa, L.gate_up), tag="f"), L.down, out=out)
             return
         ops.linear(ops.swiglu(ops.linear(xn, L.gate_up)), L.down, out=out)
 
@@ -278,17 +284,27 @@ class HybridRunner:
         x, xn, delta = self.x[:rows], self.xn[:rows], self.delta[:rows]
         ops.embed_gather(tokens, m.embed, out=x)
         have = False
+        dq = self.dq
         for i, L in enumerate(m.layers):
-            ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have else None, out=xn)
+            w_in = L.gdn.in_proj if L.gdn is not None else L.qkv
+            fast = self.decode_fp4 and not self.spec_rows and chunk_slot is None and dq.usable(rows, w_in)
+            xa = None
+            if fast:
+                xa = dq.norm(x, L.in_norm, c.eps, delta=delta if have else None, x_out=xn, tag="h")
+            else:
+                ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have else None, out=xn)
             if L.gdn is not None:
                 j = self.gdn_index[i]
                 self.gdn[i].forward(xn, self.gdn_state[i], delta, slot=chunk_slot or 0,
                                     row_slot=None if chunk_slot is not None else row_req, seg=seg,
-                                    snap=(self.conv_snap[j], self.ssm_snap[j]) if snap else None)
+                                    snap=(self.conv_snap[j], self.ssm_snap[j]) if snap else None, xa=xa, dq=dq)
             else:
                 cache = self.kv.layers[self.full_index[i]]
                 qkv, attn = self.qkv[:rows], self.attn[:rows]
-                ops.linear(xn, L.qkv, out=qkv)
+                if fast:
+                    ops.gemm_fp4(xa, L.qkv, out=qkv)
+                else:
+                    ops.linear(xn, L.qkv, out=qkv)
                 ops.rope_kv_write(qkv, positions, row_req, self.kv.block_table, m.inv_freq, cache, c.q_heads, c.kv_heads,
                                   c.head_dim)
                 if self.tc_attn and chunk_slot is not None and pos0 is not None:
@@ -301,10 +317,17 @@ class HybridRunner:
                 else:
                     ops.attn_decode(qkv, qkv.stride(0), cache, self.kv.block_table, row_req, positions, c.q_heads,
                                     c.kv_heads, c.head_dim, self.scale, out=attn)
-                ops.linear(attn, L.o, out=delta)
+                if fast and dq.usable(rows, L.o):
+                    ops.gemm_fp4(dq.plain(attn, "a"), L.o, out=delta)
+                else:
+                    ops.linear(attn, L.o, out=delta)
             have = True
-            ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
-            self._ffn(i, L, xn, delta)
+            xa = None
+            if fast:
+                xa = dq.norm(x, L.post_norm, c.eps, delta=delta, x_out=xn, tag="h")
+            else:
+                ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
+            self._ffn(i, L, xn, delta, xa=xa)
         ops.rmsnorm(x, m.final_norm, c.eps, delta=delta, out=xn)
         sel = xn if all_logits else xn[rows - 1:rows]
         return ops.gemm_tc(sel, m.head, out32=self.logits[:sel.shape[0]])

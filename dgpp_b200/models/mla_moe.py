@@ -238,6 +238,7 @@ class MlaCaches:
                                 ).view(slots, self.max_blocks).contiguous()
         self.scale = softmax_scale(c)
         self.scores = torch.empty(max_rows, self.max_ctx, dtype=torch.float32, device=device) if any(indexed) else None
+        self.dq = ops.DecodeQuant(device)
 
     def share_prefix(self, dst: int, tokens: int) -> None:
         """Slot `dst` reads the first `tokens` positions (a multiple of the page) from slot 0's blocks and appends into
@@ -264,14 +265,22 @@ class MlaCaches:
         cache[blk, (positions % self.page).long()] = rows
 
     def attention(self, j: int, L: MlaLayer, inv_freq: torch.Tensor, xn: torch.Tensor, positions: torch.Tensor,
-                  row_req: torch.Tensor, select: bool, out: torch.Tensor) -> torch.Tensor:
+                  row_req: torch.Tensor, select: bool, out: torch.Tensor, xa=None, fp4: bool = True) -> torch.Tensor:
         """xn [rows, H] normed rows of MLA layer j -> out [rows, H] (after the output projection).  Appends the rows'
-        latent (and index key) to the cache first; every row attends up to its own position."""
-        c = self.c
+        latent (and index key) to the cache first; every row attends up to its own position.  xa: the NVFP4 terms of xn
+        when the caller's norm kernel produced them (decode widths): the projections then run block-scaled."""
+        c, dq = self.c, self.dq
         rows = xn.shape[0]
-        cq = ops.rmsnorm(ops.linear(xn, L.q_a), L.q_a_norm, c.eps)
-        q = ops.linear(cq, L.q_b).view(rows, c.heads, c.nope + c.rope)
-        kv = ops.linear(xn, L.kv_a)
+        fast = fp4 and dq.usable(rows, L.q_a, L.q_b, L.kv_a, L.o)
+        if fast:
+            xa = xa if xa is not None else dq.plain(xn, "h")
+            cqa = dq.norm(ops.gemm_fp4(xa, L.q_a), L.q_a_norm, c.eps, tag="q")
+            q = ops.gemm_fp4(cqa, L.q_b).view(rows, c.heads, c.nope + c.rope)
+            kv = ops.gemm_fp4(xa, L.kv_a)
+        else:
+            cq = ops.rmsnorm(ops.linear(xn, L.q_a), L.q_a_norm, c.eps)
+            q = ops.linear(cq, L.q_b).view(rows, c.heads, c.nope + c.rope)
+            kv = ops.linear(xn, L.kv_a)
         # latent norm + rotary key -> cache slot; key up-projection folded into the query, rotary part appended
         ops.mla_kv_prep(kv, L.kv_a_norm, c.eps, inv_freq, positions, row_req, self.block_table, self.latent[j],
                         c.kv_lora, c.rope)
@@ -282,7 +291,8 @@ class MlaCaches:
         elif L.idx_q is not None:
             self._append(self.kidx[j], ops.linear(xn, L.idx_k), row_req, positions)
         if L.idx_q is not None and select:
-            qi = ops.linear(xn, L.idx_q).view(rows, c.index_heads, c.index_dim)
+            qi = (ops.gemm_fp4(xa, L.idx_q) if fast and dq.usable(rows, L.idx_q) else ops.linear(xn, L.idx_q)
+                  ).view(rows, c.index_heads, c.index_dim)
             wi = ops.linear(xn, L.idx_w).float().contiguous()
             sc = ops.dsa_index(qi, wi, self.kidx[j], self.block_table, row_req, positions, self.max_ctx,
                                scores=self.scores[:rows], k_scale=self.kscale[j])
@@ -293,6 +303,8 @@ class MlaCaches:
         lat = ops.mla_decode(q_full, self.latent[j], self.block_table, row_req, positions, self.scale, c.kv_lora,
                              c.rope, sel=sel, splits=splits)
         a = ops.mla_v_up(lat, L.w_uv)
+        if fast:
+            return ops.gemm_fp4(dq.plain(a, "a"), L.o, out=out)
         return ops.linear(a, L.o, out=out)
 
 
@@ -310,6 +322,7 @@ class MlaMoeRunner:
         self.lengths = [0] * slots
         self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
                     if L.moe is not None and L.moe.gu_q is not None}
+        self.decode_fp4 = True      # decode-width passes: NVFP4 linears on the block-scaled path (three-term activations)
         self.use_graphs, self._graphs, self._static = True, {}, {}
         self.pdl_graphs = True      # programmatic-dependent-launch edges between this library's kernels in captured passes
 
@@ -331,19 +344,30 @@ class MlaMoeRunner:
         xn, delta = torch.empty_like(x), torch.empty_like(x)
         ops.embed_gather(tokens, m.embed, out=x)
         have = False
+        dq = self.att.dq
         for i, L in enumerate(m.layers):
-            ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have else None, out=xn)
-            self.att.attention(i, L, m.inv_freq, xn, positions, row_req, select, delta)
-            ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
+            fast = self.decode_fp4 and dq.usable(rows, L.q_a, L.q_b, L.kv_a, L.o)
+            xa = None
+            if fast:      # norm + residual add + NVFP4 terms in one kernel; xn is still needed (bf16 linears, router)
+                xa = dq.norm(x, L.in_norm, c.eps, delta=delta if have else None, x_out=xn, tag="h")
+            else:
+                ops.rmsnorm(x, L.in_norm, c.eps, delta=delta if have else None, out=xn)
+            self.att.attention(i, L, m.inv_freq, xn, positions, row_req, select, delta, xa=xa, fp4=fast)
+            if fast:
+                xa = dq.norm(x, L.post_norm, c.eps, delta=delta, x_out=xn, tag="h")
+            else:
+                ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
             have = True
             if L.moe is not None:
                 blk = self.moe.get(i)
                 if blk is not None and rows <= blk.max_rows:
-                    blk.forward(xn, delta)
+                    blk.forward(xn, delta, xa=xa if (fast and blk.bn == dq.ROWS and blk.terms == dq.TERMS) else None)
                 elif blk is not None:
                     delta.copy_(blk.forward_gathered(xn))
                 else:
                     delta.copy_(moe_reference(xn, L.moe))
+            elif fast and dq.usable(rows, L.gate_up, L.down):
+                ops.gemm_fp4(dq.swiglu(ops.gemm_fp4(xa, L.gate_up), tag="f"), L.down, out=delta)
             else:
                 ops.linear(ops.swiglu(ops.linear(xn, L.gate_up)), L.down, out=delta)
         ops.rmsnorm(x, m.final_norm, c.eps, delta=delta, out=xn)

@@ -277,6 +277,37 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
     return out
 
 
+class DecodeQuant:
+    """Decode-width passes (<= 16 rows) run their NVFP4 linears on the block-scaled tensor path: the producing norm /
+    activation kernel writes the rows as three residual NVFP4 terms (near-bf16 together), one GEMM streams the packed
+    weights as stored.  One QuantAct per input width, reused by every layer (a layer's passes are sequential)."""
+    ROWS, TERMS = 16, 3
+
+    def __init__(self, device):
+        self.dev, self.bufs = device, {}
+
+    def usable(self, rows: int, *ws) -> bool:
+        return (rows <= self.ROWS and torch.device(self.dev).type == "cuda"
+                and all(w is not None and w.fmt == "nvfp4" and w.k % 256 == 0 for w in ws))
+
+    def buf(self, k: int, tag: str = "") -> QuantAct:
+        key = (k, tag)
+        if key not in self.bufs:
+            self.bufs[key] = QuantAct(self.ROWS, k, self.TERMS, self.ROWS, self.dev)
+        return self.bufs[key]
+
+    def plain(self, x: torch.Tensor, tag: str = "") -> QuantAct:
+        return act_quant_nvfp4(x, self.TERMS, out=self.buf(x.shape[1], tag))
+
+    def norm(self, x, w, eps, delta=None, x_out=None, tag: str = "") -> QuantAct:
+        """rmsnorm(x [+ delta]) -> terms (+ the bf16 normed rows in x_out); with a delta the sum is written back to x."""
+        return act_quant_nvfp4(x, self.TERMS, out=self.buf(x.shape[1], tag), mode="rmsnorm", delta=delta, norm_w=w,
+                                   x_out=x_out, eps=eps)
+
+    def swiglu(self, gate_up: torch.Tensor, limit: float = 0.0, tag: str = "") -> QuantAct:
+        return act_quant_nvfp4(gate_up, self.TERMS, out=self.buf(gate_up.shape[1] // 2, tag), mode="swiglu", limit=limit)
+
+
 def attn_combine_quant(scratch, rows: int, splits: int, hq: int, d: int, out: QuantAct, x_out=None) -> QuantAct:
     """Fold the split-KV partials of a decode-attention pass (attn_decode_tc(..., partials_only=True)) and quantise
     the attention output rows [rows, hq * d] to residual NVFP4 terms in one launch; same arithmetic as the stand-alone

@@ -182,3 +182,39 @@ def test_decode_of_more_than_16_rows_uses_the_wide_blocks(dev):
             assert (got[k][s] - want).abs().max().item() <= 0.03 * want.abs().max().item() + 0.02, (s, k)
     torch.cuda.synchronize()
     ops.check_status()
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_decode_width_block_scaled_linears(dev, moe):
+    """NVFP4 weights: decode passes of up to 16 rows run their projections block-scaled (norm kernels emit the
+    three-term rows); logits stay within the oracle's tolerance, prefill keeps the exact path."""
+    from dgpp_b200.models.hybrid import HybridConfig, HybridModel, HybridRunner
+    from dgpp_b200.models.moe import MoEConfig
+    from dgpp_b200.ops import core as ops
+
+    cfg = HybridConfig(layers=4, hidden=512, full_every=4, q_heads=4, kv_heads=2, head_dim=128, gdn_k_heads=2,
+                       gdn_v_heads=4, gdn_dk=128, gdn_dv=128, ffn=1024, vocab=2048,
+                       moe=MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512, shared_ffn=512) if moe else None)
+    m = HybridModel.random_init(cfg, dev, seed=5, std=0.05, fmt="nvfp4")
+    g = torch.Generator().manual_seed(1)
+    a = torch.randint(0, cfg.vocab, (60,), generator=g).tolist()
+    want = m.forward_reference(torch.tensor(a, device=dev))
+    outs = {}
+    for fp4 in (True, False):
+        r = HybridRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+        r.decode_fp4 = fp4
+        r.prefill(0, a[:50], chunk=32)
+        r.prefill(1, a[:44], chunk=32)
+        outs[fp4] = [r.decode([0, 1], [a[50 + s], a[44 + s]])[0].clone() for s in range(5)]
+        assert bool(r.dq.bufs) == fp4
+    torch.cuda.synchronize()
+    ops.check_status()
+    for s in range(5):
+        for fp4 in (True, False):
+            got, ref_row = outs[fp4][s], want[50 + s]
+            if moe:
+                cos = torch.nn.functional.cosine_similarity(got.float(), ref_row.float(), dim=0).item()
+                assert cos >= 0.98, (fp4, s, cos)
+            else:
+                err = (got - ref_row).abs().max().item()
+                assert err <= 0.08 * ref_row.abs().max().item() + 0.03, (fp4, s, err)

@@ -91,3 +91,46 @@ def test_yarn_scaled_rotary_and_shared_or_cloned_prefixes(dev):
         assert (out2[0] - want[193]).abs().max().item() <= 0.12 * want[193].abs().max().item() + 0.02
     torch.cuda.synchronize()
     ops.check_status()
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_decode_width_block_scaled_linears(dev, moe):
+    """NVFP4 weights: decode-width passes take the block-scaled path (norm kernels emit three-term NVFP4 rows, packed
+    weights stream as stored); logits stay within the oracle's tolerance and close to the converter path's."""
+    from dgpp_b200.models.mla_moe import MlaMoeConfig, MlaMoeModel, MlaMoeRunner
+    from dgpp_b200.models.moe import MoEConfig
+    from dgpp_b200.ops import core as ops
+
+    cfg = MlaMoeConfig(layers=3, hidden=1024, heads=8, q_lora=256, kv_lora=128, nope=64, rope=32, v_dim=64, ffn=2048,
+                       vocab=2048, dense_layers=1, index_heads=4, index_dim=128, index_topk=48, index_key_fp8=True,
+                       moe=MoEConfig(hidden=1024, experts=16, top_k=4, moe_ffn=512, shared_ffn=512) if moe else None)
+    m = MlaMoeModel.random_init(cfg, dev, seed=3, std=0.04, fmt="nvfp4")
+    assert m.layers[0].q_a.fmt == "nvfp4" and m.layers[0].o.fmt == "nvfp4"
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(0, cfg.vocab, (90,), generator=g).tolist()
+    want = m.forward_reference(torch.tensor(toks, device=dev))
+    outs = {}
+    for fp4 in (True, False):
+        r = MlaMoeRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+        r.decode_fp4 = fp4
+        r.prefill(0, toks[:80], chunk=64)
+        r.prefill(1, toks[:70], chunk=64)
+        seq = []
+        for s in range(6):
+            out = r.decode([0, 1] if s < 3 else [0], [toks[80 + s], toks[70 + s]] if s < 3 else [toks[80 + s]])
+            seq.append(out[0].clone())
+        outs[fp4] = seq
+        if fp4:
+            assert r.att.dq.bufs, "the block-scaled path did not run"
+    torch.cuda.synchronize()
+    ops.check_status()
+    for s in range(6):
+        ref_row = want[80 + s]
+        for fp4 in (True, False):
+            got = outs[fp4][s]
+            if moe:
+                cos = torch.nn.functional.cosine_similarity(got.float(), ref_row.float(), dim=0).item()
+                assert cos >= 0.98, (fp4, s, cos)
+            else:
+                err = (got - ref_row).abs().max().item()
+                assert err <= 0.12 * ref_row.abs().max().item() + 0.03, (fp4, s, err)
