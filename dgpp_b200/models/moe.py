@@ -111,10 +111,17 @@ class MoEWeights:
             sf = torch.cat([tile_scales(w.scale.view(w.n, w.k // 16)).reshape(-1) for w in ws]).contiguous()
             al = torch.tensor([w.alpha for w in ws], dtype=torch.float32, device=q.device)
             return q, sf, al
-        self.gu_q, self.gu_sf, self.gu_alpha = cat(self.experts_gu)
+        # A shared expert of the routed experts' shape rides in the same stack as one more expert (index = number of
+        # local experts): the decode path then runs it inside the two grouped GEMMs as an always-listed slot instead of
+        # two further launches and a quantiser of its own.
+        self.shared_stacked = (self.shared_gu is not None and self.cfg.shared_ffn == self.cfg.moe_ffn
+                               and bool(self.experts_gu) and self.shared_gu.fmt == self.experts_gu[0].fmt)
+        extra_gu = [self.shared_gu] if self.shared_stacked else []
+        extra_dn = [self.shared_down] if self.shared_stacked else []
+        self.gu_q, self.gu_sf, self.gu_alpha = cat(self.experts_gu + extra_gu)
         if self.gu_q is not None and not MoEWeights.KEEP_EXPERT_LISTS:
             self.experts_gu = []                    # (the per-expert tensors only serve the oracles)
-        self.down_q, self.down_sf, self.down_alpha = cat(self.experts_down)
+        self.down_q, self.down_sf, self.down_alpha = cat(self.experts_down + extra_dn)
         if self.down_q is not None and not MoEWeights.KEEP_EXPERT_LISTS:
             self.experts_down = []
         if self.gu_q is None or self.down_q is None:
@@ -201,24 +208,31 @@ class MoEBlock:
         i32 = dict(dtype=torch.int32, device=device)
         self.ids = torch.zeros(max_rows, c.top_k, **i32)
         self.wts = torch.zeros(max_rows, c.top_k, dtype=torch.float32, device=device)
-        self.group_list = torch.full((self.slots,), -1, **i32)
+        # with a stacked shared expert the slot after the routed ones always lists it
+        self.sh_slot = self.slots if getattr(w, "shared_stacked", False) else -1
+        nslots = self.slots + (1 if self.sh_slot >= 0 else 0)
+        self.stack_experts = self.local_experts + (1 if self.sh_slot >= 0 else 0)
+        self.group_list = torch.full((nslots,), -1, **i32)
+        if self.sh_slot >= 0:
+            self.group_list[self.sh_slot] = self.local_experts
         self.slot_of = torch.full((c.experts,), -1, **i32)
         self.n_active = torch.zeros(1, **i32)
 
         def shared(name, make):
             if pool is None:
                 return make()
-            key = (name, self.slots, self.bn, max_rows, c.hidden, c.moe_ffn, c.shared_ffn, act_terms)
+            key = (name, nslots, self.bn, max_rows, c.hidden, c.moe_ffn, c.shared_ffn, act_terms)
             if key not in pool:
                 pool[key] = make()
             return pool[key]
 
-        self.h = shared("h", lambda: torch.zeros(self.slots, self.bn, 2 * c.moe_ffn, dtype=BF, device=device))
-        self.y = shared("y", lambda: torch.zeros(self.slots, self.bn, c.hidden, dtype=BF, device=device))
+        self.h = shared("h", lambda: torch.zeros(nslots, self.bn, 2 * c.moe_ffn, dtype=BF, device=device))
+        self.y = shared("y", lambda: torch.zeros(nslots, self.bn, c.hidden, dtype=BF, device=device))
         self.qa_in = shared("qa_in", lambda: ops.QuantAct(self.bn, c.hidden, act_terms, self.bn, device))
-        self.qa_mid = shared("qa_mid", lambda: ops.QuantAct(self.slots * self.bn, c.moe_ffn, act_terms, self.bn, device))
+        self.qa_mid = shared("qa_mid", lambda: ops.QuantAct(nslots * self.bn, c.moe_ffn, act_terms, self.bn, device))
+        self.nslots = nslots
         self.shared = None
-        if w.shared_gu is not None:
+        if w.shared_gu is not None and self.sh_slot < 0:
             self.shared = shared("shared", lambda: torch.zeros(max_rows, c.hidden, dtype=BF, device=device))
             self.sh_gu = shared("sh_gu", lambda: torch.zeros(max_rows, 2 * c.shared_ffn, dtype=BF, device=device))
             self.qa_sh = shared("qa_sh", lambda: ops.QuantAct(self.bn, c.shared_ffn, act_terms, self.bn, device))
@@ -238,13 +252,13 @@ class MoEBlock:
                       c.routed_scaling, ids=self.ids[:rows], weights=self.wts[:rows])
         ops.moe_active(self.ids[:rows], rows, c.experts, self.slots, self.group_list, self.slot_of, self.n_active,
                        self.e0, self.e1)
-        ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, self.h, rows, 2 * c.moe_ffn, c.hidden, self.local_experts,
+        ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, self.h, rows, 2 * c.moe_ffn, c.hidden, self.stack_experts,
                              self.group_list, group_b=False)
-        xm = ops.act_quant_nvfp4(self.h.view(self.slots * self.bn, 2 * c.moe_ffn), self.terms, out=self.qa_mid,
+        xm = ops.act_quant_nvfp4(self.h.view(self.nslots * self.bn, 2 * c.moe_ffn), self.terms, out=self.qa_mid,
                                  mode="swiglu", limit=c.swiglu_limit, group_list=self.group_list, group_rows=rows)
-        ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, self.y, rows, c.hidden, c.moe_ffn, self.local_experts,
+        ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, self.y, rows, c.hidden, c.moe_ffn, self.stack_experts,
                              self.group_list, group_b=True)
-        sh = None
+        sh = self.y[self.sh_slot] if self.sh_slot >= 0 else None          # [bn, H]: the shared expert's rows
         if self.shared is not None:
             ops.gemm_fp4(xa, w.shared_gu_k, out=self.sh_gu[:rows])
             xs = ops.act_quant_nvfp4(self.sh_gu[:rows], self.terms, out=self.qa_sh, mode="swiglu", limit=c.swiglu_limit)
