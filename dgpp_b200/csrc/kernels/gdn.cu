@@ -252,6 +252,23 @@ __global__ void __launch_bounds__(256) gdn_conv_state_kernel(ConvArgs a) {
   for (int i = 0; i < a.W - 1; ++i) st[static_cast<size_t>(i) * a.C] = nv[i];
 }
 
+// Decode form (one new token per request, no snapshots): output and tail shift in one pass.  A thread owns one
+// (request, channel): it reads the tail and the new input, writes the output, then the shifted tail.  grid (C / 256, rows).
+__global__ void __launch_bounds__(256) gdn_conv_decode_kernel(ConvArgs a) {
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.C) return;
+  const int t = blockIdx.y;
+  float* st = a.state + static_cast<size_t>(a.row_slot[t]) * (a.W - 1) * a.C + c;
+  float v[4];
+  for (int i = 0; i < a.W - 1; ++i) v[i] = st[static_cast<size_t>(i) * a.C];
+  v[a.W - 1] = bf16_to_f32(a.x[static_cast<size_t>(t) * a.x_stride + c]);
+  float acc = a.bias ? bf16_to_f32(a.bias[c]) : 0.f;
+  for (int i = 0; i < a.W; ++i) acc = fmaf(bf16_to_f32(a.w[c * a.W + i]), v[i], acc);
+  a.out[static_cast<size_t>(t) * a.C + c] = f32_to_bf16(acc / (1.f + expf(-acc)));
+  for (int i = 0; i < a.W - 1; ++i) st[static_cast<size_t>(i) * a.C] = v[i + 1];
+}
+
 // out[t, h, :] = rmsnorm(o[t, h, :]) * w * silu(z[t, h, :]); one warp per (row, head).
 __global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const bf16* __restrict__ o, const bf16* __restrict__ z,
                                                             int64_t z_stride, const bf16* __restrict__ w,
@@ -397,6 +414,11 @@ static int gdn_conv_launch(const void* x, int64_t x_stride, const void* w, const
   a.out = static_cast<bf16*>(out);
   a.T = T; a.C = C; a.W = W; a.sequential = sequential;
   a.seg = seg; a.snap = static_cast<float*>(snap);
+  if (!sequential && seg == 0 && !snap) {       // batched decode rows: one kernel
+    gdn_conv_decode_kernel<<<dim3(dgpp_ceil_div(C, 256), T), 256, 0, st>>>(a);
+    DGPP_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
   gdn_conv_kernel<<<dim3(dgpp_ceil_div(C, 256), T), 256, 0, st>>>(a);
   DGPP_CUDA_OK(cudaGetLastError());
   if (W > 1) {
