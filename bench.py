@@ -157,6 +157,7 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--prefill-chunk", type=int, default=0, help="--config 2 / 3: rows per prefill pass (0: 2048)")
     ap.add_argument("--index-bf16", action="store_true", help="--config 3: keep the index keys in bf16 (default: e4m3 + per-token scale)")
+    ap.add_argument("--no-dp-extra", action="store_true", help="N > 1: skip the data-parallel replica measurement in extras")
     ap.add_argument("--prompt-lens", default="", help="--config 2 / 3: several long prompt lengths in one run, e.g. 32768,131072")
     ap.add_argument("--mtp", type=int, default=0, choices=(0, 1, 2, 3),
                     help="--config 4: speculative decoding with this many MTP drafts per step (0 = off)")
@@ -339,6 +340,28 @@ def main() -> int:
         extras["doll_shape_bf16_c1_tok_s"] = 1000.0 * K / md
         extras["doll_shape_bf16_c1_ms_per_step"] = md / K
         extras["doll_shape_clocks"] = cd
+        ops.check_status()
+
+    # ---- the same global batch on N full replicas (no collectives): what data parallelism gives at this model size
+    if world > 1 and C % world == 0 and not args.no_dp_extra:
+        del eng, model, reducer
+        torch.cuda.empty_cache()
+        rmodel = DenseModel.random_init(cfg, device=dev, seed=0)
+        b = C // world
+        room = L + 2 * W + K * (max_repeats + 2) + 16
+        reng = LLMEngine(rmodel, max_batch=b, max_seq_len=room, prefill_chunk=2048)
+        rfirst = torch.zeros(b, dtype=torch.int32, device=dev)
+        for s_, p_ in enumerate(prompts[rank * b:(rank + 1) * b]):
+            assert reng.kv.reserve(s_, room)
+            rfirst[s_:s_ + 1].copy_(reng.prefill(s_, p_))
+        reng.start_decode(list(range(b)), rfirst)
+        tr, cr = timed_decode(reng, b)
+        mr = sorted(tr)[len(tr) // 2]
+        extras["dp_replicas_tok_s"] = 1000.0 * C * K / mr
+        extras["dp_replicas_ms_per_step"] = mr / K
+        extras["dp_replicas_note"] = (f"{world} full model replicas, {b} of the {C} sequences on each, no collectives; step time "
+                                      "is the max over ranks; not the headline (which is tensor parallel), shown for scale")
+        extras["dp_replicas_clocks"] = cr
         ops.check_status()
 
     if rank == 0:

@@ -511,7 +511,7 @@ class HybridRunner:
         dev = self.dev
         i32 = dict(dtype=torch.int32, device=dev)
         if drafts is None:
-            # round 0: every pair that waits (hidden rows of the last step, their next tokens ending in the pending one)
+            # draft pass 0: every pair that waits (hidden rows of the last step, their next tokens ending in the pending one)
             hid, toks, pos, req, last = [], [], [], [], []
             for s, p in zip(slots, pending):
                 h = self.mtp_prev[s]
