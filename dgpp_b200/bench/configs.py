@@ -203,11 +203,75 @@ def run_config2(args, dev, indexer: bool = False) -> dict:
     return out
 
 
+def run_config2_ep(args, dev, rank: int, world: int) -> dict:
+    """Config 2 under expert parallelism on `world` GPUs of one box: attention weights replicated, every MoE layer's experts
+    split over the ranks, each rank serving C / world of the C = 8 requests; the rows of a layer go to their experts'
+    owners and come back through the token-sharded all-to-all kernels.  All ranks step in lockstep."""
+    import torch.distributed as dist
+
+    from ..models.mla_moe import MlaMoeConfig, MlaMoeModel, MlaMoeRunner
+    from ..models.moe import MoEConfig
+
+    layers = args.layers if args.layers < 48 else 48
+    cfg = MlaMoeConfig(layers=layers, hidden=4096, heads=32, q_lora=1024, kv_lora=512, nope=128, rope=64, v_dim=128,
+                       ffn=12288, dense_layers=min(2, layers), vocab=129280,
+                       moe=MoEConfig(hidden=4096, experts=256, top_k=8, moe_ffn=1536, shared_ffn=1536, n_group=8,
+                                     topk_group=4, router="sigmoid", routed_scaling=2.5))
+    _lean_experts(args)
+    model = MlaMoeModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4", ep_rank=rank, ep_size=world)
+    C = 8
+    assert C % world == 0
+    mine = C // world
+    L = args.prompt_len
+    chunk = int(getattr(args, "prefill_chunk", 0) or 0) or 2048
+    runner = MlaMoeRunner(model, max_rows=chunk, slots=mine, max_seq_len=L + 512, device=dev)
+    g = torch.Generator().manual_seed(2 + rank)
+
+    def mx(v: float) -> float:
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dist.barrier()
+    out = {"config": 2, "parallelism": f"ep{world}: experts split over {world} GPUs (token-sharded all-to-all inside the captured "
+                                       f"pass), attention replicated, {mine} of the {C} requests per GPU",
+           "layers": layers, "valid": layers == 48}
+    out[f"prefill_s_{L}"] = mx(_time_prefill(runner, cfg.vocab, 0, L, g, chunk))
+    for s in range(1, mine):
+        runner.reset(s)
+        runner.prefill(s, torch.randint(0, cfg.vocab, (L,), generator=g).tolist(), chunk=chunk)
+    dist.barrier()
+    ms1 = mx(_time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g))
+    dist.barrier()
+    msc = mx(_time_decode(runner, cfg.vocab, list(range(mine)), args.steps, args.warmup, g))
+    out.update(c1_ms_per_step=ms1, c1_decode_tok_s=1000.0 / ms1,
+               c1_note=f"one request per GPU ({world} in all, the others keep the exchange in step): tok/s of one request",
+               c8_ms_per_step=msc, c8_decode_tok_s=1000.0 * C / msc, steps=args.steps, context=L)
+    return out
+
+
 def run(config: int, args) -> int:
     from ..ops import core as ops
 
-    dev = torch.device("cuda", 0)
+    import os
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        assert config == 2, "more than one GPU: --config 2 runs expert parallel; the other family arms are single-GPU"
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+        res = run_config2_ep(args, dev, rank, world)
+        ops.check_status()
+        res["n_gpus"] = world
+        res["data"] = "synthetic"
+        if rank == 0:
+            print(json.dumps(res))
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0
     if config == 4:
         res = run_config4(args, dev)
     elif config in (2, 3):

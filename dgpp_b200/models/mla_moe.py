@@ -157,7 +157,10 @@ class MlaMoeModel:
         self.cfg, self.embed, self.layers, self.final_norm, self.head, self.inv_freq = cfg, embed, layers, final_norm, head, inv_freq
 
     @staticmethod
-    def random_init(cfg: MlaMoeConfig, device, seed: int = 0, std: float = 0.05, fmt: str = "bf16") -> "MlaMoeModel":
+    def random_init(cfg: MlaMoeConfig, device, seed: int = 0, std: float = 0.05, fmt: str = "bf16", ep_rank: int = 0,
+                    ep_size: int = 1) -> "MlaMoeModel":
+        """ep_size > 1 (expert parallelism): every rank draws the same model and keeps its contiguous block of every MoE
+        layer's experts (plus a copy of the shared expert, which runs on the rank's own rows); everything else is replicated."""
         g = torch.Generator(device=device)
         g.manual_seed(seed)
         rnd = lambda n, k: torch.randn(n, k, device=device, dtype=torch.float32, generator=g) * std
@@ -172,7 +175,8 @@ class MlaMoeModel:
                          (torch.randn(c.heads, c.v_dim, c.kv_lora, device=device, generator=g) * std * 2).to(BF),
                          lin(H, c.heads * c.v_dim))
             if cfg.moe is not None and i >= cfg.dense_layers:
-                L.moe = MoEWeights.random_init(cfg.moe, device, seed=seed * 1000 + i, std=std)
+                L.moe = MoEWeights.random_init(cfg.moe, device, seed=seed * 1000 + i, std=std, ep_rank=ep_rank, ep_size=ep_size,
+                                               shared_everywhere=ep_size > 1)
             else:
                 L.gate_up, L.down = lin(2 * c.ffn, H), lin(H, c.ffn)
             if cfg.index_heads:
@@ -320,8 +324,22 @@ class MlaMoeRunner:
         self.page, self.max_blocks, self.max_ctx = self.att.page, self.att.max_blocks, self.att.max_ctx
         self.latent, self.kidx, self.block_table = self.att.latent, self.att.kidx, self.att.block_table
         self.lengths = [0] * slots
+        # expert parallelism: a model whose MoE layers hold a block of the experts runs them through the token-sharded
+        # all-to-all (this rank's rows go to the experts' owners and come back); every rank then calls the model in
+        # lockstep, each with its own rows.  One communicator and one set of tile buffers serve all layers.
+        self.ep, self.ep_small = {}, {}
+        first = next((L.moe for L in model.layers if L.moe is not None), None)
+        if first is not None and (first.e_end or c.moe.experts) - first.e_begin < c.moe.experts:
+            from ..parallel.ep import EpMoE
+            comm, pool, pool_small = None, {}, {}
+            for i, L in enumerate(model.layers):
+                if L.moe is not None:
+                    self.ep[i] = EpMoE(L.moe, max_rows, device, comm=comm, pool=pool)
+                    comm = comm or (self.ep[i].comm, self.ep[i].world, self.ep[i].rank, self.ep[i]._blob)
+                    # decode widths get their own small tile lists (the prefill-sized ones cost a decode step their grid)
+                    self.ep_small[i] = EpMoE(L.moe, 16, device, comm=comm, pool=pool_small) if max_rows > 16 else self.ep[i]
         self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
-                    if L.moe is not None and L.moe.gu_q is not None}
+                    if L.moe is not None and L.moe.gu_q is not None and not self.ep}
         self.decode_fp4 = True      # decode-width passes: NVFP4 linears on the block-scaled path (three-term activations)
         self.use_graphs, self._graphs, self._static = True, {}, {}
         self.pdl_graphs = True      # programmatic-dependent-launch edges between this library's kernels in captured passes
@@ -358,7 +376,9 @@ class MlaMoeRunner:
             else:
                 ops.rmsnorm(x, L.post_norm, c.eps, delta=delta, out=xn)
             have = True
-            if L.moe is not None:
+            if L.moe is not None and i in self.ep:
+                (self.ep_small[i] if rows <= 16 else self.ep[i]).forward(xn, out=delta)
+            elif L.moe is not None:
                 blk = self.moe.get(i)
                 if blk is not None and rows <= blk.max_rows:
                     blk.forward(xn, delta, xa=xa if (fast and blk.bn == dq.ROWS and blk.terms == dq.TERMS) else None)

@@ -63,7 +63,9 @@ class EpMoE:
     """One MoE block under expert parallelism.  `w` holds this rank's expert block (stacked) and, when the model has a
     shared expert, a copy of it (the shared expert runs on the rank's own rows)."""
 
-    def __init__(self, w: MoEWeights, max_rows: int, device, group=None, act_terms: int = 3):
+    def __init__(self, w: MoEWeights, max_rows: int, device, group=None, act_terms: int = 3, comm=None, pool=None):
+        """comm: a communicator from `open_comm` shared by the blocks of one model (their exchanges are sequential; the
+        slot size must fit max_rows * top_k pairs); pool: a dict through which those blocks share their tile buffers."""
         c = w.cfg
         assert w.gu_q is not None, "call MoEWeights.stack() on the device first"
         self.w, self.c, self.dev, self.terms = w, c, device, act_terms
@@ -72,7 +74,9 @@ class EpMoE:
         lib.dgpp_ep_slot_bytes.restype = L
         lib.dgpp_ep_slot_bytes.argtypes = [I, I]
         slot = lib.dgpp_ep_slot_bytes(c.hidden, self.max_pairs)
-        self.comm, self.world, self.rank, self._blob = open_comm(slot, device, group)
+        self.slot_bytes = slot
+        self.comm, self.world, self.rank, self._blob = comm if comm is not None else open_comm(slot, device, group)
+        self.owns_comm = comm is None
         assert c.experts % self.world == 0, "experts must divide over the ranks"
         per = c.experts // self.world
         self.local = per
@@ -87,11 +91,20 @@ class EpMoE:
         self.pair_row = torch.full((cap,), -1, **i32)
         self.tiles, self.n_tiles = torch.full((self.max_tiles,), -1, **i32), torch.zeros(1, **i32)
         rows = self.max_tiles * self.bn
-        self.xs = torch.zeros(rows, c.hidden, dtype=BF, device=device)
-        self.h = torch.zeros(self.max_tiles, self.bn, 2 * c.moe_ffn, dtype=BF, device=device)
-        self.y = torch.zeros(self.max_tiles, self.bn, c.hidden, dtype=BF, device=device)
-        self.qa_x = ops.QuantAct(rows, c.hidden, act_terms, self.bn, device)
-        self.qa_mid = ops.QuantAct(rows, c.moe_ffn, act_terms, self.bn, device)
+
+        def shared(name, make):
+            if pool is None:
+                return make()
+            key = (name, self.max_tiles, c.hidden, c.moe_ffn, act_terms)
+            if key not in pool:
+                pool[key] = make()
+            return pool[key]
+
+        self.xs = shared("xs", lambda: torch.zeros(rows, c.hidden, dtype=BF, device=device))
+        self.h = shared("h", lambda: torch.zeros(self.max_tiles, self.bn, 2 * c.moe_ffn, dtype=BF, device=device))
+        self.y = shared("y", lambda: torch.zeros(self.max_tiles, self.bn, c.hidden, dtype=BF, device=device))
+        self.qa_x = shared("qa_x", lambda: ops.QuantAct(rows, c.hidden, act_terms, self.bn, device))
+        self.qa_mid = shared("qa_mid", lambda: ops.QuantAct(rows, c.moe_ffn, act_terms, self.bn, device))
 
     def forward(self, xn: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """xn: this rank's rows [T, H] bf16 (1 <= T <= max_rows; every rank calls with its own T).  Returns [T, H]."""
@@ -134,6 +147,6 @@ class EpMoE:
         return 2.0 * c.top_k * c.hidden * 2 * (self.world - 1) / self.world
 
     def close(self) -> None:
-        if self.comm:
+        if self.comm and self.owns_comm:
             call("dgpp_comm_destroy", self.comm)
             self.comm = None
