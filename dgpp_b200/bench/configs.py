@@ -250,6 +250,48 @@ def run_config2_ep(args, dev, rank: int, world: int) -> dict:
     return out
 
 
+def run_config4_ep(args, dev, rank: int, world: int) -> dict:
+    """Config 4 under expert parallelism: GDN / attention layers replicated, the 512 experts of every layer split over the
+    ranks, each rank serving C / world of the C = 8 requests (see run_config2_ep)."""
+    import torch.distributed as dist
+
+    from ..models.hybrid import HybridConfig, HybridModel, HybridRunner
+    from ..models.moe import MoEConfig
+
+    layers = args.layers if args.layers < 48 else 48
+    cfg = HybridConfig(layers=layers, hidden=2048, full_every=4, q_heads=16, kv_heads=2, head_dim=256, gdn_k_heads=16,
+                       gdn_v_heads=16, gdn_dk=128, gdn_dv=128, vocab=151936,
+                       moe=MoEConfig(hidden=2048, experts=512, top_k=10, moe_ffn=512, shared_ffn=512, router="softmax"))
+    _lean_experts(args)
+    model = HybridModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4", ep_rank=rank, ep_size=world)
+    C, chunk, L = 8, 2048, args.prompt_len
+    mine = C // world
+    runner = HybridRunner(model, max_rows=chunk, slots=mine, max_seq_len=L + 1024, device=dev)
+    g = torch.Generator().manual_seed(4 + rank)
+
+    def mx(v: float) -> float:
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dist.barrier()
+    out = {"config": 4, "parallelism": f"ep{world}: experts split over {world} GPUs (token-sharded all-to-all inside the captured "
+                                       f"pass), mixers replicated, {mine} of the {C} requests per GPU",
+           "layers": layers, "valid": layers == 48}
+    out[f"prefill_s_{L}"] = mx(_time_prefill(runner, cfg.vocab, 0, L, g, chunk))
+    for s in range(1, mine):
+        runner.reset(s)
+        runner.prefill(s, torch.randint(0, cfg.vocab, (L,), generator=g).tolist(), chunk=chunk)
+    dist.barrier()
+    ms1 = mx(_time_decode(runner, cfg.vocab, [0], args.steps, args.warmup, g))
+    dist.barrier()
+    msc = mx(_time_decode(runner, cfg.vocab, list(range(mine)), args.steps, args.warmup, g))
+    out.update(c1_ms_per_step=ms1, c1_decode_tok_s=1000.0 / ms1,
+               c1_note=f"one request per GPU ({world} in all, the others keep the exchange in step): tok/s of one request",
+               c8_ms_per_step=msc, c8_decode_tok_s=1000.0 * C / msc, steps=args.steps, context=L)
+    return out
+
+
 def run(config: int, args) -> int:
     from ..ops import core as ops
 
@@ -259,11 +301,11 @@ def run(config: int, args) -> int:
     torch.cuda.set_device(dev)
     if world > 1:
         import torch.distributed as dist
-        assert config == 2, "more than one GPU: --config 2 runs expert parallel; the other family arms are single-GPU"
+        assert config in (2, 4), "more than one GPU: --config 2 and 4 run expert parallel; config 3 is a single-GPU arm"
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
-        res = run_config2_ep(args, dev, rank, world)
+        res = run_config2_ep(args, dev, rank, world) if config == 2 else run_config4_ep(args, dev, rank, world)
         ops.check_status()
         res["n_gpus"] = world
         res["data"] = "synthetic"

@@ -116,6 +116,26 @@ def main() -> int:
         same += int(a.argmax()) == int(b.argmax())
     torch.cuda.synchronize()
     say(f"model decode logits over 6 graph-replayed steps: worst cosine {worst:.6f}, argmax equal in {same} of 6", worst >= 0.995)
+    # the hybrid family through the same path
+    from dgpp_b200.models.hybrid import HybridConfig, HybridModel, HybridRunner
+    hcfg = HybridConfig(layers=4, hidden=512, full_every=4, q_heads=4, kv_heads=2, head_dim=128, gdn_k_heads=2, gdn_v_heads=4,
+                        gdn_dk=128, gdn_dv=128, ffn=1024, vocab=2048,
+                        moe=MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512, shared_ffn=512))
+    hfull = HybridRunner(HybridModel.random_init(hcfg, dev, seed=5, std=0.05, fmt="nvfp4"), 64, 1, 256, dev)
+    hpart = HybridRunner(HybridModel.random_init(hcfg, dev, seed=5, std=0.05, fmt="nvfp4", ep_rank=rank, ep_size=world), 64, 1,
+                         256, dev)
+    htoks = torch.randint(0, hcfg.vocab, (70,), generator=g3).tolist()
+    a = hfull.prefill(0, htoks[:64], chunk=32)[-1].clone()
+    b = hpart.prefill(0, htoks[:64], chunk=32)[-1].clone()
+    cos = torch.nn.functional.cosine_similarity(a.float(), b.float(), dim=0).item()
+    worst = 1.0
+    for s_ in range(5):
+        a = hfull.decode([0], [htoks[64 + s_]])[0]
+        b = hpart.decode([0], [htoks[64 + s_]])[0]
+        worst = min(worst, torch.nn.functional.cosine_similarity(a.float(), b.float(), dim=0).item())
+    torch.cuda.synchronize()
+    say(f"hybrid model, expert parallel vs one rank: prefill cosine {cos:.6f}, worst decode cosine {worst:.6f}",
+        cos >= 0.999 and worst >= 0.995)
     try:
         ops.check_status()
         say("device status clean after the model run")

@@ -79,7 +79,10 @@ class HybridModel:
     mtp_layer: Optional[HybridLayer] = None       # one full-attention block
 
     @staticmethod
-    def random_init(cfg: HybridConfig, device, seed: int = 0, std: float = 0.05, fmt: str = "bf16") -> "HybridModel":
+    def random_init(cfg: HybridConfig, device, seed: int = 0, std: float = 0.05, fmt: str = "bf16", ep_rank: int = 0,
+                    ep_size: int = 1) -> "HybridModel":
+        """ep_size > 1 (expert parallelism): this rank keeps its contiguous block of every MoE layer's experts (and a copy
+        of the shared expert); the mixers, norms, embeddings and the head are replicated."""
         g = torch.Generator(device=device)
         g.manual_seed(seed)
         H, d = cfg.hidden, cfg.head_dim
@@ -96,7 +99,8 @@ class HybridModel:
             if cfg.moe is not None:
                 mc = MoEConfig(**{**cfg.moe.__dict__, "hidden": H})
                 L.moe = MoEWeights.random_init(mc, device, seed=seed * 1000 + i, std=std,
-                                               fmt="nvfp4" if torch.device(device).type == "cuda" else "bf16")
+                                               fmt="nvfp4" if torch.device(device).type == "cuda" else "bf16",
+                                               ep_rank=ep_rank, ep_size=ep_size, shared_everywhere=ep_size > 1)
             else:
                 L.gate_up = quantize(rnd(2 * cfg.ffn, H), fmt)
                 L.down = quantize(rnd(H, cfg.ffn), fmt)
@@ -194,8 +198,19 @@ class HybridRunner:
         self.gdn = {i: GdnLayer(model.layers[i].gdn, max_rows, device) for i in self.gdn_state}
         self.full_index = {i: j for j, i in enumerate(i for i in range(c.layers) if c.is_full(i))}
         self.moe_wide, self._moe_pool = {}, {}
+        # expert parallelism (see MlaMoeRunner): MoE layers holding a block of the experts go through the all-to-all
+        self.ep, self.ep_small = {}, {}
+        first = next((L.moe for L in model.layers if L.moe is not None), None)
+        if first is not None and (first.e_end or first.cfg.experts) - first.e_begin < first.cfg.experts:
+            from ..parallel.ep import EpMoE
+            comm, pool, pool_small = None, {}, {}
+            for i, L in enumerate(model.layers):
+                if L.moe is not None:
+                    self.ep[i] = EpMoE(L.moe, max_rows, device, comm=comm, pool=pool)
+                    comm = comm or (self.ep[i].comm, self.ep[i].world, self.ep[i].rank, self.ep[i]._blob)
+                    self.ep_small[i] = EpMoE(L.moe, 16, device, comm=comm, pool=pool_small) if max_rows > 16 else self.ep[i]
         self.moe = {i: MoEBlock(L.moe, min(max_rows, 16), device) for i, L in enumerate(model.layers)
-                    if L.moe is not None and L.moe.gu_q is not None}
+                    if L.moe is not None and L.moe.gu_q is not None and not self.ep}
         self.slots = slots
         self.spec_rows = 0          # rows per speculative run (1 + draft depth); 0 = speculation off
         if slots > 16:
@@ -254,6 +269,9 @@ class HybridRunner:
             st.reset(slot)
 
     def _ffn(self, i: int, L: HybridLayer, xn: torch.Tensor, out: torch.Tensor, xa=None) -> None:
+        if L.moe is not None and i in self.ep:
+            (self.ep_small[i] if xn.shape[0] <= 16 else self.ep[i]).forward(xn, out=out)
+            return
         if L.moe is not None:
             blk = self.moe.get(i)
             wide = self.moe_wide.get(i)
