@@ -223,7 +223,8 @@ def run_config2_ep(args, dev, rank: int, world: int) -> dict:
     assert C % world == 0
     mine = C // world
     L = args.prompt_len
-    chunk = int(getattr(args, "prefill_chunk", 0) or 0) or 2048
+    # the owners' tile buffers hold every rank's pairs of a pass: the chunk shrinks with the rank count
+    chunk = int(getattr(args, "prefill_chunk", 0) or 0) or max(256, 4096 // world)
     runner = MlaMoeRunner(model, max_rows=chunk, slots=mine, max_seq_len=L + 512, device=dev)
     g = torch.Generator().manual_seed(2 + rank)
 
@@ -264,7 +265,7 @@ def run_config4_ep(args, dev, rank: int, world: int) -> dict:
                        moe=MoEConfig(hidden=2048, experts=512, top_k=10, moe_ffn=512, shared_ffn=512, router="softmax"))
     _lean_experts(args)
     model = HybridModel.random_init(cfg, dev, seed=0, std=0.02, fmt="nvfp4", ep_rank=rank, ep_size=world)
-    C, chunk, L = 8, 2048, args.prompt_len
+    C, chunk, L = 8, max(256, 4096 // world), args.prompt_len
     mine = C // world
     runner = HybridRunner(model, max_rows=chunk, slots=mine, max_seq_len=L + 1024, device=dev)
     g = torch.Generator().manual_seed(4 + rank)
