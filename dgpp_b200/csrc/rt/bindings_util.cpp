@@ -5,6 +5,7 @@
 
 #include "rt/core_util.h"
 #include "rt/jpeg.h"
+#include "rt/webp.h"
 
 namespace py = pybind11;
 using namespace dgpp;
@@ -109,6 +110,24 @@ void bind_util(py::module_& m) {
     }
     return py::make_tuple(img.width, img.height, img.channels,
                           py::bytes(reinterpret_cast<const char*>(img.pixels.data()), img.pixels.size()));
+  });
+  m.def("decode_webp", [](const py::bytes& data) {
+    // (width, height, RGBA bytes) of a lossless WebP file; raises ValueError naming what is wrong (lossy files too)
+    const std::string buf = data;
+    rt::webp::Image img;
+    {
+      py::gil_scoped_release release;
+      try {
+        img = rt::webp::decode(reinterpret_cast<const uint8_t*>(buf.data()), buf.size());
+      } catch (const std::runtime_error& e) {
+        py::gil_scoped_acquire acquire;
+        throw py::value_error(e.what());
+      } catch (const std::bad_alloc&) {
+        py::gil_scoped_acquire acquire;
+        throw py::value_error("webp: image too large");
+      }
+    }
+    return py::make_tuple(img.width, img.height, py::bytes(reinterpret_cast<const char*>(img.rgba.data()), img.rgba.size()));
   });
   m.def("file_residency", [](const std::string& path) {
     int64_t size = -1;

@@ -15,6 +15,7 @@
 #include "rt/core_util.h"
 #include "rt/fake_engine.h"
 #include "rt/jpeg.h"
+#include "rt/webp.h"
 #include "rt/json.h"
 #include "rt/json_grammar.h"
 #include "rt/paged_blocks.h"
@@ -226,6 +227,81 @@ static void test_jpeg() {
   }
 }
 
+// two 24 x 20 lossless WebP files: a noisy gradient (predictor, cross-colour and subtract-green transforms, backward
+// references) and a five-colour picture (colour indexing with packed pixels)
+static const unsigned char kWebpPhoto[] = {
+    82, 73, 70, 70, 32, 3, 0, 0, 87, 69, 66, 80, 86, 80, 56, 76, 19, 3, 0, 0, 47, 23, 192, 4,
+    0, 1, 69, 109, 219, 64, 207, 74, 230, 207, 184, 59, 40, 68, 244, 127, 2, 164, 49, 241, 24, 40, 106, 219,
+    136, 41, 128, 222, 30, 239, 227, 143, 239, 192, 176, 145, 36, 169, 205, 224, 137, 136, 108, 184, 255, 127, 29, 78,
+    138, 21, 182, 109, 219, 240, 255, 115, 211, 221, 26, 69, 255, 195, 103, 182, 130, 104, 145, 21, 42, 255, 11, 250,
+    206, 56, 16, 172, 220, 151, 190, 40, 105, 16, 47, 206, 133, 174, 231, 56, 28, 10, 229, 36, 33, 157, 220, 196,
+    45, 128, 24, 128, 109, 219, 70, 150, 72, 0, 4, 148, 241, 255, 175, 109, 222, 128, 216, 54, 146, 35, 105, 186,
+    92, 215, 154, 251, 207, 63, 218, 149, 32, 128, 109, 220, 54, 0, 8, 176, 237, 254, 255, 215, 83, 33, 34, 54,
+    250, 127, 119, 85, 203, 183, 222, 183, 162, 115, 223, 239, 237, 127, 186, 254, 222, 238, 239, 95, 180, 30, 109, 235,
+    239, 31, 235, 194, 99, 253, 126, 61, 217, 191, 247, 223, 211, 252, 196, 245, 104, 245, 101, 218, 160, 41, 88, 189,
+    175, 149, 206, 73, 247, 244, 236, 215, 50, 153, 147, 59, 151, 154, 106, 155, 11, 161, 37, 157, 89, 238, 148, 92,
+    68, 103, 197, 194, 122, 179, 238, 105, 174, 37, 5, 91, 146, 133, 244, 204, 144, 132, 135, 171, 22, 148, 163, 174,
+    224, 237, 250, 254, 60, 100, 140, 142, 229, 251, 112, 52, 108, 142, 113, 167, 101, 209, 115, 39, 50, 187, 184, 140,
+    180, 173, 148, 210, 230, 206, 96, 43, 165, 226, 186, 195, 85, 64, 6, 84, 117, 57, 131, 213, 93, 100, 163, 241,
+    13, 101, 69, 128, 214, 109, 196, 17, 218, 238, 128, 57, 164, 204, 54, 45, 166, 24, 27, 79, 203, 197, 57, 152,
+    125, 242, 114, 165, 91, 61, 49, 34, 136, 26, 17, 104, 152, 206, 211, 82, 205, 63, 116, 75, 221, 73, 67, 184,
+    212, 217, 17, 122, 50, 233, 32, 47, 117, 234, 60, 74, 17, 38, 45, 41, 182, 111, 247, 246, 20, 91, 232, 139,
+    61, 170, 118, 230, 77, 69, 120, 176, 226, 53, 179, 213, 41, 87, 238, 186, 214, 70, 176, 213, 177, 24, 27, 131,
+    80, 97, 148, 167, 99, 21, 6, 17, 34, 186, 135, 209, 133, 141, 213, 35, 160, 229, 109, 223, 40, 218, 229, 2,
+    70, 222, 90, 229, 201, 77, 97, 103, 39, 68, 15, 3, 80, 115, 253, 207, 192, 124, 175, 180, 138, 123, 236, 229,
+    195, 76, 79, 209, 161, 63, 219, 88, 185, 57, 197, 108, 28, 27, 35, 204, 64, 130, 41, 189, 156, 33, 48, 19,
+    53, 145, 52, 230, 112, 230, 74, 64, 208, 238, 76, 109, 69, 0, 212, 74, 80, 115, 136, 77, 197, 46, 184, 89,
+    42, 77, 29, 178, 137, 176, 37, 240, 232, 197, 185, 231, 60, 172, 187, 224, 15, 149, 162, 222, 126, 216, 213, 205,
+    152, 74, 164, 49, 226, 224, 6, 28, 137, 2, 105, 161, 5, 125, 20, 240, 250, 168, 4, 103, 145, 97, 194, 51,
+    88, 52, 126, 217, 137, 53, 164, 208, 225, 142, 104, 174, 53, 136, 169, 85, 1, 59, 67, 81, 228, 90, 246, 156,
+    133, 139, 195, 7, 219, 103, 23, 12, 137, 123, 46, 184, 84, 195, 195, 253, 180, 129, 229, 237, 132, 215, 207, 7,
+    10, 238, 185, 104, 116, 152, 60, 136, 30, 194, 155, 105, 213, 71, 20, 176, 175, 88, 4, 135, 101, 20, 25, 111,
+    102, 170, 88, 130, 112, 190, 135, 114, 0, 207, 245, 149, 252, 26, 0, 51, 39, 173, 180, 73, 209, 70, 57, 112,
+    52, 23, 116, 100, 233, 152, 29, 123, 162, 254, 118, 86, 105, 83, 217, 47, 54, 71, 80, 99, 51, 32, 251, 242,
+    11, 202, 213, 225, 47, 57, 27, 250, 146, 209, 39, 11, 148, 67, 221, 249, 215, 187, 54, 169, 116, 102, 108, 25,
+    158, 109, 152, 136, 70, 215, 131, 241, 85, 113, 212, 51, 186, 174, 188, 206, 1, 215, 33, 16, 138, 99, 97, 241,
+    26, 130, 19, 247, 222, 54, 52, 73, 123, 221, 179, 247, 69, 200, 208, 116, 24, 198, 92, 80, 91, 131, 2, 46,
+    41, 237, 123, 117, 213, 97, 83, 140, 53, 174, 11, 103, 116, 95, 203, 92, 25, 109, 47, 144, 168, 166, 116, 244,
+    154, 34, 126, 200, 222, 239, 33, 190, 130, 53, 189, 51, 181, 86, 163, 102, 213, 67, 215, 229, 140, 51, 196, 187,
+    86, 28, 149, 98, 22, 250, 62, 156, 198, 115, 100, 210, 0, 213, 2, 0,
+};
+static const unsigned char kWebpPalette[] = {
+    82, 73, 70, 70, 216, 0, 0, 0, 87, 69, 66, 80, 86, 80, 56, 76, 204, 0, 0, 0, 47, 23, 192, 4,
+    0, 39, 64, 152, 109, 244, 29, 195, 96, 6, 119, 198, 103, 67, 144, 109, 147, 140, 97, 0, 51, 184, 230, 177,
+    9, 178, 109, 4, 70, 48, 148, 73, 221, 253, 4, 243, 31, 234, 47, 128, 117, 125, 192, 32, 0, 144, 182, 178,
+    80, 12, 128, 72, 0, 95, 0, 230, 8, 224, 33, 162, 255, 241, 218, 223, 73, 112, 221, 233, 101, 209, 0, 108,
+    136, 250, 63, 222, 86, 184, 230, 230, 117, 238, 191, 57, 226, 28, 35, 193, 154, 14, 110, 108, 242, 55, 193, 54,
+    246, 72, 222, 234, 157, 75, 3, 113, 211, 151, 14, 0, 93, 42, 19, 236, 165, 27, 83, 162, 79, 168, 109, 9,
+    130, 125, 143, 235, 243, 109, 187, 67, 127, 166, 16, 226, 126, 149, 118, 86, 235, 109, 85, 141, 75, 110, 214, 254,
+    152, 176, 149, 179, 7, 62, 177, 211, 137, 83, 95, 24, 199, 109, 110, 185, 204, 60, 121, 30, 196, 8, 213, 82,
+    162, 3, 159, 23, 88, 58, 152, 36, 13, 85, 4, 177, 176, 136, 103, 155, 166, 149, 227, 11, 252, 29, 135, 30,
+    34, 31, 94, 158, 5, 192, 157, 38,
+};
+
+static void test_webp() {
+  std::mt19937 rng(123);
+  const std::pair<const unsigned char*, size_t> files[] = {{kWebpPhoto, sizeof(kWebpPhoto)}, {kWebpPalette, sizeof(kWebpPalette)}};
+  for (const auto& f : files) {
+    const auto img = dgpp::rt::webp::decode(f.first, f.second);
+    CHECK(img.width == 24 && img.height == 20 && img.rgba.size() == 24u * 20u * 4u);
+    int ok = 0, refused = 0;
+    for (size_t cut = 0; cut < f.second; cut += 3) {
+      try { dgpp::rt::webp::decode(f.first, cut); ++ok; } catch (const std::runtime_error&) { ++refused; }
+    }
+    for (int it = 0; it < 6000; ++it) {
+      std::vector<unsigned char> buf(f.first, f.first + f.second);
+      const int hits = 1 + static_cast<int>(rng() % 4);
+      for (int h = 0; h < hits; ++h) buf[20 + rng() % (buf.size() - 20)] = static_cast<unsigned char>(rng());
+      try {
+        const auto r = dgpp::rt::webp::decode(buf.data(), buf.size());
+        CHECK(r.rgba.size() == static_cast<size_t>(r.width) * r.height * 4);
+        ++ok;
+      } catch (const std::runtime_error&) { ++refused; }
+    }
+    CHECK(ok > 0 && refused > 0);
+  }
+}
+
 int main() {
   test_blocks();
   test_scheduler();
@@ -233,6 +309,7 @@ int main() {
   test_grammar();
   test_crc_and_journal();
   test_jpeg();
+  test_webp();
   if (g_fail) { std::fprintf(stderr, "selftest: %d check(s) failed\n", g_fail); return 1; }
   std::puts("rt selftest ok");
   return 0;

@@ -4,8 +4,9 @@ turns decoded RGB into the patch canvas a vision tower expects.
 Only inline `data:` URIs are accepted: resolving remote URLs is deliberately not part of the serving path.  PNG is
 decoded here (zlib + the five scanline filters, 8 / 16-bit gray, RGB, palette, with or without alpha, non-interlaced);
 binary PPM / PGM as the trivial lossless carrier used by tests and tools; JPEG (sequential and progressive Huffman
-streams, grey / YCbCr / RGB) goes through the native decoder of the runtime library.  WebP needs a codec this build
-does not carry and is refused with a 400 that names the content part.  A decode error carries the API field of the part.
+streams, grey / YCbCr / RGB) and lossless WebP (VP8L, plain or in the extended container) go through the native decoders
+of the runtime library.  Lossy and animated WebP are refused with a 400 that names the content part and the reason.
+A decode error carries the API field of the part.
 (reference counterparts: src/serve/image_inputs.cpp prepare_image / resize_image, common/image_input.hpp; the
  reference decodes through stb_image / simplewebp.)
 """
@@ -202,6 +203,22 @@ def decode_jpeg(data: bytes, param: str = "image_url") -> np.ndarray:
     return np.repeat(a, 3, axis=2) if ch == 1 else a.copy()
 
 
+def decode_webp(data: bytes, param: str = "image_url") -> np.ndarray:
+    """RGB uint8 [h, w, 3] of a lossless WebP file; alpha is composited over white like PNG alpha."""
+    from ..runtime import rt
+
+    try:
+        w, h, px = rt.decode_webp(data)
+    except ValueError as e:
+        raise ImageInputError(str(e), param) from None
+    if not (0 < w <= MAX_IMAGE_SIDE and 0 < h <= MAX_IMAGE_SIDE):
+        raise ImageInputError(f"image side outside 1..{MAX_IMAGE_SIDE}", param)
+    a = np.frombuffer(px, np.uint8).reshape(h, w, 4)
+    if int(a[..., 3].min()) == 255:
+        return a[..., :3].copy()
+    return _over_white(a[..., :3], a[..., 3])
+
+
 def decode_image(data: bytes, param: str = "image_url") -> np.ndarray:
     if data[:8] == b"\x89PNG\r\n\x1a\n":
         return decode_png(data, param)
@@ -210,8 +227,8 @@ def decode_image(data: bytes, param: str = "image_url") -> np.ndarray:
     if data[:3] == b"\xff\xd8\xff":
         return decode_jpeg(data, param)
     if data[:4] == b"RIFF" and data[8:12] == b"WEBP":
-        raise ImageInputError("WebP images are not supported by this build (send PNG)", param)
-    raise ImageInputError("unrecognised image format (PNG, JPEG and binary PPM are accepted)", param)
+        return decode_webp(data, param)
+    raise ImageInputError("unrecognised image format (PNG, JPEG, lossless WebP and binary PPM are accepted)", param)
 
 
 def _round_half_even(x: float) -> int:
