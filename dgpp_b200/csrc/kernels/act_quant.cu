@@ -37,7 +37,7 @@ struct ClusterQuantArgs {
   float* g;
   int T, T_pad, K, R, bn, cl;
   DeviceStatus* status;
-  float eps, limit;
+  float eps, limit, alpha;     // alpha > 0: gate * sigmoid(alpha * gate) * (up + 1) in the swiglu mode
   int one_plus_w;
   // MODE 2 with fold = 1: `delta` is not read from memory but folded from the W partial tiles that the
   // tensor-parallel GEMMs pushed into this rank's symmetric region (ascending rank order, fp32, one bf16
@@ -215,7 +215,13 @@ __global__ void __launch_bounds__(kAqThreads) act_quant_cluster_kernel(ClusterQu
         for (int j = 0; j < 8; ++j) {
           float gv = bf16_to_f32(x.h[j]), uv = bf16_to_f32(u.h[j]);
           if (a.limit > 0.f) { gv = fminf(gv, a.limit); uv = fminf(fmaxf(uv, -a.limit), a.limit); }
-          const float sl = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-gv))));
+          float sl;
+          if (a.alpha > 0.f) {
+            sl = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-a.alpha * gv))));
+            uv += 1.f;
+          } else {
+            sl = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-gv))));
+          }
           x.h[j] = f32_to_bf16(sl * uv);
         }
       }
@@ -308,7 +314,7 @@ using namespace dgpp;
 DGPP_API int dgpp_act_quant_nvfp4_cluster(int mode, const void* in, int64_t in_stride, const void* delta,
                                           const void* w, void* resid_out, void* x_out, void* q, void* sf, void* g,
                                           int T, int T_pad, int K, int R, int bn, int cl, float eps, float limit,
-                                          int one_plus_w, void* comm_fold, const void* group_list, int group_rows,
+                                          float alpha, int one_plus_w, void* comm_fold, const void* group_list, int group_rows,
                                           cudaStream_t st) {
   DGPP_REQUIRE(K % 256 == 0, "act_quant: K %d must be a multiple of 256", K);
   DGPP_REQUIRE(cl == 1 || cl == 2 || cl == 4 || cl == 8, "act_quant: cluster size %d not in {1,2,4,8}", cl);
@@ -327,7 +333,7 @@ DGPP_API int dgpp_act_quant_nvfp4_cluster(int mode, const void* in, int64_t in_s
   a.q = static_cast<uint8_t*>(q);
   a.sf = static_cast<uint8_t*>(sf);
   a.g = static_cast<float*>(g);
-  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.cl = cl; a.eps = eps; a.limit = limit;
+  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.cl = cl; a.eps = eps; a.limit = limit; a.alpha = alpha;
   a.one_plus_w = one_plus_w;
   a.status = device_status_ptr();
   a.group_list = static_cast<const int32_t*>(group_list);
@@ -371,7 +377,7 @@ DGPP_API int dgpp_attn_combine_quant(const void* part_ml, const void* part_acc, 
   a.q = static_cast<uint8_t*>(q);
   a.sf = static_cast<uint8_t*>(sf);
   a.g = static_cast<float*>(g);
-  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.cl = cl; a.eps = 0.f; a.limit = 0.f;
+  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.cl = cl; a.eps = 0.f; a.limit = 0.f; a.alpha = 0.f;
   a.status = device_status_ptr();
   a.part_ml = static_cast<const float*>(part_ml);
   a.part_acc = static_cast<const float*>(part_acc);

@@ -6,6 +6,9 @@
 //
 // Cache layout: k/v [blocks, hkv, page, D]; fp8 caches carry one fp32 scale per (token, kv head).
 // A row attends to cache positions 0 .. positions[row] inclusive (its own K/V were just appended).
+// Block-sparse form: with a selection list sel [rows, hkv, sel_k] (ascending block ids of sel_block tokens, -1 padded
+// at the end, the block that holds the row's own position last) every (row, kv head) attends only to the tokens of
+// its listed blocks; the kernel walks the concatenation of those blocks as one virtual sequence.
 // (operator family: src/kernels/full_attn.cu:163,370 row kernel + combine, src/kernels/glm4_attn.cu:150,278)
 #include <math.h>
 
@@ -32,6 +35,8 @@ struct AttnDecodeParams {
   float scale;            // softmax scale (1/sqrt(D) times any rope mscale^2)
   int window;             // > 0: attend only to the last `window` positions (sliding window); 0 = full
   const float* sink;      // optional [hq]: one more softmax column per head with this logit and no value
+  const int32_t* sel;     // optional [rows, hkv, sel_k] block selection (see the header); null = dense
+  int sel_k, sel_block;
 };
 
 // Normalisation with the optional sink column: out = acc / (l + exp(sink - m)), computed against max(m, sink).
@@ -59,7 +64,15 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_kernel(AttnDecodeP
   const int kvh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = p.row_req[row];
-  const int len = p.positions[row] + 1;
+  const int pos = p.positions[row];
+  int len = pos + 1;
+  const int32_t* sl = nullptr;
+  if (p.sel != nullptr) {
+    sl = p.sel + (static_cast<size_t>(row) * p.hkv + kvh) * p.sel_k;
+    int n = 0;
+    for (int j = 0; j < p.sel_k; ++j) n += sl[j] >= 0 ? 1 : 0;
+    len = n > 0 ? (n - 1) * p.sel_block + pos % p.sel_block + 1 : 0;      // every listed block is full but the last
+  }
   const int first = (p.window > 0 && len > p.window) ? len - p.window : 0;
   const int span = len - first;
   int per = (span + p.splits - 1) / p.splits;
@@ -86,7 +99,8 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_kernel(AttnDecodeP
   for (int t0 = t_begin + warp * 32; t0 < t_end; t0 += kDecWarps * 32) {
     const int t = t0 + lane;
     const bool valid = t < t_end;
-    const int tc = valid ? t : t_end - 1;
+    int tc = valid ? t : t_end - 1;
+    if (sl != nullptr) tc = min(sl[tc / p.sel_block] * p.sel_block + tc % p.sel_block, pos);   // virtual -> cache position
     const size_t tok = (static_cast<size_t>(bt[tc / p.page]) * p.hkv + kvh) * p.page + tc % p.page;
     float s[G];
 #pragma unroll
@@ -262,8 +276,11 @@ static int attn_decode_impl(const void* q, int64_t q_stride, const void* k_cache
                             const void* k_scale, const void* v_scale, const void* block_table,
                             const void* row_req, const void* positions, void* part_ml, void* part_acc, void* out,
                             int rows, int hq, int hkv, int d, int page, int max_blocks, int splits, int kv_fp8,
-                            float scale, int window, const void* sink, cudaStream_t st) {
+                            float scale, int window, const void* sink, const void* sel, int sel_k, int sel_block,
+                            cudaStream_t st) {
   DGPP_REQUIRE(hkv > 0 && hq % hkv == 0, "attn_decode: hq %d not a multiple of hkv %d", hq, hkv);
+  DGPP_REQUIRE(sel == nullptr || (sel_k >= 1 && sel_block >= 1 && window == 0),
+               "attn_decode: a block selection needs sel_k >= 1, sel_block >= 1 and no sliding window");
   DGPP_REQUIRE(splits >= 1, "attn_decode: splits must be >= 1");
   DGPP_REQUIRE(splits == 1 || (part_ml && part_acc), "attn_decode: scratch required when splits > 1");
   if (rows == 0) return 0;
@@ -283,6 +300,8 @@ static int attn_decode_impl(const void* q, int64_t q_stride, const void* k_cache
   p.rows = rows; p.hq = hq; p.hkv = hkv; p.page = page; p.max_blocks = max_blocks; p.splits = splits;
   p.kv_fp8 = kv_fp8; p.scale = scale; p.window = window;
   p.sink = static_cast<const float*>(sink);
+  p.sel = static_cast<const int32_t*>(sel);
+  p.sel_k = sel_k; p.sel_block = sel_block;
   const int g = hq / hkv;
 #define DGPP_DEC_CASE(DD, GG) \
   if (d == DD && g == GG) return launch_decode<DD, GG>(p, st);
@@ -300,7 +319,21 @@ DGPP_API int dgpp_attn_decode(const void* q, int64_t q_stride, const void* k_cac
                               int rows, int hq, int hkv, int d, int page, int max_blocks, int splits, int kv_fp8,
                               float scale, int window, cudaStream_t st) {
   return attn_decode_impl(q, q_stride, k_cache, v_cache, k_scale, v_scale, block_table, row_req, positions, part_ml,
-                          part_acc, out, rows, hq, hkv, d, page, max_blocks, splits, kv_fp8, scale, window, nullptr, st);
+                          part_acc, out, rows, hq, hkv, d, page, max_blocks, splits, kv_fp8, scale, window, nullptr, nullptr, 0, 0, st);
+}
+
+// Block-sparse attention: sel [rows, hkv, sel_k] int32 as described at the top of this file.
+// (reference counterpart: src/kernels/minimax.hpp minimax_attn_partial + the partial merge.)
+DGPP_API int dgpp_attn_decode_sparse(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                                     const void* k_scale, const void* v_scale, const void* block_table,
+                                     const void* row_req, const void* positions, void* part_ml, void* part_acc,
+                                     void* out, int rows, int hq, int hkv, int d, int page, int max_blocks, int splits,
+                                     int kv_fp8, float scale, const void* sel, int sel_k, int sel_block,
+                                     cudaStream_t st) {
+  DGPP_REQUIRE(sel != nullptr, "attn_decode_sparse: no selection list");
+  return attn_decode_impl(q, q_stride, k_cache, v_cache, k_scale, v_scale, block_table, row_req, positions, part_ml,
+                          part_acc, out, rows, hq, hkv, d, page, max_blocks, splits, kv_fp8, scale, 0, nullptr, sel,
+                          sel_k, sel_block, st);
 }
 
 // Sliding-window attention with per-head sink logits (sink: [hq] fp32, the logit of a value-less softmax column).
@@ -311,7 +344,7 @@ DGPP_API int dgpp_attn_decode_sink(const void* q, int64_t q_stride, const void* 
                                    int rows, int hq, int hkv, int d, int page, int max_blocks, int splits, int kv_fp8,
                                    float scale, int window, const void* sink, cudaStream_t st) {
   return attn_decode_impl(q, q_stride, k_cache, v_cache, k_scale, v_scale, block_table, row_req, positions, part_ml,
-                          part_acc, out, rows, hq, hkv, d, page, max_blocks, splits, kv_fp8, scale, window, sink, st);
+                          part_acc, out, rows, hq, hkv, d, page, max_blocks, splits, kv_fp8, scale, window, sink, nullptr, 0, 0, st);
 }
 
 // ------------------------------------------------------------------------------------------------------------

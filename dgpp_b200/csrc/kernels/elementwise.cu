@@ -98,8 +98,9 @@ rmsnorm_kernel(const bf16* __restrict__ resid, const bf16* __restrict__ delta, c
 }
 
 // gate_up: [rows, 2*inter] (gate then up); out: [rows, inter].  limit > 0 clamps gate above and up both sides.
+// alpha > 0 selects the scaled-sigmoid form  gate * sigmoid(alpha * gate) * (up + 1)  (alpha = 0: silu(gate) * up).
 __global__ void __launch_bounds__(kRowThreads)
-swiglu_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter, float limit) {
+swiglu_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter, float limit, float alpha) {
   pdl_wait();
   const size_t row = blockIdx.y;
   const bf16* g = gate_up + row * 2 * inter;
@@ -117,7 +118,13 @@ swiglu_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inte
       gv = fminf(gv, limit);
       uv = fminf(fmaxf(uv, -limit), limit);
     }
-    float s = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-gv))));
+    float s;
+    if (alpha > 0.f) {
+      s = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-alpha * gv))));
+      uv += 1.f;
+    } else {
+      s = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-gv))));
+    }
     o.h[j] = f32_to_bf16(s * uv);
   }
   reinterpret_cast<uint4*>(out + row * inter)[i] = o.u;
@@ -323,12 +330,13 @@ DGPP_API int dgpp_rmsnorm(const void* resid, const void* delta, const void* w, v
   return 0;
 }
 
-DGPP_API int dgpp_swiglu(const void* gate_up, void* out, int rows, int inter, float limit, cudaStream_t st) {
+DGPP_API int dgpp_swiglu(const void* gate_up, void* out, int rows, int inter, float limit, float alpha,
+                         cudaStream_t st) {
   DGPP_REQUIRE(inter % 8 == 0, "swiglu: inter %d must be a multiple of 8", inter);
   if (rows == 0) return 0;
   dim3 grid(dgpp_ceil_div(inter / 8, kRowThreads), rows);
   swiglu_kernel<<<grid, kRowThreads, 0, st>>>(static_cast<const bf16*>(gate_up), static_cast<bf16*>(out), inter,
-                                             limit);
+                                             limit, alpha);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -499,7 +499,7 @@ struct QuantArgs {
   uint8_t* sf;
   float* g;
   int T, T_pad, K, R, bn;
-  float eps, limit;
+  float eps, limit, alpha;     // alpha > 0: gate * sigmoid(alpha * gate) * (up + 1) in the swiglu mode
   int one_plus_w;
 };
 
@@ -579,7 +579,13 @@ __global__ void __launch_bounds__(256) fused_act_quant_kernel(QuantArgs a) {
         for (int j = 0; j < 8; ++j) {
           float gv = bf16_to_f32(x.h[j]), uv = bf16_to_f32(u.h[j]);
           if (a.limit > 0.f) { gv = fminf(gv, a.limit); uv = fminf(fmaxf(uv, -a.limit), a.limit); }
-          const float sl = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-gv))));
+          float sl;
+          if (a.alpha > 0.f) {
+            sl = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-a.alpha * gv))));
+            uv += 1.f;
+          } else {
+            sl = bf16_to_f32(f32_to_bf16(gv / (1.f + __expf(-gv))));
+          }
           x.h[j] = f32_to_bf16(sl * uv);
         }
       }
@@ -691,7 +697,7 @@ using namespace dgpp;
 // R * (T_pad / bn) * (K / 256) * 4 * atoms * 512 bytes with atoms = (bn > 128 ? 2 : 1).
 DGPP_API int dgpp_act_quant_nvfp4(int mode, const void* in, int64_t in_stride, const void* delta, const void* w,
                                   void* resid_out, void* x_out, void* q, void* sf, void* g, int T, int T_pad, int K,
-                                  int R, int bn, float eps, float limit, int one_plus_w, cudaStream_t st) {
+                                  int R, int bn, float eps, float limit, float alpha, int one_plus_w, cudaStream_t st) {
   DGPP_REQUIRE(K % 256 == 0, "act_quant: K %d must be a multiple of 256", K);
   DGPP_REQUIRE(R >= 1 && R <= 4, "act_quant: R %d outside 1..4", R);
   DGPP_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "act_quant: bad token tile %d", bn);
@@ -708,7 +714,7 @@ DGPP_API int dgpp_act_quant_nvfp4(int mode, const void* in, int64_t in_stride, c
   a.q = static_cast<uint8_t*>(q);
   a.sf = static_cast<uint8_t*>(sf);
   a.g = static_cast<float*>(g);
-  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.eps = eps; a.limit = limit; a.one_plus_w = one_plus_w;
+  a.T = T; a.T_pad = T_pad; a.K = K; a.R = R; a.bn = bn; a.eps = eps; a.limit = limit; a.alpha = alpha; a.one_plus_w = one_plus_w;
   const size_t smem = static_cast<size_t>(K) * 2;
   static bool attr = false;
   if (!attr) {

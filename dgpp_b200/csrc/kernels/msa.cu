@@ -1,0 +1,253 @@
+// Block-sparse attention index (the selection half of block-sparse GQA; the attention half is the block-selection
+// form of the paged decode kernel).  Every token stores one index key of DI values; every kv head owns one index
+// query head.  A (row, index head) scores each block of `sel_block` tokens by the largest query-key product among
+// the block's visible tokens, always keeps the block that holds the row's own position, and keeps the `topk` best
+// blocks in all (ties go to the lower block id).  The list comes out in ascending block order, -1 padded.
+//
+//   msa_index_prep    per-head RMSNorm (optionally 1 + w) and partial rotary embedding of the index queries and the
+//                     index key of every row, in place; the key is appended to the paged index cache
+//                     [blocks, page, DI] bf16 (same block table as the KV cache)
+//   msa_index_select  scores + selection, one CTA per (index head, row)
+// (reference counterparts: src/kernels/minimax.hpp minimax_norm_rope, minimax_index_append, minimax_index_score,
+//  minimax_index_select; src/models/minimax/reference.cpp select_blocks is the arithmetic contract.)
+#include <math.h>
+
+#include "common/common.h"
+#include "common/dtypes.cuh"
+#include "common/ptx.cuh"
+
+namespace dgpp {
+
+struct MsaPrepParams {
+  bf16* iqk;                   // [rows, (ih + 1) * DI]: index query heads, then the index key
+  const int32_t* positions;    // [rows]
+  const int32_t* row_req;      // [rows]
+  const int32_t* block_table;  // [requests, max_blocks]
+  const float* inv_freq;       // [rot_dim / 2]
+  const bf16* q_norm_w;        // [DI] or null
+  const bf16* k_norm_w;        // [DI] or null
+  bf16* index_cache;           // [blocks, page, DI]
+  int rows, ih, rot_dim, page, max_blocks, one_plus_w;
+  float eps;
+};
+
+// One warp per (row, head); element j of lane l is dim l + 32 j.
+template <int DI>
+__global__ void __launch_bounds__(128) msa_index_prep_kernel(MsaPrepParams p) {
+  pdl_wait();
+  constexpr int PER = DI / 32;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int heads = p.ih + 1;
+  if (warp >= p.rows * heads) return;
+  const int row = warp / heads, head = warp % heads;
+  const bool is_key = head == p.ih;
+  bf16* src = p.iqk + (static_cast<size_t>(row) * heads + head) * DI;
+  float v[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) v[j] = bf16_to_f32(src[lane + 32 * j]);
+  const bf16* nw = is_key ? p.k_norm_w : p.q_norm_w;
+  if (nw != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) ss += v[j] * v[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss / DI + p.eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      float g = bf16_to_f32(nw[lane + 32 * j]);
+      if (p.one_plus_w) g += 1.f;
+      v[j] = bf16_to_f32(f32_to_bf16(bf16_to_f32(f32_to_bf16(v[j] * rstd)) * g));
+    }
+  }
+  const int pos = p.positions[row];
+  const int half = p.rot_dim / 2;
+  float r[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int a = lane + 32 * j;
+    const int pd = a < half ? a + half : (a < p.rot_dim ? a - half : a);      // rotate-half partner
+    float partner = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < PER; ++jj) {
+      const float cand = __shfl_sync(0xffffffffu, v[jj], pd & 31);
+      if ((pd >> 5) == jj) partner = cand;
+    }
+    if (a < p.rot_dim) {
+      float sn, cs;
+      sincosf(static_cast<float>(pos) * p.inv_freq[a < half ? a : a - half], &sn, &cs);
+      r[j] = a < half ? v[j] * cs - partner * sn : v[j] * cs + partner * sn;
+    } else {
+      r[j] = v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) src[lane + 32 * j] = f32_to_bf16(r[j]);
+  if (!is_key) return;
+  const int blk = p.block_table[static_cast<size_t>(p.row_req[row]) * p.max_blocks + pos / p.page];
+  bf16* dst = p.index_cache + (static_cast<size_t>(blk) * p.page + pos % p.page) * DI;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) dst[lane + 32 * j] = f32_to_bf16(r[j]);
+}
+
+struct MsaSelectParams {
+  const bf16* iqk;             // [rows, iqk_stride]: index query head h at column h * DI
+  int64_t iqk_stride;
+  const bf16* index_cache;     // [blocks, page, DI]
+  const int32_t* block_table;
+  const int32_t* row_req;
+  const int32_t* positions;
+  int32_t* sel;                // [rows, ih, topk]
+  float* scores;               // optional [rows, ih, max_sel] block scores as used for the choice (unwritten past the row's blocks)
+  int rows, ih, page, max_blocks, sel_block, topk, max_sel;
+};
+
+constexpr int kMsaThreads = 256;
+constexpr int kMsaMaxTopk = 64;
+
+template <int DI>
+__global__ void __launch_bounds__(kMsaThreads) msa_index_select_kernel(MsaSelectParams p) {
+  extern __shared__ float sc[];                  // [max_sel] block scores
+  __shared__ float q_s[DI];
+  __shared__ float wv[kMsaThreads / 32];
+  __shared__ int wi[kMsaThreads / 32];
+  __shared__ int chosen[kMsaMaxTopk];
+  pdl_wait();
+  const int h = blockIdx.x, row = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = p.positions[row];
+  const int nblk = min(pos / p.sel_block + 1, p.max_sel);
+  for (int d = threadIdx.x; d < DI; d += kMsaThreads)
+    q_s[d] = bf16_to_f32(p.iqk[static_cast<size_t>(row) * p.iqk_stride + h * DI + d]);
+  __syncthreads();
+  const int32_t* bt = p.block_table + static_cast<size_t>(p.row_req[row]) * p.max_blocks;
+  for (int b = warp; b < nblk; b += kMsaThreads / 32) {
+    float mx = -INFINITY;
+    const int t_end = min((b + 1) * p.sel_block, pos + 1);
+    for (int t = b * p.sel_block + lane; t < t_end; t += 32) {
+      const uint4* kr = reinterpret_cast<const uint4*>(
+          p.index_cache + (static_cast<size_t>(bt[t / p.page]) * p.page + t % p.page) * DI);
+      float s = 0.f;
+#pragma unroll 4
+      for (int c = 0; c < DI / 8; ++c) {
+        Pack16 kb;
+        kb.u = kr[c];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s = fmaf(q_s[c * 8 + j], bf16_to_f32(kb.h[j]), s);
+      }
+      mx = fmaxf(mx, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) sc[b] = mx;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && nblk > 0) sc[nblk - 1] = INFINITY;       // the row's own block is always kept
+  __syncthreads();
+  if (p.scores != nullptr)
+    for (int b = threadIdx.x; b < nblk; b += kMsaThreads)
+      p.scores[(static_cast<size_t>(row) * p.ih + h) * p.max_sel + b] = sc[b];
+  const int keep = min(p.topk, nblk);
+  for (int r = 0; r < keep; ++r) {
+    // block-wide argmax over the scores not yet taken (taken entries hold NaN-free -inf and are skipped)
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int b = threadIdx.x; b < nblk; b += kMsaThreads) {
+      const float s = sc[b];
+      if (s > -INFINITY && (s > bv || (s == bv && b < bi) || bi == 0x7fffffff)) { bv = s; bi = b; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { wv[warp] = bv; wi[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float fv = wv[0];
+      int fi = wi[0];
+      for (int w = 1; w < kMsaThreads / 32; ++w) {
+        if (wi[w] != 0x7fffffff && (fi == 0x7fffffff || wv[w] > fv || (wv[w] == fv && wi[w] < fi))) { fv = wv[w]; fi = wi[w]; }
+      }
+      chosen[r] = fi;
+      if (fi != 0x7fffffff) sc[fi] = -INFINITY;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    // ascending order (a handful of entries: insertion sort), then the -1 padding
+    int n = 0;
+    for (int r = 0; r < keep; ++r)
+      if (chosen[r] != 0x7fffffff) chosen[n++] = chosen[r];
+    for (int i = 1; i < n; ++i) {
+      const int v = chosen[i];
+      int j = i - 1;
+      while (j >= 0 && chosen[j] > v) { chosen[j + 1] = chosen[j]; --j; }
+      chosen[j + 1] = v;
+    }
+    int32_t* out = p.sel + (static_cast<size_t>(row) * p.ih + h) * p.topk;
+    for (int r = 0; r < p.topk; ++r) out[r] = r < n ? chosen[r] : -1;
+  }
+}
+
+}  // namespace dgpp
+
+using namespace dgpp;
+
+DGPP_API int dgpp_msa_index_prep(void* iqk, const void* positions, const void* row_req, const void* block_table,
+                                 const void* inv_freq, const void* q_norm_w, const void* k_norm_w, void* index_cache,
+                                 int rows, int ih, int di, int rot_dim, int page, int max_blocks, float eps,
+                                 int one_plus_w, cudaStream_t st) {
+  DGPP_REQUIRE(di == 64 || di == 128, "msa_index_prep: index width %d not in {64, 128}", di);
+  DGPP_REQUIRE(rot_dim >= 2 && rot_dim <= di && rot_dim % 2 == 0, "msa_index_prep: bad rotary width %d", rot_dim);
+  DGPP_REQUIRE(ih >= 1 && page >= 1, "msa_index_prep: bad geometry");
+  if (rows == 0) return 0;
+  MsaPrepParams p;
+  p.iqk = static_cast<bf16*>(iqk);
+  p.positions = static_cast<const int32_t*>(positions);
+  p.row_req = static_cast<const int32_t*>(row_req);
+  p.block_table = static_cast<const int32_t*>(block_table);
+  p.inv_freq = static_cast<const float*>(inv_freq);
+  p.q_norm_w = static_cast<const bf16*>(q_norm_w);
+  p.k_norm_w = static_cast<const bf16*>(k_norm_w);
+  p.index_cache = static_cast<bf16*>(index_cache);
+  p.rows = rows; p.ih = ih; p.rot_dim = rot_dim; p.page = page; p.max_blocks = max_blocks; p.one_plus_w = one_plus_w;
+  p.eps = eps;
+  const int warps = rows * (ih + 1);
+  const int grid = dgpp_ceil_div(warps, 4);
+  if (di == 64) msa_index_prep_kernel<64><<<grid, 128, 0, st>>>(p);
+  else msa_index_prep_kernel<128><<<grid, 128, 0, st>>>(p);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+DGPP_API int dgpp_msa_index_select(const void* iqk, int64_t iqk_stride, const void* index_cache,
+                                   const void* block_table, const void* row_req, const void* positions, void* sel,
+                                   void* scores, int rows, int ih, int di, int page, int max_blocks, int sel_block,
+                                   int topk, int max_sel, cudaStream_t st) {
+  DGPP_REQUIRE(di == 64 || di == 128, "msa_index_select: index width %d not in {64, 128}", di);
+  DGPP_REQUIRE(topk >= 1 && topk <= kMsaMaxTopk, "msa_index_select: topk %d outside 1..%d", topk, kMsaMaxTopk);
+  DGPP_REQUIRE(sel_block >= 1 && max_sel >= 1 && max_sel <= 8192, "msa_index_select: %d blocks of %d tokens unsupported",
+               max_sel, sel_block);
+  DGPP_REQUIRE(ih >= 1 && ih <= 65535 && rows <= 65535, "msa_index_select: grid out of range");
+  if (rows == 0) return 0;
+  MsaSelectParams p;
+  p.iqk = static_cast<const bf16*>(iqk);
+  p.iqk_stride = iqk_stride;
+  p.index_cache = static_cast<const bf16*>(index_cache);
+  p.block_table = static_cast<const int32_t*>(block_table);
+  p.row_req = static_cast<const int32_t*>(row_req);
+  p.positions = static_cast<const int32_t*>(positions);
+  p.sel = static_cast<int32_t*>(sel);
+  p.scores = static_cast<float*>(scores);
+  p.rows = rows; p.ih = ih; p.page = page; p.max_blocks = max_blocks; p.sel_block = sel_block; p.topk = topk;
+  p.max_sel = max_sel;
+  const size_t smem = static_cast<size_t>(max_sel) * sizeof(float);
+  dim3 grid(ih, rows);
+  if (di == 64) msa_index_select_kernel<64><<<grid, kMsaThreads, smem, st>>>(p);
+  else msa_index_select_kernel<128><<<grid, kMsaThreads, smem, st>>>(p);
+  DGPP_CUDA_OK(cudaGetLastError());
+  return 0;
+}

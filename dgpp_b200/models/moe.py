@@ -38,6 +38,7 @@ class MoEConfig:
     norm_topk_prob: bool = True
     routed_scaling: float = 1.0
     swiglu_limit: float = 0.0
+    swiglu_alpha: float = 0.0      # > 0: gate * sigmoid(alpha * gate) * (up + 1) instead of silu(gate) * up
 
 
 @dataclass
@@ -174,11 +175,11 @@ def moe_reference(x: torch.Tensor, w: MoEWeights, ids=None, wts=None) -> torch.T
         rows = (ids == e).any(-1).nonzero().flatten()
         xe = x[rows]
         h = ref.linear(xe, w.experts_gu[e - e0])
-        y = ref.linear(ref.swiglu(h, c.swiglu_limit), w.experts_down[e - e0])
+        y = ref.linear(ref.swiglu(h, c.swiglu_limit, c.swiglu_alpha), w.experts_down[e - e0])
         we = (wts * (ids == e)).sum(-1)[rows]
         acc[rows] += we.unsqueeze(-1) * y.float()
     if w.shared_gu is not None:
-        acc += ref.linear(ref.swiglu(ref.linear(x, w.shared_gu), c.swiglu_limit), w.shared_down).float()
+        acc += ref.linear(ref.swiglu(ref.linear(x, w.shared_gu), c.swiglu_limit, c.swiglu_alpha), w.shared_down).float()
     return ref.act(acc)
 
 
@@ -255,13 +256,13 @@ class MoEBlock:
         ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, self.h, rows, 2 * c.moe_ffn, c.hidden, self.stack_experts,
                              self.group_list, group_b=False)
         xm = ops.act_quant_nvfp4(self.h.view(self.nslots * self.bn, 2 * c.moe_ffn), self.terms, out=self.qa_mid,
-                                 mode="swiglu", limit=c.swiglu_limit, group_list=self.group_list, group_rows=rows)
+                                 mode="swiglu", limit=c.swiglu_limit, alpha=c.swiglu_alpha, group_list=self.group_list, group_rows=rows)
         ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, self.y, rows, c.hidden, c.moe_ffn, self.stack_experts,
                              self.group_list, group_b=True)
         sh = self.y[self.sh_slot] if self.sh_slot >= 0 else None          # [bn, H]: the shared expert's rows
         if self.shared is not None:
             ops.gemm_fp4(xa, w.shared_gu_k, out=self.sh_gu[:rows])
-            xs = ops.act_quant_nvfp4(self.sh_gu[:rows], self.terms, out=self.qa_sh, mode="swiglu", limit=c.swiglu_limit)
+            xs = ops.act_quant_nvfp4(self.sh_gu[:rows], self.terms, out=self.qa_sh, mode="swiglu", limit=c.swiglu_limit, alpha=c.swiglu_alpha)
             ops.gemm_fp4(xs, w.shared_down_k, out=self.shared[:rows])
             sh = self.shared
         if push_comm:
@@ -291,13 +292,13 @@ class MoEBlock:
         xa = ops.act_quant_nvfp4(xs, R, out=ws["qa_x"], group_list=tiles, group_rows=bn)
         ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, h, bn, 2 * c.moe_ffn, c.hidden, self.local_experts, tiles,
                              group_b=True)
-        xm = ops.act_quant_nvfp4(h.view(rows, 2 * c.moe_ffn), R, out=ws["qa_mid"], mode="swiglu", limit=c.swiglu_limit,
+        xm = ops.act_quant_nvfp4(h.view(rows, 2 * c.moe_ffn), R, out=ws["qa_mid"], mode="swiglu", limit=c.swiglu_limit, alpha=c.swiglu_alpha,
                                  group_list=tiles, group_rows=bn)
         ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, y, bn, c.hidden, c.moe_ffn, self.local_experts, tiles,
                              group_b=True)
         sh = None
         if w.shared_gu is not None:
-            sh = ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu), limit=c.swiglu_limit), w.shared_down)
+            sh = ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu), limit=c.swiglu_limit, alpha=c.swiglu_alpha), w.shared_down)
         out = torch.empty(T, c.hidden, dtype=BF, device=xn.device)
         return ops.moe_combine_rows(y.view(rows, c.hidden), sh, pair_row, wts, out)
 
@@ -314,10 +315,10 @@ class MoEBlock:
             rows = hit.any(-1).nonzero().flatten()
             xe = xn.index_select(0, rows).contiguous()
             h = ops.linear(xe, w.experts_gu[e - self.e0])
-            y = ops.linear(ops.swiglu(h, limit=c.swiglu_limit), w.experts_down[e - self.e0])
+            y = ops.linear(ops.swiglu(h, limit=c.swiglu_limit, alpha=c.swiglu_alpha), w.experts_down[e - self.e0])
             acc.index_add_(0, rows, (wts * hit).sum(-1)[rows].unsqueeze(-1) * y.float())
         if w.shared_gu is not None:
-            acc += ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu), limit=c.swiglu_limit), w.shared_down).float()
+            acc += ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu), limit=c.swiglu_limit, alpha=c.swiglu_alpha), w.shared_down).float()
         return acc.to(BF)
 
 

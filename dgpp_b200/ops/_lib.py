@@ -25,7 +25,7 @@ _SIGNATURES = {
     "dgpp_status_clear": [],
     "dgpp_embed_gather": [P, P, P, I, I, I, P],
     "dgpp_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
-    "dgpp_swiglu": [P, P, I, I, F, P],
+    "dgpp_swiglu": [P, P, I, I, F, F, P],
     "dgpp_argmax": [P, I, L, I, I, I, P, P, P],
     "dgpp_copy_bytes": [P, P, L, P],
     "dgpp_add_bf16": [P, P, P, L, P],
@@ -33,13 +33,16 @@ _SIGNATURES = {
     "dgpp_rope_kv_write": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
     "dgpp_attn_decode": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_decode_sink": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
+    "dgpp_attn_decode_sparse": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, P],
+    "dgpp_msa_index_prep": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "dgpp_msa_index_select": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "dgpp_attn_decode_tc": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_prefill_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_prefill_tc256": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_decode_advance": [P, P, P, P, P, I, I, P],
-    "dgpp_act_quant_nvfp4": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+    "dgpp_act_quant_nvfp4": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, F, I, P],
     "dgpp_attn_combine_quant": [P, P, I, I, I, P, P, P, P, I, I, I, I, I, P],
-    "dgpp_act_quant_nvfp4_cluster": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P, P, I, P],
+    "dgpp_act_quant_nvfp4_cluster": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, I, P, P, I, P],
     "dgpp_gemm_fp4_set_prefetch": [P, L],
     "dgpp_gemm_fp4_set_preload": [I],
     "dgpp_vis_patchify": [P, P, I, I, I, I, P, P, P],

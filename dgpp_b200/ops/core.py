@@ -60,13 +60,13 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, delta: Optional
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, limit: float = 0.0) -> torch.Tensor:
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
     _chk(gate_up, torch.bfloat16, "gate_up")
     rows, two_i = gate_up.shape
     inter = two_i // 2
     if out is None:
         out = torch.empty(rows, inter, dtype=torch.bfloat16, device=gate_up.device)
-    call("dgpp_swiglu", ptr(gate_up), ptr(out), rows, inter, float(limit), stream_ptr())
+    call("dgpp_swiglu", ptr(gate_up), ptr(out), rows, inter, float(limit), float(alpha), stream_ptr())
     return out
 
 
@@ -244,7 +244,7 @@ class QuantAct:
 def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = None, bn: Optional[int] = None,
                     mode: str = "plain", delta=None, norm_w=None, resid_out=None, x_out=None, eps: float = 1e-6,
                     limit: float = 0.0, one_plus_w: bool = False, fold_comm=None, group_list=None,
-                    group_rows: int = 0) -> QuantAct:
+                    group_rows: int = 0, alpha: float = 0.0) -> QuantAct:
     """Quantise rows to residual NVFP4 terms, optionally fused with the producing operator:
     mode "plain": x [T, K];  "swiglu": x = [gate | up] [T, 2K];  "rmsnorm": x = residual [T, K] (+ delta), norm_w.
     fold_comm (rmsnorm mode): native peer-communicator handle; the delta is then the fixed-order fold of the tiles
@@ -268,12 +268,13 @@ def act_quant_nvfp4(x: torch.Tensor, terms: int = 3, out: Optional[QuantAct] = N
     if cl:
         call("dgpp_act_quant_nvfp4_cluster", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out),
              ptr(x_out), ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, cl,
-             float(eps), float(limit), int(one_plus_w), fold_comm, ptr(group_list), group_rows, stream_ptr())
+             float(eps), float(limit), float(alpha), int(one_plus_w), fold_comm, ptr(group_list), group_rows,
+             stream_ptr())
     else:
         assert not fold_comm and group_list is None, "the all-reduce fold needs the cluster quantiser"
         call("dgpp_act_quant_nvfp4", m, ptr(x), x.stride(0), ptr(delta), ptr(norm_w), ptr(resid_out), ptr(x_out),
              ptr(out.q), ptr(out.sf), ptr(out.g), rows, out.rows_pad, k, out.terms, out.bn, float(eps),
-             float(limit), int(one_plus_w), stream_ptr())
+             float(limit), float(alpha), int(one_plus_w), stream_ptr())
     return out
 
 
@@ -442,9 +443,12 @@ def rope_kv_write(qkv, positions, row_req, block_table, inv_freq, cache, hq: int
 
 
 def attn_decode(q, q_stride: int, cache, block_table, row_req, positions, hq: int, hkv: int, d: int,
-                scale: float, splits: int = 1, scratch=None, out=None, window: int = 0, sink=None):
+                scale: float, splits: int = 1, scratch=None, out=None, window: int = 0, sink=None, sel=None,
+                sel_block: int = 0):
     """CUDA-core decode attention over the paged cache (bf16 or FP8).  window > 0: sliding window; sink: optional
-    [hq] fp32 logits of a value-less softmax column (sliding-window + sink attention families)."""
+    [hq] fp32 logits of a value-less softmax column (sliding-window + sink attention families); sel: optional
+    [rows, hkv, k] int32 ascending block ids of `sel_block` tokens (-1 padded, the row's own block last): every
+    (row, kv head) then attends only to its listed blocks."""
     rows = positions.numel()
     if out is None:
         out = torch.empty(rows, hq * d, dtype=torch.bfloat16, device=positions.device)
@@ -454,6 +458,14 @@ def attn_decode(q, q_stride: int, cache, block_table, row_req, positions, hq: in
             scratch = (torch.empty(rows * hq * splits * 2, dtype=torch.float32, device=out.device),
                        torch.empty(rows * hq * splits * d, dtype=torch.float32, device=out.device))
         ml, acc = scratch
+    if sel is not None:
+        _chk(sel, torch.int32, "sel")
+        assert sink is None and window == 0 and sel.shape[0] == rows and sel.shape[1] == hkv and sel_block > 0
+        call("dgpp_attn_decode_sparse", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale),
+             ptr(cache.v_scale), ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq,
+             hkv, d, cache.page, block_table.shape[1], splits, int(cache.fp8), float(scale), ptr(sel), sel.shape[2],
+             sel_block, stream_ptr())
+        return out
     if sink is not None:
         _chk(sink, torch.float32, "sink")
         assert sink.numel() == hq
@@ -465,6 +477,32 @@ def attn_decode(q, q_stride: int, cache, block_table, row_req, positions, hq: in
     call("dgpp_attn_decode", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale),
          ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq, hkv, d, cache.page,
          block_table.shape[1], splits, int(cache.fp8), float(scale), window, stream_ptr())
+    return out
+
+
+def msa_index_prep(iqk, positions, row_req, block_table, inv_freq, q_norm_w, k_norm_w, index_cache, ih: int, di: int,
+                   rot_dim: int, eps: float = 1e-6, one_plus_w: bool = False) -> None:
+    """In place on iqk [rows, (ih + 1) * di] bf16 (index query heads, then the index key of the row): per-head RMSNorm
+    and rotary embedding on the first rot_dim dims; the key is appended to index_cache [blocks, page, di] bf16."""
+    _chk(iqk, torch.bfloat16, "iqk")
+    _chk(index_cache, torch.bfloat16, "index_cache")
+    assert iqk.shape[1] == (ih + 1) * di and iqk.is_contiguous() and index_cache.shape[2] == di
+    call("dgpp_msa_index_prep", ptr(iqk), ptr(positions), ptr(row_req), ptr(block_table), ptr(inv_freq), ptr(q_norm_w),
+         ptr(k_norm_w), ptr(index_cache), iqk.shape[0], ih, di, rot_dim, index_cache.shape[1], block_table.shape[1],
+         float(eps), int(one_plus_w), stream_ptr())
+
+
+def msa_index_select(iqk, index_cache, block_table, row_req, positions, ih: int, di: int, sel_block: int, topk: int,
+                     max_sel: int, out=None, scores=None):
+    """Block selection of block-sparse attention -> int32 [rows, ih, topk]: ascending ids of the `topk` blocks (of
+    sel_block tokens) with the largest per-block maximum of <index query, index key> over the visible tokens, the
+    row's own block always among them; -1 padded.  scores: optional fp32 [rows, ih, max_sel] out."""
+    rows = positions.numel()
+    if out is None:
+        out = torch.empty(rows, ih, topk, dtype=torch.int32, device=positions.device)
+    call("dgpp_msa_index_select", ptr(iqk), iqk.stride(0), ptr(index_cache), ptr(block_table), ptr(row_req),
+         ptr(positions), ptr(out), ptr(scores), rows, ih, di, index_cache.shape[1], block_table.shape[1], sel_block,
+         topk, max_sel, stream_ptr())
     return out
 
 

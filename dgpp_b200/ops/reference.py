@@ -53,12 +53,16 @@ def rmsnorm(x, w, eps=1e-6, delta=None, one_plus_w=False):
     return act(_r(xf * rstd) * g), act(xf)
 
 
-def swiglu(gate_up, limit: float = 0.0):
+def swiglu(gate_up, limit: float = 0.0, alpha: float = 0.0):
+    """alpha = 0: silu(gate) * up; alpha > 0: gate * sigmoid(alpha * gate) * (up + 1).  limit > 0 clamps gate above and
+    up on both sides first."""
     inter = gate_up.shape[-1] // 2
     g, u = gate_up[..., :inter].float(), gate_up[..., inter:].float()
     if limit > 0:
         g = g.clamp(max=limit)
         u = u.clamp(-limit, limit)
+    if alpha > 0:
+        return act(_r(g * torch.sigmoid(alpha * g)) * (u + 1.0))
     return act(_r(g * torch.sigmoid(g)) * u)
 
 

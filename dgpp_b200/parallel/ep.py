@@ -127,13 +127,13 @@ class EpMoE:
         ops.gemm_fp4_grouped(xa, w.gu_q, w.gu_sf, w.gu_alpha, self.h, self.bn, 2 * c.moe_ffn, H, self.local, self.tiles,
                              group_b=True)
         xm = ops.act_quant_nvfp4(self.h.view(rows, 2 * c.moe_ffn), self.terms, out=self.qa_mid, mode="swiglu",
-                                 limit=c.swiglu_limit, group_list=self.tiles, group_rows=self.bn)
+                                 limit=c.swiglu_limit, alpha=c.swiglu_alpha, group_list=self.tiles, group_rows=self.bn)
         ops.gemm_fp4_grouped(xm, w.down_q, w.down_sf, w.down_alpha, self.y, self.bn, H, c.moe_ffn, self.local, self.tiles,
                              group_b=True)
         call("dgpp_ep_return", self.comm, ptr(self.recv_src), ptr(self.pair_row), ptr(self.y), k, H, E, mp, st)
         sh = None
         if w.shared_gu is not None:
-            sh = ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu_k or w.shared_gu), limit=c.swiglu_limit),
+            sh = ops.linear(ops.swiglu(ops.linear(xn, w.shared_gu_k or w.shared_gu), limit=c.swiglu_limit, alpha=c.swiglu_alpha),
                             w.shared_down_k or w.shared_down)
         if out is None:
             out = torch.empty(T, H, dtype=BF, device=xn.device)

@@ -1,0 +1,157 @@
+"""Block-sparse GQA family on the GPU: the index kernels and the block-selection form of the decode attention against
+PyTorch, the scaled-sigmoid activation in both of its kernels, and the kernel runner against its oracle."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda:0")
+
+
+def test_index_prep_select_and_sparse_attention(dev):
+    from dgpp_b200.engine.kv_cache import PagedKV
+    from dgpp_b200.models.minimax import select_blocks_reference
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.ops import reference as ref
+
+    g = torch.Generator(device=dev).manual_seed(7)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    T, hq, hkv, d, di, rot, page, blk, topk = 300, 8, 2, 128, 128, 64, 16, 32, 3
+    kv = PagedKV(1, hkv, d, 64, 2, 24, page, True, dev)
+    assert kv.reserve(1, T)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    req = torch.full((T,), 1, dtype=torch.int32, device=dev)
+    inv, _ = ref.rope_inv_freq(rot, 1e4, dev)
+    qn, kn = (0.1 * rnd(di)).to(BF), (0.1 * rnd(di)).to(BF)
+    iqk0 = rnd(T, (hkv + 1) * di).to(BF)
+    iqk = iqk0.clone()
+    cache = torch.zeros(64, page, di, dtype=BF, device=dev)
+    ops.msa_index_prep(iqk, pos, req, kv.block_table, inv, qn, kn, cache, hkv, di, rot, 1e-6, one_plus_w=True)
+    x = iqk0.float().view(T, hkv + 1, di)
+    iq = ref.apply_rope(ref.head_norm(x[:, :hkv], qn, 1e-6, True), pos.long(), inv, rot)
+    ik = ref.apply_rope(ref.head_norm(x[:, hkv:], kn, 1e-6, True), pos.long(), inv, rot)[:, 0]
+    got = iqk.float().view(T, hkv + 1, di)
+    assert (got[:, :hkv] - iq).abs().max().item() <= 0.04 and (got[:, hkv] - ik).abs().max().item() <= 0.04
+    table = kv.block_table[1].long()
+    stored = cache[table[pos.long() // page], pos.long() % page]
+    assert torch.equal(stored, iqk.view(T, hkv + 1, di)[:, hkv])
+    # selection from the values the kernel itself wrote (the rule, not the rounding, is under test)
+    max_sel = (T + blk - 1) // blk
+    scores = torch.full((T, hkv, max_sel), float("nan"), device=dev)
+    sel = ops.msa_index_select(iqk, cache, kv.block_table, req, pos, hkv, di, blk, topk, max_sel, scores=scores)
+    keep = select_blocks_reference(got[:, :hkv].contiguous(), got[:, hkv].contiguous(), blk, topk)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = torch.full((T, hkv, topk), -1, dtype=torch.int32, device=dev)
+    for t in range(T):
+        for h in range(hkv):
+            ids = torch.nonzero(keep[t, h]).flatten()
+            want[t, h, :ids.numel()] = ids.int()
+    mism = (sel != want).any(-1).float().mean().item()
+    assert mism <= 0.01, mism                                  # near-ties may order differently in fp32
+    assert bool((sel[:, :, 0] >= 0).all()) and bool((sel[T - 1] >= 0).all())
+    own = torch.where(sel >= 0, sel, torch.full_like(sel, -1)).amax(-1)
+    assert torch.equal(own, (pos // blk).view(T, 1).expand(T, hkv))       # the own block is kept and comes last
+
+    # attention over the kernel's own selection
+    qkv = (rnd(T, (hq + 2 * hkv) * d) * 0.5).to(BF)
+    inv_full, _ = ref.rope_inv_freq(d, 1e4, dev)
+    ops.rope_kv_write(qkv, pos, req, kv.block_table, inv_full, kv.layers[0], hq, hkv, d)
+    for splits in (1, 4):
+        out = ops.attn_decode(qkv, qkv.stride(0), kv.layers[0], kv.block_table, req, pos, hq, hkv, d, 1 / math.sqrt(d),
+                              splits=splits, sel=sel, sel_block=blk)
+        L = kv.layers[0]
+        kd = (L.k.view(torch.float8_e4m3fn).float() * L.k_scale.unsqueeze(-1))[table[pos.long() // page], :, pos.long() % page]
+        vd = (L.v.view(torch.float8_e4m3fn).float() * L.v_scale.unsqueeze(-1))[table[pos.long() // page], :, pos.long() % page]
+        q = qkv[:, :hq * d].float().view(T, hq, d)
+        kept = torch.zeros(T, hkv, max_sel + 1, dtype=torch.bool, device=dev)
+        kept.scatter_(2, torch.where(sel >= 0, sel, torch.full_like(sel, max_sel)).long(), True)
+        tt = torch.arange(T, device=dev)
+        allowed = kept[:, :, tt // blk] & (tt.view(1, 1, T) <= tt.view(T, 1, 1))
+        gq = hq // hkv
+        s = torch.einsum("qhd,khd->hqk", q, kd.repeat_interleave(gq, 1)) / math.sqrt(d)
+        s = s.masked_fill(~allowed.permute(1, 0, 2).repeat_interleave(gq, 0), float("-inf"))
+        ref_out = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vd.repeat_interleave(gq, 1)).reshape(T, hq * d)
+        torch.cuda.synchronize()
+        ops.check_status()
+        err = (out.float() - ref_out).abs().max().item()
+        assert err <= 0.02 * ref_out.abs().max().item() + 0.01, (splits, err)
+        dense = ops.attn_decode(qkv, qkv.stride(0), kv.layers[0], kv.block_table, req, pos, hq, hkv, d, 1 / math.sqrt(d))
+        assert (dense.float() - out.float())[200:].abs().max().item() > 1e-3      # the selection changes late rows
+
+
+def test_scaled_sigmoid_activation_kernels(dev):
+    from dgpp_b200.ops import core as ops
+    from dgpp_b200.ops import reference as ref
+
+    g = torch.Generator(device=dev).manual_seed(1)
+    gu = (torch.randn(48, 1024, device=dev, generator=g) * 4).to(BF)
+    for limit, alpha in ((7.0, 1.702), (0.0, 1.0), (7.0, 0.0)):
+        want = ref.swiglu(gu, limit, alpha)
+        got = ops.swiglu(gu, limit=limit, alpha=alpha)
+        assert (got.float() - want.float()).abs().max().item() <= 0.02 * want.float().abs().max().item()
+        # the fused quantiser sees the same activation (x_out is its bf16 view of the rows it quantises)
+        for rows in (8, 48):
+            x_out = torch.empty(rows, 512, dtype=BF, device=dev)
+            ops.act_quant_nvfp4(gu[:rows], 3, mode="swiglu", limit=limit, alpha=alpha, x_out=x_out)
+            assert (x_out.float() - want[:rows].float()).abs().max().item() <= 0.02 * want.float().abs().max().item()
+    torch.cuda.synchronize()
+    ops.check_status()
+
+
+@pytest.mark.parametrize("moe,topk", [(False, 16), (False, 3), (True, 16)])
+def test_minimax_runner_matches_oracle(dev, moe, topk):
+    """topk 16 keeps every block of these short requests (the whole pipeline under a tight bound, block lists
+    included); topk 3 drops blocks: a near-tie between two blocks' index scores may then resolve differently under
+    the kernels' rounding than in the oracle and move that row's logits, so that case is judged over all rows; so is
+    the mixture-of-experts case (a near-tie in the router picks another expert: a step, not a rounding error)."""
+    from dgpp_b200.models.minimax import MinimaxConfig, MinimaxModel, MinimaxRunner
+    from dgpp_b200.models.moe import MoEConfig
+    from dgpp_b200.ops import core as ops
+
+    mc = MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512, shared_ffn=512, routed_scaling=2.0, swiglu_limit=7.0,
+                   swiglu_alpha=1.702) if moe else None
+    cfg = MinimaxConfig(layers=3, hidden=512, q_heads=8, kv_heads=2, head_dim=128, rotary_dim=64, index_dim=128,
+                        sparse_block=16, sparse_topk=topk, dense_ffn=1024, vocab=2048, moe=mc,
+                        moe_layers=[False, True, True] if moe else [])
+    m = MinimaxModel.random_init(cfg, dev, seed=6)
+    r = MinimaxRunner(m, max_rows=64, slots=2, max_seq_len=256, device=dev)
+    g = torch.Generator().manual_seed(2)
+    a = torch.randint(0, cfg.vocab, (110,), generator=g).tolist()
+    b = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    la = r.prefill(1, a[:100], chunk=64).clone()
+    lb = r.prefill(0, b[:30], chunk=16).clone()
+    want_a = m.forward_reference(torch.tensor(a, device=dev))
+    want_b = m.forward_reference(torch.tensor(b, device=dev))
+    torch.cuda.synchronize()
+    ops.check_status()
+    cosines = []
+
+    def close(got, want, what):
+        cos = torch.nn.functional.cosine_similarity(got.float(), want.float(), dim=0).item()
+        cosines.append(cos)
+        if topk >= 16 and not moe:
+            assert cos >= 0.985, (what, cos)
+            err = (got - want).abs().max().item()
+            assert err <= 0.08 * want.abs().max().item() + 0.03, (what, err)
+
+    close(la[-1], want_a[99], "prefill a")
+    close(lb[-1], want_b[29], "prefill b")
+    for s in range(8):
+        out = r.decode([1, 0], [a[100 + s], b[30 + s]])
+        close(out[0], want_a[100 + s], f"decode a {s}")
+        close(out[1], want_b[30 + s], f"decode b {s}")
+    torch.cuda.synchronize()
+    ops.check_status()
+    good = sum(1 for c in cosines if c >= 0.98)
+    assert good >= 0.75 * len(cosines) and min(cosines) >= 0.5, cosines
+    r.reset(0)
+    assert torch.equal(r.prefill(0, b[:30], chunk=16), lb)
