@@ -528,7 +528,7 @@ def main(argv=None) -> int:
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--model", default="tiny", choices=["tiny", "fake", "hybrid-tiny", "hybrid", "glm-flash-tiny", "dory-tiny", "flash-next-tiny",
-                                                           "minimax-tiny"])
+                                                           "minimax-tiny", "mimo-tiny"])
     ap.add_argument("--slots", type=int, default=8)
     ap.add_argument("--max-context", type=int, default=4096, help="hybrid models: tokens per request (prompt + output)")
     ap.add_argument("--prefill-chunk", type=int, default=0, help="hybrid models: rows per prefill pass (0: 256 tiny, 2048 full)")
@@ -579,7 +579,7 @@ def main(argv=None) -> int:
         # ids above the byte vocabulary get a printable piece each, so that streamed chunks carry text for every token
         tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)] +
                                       [(f"<{i}>", i, False) for i in range(258, hc.vocab)], rt.SplitPattern.Qwen2)
-    elif args.model in ("glm-flash-tiny", "dory-tiny", "flash-next-tiny", "minimax-tiny"):
+    elif args.model in ("glm-flash-tiny", "dory-tiny", "flash-next-tiny", "minimax-tiny", "mimo-tiny"):
         # the smaller families behind the generic runner adapter (random-init smoke models, greedy, needs a GPU)
         from ..engine.adapters import RunnerEngine
         from ..models.moe import MoEConfig
@@ -594,6 +594,10 @@ def main(argv=None) -> int:
             from ..models.dory import DoryConfig, DoryModel, DoryRunner
             runner = DoryRunner(DoryModel.random_init(DoryConfig(vocab=4096), "cuda", seed=0), 256, args.slots,
                                 args.max_context, "cuda")
+        elif args.model == "mimo-tiny":
+            from ..models.mimo import MimoConfig, MimoModel, MimoRunner
+            mc = MimoConfig(vocab=4096, moe=MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512))
+            runner = MimoRunner(MimoModel.random_init(mc, "cuda", seed=0), 256, args.slots, args.max_context, "cuda")
         elif args.model == "minimax-tiny":
             from ..models.minimax import MinimaxConfig, MinimaxModel, MinimaxRunner
             mc = MinimaxConfig(vocab=4096, moe_layers=[False, True, True, True],
