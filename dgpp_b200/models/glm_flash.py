@@ -12,6 +12,8 @@ Token mixers: three of every `mla_every` layers are KDA (delta-rule linear atten
 a causal depthwise convolution in front, an output gate and a per-head RMS norm behind; fp32 state per request), the
 remaining one is multi-head latent attention over a paged latent cache (optionally with the sparse lightning index).
 FFN: dense SwiGLU in the first `dense_layers` layers, mixture of experts after.  The head reads a final collapse.
+Optional hashed n-gram memory sites (`engram`, `engram_layers`): in front of a listed layer every stream takes in a
+value looked up by a hash of the token's last 2 .. max_ngram tokens (`models/engram.py`).
 
 ``GlmFlashModel.forward_reference`` is the PyTorch oracle (token by token recurrence, plain non-absorbed attention);
 ``GlmFlashRunner`` launches the sm_100a kernels: `mhc_compute` / `mhc_fold`, `gdn_conv` + `kda_recurrent` +
@@ -31,6 +33,7 @@ import torch.nn.functional as F
 from ..ops import core as ops
 from ..ops import reference as ref
 from ..quant.formats import QuantLinear, quantize
+from .engram import Engram, EngramConfig
 from .mla_moe import MlaCaches, MlaLayer, mla_attention_reference
 from .moe import MoEBlock, MoEConfig, MoEWeights, moe_reference
 
@@ -69,6 +72,8 @@ class GlmFlashConfig:
     eps: float = 1e-6
     rope_theta: float = 1e4
     page: int = 64
+    engram: Optional[EngramConfig] = None      # hashed n-gram memory in front of the layers listed in engram_layers
+    engram_layers: tuple = ()
 
     def is_mla(self, i: int) -> bool:
         return (i + 1) % self.mla_every == 0
@@ -144,6 +149,7 @@ class GlmFlashModel:
     def __init__(self, cfg: GlmFlashConfig, embed, layers: List[GlmFlashLayer], final_hc: HcSite, head: QuantLinear,
                  inv_freq):
         self.cfg, self.embed, self.layers, self.final_hc, self.head, self.inv_freq = cfg, embed, layers, final_hc, head, inv_freq
+        self.engram: Optional[Engram] = None
 
     @staticmethod
     def random_init(cfg: GlmFlashConfig, device, seed: int = 0, std: float = 0.05, fmt: str = "bf16") -> "GlmFlashModel":
@@ -181,7 +187,10 @@ class GlmFlashModel:
             layers.append(L)
         embed = (rnd(c.vocab, H) * std * 8).to(BF)
         inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.rope, 2, device=device).float() / c.rope))
-        return GlmFlashModel(cfg, embed, layers, site(), quantize(rnd(c.vocab, H) * std, "bf16"), inv)
+        m = GlmFlashModel(cfg, embed, layers, site(), quantize(rnd(c.vocab, H) * std, "bf16"), inv)
+        if c.engram is not None and c.engram_layers:
+            m.engram = Engram.random_init(c.engram, c.engram_layers, c.vocab, n, H, device, seed=seed, std=std, eps=c.eps)
+        return m
 
     # ------------------------------------------------------------------ oracle
     def forward_reference(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -198,7 +207,12 @@ class GlmFlashModel:
             xn = ref.rmsnorm(col, hc.norm, c.eps)[0]
             streams = ref.mhc_fold(streams, block(xn), post, comb)
 
-        for L in self.layers:
+        prev = None
+        if self.engram is not None:
+            prev = torch.tensor(self.engram.prev_rows(tokens.tolist(), []), dtype=torch.int32, device=dev)
+        for i, L in enumerate(self.layers):
+            if self.engram is not None and i in self.engram.layers:
+                streams = self.engram.apply_reference(i, streams, tokens.to(dev), prev)
             if L.mla is not None:
                 site(L.att_hc, lambda xn: mla_attention_reference(c, self.inv_freq, L.mla, xn, pos))
             else:
@@ -241,11 +255,13 @@ class GlmFlashRunner:
         self.prep = torch.empty(max_rows * (2 * c.k_heads * c.dk + 2 * c.v_heads + c.v_heads * c.dk), dtype=torch.float32,
                                 device=device)
         self.lengths = [0] * slots
+        self.history = [[] for _ in range(slots)]      # the newest tokens of every request (the n-gram memory's lookback)
         self.use_graphs, self._graphs, self._static = True, {}, {}
         self.pdl_graphs = True      # programmatic-dependent-launch edges between this library's kernels in captured passes
 
     def reset(self, slot: int) -> None:
         self.lengths[slot] = 0
+        self.history[slot] = []
         self.ssm_pool[:, slot].zero_()
         self.conv_pool[:, slot].zero_()
 
@@ -289,7 +305,8 @@ class GlmFlashRunner:
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor,
-                chunk_slot: Optional[int] = None, all_logits: bool = True, select: bool = True) -> torch.Tensor:
+                chunk_slot: Optional[int] = None, all_logits: bool = True, select: bool = True,
+                prev: Optional[torch.Tensor] = None) -> torch.Tensor:
         """int32 [rows] device tensors -> fp32 logits [rows, V] (all_logits=False: the last row's, [1, V]).  chunk_slot
         given: the rows are consecutive tokens of that request (prefill chunk); otherwise one decode token per row."""
         m, c = self.m, self.c
@@ -298,6 +315,8 @@ class GlmFlashRunner:
         ops.embed_gather(tokens, m.embed, out=self.h[:rows])
         st.copy_(self.h[:rows].unsqueeze(1).expand(rows, c.streams, c.hidden))
         for i, L in enumerate(m.layers):
+            if m.engram is not None and i in m.engram.layers:
+                m.engram.apply(i, st, tokens, prev)
             if L.mla is not None:
                 j = self.mla_index[i]
                 self._site(L.att_hc, rows, lambda xn, out: self.att.attention(j, L.mla, m.inv_freq, xn, positions, row_req,
@@ -322,8 +341,12 @@ class GlmFlashRunner:
             t = torch.tensor(part, dtype=torch.int32, device=self.dev)
             pos = torch.arange(start + o, start + o + len(part), dtype=torch.int32, device=self.dev)
             req = torch.full((len(part),), slot, dtype=torch.int32, device=self.dev)
+            prev = None
+            if self.m.engram is not None:
+                prev = torch.tensor(self.m.engram.prev_rows(part, self.history[slot]), dtype=torch.int32, device=self.dev)
+                self.history[slot] = self.m.engram.keep(self.history[slot], part)
             out = self.forward(t, pos, req, chunk_slot=slot, all_logits=False,
-                               select=start + o + len(part) > self.c.index_topk)
+                               select=start + o + len(part) > self.c.index_topk, prev=prev)
         self.lengths[slot] = start + len(tokens)
         return out
 
@@ -335,15 +358,21 @@ class GlmFlashRunner:
         b = len(slots)
         positions = [self.lengths[s] for s in slots]
         select = bool(self.c.index_heads) and max(positions) + 1 > self.c.index_topk
-        host = torch.tensor([tokens, positions, slots], dtype=torch.int32)
+        rows3 = [tokens, positions, slots]
+        eng = self.m.engram
+        if eng is not None:
+            per = [eng.prev_rows([t], self.history[s]) for s, t in zip(slots, tokens)]
+            rows3 = rows3 + [[per[r][k][0] for r in range(b)] for k in range(eng.cfg.max_ngram - 1)]
+        host = torch.tensor(rows3, dtype=torch.int32)
+        rest = lambda t: t[3:] if t.shape[0] > 3 else None
         if not (self.use_graphs and torch.device(self.dev).type == "cuda"):
             d = host.to(self.dev)
-            out = self.forward(d[0], d[1], d[2], select=select)
+            out = self.forward(d[0], d[1], d[2], select=select, prev=rest(d))
         else:
             key = (b, select)
             st = self._static.get(key)
             if st is None:
-                st = self._static[key] = torch.zeros(3, b, dtype=torch.int32, device=self.dev)
+                st = self._static[key] = torch.zeros(host.shape[0], b, dtype=torch.int32, device=self.dev)
             st.copy_(host, non_blocking=True)
             g = self._graphs.get(key)
             if g is None:
@@ -351,16 +380,19 @@ class GlmFlashRunner:
                 side = torch.cuda.Stream()
                 side.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
-                    self.forward(st[0], st[1], st[2], select=select)
+                    self.forward(st[0], st[1], st[2], select=select, prev=rest(st))
                 torch.cuda.current_stream().wait_stream(side)
                 torch.cuda.synchronize()
                 from ..engine.graph import capture_with_pdl
-                graph, out, _ = capture_with_pdl(lambda: self.forward(st[0], st[1], st[2], select=select), self.pdl_graphs)
+                graph, out, _ = capture_with_pdl(lambda: self.forward(st[0], st[1], st[2], select=select, prev=rest(st)),
+                                                 self.pdl_graphs)
                 for t, s0 in zip(self._state_tensors(), saved):
                     t.copy_(s0)
                 g = self._graphs[key] = (graph, out)
             graph, out = g
             graph.replay()
-        for s in slots:
+        for s, t in zip(slots, tokens):
             self.lengths[s] += 1
+            if eng is not None:
+                self.history[s] = eng.keep(self.history[s], [t])
         return out

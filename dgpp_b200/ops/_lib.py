@@ -34,6 +34,8 @@ _SIGNATURES = {
     "dgpp_attn_decode": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_decode_sink": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
     "dgpp_attn_decode_sparse": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, P],
+    "dgpp_engram_embed": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, L, P],
+    "dgpp_engram_gate": [P, P, P, P, I, I, I, F, P],
     "dgpp_msa_index_prep": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "dgpp_msa_index_select": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "dgpp_attn_decode_tc": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],

@@ -759,6 +759,35 @@ def ple_embed_add(tokens: torch.Tensor, prev: torch.Tensor, table: torch.Tensor,
     return x
 
 
+def engram_embed(tokens, prev, token_map, multipliers, primes, offsets, table, table_sf, pad_class: int, out=None,
+                 ids=None):
+    """Hashed n-gram memory lookup: tokens [rows] and prev [max_ngram - 1, rows] int32 (row k: the token k + 1 positions
+    back, -1 before the start) -> bf16 [rows, (max_ngram - 1) * heads * D] dequantised table rows.  multipliers
+    [max_ngram], primes / offsets [max_ngram - 1, heads] int64; table [rows, D] e4m3 bytes, table_sf [rows, D / 32]
+    e8m0 bytes.  ids: optional int32 [rows, (max_ngram - 1) * heads] out."""
+    rows, max_ngram = tokens.numel(), multipliers.numel()
+    heads, d = primes.shape[1], table.shape[1]
+    assert prev.shape == (max_ngram - 1, rows) and prev.is_contiguous() and primes.shape == offsets.shape == (max_ngram - 1, heads)
+    assert multipliers.dtype == primes.dtype == offsets.dtype == torch.int64 and table.dtype == table_sf.dtype == torch.uint8
+    if out is None:
+        out = torch.empty(rows, (max_ngram - 1) * heads * d, dtype=torch.bfloat16, device=tokens.device)
+    call("dgpp_engram_embed", ptr(tokens), ptr(prev), ptr(token_map), ptr(multipliers), ptr(primes), ptr(offsets),
+         ptr(table), ptr(table_sf), ptr(out), ptr(ids), rows, max_ngram, heads, d, int(pad_class), token_map.numel(),
+         table.shape[0], stream_ptr())
+    return out
+
+
+def engram_gate(streams, kv, q_weight, k_weight, eps: float = 1e-6):
+    """streams [rows, hc, H] bf16 in place: stream i takes the value of kv [rows, (hc + 1) * H] (keys, then the value)
+    in through sigmoid(signed sqrt of its normalised weighted dot with key i)."""
+    _chk(streams, torch.bfloat16, "streams")
+    _chk(kv, torch.bfloat16, "kv")
+    rows, hc, h = streams.shape
+    assert kv.shape == (rows, (hc + 1) * h) and kv.is_contiguous() and streams.is_contiguous()
+    call("dgpp_engram_gate", ptr(streams), ptr(kv), ptr(q_weight), ptr(k_weight), rows, hc, h, float(eps), stream_ptr())
+    return streams
+
+
 def hadamard32_rows(x: torch.Tensor, out: Optional[torch.Tensor] = None, period: int = 0) -> torch.Tensor:
     """Normalised block-32 Walsh-Hadamard rotation of bf16 rows (in place when out is x); rows r with
     r % period == period - 1 are not touched (period 0: all rows)."""

@@ -277,3 +277,43 @@ def mhc_fold(streams, h, post, comb):
     placed = _bf(post.float().unsqueeze(-1) * h.float().unsqueeze(1))                      # [t, n, D]
     mix = _bf(torch.einsum("tji,tjd->tid", comb.float(), streams.float()))
     return (placed + mix).to(torch.bfloat16)
+
+
+def engram_ids(tokens, prev, token_map, multipliers, primes, offsets, pad_class: int):
+    """Oracle of the hash of ops.engram_embed -> int64 [rows, (max_ngram - 1) * heads] table rows.  64-bit wrapping
+    products (torch int64 arithmetic wraps), XOR-accumulated over the lookback, modulo the per-(size, head) prime with a
+    non-negative remainder, plus the per-(size, head) offset."""
+    vocab = token_map.numel()
+
+    def cls(t):
+        t = t.long()
+        ok = (t >= 0) & (t < vocab)
+        return torch.where(ok, token_map.long()[t.clamp(0, vocab - 1)], torch.full_like(t, pad_class))
+
+    rolling = cls(tokens) * multipliers[0]
+    out = []
+    for n in range(1, multipliers.numel()):
+        rolling = rolling ^ (cls(prev[n - 1]) * multipliers[n])
+        out.append(torch.remainder(rolling.unsqueeze(-1), primes[n - 1].unsqueeze(0)) + offsets[n - 1].unsqueeze(0))
+    return torch.cat(out, -1)
+
+
+def engram_embed(tokens, prev, token_map, multipliers, primes, offsets, table, table_sf, pad_class: int):
+    ids = engram_ids(tokens, prev, token_map, multipliers, primes, offsets, pad_class)
+    rows, d = ids.shape[0], table.shape[1]
+    val = table[ids].view(torch.float8_e4m3fn).float()                                    # [rows, slots, D]
+    sc = torch.exp2(table_sf[ids].float() - 127.0).repeat_interleave(32, dim=-1)
+    return act(val * sc).reshape(rows, -1)
+
+
+def engram_gate(streams, kv, q_weight, k_weight, eps: float = 1e-6):
+    rows, hc, h = streams.shape
+    x = streams.float()
+    key = kv[:, :hc * h].float().view(rows, hc, h)
+    val = kv[:, hc * h:].float().view(rows, 1, h)
+    w = q_weight.float() * k_weight.float()
+    rstd = torch.rsqrt(x.pow(2).mean(-1) + eps) * torch.rsqrt(key.pow(2).mean(-1) + eps)
+    dot = (x * w * key).sum(-1) * rstd / math.sqrt(h)
+    sgn = torch.where(torch.signbit(dot), -torch.ones_like(dot), torch.ones_like(dot))      # copysign: +0 counts as positive
+    gate = torch.sigmoid(sgn * torch.sqrt(dot.abs().clamp_min(1e-6)))
+    return act(x + gate.unsqueeze(-1) * val)
