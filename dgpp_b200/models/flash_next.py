@@ -10,12 +10,17 @@ its output into every branch with a per-branch strength:
     R_i    += y * 2 sigmoid(<w_inject_i, rn> / hc)
 
 The token embedding is the vocabulary row plus a row of a hashed table indexed by (previous token, token), so a
-request remembers its last token between passes.  The full-attention layers here are plain causal GQA over the paged
-FP8 cache (the family's sparse-attention variant is not part of this build).
+request remembers its last token between passes.  The full-attention layers are causal GQA over the paged FP8 cache,
+dense or (with `qsa`) block-sparse with pooled index keys: every token projects `index_heads` index queries (RMSNorm
+with 1 + w, rotary) and one raw index key; when a block of `page` tokens completes, its raw keys are averaged,
+normalised and rotated at the block's first position into one compressed key; a row scores every complete visible
+block by sum_h relu(<q_h, c_b>) / sqrt(index_dim), keeps the `select_k` best (ties to the lower block) plus its own
+incomplete block, and attends only to the tokens of those blocks (one list per row, shared by the kv heads).
 Oracle: ``FlashNextModel.forward_reference``; kernels: `gr_gate_act`, `gr_mix_finish`, `gr_combine`, the GDN layer
-kernels, rotary + KV append, tcgen05 attention, the MoE block, tensor-core linears.
+kernels, rotary + KV append, tcgen05 attention (dense) or `msa_index_prep` (raw keys) / `qsa_compress` / `qsa_select` and
+the block-selection form of the paged decode attention (sparse), the MoE block, tensor-core linears.
 (reference counterparts: src/models/qwen/forward.cpp, layers.cpp (GR residual, PLE), src/kernels/qwen_gr.cu,
- src/kernels/gdn_chunk.cu, src/models/qwen/moe_layer.cpp.)
+ src/kernels/qsa.hpp (indexer, score, select, listed attention), src/kernels/gdn_chunk.cu, src/models/qwen/moe_layer.cpp.)
 """
 from __future__ import annotations
 
@@ -33,6 +38,13 @@ from .moe import MoEBlock, MoEConfig, MoEWeights, moe_reference
 from .rows import RowRunner
 
 BF = torch.bfloat16
+
+
+@dataclass
+class QsaConfig:
+    index_heads: int = 4
+    index_dim: int = 128
+    select_k: int = 2            # complete blocks kept per row (the row's own incomplete block comes on top)
 
 
 @dataclass
@@ -55,7 +67,8 @@ class FlashNextConfig:
     ple_rows: int = 4096         # hashed bigram table (0 = none)
     rope_theta: float = 1e4
     eps: float = 1e-6
-    page: int = 64
+    page: int = 64               # KV page = the pooled block of the sparse index
+    qsa: Optional[QsaConfig] = None
 
     def is_full(self, i: int) -> bool:
         return (i + 1) % self.full_every == 0
@@ -85,6 +98,33 @@ class FlashNextLayer:
     gate_up: Optional[QuantLinear] = None
     down: Optional[QuantLinear] = None
     moe: Optional[MoEWeights] = None
+    index: Optional[QuantLinear] = None          # [(index_heads + 1) * index_dim, H]: index queries, then the raw key
+    index_q_norm: Optional[torch.Tensor] = None  # [index_dim] bf16, applied as 1 + w
+    index_k_norm: Optional[torch.Tensor] = None
+
+
+def qsa_keep_reference(iq: torch.Tensor, raw_k: torch.Tensor, k_norm, inv_freq, page: int, select_k: int, eps: float) -> torch.Tensor:
+    """iq [T, ih, di] (normed, rotated), raw_k [T, di] fp32 of one request from position 0 -> bool [T, nblocks]: the
+    blocks every row attends to (complete blocks by score, own incomplete block always)."""
+    T, ih, di = iq.shape
+    nb = (T + page - 1) // page
+    full = T // page
+    keep = torch.zeros(T, nb, dtype=torch.bool, device=iq.device)
+    t = torch.arange(T, device=iq.device)
+    if full:
+        mean = ref._r(raw_k[:full * page].view(full, page, di).mean(1))
+        first = torch.arange(full, device=iq.device) * page
+        comp = ref.apply_rope(ref.head_norm(mean.unsqueeze(1), k_norm, eps, True), first, inv_freq, di)[:, 0]     # [full, di]
+        s = torch.relu(torch.einsum("thd,bd->thb", iq, comp)).sum(1) / (di ** 0.5)                               # [T, full]
+        visible = ((t + 1) // page).view(T, 1)
+        s = s.masked_fill(torch.arange(full, device=iq.device).view(1, full) >= visible, float("-inf"))
+        order = torch.argsort(-s, dim=-1, stable=True)[:, :select_k]
+        picked = torch.zeros(T, full, dtype=torch.bool, device=iq.device)
+        picked.scatter_(1, order, True)
+        keep[:, :full] = picked & (s > float("-inf"))
+    tail = (t + 1) % page != 0
+    keep[t[tail], (t // page)[tail]] = True
+    return keep
 
 
 class FlashNextModel:
@@ -92,6 +132,7 @@ class FlashNextModel:
                  head: QuantLinear, inv_freq):
         self.cfg, self.embed, self.ple, self.layers, self.final, self.final_norm, self.head, self.inv_freq = \
             cfg, embed, ple, layers, final, final_norm, head, inv_freq
+        self.inv_idx = None if cfg.qsa is None else ref.rope_inv_freq(cfg.qsa.index_dim, cfg.rope_theta, embed.device)[0]
 
     @staticmethod
     def random_init(cfg: FlashNextConfig, device, seed: int = 0, std: float = 0.05, fmt: str = "bf16") -> "FlashNextModel":
@@ -110,6 +151,10 @@ class FlashNextModel:
             L = FlashNextLayer(site(), site())
             if c.is_full(i):
                 L.qkv, L.o = lin((c.q_heads + 2 * c.kv_heads) * d, H), lin(H, c.q_heads * d)
+                if c.qsa is not None:
+                    q = c.qsa
+                    L.index = quantize(rnd((q.index_heads + 1) * q.index_dim, H) * std * 2, "bf16")
+                    L.index_q_norm, L.index_k_norm = (0.1 * rnd(q.index_dim)).to(BF), (0.1 * rnd(q.index_dim)).to(BF)
             else:
                 L.gdn = GdnWeights.random_init(c.gdn_cfg(), device, seed=seed * 77 + i, std=std, fmt=fmt)
             if c.moe is not None:
@@ -159,7 +204,23 @@ class FlashNextModel:
             q = ref.apply_rope(qkv[:, :nq].view(T, c.q_heads, d), pos, self.inv_freq, d)
             k = ref.apply_rope(qkv[:, nq:nq + nkv].view(T, c.kv_heads, d), pos, self.inv_freq, d)
             v = ref._r(qkv[:, nq + nkv:].view(T, c.kv_heads, d))
-            a = ref.attention(q, k, v, 1.0 / math.sqrt(d), causal_offset=0)
+            if c.qsa is None:
+                a = ref.attention(q, k, v, 1.0 / math.sqrt(d), causal_offset=0)
+                return ref.linear(ref.act(a.reshape(T, nq)), L.o)
+            qs = c.qsa
+            iqk = ref.linear(xin, L.index).float().view(T, qs.index_heads + 1, qs.index_dim)
+            iq = ref.apply_rope(ref.head_norm(iqk[:, :qs.index_heads], L.index_q_norm, c.eps, True), pos, self.inv_idx, qs.index_dim)
+            keep = qsa_keep_reference(iq, iqk[:, qs.index_heads], L.index_k_norm, self.inv_idx, c.page, qs.select_k, c.eps)
+            kq, ks = ref.quant_kv_fp8(k)
+            vq, vs = ref.quant_kv_fp8(v)
+            k = kq.view(torch.float8_e4m3fn).float() * ks.unsqueeze(-1)
+            v = vq.view(torch.float8_e4m3fn).float() * vs.unsqueeze(-1)
+            g = c.q_heads // c.kv_heads
+            t = torch.arange(T, device=dev)
+            allowed = keep[:, t // c.page] & (t.view(1, T) <= t.view(T, 1))                   # [T, T]
+            s = torch.einsum("qhd,khd->hqk", q, k.repeat_interleave(g, 1)) / math.sqrt(d)
+            s = s.masked_fill(~allowed.unsqueeze(0), float("-inf"))
+            a = torch.einsum("hqk,khd->qhd", torch.nan_to_num(torch.softmax(s, -1)), v.repeat_interleave(g, 1))
             return ref.linear(ref.act(a.reshape(T, nq)), L.o)
 
         for L in self.layers:
@@ -204,6 +265,16 @@ class FlashNextRunner(RowRunner):
         self.qkv = e(max_rows, (c.q_heads + 2 * c.kv_heads) * c.head_dim)
         self.attn = e(max_rows, c.q_heads * c.head_dim)
         self.last_token = [0] * slots
+        if c.qsa is not None:
+            q, blocks = c.qsa, self.kv.layers[0].k.shape[0]
+            self.idx_raw = [torch.zeros(blocks, c.page, q.index_dim, dtype=BF, device=device) for _ in self.full_index]
+            self.idx_comp = [torch.zeros(blocks, q.index_dim, dtype=BF, device=device) for _ in self.full_index]
+            self.iqk = e(max_rows, (q.index_heads + 1) * q.index_dim)
+            self.sel = torch.empty(max_rows, c.kv_heads, q.select_k + 1, dtype=torch.int32, device=device)
+            self.max_sel = (max_seq_len + c.page - 1) // c.page + 1
+            self.sp_splits = 4
+            self.sp_scratch = (torch.empty(max_rows * c.q_heads * self.sp_splits * 2, dtype=torch.float32, device=device),
+                               torch.empty(max_rows * c.q_heads * self.sp_splits * c.head_dim, dtype=torch.float32, device=device))
 
     def _state_tensors(self):
         return [self.conv_pool, self.ssm_pool]
@@ -223,6 +294,21 @@ class FlashNextRunner(RowRunner):
 
     def _note_tokens(self, slot, tokens):
         self.last_token[slot] = tokens[-1]
+
+    def _sparse_attention(self, j: int, L: FlashNextLayer, xin, qkv, positions, row_req, attn) -> None:
+        c, q, rows = self.c, self.c.qsa, xin.shape[0]
+        cache, bt = self.kv.layers[j], self.kv.block_table
+        iqk, sel = self.iqk[:rows], self.sel[:rows]
+        ops.rope_kv_write(qkv, positions, row_req, bt, self.m.inv_freq, cache, c.q_heads, c.kv_heads, c.head_dim)
+        ops.linear(xin, L.index, out=iqk)
+        ops.msa_index_prep(iqk, positions, row_req, bt, self.m.inv_idx, L.index_q_norm, None, self.idx_raw[j], q.index_heads,
+                           q.index_dim, q.index_dim, c.eps, one_plus_w=True, raw_key=True)
+        ops.qsa_compress(self.idx_raw[j], self.idx_comp[j], positions, row_req, bt, self.m.inv_idx, L.index_k_norm, q.index_dim,
+                         c.eps, one_plus_w=True)
+        ops.qsa_select(iqk, self.idx_comp[j], bt, row_req, positions, q.index_heads, q.index_dim, c.page, q.select_k,
+                       self.max_sel, copies=c.kv_heads, out=sel)
+        ops.attn_decode(qkv, qkv.stride(0), cache, bt, row_req, positions, c.q_heads, c.kv_heads, c.head_dim, self.att_scale,
+                        splits=self.sp_splits, scratch=self.sp_scratch, out=attn, sel=sel, sel_block=c.page)
 
     def _mix(self, s: GrSite, rows: int) -> torch.Tensor:
         c = self.c
@@ -264,7 +350,10 @@ class FlashNextRunner(RowRunner):
                 def attention(xin, out):
                     qkv, attn = self.qkv[:rows], self.attn[:rows]
                     ops.linear(xin, L.qkv, out=qkv)
-                    self._attention_rows(self.full_index[i], qkv, positions, row_req, m.inv_freq, chunk_slot, pos0, attn)
+                    if c.qsa is None:
+                        self._attention_rows(self.full_index[i], qkv, positions, row_req, m.inv_freq, chunk_slot, pos0, attn)
+                    else:
+                        self._sparse_attention(self.full_index[i], L, xin, qkv, positions, row_req, attn)
                     ops.linear(attn, L.o, out=out)
                 self._site(L.mix, rows, attention)
             self._site(L.ffn_site, rows, lambda xin, out: self._ffn(i, L, xin, out))

@@ -36,7 +36,9 @@ _SIGNATURES = {
     "dgpp_attn_decode_sparse": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, P],
     "dgpp_engram_embed": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, L, P],
     "dgpp_engram_gate": [P, P, P, P, I, I, I, F, P],
-    "dgpp_msa_index_prep": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "dgpp_msa_index_prep": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "dgpp_qsa_compress": [P, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
+    "dgpp_qsa_select": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "dgpp_msa_index_select": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "dgpp_attn_decode_tc": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_prefill_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],

@@ -481,15 +481,42 @@ def attn_decode(q, q_stride: int, cache, block_table, row_req, positions, hq: in
 
 
 def msa_index_prep(iqk, positions, row_req, block_table, inv_freq, q_norm_w, k_norm_w, index_cache, ih: int, di: int,
-                   rot_dim: int, eps: float = 1e-6, one_plus_w: bool = False) -> None:
+                   rot_dim: int, eps: float = 1e-6, one_plus_w: bool = False, raw_key: bool = False) -> None:
     """In place on iqk [rows, (ih + 1) * di] bf16 (index query heads, then the index key of the row): per-head RMSNorm
-    and rotary embedding on the first rot_dim dims; the key is appended to index_cache [blocks, page, di] bf16."""
+    and rotary embedding on the first rot_dim dims; the key is appended to index_cache [blocks, page, di] bf16.
+    raw_key: the key is appended untouched (pooled-key form: blocks are compressed later by `qsa_compress`)."""
     _chk(iqk, torch.bfloat16, "iqk")
     _chk(index_cache, torch.bfloat16, "index_cache")
     assert iqk.shape[1] == (ih + 1) * di and iqk.is_contiguous() and index_cache.shape[2] == di
     call("dgpp_msa_index_prep", ptr(iqk), ptr(positions), ptr(row_req), ptr(block_table), ptr(inv_freq), ptr(q_norm_w),
          ptr(k_norm_w), ptr(index_cache), iqk.shape[0], ih, di, rot_dim, index_cache.shape[1], block_table.shape[1],
-         float(eps), int(one_plus_w), stream_ptr())
+         float(eps), int(one_plus_w), int(raw_key), stream_ptr())
+
+
+def qsa_compress(raw_cache, comp_cache, positions, row_req, block_table, inv_freq, k_norm_w, rot_dim: int,
+                 eps: float = 1e-6, one_plus_w: bool = True) -> None:
+    """For every row whose position completes a block of raw_cache [blocks, kpool, di] bf16: the block's keys averaged
+    (fp32 mean, bf16), RMS-normalised and rotated at the block's first position -> comp_cache [blocks, di] bf16."""
+    _chk(raw_cache, torch.bfloat16, "raw_cache")
+    _chk(comp_cache, torch.bfloat16, "comp_cache")
+    assert comp_cache.shape == (raw_cache.shape[0], raw_cache.shape[2])
+    call("dgpp_qsa_compress", ptr(raw_cache), ptr(comp_cache), ptr(positions), ptr(row_req), ptr(block_table),
+         ptr(inv_freq), ptr(k_norm_w), positions.numel(), raw_cache.shape[2], raw_cache.shape[1], rot_dim,
+         block_table.shape[1], float(eps), int(one_plus_w), stream_ptr())
+
+
+def qsa_select(iqk, comp_cache, block_table, row_req, positions, ih: int, di: int, kpool: int, select_k: int, max_sel: int,
+               copies: int = 1, out=None, scores=None):
+    """Pooled-key block selection -> int32 [rows, copies, select_k + 1]: ascending ids of the select_k complete visible
+    blocks with the largest sum over index heads of relu(<q_h, compressed key>) / sqrt(di) (all of them when there
+    are no more; ties to the lower id) plus the row's own incomplete block; -1 padded; the same list `copies` times
+    (one per kv head for `attn_decode`)."""
+    rows = positions.numel()
+    if out is None:
+        out = torch.empty(rows, copies, select_k + 1, dtype=torch.int32, device=positions.device)
+    call("dgpp_qsa_select", ptr(iqk), iqk.stride(0), ptr(comp_cache), ptr(block_table), ptr(row_req), ptr(positions),
+         ptr(out), ptr(scores), rows, ih, di, block_table.shape[1], kpool, select_k, max_sel, copies, stream_ptr())
+    return out
 
 
 def msa_index_select(iqk, index_cache, block_table, row_req, positions, ih: int, di: int, sel_block: int, topk: int,
