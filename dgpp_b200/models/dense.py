@@ -207,11 +207,13 @@ class DenseModel:
     # ------------------------------------------------------------------ PyTorch oracle
     @torch.no_grad()
     def forward_reference(self, tokens: torch.Tensor, start_pos: int = 0, kv: Optional[list] = None,
-                          all_reduce=None, return_hidden: bool = False, lora=None, embed_spans=None):
+                          all_reduce=None, return_hidden: bool = False, lora=None, embed_spans=None, capture=None):
         """Full-precision-accumulate reference of one request: tokens [T] at positions start_pos.. .
         `kv` is a list (per layer) of (k, v) fp32 tensors [Tk, hkv, d] that is extended in place; KV
         values go through the same FP8 round trip as the paged cache when cfg.kv_fp8.  `lora`: a bound
-        ``adapters.lora.LoraAdapter`` whose updates are added to the bf16 outputs of the projections."""
+        ``adapters.lora.LoraAdapter`` whose updates are added to the bf16 outputs of the projections.  `capture`: a dict
+        whose integer keys name layers; each gets the bf16 residual stream entering that layer [T, hidden] (key
+        `layers`: the stream entering the final norm)."""
         from ..adapters.lora import lora_reference
 
         def adapt(li, proj, xin, out):
@@ -239,6 +241,8 @@ class DenseModel:
         scale = 1.0 / math.sqrt(d)  # the YaRN attention factor is carried by cos/sin (mscale)
         for li, L in enumerate(self.layers):
             xn, x = ref.rmsnorm(x, L.in_norm, c.eps, delta)
+            if capture is not None and li in capture:
+                capture[li] = x.clone()
             qkv = adapt(li, "qkv", xn, ref.linear(xn, L.qkv)).float()
             q = qkv[:, :hq * d].view(T, hq, d)
             k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
@@ -270,6 +274,8 @@ class DenseModel:
             if all_reduce is not None:
                 delta = all_reduce(delta)
         xn, x = ref.rmsnorm(x, self.final_norm, c.eps, delta)
+        if capture is not None and c.layers in capture:
+            capture[c.layers] = x.clone()
         if return_hidden:
             return xn, kv
         logits = ref.linear(xn, self.head, out_fp32=True)
