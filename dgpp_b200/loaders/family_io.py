@@ -169,3 +169,16 @@ def _restack(obj: Any, device) -> None:
         if isinstance(v, (list, tuple, dict)) or dataclasses.is_dataclass(v) or (hasattr(v, "__dict__") and not callable(v)
                                                                                  and type(v).__module__.startswith("dgpp_b200")):
             _restack(v, device)
+
+
+def runner_for(model: Any, max_rows: int, slots: int, max_seq_len: int, device="cuda") -> Any:
+    """The kernel runner of a family model (what `engine.adapters.RunnerEngine` drives)."""
+    from ..models.dory import DoryRunner
+    from ..models.flash_next import FlashNextRunner
+    from ..models.glm_flash import GlmFlashRunner
+    from ..models.mimo import MimoRunner
+    from ..models.minimax import MinimaxRunner
+
+    cls = {"glm_flash": GlmFlashRunner, "dory": DoryRunner, "flash_next": FlashNextRunner, "minimax": MinimaxRunner,
+           "mimo": MimoRunner}[_family_of(model)]
+    return cls(model, max_rows, slots, max_seq_len, device)

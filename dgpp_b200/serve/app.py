@@ -529,6 +529,8 @@ def main(argv=None) -> int:
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--model", default="tiny", choices=["tiny", "fake", "hybrid-tiny", "hybrid", "glm-flash-tiny", "dory-tiny", "flash-next-tiny",
                                                            "minimax-tiny", "mimo-tiny"])
+    ap.add_argument("--family-dir", default="",
+                    help="a native family checkpoint (dgpp_b200.loaders.family_io.save_family) served through the runner adapter")
     ap.add_argument("--slots", type=int, default=8)
     ap.add_argument("--max-context", type=int, default=4096, help="hybrid models: tokens per request (prompt + output)")
     ap.add_argument("--prefill-chunk", type=int, default=0, help="hybrid models: rows per prefill pass (0: 256 tiny, 2048 full)")
@@ -545,9 +547,9 @@ def main(argv=None) -> int:
         return serve_deployment(args.config)
     tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)], rt.SplitPattern.Qwen2)
     sched_config = None
-    if args.model == "fake":
+    if args.model == "fake" and not args.family_dir:
         eng = rt.FakeEngine(slots=args.slots, block_tokens=16, blocks=4096, max_context=8192, vocab=256)
-    elif args.model in ("hybrid-tiny", "hybrid"):
+    elif args.model in ("hybrid-tiny", "hybrid") and not args.family_dir:
         # Gated DeltaNet + gated attention + MoE family behind the same scheduler / HTTP surface (needs a GPU).
         # "hybrid" is the full shape (48 layers 3:1, hidden 2048, 512 experts top-10 + shared, head_dim 256, NVFP4
         # weights, random-init); "hybrid-tiny" a four-layer smoke model.
@@ -579,12 +581,16 @@ def main(argv=None) -> int:
         # ids above the byte vocabulary get a printable piece each, so that streamed chunks carry text for every token
         tok = rt.Tokenizer.byte_level([], [("<|im_start|>", 256, True), ("<|im_end|>", 257, True)] +
                                       [(f"<{i}>", i, False) for i in range(258, hc.vocab)], rt.SplitPattern.Qwen2)
-    elif args.model in ("glm-flash-tiny", "dory-tiny", "flash-next-tiny", "minimax-tiny", "mimo-tiny"):
-        # the smaller families behind the generic runner adapter (random-init smoke models, greedy, needs a GPU)
+    elif args.family_dir or args.model in ("glm-flash-tiny", "dory-tiny", "flash-next-tiny", "minimax-tiny", "mimo-tiny"):
+        # the smaller families behind the generic runner adapter (a native family checkpoint, or random-init smoke
+        # models; greedy, needs a GPU)
         from ..engine.adapters import RunnerEngine
         from ..models.moe import MoEConfig
 
-        if args.model == "glm-flash-tiny":
+        if args.family_dir:
+            from ..loaders.family_io import load_family, runner_for
+            runner = runner_for(load_family(args.family_dir, "cuda"), 256, args.slots, args.max_context, "cuda")
+        elif args.model == "glm-flash-tiny":
             from ..models.glm_flash import GlmFlashConfig, GlmFlashModel, GlmFlashRunner
             fc = GlmFlashConfig(layers=4, hidden=512, vocab=4096, mla_every=2, k_heads=2, v_heads=4, heads=8, q_lora=256,
                                 kv_lora=128, nope=64, rope=32, v_dim=64, ffn=1024,

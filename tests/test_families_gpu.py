@@ -183,3 +183,27 @@ def test_flash_next_pooled_key_sparse_attention(dev):
         torch.cuda.synchronize()
         ops.check_status()
         assert sum(1 for c in cosines if c >= 0.98) >= 0.75 * len(cosines) and min(cosines) >= 0.5, cosines
+
+
+def test_family_checkpoint_round_trip_on_the_device(dev, tmp_path):
+    """A written family checkpoint loads onto the GPU (expert matrices restacked for the grouped GEMM) and its runner
+    gives the logits of the original model's runner bit for bit."""
+    from dgpp_b200.loaders.family_io import load_family, runner_for, save_family
+    from dgpp_b200.models.mimo import MimoConfig, MimoModel
+    from dgpp_b200.models.moe import MoEConfig
+
+    cfg = MimoConfig(layers=4, hidden=512, q_heads=8, kv_heads=2, swa_kv_heads=4, head_dim=128, rotary_dim=64, window=24,
+                     ffn=1024, vocab=2048, moe=MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512))
+    m = MimoModel.random_init(cfg, dev, seed=8)
+    save_family(m, str(tmp_path / "ck"))
+    back = load_family(str(tmp_path / "ck"), dev)
+    assert back.layers[1].moe.gu_q is not None
+    a = torch.randint(0, cfg.vocab, (70,), generator=torch.Generator().manual_seed(1)).tolist()
+    outs = []
+    for model in (m, back):
+        r = runner_for(model, 64, 2, 256, dev)
+        lg = [r.prefill(0, a[:60], chunk=32).clone()]
+        for s in range(3):
+            lg.append(r.decode([0], [a[60 + s]]).clone())
+        outs.append(torch.cat(lg))
+    assert torch.equal(outs[0], outs[1])
