@@ -209,6 +209,64 @@ def bench_attn_decode(args, dev):
            hq=hq, hkv=hkv, head_dim=d, splits=sp)
 
 
+def bench_sparse_attn(args, dev):
+    """Block-sparse decode: index scores + block selection (token-key form), then attention over the kept blocks."""
+    from ..ops import core as ops, reference as ref
+
+    hq, hkv, ctx, rows, d, blk, topk = args.hq, args.hkv, args.ctx, args.rows, args.head_dim, args.sparse_block, args.sparse_topk
+    kv, _ = _cache(dev, hq, hkv, ctx, page=blk, slots=rows, d=d)
+    blocks = kv.layers[0].k.shape[0]
+    di = 128
+    index = torch.randn(blocks, blk, di, device=dev).to(BF)
+    iqk = torch.randn(rows, (hkv + 1) * di, device=dev).to(BF)
+    q = torch.randn(rows, (hq + 2 * hkv) * d, device=dev).to(BF)
+    pos = torch.full((rows,), ctx - 1, device=dev, dtype=torch.int32)
+    req = torch.arange(rows, device=dev, dtype=torch.int32)
+    max_sel = ctx // blk + 1
+    sel = torch.empty(rows, hkv, topk, dtype=torch.int32, device=dev)
+    out = torch.empty(rows, hq * d, device=dev, dtype=BF)
+    sp = args.splits or 8
+    scratch = (torch.empty(rows * hq * sp * 2, device=dev), torch.empty(rows * hq * sp * d, device=dev))
+    scores = torch.empty(rows, hkv, max_sel, device=dev)
+    f_sel = lambda: ops.msa_index_select(iqk, index, kv.block_table, req, pos, hkv, di, blk, topk, max_sel, out=sel, scores=scores)
+    f_att = lambda: ops.attn_decode(q, q.stride(0), kv.layers[0], kv.block_table, req, pos, hq, hkv, d, 0.088, splits=sp,
+                                    scratch=scratch, out=out, sel=sel, sel_block=blk)
+    f_sel()
+    ms_sel = run([f_sel] * 4, args)
+    ms_att = run([f_att] * 4, args)
+    ops.check_status()
+    report(args, "msa_index_select", ms_sel, bytes_=2.0 * rows * ctx * di, rows=rows, ctx=ctx, index_heads=hkv, block=blk, topk=topk)
+    kept = min(topk, ctx // blk + 1) * blk
+    report(args, "attn_decode_sparse", ms_att, bytes_=2.0 * rows * kept * hkv * d, rows=rows, ctx=ctx, kept_tokens=kept, hq=hq,
+           hkv=hkv, head_dim=d, splits=sp)
+
+
+def bench_engram(args, dev):
+    """Hashed n-gram memory site: lookup (hash + gather + decode), projection, stream gate."""
+    from ..models.engram import Engram, EngramConfig
+    from ..ops import core as ops
+
+    rows, H, hc = args.rows, args.k, 4
+    cfg = EngramConfig(max_ngram=4, heads=4, head_dim=128, bucket=args.bucket)
+    e = Engram.random_init(cfg, [0], 131072, hc, H, dev, seed=0)
+    L = e.layers[0]
+    toks = torch.randint(0, 131072, (rows,), device=dev, dtype=torch.int32)
+    prev = torch.randint(0, 131072, (3, rows), device=dev, dtype=torch.int32)
+    st = torch.randn(rows, hc, H, device=dev).to(BF)
+    emb = ops.engram_embed(toks, prev, e.token_map, L.multipliers, L.primes, L.offsets, L.table, L.table_sf, e.pad_class)
+    kvp = ops.linear(emb, L.wkv)
+    f_emb = lambda: ops.engram_embed(toks, prev, e.token_map, L.multipliers, L.primes, L.offsets, L.table, L.table_sf,
+                                     e.pad_class, out=emb)
+    f_gate = lambda: ops.engram_gate(st, kvp, L.q_weight, L.k_weight, 1e-6)
+    ms_e = run([f_emb] * 4, args)
+    ms_g = run([f_gate] * 4, args)
+    ops.check_status()
+    slots = cfg.slots
+    report(args, "engram_embed", ms_e, bytes_=rows * slots * (cfg.head_dim * 3 + cfg.head_dim // 32), rows=rows, slots=slots,
+           table_rows=int(L.table.shape[0]))
+    report(args, "engram_gate", ms_g, bytes_=rows * (2 * hc * H * 2 + (hc + 1) * H * 2), rows=rows, streams=hc, hidden=H)
+
+
 def bench_attn_prefill(args, dev):
     from ..ops import core as ops
 
@@ -345,7 +403,10 @@ def bench_decode_layer(args, dev):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm_fp4", "gemm_tc", "gemm_fp8", "attn_decode", "attn_prefill", "act_quant", "gdn",
-                                       "moe", "mla", "decode_layer"])
+                                       "moe", "mla", "decode_layer", "sparse_attn", "engram"])
+    ap.add_argument("--sparse-block", type=int, default=128)
+    ap.add_argument("--sparse-topk", type=int, default=16)
+    ap.add_argument("--bucket", type=int, default=200003, help="engram: rows per (n-gram size, head) range")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
@@ -371,7 +432,7 @@ def main(argv=None) -> int:
     torch.manual_seed(0)
     {"gemm_fp4": bench_gemm_fp4, "gemm_tc": bench_gemm_tc, "gemm_fp8": bench_gemm_fp8, "mla": bench_mla, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill,
      "act_quant": bench_act_quant, "gdn": bench_gdn, "moe": bench_moe,
-     "decode_layer": bench_decode_layer}[args.kernel](args, dev)
+     "decode_layer": bench_decode_layer, "sparse_attn": bench_sparse_attn, "engram": bench_engram}[args.kernel](args, dev)
     return 0
 
 

@@ -7,7 +7,8 @@
 //   msa_index_prep    per-head RMSNorm (optionally 1 + w) and partial rotary embedding of the index queries and the
 //                     index key of every row, in place; the key is appended to the paged index cache
 //                     [blocks, page, DI] bf16 (same block table as the KV cache)
-//   msa_index_select  scores + selection, one CTA per (index head, row)
+//   msa_index_select  block scores (one warp per sparse block, all index heads of a row at once, keys staged
+//                     through shared memory with coalesced 16-byte loads), then the pick, one CTA per (index head, row)
 //
 // Pooled-key form (one list per row, shared by every kv head): the index keys are appended raw; when a block of
 // `kpool` tokens completes, its keys are averaged once (fp32 mean, one bf16 rounding), normalised, rotated at the
@@ -115,7 +116,8 @@ struct MsaSelectParams {
   const int32_t* row_req;
   const int32_t* positions;
   int32_t* sel;                // [rows, ih, topk]
-  float* scores;               // optional [rows, ih, max_sel] block scores as used for the choice (unwritten past the row's blocks)
+  float* scores;               // [rows, ih, max_sel] block scores (workspace of the two-kernel selection; the row's own
+                               // block holds its real score here, the pick treats it as +inf)
   int rows, ih, page, max_blocks, sel_block, topk, max_sel;
 };
 
@@ -171,48 +173,95 @@ __device__ __forceinline__ void msa_topk_write(float* sc, int nblk, int keep, in
   }
 }
 
+constexpr int kMsaScoreWarps = 4;      // sparse blocks per CTA of the score kernel (one per warp)
+constexpr int kMsaMaxIndexHeads = 8;
+
+// Block scores.  grid (ceil(max_sel / kMsaScoreWarps), rows), kMsaScoreWarps warps: warp w scores sparse block
+// blockIdx.x * kMsaScoreWarps + w of the row for every index head at once (each key is read once).  32 tokens at a
+// time travel through shared memory with 16-byte coalesced loads; lane t then owns token t of the tile and runs the
+// dot products of all heads against it (queries are broadcast reads).  scores [rows, ih, max_sel].
 template <int DI>
-__global__ void __launch_bounds__(kMsaThreads) msa_index_select_kernel(MsaSelectParams p) {
-  extern __shared__ float sc[];                  // [max_sel] block scores
-  __shared__ float q_s[DI];
+__global__ void __launch_bounds__(kMsaScoreWarps * 32) msa_index_score_kernel(MsaSelectParams p) {
+  constexpr int ROW = DI + 8;                    // padded tile row (bf16): 16-byte reads of 32 lanes spread over the banks
+  extern __shared__ __align__(16) unsigned char msa_smem[];
+  float* q_s = reinterpret_cast<float*>(msa_smem);                                   // [ih][DI]
+  bf16* tiles = reinterpret_cast<bf16*>(msa_smem + static_cast<size_t>(p.ih) * DI * sizeof(float));
+  pdl_wait();
+  const int row = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = p.positions[row];
+  const int nblk = min(pos / p.sel_block + 1, p.max_sel);
+  if (blockIdx.x * kMsaScoreWarps >= nblk) return;
+  for (int i = threadIdx.x; i < p.ih * DI; i += kMsaScoreWarps * 32)
+    q_s[i] = bf16_to_f32(p.iqk[static_cast<size_t>(row) * p.iqk_stride + i]);
+  __syncthreads();
+  const int b = blockIdx.x * kMsaScoreWarps + warp;
+  if (b >= nblk) return;
+  bf16* tile = tiles + static_cast<size_t>(warp) * 32 * ROW;
+  const int32_t* bt = p.block_table + static_cast<size_t>(p.row_req[row]) * p.max_blocks;
+  float mx[kMsaMaxIndexHeads];
+#pragma unroll
+  for (int h = 0; h < kMsaMaxIndexHeads; ++h) mx[h] = -INFINITY;
+  const int t_end = min((b + 1) * p.sel_block, pos + 1);
+  for (int t0 = b * p.sel_block; t0 < t_end; t0 += 32) {
+    const int n = min(32, t_end - t0);
+    // n tokens x (DI / 8) chunks of 16 bytes, consecutive lanes on consecutive chunks of a token
+    for (int i = lane; i < n * (DI / 8); i += 32) {
+      const int tt = i / (DI / 8), c = i % (DI / 8);
+      const int t = t0 + tt;
+      const uint4 v = reinterpret_cast<const uint4*>(
+          p.index_cache + (static_cast<size_t>(bt[t / p.page]) * p.page + t % p.page) * DI)[c];
+      *reinterpret_cast<uint4*>(tile + tt * ROW + c * 8) = v;
+    }
+    __syncwarp();
+    if (lane < n) {
+      float s[kMsaMaxIndexHeads];
+#pragma unroll
+      for (int h = 0; h < kMsaMaxIndexHeads; ++h) s[h] = 0.f;
+#pragma unroll 4
+      for (int c = 0; c < DI / 8; ++c) {
+        Pack16 kb;
+        kb.u = *reinterpret_cast<const uint4*>(tile + lane * ROW + c * 8);
+        float kf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) kf[j] = bf16_to_f32(kb.h[j]);
+#pragma unroll
+        for (int h = 0; h < kMsaMaxIndexHeads; ++h) {
+          if (h < p.ih) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[h] = fmaf(q_s[h * DI + c * 8 + j], kf[j], s[h]);
+          }
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < kMsaMaxIndexHeads; ++h) mx[h] = fmaxf(mx[h], s[h]);
+    }
+    __syncwarp();
+  }
+#pragma unroll
+  for (int h = 0; h < kMsaMaxIndexHeads; ++h) {
+    if (h < p.ih) {
+      float v = mx[h];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+      if (lane == 0) p.scores[(static_cast<size_t>(row) * p.ih + h) * p.max_sel + b] = v;
+    }
+  }
+}
+
+// Selection from the block scores.  grid (ih, rows).
+__global__ void __launch_bounds__(kMsaThreads) msa_index_pick_kernel(MsaSelectParams p) {
+  extern __shared__ float sc[];                  // [max_sel]
   __shared__ float wv[kMsaThreads / 32];
   __shared__ int wi[kMsaThreads / 32];
   __shared__ int chosen[kMsaMaxTopk + 1];
   pdl_wait();
   const int h = blockIdx.x, row = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = p.positions[row];
   const int nblk = min(pos / p.sel_block + 1, p.max_sel);
-  for (int d = threadIdx.x; d < DI; d += kMsaThreads)
-    q_s[d] = bf16_to_f32(p.iqk[static_cast<size_t>(row) * p.iqk_stride + h * DI + d]);
+  const float* src = p.scores + (static_cast<size_t>(row) * p.ih + h) * p.max_sel;
+  for (int b = threadIdx.x; b < nblk; b += kMsaThreads) sc[b] = b == nblk - 1 ? INFINITY : src[b];   // own block always kept
   __syncthreads();
-  const int32_t* bt = p.block_table + static_cast<size_t>(p.row_req[row]) * p.max_blocks;
-  for (int b = warp; b < nblk; b += kMsaThreads / 32) {
-    float mx = -INFINITY;
-    const int t_end = min((b + 1) * p.sel_block, pos + 1);
-    for (int t = b * p.sel_block + lane; t < t_end; t += 32) {
-      const uint4* kr = reinterpret_cast<const uint4*>(
-          p.index_cache + (static_cast<size_t>(bt[t / p.page]) * p.page + t % p.page) * DI);
-      float s = 0.f;
-#pragma unroll 4
-      for (int c = 0; c < DI / 8; ++c) {
-        Pack16 kb;
-        kb.u = kr[c];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) s = fmaf(q_s[c * 8 + j], bf16_to_f32(kb.h[j]), s);
-      }
-      mx = fmaxf(mx, s);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) sc[b] = mx;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0 && nblk > 0) sc[nblk - 1] = INFINITY;       // the row's own block is always kept
-  __syncthreads();
-  if (p.scores != nullptr)
-    for (int b = threadIdx.x; b < nblk; b += kMsaThreads)
-      p.scores[(static_cast<size_t>(row) * p.ih + h) * p.max_sel + b] = sc[b];
   msa_topk_write(sc, nblk, min(p.topk, nblk), -1, chosen, wv, wi,
                  p.sel + (static_cast<size_t>(row) * p.ih + h) * p.topk, p.topk, 1, 0);
 }
@@ -379,7 +428,9 @@ DGPP_API int dgpp_msa_index_select(const void* iqk, int64_t iqk_stride, const vo
   DGPP_REQUIRE(topk >= 1 && topk <= kMsaMaxTopk, "msa_index_select: topk %d outside 1..%d", topk, kMsaMaxTopk);
   DGPP_REQUIRE(sel_block >= 1 && max_sel >= 1 && max_sel <= 8192, "msa_index_select: %d blocks of %d tokens unsupported",
                max_sel, sel_block);
-  DGPP_REQUIRE(ih >= 1 && ih <= 65535 && rows <= 65535, "msa_index_select: grid out of range");
+  DGPP_REQUIRE(ih >= 1 && ih <= kMsaMaxIndexHeads && rows <= 65535, "msa_index_select: %d index heads (1..%d) / %d rows",
+               ih, kMsaMaxIndexHeads, rows);
+  DGPP_REQUIRE(scores != nullptr, "msa_index_select: the block-score workspace [rows, ih, max_sel] is required");
   if (rows == 0) return 0;
   MsaSelectParams p;
   p.iqk = static_cast<const bf16*>(iqk);
@@ -392,10 +443,14 @@ DGPP_API int dgpp_msa_index_select(const void* iqk, int64_t iqk_stride, const vo
   p.scores = static_cast<float*>(scores);
   p.rows = rows; p.ih = ih; p.page = page; p.max_blocks = max_blocks; p.sel_block = sel_block; p.topk = topk;
   p.max_sel = max_sel;
-  const size_t smem = static_cast<size_t>(max_sel) * sizeof(float);
-  dim3 grid(ih, rows);
-  if (di == 64) msa_index_select_kernel<64><<<grid, kMsaThreads, smem, st>>>(p);
-  else msa_index_select_kernel<128><<<grid, kMsaThreads, smem, st>>>(p);
+  // scores, then the pick
+  const size_t smem_score = static_cast<size_t>(ih) * di * sizeof(float) +
+                            static_cast<size_t>(kMsaScoreWarps) * 32 * (di + 8) * sizeof(bf16);
+  dim3 grid_score(dgpp_ceil_div(max_sel, kMsaScoreWarps), rows);
+  if (di == 64) msa_index_score_kernel<64><<<grid_score, kMsaScoreWarps * 32, smem_score, st>>>(p);
+  else msa_index_score_kernel<128><<<grid_score, kMsaScoreWarps * 32, smem_score, st>>>(p);
+  DGPP_CUDA_OK(cudaGetLastError());
+  msa_index_pick_kernel<<<dim3(ih, rows), kMsaThreads, static_cast<size_t>(max_sel) * sizeof(float), st>>>(p);
   DGPP_CUDA_OK(cudaGetLastError());
   return 0;
 }

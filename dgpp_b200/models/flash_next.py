@@ -272,7 +272,7 @@ class FlashNextRunner(RowRunner):
             self.iqk = e(max_rows, (q.index_heads + 1) * q.index_dim)
             self.sel = torch.empty(max_rows, c.kv_heads, q.select_k + 1, dtype=torch.int32, device=device)
             self.max_sel = (max_seq_len + c.page - 1) // c.page + 1
-            self.sp_splits = 4
+            self.sp_splits = 8
             self.sp_scratch = (torch.empty(max_rows * c.q_heads * self.sp_splits * 2, dtype=torch.float32, device=device),
                                torch.empty(max_rows * c.q_heads * self.sp_splits * c.head_dim, dtype=torch.float32, device=device))
 

@@ -194,10 +194,11 @@ class MinimaxRunner(RowRunner):
         self.iqk = e(max_rows, (c.kv_heads + 1) * c.index_dim)
         self.attn = e(max_rows, c.q_heads * d)
         self.sel = torch.empty(max_rows, c.kv_heads, c.sparse_topk, dtype=torch.int32, device=device)
+        self.idx_scores = torch.empty(max_rows, c.kv_heads, self.max_sel, dtype=torch.float32, device=device)
         self.gu = e(max_rows, 2 * c.dense_ffn)
         self.act = e(max_rows, c.dense_ffn)
         # a row reads at most sparse_topk blocks: a few chunks per (row, kv head) fill the machine at decode widths
-        self.splits = 4
+        self.splits = 8
         self.scratch = (torch.empty(max_rows * c.q_heads * self.splits * 2, dtype=torch.float32, device=device),
                         torch.empty(max_rows * c.q_heads * self.splits * d, dtype=torch.float32, device=device))
 
@@ -212,7 +213,7 @@ class MinimaxRunner(RowRunner):
         ops.msa_index_prep(iqk, positions, row_req, bt, self.m.inv_freq, L.index_q_norm, L.index_k_norm, self.index[i].k,
                            c.kv_heads, c.index_dim, c.rotary_dim, c.eps, one_plus_w=True)
         ops.msa_index_select(iqk, self.index[i].k, bt, row_req, positions, c.kv_heads, c.index_dim, c.sparse_block,
-                             c.sparse_topk, self.max_sel, out=sel)
+                             c.sparse_topk, self.max_sel, out=sel, scores=self.idx_scores[:rows])
         ops.attn_decode(qkv, qkv.stride(0), cache, bt, row_req, positions, c.q_heads, c.kv_heads, c.head_dim,
                         self.att_scale, splits=self.splits, scratch=self.scratch, out=attn, sel=sel, sel_block=c.sparse_block)
         ops.linear(attn, L.o, out=out)

@@ -523,10 +523,13 @@ def msa_index_select(iqk, index_cache, block_table, row_req, positions, ih: int,
                      max_sel: int, out=None, scores=None):
     """Block selection of block-sparse attention -> int32 [rows, ih, topk]: ascending ids of the `topk` blocks (of
     sel_block tokens) with the largest per-block maximum of <index query, index key> over the visible tokens, the
-    row's own block always among them; -1 padded.  scores: optional fp32 [rows, ih, max_sel] out."""
+    row's own block always among them; -1 padded.  scores: fp32 [rows, ih, max_sel] workspace (the block scores stay
+    there; allocated when not given: pass one inside captured passes)."""
     rows = positions.numel()
     if out is None:
         out = torch.empty(rows, ih, topk, dtype=torch.int32, device=positions.device)
+    if scores is None:
+        scores = torch.empty(rows, ih, max_sel, dtype=torch.float32, device=positions.device)
     call("dgpp_msa_index_select", ptr(iqk), iqk.stride(0), ptr(index_cache), ptr(block_table), ptr(row_req),
          ptr(positions), ptr(out), ptr(scores), rows, ih, di, index_cache.shape[1], block_table.shape[1], sel_block,
          topk, max_sel, stream_ptr())
