@@ -239,6 +239,13 @@ def bench_sparse_attn(args, dev):
     kept = min(topk, ctx // blk + 1) * blk
     report(args, "attn_decode_sparse", ms_att, bytes_=2.0 * rows * kept * hkv * d, rows=rows, ctx=ctx, kept_tokens=kept, hq=hq,
            hkv=hkv, head_dim=d, splits=sp)
+    for tsp in (1, 2, 4):
+        f_tc = lambda: ops.attn_decode_tc(q, q.stride(0), kv.layers[0], kv.block_table, req, pos, hq, hkv, d, 0.088, splits=tsp,
+                                          scratch=scratch, out=out, sel=sel, sel_block=blk)
+        ms_tc = run([f_tc] * 4, args)
+        ops.check_status()
+        report(args, "attn_decode_tc_sparse", ms_tc, bytes_=2.0 * rows * kept * hkv * d, rows=rows, ctx=ctx, kept_tokens=kept,
+               hq=hq, hkv=hkv, head_dim=d, splits=tsp)
 
 
 def bench_engram(args, dev):

@@ -18,6 +18,9 @@
 // accumulation (128 threads).  S^T, O^T and the P operand are double buffered so MMA1 of tile i + 1
 // overlaps the softmax of tile i.  Every wait is bounded (status code + clean exit).
 // Partials (m, l, acc) use the layout of attn_decode.cu and are merged by the same combine kernel.
+// Block-selection form (sel [rows, hkv, sel_k], see attn_decode.cu): the CTA walks the concatenation of the listed
+// blocks as one virtual sequence; the producer and the scale loads translate virtual positions to cache positions
+// (sel_block is a multiple of the page, so a page never straddles two listed blocks).
 // (reference counterparts: src/kernels/full_attn.cu:163,1234 decode row / block-decode kernels, mma.sync m16n8k32.)
 #include <cuda.h>
 #include <math.h>
@@ -49,6 +52,8 @@ struct AttnTcParams {
   DeviceStatus* status;
   int rows, hq, hkv, page, max_blocks, splits, window;
   float scale;
+  const int32_t* sel;     // optional block selection, null = dense
+  int sel_k, sel_block;
 };
 
 __device__ __forceinline__ uint32_t sw128_byte(uint32_t row, uint32_t byte_in_row) {
@@ -85,7 +90,24 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
   const int req = p.row_req[row];
-  const int len = p.positions[row] + 1;
+  const int pos_row = p.positions[row];
+  int len = pos_row + 1;
+  const int32_t* sl = nullptr;
+  int sel_n = 0;
+  if (p.sel != nullptr) {
+    // the list is the previous kernel's output: nothing of it may be read before that kernel has finished
+    pdl_wait();
+    sl = p.sel + (static_cast<size_t>(row) * p.hkv + kvh) * p.sel_k;
+    for (int j = 0; j < p.sel_k; ++j) sel_n += sl[j] >= 0 ? 1 : 0;
+    len = sel_n > 0 ? (sel_n - 1) * p.sel_block + pos_row % p.sel_block + 1 : 0;   // every listed block is full but the last
+  }
+  // virtual position -> cache position (identity without a selection; clamped into the listed blocks and to the row's
+  // own position, so that padding tokens of the last tile still address pages the request owns)
+  auto cache_pos = [&](int v) {
+    if (sl == nullptr) return v;
+    const int vb = max(0, min(v / p.sel_block, sel_n - 1));
+    return min(sl[vb] * p.sel_block + v % p.sel_block, pos_row);
+  };
   const int first = (p.window > 0 && len > p.window) ? len - p.window : 0;
   const int base = first & ~(kAdTile - 1);
   const int total_tiles = (len - base + kAdTile - 1) / kAdTile;
@@ -164,7 +186,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         mbar_expect_tx(&kv_full[s], 2 * kStage);
         const int page0 = (base + (tile_begin + i) * kAdTile) / p.page;
         for (int pg = 0; pg < ppt; ++pg) {
-          const int pi = min(page0 + pg, p.max_blocks - 1);
+          const int pi = min(sl == nullptr ? page0 + pg : cache_pos((page0 + pg) * p.page) / p.page, p.max_blocks - 1);
           const int blk = bt[pi];
           const int r0 = (blk * p.hkv + kvh) * p.page;
 #pragma unroll
@@ -245,7 +267,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     auto load_scales = [&](int i, float& ks, float& vs, bool& valid) {
       const int t = base + (tile_begin + i) * kAdTile + idx;
       valid = t >= first && t < len;
-      const int tc = min(t, len - 1);
+      const int tc = cache_pos(max(0, min(t, len - 1)));
       const int pi = min(tc / p.page, p.max_blocks - 1);
       const size_t tok = (static_cast<size_t>(bt[pi]) * p.hkv + kvh) * p.page + tc % p.page;
       ks = p.k_scale[tok];
@@ -450,8 +472,12 @@ DGPP_API int dgpp_attn_decode_tc(const void* q, int64_t q_stride, const void* k_
                                  const void* k_scale, const void* v_scale, const void* block_table,
                                  const void* row_req, const void* positions, void* part_ml, void* part_acc,
                                  void* out, int rows, int hq, int hkv, int d, int page, int max_blocks,
-                                 int num_blocks, int splits, float scale, int window, cudaStream_t st) {
+                                 int num_blocks, int splits, float scale, int window, const void* sel, int sel_k,
+                                 int sel_block, cudaStream_t st) {
   DGPP_REQUIRE(d == 128 || d == 256, "attn_decode_tc: head_dim %d (128 or 256)", d);
+  DGPP_REQUIRE(sel == nullptr || (sel_k >= 1 && sel_block >= page && sel_block % page == 0 && window == 0),
+               "attn_decode_tc: a block selection needs sel_k >= 1, blocks of whole pages (%d / %d) and no window", sel_block,
+               page);
   DGPP_REQUIRE(hkv > 0 && hq % hkv == 0 && hq / hkv <= 8, "attn_decode_tc: unsupported head grouping %d/%d", hq, hkv);
   DGPP_REQUIRE(page == 16 || page == 32 || page == 64 || page == 128, "attn_decode_tc: page %d unsupported", page);
   DGPP_REQUIRE(splits >= 1 && (splits == 1 || (part_ml && part_acc)), "attn_decode_tc: scratch required for splits");
@@ -471,6 +497,8 @@ DGPP_API int dgpp_attn_decode_tc(const void* q, int64_t q_stride, const void* k_
   p.status = device_status_ptr();
   p.rows = rows; p.hq = hq; p.hkv = hkv; p.page = page; p.max_blocks = max_blocks; p.splits = splits;
   p.window = window; p.scale = scale;
+  p.sel = static_cast<const int32_t*>(sel);
+  p.sel_k = sel_k; p.sel_block = sel_block;
   const uint64_t total_rows = static_cast<uint64_t>(num_blocks) * hkv * page;
   CUtensorMap tK, tV;
   if (make_tmap_2d(&tK, k_cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d, total_rows, d, 128, page,

@@ -307,8 +307,9 @@ class FlashNextRunner(RowRunner):
                          c.eps, one_plus_w=True)
         ops.qsa_select(iqk, self.idx_comp[j], bt, row_req, positions, q.index_heads, q.index_dim, c.page, q.select_k,
                        self.max_sel, copies=c.kv_heads, out=sel)
-        ops.attn_decode(qkv, qkv.stride(0), cache, bt, row_req, positions, c.q_heads, c.kv_heads, c.head_dim, self.att_scale,
-                        splits=self.sp_splits, scratch=self.sp_scratch, out=attn, sel=sel, sel_block=c.page)
+        fn = ops.attn_decode_tc if (self.tc_attn and rows <= 32) else ops.attn_decode
+        fn(qkv, qkv.stride(0), cache, bt, row_req, positions, c.q_heads, c.kv_heads, c.head_dim, self.att_scale,
+           splits=self.sp_splits, scratch=self.sp_scratch, out=attn, sel=sel, sel_block=c.page)
 
     def _mix(self, s: GrSite, rows: int) -> torch.Tensor:
         c = self.c

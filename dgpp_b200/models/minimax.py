@@ -214,8 +214,9 @@ class MinimaxRunner(RowRunner):
                            c.kv_heads, c.index_dim, c.rotary_dim, c.eps, one_plus_w=True)
         ops.msa_index_select(iqk, self.index[i].k, bt, row_req, positions, c.kv_heads, c.index_dim, c.sparse_block,
                              c.sparse_topk, self.max_sel, out=sel, scores=self.idx_scores[:rows])
-        ops.attn_decode(qkv, qkv.stride(0), cache, bt, row_req, positions, c.q_heads, c.kv_heads, c.head_dim,
-                        self.att_scale, splits=self.splits, scratch=self.scratch, out=attn, sel=sel, sel_block=c.sparse_block)
+        fn = ops.attn_decode_tc if (self.tc_attn and rows <= 32 and c.sparse_block % 16 == 0) else ops.attn_decode
+        fn(qkv, qkv.stride(0), cache, bt, row_req, positions, c.q_heads, c.kv_heads, c.head_dim, self.att_scale,
+           splits=self.splits, scratch=self.scratch, out=attn, sel=sel, sel_block=c.sparse_block)
         ops.linear(attn, L.o, out=out)
 
     def _ffn(self, i: int, L: MinimaxLayer, xn, out) -> None:

@@ -40,7 +40,7 @@ _SIGNATURES = {
     "dgpp_qsa_compress": [P, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
     "dgpp_qsa_select": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "dgpp_msa_index_select": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
-    "dgpp_attn_decode_tc": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "dgpp_attn_decode_tc": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, I, I, P],
     "dgpp_attn_prefill_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_attn_prefill_tc256": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "dgpp_decode_advance": [P, P, P, P, P, I, I, P],

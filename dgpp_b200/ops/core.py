@@ -574,7 +574,7 @@ def stream_wait(timeout_s: float, stream=None) -> bool:
 
 def attn_decode_tc(q, q_stride: int, cache, block_table, row_req, positions, hq: int, hkv: int, d: int,
                    scale: float, splits: int = 1, scratch=None, out=None, window: int = 0,
-                   partials_only: bool = False):
+                   partials_only: bool = False, sel=None, sel_block: int = 0):
     """Tensor-core (tcgen05, FP8 operands) decode attention over an FP8 paged cache; head_dim 128 or 256.
     partials_only (splits > 1): stop after the split-KV pass and leave the (max, sum) pairs and unnormalised
     accumulators in `scratch` for attn_combine_quant, which folds them while it quantises; returns None."""
@@ -594,7 +594,8 @@ def attn_decode_tc(q, q_stride: int, cache, block_table, row_req, positions, hq:
         ml, acc = scratch
     call("dgpp_attn_decode_tc", ptr(q), q_stride, ptr(cache.k), ptr(cache.v), ptr(cache.k_scale),
          ptr(cache.v_scale), ptr(block_table), ptr(row_req), ptr(positions), ptr(ml), ptr(acc), ptr(out), rows, hq,
-         hkv, d, cache.page, block_table.shape[1], cache.k.shape[0], splits, float(scale), window, stream_ptr())
+         hkv, d, cache.page, block_table.shape[1], cache.k.shape[0], splits, float(scale), window, ptr(sel),
+         0 if sel is None else sel.shape[2], sel_block, stream_ptr())
     return out
 
 
