@@ -113,10 +113,12 @@ void bind_grammar(py::module_& m) {
      py::arg("budget") = int64_t(-1));
 
   // ---- streaming tool-call parser
-  py::enum_<tools::Format>(m, "ToolFormat").value("JsonTags", tools::Format::JsonTags).value("ArgTags", tools::Format::ArgTags).value("Dsml", tools::Format::Dsml);
+  py::enum_<tools::Format>(m, "ToolFormat").value("JsonTags", tools::Format::JsonTags).value("ArgTags", tools::Format::ArgTags).value("Dsml", tools::Format::Dsml).value("NsXml", tools::Format::NsXml);
   py::class_<tools::ToolParser>(m, "ToolParser")
       .def(py::init<tools::Format, std::string>(), py::arg("format"), py::arg("id_prefix") = "call_")
       .def("calls", &tools::ToolParser::calls)
+      .def("set_namespace", &tools::ToolParser::set_namespace)
+      .def("set_tools", [](tools::ToolParser& p, const std::string& tools_json) { p.set_tools(json::parse(tools_json)); })
       // events: ("content", text) or ("tool_call", index, id, name, arguments_json)
       .def("feed", [](tools::ToolParser& p, const py::bytes& piece) {
         py::list out;

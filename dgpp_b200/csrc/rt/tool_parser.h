@@ -8,6 +8,12 @@
 //   Dsml       <｜DSML｜tool_calls> <｜DSML｜invoke name="f"> <｜DSML｜parameter name="k" string="true|false">v</｜DSML｜parameter>
 //              ... </｜DSML｜invoke> </｜DSML｜tool_calls>   (every invoke is one call; string="false" values are JSON; the
 //              tool_calls wrapper tags are formatting and never reach the content)
+//   NsXml      NS<tool_call> NS<invoke name="f"> NS<k>v NS</k> ... NS</invoke> ... NS</tool_call>   (MiniMax style: the
+//              namespace marker NS, "]<]minimax[>[" by default, precedes every structural tag, so '<' and '&' inside
+//              values are plain bytes; a block may hold several invokes = several calls; values nest: an object is
+//              NS<key>...NS</key> children, an array NS<item>...NS</item> children.  A scalar takes its JSON type from
+//              the tool's parameter schema when the tools were given (`set_tools`), else it is kept as a JSON literal
+//              when it reads as a number / true / false / null and as a string otherwise)
 // Content outside the tags is released as soon as it cannot be the beginning of an opening tag.  A call is emitted
 // when its closing tag has arrived (name, arguments as one JSON text, running index, generated id).  A body that is
 // not a valid call, or text still open at finish(), is returned as content: nothing the model wrote is dropped.
@@ -23,7 +29,7 @@
 namespace dgpp {
 namespace tools {
 
-enum class Format { JsonTags, ArgTags, Dsml };
+enum class Format { JsonTags, ArgTags, Dsml, NsXml };
 
 struct Event {
   bool is_call = false;
@@ -39,11 +45,22 @@ class ToolParser {
       open_ = "<\xef\xbd\x9c" "DSML\xef\xbd\x9c" "invoke";
       close_ = "</\xef\xbd\x9c" "DSML\xef\xbd\x9c" "invoke>";
       silent_ = {"<\xef\xbd\x9c" "DSML\xef\xbd\x9c" "tool_calls>", "</\xef\xbd\x9c" "DSML\xef\xbd\x9c" "tool_calls>"};
+    } else if (f == Format::NsXml) {
+      set_namespace("]<]minimax[>[");
     } else {
       open_ = "<tool_call>";
       close_ = "</tool_call>";
     }
   }
+
+  // NsXml: the namespace marker of the model's template.
+  void set_namespace(const std::string& ns) {
+    ns_ = ns;
+    open_ = ns + "<tool_call>";
+    close_ = ns + "</tool_call>";
+  }
+  // The request's tools (an OpenAI `tools` array): NsXml reads the parameter schemas for value types.
+  void set_tools(const json::Value& tools) { tools_ = tools; }
 
   std::vector<Event> feed(const std::string& piece) {
     buf_ += piece;
@@ -97,6 +114,21 @@ class ToolParser {
         const std::string body = buf_.substr(0, p);
         buf_.erase(0, p + close_.size());
         inside_ = false;
+        if (fmt_ == Format::NsXml) {
+          std::vector<Event> calls;
+          if (parse_ns_block(body, calls)) {
+            for (auto& c : calls) {
+              c.is_call = true;
+              c.index = calls_++;
+              c.id = id_prefix_ + std::to_string(c.index);
+              out.push_back(std::move(c));
+            }
+            skip_newline_ = true;
+          } else {
+            emit_content(out, open_ + body + close_);
+          }
+          continue;
+        }
         Event e;
         if (parse_body(body, e)) {
           e.is_call = true;
@@ -213,7 +245,124 @@ class ToolParser {
     return true;
   }
 
+  // ---- NsXml
+  struct NsReader {
+    const std::string& t;
+    const std::string& ns;
+    size_t pos = 0;
+    bool accept(const std::string& s) {
+      if (t.compare(pos, s.size(), s) != 0) return false;
+      pos += s.size();
+      return true;
+    }
+    void ws() {
+      while (pos < t.size() && (t[pos] == ' ' || t[pos] == '\n' || t[pos] == '\r' || t[pos] == '\t')) ++pos;
+    }
+    static std::string type_of(const json::Value* schema) {
+      if (!schema || !schema->is_object()) return "";
+      const json::Value* ty = schema->find("type");
+      if (ty && ty->is_string()) return ty->as_string();
+      if (ty && ty->is_array())
+        for (const auto& x : ty->items())
+          if (x.is_string() && x.as_string() != "null") return x.as_string();
+      if (schema->find("properties")) return "object";
+      if (schema->find("items")) return "array";
+      return "";
+    }
+    // the value between the current position and NS</close>; consumes the closing tag
+    bool value(const std::string& close, const json::Value* schema, json::Value* out, int depth, bool root) {
+      if (depth > 64) return false;
+      const std::string closer = ns + "</" + close + ">";
+      const std::string type = type_of(schema);
+      size_t look = pos;
+      while (look < t.size() && (t[look] == ' ' || t[look] == '\n' || t[look] == '\r' || t[look] == '\t')) ++look;
+      const bool children = t.compare(look, ns.size() + 1, ns + "<") == 0 && t.compare(look, closer.size(), closer) != 0;
+      const bool array = type == "array" ? (children || t.compare(look, closer.size(), closer) == 0)
+                                         : (type.empty() && children && t.compare(look, ns.size() + 6, ns + "<item>") == 0);
+      const bool object = !array && (root || (type == "object" && (children || t.compare(look, closer.size(), closer) == 0)) ||
+                                     (type.empty() && children));
+      if (array || object) {
+        *out = array ? json::Value::array() : json::Value::object();
+        for (;;) {
+          ws();
+          if (accept(closer)) return true;
+          if (!accept(ns + "<")) return false;
+          const size_t end = t.find('>', pos);
+          if (end == std::string::npos || end == pos) return false;
+          const std::string key = t.substr(pos, end - pos);
+          if (key.find_first_of("<>/\"' \n\r\t") != std::string::npos) return false;
+          if (array && key != "item") return false;
+          if (!array && out->find(key)) return false;
+          pos = end + 1;
+          const json::Value* child = nullptr;
+          if (schema && schema->is_object()) {
+            if (array) {
+              child = schema->find("items");
+            } else {
+              const json::Value* props = schema->find("properties");
+              if (props && props->is_object()) child = props->find(key);
+              if (!child) {
+                const json::Value* extra = schema->find("additionalProperties");
+                if (extra && extra->is_object()) child = extra;
+              }
+            }
+          }
+          json::Value v;
+          if (!value(key, child, &v, depth + 1, false)) return false;
+          if (array) out->push(std::move(v));
+          else out->set(key, std::move(v));
+        }
+      }
+      const size_t end = t.find(closer, pos);
+      if (end == std::string::npos) return false;
+      const std::string raw = t.substr(pos, end - pos);
+      pos = end + closer.size();
+      if (type == "string") { *out = json::Value(raw); return true; }
+      // a JSON literal when it reads as one (always tried for the non-string types, and for untyped scalars only
+      // numbers / true / false / null count)
+      try {
+        json::Value lit = json::parse(trim(raw));
+        const bool scalar_lit = lit.is_number() || lit.is_bool() || lit.is_null();
+        if (!type.empty() || scalar_lit) { *out = std::move(lit); return true; }
+      } catch (const std::exception&) {
+      }
+      *out = json::Value(raw);
+      return true;
+    }
+  };
+  const json::Value* params_schema(const std::string& name) const {
+    if (!tools_.is_array()) return nullptr;
+    for (const auto& tool : tools_.items()) {
+      const json::Value* fn = tool.is_object() ? tool.find("function") : nullptr;
+      if (!fn || !fn->is_object()) continue;
+      const json::Value* n = fn->find("name");
+      if (n && n->is_string() && n->as_string() == name) return fn->find("parameters");
+    }
+    return nullptr;
+  }
+  bool parse_ns_block(const std::string& body, std::vector<Event>& calls) const {
+    NsReader r{body, ns_};
+    for (;;) {
+      r.ws();
+      if (r.pos == body.size()) return !calls.empty();
+      if (!r.accept(ns_ + "<invoke name=\"")) return false;
+      const size_t q = body.find('"', r.pos);
+      if (q == std::string::npos || q == r.pos) return false;
+      Event e;
+      e.name = body.substr(r.pos, q - r.pos);
+      if (e.name.find_first_of("<>\r\n") != std::string::npos) return false;
+      r.pos = q;
+      if (!r.accept("\">")) return false;
+      json::Value args;
+      if (!r.value("invoke", params_schema(e.name), &args, 0, true)) return false;
+      e.arguments = args.dump();
+      calls.push_back(std::move(e));
+    }
+  }
+
   Format fmt_;
+  std::string ns_;
+  json::Value tools_;
   std::string id_prefix_;
   std::string open_, close_;
   std::vector<std::string> silent_;

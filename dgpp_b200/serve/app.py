@@ -348,6 +348,8 @@ class Server:
                                    rt.StopScanner(list(r["stop"])), t_submit=time.time())
             if chat and r["tools_json"] not in ("null", "[]") and json.loads(r["tool_choice_json"]) != "none":
                 self.live[rid].tool_parser = rt.ToolParser(self.tool_format, f"call_{uuid.uuid4().hex[:12]}_")
+                if self.tool_format == rt.ToolFormat.NsXml:          # value types come from the tools' parameter schemas
+                    self.live[rid].tool_parser.set_tools(r["tools_json"])
             kw = dict(eos_ids=[] if r["ignore_eos"] else self.eos_ids, ignore_eos=r["ignore_eos"],
                       prefix_cache=r["prefix_cache"], cache_key=r["prompt_cache_key"])
             if self.world is not None:
