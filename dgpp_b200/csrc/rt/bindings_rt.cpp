@@ -50,6 +50,19 @@ class PyEngine : public SchedulerEngine {
   std::vector<std::vector<int32_t>> step_batch(const std::vector<int>& slots) override {
     PYBIND11_OVERRIDE_PURE(std::vector<std::vector<int32_t>>, SchedulerEngine, step_batch, slots);
   }
+  // Python: mixed_step((slot, tokens, pos, last), slots) -> None (no such pass) or (first, [[tokens of slots[i]], ...])
+  bool mixed_step(const PrefillPiece& p, const std::vector<int>& slots, int32_t* first,
+                  std::vector<std::vector<int32_t>>* out) override {
+    py::gil_scoped_acquire gil;
+    py::function f = py::get_override(static_cast<const SchedulerEngine*>(this), "mixed_step");
+    if (!f) return false;
+    py::object r = f(py::make_tuple(p.slot, std::vector<int32_t>(p.tokens, p.tokens + p.count), p.pos, p.last), slots);
+    if (r.is_none()) return false;
+    py::tuple t = r.cast<py::tuple>();
+    *first = t[0].cast<int32_t>();
+    *out = t[1].cast<std::vector<std::vector<int32_t>>>();
+    return true;
+  }
   int max_tokens_per_step() const override { PYBIND11_OVERRIDE(int, SchedulerEngine, max_tokens_per_step); }
   int64_t usable_prefix(const std::vector<int32_t>& blocks) const override {
     PYBIND11_OVERRIDE(int64_t, SchedulerEngine, usable_prefix, blocks);
@@ -118,7 +131,7 @@ class PyScheduler {
     const PrefixStats& p = sched_->prefix_stats();
     py::dict d;
     d["ticks"] = m.ticks; d["admitted"] = m.admitted; d["retired"] = m.retired; d["shed"] = m.shed;
-    d["decode_passes"] = m.decode_passes; d["decode_tokens"] = m.decode_tokens;
+    d["decode_passes"] = m.decode_passes; d["decode_tokens"] = m.decode_tokens; d["mixed_passes"] = m.mixed_passes;
     d["prefill_tokens"] = m.prefill_tokens; d["prefill_calls"] = m.prefill_calls;
     d["prefix_hit_tokens"] = m.prefix_hit_tokens; d["cancelled"] = m.cancelled;
     d["queue_peak"] = m.queue_peak; d["active_peak"] = m.active_peak;
@@ -156,6 +169,8 @@ void bind_more(py::module_& m) {
       .def_readonly("prefill_calls", &FakeEngine::prefill_calls)
       .def_readonly("prefill_tokens", &FakeEngine::prefill_tokens)
       .def_readonly("decode_passes", &FakeEngine::decode_passes)
+      .def_readonly("mixed_calls", &FakeEngine::mixed_calls)
+      .def_readwrite("mixed", &FakeEngine::mixed)
       .def_static("expected", &FakeEngine::expected);
 
   py::enum_<AdmissionPolicy>(m, "AdmissionPolicy")
@@ -172,7 +187,8 @@ void bind_more(py::module_& m) {
       .def_readwrite("prefix_min_tokens", &SchedulerConfig::prefix_min_tokens)
       .def_readwrite("prefix_max_entries", &SchedulerConfig::prefix_max_entries)
       .def_readwrite("grow_margin_tokens", &SchedulerConfig::grow_margin_tokens)
-      .def_readwrite("prefill_group_max", &SchedulerConfig::prefill_group_max);
+      .def_readwrite("prefill_group_max", &SchedulerConfig::prefill_group_max)
+      .def_readwrite("mixed_pass", &SchedulerConfig::mixed_pass);
 
   py::class_<PyScheduler>(m, "Scheduler")
       .def(py::init<py::object, const SchedulerConfig&>())

@@ -226,6 +226,7 @@ struct ClusterConfig {
   int64_t max_context = 32768;
   int prefill_chunk = 2048;
   int prefill_group_max = 4;                // readers packed into one prefill pass (1 = one request per pass)
+  bool mixed_pass = false;                  // a reader's chunk rides in the pass of the decode step
   std::string kv_dtype = "fp8";
   int64_t kv_headroom_mib = 4096;
   bool prefix_cache = true;
@@ -254,6 +255,7 @@ struct ClusterConfig {
     if (!v.is_object()) throw std::runtime_error("config: the top level must be an object");
     static const std::set<std::string> known = {
         "model", "host", "port", "tensor_parallel", "expert_parallel", "max_concurrency", "max_context", "prefill_chunk", "prefill_group_max",
+        "mixed_pass",
         "kv_dtype", "kv_headroom_mib", "prefix_cache", "prefix_min_tokens", "scheduler_policy", "mtp_depth",
         "sampling_candidates", "fuse_all_reduce", "log_level", "engine_decode_splits", "engine_fuse_combine",
         "engine_l2_prefetch", "engine_fp4_splits", "engine_cluster_splitk", "engine_fp4_preload", "engine_layer_kernel",
@@ -271,6 +273,7 @@ struct ClusterConfig {
     c.max_context = v.get_int("max_context", c.max_context);
     c.prefill_chunk = static_cast<int>(v.get_int("prefill_chunk", c.prefill_chunk));
     c.prefill_group_max = static_cast<int>(v.get_int("prefill_group_max", c.prefill_group_max));
+    c.mixed_pass = v.get_bool("mixed_pass", false);
     c.kv_dtype = v.get_string("kv_dtype", c.kv_dtype);
     c.kv_headroom_mib = v.get_int("kv_headroom_mib", c.kv_headroom_mib);
     c.prefix_cache = v.get_bool("prefix_cache", true);
@@ -317,6 +320,7 @@ struct ClusterConfig {
     v.set("kv_dtype", kv_dtype); v.set("kv_headroom_mib", kv_headroom_mib); v.set("log_level", log_level);
     v.set("max_concurrency", max_concurrency); v.set("max_context", max_context); v.set("model", model);
     v.set("mtp_depth", mtp_depth); v.set("port", port); v.set("prefill_chunk", prefill_chunk); v.set("prefill_group_max", prefill_group_max);
+    v.set("mixed_pass", mixed_pass);
     v.set("prefix_cache", prefix_cache); v.set("prefix_min_tokens", prefix_min_tokens);
     v.set("sampling_candidates", sampling_candidates); v.set("scheduler_policy", scheduler_policy);
     v.set("tensor_parallel", tensor_parallel);

@@ -75,6 +75,16 @@ class FakeEngine : public SchedulerEngine {
     }
     return out;
   }
+  bool mixed_step(const PrefillPiece& piece, const std::vector<int>& slots, int32_t* first,
+                  std::vector<std::vector<int32_t>>* out) override {
+    if (!mixed) return false;
+    ++mixed_calls;
+    *out = step_batch(slots);
+    *first = prefill(piece.slot, piece.tokens, piece.pos, piece.count, piece.last);
+    --decode_passes;          // one engine call, counted as mixed
+    --prefill_calls;
+    return true;
+  }
   std::vector<int32_t> slot_blocks(int slot) const override { return slots_.at(slot).blocks; }
   void retain_block(int32_t b) override { table_.retain(b); }
   void release_block(int32_t b) override { table_.release(b); }
@@ -85,7 +95,8 @@ class FakeEngine : public SchedulerEngine {
     s = S();
   }
 
-  int64_t prefill_calls = 0, prefill_tokens = 0, decode_passes = 0;
+  int64_t prefill_calls = 0, prefill_tokens = 0, decode_passes = 0, mixed_calls = 0;
+  bool mixed = false;            // answer mixed_step (tests of the scheduler's mixed pass)
 
   // The token stream a request must produce, independent of scheduling (oracle for tests).
   static std::vector<int32_t> expected(const std::vector<int32_t>& prompt, int64_t n, int vocab) {

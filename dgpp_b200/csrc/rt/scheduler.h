@@ -68,6 +68,15 @@ class SchedulerEngine {
   }
   // One decode pass; result[i] holds the new tokens of slots[i] (one, or several with speculative decoding).
   virtual std::vector<std::vector<int32_t>> step_batch(const std::vector<int>& slots) = 0;
+  // Mixed pass: the rows of one prefill piece and one decode step of `slots` in ONE engine call (the weights are read
+  // once, the decoders do not wait behind the reader's chunk).  Returns false when the engine has no such pass for
+  // these requests; the scheduler then runs the piece and the decode pass one after the other.  *first: the piece's
+  // first generated token when it is `last`, else -1; (*out)[i]: the new tokens of slots[i].
+  virtual bool mixed_step(const PrefillPiece& piece, const std::vector<int>& slots, int32_t* first,
+                          std::vector<std::vector<int32_t>>* out) {
+    (void)piece; (void)slots; (void)first; (void)out;
+    return false;
+  }
   virtual int max_tokens_per_step() const { return 1; }
   // Physical blocks of a slot, in position order (for publishing to the prefix cache).
   virtual std::vector<int32_t> slot_blocks(int slot) const = 0;
@@ -129,12 +138,16 @@ struct SchedulerConfig {
   // `prefill_group_max` pieces whose tokens sum to at most `prefill_chunk` (oldest reader first, every reader gets an
   // equal share of what the budget leaves before the leftovers go to the oldest).  1 = one reader per engine call.
   int prefill_group_max = 1;
+  // Mixed passes: while requests are decoding, the oldest reader's next chunk rides in the same engine call as their
+  // decode step (engines without such a pass keep the two calls).  At most `prefill_budget_busy` prompt tokens.
+  bool mixed_pass = false;
 };
 
 struct SchedMeters {
   int64_t ticks = 0, admitted = 0, retired = 0, shed = 0, decode_passes = 0, decode_tokens = 0;
   int64_t prefill_tokens = 0, prefill_calls = 0, prefix_hit_tokens = 0, cancelled = 0;
   int64_t queue_peak = 0, active_peak = 0;
+  int64_t mixed_passes = 0;      // engine calls that carried a prefill piece and a decode step together
 };
 
 class Scheduler {
@@ -179,8 +192,10 @@ class Scheduler {
     sweep_cancels();
     if (cfg_.policy == AdmissionPolicy::GrowOnDemand) grow_reservations();
     admit();
+    tick_prefill_used_ = 0;
+    const bool decoded = cfg_.mixed_pass && mixed_pass(&produced);
     produced += advance_prefills();
-    produced += decode_pass();
+    if (!decoded) produced += decode_pass();
     meters_.active_peak = std::max<int64_t>(meters_.active_peak, active_count());
     return produced;
   }
@@ -381,10 +396,57 @@ class Scheduler {
     }
   }
 
+  // The oldest reader's next chunk together with one decode step of everybody who is decoding.  True when the engine
+  // ran the mixed pass (the tick then needs no decode pass of its own); the chunk counts against the tick's budget.
+  bool mixed_pass(int64_t* produced) {
+    std::vector<int> batch;
+    int reader = -1;
+    for (size_t s = 0; s < slots_.size(); ++s) {
+      if (!slots_[s].live) continue;
+      if (slots_[s].phase == Phase::Decode) batch.push_back(static_cast<int>(s));
+      else if (slots_[s].phase == Phase::Prefill && (reader < 0 || slots_[s].arrival < slots_[reader].arrival))
+        reader = static_cast<int>(s);
+    }
+    if (batch.empty() || reader < 0) return false;
+    Slot& sl = slots_[reader];
+    const int64_t left = sl.prompt_len - sl.prefilled;
+    const int64_t n = std::min<int64_t>({left, cfg_.prefill_budget_busy, cfg_.prefill_chunk});
+    if (n <= 0) return false;
+    const SchedulerEngine::PrefillPiece piece{reader, sl.tokens.data() + sl.prefilled, sl.prefilled, n, n == left};
+    int32_t first = -1;
+    std::vector<std::vector<int32_t>> out;
+    if (!eng_->mixed_step(piece, batch, &first, &out) || out.size() != batch.size()) return false;
+    ++meters_.mixed_passes;
+    ++meters_.prefill_calls;
+    ++meters_.decode_passes;
+    fold("prefill", sl.req.id, (sl.prefilled << 20) | n);
+    meters_.prefill_tokens += n;
+    sl.prefilled += n;
+    tick_prefill_used_ += n;
+    // the decoders first (their tokens were computed against the state before this pass), then the reader's first token
+    int64_t got = 0;
+    for (size_t i = 0; i < batch.size(); ++i) {
+      const int s = batch[i];
+      slots_[s].prefilled = static_cast<int64_t>(slots_[s].tokens.size());
+      for (int32_t t : out[i]) {
+        if (!slots_[s].live) break;
+        got += accept_token(s, t) ? 1 : 0;
+      }
+    }
+    meters_.decode_tokens += got;
+    if (piece.last) {
+      sl.phase = Phase::Decode;
+      publish(reader, sl.prompt_len);
+      got += accept_token(reader, first) ? 1 : 0;
+    }
+    *produced += got;
+    return true;
+  }
+
   int64_t advance_prefills() {
     bool decoders = false;
     for (const auto& s : slots_) decoders |= s.live && s.phase == Phase::Decode;
-    int64_t budget = decoders ? cfg_.prefill_budget_busy : cfg_.prefill_budget_idle;
+    int64_t budget = (decoders ? cfg_.prefill_budget_busy : cfg_.prefill_budget_idle) - tick_prefill_used_;
     int64_t produced = 0;
     // oldest reader first
     std::vector<int> order;
@@ -550,6 +612,7 @@ class Scheduler {
   std::deque<Pending> queue_;
   std::vector<std::string> cancels_;
   SchedMeters meters_;
+  int64_t tick_prefill_used_ = 0;      // prompt tokens a mixed pass already took out of this tick's budget
   int64_t next_arrival_ = 0;
   uint64_t digest_ = kFnvSeed;
 };

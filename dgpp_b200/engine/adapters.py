@@ -454,6 +454,34 @@ class KernelEngine(EmbedSplice, rt.SchedulerEngine):
                 out.append(-1)
         return out
 
+    def mixed_step(self, piece, slots):
+        """One pass for a prefill piece and one decode step of `slots`: the piece's rows and one row per decoder (its
+        pending token at its next position) go through `LLMEngine.prefill_group` together, so the weights are read once
+        and the decoders do not wait behind the chunk.  None (the scheduler then runs the two calls) when a request of
+        the pass samples, follows a grammar, carries embedding spans or drafts, or the rows do not fit one pass."""
+        s0, toks, pos, last = piece[0], list(piece[1]), piece[2], bool(piece[3])
+        slots = list(slots)
+        involved = [s0] + slots
+        plain = all(not self.slot_cfg[s] and self._slot_embeds[s] is None for s in involved) and not self.spec_k
+        if not plain or len(toks) + len(slots) > self.e.prefill_chunk:
+            return None
+        pieces = [(s0, self._real_ids(toks), pos, last)] + [(s, [self.pending[s]], self.filled[s], True) for s in slots]
+        with self.timer.phase("prefill"):
+            picks = self.e.prefill_group(pieces).tolist()
+        self._poll_device()
+        self.filled[s0] = pos + len(toks)
+        k, first = 0, -1
+        if last:
+            first, k = int(picks[0]), 1
+            self.pending[s0] = first
+        out = []
+        for s in slots:
+            tok = int(picks[k]); k += 1
+            self.filled[s] += 1
+            self.pending[s] = tok
+            out.append([tok])
+        return first, out
+
     def _spec_graph(self, rows: int):
         """One captured forward per row count (rows = requests + draft rows of this pass)."""
         g = self.spec_graphs.get(rows)

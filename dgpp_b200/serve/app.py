@@ -743,6 +743,7 @@ def serve_deployment(config_path: str) -> int:
     sc = rt.SchedulerConfig()
     sc.prefill_chunk = int(cfg["prefill_chunk"])
     sc.prefill_group_max = int(cfg["prefill_group_max"])
+    sc.mixed_pass = bool(cfg.get("mixed_pass", False))
     leader = None
     if world > 1:
         from .world import WorldLeader, run_follower

@@ -350,3 +350,41 @@ def test_engine_can_shorten_a_prefix_hit():
     assert eng.attached == [4]                            # 7 blocks matched, the engine resumes at block 4
     assert s.meters()["prefix_hit_tokens"] == 64
     assert (64, len(prompt) - 64) in eng.prefilled or sum(n for p, n in eng.prefilled if p >= 64) >= len(prompt) - 64
+
+
+def test_mixed_passes_carry_decoders_with_the_readers_chunk():
+    """With mixed passes on, a reader's chunk and the decode step of everybody decoding are one engine call: same
+    tokens as without, fewer engine calls, and decoders advance in every tick a reader is prefilling."""
+    reqs = _trace(n=24, seed=5)
+
+    def run(mixed, engine_mixed=True):
+        eng = rt.FakeEngine(slots=4, block_tokens=16, blocks=200, max_context=1024, vocab=4096)
+        eng.mixed = engine_mixed
+        cfg = rt.SchedulerConfig()
+        cfg.prefix_cache = False
+        cfg.prefill_budget_idle = cfg.prefill_budget_busy = cfg.prefill_chunk = 24
+        cfg.mixed_pass = mixed
+        s = rt.Scheduler(eng, cfg)
+        for rid, p in reqs.items():
+            s.submit(rid, p, 32)
+        s.run(200000)
+        out = {}
+        for kind, rid, a, b in s.events():
+            if kind == "token":
+                out.setdefault(rid, []).append(a)
+        return s.meters(), eng, out
+
+    m0, e0, out0 = run(False)
+    m1, e1, out1 = run(True)
+    for rid, p in reqs.items():
+        assert out0[rid] == out1[rid] == rt.FakeEngine.expected(p, 32, 4096), rid
+    assert m0["mixed_passes"] == 0 and m1["mixed_passes"] > 0 and e1.mixed_calls == m1["mixed_passes"]
+    calls0 = e0.prefill_calls + e0.decode_passes
+    calls1 = e1.prefill_calls + e1.decode_passes + e1.mixed_calls
+    # every mixed pass saves a call, give or take the few ticks whose plan shifts (a reader that finishes inside a mixed
+    # pass takes its first decode step one tick later)
+    assert calls1 < calls0 and abs((calls0 - calls1) - m1["mixed_passes"]) <= 0.05 * m1["mixed_passes"]
+    assert m1["prefill_tokens"] == m0["prefill_tokens"] == sum(len(p) for p in reqs.values())
+    # an engine without a mixed pass: the scheduler falls back to the two calls, nothing changes
+    m2, e2, out2 = run(True, engine_mixed=False)
+    assert out2 == out0 and m2["mixed_passes"] == 0 and e2.prefill_calls == e0.prefill_calls
