@@ -118,6 +118,7 @@ void bind_grammar(py::module_& m) {
       .def(py::init<tools::Format, std::string>(), py::arg("format"), py::arg("id_prefix") = "call_")
       .def("calls", &tools::ToolParser::calls)
       .def("set_namespace", &tools::ToolParser::set_namespace)
+      .def("set_dsml_spaced", &tools::ToolParser::set_dsml_spaced)
       .def("set_tools", [](tools::ToolParser& p, const std::string& tools_json) { p.set_tools(json::parse(tools_json)); })
       // events: ("content", text) or ("tool_call", index, id, name, arguments_json)
       .def("feed", [](tools::ToolParser& p, const py::bytes& piece) {

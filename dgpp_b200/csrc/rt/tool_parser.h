@@ -7,7 +7,9 @@
 //              that parses as JSON is kept as JSON, anything else becomes a string)
 //   Dsml       <｜DSML｜tool_calls> <｜DSML｜invoke name="f"> <｜DSML｜parameter name="k" string="true|false">v</｜DSML｜parameter>
 //              ... </｜DSML｜invoke> </｜DSML｜tool_calls>   (every invoke is one call; string="false" values are JSON; the
-//              tool_calls wrapper tags are formatting and never reach the content)
+//              tool_calls wrapper tags are formatting and never reach the content).  Second dialect (`set_dsml_spaced`):
+//              the marker is followed by a space and the block is "calls": <｜DSML｜ calls> <｜DSML｜ invoke name="ns::f">
+//              <｜DSML｜ parameter name="k" ...>; a name may carry a "namespace::" prefix, which is dropped
 //   NsXml      NS<tool_call> NS<invoke name="f"> NS<k>v NS</k> ... NS</invoke> ... NS</tool_call>   (MiniMax style: the
 //              namespace marker NS, "]<]minimax[>[" by default, precedes every structural tag, so '<' and '&' inside
 //              values are plain bytes; a block may hold several invokes = several calls; values nest: an object is
@@ -53,6 +55,16 @@ class ToolParser {
     }
   }
 
+  // Dsml: the dialect whose marker is followed by a space and whose block is called "calls".
+  void set_dsml_spaced(bool spaced) {
+    const std::string m = std::string("\xef\xbd\x9c" "DSML\xef\xbd\x9c") + (spaced ? " " : "");
+    const std::string block = spaced ? "calls" : "tool_calls";
+    open_ = "<" + m + "invoke";
+    close_ = "</" + m + "invoke>";
+    silent_ = {"<" + m + block + ">", "</" + m + block + ">"};
+    dsml_param_ = "<" + m + "parameter";
+    dsml_param_end_ = "</" + m + "parameter>";
+  }
   // NsXml: the namespace marker of the model's template.
   void set_namespace(const std::string& ns) {
     ns_ = ns;
@@ -184,8 +196,8 @@ class ToolParser {
     }
     if (fmt_ == Format::Dsml) {
       // body:  name="f">  then parameter elements
-      static const std::string kParam = "<\xef\xbd\x9c" "DSML\xef\xbd\x9c" "parameter";
-      static const std::string kParamEnd = "</\xef\xbd\x9c" "DSML\xef\xbd\x9c" "parameter>";
+      const std::string& kParam = dsml_param_;
+      const std::string& kParamEnd = dsml_param_end_;
       auto attr = [](const std::string& head, const std::string& key, std::string* val) {
         const size_t a = head.find(key + "=\"");
         if (a == std::string::npos) return false;
@@ -196,6 +208,8 @@ class ToolParser {
       };
       const size_t gt = body.find('>');
       if (gt == std::string::npos || !attr(body.substr(0, gt), "name", &e.name) || e.name.empty()) return false;
+      const size_t nsep = e.name.rfind("::");
+      if (nsep != std::string::npos && nsep + 2 < e.name.size()) e.name = e.name.substr(nsep + 2);   // "namespace::name"
       json::Value args = json::Value::object();
       size_t p = body.find(kParam, gt);
       while (p != std::string::npos) {
@@ -361,6 +375,8 @@ class ToolParser {
   }
 
   Format fmt_;
+  std::string dsml_param_ = "<\xef\xbd\x9c" "DSML\xef\xbd\x9c" "parameter";
+  std::string dsml_param_end_ = "</\xef\xbd\x9c" "DSML\xef\xbd\x9c" "parameter>";
   std::string ns_;
   json::Value tools_;
   std::string id_prefix_;

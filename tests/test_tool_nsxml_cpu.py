@@ -75,3 +75,25 @@ def test_malformed_blocks_come_back_as_content_and_ids_count_up():
     ev = q.feed(b'@@<tool_call>@@<invoke name="g">@@<v>7@@</v>@@</invoke>@@</tool_call>') + q.finish()
     assert [(e[3], e[4]) for e in ev if e[0] == "tool_call"] == [("g", '{"v":7}')] or \
         [(e[3], json.loads(e[4])) for e in ev if e[0] == "tool_call"] == [("g", {"v": 7})]
+
+
+def test_dsml_spaced_dialect_and_namespaced_names():
+    M = "｜DSML｜"
+    text = (f"Checking.\n\n<{M} calls>\n<{M} invoke name=\"weather::get_forecast\">\n"
+            f"<{M} parameter name=\"city\" string=\"true\">Paris</{M} parameter>\n"
+            f"<{M} parameter name=\"days\" string=\"false\">3</{M} parameter>\n</{M} invoke>\n</{M} calls>")
+    for step in (1, 5, 4096):
+        p = rt.ToolParser(rt.ToolFormat.Dsml, "c")
+        p.set_dsml_spaced(True)
+        ev, data = [], text.encode()
+        for i in range(0, len(data), step):
+            ev += p.feed(data[i:i + step])
+        ev += p.finish()
+        calls = [(e[3], json.loads(e[4])) for e in ev if e[0] == "tool_call"]
+        content = b"".join(e[1] for e in ev if e[0] == "content").decode()
+        assert calls == [("get_forecast", {"city": "Paris", "days": 3})], step
+        assert content == "Checking.", (step, content)
+    # the unspaced dialect does not take the spaced tags for calls
+    p = rt.ToolParser(rt.ToolFormat.Dsml, "c")
+    ev = p.feed(text.encode()) + p.finish()
+    assert not [e for e in ev if e[0] == "tool_call"]
