@@ -57,18 +57,24 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=4096)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--server-log", default="trace_server.log")
+    ap.add_argument("--mixed-pass", action="store_true", help="start the server with mixed reader + decoder passes")
+    ap.add_argument("--prefill-budget-busy", type=int, default=0)
     ap.add_argument("--startup-s", type=float, default=600.0)
     ap.add_argument("--request-timeout-s", type=float, default=900.0)
     a = ap.parse_args(argv)
     cmd = [sys.executable, "-m", "dgpp_b200.serve.app", "--model", a.model, "--slots", str(a.slots), "--port", str(a.port),
            "--max-context", str(a.max_context), "--mtp-depth", str(a.mtp_depth), "--layers", str(a.layers)]
+    if a.mixed_pass:
+        cmd.append("--mixed-pass")
+    if a.prefill_budget_busy:
+        cmd += ["--prefill-budget-busy", str(a.prefill_budget_busy)]
     proc, url, up_s = _start(cmd, a.server_log, a.startup_s)
     lo, hi = (int(x) for x in a.suffix_tokens.split(","))
     conc = [int(x) for x in a.concurrency.split(",")]
     reqs = [int(x) for x in a.requests.split(",")]
     reqs = reqs * len(conc) if len(reqs) == 1 else reqs
     assert len(reqs) == len(conc), "--requests: one count, or one per concurrency"
-    out = {"model": a.model, "mtp_depth": a.mtp_depth, "slots": a.slots, "startup_s": round(up_s, 1),
+    out = {"model": a.model, "mixed_pass": bool(a.mixed_pass), "mtp_depth": a.mtp_depth, "slots": a.slots, "startup_s": round(up_s, 1),
            "trace": {"requests": reqs, "prefixes": a.prefixes, "prefix_tokens": a.prefix_tokens, "shared": a.shared,
                      "suffix_tokens": [lo, hi], "max_tokens": a.max_tokens, "vocab": a.vocab}, "runs": []}
     try:

@@ -542,6 +542,10 @@ def main(argv=None) -> int:
                     help="hybrid models: draft this many tokens per step with the MTP head and verify them in the same pass")
     ap.add_argument("--layers", type=int, default=48, help="--model hybrid: layer count (fewer than 48 is a smoke run)")
     ap.add_argument("--config", default="", help="deployment JSON (see dgpp_b200.cli resolve); overrides the flags above")
+    ap.add_argument("--mixed-pass", action="store_true",
+                    help="a reader's prefill chunk rides in the pass of the decode step (engines with a mixed pass)")
+    ap.add_argument("--prefill-budget-busy", type=int, default=0,
+                    help="prompt tokens per tick while requests are decoding (0: the scheduler's default)")
     ap.add_argument("--vision", action="store_true",
                     help="tiny model only: attach a random-init vision tower so that chat messages accept image_url parts")
     args = ap.parse_args(argv)
@@ -637,6 +641,11 @@ def main(argv=None) -> int:
     vision = None
     if args.vision and args.model == "tiny":
         vision = tiny_vision_frontend(cfg, "cuda" if torch.cuda.is_available() else "cpu")
+    if args.mixed_pass or args.prefill_budget_busy:
+        sched_config = sched_config or rt.SchedulerConfig()
+        sched_config.mixed_pass = bool(args.mixed_pass)
+        if args.prefill_budget_busy:
+            sched_config.prefill_budget_busy = args.prefill_budget_busy
     srv = Server(eng, tok, model_name=f"dgpp-b200-{args.model}", host=args.host, port=args.port, eos_ids=[257],
                  vision=vision, sched_config=sched_config)
     print(f"listening on http://{args.host}:{srv.start()}", flush=True)
