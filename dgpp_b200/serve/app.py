@@ -48,6 +48,10 @@ class _Live:
     t_first: float = 0.0
 
 
+TOOL_FORMATS = {"json": rt.ToolFormat.JsonTags, "arg-tags": rt.ToolFormat.ArgTags, "dsml": rt.ToolFormat.Dsml,
+                "dsml-spaced": rt.ToolFormat.Dsml, "ns-xml": rt.ToolFormat.NsXml}
+
+
 class Metrics:
     def __init__(self):
         self.c: Dict[str, float] = {"requests_total": 0, "requests_failed": 0, "prompt_tokens_total": 0,
@@ -83,6 +87,10 @@ class Server:
         self.model_name = model_name
         self.eos_ids = eos_ids or []
         self.default_max_tokens = default_max_tokens
+        # a name of TOOL_FORMATS or an rt.ToolFormat; "dsml-spaced" is the DSML dialect whose marker is followed by a space
+        self.dsml_spaced = tool_format == "dsml-spaced"
+        if isinstance(tool_format, str):
+            tool_format = TOOL_FORMATS[tool_format]
         self.tool_format = tool_format or rt.ToolFormat.JsonTags
         self.constrain_tools = constrain_tools
         self.throughput_log_s = 10.0
@@ -350,6 +358,8 @@ class Server:
                 self.live[rid].tool_parser = rt.ToolParser(self.tool_format, f"call_{uuid.uuid4().hex[:12]}_")
                 if self.tool_format == rt.ToolFormat.NsXml:          # value types come from the tools' parameter schemas
                     self.live[rid].tool_parser.set_tools(r["tools_json"])
+                if self.dsml_spaced:
+                    self.live[rid].tool_parser.set_dsml_spaced(True)
             kw = dict(eos_ids=[] if r["ignore_eos"] else self.eos_ids, ignore_eos=r["ignore_eos"],
                       prefix_cache=r["prefix_cache"], cache_key=r["prompt_cache_key"])
             if self.world is not None:
@@ -542,6 +552,8 @@ def main(argv=None) -> int:
                     help="hybrid models: draft this many tokens per step with the MTP head and verify them in the same pass")
     ap.add_argument("--layers", type=int, default=48, help="--model hybrid: layer count (fewer than 48 is a smoke run)")
     ap.add_argument("--config", default="", help="deployment JSON (see dgpp_b200.cli resolve); overrides the flags above")
+    ap.add_argument("--tool-format", default="json", choices=sorted(TOOL_FORMATS),
+                    help="how the model writes tool calls (the streaming parser's format)")
     ap.add_argument("--mixed-pass", action="store_true",
                     help="a reader's prefill chunk rides in the pass of the decode step (engines with a mixed pass)")
     ap.add_argument("--prefill-budget-busy", type=int, default=0,
@@ -647,7 +659,7 @@ def main(argv=None) -> int:
         if args.prefill_budget_busy:
             sched_config.prefill_budget_busy = args.prefill_budget_busy
     srv = Server(eng, tok, model_name=f"dgpp-b200-{args.model}", host=args.host, port=args.port, eos_ids=[257],
-                 vision=vision, sched_config=sched_config)
+                 vision=vision, sched_config=sched_config, tool_format=args.tool_format)
     print(f"listening on http://{args.host}:{srv.start()}", flush=True)
     try:
         while True:
