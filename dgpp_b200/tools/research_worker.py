@@ -140,6 +140,23 @@ class ResearchWorld:
             return getattr(self, op)(req)
 
 
+class FamilyWorld(ResearchWorld):
+    """The same operations over a model of the smaller families (anything with `forward_reference(tokens)` and
+    `cfg.vocab`): every call recomputes the whole prompt, there is no activation capture and no adapter."""
+
+    OPS = ("info", "logits", "generate", "likelihood")
+
+    def _forward(self, toks, start: int = 0, kv=None, capture=None):
+        prev = kv if kv is not None else toks[:0]
+        full = torch.cat([prev, toks]) if start else toks
+        return self.model.forward_reference(full), full
+
+    def info(self, req: dict) -> dict:
+        c = self.model.cfg
+        return {"family": type(self.model).__name__, "layers": c.layers, "hidden": c.hidden, "vocab": c.vocab,
+                "adapter": False, "device": str(self.model.embed.device)}
+
+
 class _Handler(socketserver.StreamRequestHandler):
     def handle(self):
         srv = self.server
@@ -195,10 +212,17 @@ def request(port: int, obj: dict, host: str = "127.0.0.1", timeout: float = 120.
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(description="research socket worker over a dense checkpoint (loopback only)")
     ap.add_argument("--model-dir", default="", help="dense safetensors checkpoint; empty: the tiny random-init model")
+    ap.add_argument("--family-dir", default="", help="a native family checkpoint (loaders.family_io) instead")
     ap.add_argument("--port", type=int, default=8791)
     ap.add_argument("--token", default="")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     a = ap.parse_args(argv)
+    if a.family_dir:
+        from ..loaders.family_io import load_family
+        srv = ResearchServer(FamilyWorld(load_family(a.family_dir, a.device)), a.port, a.token)
+        print(json.dumps({"research_worker": "listening", "port": srv.port}), flush=True)
+        srv.serve_forever()
+        return 0
     if a.model_dir:
         from ..loaders.checkpoint import load_dense
         model = load_dense(a.model_dir, device=a.device)

@@ -83,3 +83,27 @@ def test_adapter_install_and_errors(served, tmp_path):
     assert request(port, {"op": "info", "token": "s3"})["ok"]
     with pytest.raises(ValueError):
         ResearchServer(ResearchWorld(model), host="0.0.0.0")
+
+
+def test_family_models_answer_logits_generation_and_likelihood():
+    from dgpp_b200.models.mimo import MimoConfig, MimoModel
+    from dgpp_b200.tools.research_worker import FamilyWorld
+
+    m = MimoModel.random_init(MimoConfig(layers=2, hidden=256, q_heads=4, kv_heads=1, swa_kv_heads=2, head_dim=64, rotary_dim=32,
+                                         window=8, ffn=512, vocab=512, swa_layers=[True, False]), "cpu", seed=1)
+    w = FamilyWorld(m)
+    toks = torch.randint(0, 512, (10,), generator=torch.Generator().manual_seed(3)).tolist()
+    want = m.forward_reference(torch.tensor(toks))
+    r = w.handle({"op": "logits", "tokens": toks, "top_k": 2})
+    assert r["top"][0]["id"] == int(torch.argsort(-want[-1].float(), stable=True)[0])
+    g = w.handle({"op": "generate", "tokens": toks, "max_new": 3})["tokens"]
+    cur = list(toks)
+    for t in g:
+        assert t == int(torch.argsort(-m.forward_reference(torch.tensor(cur))[-1].float(), stable=True)[0])
+        cur.append(t)
+    lk = w.handle({"op": "likelihood", "tokens": toks, "start": 4})
+    lp = torch.log_softmax(want[:-1].float(), -1)
+    assert abs(lk["logprob"] - sum(float(lp[i - 1, toks[i]]) for i in range(4, 10))) < 1e-4
+    assert w.handle({"op": "info"})["family"] == "MimoModel"
+    with pytest.raises(ValueError, match="unknown op"):
+        w.handle({"op": "capture", "tokens": toks, "layers": [0]})
