@@ -182,3 +182,52 @@ def runner_for(model: Any, max_rows: int, slots: int, max_seq_len: int, device="
     cls = {"glm_flash": GlmFlashRunner, "dory": DoryRunner, "flash_next": FlashNextRunner, "minimax": MinimaxRunner,
            "mimo": MimoRunner}[_family_of(model)]
     return cls(model, max_rows, slots, max_seq_len, device)
+
+
+def tiny_model(family: str, device="cpu", seed: int = 0, vocab: int = 4096) -> Any:
+    """A small random-init model of `family` (the shapes the server's `--model <family>-tiny` choices use)."""
+    from ..models.moe import MoEConfig
+
+    cfg_cls, model_cls = _registry()[family]
+    moe = MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512, shared_ffn=512)
+    if family == "glm_flash":
+        cfg = cfg_cls(layers=4, hidden=512, vocab=vocab, mla_every=2, k_heads=2, v_heads=4, heads=8, q_lora=256, kv_lora=128,
+                      nope=64, rope=32, v_dim=64, ffn=1024, moe=moe)
+    elif family == "dory":
+        cfg = cfg_cls(vocab=vocab)
+    elif family == "flash_next":
+        cfg = cfg_cls(vocab=vocab, moe=moe)
+    elif family == "minimax":
+        cfg = cfg_cls(vocab=vocab, moe_layers=[False, True, True, True],
+                      moe=MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512, shared_ffn=512, routed_scaling=2.0,
+                                    swiglu_limit=7.0, swiglu_alpha=1.702))
+    else:
+        cfg = cfg_cls(vocab=vocab, moe=MoEConfig(hidden=512, experts=16, top_k=2, moe_ffn=512))
+    return model_cls.random_init(cfg, device, seed=seed)
+
+
+def main(argv=None) -> int:
+    """Writes a small random-init checkpoint of one family: a fixture for the load / forward checks and for
+    `python -m dgpp_b200.serve.app --family-dir DIR`."""
+    import argparse
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--family", required=True, choices=sorted(_registry()))
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--vocab", type=int, default=4096)
+    ap.add_argument("--check", action="store_true", help="load the directory back and compare the oracle logits of a short prompt")
+    a = ap.parse_args(argv)
+    model = tiny_model(a.family, "cpu", a.seed, a.vocab)
+    save_family(model, a.out)
+    report = {"family": a.family, "out": a.out, "tensors": sum(1 for _ in _walk(model))}
+    if a.check:
+        back = load_family(a.out, "cpu")
+        t = torch.arange(3, 19) % a.vocab
+        report["round_trip_equal"] = bool(torch.equal(back.forward_reference(t), model.forward_reference(t)))
+    print(json.dumps(report))
+    return 0 if report.get("round_trip_equal", True) else 1
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -78,3 +78,12 @@ def test_refusals_name_the_tensor(tmp_path):
     open(os.path.join(bad, "config.json"), "w").write(json.dumps(cfg))
     with pytest.raises(ValueError, match="native family"):
         load_family(bad, "cpu")
+
+
+def test_fixture_writer_cli(tmp_path, capsys):
+    from dgpp_b200.loaders.family_io import main
+
+    assert main(["--family", "dory", "--out", str(tmp_path / "fx"), "--vocab", "512", "--check"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["family"] == "dory" and rep["round_trip_equal"] is True and rep["tensors"] > 10
+    assert os.path.exists(tmp_path / "fx" / "model.safetensors")
