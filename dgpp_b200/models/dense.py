@@ -1,7 +1,7 @@
 """Dense GQA decoder (Llama/Qwen-style): RMSNorm -> fused QKV -> RoPE -> GQA attention -> o_proj ->
 RMSNorm -> SwiGLU MLP, with quantised linear layers in checkpoint layout.
 
-Tensor parallel sharding (reference contract: DESIGN.md:344-400 in the reference tree -- heads sharded,
+Tensor parallel sharding (reference contract: lines 344-400 of the reference tree's top-level design document -- heads sharded,
 q/kv/gate-up column-split, o_proj/down row-split, hidden replicated at block boundaries):
 rank r owns q heads [r*hq/W, (r+1)*hq/W), the matching kv heads, and rows [r*I/W, (r+1)*I/W) of the
 MLP intermediate; the two row-split projections are followed by an all-reduce.

@@ -7,7 +7,7 @@ layers, grouped NVFP4 expert GEMMs for the MoE blocks.  Prefill chunks of one re
 tokens share one code path.
 MTP: depth-1 head  h' = block( W_p [norm(h_t) ; norm(embed(x_{t+1}))] ),  logits = lm_head(norm(h')) predicts
 x_{t+2}; its proposals are verified by the target model in one pass (`rt.spec_judge`).
-(reference counterparts: src/models/qwen/model35.cpp run_rows:2066-2399, glm/mtp.cpp; the reference tree's own DESIGN.md:1934-2123.)
+(reference counterparts: src/models/qwen/model35.cpp run_rows:2066-2399, glm/mtp.cpp; lines 1934-2123 of the reference tree's top-level design document.)
 """
 from __future__ import annotations
 

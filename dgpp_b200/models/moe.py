@@ -8,7 +8,7 @@ routed SwiGLU experts with NVFP4 weights stacked into one matrix, optional share
   slots, ONE grouped GEMM for the down projections, ordered combine.  Every token is a column of every active
   expert's MMA (the MMA N minimum is 16 anyway); the combine picks each token's experts.  Larger batches fall back
   to per-expert GEMMs over gathered rows.
-(numerics: src/kernels/glm_moe.cu:86-331,1447 and DESIGN.md:1293-1413, both in the reference tree.)
+(numerics: src/kernels/glm_moe.cu:86-331,1447 and the reference tree's own design notes (lines 1293-1413 of its top-level design document).)
 """
 from __future__ import annotations
 
