@@ -12,7 +12,7 @@
 //   top_p   : keep the shortest prefix whose mass reaches top_p * total; total = sum of that prefix
 //   draw    : walk the kept prefix until u * total < cumulative sum
 // All sums run in canonical order with plain float adds; exp is det::exp.
-// (behavioural spec: src/sample/sampler.hpp and DESIGN.md:2125-2296, both in the reference tree.)
+// (behavioural spec: src/sample/sampler.hpp and lines 2125-2296 of its top-level design document, both in the reference tree.)
 #pragma once
 #include <stdint.h>
 

@@ -15,7 +15,7 @@
 // distribution when temperature == 0.
 // Sharded vocabularies: each rank reports its top candidates and a slice log-sum-exp computed over fixed
 // 256-wide chunks and folded pairwise; slices are merged in ascending rank order (merge_logsumexp).
-// (behavioural spec: src/sample/sampler.hpp:378-1422 and DESIGN.md:2125-2296, both in the reference tree.)
+// (behavioural spec: src/sample/sampler.hpp:378-1422 and lines 2125-2296 of its top-level design document, both in the reference tree.)
 #pragma once
 #include <algorithm>
 #include <cmath>

@@ -12,7 +12,7 @@
 //               discarded (paged KV: the length is cut; recurrent layers: restore the snapshot taken before the
 //               pass and replay the accepted rows)
 // The schedule shrinks the draft when acceptance is poor and widens it when drafts keep landing.
-// (reference counterparts: src/engine/speculative.hpp, verify_schedule.hpp, lookup_draft.hpp; the reference tree's own DESIGN.md:1934-2123.)
+// (reference counterparts: src/engine/speculative.hpp, verify_schedule.hpp, lookup_draft.hpp; lines 1934-2123 of its top-level design document.)
 #pragma once
 #include <algorithm>
 #include <cmath>
